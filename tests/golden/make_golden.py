@@ -1,0 +1,49 @@
+"""Extracts the reference's golden decoder vectors for the three encodings on this path.
+
+Run once where the reference tree is mounted:
+
+    python tests/golden/make_golden.py /root/reference
+
+It reads inference/src/quant/fixtures/{k-affine,k-signed,simple}.json (the rows the
+reference's own tests require an exact match on, inference/src/quant/decode.zig:587-592),
+keeps the rows whose encoding is Q8_0 (8), Q4_K (12) or Q6_K (14), and writes
+tests/golden/quant_rows.json: packed bytes as hex and expected values as the hex of
+their little-endian float32 bits, so that nothing is lost to decimal printing.
+The reference tree is not needed to run the tests, only to regenerate this file.
+"""
+import json
+import os
+import struct
+import sys
+
+KEEP = {8: "Q8_0", 12: "Q4_K", 14: "Q6_K"}
+FILES = ["simple.json", "k-affine.json", "k-signed.json"]
+
+
+def main(root: str) -> None:
+    rows = []
+    for name in FILES:
+        with open(os.path.join(root, "inference/src/quant/fixtures", name)) as f:
+            doc = json.load(f)
+        for r in doc["rows"]:
+            if r["encoding"] not in KEEP:
+                continue
+            values = b"".join(struct.pack("<f", v) for v in r["values"])
+            # the JSON prints shortest round-trip decimals of float32 values: check that
+            assert all(struct.unpack("<f", struct.pack("<f", v))[0] == v for v in r["values"])
+            rows.append({
+                "source": f"inference/src/quant/fixtures/{name}",
+                "revision": doc["revision"],
+                "encoding": r["encoding"],
+                "name": KEEP[r["encoding"]],
+                "bytes_hex": bytes(r["bytes"]).hex(),
+                "values_f32le_hex": values.hex(),
+            })
+    out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "quant_rows.json")
+    with open(out, "w") as f:
+        json.dump({"rows": rows}, f, indent=1)
+    print(f"wrote {out}: {[(r['name'], len(r['bytes_hex']) // 2) for r in rows]}")
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
