@@ -1,0 +1,242 @@
+/*
+ * nuclis_cuda.h: C ABI of the B200 (sm_100a) backend for nuclis's
+ * quantized-weight matmul path.
+ *
+ * The engine's Metal backend reaches its GPU through 16 generic `nu_metal_*`
+ * functions (inference/src/backends/metal/root.zig:28-44, implemented in
+ * inference/src/backends/metal/bridge.m) that compile shader source at start
+ * and record untyped dispatches. CUDA kernels are compiled ahead of time, so
+ * this ABI keeps the bridge's lifecycle functions (create, buffers,
+ * begin/commit/discard, GPU seconds, profile) and replaces the untyped
+ * `nu_metal_dispatch` with one typed entry point per operator of
+ * `metal.Backend` (inference/src/backends/metal/ops/{matvec,matmul,experts,
+ * rowwise}.zig). Each declaration cites the reference interface it replaces.
+ *
+ * Conventions, as in bridge.m:49-51 and root.zig:7-10:
+ *   - `int` results: 0 is success, any other value one of `nu_status`.
+ *   - An opaque handle per device context. A handle is NOT thread-safe: one
+ *     thread owns it, one recording is open at a time.
+ *   - Every shape or length violation is reported BEFORE anything is recorded;
+ *     a recording that met an error is dropped with `nu_cuda_discard`.
+ *   - `nu_cuda_commit` submits and waits: afterwards every recorded write is
+ *     visible to `nu_cuda_buffer_download`.
+ *   - Buffers are named by `(id, offset, len)` triples (`Buffer` of
+ *     root.zig:62-86); ids are never reused.
+ *   - Matrices are row-major GGUF rows, `columns` contiguous and block
+ *     quantized (`cpu.Matrix`, inference/src/backends/cpu/root.zig:28-36).
+ *
+ * Plain C: pointers, sizes and fixed-width integers only.
+ */
+#ifndef NUCLIS_CUDA_H
+#define NUCLIS_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Error set: quant.Error (inference/src/quant/decode.zig:22), cpu.Error
+ * (backends/cpu/root.zig:38) and the Metal backend's own errors
+ * (backends/metal/root.zig), as integers. */
+typedef enum nu_status {
+    NU_OK = 0,
+    NU_ERR_UNSUPPORTED_ENCODING = 1, /* error.UnsupportedTensorEncoding */
+    NU_ERR_INVALID_ROW_LENGTH = 2,   /* error.InvalidRowLength */
+    NU_ERR_INVALID_BYTE_LENGTH = 3,  /* error.InvalidByteLength */
+    NU_ERR_INVALID_SHAPE = 4,        /* error.InvalidShape */
+    NU_ERR_MERGE_DECLINED = 5,       /* error.MergeDeclined (ops/matvec.zig:245-257) */
+    NU_ERR_NOT_RECORDING = 6,        /* error.MetalNotRecording */
+    NU_ERR_ALREADY_RECORDING = 7,    /* error.MetalAlreadyRecording */
+    NU_ERR_BUFFER = 8,               /* error.MetalBufferFailed */
+    NU_ERR_EXECUTION = 9,            /* error.MetalExecutionFailed */
+    NU_ERR_INIT = 10,                /* error.MetalInitializationFailed */
+    NU_ERR_COMM = 11,                /* collective set-up or call failed (no reference analogue) */
+    NU_ERR_TOO_LARGE = 12            /* beyond a fixed capacity of this library */
+} nu_status;
+
+/* GGML encoding ids served (inference/src/tensor/encoding.zig:29-56). */
+enum { NU_F32 = 0, NU_F16 = 1, NU_Q8_0 = 8, NU_Q4_K = 12, NU_Q6_K = 14, NU_BF16 = 30 };
+
+/* `Buffer` of backends/metal/root.zig:62-86 without the host pointer: device
+ * memory is not host-addressable here; use upload/download. */
+typedef struct nu_buffer {
+    uint32_t id;
+    uint32_t reserved;
+    uint64_t offset; /* bytes from the start of buffer `id` */
+    uint64_t len;    /* bytes this view may touch */
+} nu_buffer;
+
+/* `cpu.Matrix` (backends/cpu/root.zig:31-36): `bytes` is the byte length of
+ * the whole matrix; the row stride is bytes / rows. */
+typedef struct nu_matrix {
+    uint32_t encoding;
+    uint32_t reserved;
+    uint64_t rows;
+    uint64_t columns;
+    uint64_t bytes;
+} nu_matrix;
+
+/* `cpu.ExpertMatrix` (backends/cpu/experts.zig:20-43): experts contiguous. */
+typedef struct nu_expert_matrix {
+    uint32_t encoding;
+    uint32_t reserved;
+    uint64_t experts;
+    uint64_t rows;
+    uint64_t columns;
+    uint64_t bytes;
+} nu_expert_matrix;
+
+/* `Segment` and `SegmentMode` of ops/matvec.zig:223-225. */
+typedef struct nu_segment {
+    nu_buffer weights;
+    nu_matrix matrix;
+    nu_buffer output;
+} nu_segment;
+enum { NU_SEGMENTS_PLAIN = 0, NU_SEGMENTS_SILU_MUL_PAIR = 1, NU_SEGMENTS_GELU_MUL_PAIR = 2 };
+
+/* `CombineShape` of ops/experts.zig:80. */
+typedef struct nu_combine_shape {
+    uint64_t columns, slots, rows, experts, in_stride, out_stride;
+} nu_combine_shape;
+
+typedef struct nu_cuda nu_cuda;
+
+/* ---- lifecycle (bridge.m nu_metal_create / nu_metal_destroy) ------------- */
+
+/* Opens CUDA device `device`, creates the stream all work runs on and the
+ * library's fixed scratch. NULL on failure with a message in `err`. */
+nu_cuda *nu_cuda_create(int device, char *err, size_t err_cap);
+void nu_cuda_destroy(nu_cuda *h);
+/* Message of the last failed call on this handle ("" if none). */
+const char *nu_cuda_last_error(const nu_cuda *h);
+/* Name of a status code, e.g. "InvalidShape". */
+const char *nu_cuda_status_name(int status);
+/* `Backend.generic_only` (root.zig:99-104): force the plain decode-and-FMA
+ * kernels even where a specialized kernel applies. */
+int nu_cuda_set_generic_only(nu_cuda *h, int on);
+
+/* ---- buffers (nu_metal_buffer_create / wrap / contents / release) -------- */
+
+/* Zero-filled device buffer of `len` bytes owned by the handle. */
+int nu_cuda_buffer_create(nu_cuda *h, size_t len, uint32_t *id);
+/* Copies host bytes into / out of a buffer; refused while recording. These
+ * replace nu_metal_buffer_contents: device memory has no host pointer. */
+int nu_cuda_buffer_upload(nu_cuda *h, uint32_t id, size_t offset, const void *src, size_t len);
+int nu_cuda_buffer_download(nu_cuda *h, uint32_t id, size_t offset, void *dst, size_t len);
+/* `Backend.wrap` (root.zig:217-230): the first wrap of a host range uploads it
+ * once; later wraps of the same start address return the same id and must ask
+ * for the same length. The host range is only read during the first call. */
+int nu_cuda_buffer_wrap(nu_cuda *h, const void *bytes, size_t len, uint32_t *id);
+/* `Backend.unwrap` / `release` (root.zig:206-242): refused while recording. */
+int nu_cuda_buffer_unwrap(nu_cuda *h, const void *bytes);
+int nu_cuda_buffer_release(nu_cuda *h, uint32_t id);
+/* Device address of a buffer, for callers that fill it with their own CUDA
+ * code (tests, benchmarks). NULL for an unknown id. */
+void *nu_cuda_buffer_device_ptr(nu_cuda *h, uint32_t id);
+/* `Backend.created_bytes` (root.zig:113-116). */
+uint64_t nu_cuda_created_bytes(const nu_cuda *h);
+
+/* ---- recording (nu_metal_begin / commit / discard / gpu_seconds) --------- */
+
+/* Opens a recording: operator calls between begin and commit are captured
+ * into a CUDA graph, not run. */
+int nu_cuda_begin(nu_cuda *h);
+/* Instantiates the recorded graph, launches it and waits. */
+int nu_cuda_commit(nu_cuda *h);
+/* Drops the open recording; nothing of it runs. No-op when idle. */
+int nu_cuda_discard(nu_cuda *h);
+/* As commit, but keeps the instantiated graph for replay: a decode step
+ * records the same operators every token, so it is recorded once. */
+int nu_cuda_commit_retain(nu_cuda *h, uint32_t *graph);
+/* Replays a retained graph `count` times back to back and waits; when
+ * `elapsed_ms` is not NULL it receives the device time of the whole batch
+ * (CUDA events on the handle's stream). */
+int nu_cuda_graph_launch(nu_cuda *h, uint32_t graph, uint32_t count, float *elapsed_ms);
+int nu_cuda_graph_release(nu_cuda *h, uint32_t graph);
+/* Seconds of device time of everything committed so far (nu_metal_gpu_seconds). */
+double nu_cuda_gpu_seconds(const nu_cuda *h);
+/* Kernels recorded or launched by this handle so far. */
+uint64_t nu_cuda_launch_count(const nu_cuda *h);
+/* The CUDA stream (a `cudaStream_t`) of this handle, for callers that time
+ * with their own events. */
+void *nu_cuda_stream(nu_cuda *h);
+/* Per-operator timing (nu_metal_profile_enable / nu_metal_profile_read):
+ * once enabled, commit runs each recorded operator between its own pair of
+ * events; `nu_cuda_profile_read` returns how many durations (seconds, in
+ * recording order) the last commit produced and copies up to `cap` of them. */
+int nu_cuda_profile_enable(nu_cuda *h, uint32_t max_ops);
+uint32_t nu_cuda_profile_read(nu_cuda *h, double *seconds, uint32_t cap);
+
+/* ---- operators ----------------------------------------------------------- */
+
+/* `Backend.embed` (ops/rowwise.zig:15-25): decode row `token` of `matrix` to
+ * F32, bit-identical to the CPU decoder. `out_dtype` NU_F32 or NU_BF16 (round
+ * to nearest even of the F32 value; no reference analogue). */
+int nu_cuda_embed(nu_cuda *h, const nu_buffer *weights, const nu_matrix *matrix, uint32_t token,
+                  const nu_buffer *output, uint32_t out_dtype);
+
+/* `Backend.matvec` (ops/matvec.zig:32-34, 85-116): output[r] = sum_c W[r,c]*input[c]. */
+int nu_cuda_matvec(nu_cuda *h, const nu_buffer *weights, const nu_matrix *matrix,
+                   const nu_buffer *input, const nu_buffer *output);
+
+/* `Backend.matvecRows` (ops/matvec.zig:149-165): 2..8 token rows, strides in floats. */
+int nu_cuda_matvec_rows(nu_cuda *h, const nu_buffer *weights, const nu_matrix *matrix,
+                        const nu_buffer *input, size_t in_stride,
+                        const nu_buffer *output, size_t out_stride, size_t tokens);
+
+/* `Backend.matmul` (ops/matmul.zig:62-108): out[t][r] = sum_c W[r,c]*in[t,c].
+ * `in_dtype` NU_F32 (the reference's contract; strides in elements) or
+ * NU_BF16 (prefill activations already rounded; no reference analogue).
+ * Buffers hold `matmul_padded(tokens)` rows as in ops/matmul.zig:29-31. */
+int nu_cuda_matmul(nu_cuda *h, const nu_buffer *weights, const nu_matrix *matrix,
+                   const nu_buffer *input, uint32_t in_dtype, size_t in_stride,
+                   const nu_buffer *output, size_t out_stride, size_t tokens);
+size_t nu_cuda_matmul_padded(size_t tokens);
+
+/* `Backend.matvecSegments` (ops/matvec.zig:245-343): up to four projections of
+ * one input in one launch; the pair modes write act(seg[0]) * seg[1] only. */
+int nu_cuda_matvec_segments(nu_cuda *h, const nu_segment *segments, size_t count,
+                            const nu_buffer *input, uint32_t mode);
+
+/* `Backend.siluMul`, `Backend.geluMul` (ops/rowwise.zig:209, 230): gate[i] = act(gate[i]) * up[i]. */
+int nu_cuda_silu_mul(nu_cuda *h, const nu_buffer *gate, const nu_buffer *up, size_t count);
+int nu_cuda_gelu_mul(nu_cuda *h, const nu_buffer *gate, const nu_buffer *up, size_t count);
+
+/* `Backend.route` (ops/experts.zig:29-34). */
+int nu_cuda_route(nu_cuda *h, const nu_buffer *logits, size_t experts, size_t k, size_t rows, size_t in_stride,
+                  const nu_buffer *indices, const nu_buffer *weights);
+
+/* `Backend.matvecExperts` / `matvecExpertsGrouped` (ops/experts.zig:44-77). */
+int nu_cuda_matvec_experts(nu_cuda *h, const nu_buffer *weights, const nu_expert_matrix *tensor,
+                           const nu_buffer *indices, size_t slots,
+                           const nu_buffer *input, size_t in_stride, size_t in_group,
+                           const nu_buffer *output, size_t out_stride);
+
+/* `Backend.geluMulRows` (ops/experts.zig:106-117). */
+int nu_cuda_gelu_mul_rows(nu_cuda *h, const nu_buffer *gate, const nu_buffer *up, const nu_buffer *output,
+                          size_t width, size_t rows, size_t gate_stride, size_t up_stride, size_t out_stride);
+
+/* `Backend.combineExperts` (ops/experts.zig:79-92); `scales` may be NULL. */
+int nu_cuda_combine_experts(nu_cuda *h, const nu_buffer *values, const nu_buffer *weights, const nu_buffer *indices,
+                            const nu_buffer *scales, const nu_buffer *output, const nu_combine_shape *shape);
+
+/* ---- tensor-parallel collective (no reference analogue: the reference is
+ * single-device) ---------------------------------------------------------- */
+
+/* Size in bytes of the opaque rendezvous id below. */
+enum { NU_COMM_ID_BYTES = 128 };
+/* Rank 0 fills `id`; the caller carries it to the other ranks by any means. */
+int nu_cuda_comm_unique_id(uint8_t id[NU_COMM_ID_BYTES]);
+/* Joins this handle to a group of `ranks` handles (one per GPU). Collective. */
+int nu_cuda_comm_init(nu_cuda *h, const uint8_t id[NU_COMM_ID_BYTES], int ranks, int rank);
+/* In-place sum over the group of `count` floats at `buffer`; recorded like an
+ * operator (NCCL allreduce over NVLink on the handle's stream). */
+int nu_cuda_allreduce_sum_f32(nu_cuda *h, const nu_buffer *buffer, size_t count);
+int nu_cuda_comm_destroy(nu_cuda *h);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NUCLIS_CUDA_H */

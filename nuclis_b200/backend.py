@@ -1,0 +1,311 @@
+"""Python host side: the operator interface of the engine's ``metal.Backend``
+(inference/src/backends/metal/root.zig:88-330, ops/{matvec,matmul,experts,rowwise}.zig)
+over the C ABI of ``libnuclis_cuda.so``.
+
+Method names, argument order and error behaviour follow the reference so that
+a test written against ``metal.Backend`` reads the same here:
+
+    backend = Backend()                       # Backend.init
+    w = backend.wrap(weight_bytes)            # upload once, cached by address
+    x = backend.create(columns * 4)           # zero-filled
+    y = backend.create(rows * 4)
+    x.write(values)
+    backend.begin()
+    backend.matvec(w, Matrix(Q4_K, rows, columns, len(weight_bytes)), x, y)
+    backend.commit()                          # submits and waits
+    out = y.floats()
+
+Every failed call raises ``NuclisError`` whose ``name`` is the reference's
+error name; shape errors are raised before anything is recorded.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from enum import IntEnum
+
+import numpy as np
+
+from . import _lib
+from .errors import NuclisError
+
+
+@dataclass(frozen=True)
+class Matrix:
+    """``cpu.Matrix`` (inference/src/backends/cpu/root.zig:31-36); ``bytes`` is the byte length."""
+    encoding: int
+    rows: int
+    columns: int
+    bytes: int
+
+    def _c(self) -> _lib.CMatrix:
+        return _lib.CMatrix(self.encoding, 0, self.rows, self.columns, self.bytes)
+
+
+@dataclass(frozen=True)
+class ExpertMatrix:
+    """``cpu.ExpertMatrix`` (inference/src/backends/cpu/experts.zig:20-43)."""
+    encoding: int
+    experts: int
+    rows: int
+    columns: int
+    bytes: int
+
+    def _c(self) -> _lib.CExpertMatrix:
+        return _lib.CExpertMatrix(self.encoding, 0, self.experts, self.rows, self.columns, self.bytes)
+
+
+class SegmentMode(IntEnum):
+    """``SegmentMode`` (ops/matvec.zig:224)."""
+    plain = 0
+    silu_mul_pair = 1
+    gelu_mul_pair = 2
+
+
+@dataclass(frozen=True)
+class CombineShape:
+    """``CombineShape`` (ops/experts.zig:80)."""
+    columns: int
+    slots: int
+    experts: int
+    in_stride: int
+    out_stride: int
+    rows: int = 1
+
+
+class Buffer:
+    """``Buffer`` (root.zig:62-86): a byte range of a device buffer; ``slice`` derives sub-ranges."""
+
+    def __init__(self, backend: "Backend", id: int, offset: int, len: int):
+        self.backend, self.id, self.offset, self.len = backend, id, offset, len
+
+    def slice(self, byte_offset: int, len: int) -> "Buffer":
+        assert byte_offset + len <= self.len
+        return Buffer(self.backend, self.id, self.offset + byte_offset, len)
+
+    def _c(self) -> _lib.CBuffer:
+        return _lib.CBuffer(self.id, 0, self.offset, self.len)
+
+    # Device memory has no host pointer: these replace `Buffer.host` / `floats()`.
+    def write(self, data) -> None:
+        a = np.ascontiguousarray(data)
+        raw = a.view(np.uint8).reshape(-1)
+        if raw.size > self.len:
+            raise NuclisError(4, "write: data longer than the view")
+        self.backend._check(self.backend._lib.nu_cuda_buffer_upload(self.backend._h, self.id, self.offset, raw.ctypes.data, raw.size))
+
+    def read(self, dtype=np.uint8, count: int | None = None) -> np.ndarray:
+        dtype = np.dtype(dtype)
+        n = self.len // dtype.itemsize if count is None else count
+        out = np.empty(n, dtype=dtype)
+        self.backend._check(self.backend._lib.nu_cuda_buffer_download(self.backend._h, self.id, self.offset, out.ctypes.data, out.nbytes))
+        return out
+
+    def floats(self) -> np.ndarray:
+        return self.read(np.float32)
+
+    @property
+    def device_ptr(self) -> int:
+        base = self.backend._lib.nu_cuda_buffer_device_ptr(self.backend._h, self.id)
+        return (base or 0) + self.offset
+
+
+@dataclass(frozen=True)
+class Segment:
+    """``Segment`` (ops/matvec.zig:223)."""
+    weights: Buffer
+    matrix: Matrix
+    output: Buffer
+
+
+class Backend:
+    """One CUDA device context. Not thread-safe: one thread owns it (root.zig:7-10)."""
+
+    matvec_rows_max = 8  # ops/matvec.zig:140-143
+    matmul_tile = 64     # ops/matmul.zig:19-21
+
+    def __init__(self, device: int = 0):
+        self._lib = _lib.load()
+        err = ctypes.create_string_buffer(512)
+        self._h = self._lib.nu_cuda_create(device, err, len(err))
+        if not self._h:
+            raise NuclisError(10, err.value.decode() or "nu_cuda_create failed")
+        self.device = device
+        self._keep = {}  # host arrays handed to wrap(), kept alive like the borrowed ranges of the reference
+
+    # ---- lifecycle ----
+    def deinit(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.nu_cuda_destroy(self._h)
+            self._h = None
+
+    close = deinit
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.deinit()
+
+    def __del__(self):
+        try:
+            self.deinit()
+        except Exception:
+            pass
+
+    def _check(self, status: int) -> None:
+        if status != 0:
+            raise NuclisError(status, self._lib.nu_cuda_last_error(self._h).decode())
+
+    @property
+    def generic_only(self) -> bool:
+        return self._generic_only if hasattr(self, "_generic_only") else False
+
+    @generic_only.setter
+    def generic_only(self, on: bool) -> None:
+        self._check(self._lib.nu_cuda_set_generic_only(self._h, int(bool(on))))
+        self._generic_only = bool(on)
+
+    # ---- buffers ----
+    def create(self, len: int) -> Buffer:
+        id = ctypes.c_uint32()
+        self._check(self._lib.nu_cuda_buffer_create(self._h, len, ctypes.byref(id)))
+        return Buffer(self, id.value, 0, len)
+
+    def release(self, buffer: Buffer) -> None:
+        if buffer.offset != 0:
+            raise NuclisError(4, "release: whole buffers only")
+        self._check(self._lib.nu_cuda_buffer_release(self._h, buffer.id))
+
+    def wrap(self, data: np.ndarray) -> Buffer:
+        """Uploads a host range once; later wraps of the same start address return the same buffer."""
+        a = np.ascontiguousarray(data)
+        raw = a.view(np.uint8).reshape(-1)
+        id = ctypes.c_uint32()
+        self._check(self._lib.nu_cuda_buffer_wrap(self._h, raw.ctypes.data, raw.size, ctypes.byref(id)))
+        self._keep[raw.ctypes.data] = raw
+        return Buffer(self, id.value, 0, raw.size)
+
+    def unwrap(self, data: np.ndarray) -> None:
+        raw = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+        self._check(self._lib.nu_cuda_buffer_unwrap(self._h, raw.ctypes.data))
+        self._keep.pop(raw.ctypes.data, None)
+
+    @property
+    def created_bytes(self) -> int:
+        return self._lib.nu_cuda_created_bytes(self._h)
+
+    # ---- recording ----
+    def begin(self) -> None:
+        self._check(self._lib.nu_cuda_begin(self._h))
+
+    def commit(self) -> None:
+        self._check(self._lib.nu_cuda_commit(self._h))
+
+    def discard(self) -> None:
+        self._check(self._lib.nu_cuda_discard(self._h))
+
+    def commit_retain(self) -> int:
+        g = ctypes.c_uint32()
+        self._check(self._lib.nu_cuda_commit_retain(self._h, ctypes.byref(g)))
+        return g.value
+
+    def graph_launch(self, graph: int, count: int = 1) -> float:
+        """Replays a retained recording ``count`` times; returns the device milliseconds of the batch."""
+        ms = ctypes.c_float()
+        self._check(self._lib.nu_cuda_graph_launch(self._h, graph, count, ctypes.byref(ms)))
+        return ms.value
+
+    def graph_release(self, graph: int) -> None:
+        self._check(self._lib.nu_cuda_graph_release(self._h, graph))
+
+    def gpu_seconds(self) -> float:
+        return self._lib.nu_cuda_gpu_seconds(self._h)
+
+    @property
+    def launch_count(self) -> int:
+        return self._lib.nu_cuda_launch_count(self._h)
+
+    @property
+    def stream(self) -> int:
+        return self._lib.nu_cuda_stream(self._h) or 0
+
+    def enable_profiling(self, max_ops: int) -> None:
+        self._check(self._lib.nu_cuda_profile_enable(self._h, max_ops))
+
+    def profile_read(self) -> np.ndarray:
+        n = self._lib.nu_cuda_profile_read(self._h, None, 0)
+        out = np.zeros(n, dtype=np.float64)
+        if n:
+            self._lib.nu_cuda_profile_read(self._h, out.ctypes.data_as(ctypes.POINTER(ctypes.c_double)), n)
+        return out
+
+    # ---- operators ----
+    def embed(self, weights: Buffer, matrix: Matrix, token: int, output: Buffer, out_dtype: int = 0) -> None:
+        self._check(self._lib.nu_cuda_embed(self._h, weights._c(), matrix._c(), token, output._c(), out_dtype))
+
+    def matvec(self, weights: Buffer, matrix: Matrix, input: Buffer, output: Buffer) -> None:
+        self._check(self._lib.nu_cuda_matvec(self._h, weights._c(), matrix._c(), input._c(), output._c()))
+
+    def matvec_rows(self, weights: Buffer, matrix: Matrix, input: Buffer, in_stride: int, output: Buffer, out_stride: int, tokens: int) -> None:
+        self._check(self._lib.nu_cuda_matvec_rows(self._h, weights._c(), matrix._c(), input._c(), in_stride, output._c(), out_stride, tokens))
+
+    def matmul(self, weights: Buffer, matrix: Matrix, input: Buffer, in_stride: int, output: Buffer, out_stride: int, tokens: int,
+               in_dtype: int = 0) -> None:
+        self._check(self._lib.nu_cuda_matmul(self._h, weights._c(), matrix._c(), input._c(), in_dtype, in_stride, output._c(), out_stride, tokens))
+
+    @staticmethod
+    def matmul_padded(tokens: int) -> int:
+        return (tokens + 63) // 64 * 64
+
+    def matvec_segments(self, segments: list[Segment], input: Buffer, mode: SegmentMode = SegmentMode.plain) -> None:
+        arr = (_lib.CSegment * max(len(segments), 1))()
+        for i, s in enumerate(segments):
+            arr[i] = _lib.CSegment(s.weights._c(), s.matrix._c(), s.output._c())
+        self._check(self._lib.nu_cuda_matvec_segments(self._h, arr, len(segments), input._c(), int(mode)))
+
+    def silu_mul(self, gate: Buffer, up: Buffer, count: int) -> None:
+        self._check(self._lib.nu_cuda_silu_mul(self._h, gate._c(), up._c(), count))
+
+    def gelu_mul(self, gate: Buffer, up: Buffer, count: int) -> None:
+        self._check(self._lib.nu_cuda_gelu_mul(self._h, gate._c(), up._c(), count))
+
+    def route(self, logits: Buffer, experts: int, k: int, rows: int, in_stride: int, indices: Buffer, weights: Buffer) -> None:
+        self._check(self._lib.nu_cuda_route(self._h, logits._c(), experts, k, rows, in_stride, indices._c(), weights._c()))
+
+    def matvec_experts(self, weights: Buffer, tensor: ExpertMatrix, indices: Buffer, slots: int, input: Buffer, in_stride: int,
+                       output: Buffer, out_stride: int) -> None:
+        self.matvec_experts_grouped(weights, tensor, indices, slots, input, in_stride, 1, output, out_stride)
+
+    def matvec_experts_grouped(self, weights: Buffer, tensor: ExpertMatrix, indices: Buffer, slots: int, input: Buffer, in_stride: int,
+                               in_group: int, output: Buffer, out_stride: int) -> None:
+        self._check(self._lib.nu_cuda_matvec_experts(self._h, weights._c(), tensor._c(), indices._c(), slots, input._c(), in_stride, in_group,
+                                                     output._c(), out_stride))
+
+    def gelu_mul_rows(self, gate: Buffer, up: Buffer, output: Buffer, width: int, rows: int, gate_stride: int, up_stride: int, out_stride: int) -> None:
+        self._check(self._lib.nu_cuda_gelu_mul_rows(self._h, gate._c(), up._c(), output._c(), width, rows, gate_stride, up_stride, out_stride))
+
+    def combine_experts(self, values: Buffer, weights: Buffer, indices: Buffer, scales: Buffer | None, output: Buffer, s: CombineShape) -> None:
+        shape = _lib.CCombineShape(s.columns, s.slots, s.rows, s.experts, s.in_stride, s.out_stride)
+        self._check(self._lib.nu_cuda_combine_experts(self._h, values._c(), weights._c(), indices._c(), scales._c() if scales is not None else None,
+                                                      output._c(), ctypes.byref(shape)))
+
+    # ---- collective ----
+    @staticmethod
+    def comm_unique_id() -> bytes:
+        lib = _lib.load()
+        buf = (ctypes.c_uint8 * 128)()
+        rc = lib.nu_cuda_comm_unique_id(buf)
+        if rc != 0:
+            raise NuclisError(rc, "nu_cuda_comm_unique_id")
+        return bytes(buf)
+
+    def comm_init(self, unique_id: bytes, ranks: int, rank: int) -> None:
+        buf = (ctypes.c_uint8 * 128).from_buffer_copy(unique_id)
+        self._check(self._lib.nu_cuda_comm_init(self._h, buf, ranks, rank))
+
+    def allreduce_sum_f32(self, buffer: Buffer, count: int) -> None:
+        self._check(self._lib.nu_cuda_allreduce_sum_f32(self._h, buffer._c(), count))
+
+    def comm_destroy(self) -> None:
+        self._check(self._lib.nu_cuda_comm_destroy(self._h))

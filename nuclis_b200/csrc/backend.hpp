@@ -1,0 +1,132 @@
+// Host side of the CUDA backend: the C++ mirror of `metal.Backend`
+// (inference/src/backends/metal/root.zig:88-330 and ops/*.zig). Same method
+// names, argument meaning and error behaviour; the C ABI in
+// include/nuclis_cuda.h is a thin wrapper over this class.
+//
+// Ownership and threading follow the reference (root.zig:7-10): created
+// buffers live until release or destruction, wrapped host ranges are uploaded
+// once and cached by start address, one thread owns a backend, one recording
+// is open at a time, and commit() waits.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/nuclis_cuda.h"
+
+namespace nu {
+
+using Buffer = nu_buffer;
+using Matrix = nu_matrix;
+using ExpertMatrix = nu_expert_matrix;
+using Segment = nu_segment;
+
+class Backend {
+public:
+    static Backend *create(int device, std::string &error);
+    ~Backend();
+
+    // ---- knobs (root.zig:99-114) ----
+    bool generic_only = false;
+
+    // ---- buffers ----
+    int createBuffer(size_t len, uint32_t *id);
+    int upload(uint32_t id, size_t offset, const void *src, size_t len);
+    int download(uint32_t id, size_t offset, void *dst, size_t len);
+    int wrap(const void *bytes, size_t len, uint32_t *id);
+    int unwrap(const void *bytes);
+    int release(uint32_t id);
+    void *devicePtr(uint32_t id);
+    uint64_t createdBytes() const { return created_bytes_; }
+
+    // ---- recording ----
+    int begin();
+    int commit();
+    int commitRetain(uint32_t *graph);
+    int graphLaunch(uint32_t graph, uint32_t count, float *elapsed_ms);
+    int graphRelease(uint32_t graph);
+    int discard();
+    double gpuSeconds() const { return gpu_seconds_; }
+    uint64_t launchCount() const { return launches_; }
+    cudaStream_t stream() const { return stream_; }
+    int profileEnable(uint32_t max_ops);
+    uint32_t profileRead(double *seconds, uint32_t cap);
+
+    // ---- operators (ops/matvec.zig, ops/matmul.zig, ops/experts.zig, ops/rowwise.zig) ----
+    int embed(const Buffer &weights, const Matrix &matrix, uint32_t token, const Buffer &output, uint32_t out_dtype);
+    int matvec(const Buffer &weights, const Matrix &matrix, const Buffer &input, const Buffer &output);
+    int matvecRows(const Buffer &weights, const Matrix &matrix, const Buffer &input, size_t in_stride,
+                   const Buffer &output, size_t out_stride, size_t tokens);
+    int matmul(const Buffer &weights, const Matrix &matrix, const Buffer &input, uint32_t in_dtype, size_t in_stride,
+               const Buffer &output, size_t out_stride, size_t tokens);
+    int matvecSegments(const Segment *segments, size_t count, const Buffer &input, uint32_t mode);
+    int actMul(uint32_t act, const Buffer &gate, const Buffer &up, size_t count);
+    int route(const Buffer &logits, size_t experts, size_t k, size_t rows, size_t in_stride, const Buffer &indices, const Buffer &weights);
+    int matvecExpertsGrouped(const Buffer &weights, const ExpertMatrix &tensor, const Buffer &indices, size_t slots,
+                             const Buffer &input, size_t in_stride, size_t in_group, const Buffer &output, size_t out_stride);
+    int geluMulRows(const Buffer &gate, const Buffer &up, const Buffer &output, size_t width, size_t rows,
+                    size_t gate_stride, size_t up_stride, size_t out_stride);
+    int combineExperts(const Buffer &values, const Buffer &weights, const Buffer &indices, const Buffer *scales,
+                       const Buffer &output, const nu_combine_shape &shape);
+
+    // ---- collective ----
+    int commInit(const uint8_t *id, int ranks, int rank);
+    int allreduceSumF32(const Buffer &buffer, size_t count);
+    int commDestroy();
+
+    const char *lastError() const { return error_.c_str(); }
+
+    static size_t matmulPadded(size_t tokens) { return (tokens + 63) / 64 * 64; }
+
+private:
+    Backend() = default;
+    struct Allocation {
+        uint8_t *ptr = nullptr;
+        size_t len = 0;
+        bool wrapped = false;
+    };
+    int fail(int status, const char *what);
+    int cuda(cudaError_t e, const char *what, int status = NU_ERR_EXECUTION);
+    // Device address of a view after checking that `need` bytes fit in it and in its buffer.
+    uint8_t *resolve(const Buffer &b, size_t need);
+    static bool overlaps(const Buffer &a, size_t a_len, const Buffer &b, size_t b_len);
+    int needRecording();
+    void opBoundary();
+    int finishCapture(cudaGraphExec_t *exec);
+    int runGraph(cudaGraphExec_t exec, uint32_t count, float *elapsed_ms);
+    int checkKernelStatus();
+
+    int device_ = 0;
+    int sm_count_ = 0;
+    cudaStream_t stream_ = nullptr;
+    cudaEvent_t ev_start_ = nullptr, ev_stop_ = nullptr;
+    std::vector<Allocation> buffers_;  // index = id; ids are never reused
+    std::unordered_map<uintptr_t, std::pair<uint32_t, size_t>> wrapped_;
+    std::unordered_map<uint32_t, cudaGraphExec_t> graphs_;
+    uint32_t next_graph_ = 1;
+    uint64_t created_bytes_ = 0;
+    bool recording_ = false;
+    double gpu_seconds_ = 0;
+    uint64_t launches_ = 0;
+    std::string error_;
+    // scratch of the split-K kernels: partial sums, arrival counters and a status word
+    float *partials_ = nullptr;
+    size_t partials_floats_ = 0;
+    uint32_t *counters_ = nullptr;
+    size_t counters_len_ = 0;
+    // per-operator profile
+    bool profiling_ = false;
+    uint32_t profile_max_ = 0;
+    std::vector<cudaEvent_t> profile_events_;
+    uint32_t profile_ops_ = 0;
+    std::vector<double> profile_last_;
+    // collective
+    void *comm_ = nullptr;  // ncclComm_t
+    int ranks_ = 1, rank_ = 0;
+};
+
+}  // namespace nu

@@ -1,0 +1,69 @@
+// Launchers of the CUDA kernels. Raw device pointers and a stream in; shapes
+// have been validated by the caller (backend.cu). Every launcher returns the
+// number of kernels it enqueued (0 on a launch error, see cudaGetLastError).
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace nu {
+
+// ---- plain decode-and-FMA kernels (any encoding, any alignment) -----------
+
+// Decodes `columns` values of one row to F32 or BF16.
+int launch_dequant_row(cudaStream_t s, uint32_t enc, const uint8_t *row, uint32_t columns, void *out, bool out_bf16);
+
+// out[t][r] = sum_c W[r,c] * in[t,c]; one warp per weight row, F32 FMA in
+// segment order, warp-shuffle reduction. `in_bf16` reads BF16 activations.
+int launch_matmul_generic(cudaStream_t s, uint32_t enc, const uint8_t *w, size_t stride, uint32_t rows, uint32_t columns,
+                          const void *in, bool in_bf16, size_t in_stride, float *out, size_t out_stride, uint32_t tokens);
+
+// Gathered form: slot s uses matrix `indices[s]` (clamped) and input row s / in_group.
+int launch_matvec_experts_generic(cudaStream_t s, uint32_t enc, const uint8_t *w, size_t stride, size_t expert_bytes,
+                                  uint32_t experts, uint32_t rows, uint32_t columns, const uint32_t *indices, uint32_t slots,
+                                  const float *in, size_t in_stride, uint32_t in_group, float *out, size_t out_stride);
+
+// ---- element-wise and routing kernels -------------------------------------
+
+enum Act : uint32_t { ACT_NONE = 0, ACT_SILU = 1, ACT_GELU = 2 };
+// out[r][i] = act(gate[r][i]) * up[r][i]; out may alias gate exactly.
+int launch_act_mul_rows(cudaStream_t s, uint32_t act, const float *gate, const float *up, float *out,
+                        uint32_t width, uint32_t rows, size_t gate_stride, size_t up_stride, size_t out_stride);
+int launch_route(cudaStream_t s, const float *logits, uint32_t experts, uint32_t k, uint32_t rows, size_t in_stride,
+                 uint32_t *indices, float *weights);
+int launch_combine_experts(cudaStream_t s, const float *values, const float *weights, const uint32_t *indices, const float *scales,
+                           float *out, uint32_t columns, uint32_t slots, uint32_t rows, size_t in_stride, size_t out_stride, uint32_t experts);
+
+// ---- fused dequant tensor-core GEMV / small-M GEMM (1..8 token rows) ------
+
+struct FastSegment {
+    const uint8_t *w;  // first row of the (expert's) matrix
+    size_t stride;     // bytes per weight row
+    uint32_t rows;
+    float *out;        // [tokens][out_stride]
+    size_t out_stride;
+};
+struct FastJob {
+    uint32_t enc;
+    uint32_t columns;
+    uint32_t tokens;  // 1..8
+    const float *in;  // [tokens][in_stride]
+    size_t in_stride;
+    uint32_t count;  // segments, 1..4
+    uint32_t mode;   // ACT_NONE: plain; ACT_SILU/ACT_GELU: out = act(seg0) * seg1 (count == 2)
+    FastSegment seg[4];
+    // Scratch owned by the handle: split-K partial sums and arrival counters
+    // (zero between launches; the kernel leaves them zero).
+    float *partials;
+    size_t partials_floats;
+    uint32_t *counters;
+    size_t counters_len;
+    int sm_count;
+};
+// Opts every variant into its dynamic shared memory size; once per device, outside any capture.
+bool fast_configure();
+// Whether the fast kernel serves this job (encoding, alignment, sizes, scratch).
+bool fast_supported(const FastJob &job);
+int launch_fast(cudaStream_t s, const FastJob &job);
+
+}  // namespace nu

@@ -1,0 +1,239 @@
+// Plain kernels: the decode-and-FMA matvec/matmul that serves any encoding at
+// any alignment (the role of nu_matvec / nu_matvec_rows / nu_matvec_experts,
+// inference/src/backends/metal/kernels/matvec.metal:5-21, matvec_rows.metal:274-298,
+// experts.metal:16-36), the standalone row decoder (nu_embed, rowwise.metal:3-11)
+// and the element-wise, routing and combine kernels of the expert path
+// (experts.metal:46-120, 153-161). These are the slow, obviously-right forms the
+// specialized kernels are checked against on the device.
+#include <cuda_bf16.h>
+
+#include "kernels.hpp"
+#include "nu_device.cuh"
+
+namespace nu {
+
+// ---- row decode ------------------------------------------------------------
+
+__global__ void dequant_row_kernel(uint32_t enc, const uint8_t *row, uint32_t segments, float *out_f32, __nv_bfloat16 *out_bf16) {
+    const uint32_t seg = blockIdx.x * blockDim.x + threadIdx.x;
+    if (seg >= segments) return;
+    float v[16];
+    dequant16(enc, row, seg, v);
+    if (out_f32) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) out_f32[seg * 16 + i] = v[i];
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) out_bf16[seg * 16 + i] = __float2bfloat16_rn(v[i]);
+    }
+}
+
+int launch_dequant_row(cudaStream_t s, uint32_t enc, const uint8_t *row, uint32_t columns, void *out, bool out_bf16) {
+    const uint32_t segments = columns / 16;
+    dequant_row_kernel<<<(segments + 255) / 256, 256, 0, s>>>(enc, row, segments, out_bf16 ? nullptr : (float *)out,
+                                                             out_bf16 ? (__nv_bfloat16 *)out : nullptr);
+    return 1;
+}
+
+// ---- generic matvec / matmul ------------------------------------------------
+
+constexpr int GENERIC_TOKENS = 8;   // token rows one warp accumulates at once
+constexpr int GENERIC_WARPS = 8;    // warps (= weight rows) per block
+
+template <bool IN_BF16>
+__device__ __forceinline__ float load_in(const void *in, size_t index) {
+    if (IN_BF16) return __bfloat162float(((const __nv_bfloat16 *)in)[index]);
+    return ((const float *)in)[index];
+}
+
+// One warp per weight row; lanes stride over 16-value segments; each decoded
+// value is multiplied into up to 8 token accumulators; tokens beyond 8 are
+// covered by blockIdx.y.
+template <bool IN_BF16>
+__device__ __forceinline__ void generic_row(uint32_t enc, const uint8_t *row, uint32_t columns, const void *in, size_t in_stride,
+                                            uint32_t tokens, float *out, size_t out_stride, uint32_t r) {
+    const uint32_t lane = threadIdx.x & 31;
+    float acc[GENERIC_TOKENS];
+#pragma unroll
+    for (int t = 0; t < GENERIC_TOKENS; ++t) acc[t] = 0.0f;
+    for (uint32_t seg = lane; seg < columns / 16; seg += 32) {
+        float v[16];
+        dequant16(enc, row, seg, v);
+#pragma unroll
+        for (int t = 0; t < GENERIC_TOKENS; ++t) {
+            if ((uint32_t)t < tokens) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[t] = fmaf(v[i], load_in<IN_BF16>(in, (size_t)t * in_stride + seg * 16 + i), acc[t]);
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < GENERIC_TOKENS; ++t) {
+        float a = acc[t];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+        if (lane == 0 && (uint32_t)t < tokens) out[(size_t)t * out_stride + r] = a;
+    }
+}
+
+template <bool IN_BF16>
+__global__ void matmul_generic_kernel(uint32_t enc, const uint8_t *w, size_t stride, uint32_t rows, uint32_t columns,
+                                      const void *in, size_t in_stride, float *out, size_t out_stride, uint32_t tokens) {
+    const uint32_t r = blockIdx.x * GENERIC_WARPS + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const uint32_t t0 = blockIdx.y * GENERIC_TOKENS;
+    const uint32_t n = min(tokens - t0, (uint32_t)GENERIC_TOKENS);
+    const void *x = IN_BF16 ? (const void *)((const __nv_bfloat16 *)in + (size_t)t0 * in_stride)
+                            : (const void *)((const float *)in + (size_t)t0 * in_stride);
+    generic_row<IN_BF16>(enc, w + (size_t)r * stride, columns, x, in_stride, n, out + (size_t)t0 * out_stride, out_stride, r);
+}
+
+int launch_matmul_generic(cudaStream_t s, uint32_t enc, const uint8_t *w, size_t stride, uint32_t rows, uint32_t columns,
+                          const void *in, bool in_bf16, size_t in_stride, float *out, size_t out_stride, uint32_t tokens) {
+    dim3 grid((rows + GENERIC_WARPS - 1) / GENERIC_WARPS, (tokens + GENERIC_TOKENS - 1) / GENERIC_TOKENS);
+    if (in_bf16)
+        matmul_generic_kernel<true><<<grid, GENERIC_WARPS * 32, 0, s>>>(enc, w, stride, rows, columns, in, in_stride, out, out_stride, tokens);
+    else
+        matmul_generic_kernel<false><<<grid, GENERIC_WARPS * 32, 0, s>>>(enc, w, stride, rows, columns, in, in_stride, out, out_stride, tokens);
+    return 1;
+}
+
+__global__ void matvec_experts_generic_kernel(uint32_t enc, const uint8_t *w, size_t stride, size_t expert_bytes, uint32_t experts,
+                                              uint32_t rows, uint32_t columns, const uint32_t *indices,
+                                              const float *in, size_t in_stride, uint32_t in_group, float *out, size_t out_stride) {
+    const uint32_t slot = blockIdx.y;
+    const uint32_t r = blockIdx.x * GENERIC_WARPS + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    // A corrupt routing buffer can never read past the tensor (experts.metal:25).
+    const uint32_t expert = min(indices[slot], experts - 1);
+    const uint8_t *row = w + (size_t)expert * expert_bytes + (size_t)r * stride;
+    generic_row<false>(enc, row, columns, in + (size_t)(slot / in_group) * in_stride, 0, 1, out + (size_t)slot * out_stride, 0, r);
+}
+
+int launch_matvec_experts_generic(cudaStream_t s, uint32_t enc, const uint8_t *w, size_t stride, size_t expert_bytes,
+                                  uint32_t experts, uint32_t rows, uint32_t columns, const uint32_t *indices, uint32_t slots,
+                                  const float *in, size_t in_stride, uint32_t in_group, float *out, size_t out_stride) {
+    dim3 grid((rows + GENERIC_WARPS - 1) / GENERIC_WARPS, slots);
+    matvec_experts_generic_kernel<<<grid, GENERIC_WARPS * 32, 0, s>>>(enc, w, stride, expert_bytes, experts, rows, columns, indices,
+                                                                      in, in_stride, in_group, out, out_stride);
+    return 1;
+}
+
+// ---- act(gate) * up ----------------------------------------------------------
+
+__global__ void act_mul_rows_kernel(uint32_t act, const float *gate, const float *up, float *out, uint32_t width, uint32_t rows,
+                                    size_t gate_stride, size_t up_stride, size_t out_stride) {
+    const size_t id = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (id >= (size_t)width * rows) return;
+    const size_t r = id / width, i = id % width;
+    const float g = gate[r * gate_stride + i];
+    const float a = act == ACT_SILU ? silu_f32(g) : (act == ACT_GELU ? gelu_f32(g) : g);
+    out[r * out_stride + i] = a * up[r * up_stride + i];
+}
+
+int launch_act_mul_rows(cudaStream_t s, uint32_t act, const float *gate, const float *up, float *out,
+                        uint32_t width, uint32_t rows, size_t gate_stride, size_t up_stride, size_t out_stride) {
+    const size_t n = (size_t)width * rows;
+    act_mul_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(act, gate, up, out, width, rows, gate_stride, up_stride, out_stride);
+    return 1;
+}
+
+// ---- router -------------------------------------------------------------------
+// One 256-thread block per row of logits: softmax in F32, then k rounds of
+// arg-max by (logit desc, index asc) on the logits themselves, so that the
+// rounding of exp cannot reorder near ties; weights renormalized over the
+// selected experts with the sum clamped below at the smallest F16 normal.
+
+constexpr int ROUTE_THREADS = 256;
+constexpr int ROUTE_MAX_K = 64;
+
+__global__ void route_kernel(const float *logits, uint32_t experts, uint32_t k, size_t in_stride, uint32_t *indices, float *weights) {
+    __shared__ float part_v[8];
+    __shared__ uint32_t part_i[8];
+    __shared__ float selected[ROUTE_MAX_K];
+    const uint32_t row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bool live = tid < experts;
+    const float logit = live ? logits[(size_t)row * in_stride + tid] : -INFINITY;
+    float m = logit;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) part_v[warp] = m;
+    __syncthreads();
+    m = part_v[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) m = fmaxf(m, part_v[i]);
+    __syncthreads();
+    const float e = live ? expf(logit - m) : 0.0f;
+    float total = e;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+    if (lane == 0) part_v[warp] = total;
+    __syncthreads();
+    total = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) total += part_v[i];
+    const float probability = e / total;
+    bool taken = !live;
+    for (uint32_t r = 0; r < k; ++r) {
+        __syncthreads();
+        float v = taken ? -INFINITY : logit;
+        uint32_t idx = taken ? 0xffffffffu : tid;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+        }
+        if (lane == 0) { part_v[warp] = v; part_i[warp] = idx; }
+        __syncthreads();
+        v = part_v[0];
+        idx = part_i[0];
+#pragma unroll
+        for (int i = 1; i < 8; ++i)
+            if (part_v[i] > v || (part_v[i] == v && part_i[i] < idx)) { v = part_v[i]; idx = part_i[i]; }
+        if (tid == idx) {
+            taken = true;
+            selected[r] = probability;
+            indices[(size_t)row * k + r] = idx;
+        }
+    }
+    __syncthreads();
+    // The selected probabilities summed in slot order, as a serial loop would.
+    float sum = 0.0f;
+    for (uint32_t r = 0; r < k; ++r) sum += selected[r];
+    if (tid < k) weights[(size_t)row * k + tid] = selected[tid] / fmaxf(sum, 6.103515625e-5f);
+}
+
+int launch_route(cudaStream_t s, const float *logits, uint32_t experts, uint32_t k, uint32_t rows, size_t in_stride,
+                 uint32_t *indices, float *weights) {
+    route_kernel<<<rows, ROUTE_THREADS, 0, s>>>(logits, experts, k, in_stride, indices, weights);
+    return 1;
+}
+
+// ---- combine --------------------------------------------------------------------
+
+__global__ void combine_experts_kernel(const float *values, const float *weights, const uint32_t *indices, const float *scales,
+                                       float *out, uint32_t columns, uint32_t slots, uint32_t rows, size_t in_stride, size_t out_stride,
+                                       uint32_t experts) {
+    const size_t id = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (id >= (size_t)columns * rows) return;
+    const uint32_t row = (uint32_t)(id / columns), c = (uint32_t)(id % columns);
+    float acc = 0.0f;
+    for (uint32_t s = 0; s < slots; ++s) {
+        const size_t slot = (size_t)row * slots + s;
+        float w = weights[slot];
+        if (scales) w *= scales[min(indices[slot], experts - 1)];
+        acc = fmaf(w, values[slot * in_stride + c], acc);
+    }
+    out[(size_t)row * out_stride + c] = acc;
+}
+
+int launch_combine_experts(cudaStream_t s, const float *values, const float *weights, const uint32_t *indices, const float *scales,
+                           float *out, uint32_t columns, uint32_t slots, uint32_t rows, size_t in_stride, size_t out_stride, uint32_t experts) {
+    const size_t n = (size_t)columns * rows;
+    combine_experts_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(values, weights, indices, scales, out, columns, slots, rows,
+                                                                       in_stride, out_stride, experts);
+    return 1;
+}
+
+}  // namespace nu

@@ -1,0 +1,117 @@
+// Device-side block decoders shared by every kernel that must agree bit for
+// bit with the CPU decoder (quant.row, inference/src/quant/decode.zig:30-103).
+// Byte-indexed exactly like the reference so any alignment works; the fast
+// kernels have their own packed unpackers and are checked against these.
+#pragma once
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace nu {
+
+enum Encoding : uint32_t { F32 = 0, F16 = 1, Q8_0 = 8, Q4_K = 12, Q6_K = 14, BF16 = 30 };
+
+struct Layout { uint32_t elements, bytes; };
+
+// encoding.zig:29-56 for the encodings this library serves; elements == 0 means unknown.
+__host__ __device__ inline Layout layout(uint32_t id) {
+    switch (id) {
+    case F32: return {1, 4};
+    case F16: return {1, 2};
+    case Q8_0: return {32, 34};
+    case Q4_K: return {256, 144};
+    case Q6_K: return {256, 210};
+    case BF16: return {1, 2};
+    default: return {0, 0};
+    }
+}
+
+// decode.zig:432-435: little-endian binary16 widened exactly.
+__device__ __forceinline__ float half_at(const uint8_t *p) {
+    const unsigned short bits = (unsigned short)p[0] | ((unsigned short)p[1] << 8);
+    return __half2float(__ushort_as_half(bits));
+}
+
+// Decodes the 16 consecutive values [16*seg, 16*seg+16) of one row.
+// Products and the subtraction are separate IEEE operations (no contraction),
+// as in the reference: (d*s)*q - (dmin*m) for Q4_K, (d*scale)*q for Q6_K.
+__device__ __forceinline__ void dequant16(uint32_t enc, const uint8_t *row, uint32_t seg, float out[16]) {
+    const uint32_t first = seg * 16;
+    switch (enc) {
+    case F32:
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const uint8_t *p = row + (size_t)(first + i) * 4;
+            out[i] = __uint_as_float((uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24));
+        }
+        break;
+    case F16:
+#pragma unroll
+        for (int i = 0; i < 16; ++i) out[i] = half_at(row + (size_t)(first + i) * 2);
+        break;
+    case BF16:
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const uint8_t *p = row + (size_t)(first + i) * 2;
+            out[i] = __uint_as_float(((uint32_t)p[0] | ((uint32_t)p[1] << 8)) << 16);
+        }
+        break;
+    case Q8_0: {
+        const uint8_t *block = row + (size_t)(first / 32) * 34;
+        const float d = half_at(block);
+        const uint8_t *q = block + 2 + (first % 32);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) out[i] = __fmul_rn(d, (float)(int8_t)q[i]);
+        break;
+    }
+    case Q4_K: {
+        const uint8_t *block = row + (size_t)(first / 256) * 144;
+        const uint32_t in_block = first % 256;
+        const uint32_t g = in_block / 32, c0 = in_block % 32;
+        const uint8_t *sc = block + 4;
+        uint32_t s, m;
+        if (g < 4) {
+            s = sc[g] & 63u;
+            m = sc[g + 4] & 63u;
+        } else {
+            s = (sc[g + 4] & 15u) | ((uint32_t)(sc[g - 4] >> 6) << 4);
+            m = (uint32_t)(sc[g + 4] >> 4) | ((uint32_t)(sc[g] >> 6) << 4);
+        }
+        const float multiplier = __fmul_rn(half_at(block), (float)s);
+        const float offset = __fmul_rn(half_at(block + 2), (float)m);
+        const uint8_t *qs = block + 16 + (g / 2) * 32 + c0;
+        const uint32_t shift = (g & 1u) * 4;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) out[i] = __fsub_rn(__fmul_rn(multiplier, (float)((qs[i] >> shift) & 15u)), offset);
+        break;
+    }
+    case Q6_K: {
+        const uint8_t *block = row + (size_t)(first / 256) * 210;
+        const uint32_t i0 = first % 256;
+        const uint32_t hh = i0 / 128, quarter = (i0 % 128) / 32, c0 = i0 % 32;
+        const float d = half_at(block + 208);
+        const float ds = __fmul_rn(d, (float)(int8_t)block[192 + i0 / 16]);
+        const uint8_t *ql = block + hh * 64 + (quarter % 2) * 32 + c0;
+        const uint8_t *qh = block + 128 + hh * 32 + c0;
+        const uint32_t low_shift = (quarter / 2) * 4, high_shift = quarter * 2;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int value = (int)(((ql[i] >> low_shift) & 15u) | (((qh[i] >> high_shift) & 3u) << 4)) - 32;
+            out[i] = __fmul_rn(ds, (float)value);
+        }
+        break;
+    }
+    default:
+#pragma unroll
+        for (int i = 0; i < 16; ++i) out[i] = 0.0f;
+    }
+}
+
+// F32 forms of the activations, as the reference's GPU kernels compute them
+// (inference/src/backends/metal/kernels/common.metal:6-16).
+__device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float tanh_clamped(float x) { return tanhf(fminf(fmaxf(x, -20.0f), 20.0f)); }
+__device__ __forceinline__ float gelu_f32(float x) {
+    return 0.5f * x * (1.0f + tanh_clamped(0.7978845608028654f * x * (1.0f + 0.044715f * x * x)));
+}
+
+}  // namespace nu
