@@ -66,4 +66,9 @@ bool fast_configure();
 bool fast_supported(const FastJob &job);
 int launch_fast(cudaStream_t s, const FastJob &job);
 
+// ---- Q4_K decode GEMV (one activation row), direct global loads ----------------
+bool q4k_decode_configure();
+bool q4k_decode_supported(const FastJob &job);
+int launch_q4k_decode(cudaStream_t s, const FastJob &job);
+
 }  // namespace nu
