@@ -715,7 +715,7 @@ static EncodeTiledFn encode_tiled() {
 }
 
 // A uint8 tensor [rows][row_bytes] with `stride` bytes between rows, copied in boxes of box_rows x box_bytes.
-static bool encode_map(CUtensorMap *map, const uint8_t *base, uint64_t row_bytes, uint64_t rows, uint64_t stride, uint32_t box_bytes, uint32_t box_rows) {
+bool encode_weight_map(CUtensorMap *map, const uint8_t *base, uint64_t row_bytes, uint64_t rows, uint64_t stride, uint32_t box_bytes, uint32_t box_rows) {
     EncodeTiledFn fn = encode_tiled();
     if (!fn) return false;
     const cuuint64_t dims[2] = {row_bytes, rows};
@@ -743,7 +743,7 @@ static bool fill_params(const FastJob &job, fast::Params &p) {
     for (uint32_t s = 0; s < job.count; ++s) {
         const FastSegment &g = job.seg[s];
         if (g.rows == 0 || (uintptr_t)g.w % 16 != 0 || g.stride % 16 != 0 || (uintptr_t)g.out % 4 != 0) return false;
-        if (!encode_map(&p.map[s], g.w, (uint64_t)p.ksb * 144, g.rows, g.stride, 144, 16)) return false;
+        if (!encode_weight_map(&p.map[s], g.w, (uint64_t)p.ksb * 144, g.rows, g.stride, 144, 16)) return false;
         p.out[s] = g.out;
         p.out_stride[s] = g.out_stride;
         p.rows[s] = g.rows;
