@@ -653,8 +653,7 @@ int Backend::allreduceSumF32(const Buffer &buffer, size_t count) {
         error_ = std::string("allreduce: ") + (g_nccl.GetErrorString ? g_nccl.GetErrorString(rc) : "NCCL error");
         return NU_ERR_COMM;
     }
-    ++launches_;
-    opBoundary();
+    opBoundary();  // a library collective: not counted among this library's own kernel launches
     return NU_OK;
 }
 
