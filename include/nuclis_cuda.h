@@ -72,7 +72,7 @@ typedef struct nu_buffer {
  * the whole matrix; the row stride is bytes / rows. */
 typedef struct nu_matrix {
     uint32_t encoding;
-    uint32_t reserved;
+    uint32_t layout; /* 0: GGUF rows as stored in the file; otherwise the value nu_cuda_matrix_prepare returned */
     uint64_t rows;
     uint64_t columns;
     uint64_t bytes;
@@ -137,6 +137,19 @@ int nu_cuda_buffer_release(nu_cuda *h, uint32_t id);
 void *nu_cuda_buffer_device_ptr(nu_cuda *h, uint32_t id);
 /* `Backend.created_bytes` (root.zig:113-116). */
 uint64_t nu_cuda_created_bytes(const nu_cuda *h);
+
+/* Re-lays a matrix once, at load time, into the form the specialized kernels read
+ * (no reference analogue; the reference wraps the file bytes as they are,
+ * root.zig:217-230). GGUF rows of some encodings start on 2-byte boundaries
+ * (Q6_K blocks are 210 bytes), which no vector load or bulk copy can address;
+ * the prepared form holds the same bytes in 16-byte aligned planes and decodes
+ * to the same values bit for bit. `prepared` must be as long as the matrix and
+ * must not overlap it; `layout` receives the value to put in `nu_matrix.layout`
+ * (0 when the encoding needs no re-layout: the bytes are then copied as they
+ * are). Refused while recording. Every operator that takes a matrix accepts
+ * both forms, except the expert operators (GGUF form only). */
+int nu_cuda_matrix_prepare(nu_cuda *h, const nu_buffer *weights, const nu_matrix *matrix,
+                           const nu_buffer *prepared, uint32_t *layout);
 
 /* ---- recording (nu_metal_begin / commit / discard / gpu_seconds) --------- */
 

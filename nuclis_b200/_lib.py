@@ -21,7 +21,7 @@ class CBuffer(ctypes.Structure):
 
 
 class CMatrix(ctypes.Structure):
-    _fields_ = [("encoding", u32), ("reserved", u32), ("rows", u64), ("columns", u64), ("bytes", u64)]
+    _fields_ = [("encoding", u32), ("layout", u32), ("rows", u64), ("columns", u64), ("bytes", u64)]
 
 
 class CExpertMatrix(ctypes.Structure):
@@ -53,6 +53,7 @@ SIGNATURES = {
     "nu_cuda_buffer_release": (cint, [vp, u32]),
     "nu_cuda_buffer_device_ptr": (vp, [vp, u32]),
     "nu_cuda_created_bytes": (u64, [vp]),
+    "nu_cuda_matrix_prepare": (cint, [vp, BP, MP, BP, ctypes.POINTER(u32)]),
     "nu_cuda_begin": (cint, [vp]),
     "nu_cuda_commit": (cint, [vp]),
     "nu_cuda_discard": (cint, [vp]),

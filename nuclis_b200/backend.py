@@ -37,9 +37,10 @@ class Matrix:
     rows: int
     columns: int
     bytes: int
+    layout: int = 0  # 0: GGUF rows; otherwise what Backend.prepare returned
 
     def _c(self) -> _lib.CMatrix:
-        return _lib.CMatrix(self.encoding, 0, self.rows, self.columns, self.bytes)
+        return _lib.CMatrix(self.encoding, self.layout, self.rows, self.columns, self.bytes)
 
 
 @dataclass(frozen=True)
@@ -190,6 +191,14 @@ class Backend:
         raw = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
         self._check(self._lib.nu_cuda_buffer_unwrap(self._h, raw.ctypes.data))
         self._keep.pop(raw.ctypes.data, None)
+
+    def prepare(self, weights: Buffer, matrix: Matrix, prepared: Buffer | None = None) -> tuple[Buffer, Matrix]:
+        """Re-lays a matrix once, at load time, into the form the specialized kernels read (same bytes,
+        same values; see nu_cuda_matrix_prepare). Returns the prepared buffer and its descriptor."""
+        out = prepared if prepared is not None else self.create(matrix.bytes)
+        layout = ctypes.c_uint32()
+        self._check(self._lib.nu_cuda_matrix_prepare(self._h, weights._c(), matrix._c(), out._c(), ctypes.byref(layout)))
+        return out, Matrix(matrix.encoding, matrix.rows, matrix.columns, matrix.bytes, layout.value)
 
     @property
     def created_bytes(self) -> int:

@@ -31,6 +31,11 @@ int validateRow(uint32_t enc, size_t byte_count, size_t element_count) {
 
 bool fits_u32(uint64_t v) { return v <= 0xffffffffull; }
 
+// A matrix is in GGUF form (0) or in the form prepare gave it; anything else is a caller error.
+bool layoutOk(const nu_matrix &m) {
+    return m.layout == 0 || (fits_u32(m.rows) && fits_u32(m.columns) && m.layout == prepared_layout(m.encoding, (uint32_t)m.rows, (uint32_t)m.columns));
+}
+
 }  // namespace
 
 // ---- lifecycle -------------------------------------------------------------------------
@@ -193,6 +198,23 @@ bool Backend::overlaps(const Buffer &a, size_t a_len, const Buffer &b, size_t b_
     return a.offset <= b.offset ? b.offset - a.offset < a_len : a.offset - b.offset < b_len;
 }
 
+// No reference analogue: see nu_cuda_matrix_prepare in the header and prepare.cu.
+int Backend::prepare(const Buffer &weights, const Matrix &m, const Buffer &prepared, uint32_t *layout_out) {
+    if (recording_) return fail(NU_ERR_ALREADY_RECORDING, "prepare: a recording is open");
+    if (!layout_out || m.rows == 0 || m.columns == 0 || m.bytes % m.rows != 0 || m.layout != 0) return fail(NU_ERR_INVALID_SHAPE, "prepare: shape");
+    if (int rc = validateRow(m.encoding, m.bytes / m.rows, m.columns)) return fail(rc, "prepare: row layout");
+    if (!fits_u32(m.rows) || !fits_u32(m.columns)) return fail(NU_ERR_INVALID_SHAPE, "prepare: too large");
+    const uint8_t *src = resolve(weights, m.bytes);
+    uint8_t *dst = resolve(prepared, m.bytes);
+    if (!src || !dst || overlaps(weights, m.bytes, prepared, m.bytes)) return fail(NU_ERR_INVALID_SHAPE, "prepare: buffers too short or overlapping");
+    cudaSetDevice(device_);
+    launches_ += launch_prepare(stream_, m.encoding, src, dst, (uint32_t)m.rows, (uint32_t)m.columns);
+    if (int rc = cuda(cudaGetLastError(), "prepare: launch")) return rc;
+    if (int rc = cuda(cudaStreamSynchronize(stream_), "prepare: wait")) return rc;
+    *layout_out = prepared_layout(m.encoding, (uint32_t)m.rows, (uint32_t)m.columns);
+    return NU_OK;
+}
+
 // ---- recording ----------------------------------------------------------------------------
 
 int Backend::begin() {
@@ -349,13 +371,14 @@ int Backend::embed(const Buffer &weights, const Matrix &m, uint32_t token, const
     const size_t stride = m.bytes / m.rows;
     if (int rc = validateRow(m.encoding, stride, m.columns)) return fail(rc, "embed: row layout");
     if (out_dtype != NU_F32 && out_dtype != NU_BF16) return fail(NU_ERR_INVALID_SHAPE, "embed: output type");
+    if (!layoutOk(m)) return fail(NU_ERR_INVALID_SHAPE, "embed: unknown matrix layout");
     if (!fits_u32(m.columns)) return fail(NU_ERR_INVALID_SHAPE, "embed: columns");
     const size_t out_bytes = m.columns * (out_dtype == NU_F32 ? 4 : 2);
     const uint8_t *w = resolve(weights, m.bytes);
     uint8_t *out = resolve(output, out_bytes);
     if (!w || !out || output.offset % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "embed: buffer too short");
     if (int rc = needRecording()) return rc;
-    launches_ += launch_dequant_row(stream_, m.encoding, w + (size_t)token * stride, (uint32_t)m.columns, out, out_dtype == NU_BF16);
+    launches_ += launch_dequant_row(stream_, m.encoding, m.layout, w, stride, (uint32_t)m.rows, token, (uint32_t)m.columns, out, out_dtype == NU_BF16);
     opBoundary();
     return cuda(cudaGetLastError(), "embed: launch");
 }
@@ -366,18 +389,19 @@ int Backend::matvec(const Buffer &weights, const Matrix &m, const Buffer &input,
     const size_t stride = m.bytes / m.rows;
     if (int rc = validateRow(m.encoding, stride, m.columns)) return fail(rc, "matvec: row layout");
     if (!fits_u32(m.rows) || !fits_u32(m.columns)) return fail(NU_ERR_INVALID_SHAPE, "matvec: too large");
+    if (!layoutOk(m)) return fail(NU_ERR_INVALID_SHAPE, "matvec: unknown matrix layout");
     const uint8_t *w = resolve(weights, m.bytes);
     const float *in = (const float *)resolve(input, m.columns * 4);
     float *out = (float *)resolve(output, m.rows * 4);
     if (!w || !in || !out || input.offset % 4 != 0 || output.offset % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "matvec: buffer too short");
     if (int rc = needRecording()) return rc;
     FastJob job{};
-    job.enc = m.encoding; job.columns = (uint32_t)m.columns; job.tokens = 1; job.in = in; job.in_stride = m.columns;
+    job.enc = m.encoding; job.layout = m.layout; job.columns = (uint32_t)m.columns; job.tokens = 1; job.in = in; job.in_stride = m.columns;
     job.count = 1; job.mode = ACT_NONE;
     job.seg[0] = {w, stride, (uint32_t)m.rows, out, m.rows};
     job.partials = partials_; job.partials_floats = partials_floats_; job.counters = counters_; job.counters_len = counters_len_; job.sm_count = sm_count_;
     if (!generic_only && fast_supported(job)) launches_ += launch_fast(stream_, job);
-    else launches_ += launch_matmul_generic(stream_, m.encoding, w, stride, (uint32_t)m.rows, (uint32_t)m.columns, in, false, m.columns, out, m.rows, 1);
+    else launches_ += launch_matmul_generic(stream_, m.encoding, m.layout, w, stride, (uint32_t)m.rows, (uint32_t)m.columns, in, false, m.columns, out, m.rows, 1);
     opBoundary();
     return cuda(cudaGetLastError(), "matvec: launch");
 }
@@ -391,6 +415,7 @@ int Backend::matvecRows(const Buffer &weights, const Matrix &m, const Buffer &in
     if (tokens < 2 || tokens > 8) return fail(NU_ERR_INVALID_SHAPE, "matvec_rows: 2..8 tokens");
     if (in_stride < m.columns || out_stride < m.rows) return fail(NU_ERR_INVALID_SHAPE, "matvec_rows: strides");
     if (!fits_u32(m.rows) || !fits_u32(m.columns)) return fail(NU_ERR_INVALID_SHAPE, "matvec_rows: too large");
+    if (!layoutOk(m)) return fail(NU_ERR_INVALID_SHAPE, "matvec_rows: unknown matrix layout");
     const uint8_t *w = resolve(weights, m.bytes);
     const float *in = (const float *)resolve(input, ((tokens - 1) * in_stride + m.columns) * 4);
     float *out = (float *)resolve(output, ((tokens - 1) * out_stride + m.rows) * 4);
@@ -398,12 +423,12 @@ int Backend::matvecRows(const Buffer &weights, const Matrix &m, const Buffer &in
     if (input.offset % 16 != 0 || in_stride % 4 != 0 || output.offset % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "matvec_rows: alignment");
     if (int rc = needRecording()) return rc;
     FastJob job{};
-    job.enc = m.encoding; job.columns = (uint32_t)m.columns; job.tokens = (uint32_t)tokens; job.in = in; job.in_stride = in_stride;
+    job.enc = m.encoding; job.layout = m.layout; job.columns = (uint32_t)m.columns; job.tokens = (uint32_t)tokens; job.in = in; job.in_stride = in_stride;
     job.count = 1; job.mode = ACT_NONE;
     job.seg[0] = {w, stride, (uint32_t)m.rows, out, out_stride};
     job.partials = partials_; job.partials_floats = partials_floats_; job.counters = counters_; job.counters_len = counters_len_; job.sm_count = sm_count_;
     if (!generic_only && fast_supported(job)) launches_ += launch_fast(stream_, job);
-    else launches_ += launch_matmul_generic(stream_, m.encoding, w, stride, (uint32_t)m.rows, (uint32_t)m.columns, in, false, in_stride, out, out_stride, (uint32_t)tokens);
+    else launches_ += launch_matmul_generic(stream_, m.encoding, m.layout, w, stride, (uint32_t)m.rows, (uint32_t)m.columns, in, false, in_stride, out, out_stride, (uint32_t)tokens);
     opBoundary();
     return cuda(cudaGetLastError(), "matvec_rows: launch");
 }
@@ -417,6 +442,7 @@ int Backend::matmul(const Buffer &weights, const Matrix &m, const Buffer &input,
     if (int rc = validateRow(m.encoding, stride, m.columns)) return fail(rc, "matmul: row layout");
     if (in_dtype != NU_F32 && in_dtype != NU_BF16) return fail(NU_ERR_INVALID_SHAPE, "matmul: input type");
     if (!fits_u32(m.rows) || !fits_u32(m.columns) || !fits_u32(tokens)) return fail(NU_ERR_INVALID_SHAPE, "matmul: too large");
+    if (!layoutOk(m)) return fail(NU_ERR_INVALID_SHAPE, "matmul: unknown matrix layout");
     const size_t padded = matmulPadded(tokens);
     const size_t esize = in_dtype == NU_F32 ? 4 : 2;
     const uint8_t *w = resolve(weights, m.bytes);
@@ -429,7 +455,7 @@ int Backend::matmul(const Buffer &weights, const Matrix &m, const Buffer &input,
     if (!generic_only && in_dtype == NU_F32 && tokens <= 64) {
         // Up to 8 tokens in one pass of the weights; a few more in passes of 8.
         FastJob job{};
-        job.enc = m.encoding; job.columns = (uint32_t)m.columns; job.count = 1; job.mode = ACT_NONE; job.in_stride = in_stride;
+        job.enc = m.encoding; job.layout = m.layout; job.columns = (uint32_t)m.columns; job.count = 1; job.mode = ACT_NONE; job.in_stride = in_stride;
         job.partials = partials_; job.partials_floats = partials_floats_; job.counters = counters_; job.counters_len = counters_len_; job.sm_count = sm_count_;
         job.tokens = (uint32_t)(tokens < 8 ? tokens : 8);
         job.in = (const float *)in;
@@ -445,7 +471,7 @@ int Backend::matmul(const Buffer &weights, const Matrix &m, const Buffer &input,
         }
     }
     if (!done)
-        launches_ += launch_matmul_generic(stream_, m.encoding, w, stride, (uint32_t)m.rows, (uint32_t)m.columns, in, in_dtype == NU_BF16, in_stride, out, out_stride, (uint32_t)tokens);
+        launches_ += launch_matmul_generic(stream_, m.encoding, m.layout, w, stride, (uint32_t)m.rows, (uint32_t)m.columns, in, in_dtype == NU_BF16, in_stride, out, out_stride, (uint32_t)tokens);
     opBoundary();
     return cuda(cudaGetLastError(), "matmul: launch");
 }
@@ -462,7 +488,7 @@ int Backend::matvecSegments(const Segment *segments, size_t count, const Buffer 
                                       segments[0].output.id != segments[1].output.id || segments[0].output.offset != segments[1].output.offset))
         return fail(NU_ERR_INVALID_SHAPE, "segments: a pair needs two equal segments naming one output");
     FastJob job{};
-    job.enc = segments[0].matrix.encoding; job.columns = (uint32_t)columns; job.tokens = 1; job.in = in; job.in_stride = columns;
+    job.enc = segments[0].matrix.encoding; job.layout = segments[0].matrix.layout; job.columns = (uint32_t)columns; job.tokens = 1; job.in = in; job.in_stride = columns;
     job.count = (uint32_t)count; job.mode = mode == NU_SEGMENTS_PLAIN ? ACT_NONE : (mode == NU_SEGMENTS_SILU_MUL_PAIR ? ACT_SILU : ACT_GELU);
     job.partials = partials_; job.partials_floats = partials_floats_; job.counters = counters_; job.counters_len = counters_len_; job.sm_count = sm_count_;
     bool same_encoding = true;
@@ -484,7 +510,8 @@ int Backend::matvecSegments(const Segment *segments, size_t count, const Buffer 
                 if (overlaps(s.output, m.rows * 4, segments[j].output, segments[j].matrix.rows * 4)) return fail(NU_ERR_INVALID_SHAPE, "segments: outputs overlap");
         total_rows += m.rows;
         if (total_rows > 0xffffffffull) return fail(NU_ERR_INVALID_SHAPE, "segments: too many rows");
-        same_encoding = same_encoding && m.encoding == job.enc;
+        if (!layoutOk(m)) return fail(NU_ERR_INVALID_SHAPE, "segments: unknown matrix layout");
+        same_encoding = same_encoding && m.encoding == job.enc && m.layout == job.layout;
         job.seg[i] = {w, stride, (uint32_t)m.rows, out, m.rows};
     }
     // One launch needs one unpacker: a merge of mixed encodings, or one the
@@ -727,6 +754,11 @@ int nu_cuda_buffer_unwrap(nu_cuda *h, const void *bytes) { NU_H(h); return h->b-
 int nu_cuda_buffer_release(nu_cuda *h, uint32_t id) { NU_H(h); return h->b->release(id); }
 void *nu_cuda_buffer_device_ptr(nu_cuda *h, uint32_t id) { return h ? h->b->devicePtr(id) : nullptr; }
 uint64_t nu_cuda_created_bytes(const nu_cuda *h) { return h ? h->b->createdBytes() : 0; }
+
+int nu_cuda_matrix_prepare(nu_cuda *h, const nu_buffer *weights, const nu_matrix *matrix, const nu_buffer *prepared, uint32_t *layout) {
+    NU_H(h); NU_P(weights && matrix && prepared && layout);
+    return h->b->prepare(*weights, *matrix, *prepared, layout);
+}
 
 int nu_cuda_begin(nu_cuda *h) { NU_H(h); return h->b->begin(); }
 int nu_cuda_commit(nu_cuda *h) { NU_H(h); return h->b->commit(); }

@@ -42,6 +42,7 @@ public:
     int release(uint32_t id);
     void *devicePtr(uint32_t id);
     uint64_t createdBytes() const { return created_bytes_; }
+    int prepare(const Buffer &weights, const Matrix &matrix, const Buffer &prepared, uint32_t *layout);
 
     // ---- recording ----
     int begin();

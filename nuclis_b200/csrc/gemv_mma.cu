@@ -727,7 +727,7 @@ bool encode_weight_map(CUtensorMap *map, const uint8_t *base, uint64_t row_bytes
 }
 
 static bool fill_params(const FastJob &job, fast::Params &p) {
-    if (job.enc != Q4_K) return false;
+    if (job.enc != Q4_K || job.layout != 0) return false;
     if (job.tokens < 1 || job.tokens > 8 || job.count < 1 || job.count > 4) return false;
     if (job.columns == 0 || job.columns % 256 != 0) return false;
     if ((uintptr_t)job.in % 16 != 0 || (job.tokens > 1 && job.in_stride % 4 != 0)) return false;
@@ -784,7 +784,7 @@ static bool fill_params(const FastJob &job, fast::Params &p) {
 }
 
 bool fast_supported(const FastJob &job) {
-    if (q4k_decode_supported(job)) return true;
+    if (q4k_decode_supported(job) || q6k_decode_supported(job)) return true;
     fast::Params p;
     return fill_params(job, p);
 }
@@ -796,7 +796,7 @@ static bool configure_variant() {
 }
 
 bool fast_configure() {
-    return q4k_decode_configure() && configure_variant<Q4_K, 1>() && configure_variant<Q4_K, 2>() && configure_variant<Q4_K, 4>() && configure_variant<Q4_K, 8>();
+    return q4k_decode_configure() && q6k_decode_configure() && configure_variant<Q4_K, 1>() && configure_variant<Q4_K, 2>() && configure_variant<Q4_K, 4>() && configure_variant<Q4_K, 8>();
 }
 
 template <int ENC, int TS>
@@ -810,6 +810,7 @@ static int launch_variant(cudaStream_t s, const fast::Params &p, int sm_count) {
 
 int launch_fast(cudaStream_t s, const FastJob &job) {
     if (q4k_decode_supported(job)) return launch_q4k_decode(s, job);
+    if (q6k_decode_supported(job)) return launch_q6k_decode(s, job);
     fast::Params p;
     if (!fill_params(job, p)) return 0;
     // The status word lives at the end of the counters array.

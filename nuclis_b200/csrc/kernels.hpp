@@ -11,11 +11,13 @@ namespace nu {
 // ---- plain decode-and-FMA kernels (any encoding, any alignment) -----------
 
 // Decodes `columns` values of one row to F32 or BF16.
-int launch_dequant_row(cudaStream_t s, uint32_t enc, const uint8_t *row, uint32_t columns, void *out, bool out_bf16);
+// `w` is the start of the matrix, `row` the row to decode; `layout` as in nu_matrix.
+int launch_dequant_row(cudaStream_t s, uint32_t enc, uint32_t layout, const uint8_t *w, size_t stride, uint32_t rows, uint32_t row, uint32_t columns,
+                       void *out, bool out_bf16);
 
 // out[t][r] = sum_c W[r,c] * in[t,c]; one warp per weight row, F32 FMA in
 // segment order, warp-shuffle reduction. `in_bf16` reads BF16 activations.
-int launch_matmul_generic(cudaStream_t s, uint32_t enc, const uint8_t *w, size_t stride, uint32_t rows, uint32_t columns,
+int launch_matmul_generic(cudaStream_t s, uint32_t enc, uint32_t layout, const uint8_t *w, size_t stride, uint32_t rows, uint32_t columns,
                           const void *in, bool in_bf16, size_t in_stride, float *out, size_t out_stride, uint32_t tokens);
 
 // Gathered form: slot s uses matrix `indices[s]` (clamped) and input row s / in_group.
@@ -45,6 +47,7 @@ struct FastSegment {
 };
 struct FastJob {
     uint32_t enc;
+    uint32_t layout;  // 0: GGUF rows; 1: the planar form made by launch_prepare (see prepare.cu)
     uint32_t columns;
     uint32_t tokens;  // 1..8
     const float *in;  // [tokens][in_stride]
@@ -66,9 +69,17 @@ bool fast_configure();
 bool fast_supported(const FastJob &job);
 int launch_fast(cudaStream_t s, const FastJob &job);
 
-// ---- Q4_K decode GEMV (one activation row), direct global loads ----------------
+// ---- decode GEMV (one activation row) per encoding --------------------------------
 bool q4k_decode_configure();
 bool q4k_decode_supported(const FastJob &job);
 int launch_q4k_decode(cudaStream_t s, const FastJob &job);
+bool q6k_decode_configure();
+bool q6k_decode_supported(const FastJob &job);
+int launch_q6k_decode(cudaStream_t s, const FastJob &job);
+
+// ---- planar re-layout of a matrix for the specialized kernels ---------------------
+// Layout the matrix takes after preparation: 0 when the specialized kernels read the GGUF rows as they are.
+uint32_t prepared_layout(uint32_t enc, uint32_t rows, uint32_t columns);
+int launch_prepare(cudaStream_t s, uint32_t enc, const uint8_t *src, uint8_t *dst, uint32_t rows, uint32_t columns);
 
 }  // namespace nu

@@ -14,11 +14,19 @@ namespace nu {
 
 // ---- row decode ------------------------------------------------------------
 
-__global__ void dequant_row_kernel(uint32_t enc, const uint8_t *row, uint32_t segments, float *out_f32, __nv_bfloat16 *out_bf16) {
+// Decodes 16 values of row r: from the GGUF rows, or from the planar form of prepare.cu.
+__device__ __forceinline__ void decode16(uint32_t enc, uint32_t layout, const uint8_t *w, size_t stride, uint32_t rows, uint32_t columns, uint32_t r,
+                                         uint32_t seg, float v[16]) {
+    if (layout == 1) dequant16_planar_q6k(w, rows, columns / 256, r, seg, v);
+    else dequant16(enc, w + (size_t)r * stride, seg, v);
+}
+
+__global__ void dequant_row_kernel(uint32_t enc, uint32_t layout, const uint8_t *w, size_t stride, uint32_t rows, uint32_t row, uint32_t columns,
+                                   float *out_f32, __nv_bfloat16 *out_bf16) {
     const uint32_t seg = blockIdx.x * blockDim.x + threadIdx.x;
-    if (seg >= segments) return;
+    if (seg >= columns / 16) return;
     float v[16];
-    dequant16(enc, row, seg, v);
+    decode16(enc, layout, w, stride, rows, columns, row, seg, v);
     if (out_f32) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) out_f32[seg * 16 + i] = v[i];
@@ -28,9 +36,10 @@ __global__ void dequant_row_kernel(uint32_t enc, const uint8_t *row, uint32_t se
     }
 }
 
-int launch_dequant_row(cudaStream_t s, uint32_t enc, const uint8_t *row, uint32_t columns, void *out, bool out_bf16) {
+int launch_dequant_row(cudaStream_t s, uint32_t enc, uint32_t layout, const uint8_t *w, size_t stride, uint32_t rows, uint32_t row, uint32_t columns,
+                       void *out, bool out_bf16) {
     const uint32_t segments = columns / 16;
-    dequant_row_kernel<<<(segments + 255) / 256, 256, 0, s>>>(enc, row, segments, out_bf16 ? nullptr : (float *)out,
+    dequant_row_kernel<<<(segments + 255) / 256, 256, 0, s>>>(enc, layout, w, stride, rows, row, columns, out_bf16 ? nullptr : (float *)out,
                                                              out_bf16 ? (__nv_bfloat16 *)out : nullptr);
     return 1;
 }
@@ -50,15 +59,15 @@ __device__ __forceinline__ float load_in(const void *in, size_t index) {
 // value is multiplied into up to 8 token accumulators; tokens beyond 8 are
 // covered by blockIdx.y.
 template <bool IN_BF16>
-__device__ __forceinline__ void generic_row(uint32_t enc, const uint8_t *row, uint32_t columns, const void *in, size_t in_stride,
-                                            uint32_t tokens, float *out, size_t out_stride, uint32_t r) {
+__device__ __forceinline__ void generic_row(uint32_t enc, uint32_t layout, const uint8_t *w, size_t stride, uint32_t rows, uint32_t columns,
+                                            const void *in, size_t in_stride, uint32_t tokens, float *out, size_t out_stride, uint32_t r) {
     const uint32_t lane = threadIdx.x & 31;
     float acc[GENERIC_TOKENS];
 #pragma unroll
     for (int t = 0; t < GENERIC_TOKENS; ++t) acc[t] = 0.0f;
     for (uint32_t seg = lane; seg < columns / 16; seg += 32) {
         float v[16];
-        dequant16(enc, row, seg, v);
+        decode16(enc, layout, w, stride, rows, columns, r, seg, v);
 #pragma unroll
         for (int t = 0; t < GENERIC_TOKENS; ++t) {
             if ((uint32_t)t < tokens) {
@@ -77,7 +86,7 @@ __device__ __forceinline__ void generic_row(uint32_t enc, const uint8_t *row, ui
 }
 
 template <bool IN_BF16>
-__global__ void matmul_generic_kernel(uint32_t enc, const uint8_t *w, size_t stride, uint32_t rows, uint32_t columns,
+__global__ void matmul_generic_kernel(uint32_t enc, uint32_t layout, const uint8_t *w, size_t stride, uint32_t rows, uint32_t columns,
                                       const void *in, size_t in_stride, float *out, size_t out_stride, uint32_t tokens) {
     const uint32_t r = blockIdx.x * GENERIC_WARPS + (threadIdx.x >> 5);
     if (r >= rows) return;
@@ -85,16 +94,16 @@ __global__ void matmul_generic_kernel(uint32_t enc, const uint8_t *w, size_t str
     const uint32_t n = min(tokens - t0, (uint32_t)GENERIC_TOKENS);
     const void *x = IN_BF16 ? (const void *)((const __nv_bfloat16 *)in + (size_t)t0 * in_stride)
                             : (const void *)((const float *)in + (size_t)t0 * in_stride);
-    generic_row<IN_BF16>(enc, w + (size_t)r * stride, columns, x, in_stride, n, out + (size_t)t0 * out_stride, out_stride, r);
+    generic_row<IN_BF16>(enc, layout, w, stride, rows, columns, x, in_stride, n, out + (size_t)t0 * out_stride, out_stride, r);
 }
 
-int launch_matmul_generic(cudaStream_t s, uint32_t enc, const uint8_t *w, size_t stride, uint32_t rows, uint32_t columns,
+int launch_matmul_generic(cudaStream_t s, uint32_t enc, uint32_t layout, const uint8_t *w, size_t stride, uint32_t rows, uint32_t columns,
                           const void *in, bool in_bf16, size_t in_stride, float *out, size_t out_stride, uint32_t tokens) {
     dim3 grid((rows + GENERIC_WARPS - 1) / GENERIC_WARPS, (tokens + GENERIC_TOKENS - 1) / GENERIC_TOKENS);
     if (in_bf16)
-        matmul_generic_kernel<true><<<grid, GENERIC_WARPS * 32, 0, s>>>(enc, w, stride, rows, columns, in, in_stride, out, out_stride, tokens);
+        matmul_generic_kernel<true><<<grid, GENERIC_WARPS * 32, 0, s>>>(enc, layout, w, stride, rows, columns, in, in_stride, out, out_stride, tokens);
     else
-        matmul_generic_kernel<false><<<grid, GENERIC_WARPS * 32, 0, s>>>(enc, w, stride, rows, columns, in, in_stride, out, out_stride, tokens);
+        matmul_generic_kernel<false><<<grid, GENERIC_WARPS * 32, 0, s>>>(enc, layout, w, stride, rows, columns, in, in_stride, out, out_stride, tokens);
     return 1;
 }
 
@@ -106,8 +115,8 @@ __global__ void matvec_experts_generic_kernel(uint32_t enc, const uint8_t *w, si
     if (r >= rows) return;
     // A corrupt routing buffer can never read past the tensor (experts.metal:25).
     const uint32_t expert = min(indices[slot], experts - 1);
-    const uint8_t *row = w + (size_t)expert * expert_bytes + (size_t)r * stride;
-    generic_row<false>(enc, row, columns, in + (size_t)(slot / in_group) * in_stride, 0, 1, out + (size_t)slot * out_stride, 0, r);
+    generic_row<false>(enc, 0, w + (size_t)expert * expert_bytes, stride, rows, columns, in + (size_t)(slot / in_group) * in_stride, 0, 1,
+                       out + (size_t)slot * out_stride, 0, r);
 }
 
 int launch_matvec_experts_generic(cudaStream_t s, uint32_t enc, const uint8_t *w, size_t stride, size_t expert_bytes,

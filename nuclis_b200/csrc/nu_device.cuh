@@ -106,6 +106,24 @@ __device__ __forceinline__ void dequant16(uint32_t enc, const uint8_t *row, uint
     }
 }
 
+// The same 16 values from the planar form of a Q6_K matrix (prepare.cu): `base` is the start of the
+// matrix, `row` the row index. Bit-identical to dequant16 on the GGUF form.
+__device__ __forceinline__ void dequant16_planar_q6k(const uint8_t *base, uint32_t rows, uint32_t ksb, uint32_t row, uint32_t seg, float out[16]) {
+    const uint32_t sb = seg / 16, i0 = (seg % 16) * 16;
+    const uint32_t hh = i0 / 128, quarter = (i0 % 128) / 32, ch = (i0 % 32) / 16, t = hh * 2 + ch;
+    const uint8_t *rec = base + ((size_t)row * ksb + sb) * 208;
+    const uint8_t *dp = base + (size_t)rows * ksb * 208 + ((size_t)sb * rows + row) * 2;
+    const float ds = __fmul_rn(half_at(dp), (float)(int8_t)rec[192 + i0 / 16]);
+    const uint8_t *ql = rec + t * 48 + (quarter % 2) * 16;
+    const uint8_t *qh = rec + t * 48 + 32;
+    const uint32_t low_shift = (quarter / 2) * 4, high_shift = quarter * 2;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int value = (int)(((ql[i] >> low_shift) & 15u) | (((qh[i] >> high_shift) & 3u) << 4)) - 32;
+        out[i] = __fmul_rn(ds, (float)value);
+    }
+}
+
 // F32 forms of the activations, as the reference's GPU kernels compute them
 // (inference/src/backends/metal/kernels/common.metal:6-16).
 __device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + expf(-x)); }

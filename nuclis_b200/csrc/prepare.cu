@@ -1,0 +1,61 @@
+// Planar re-layout of block-quantized matrices (no reference analogue).
+//
+// GGUF stores a Q6_K row as 210-byte blocks, so rows and blocks start on 2-byte
+// boundaries: no vector load and no bulk copy can address them. At load time
+// (the moment the reference wraps a tensor, inference/src/backends/metal/root.zig:217-230)
+// a matrix may be re-laid once into the same number of bytes:
+//
+//   Q6_K, layout 1 (rows a multiple of 16):
+//     main plane  [rows][superblocks][208]: for t = 0..3 (half hh = t >> 1 of the block, column
+//                 half ch = t & 1): 16 bytes ql[hh*64 + 16ch ..], 16 bytes ql[hh*64 + 32 + 16ch ..],
+//                 16 bytes qh[hh*32 + 16ch ..]; then the 16 scale bytes
+//     scale plane [superblocks][rows] f16: the d of each block, transposed
+//
+// Every byte is copied, none is changed: decoding the planar form gives the
+// values of the GGUF form bit for bit (dequant16_planar in nu_device.cuh).
+#include "kernels.hpp"
+#include "nu_device.cuh"
+
+namespace nu {
+
+uint32_t prepared_layout(uint32_t enc, uint32_t rows, uint32_t columns) {
+    if (enc == Q6_K && rows % 16 == 0 && columns % 256 == 0) return 1;
+    return 0;
+}
+
+__global__ void prepare_q6k_kernel(const uint8_t *src, uint8_t *dst, uint32_t rows, uint32_t ksb) {
+    const size_t blocks = (size_t)rows * ksb;
+    const size_t id = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (id >= blocks * 210) return;
+    const size_t block = id / 210;
+    const uint32_t b = (uint32_t)(id % 210);
+    const uint32_t row = (uint32_t)(block / ksb), sb = (uint32_t)(block % ksb);
+    const uint8_t *in = src + block * 210;
+    if (b < 192) {
+        const uint32_t t = b / 48, part = (b % 48) / 16, j = b % 16, hh = t >> 1, ch = t & 1;
+        const uint32_t from = part == 0 ? hh * 64 + 16 * ch + j : part == 1 ? hh * 64 + 32 + 16 * ch + j : 128 + hh * 32 + 16 * ch + j;
+        dst[block * 208 + b] = in[from];
+    } else if (b < 208) {
+        dst[block * 208 + b] = in[b];
+    } else {
+        dst[blocks * 208 + ((size_t)sb * rows + row) * 2 + (b - 208)] = in[b];
+    }
+}
+
+__global__ void copy_bytes_kernel(const uint8_t *src, uint8_t *dst, size_t n) {
+    const size_t id = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (id < n) dst[id] = src[id];
+}
+
+int launch_prepare(cudaStream_t s, uint32_t enc, const uint8_t *src, uint8_t *dst, uint32_t rows, uint32_t columns) {
+    const Layout l = layout(enc);
+    const size_t bytes = (size_t)rows * (columns / l.elements) * l.bytes;
+    if (prepared_layout(enc, rows, columns) == 1) {
+        prepare_q6k_kernel<<<(unsigned)((bytes + 255) / 256), 256, 0, s>>>(src, dst, rows, columns / 256);
+    } else {
+        copy_bytes_kernel<<<(unsigned)((bytes + 255) / 256), 256, 0, s>>>(src, dst, bytes);
+    }
+    return 1;
+}
+
+}  // namespace nu

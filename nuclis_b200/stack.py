@@ -83,6 +83,16 @@ class Stack:
                                                   (w.down, s.down_encoding, s.hidden, l.ffn_rows)]):
             synth.fill_matrix_torch(device_tensor(buf), e, rows, cols, seed * 8 + i)
 
+    def prepare_layer(self, w: LayerWeights) -> None:
+        """Load-time re-layout of the matrices whose GGUF rows the specialized kernels cannot address
+        (the Q6_K down projection): same bytes, same values. The GGUF copy is released."""
+        b = self.backend
+        raw = Matrix(self.m_down.encoding, self.m_down.rows, self.m_down.columns, self.m_down.bytes)
+        prepared, m = b.prepare(w.down, raw)
+        b.release(w.down)
+        w.down = prepared
+        self.m_down = m
+
     # ---- the recording of one step ----
     def record(self, allreduce: bool | None = None) -> int:
         """Records every layer's chain into the open recording; returns how many operators it recorded."""
@@ -151,12 +161,16 @@ def device_tensor(buf: Buffer):
 
 
 def make_stack(backend: Backend, tokens: int, layers: int, ranks: int = 1, rank: int = 0, seed: int = 0,
-               shapes: LayerShapes | None = None) -> Stack:
+               shapes: LayerShapes | None = None, prepare: bool = True) -> Stack:
     shapes = shapes or LayerShapes()
     st = Stack(backend, shapes, rank_shapes(shapes, ranks, rank), tokens)
     for i in range(layers):
         w = st.add_layer_buffers()
         st.fill_layer_torch(w, seed * 100003 + i * 64 + rank)
+        if prepare:
+            import torch
+            torch.cuda.synchronize()
+            st.prepare_layer(w)
     return st
 
 

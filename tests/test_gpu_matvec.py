@@ -255,3 +255,74 @@ def test_wrap_caches_by_address_and_ids_are_not_reused(backend):
     with pytest.raises(NuclisError):
         first.read()
     backend.release(fresh)
+
+
+# ---- the planar form of nu_cuda_matrix_prepare (Q6_K) ---------------------------------------------
+
+def test_prepared_q6_k_decodes_bit_for_bit(backend, golden_rows):
+    # golden blocks tiled into 16 rows, then random rows: every row of the prepared form decodes to
+    # the bits the CPU decoder gives for the GGUF form
+    row = next(r for r in golden_rows if r["encoding"] == enc.Q6_K)
+    for w, rows, columns in [(tiled_fixture_matrix(row, 16, 1280), 16, 1280), (make_case(enc.Q6_K, 48, 2304, 1, seed=77)[0], 48, 2304)]:
+        m = Matrix(enc.Q6_K, rows, columns, w.size)
+        wb = backend.wrap(w)
+        pb, pm = backend.prepare(wb, m)
+        assert pm.layout == 1 and pm.bytes == m.bytes
+        out = backend.create(columns * 4)
+        stride = w.size // rows
+        for token in (0, 1, rows // 2, rows - 1):
+            backend.begin()
+            backend.embed(pb, pm, token, out)
+            backend.commit()
+            want = oracle.row(enc.Q6_K, w[token * stride:(token + 1) * stride], columns)
+            assert np.array_equal(out.floats().view(np.uint32), want.view(np.uint32)), (rows, token)
+        backend.unwrap(w)
+        backend.release(pb)
+        backend.release(out)
+
+
+@pytest.mark.parametrize("shape", [(80, 1280), (4096, 4096), (17408, 5120), (5120, 17408)])
+@pytest.mark.parametrize("generic", [False, True])
+def test_prepared_q6_k_matvec_matches_oracle(backend, shape, generic):
+    rows, columns = shape
+    w, x, m = make_case(enc.Q6_K, rows, columns, 1, seed=21)
+    want, mag = expect(enc.Q6_K, rows, columns, w, x)
+    wb = backend.wrap(w)
+    pb, pm = backend.prepare(wb, m)
+    xb = backend.create(columns * 4)
+    yb = backend.create(rows * 4)
+    xb.write(x)
+    yb.write(np.full(rows, np.nan, dtype=np.float32))
+    backend.generic_only = generic
+    try:
+        backend.begin()
+        backend.matvec(pb, pm, xb, yb)
+        backend.commit()
+    finally:
+        backend.generic_only = False
+    assert_matvec_close(yb.floats(), want[0], mag[0], f"prepared Q6_K {shape} generic {generic}")
+    backend.unwrap(w)
+    for buf in (pb, xb, yb):
+        backend.release(buf)
+
+
+def test_prepare_contract(backend):
+    w, _, m = make_case(enc.Q6_K, 20, 512, 1, seed=5)  # 20 rows: not a multiple of 16, stays in GGUF form
+    wb = backend.wrap(w)
+    pb, pm = backend.prepare(wb, m)
+    assert pm.layout == 0 and np.array_equal(pb.read(), w)
+    w4, _, m4 = make_case(enc.Q4_K, 32, 512, 1, seed=5)  # Q4_K needs no re-layout
+    w4b = backend.wrap(w4)
+    p4b, p4m = backend.prepare(w4b, m4)
+    assert p4m.layout == 0 and np.array_equal(p4b.read(), w4)
+    with pytest.raises(NuclisError):
+        backend.prepare(wb, m, prepared=wb)  # overlapping
+    with pytest.raises(NuclisError):
+        backend.prepare(wb, Matrix(enc.Q6_K, 20, 512, w.size, layout=1))  # already prepared
+    backend.begin()
+    with pytest.raises(NuclisError) as e:
+        backend.matvec(wb, Matrix(enc.Q6_K, 20, 512, w.size, layout=7), backend.create(512 * 4), backend.create(20 * 4))
+    assert e.value.name == "InvalidShape"
+    backend.discard()
+    backend.unwrap(w)
+    backend.unwrap(w4)
