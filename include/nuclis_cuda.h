@@ -247,6 +247,8 @@ int nu_cuda_comm_init(nu_cuda *h, const uint8_t id[NU_COMM_ID_BYTES], int ranks,
 /* In-place sum over the group of `count` floats at `buffer`; recorded like an
  * operator (NCCL allreduce over NVLink on the handle's stream). */
 int nu_cuda_allreduce_sum_f32(nu_cuda *h, const nu_buffer *buffer, size_t count);
+/* Leaves the group. Every retained graph of the handle is released first (a graph
+ * that holds a collective keeps the communicator alive). */
 int nu_cuda_comm_destroy(nu_cuda *h);
 
 #ifdef __cplusplus

@@ -666,6 +666,13 @@ int Backend::commInit(const uint8_t *id, int ranks, int rank) {
     }
     ranks_ = ranks;
     rank_ = rank;
+    // NCCL sets its channels up at the first collective (allocations, a host exchange with the peers).
+    // That must not happen inside a stream capture: run one small allreduce here, on the scratch.
+    const int warm = g_nccl.AllReduce(partials_, partials_, 256, kNcclFloat, kNcclSum, comm_, stream_);
+    if (warm != 0 || cudaStreamSynchronize(stream_) != cudaSuccess) {
+        error_ = "comm_init: the warm-up allreduce failed";
+        return NU_ERR_COMM;
+    }
     return NU_OK;
 }
 
@@ -686,6 +693,13 @@ int Backend::allreduceSumF32(const Buffer &buffer, size_t count) {
 
 int Backend::commDestroy() {
     if (!comm_) return NU_OK;
+    if (recording_) return fail(NU_ERR_ALREADY_RECORDING, "comm_destroy: a recording is open");
+    // A retained graph that holds a collective keeps the communicator busy: NCCL waits for it.
+    // Retained graphs are therefore dropped with the group they may refer to.
+    cudaSetDevice(device_);
+    cudaStreamSynchronize(stream_);
+    for (auto &g : graphs_) cudaGraphExecDestroy(g.second);
+    graphs_.clear();
     g_nccl.CommDestroy(comm_);
     comm_ = nullptr;
     ranks_ = 1;

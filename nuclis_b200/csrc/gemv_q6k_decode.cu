@@ -92,7 +92,7 @@ struct Q6K {
             for (int h = 0; h < 2; ++h) {
                 const uint32_t sw = (hh ? ((qr >> 1) ? sc[h].w : sc[h].z) : ((qr >> 1) ? sc[h].y : sc[h].x)) ^ 0x80808080u;
                 const float fm = __uint_as_float(__byte_perm(sw, 0x4b000000u, 0x7650u + 2 * (qr & 1) + ch));  // 2^23 + sc + 128
-                const float ds = fmaf(fm, d[h], -8388736.0f * d[h]);                                          // d * sc
+                const float ds = (fm - 8388736.0f) * d[h];  // d * sc: the subtraction is exact, one rounding as in the decoder
                 const float inner = fmaf(c[2 * h] + c[2 * h + 1], 16777216.0f, bias);
                 acc[h] = fmaf(ds, inner, acc[h]);
             }

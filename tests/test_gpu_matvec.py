@@ -319,9 +319,10 @@ def test_prepare_contract(backend):
         backend.prepare(wb, m, prepared=wb)  # overlapping
     with pytest.raises(NuclisError):
         backend.prepare(wb, Matrix(enc.Q6_K, 20, 512, w.size, layout=1))  # already prepared
+    xb, yb = backend.create(512 * 4), backend.create(20 * 4)
     backend.begin()
     with pytest.raises(NuclisError) as e:
-        backend.matvec(wb, Matrix(enc.Q6_K, 20, 512, w.size, layout=7), backend.create(512 * 4), backend.create(20 * 4))
+        backend.matvec(wb, Matrix(enc.Q6_K, 20, 512, w.size, layout=7), xb, yb)
     assert e.value.name == "InvalidShape"
     backend.discard()
     backend.unwrap(w)
