@@ -235,6 +235,32 @@ int nu_cuda_gelu_mul_rows(nu_cuda *h, const nu_buffer *gate, const nu_buffer *up
 int nu_cuda_combine_experts(nu_cuda *h, const nu_buffer *values, const nu_buffer *weights, const nu_buffer *indices,
                             const nu_buffer *scales, const nu_buffer *output, const nu_combine_shape *shape);
 
+/* Q4_K decode GEMV for callers that must not allocate. It has no counterpart in the
+ * reference. Some hosts of this library run where device memory cannot be obtained at
+ * call time: inside another runtime's memory plan that has handed out all of its arena,
+ * in a plugin sandbox that forbids cudaMalloc, or in a real-time loop where an allocation's
+ * latency and failure mode are unacceptable. `nu_cuda_create` allocates its scratch with
+ * cudaMalloc; this entry point needs no handle and calls no cudaMalloc, cudaFree or
+ * allocating library routine. The split-K partial sums and arrival counters of the kernel
+ * live in an array inside the library image (about 1 MiB, held by every GPU that loads the
+ * library until the process exits).
+ *
+ *   weights  device pointer, 16-byte aligned: `rows` contiguous GGUF Q4_K rows of `columns`
+ *            values, `stride` = columns / 256 * 144 bytes apart
+ *   input    device pointer, 16-byte aligned: `columns` floats
+ *   output   device pointer: `rows` floats
+ *   stream   a cudaStream_t (NULL for the default stream); the call only enqueues work
+ *
+ * Limits: at most 65,536 rows, 20,480 columns and 1 MiB of partial sums; beyond them the
+ * call fails with NU_ERR_TOO_LARGE and a message in `err`, before anything is enqueued.
+ * The first call on a device looks the array's device address up and configures the kernel:
+ * make that first call outside any stream capture. All calls on a device share the one array,
+ * which keeps the previous call's contents (the counters are cleared at the start of each
+ * call): two calls whose kernels overlap on the GPU, on different streams, race on it.
+ * Results are those of nu_cuda_matvec on the same data. */
+int nu_cuda_matvec_q4k_static(const void *weights, size_t stride, uint32_t rows, uint32_t columns,
+                              const float *input, float *output, void *stream, char *err, size_t err_cap);
+
 /* ---- tensor-parallel collective (no reference analogue: the reference is
  * single-device) ---------------------------------------------------------- */
 

@@ -77,6 +77,7 @@ SIGNATURES = {
     "nu_cuda_matvec_experts": (cint, [vp, BP, EP, BP, sz, BP, sz, sz, BP, sz]),
     "nu_cuda_gelu_mul_rows": (cint, [vp, BP, BP, BP, sz, sz, sz, sz, sz]),
     "nu_cuda_combine_experts": (cint, [vp, BP, BP, BP, BP, BP, ctypes.POINTER(CCombineShape)]),
+    "nu_cuda_matvec_q4k_static": (cint, [vp, sz, u32, u32, vp, vp, vp, ctypes.c_char_p, sz]),
     "nu_cuda_comm_unique_id": (cint, [u8p]),
     "nu_cuda_comm_init": (cint, [vp, u8p, cint, cint]),
     "nu_cuda_allreduce_sum_f32": (cint, [vp, BP, sz]),

@@ -37,6 +37,8 @@
 // arrive for a row tile adds them in slice order. No sum depends on timing.
 #include "decode_kernel.cuh"
 
+#include "../../include/nuclis_cuda.h"
+
 namespace nu {
 namespace dec {
 
@@ -153,4 +155,67 @@ int launch_q4k_decode(cudaStream_t s, const FastJob &job) {
     return dec::launch<dec::Q4K>(s, job, p);
 }
 
+// ---- the entry point that allocates nothing ------------------------------------------------------
+// The split-K sums and arrival counters of the decode kernel normally live in memory the handle
+// allocated at creation. Here they live in an array that is part of the loaded library image.
+
+namespace {
+constexpr size_t kStaticPartialFloats = 256 * 1024;  // 1 MiB of partial sums
+constexpr size_t kStaticCounters = 4096;             // output tiles of 16 rows: matrices of up to 65,536 rows
+struct StaticScratch {
+    float partials[kStaticPartialFloats];
+    uint32_t counters[kStaticCounters + 1];  // + the status word the kernel raises when a bounded wait runs out
+};
+static __device__ __align__(256) StaticScratch g_static_scratch;
+
+struct StaticDevice {
+    bool ready = false;
+    StaticScratch *scratch = nullptr;  // the device address of g_static_scratch on this device
+    int sm_count = 0;
+};
+StaticDevice g_static_devices[64];
+}  // namespace
+
 }  // namespace nu
+
+extern "C" int nu_cuda_matvec_q4k_static(const void *weights, size_t stride, uint32_t rows, uint32_t columns, const float *input, float *output,
+                                         void *stream, char *err, size_t err_cap) {
+    using namespace nu;
+    auto fail = [&](int status, const char *what) {
+        if (err && err_cap) snprintf(err, err_cap, "%s", what);
+        return status;
+    };
+    if (!weights || !input || !output || rows == 0 || columns == 0) return fail(NU_ERR_INVALID_SHAPE, "matvec_q4k_static: null pointer or empty shape");
+    if (columns % 256 != 0 || stride != (size_t)columns / 256 * 144) return fail(NU_ERR_INVALID_SHAPE, "matvec_q4k_static: rows must be whole, contiguous Q4_K superblocks");
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return fail(NU_ERR_INIT, "matvec_q4k_static: no current CUDA device");
+    StaticDevice &d = g_static_devices[device];
+    if (!d.ready) {
+        // Once per device, with that device current: in host code the array's name is only a stand-in,
+        // the kernel needs the address the symbol has on this device.
+        void *ptr = nullptr;
+        cudaDeviceProp prop{};
+        if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || !ptr) return fail(NU_ERR_INIT, "matvec_q4k_static: cudaGetSymbolAddress failed");
+        if (cudaGetDeviceProperties(&prop, device) != cudaSuccess || prop.major != 10) return fail(NU_ERR_INIT, "matvec_q4k_static: needs an sm_100 device");
+        if (!q4k_decode_configure()) return fail(NU_ERR_INIT, "matvec_q4k_static: kernel set-up failed");
+        d.scratch = (StaticScratch *)ptr;
+        d.sm_count = prop.multiProcessorCount;
+        d.ready = true;
+    }
+    FastJob job{};
+    job.enc = Q4_K; job.layout = 0; job.columns = columns; job.tokens = 1; job.in = input; job.in_stride = columns;
+    job.count = 1; job.mode = ACT_NONE;
+    job.seg[0] = {(const uint8_t *)weights, stride, rows, output, rows};
+    job.partials = d.scratch->partials; job.partials_floats = kStaticPartialFloats;
+    job.counters = d.scratch->counters; job.counters_len = kStaticCounters;
+    job.sm_count = d.sm_count;
+    dec::Params p;
+    if (!dec::fill(job, p, true))
+        return fail(NU_ERR_TOO_LARGE, "matvec_q4k_static: beyond the built-in scratch (65,536 rows, 20,480 columns, 1 MiB of partial sums) or pointers not 16-byte aligned");
+    cudaStream_t s = (cudaStream_t)stream;
+    // The array keeps whatever the last call left: the counters and the status word must start at zero.
+    if (cudaMemsetAsync(d.scratch->counters, 0, sizeof d.scratch->counters, s) != cudaSuccess) return fail(NU_ERR_EXECUTION, "matvec_q4k_static: clearing the counters failed");
+    dec::launch<dec::Q4K>(s, job, p);
+    if (cudaGetLastError() != cudaSuccess) return fail(NU_ERR_EXECUTION, "matvec_q4k_static: launch failed");
+    return NU_OK;
+}
