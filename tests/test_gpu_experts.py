@@ -1,0 +1,135 @@
+"""GPU parity of the mixture-of-experts operators against the CPU oracle.
+
+Follows the reference's expert checks (inference/metal-check.zig:1594-1648 router with ties,
+:1711-1727 gathered matvec with poisoned unselected experts, :1760-1831 decode chain against
+cpu.experts.ffn at 2e-5 * (1 + max|y|)). Shapes: the 26B-A4B-style config (128 experts, top-8,
+hidden 2816, expert intermediate 704; gate_up fused as [experts][2*ff][hidden] Q4_K, down as
+[experts][hidden][ff] in Q8_0, the block size a 704-wide row is stored in).
+"""
+import numpy as np
+import pytest
+
+import oracle
+from nuclis_b200 import Backend, CombineShape, ExpertMatrix, NuclisError, encoding as enc, synth
+
+pytestmark = pytest.mark.gpu
+
+EXPERTS, K, HIDDEN, FF = 128, 8, 2816, 704
+
+
+@pytest.fixture(scope="module")
+def backend():
+    b = Backend(0)
+    yield b
+    b.deinit()
+
+
+@pytest.fixture(scope="module")
+def tensors():
+    gate_up = synth.matrix(enc.Q4_K, EXPERTS * 2 * FF, HIDDEN, seed=901)
+    down = synth.matrix(enc.Q8_0, EXPERTS * HIDDEN, FF, seed=902)
+    return gate_up, down
+
+
+def test_router_indices_exact_and_weights_close(backend):
+    rng = np.random.default_rng(5)
+    rows = 9
+    logits = rng.standard_normal((rows, EXPERTS)).astype(np.float32)
+    logits[0, 3] = logits[0, 77] = logits[0].max() + 1.0   # a tie at the top: lowest index first
+    logits[1, :] = 0.25                                     # all equal
+    logits[2, 5] = -800.0
+    lb = backend.create(logits.nbytes)
+    ib = backend.create(rows * K * 4)
+    wb = backend.create(rows * K * 4)
+    lb.write(logits)
+    backend.begin()
+    backend.route(lb, EXPERTS, K, rows, EXPERTS, ib, wb)
+    backend.commit()
+    idx = ib.read(np.uint32).reshape(rows, K)
+    w = wb.floats().reshape(rows, K)
+    for r in range(rows):
+        want_idx, want_w = oracle.route(logits[r], K)
+        assert np.array_equal(idx[r], want_idx), r
+        assert np.max(np.abs(w[r] - want_w)) <= 1e-6, r
+    with pytest.raises(NuclisError):
+        backend.begin()
+        try:
+            backend.route(lb, EXPERTS, EXPERTS + 1, rows, EXPERTS, ib, wb)
+        finally:
+            backend.discard()
+    for buf in (lb, ib, wb):
+        backend.release(buf)
+
+
+@pytest.mark.parametrize("tokens", [1, 8])
+def test_expert_chain_matches_cpu_ffn(backend, tensors, tokens):
+    gate_up, down = tensors
+    rng = np.random.default_rng(17 + tokens)
+    x = rng.standard_normal((tokens, HIDDEN)).astype(np.float32)
+    logits = rng.standard_normal((tokens, EXPERTS)).astype(np.float32)
+    scales = (0.5 + rng.random(EXPERTS)).astype(np.float32)
+    gu_t = ExpertMatrix(enc.Q4_K, EXPERTS, 2 * FF, HIDDEN, gate_up.size)
+    dn_t = ExpertMatrix(enc.Q8_0, EXPERTS, HIDDEN, FF, down.size)
+    slots = tokens * K
+    gub, dnb = backend.wrap(gate_up), backend.wrap(down)
+    xb = backend.create(x.nbytes)
+    lb = backend.create(logits.nbytes)
+    sb = backend.create(scales.nbytes)
+    ib = backend.create(slots * 4)
+    wb = backend.create(slots * 4)
+    gu_out = backend.create(slots * 2 * FF * 4)
+    hid = backend.create(slots * FF * 4)
+    y = backend.create(slots * HIDDEN * 4)
+    out = backend.create(tokens * HIDDEN * 4)
+    xb.write(x); lb.write(logits); sb.write(scales)
+    backend.begin()
+    backend.route(lb, EXPERTS, K, tokens, EXPERTS, ib, wb)
+    # gate-up: the k slots of a token share its input row (in_group = k); one token: in_stride 0 shares the row
+    backend.matvec_experts_grouped(gub, gu_t, ib, slots, xb, HIDDEN if tokens > 1 else 0, K if tokens > 1 else 1, gu_out, 2 * FF)
+    backend.gelu_mul_rows(gu_out, gu_out.slice(FF * 4, gu_out.len - FF * 4), hid, FF, slots, 2 * FF, 2 * FF, FF)
+    backend.matvec_experts(dnb, dn_t, ib, slots, hid, FF, y, HIDDEN)
+    backend.combine_experts(y, wb, ib, sb, out, CombineShape(columns=HIDDEN, slots=K, experts=EXPERTS, in_stride=HIDDEN, out_stride=HIDDEN, rows=tokens))
+    backend.commit()
+    got = out.floats().reshape(tokens, HIDDEN)
+    for t in range(tokens):
+        idx, w = oracle.route(logits[t], K)
+        want = oracle.ffn((enc.Q4_K, EXPERTS, 2 * FF, HIDDEN, gate_up), (enc.Q8_0, EXPERTS, HIDDEN, FF, down), x[t], idx, w, down_scale=scales)
+        bound = 2e-5 * (1 + np.max(np.abs(want)))
+        assert np.max(np.abs(got[t] - want)) <= bound, (t, np.max(np.abs(got[t] - want)), bound)
+    backend.unwrap(gate_up); backend.unwrap(down)
+    for buf in (xb, lb, sb, ib, wb, gu_out, hid, y, out):
+        backend.release(buf)
+
+
+def test_gathered_matvec_reads_only_selected_experts(backend):
+    # unselected experts hold NaN-decoding bytes (scale 0x7e00): a stray read poisons the output
+    experts, rows, cols = 6, 32, 256
+    good = synth.matrix(enc.Q8_0, experts * rows, cols, seed=3).reshape(experts, -1).copy()
+    per = good.shape[1]
+    selected = [4, 1]
+    for e in range(experts):
+        if e not in selected:
+            good[e].reshape(-1, 34)[:, 0:2] = [0x00, 0x7E]
+    data = good.reshape(-1)
+    t = ExpertMatrix(enc.Q8_0, experts, rows, cols, data.size)
+    x = np.random.default_rng(1).standard_normal(cols).astype(np.float32)
+    wb = backend.wrap(data)
+    xb = backend.create(cols * 4); xb.write(x)
+    ib = backend.create(8); ib.write(np.array(selected, dtype=np.uint32))
+    yb = backend.create(2 * rows * 4)
+    backend.begin()
+    backend.matvec_experts(wb, t, ib, 2, xb, 0, yb, rows)
+    backend.commit()
+    got = yb.floats().reshape(2, rows)
+    for s, e in enumerate(selected):
+        want = oracle.matvec(enc.Q8_0, rows, cols, data[e * per:(e + 1) * per], x)
+        assert np.all(np.isfinite(got[s]))
+        assert np.allclose(got[s], want, rtol=1e-5, atol=1e-5)
+    # an index past the tensor is clamped, never read out of bounds
+    ib.write(np.array([99, 1], dtype=np.uint32))
+    backend.begin()
+    backend.matvec_experts(wb, t, ib, 2, xb, 0, yb, rows)
+    backend.commit()
+    backend.unwrap(data)
+    for buf in (xb, ib, yb):
+        backend.release(buf)
