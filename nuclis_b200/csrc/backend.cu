@@ -452,7 +452,7 @@ int Backend::matmul(const Buffer &weights, const Matrix &m, const Buffer &input,
     if (input.offset % 16 != 0 || in_stride % 4 != 0 || output.offset % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "matmul: alignment");
     if (int rc = needRecording()) return rc;
     bool done = false;
-    if (!generic_only && in_dtype == NU_F32 && tokens <= 64) {
+    if (!generic_only && in_dtype == NU_F32 && tokens <= 32) {
         // Up to 8 tokens in one pass of the weights; a few more in passes of 8.
         FastJob job{};
         job.enc = m.encoding; job.layout = m.layout; job.columns = (uint32_t)m.columns; job.count = 1; job.mode = ACT_NONE; job.in_stride = in_stride;
@@ -467,6 +467,24 @@ int Backend::matmul(const Buffer &weights, const Matrix &m, const Buffer &input,
                 job.seg[0].out = out + t0 * out_stride;
                 launches_ += launch_fast(stream_, job);
             }
+            done = true;
+        }
+    }
+    if (!done && !generic_only && tokens > 8) {
+        // Many token rows: the tensor-core prefill tile. F32 activations are first rounded to BF16 into
+        // the handle's scratch when they fit there (the reference's tiles round them to half the same way).
+        PrefillJob pj{};
+        pj.enc = m.encoding; pj.layout = m.layout; pj.w = w; pj.stride = stride; pj.rows = (uint32_t)m.rows; pj.columns = (uint32_t)m.columns;
+        pj.tokens = (uint32_t)tokens; pj.padded_tokens = (uint32_t)padded; pj.out = out; pj.out_stride = out_stride;
+        pj.status = counters_ + counters_len_;
+        if (in_dtype == NU_BF16) {
+            pj.in = in; pj.in_stride = in_stride;
+        } else if (padded * m.columns * 2 <= partials_floats_ * sizeof(float)) {
+            pj.in = partials_; pj.in_stride = m.columns;
+        }
+        if (pj.in && prefill_supported(pj)) {
+            if (in_dtype != NU_BF16) launches_ += launch_f32_to_bf16_rows(stream_, (const float *)in, in_stride, partials_, m.columns, (uint32_t)m.columns, (uint32_t)tokens);
+            launches_ += launch_prefill(stream_, pj);
             done = true;
         }
     }

@@ -714,6 +714,20 @@ static EncodeTiledFn encode_tiled() {
     return fn;
 }
 
+// A two-dimensional tensor [outer][inner] of `elem_bytes`-wide elements, `stride_bytes` between rows.
+bool encode_tiled_map(CUtensorMap *map, CUtensorMapDataType type, uint32_t elem_bytes, const void *base, uint64_t inner, uint64_t outer,
+                      uint64_t stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return false;
+    (void)elem_bytes;
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {stride_bytes};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, type, 2, (void *)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // A uint8 tensor [rows][row_bytes] with `stride` bytes between rows, copied in boxes of box_rows x box_bytes.
 bool encode_weight_map(CUtensorMap *map, const uint8_t *base, uint64_t row_bytes, uint64_t rows, uint64_t stride, uint32_t box_bytes, uint32_t box_rows) {
     EncodeTiledFn fn = encode_tiled();
@@ -796,7 +810,7 @@ static bool configure_variant() {
 }
 
 bool fast_configure() {
-    return q4k_decode_configure() && q6k_decode_configure() && configure_variant<Q4_K, 1>() && configure_variant<Q4_K, 2>() && configure_variant<Q4_K, 4>() && configure_variant<Q4_K, 8>();
+    return q4k_decode_configure() && q6k_decode_configure() && prefill_configure() && configure_variant<Q4_K, 1>() && configure_variant<Q4_K, 2>() && configure_variant<Q4_K, 4>() && configure_variant<Q4_K, 8>();
 }
 
 template <int ENC, int TS>

@@ -77,6 +77,24 @@ bool q6k_decode_configure();
 bool q6k_decode_supported(const FastJob &job);
 int launch_q6k_decode(cudaStream_t s, const FastJob &job);
 
+// ---- prefill GEMM on tcgen05 (many token rows, bf16 operands, f32 accumulate) -------
+struct PrefillJob {
+    uint32_t enc, layout;
+    const uint8_t *w;
+    size_t stride;
+    uint32_t rows, columns;
+    const void *in;          // bf16 [padded_tokens][in_stride]
+    size_t in_stride;        // in elements
+    uint32_t tokens, padded_tokens;
+    float *out;              // [tokens][out_stride]
+    size_t out_stride;
+    uint32_t *status;
+};
+bool prefill_configure();
+bool prefill_supported(const PrefillJob &job);
+int launch_prefill(cudaStream_t s, const PrefillJob &job);
+int launch_f32_to_bf16_rows(cudaStream_t s, const float *in, size_t in_stride, void *out, size_t out_stride, uint32_t columns, uint32_t tokens);
+
 // ---- planar re-layout of a matrix for the specialized kernels ---------------------
 // Layout the matrix takes after preparation: 0 when the specialized kernels read the GGUF rows as they are.
 uint32_t prepared_layout(uint32_t enc, uint32_t rows, uint32_t columns);

@@ -1,0 +1,119 @@
+"""GPU parity of the prefill GEMM (tensor-core tiles, bf16 operands, f32 accumulate) against the
+CPU oracle evaluated on the bf16-rounded activations. Stated bound of this path: relative L2
+<= 2e-2; per element we hold it to 4e-3 * sum|w*x| + 1e-6 (both operands rounded to 8 bits).
+Mirrors the reference's batched checks (inference/metal-check.zig:4357-4469: 40 rows x
+{1280, 5120} columns x tokens {37, 20, 16, 9, 8, 5, 1}, half tiles within 2e-4 * sum|w*x|)."""
+import numpy as np
+import pytest
+
+import oracle
+from nuclis_b200 import Backend, Matrix, NuclisError, encoding as enc, synth
+from parity import rel_l2
+
+pytestmark = pytest.mark.gpu
+
+BF16 = enc.BF16
+
+
+def to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """float32 -> bfloat16 bit patterns, round to nearest even."""
+    b = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    return ((b + 0x7FFF + ((b >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def from_bf16_bits(h: np.ndarray) -> np.ndarray:
+    return (h.astype(np.uint32) << 16).view(np.float32)
+
+
+@pytest.fixture(scope="module")
+def backend():
+    b = Backend(0)
+    yield b
+    b.deinit()
+
+
+def run_matmul(b, w, m, x, in_dtype, check_tokens=None, prepare=False):
+    tokens, columns = x.shape
+    padded = Backend.matmul_padded(tokens)
+    wb = b.wrap(w)
+    mm = m
+    pb = None
+    if prepare:
+        pb, mm = b.prepare(wb, m)
+    if in_dtype == BF16:
+        xin = np.zeros((padded, columns), dtype=np.uint16)
+        xin[:tokens] = to_bf16_bits(x)
+        xr = from_bf16_bits(xin[:tokens])
+    else:
+        xin = np.zeros((padded, columns), dtype=np.float32)
+        xin[:tokens] = x
+        xr = from_bf16_bits(to_bf16_bits(x)) if tokens > 8 else x
+    xb = b.create(xin.nbytes)
+    yb = b.create(padded * m.rows * 4)
+    xb.write(xin)
+    yb.write(np.full(padded * m.rows, np.nan, dtype=np.float32))
+    b.begin()
+    b.matmul(pb if prepare else wb, mm, xb, columns, yb, m.rows, tokens, in_dtype=in_dtype)
+    b.commit()
+    got = yb.floats().reshape(padded, m.rows)[:tokens]
+    b.unwrap(w)
+    for buf in (xb, yb) + ((pb,) if pb is not None else ()):
+        b.release(buf)
+    rows_to_check = range(tokens) if check_tokens is None else check_tokens
+    for t in rows_to_check:
+        want = oracle.matvec(m.encoding, m.rows, m.columns, w, xr[t])
+        mag = oracle.matvec_abs(m.encoding, m.rows, m.columns, w, xr[t])
+        assert np.all(np.isfinite(got[t])), f"token {t}: non-finite"
+        worst = np.max(np.abs(got[t] - want) / (4e-3 * mag + 1e-6))
+        assert worst <= 1.0, f"token {t}: element error {worst:.2f}x the bound"
+        assert rel_l2(got[t], want) <= 2e-2
+    return got
+
+
+@pytest.mark.parametrize("encoding", [enc.Q4_K, enc.Q6_K, enc.Q8_0])
+@pytest.mark.parametrize("tokens", [9, 37, 64, 130, 300])
+def test_prefill_tiles_match_oracle(backend, encoding, tokens):
+    rows, columns = 136, 1280   # 136 rows: one full 128-row tile and a ragged one
+    w = synth.matrix(encoding, rows, columns, seed=60 + tokens)
+    x = synth.activations(tokens, columns, seed=61 + tokens)
+    run_matmul(backend, w, Matrix(encoding, rows, columns, w.size), x, BF16)
+
+
+def test_prefill_accepts_f32_activations_and_the_planar_form(backend):
+    rows, columns, tokens = 256, 2304, 40
+    w = synth.matrix(enc.Q6_K, rows, columns, seed=70)
+    x = synth.activations(tokens, columns, seed=71)
+    m = Matrix(enc.Q6_K, rows, columns, w.size)
+    a = run_matmul(backend, w, m, x, enc.F32)
+    c = run_matmul(backend, w, m, x, enc.F32, prepare=True)
+    assert np.array_equal(a, c)  # the planar form decodes to the same bits, so the same products
+
+
+@pytest.mark.parametrize("case", [(enc.Q4_K, 17408, 5120, False), (enc.Q6_K, 5120, 17408, True)])
+def test_prefill_config_shapes_at_512_tokens(backend, case):
+    encoding, rows, columns, prepare = case
+    tokens = 512
+    w = synth.matrix(encoding, rows, columns, seed=80)
+    x = synth.activations(tokens, columns, seed=81)
+    # the oracle costs about 0.1 s per token row here: check a sample of the token rows in full
+    run_matmul(backend, w, Matrix(encoding, rows, columns, w.size), x, BF16, check_tokens=[0, 1, 255, 256, 511], prepare=prepare)
+
+
+def test_prefill_contract(backend):
+    rows, columns = 128, 512
+    w = synth.matrix(enc.Q4_K, rows, columns, seed=1)
+    wb = backend.wrap(w)
+    m = Matrix(enc.Q4_K, rows, columns, w.size)
+    xb = backend.create(64 * columns * 2)
+    yb = backend.create(64 * rows * 4)
+    backend.begin()
+    with pytest.raises(NuclisError):
+        backend.matmul(wb, m, xb, columns, yb, rows, 65, in_dtype=BF16)   # buffers hold 64 rows, 65 tokens need 128
+    with pytest.raises(NuclisError):
+        backend.matmul(wb, Matrix(enc.Q4_K, rows + 4, columns, w.size), xb, columns, yb, rows + 4, 16, in_dtype=BF16)  # rows % 8
+    with pytest.raises(NuclisError):
+        backend.matmul(wb, m, xb, columns, yb, rows, 16, in_dtype=7)
+    backend.discard()
+    backend.unwrap(w)
+    backend.release(xb)
+    backend.release(yb)
