@@ -20,6 +20,8 @@
 
 namespace nu {
 
+struct FastJob;
+
 using Buffer = nu_buffer;
 using Matrix = nu_matrix;
 using ExpertMatrix = nu_expert_matrix;
@@ -100,6 +102,7 @@ private:
     int finishCapture(cudaGraphExec_t *exec);
     int runGraph(cudaGraphExec_t exec, uint32_t count, float *elapsed_ms);
     int checkKernelStatus();
+    bool decodePasses(FastJob job, const float *in, size_t in_stride, float *out, size_t out_stride, uint32_t tokens);
 
     int device_ = 0;
     int sm_count_ = 0;

@@ -47,7 +47,7 @@ struct FastSegment {
 };
 struct FastJob {
     uint32_t enc;
-    uint32_t layout;  // 0: GGUF rows; 1: the planar form made by launch_prepare (see prepare.cu)
+    uint32_t layout;  // 0: GGUF rows; 1, 2: the planar forms made by launch_prepare (see prepare.cu)
     uint32_t columns;
     uint32_t tokens;  // 1..8
     const float *in;  // [tokens][in_stride]
@@ -76,6 +76,9 @@ int launch_q4k_decode(cudaStream_t s, const FastJob &job);
 bool q6k_decode_configure();
 bool q6k_decode_supported(const FastJob &job);
 int launch_q6k_decode(cudaStream_t s, const FastJob &job);
+bool q8_0_decode_configure();
+bool q8_0_decode_supported(const FastJob &job);
+int launch_q8_0_decode(cudaStream_t s, const FastJob &job);
 
 // ---- prefill GEMM on tcgen05 (many token rows, bf16 operands, f32 accumulate) -------
 struct PrefillJob {

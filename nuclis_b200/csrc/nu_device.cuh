@@ -124,6 +124,15 @@ __device__ __forceinline__ void dequant16_planar_q6k(const uint8_t *base, uint32
     }
 }
 
+// The same from the planar form of a Q8_0 matrix (prepare.cu).
+__device__ __forceinline__ void dequant16_planar_q8_0(const uint8_t *base, uint32_t rows, uint32_t columns, uint32_t row, uint32_t seg, float out[16]) {
+    const uint8_t *q = base + (size_t)row * columns + (size_t)seg * 16;
+    const uint8_t *dp = base + (size_t)rows * columns + ((size_t)(seg / 2) * rows + row) * 2;
+    const float d = half_at(dp);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) out[i] = __fmul_rn(d, (float)(int8_t)q[i]);
+}
+
 // F32 forms of the activations, as the reference's GPU kernels compute them
 // (inference/src/backends/metal/kernels/common.metal:6-16).
 __device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + expf(-x)); }

@@ -115,6 +115,7 @@ __device__ __forceinline__ void decode64(const Params &p, uint32_t r, uint32_t k
     for (int s = 0; s < 4; ++s) {
         float v[16];
         if (p.layout == 1) dequant16_planar_q6k(p.w, p.rows, p.columns / 256, r, k0 / 16 + s, v);
+        else if (p.layout == 2) dequant16_planar_q8_0(p.w, p.rows, p.columns, r, k0 / 16 + s, v);
         else dequant16(p.enc, p.w + (size_t)r * p.stride, k0 / 16 + s, v);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {

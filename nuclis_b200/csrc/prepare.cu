@@ -11,6 +11,10 @@
 //                 16 bytes qh[hh*32 + 16ch ..]; then the 16 scale bytes
 //     scale plane [superblocks][rows] f16: the d of each block, transposed
 //
+//   Q8_0, layout 2 (rows a multiple of 16, columns a multiple of 256):
+//     code plane  [rows][columns] int8: the 32 codes of each block, blocks in row order
+//     scale plane [columns/32][rows] f16: the d of each block, transposed
+//
 // Every byte is copied, none is changed: decoding the planar form gives the
 // values of the GGUF form bit for bit (dequant16_planar in nu_device.cuh).
 #include "kernels.hpp"
@@ -20,6 +24,7 @@ namespace nu {
 
 uint32_t prepared_layout(uint32_t enc, uint32_t rows, uint32_t columns) {
     if (enc == Q6_K && rows % 16 == 0 && columns % 256 == 0) return 1;
+    if (enc == Q8_0 && rows % 16 == 0 && columns % 256 == 0) return 2;
     return 0;
 }
 
@@ -42,6 +47,17 @@ __global__ void prepare_q6k_kernel(const uint8_t *src, uint8_t *dst, uint32_t ro
     }
 }
 
+__global__ void prepare_q8_0_kernel(const uint8_t *src, uint8_t *dst, uint32_t rows, uint32_t kb) {
+    const size_t blocks = (size_t)rows * kb;
+    const size_t id = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (id >= blocks * 34) return;
+    const size_t block = id / 34;
+    const uint32_t b = (uint32_t)(id % 34);
+    const uint32_t row = (uint32_t)(block / kb), blk = (uint32_t)(block % kb);
+    if (b >= 2) dst[block * 32 + (b - 2)] = src[id];
+    else dst[blocks * 32 + ((size_t)blk * rows + row) * 2 + b] = src[id];
+}
+
 __global__ void copy_bytes_kernel(const uint8_t *src, uint8_t *dst, size_t n) {
     const size_t id = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (id < n) dst[id] = src[id];
@@ -50,8 +66,11 @@ __global__ void copy_bytes_kernel(const uint8_t *src, uint8_t *dst, size_t n) {
 int launch_prepare(cudaStream_t s, uint32_t enc, const uint8_t *src, uint8_t *dst, uint32_t rows, uint32_t columns) {
     const Layout l = layout(enc);
     const size_t bytes = (size_t)rows * (columns / l.elements) * l.bytes;
-    if (prepared_layout(enc, rows, columns) == 1) {
+    const uint32_t to = prepared_layout(enc, rows, columns);
+    if (to == 1) {
         prepare_q6k_kernel<<<(unsigned)((bytes + 255) / 256), 256, 0, s>>>(src, dst, rows, columns / 256);
+    } else if (to == 2) {
+        prepare_q8_0_kernel<<<(unsigned)((bytes + 255) / 256), 256, 0, s>>>(src, dst, rows, columns / 32);
     } else {
         copy_bytes_kernel<<<(unsigned)((bytes + 255) / 256), 256, 0, s>>>(src, dst, bytes);
     }

@@ -259,34 +259,39 @@ def test_wrap_caches_by_address_and_ids_are_not_reused(backend):
 
 # ---- the planar form of nu_cuda_matrix_prepare (Q6_K) ---------------------------------------------
 
-def test_prepared_q6_k_decodes_bit_for_bit(backend, golden_rows):
+PLANAR = {enc.Q6_K: 1, enc.Q8_0: 2}
+
+
+@pytest.mark.parametrize("encoding", [enc.Q6_K, enc.Q8_0])
+def test_prepared_form_decodes_bit_for_bit(backend, golden_rows, encoding):
     # golden blocks tiled into 16 rows, then random rows: every row of the prepared form decodes to
     # the bits the CPU decoder gives for the GGUF form
-    row = next(r for r in golden_rows if r["encoding"] == enc.Q6_K)
-    for w, rows, columns in [(tiled_fixture_matrix(row, 16, 1280), 16, 1280), (make_case(enc.Q6_K, 48, 2304, 1, seed=77)[0], 48, 2304)]:
-        m = Matrix(enc.Q6_K, rows, columns, w.size)
+    row = next(r for r in golden_rows if r["encoding"] == encoding)
+    for w, rows, columns in [(tiled_fixture_matrix(row, 16, 1280), 16, 1280), (make_case(encoding, 48, 2304, 1, seed=77)[0], 48, 2304)]:
+        m = Matrix(encoding, rows, columns, w.size)
         wb = backend.wrap(w)
         pb, pm = backend.prepare(wb, m)
-        assert pm.layout == 1 and pm.bytes == m.bytes
+        assert pm.layout == PLANAR[encoding] and pm.bytes == m.bytes
         out = backend.create(columns * 4)
         stride = w.size // rows
         for token in (0, 1, rows // 2, rows - 1):
             backend.begin()
             backend.embed(pb, pm, token, out)
             backend.commit()
-            want = oracle.row(enc.Q6_K, w[token * stride:(token + 1) * stride], columns)
+            want = oracle.row(encoding, w[token * stride:(token + 1) * stride], columns)
             assert np.array_equal(out.floats().view(np.uint32), want.view(np.uint32)), (rows, token)
         backend.unwrap(w)
         backend.release(pb)
         backend.release(out)
 
 
+@pytest.mark.parametrize("encoding", [enc.Q6_K, enc.Q8_0])
 @pytest.mark.parametrize("shape", [(80, 1280), (4096, 4096), (17408, 5120), (5120, 17408)])
 @pytest.mark.parametrize("generic", [False, True])
-def test_prepared_q6_k_matvec_matches_oracle(backend, shape, generic):
+def test_prepared_matvec_matches_oracle(backend, encoding, shape, generic):
     rows, columns = shape
-    w, x, m = make_case(enc.Q6_K, rows, columns, 1, seed=21)
-    want, mag = expect(enc.Q6_K, rows, columns, w, x)
+    w, x, m = make_case(encoding, rows, columns, 1, seed=21)
+    want, mag = expect(encoding, rows, columns, w, x)
     wb = backend.wrap(w)
     pb, pm = backend.prepare(wb, m)
     xb = backend.create(columns * 4)
@@ -300,7 +305,7 @@ def test_prepared_q6_k_matvec_matches_oracle(backend, shape, generic):
         backend.commit()
     finally:
         backend.generic_only = False
-    assert_matvec_close(yb.floats(), want[0], mag[0], f"prepared Q6_K {shape} generic {generic}")
+    assert_matvec_close(yb.floats(), want[0], mag[0], f"prepared enc {encoding} {shape} generic {generic}")
     backend.unwrap(w)
     for buf in (pb, xb, yb):
         backend.release(buf)
@@ -327,3 +332,23 @@ def test_prepare_contract(backend):
     backend.discard()
     backend.unwrap(w)
     backend.unwrap(w4)
+
+
+@pytest.mark.parametrize("encoding", [enc.Q6_K, enc.Q8_0])
+@pytest.mark.parametrize("tokens", [2, 8])
+def test_prepared_matvec_rows_match_oracle(backend, encoding, tokens):
+    rows, columns = 1056, 2304
+    w, x, m = make_case(encoding, rows, columns, tokens, seed=91 + tokens)
+    want, mag = expect(encoding, rows, columns, w, x)
+    wb = backend.wrap(w)
+    pb, pm = backend.prepare(wb, m)
+    xb = backend.create(x.nbytes)
+    yb = backend.create(tokens * rows * 4)
+    xb.write(x)
+    backend.begin()
+    backend.matvec_rows(pb, pm, xb, columns, yb, rows, tokens)
+    backend.commit()
+    assert_matvec_close(yb.floats().reshape(tokens, rows), want, mag, f"prepared rows enc {encoding} tokens {tokens}")
+    backend.unwrap(w)
+    for buf in (pb, xb, yb):
+        backend.release(buf)
