@@ -163,9 +163,8 @@ def run_gpu(args, rank: int, world: int, local: int):
         dist.init_process_group("gloo", rank=rank, world_size=world)
     b = Backend(local)
     if world > 1:
-        uid = [Backend.comm_unique_id() if rank == 0 else None]
-        dist.broadcast_object_list(uid, src=0)
-        b.comm_init(uid[0], world, rank)
+        from nuclis_b200.group import join, torch_all_gather
+        join(b, rank, world, torch_all_gather(), peer_memory=not args.nccl_only)
     tokens = args.tokens
     stack = make_stack(b, tokens, LAYERS, ranks=world, rank=rank, seed=args.seed)
     torch.cuda.synchronize()
@@ -277,6 +276,7 @@ def main():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--cpu-layers", type=int, default=4)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--nccl-only", action="store_true", help="sum the short vectors with NCCL instead of the peer-memory allreduce")
     args = ap.parse_args()
     rank, world, local = dist_env()
     if args.impl == "reference":

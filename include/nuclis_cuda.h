@@ -270,9 +270,19 @@ enum { NU_COMM_ID_BYTES = 128 };
 int nu_cuda_comm_unique_id(uint8_t id[NU_COMM_ID_BYTES]);
 /* Joins this handle to a group of `ranks` handles (one per GPU). Collective. */
 int nu_cuda_comm_init(nu_cuda *h, const uint8_t id[NU_COMM_ID_BYTES], int ranks, int rank);
-/* In-place sum over the group of `count` floats at `buffer`; recorded like an
- * operator (NCCL allreduce over NVLink on the handle's stream). */
+/* In-place sum over the group of `count` floats at `buffer` (16-byte aligned); recorded like an
+ * operator. */
 int nu_cuda_allreduce_sum_f32(nu_cuda *h, const nu_buffer *buffer, size_t count);
+/* One-shot allreduce over peer memory for short vectors (at most 65,536 floats): at 20 KB a
+ * collective is pure latency, and this path costs a peer store, a flag and a local sum instead of
+ * a library call. Each rank calls nu_cuda_comm_peer_handle (it allocates the rank's inbox and
+ * returns a 64-byte interprocess handle), the handles travel to every rank by any means, ordered by
+ * rank, and each rank calls nu_cuda_comm_attach_peers with all of them. From then on
+ * nu_cuda_allreduce_sum_f32 uses this path for vectors that fit and NCCL (if a group was joined)
+ * for longer ones. All ranks must make the same sequence of allreduce calls. One process per GPU. */
+enum { NU_PEER_HANDLE_BYTES = 64 };
+int nu_cuda_comm_peer_handle(nu_cuda *h, uint8_t handle[NU_PEER_HANDLE_BYTES]);
+int nu_cuda_comm_attach_peers(nu_cuda *h, const uint8_t *handles, int ranks, int rank);
 /* Leaves the group. Every retained graph of the handle is released first (a graph
  * that holds a collective keeps the communicator alive). */
 int nu_cuda_comm_destroy(nu_cuda *h);

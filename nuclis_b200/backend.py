@@ -316,5 +316,16 @@ class Backend:
     def allreduce_sum_f32(self, buffer: Buffer, count: int) -> None:
         self._check(self._lib.nu_cuda_allreduce_sum_f32(self._h, buffer._c(), count))
 
+    def comm_peer_handle(self) -> bytes:
+        """This rank's inbox for the one-shot allreduce, as a 64-byte interprocess handle."""
+        buf = (ctypes.c_uint8 * 64)()
+        self._check(self._lib.nu_cuda_comm_peer_handle(self._h, buf))
+        return bytes(buf)
+
+    def comm_attach_peers(self, handles: list[bytes], rank: int) -> None:
+        """Opens every rank's inbox (handles ordered by rank); short allreduces then bypass NCCL."""
+        flat = (ctypes.c_uint8 * (64 * len(handles))).from_buffer_copy(b"".join(handles))
+        self._check(self._lib.nu_cuda_comm_attach_peers(self._h, flat, len(handles), rank))
+
     def comm_destroy(self) -> None:
         self._check(self._lib.nu_cuda_comm_destroy(self._h))

@@ -19,6 +19,10 @@ namespace {
 constexpr size_t kPad = 256;                       // slack after every allocation: bulk copies may read up to 15 bytes past a row
 constexpr size_t kPartialsFloats = 4u << 20;       // 16 MiB of split-K partial sums
 constexpr size_t kCounters = 1u << 16;             // row-block arrival counters
+constexpr size_t kPushCapacity = 8 * 8192;         // floats per inbox slot: 8 token rows of up to 8192 values
+constexpr size_t kPushFloatBytes = 2 * PUSH_MAX_RANKS * kPushCapacity * sizeof(float);
+constexpr size_t kPushFlagBytes = 2 * PUSH_MAX_RANKS * PUSH_MAX_BLOCKS * sizeof(uint32_t);
+constexpr size_t kPushBytes = kPushFloatBytes + kPushFlagBytes + PUSH_MAX_BLOCKS * sizeof(uint32_t);
 
 // quant.validateRow, inference/src/quant/decode.zig:108-120.
 int validateRow(uint32_t enc, size_t byte_count, size_t element_count) {
@@ -87,6 +91,7 @@ Backend::~Backend() {
     for (auto &g : graphs_) cudaGraphExecDestroy(g.second);
     for (auto &a : buffers_) if (a.ptr) cudaFree(a.ptr);
     for (auto &ev : profile_events_) cudaEventDestroy(ev);
+    if (inbox_) cudaFree(inbox_);
     if (partials_) cudaFree(partials_);
     if (counters_) cudaFree(counters_);
     if (ev_start_) cudaEventDestroy(ev_start_);
@@ -227,6 +232,7 @@ int Backend::begin() {
         if (int rc = cuda(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal), "begin: capture")) return rc;
     }
     recording_ = true;
+    written_.clear();
     return NU_OK;
 }
 
@@ -234,6 +240,18 @@ int Backend::needRecording() {
     if (!recording_) return fail(NU_ERR_NOT_RECORDING, "no recording is open (call begin first)");
     cudaSetDevice(device_);
     return NU_OK;
+}
+
+// Buffers an operator of the open recording has written. A decode kernel starts reading its
+// weights before the kernel ahead of it has ended; that is only safe for weights nothing in the
+// recording wrote (the normal case: weights are constants uploaded before the recording).
+void Backend::wrote(const Buffer &b) {
+    for (uint32_t id : written_) if (id == b.id) return;
+    written_.push_back(b.id);
+}
+bool Backend::written(const Buffer &b) const {
+    for (uint32_t id : written_) if (id == b.id) return true;
+    return false;
 }
 
 // Called after each operator has enqueued its kernels.
@@ -261,7 +279,7 @@ int Backend::checkKernelStatus() {
     if (status != 0) {
         cudaMemsetAsync(counters_, 0, (counters_len_ + 1) * sizeof(uint32_t), stream_);
         cudaStreamSynchronize(stream_);
-        return fail(NU_ERR_EXECUTION, "a kernel gave up a bounded wait (copy never completed)");
+        return fail(NU_ERR_EXECUTION, status == 2 ? "allreduce over peer memory: a rank never arrived (bounded wait ran out); the path stays closed" : "a kernel gave up a bounded wait (copy never completed)");
     }
     return NU_OK;
 }
@@ -379,6 +397,7 @@ int Backend::embed(const Buffer &weights, const Matrix &m, uint32_t token, const
     if (!w || !out || output.offset % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "embed: buffer too short");
     if (int rc = needRecording()) return rc;
     launches_ += launch_dequant_row(stream_, m.encoding, m.layout, w, stride, (uint32_t)m.rows, token, (uint32_t)m.columns, out, out_dtype == NU_BF16);
+    wrote(output);
     opBoundary();
     return cuda(cudaGetLastError(), "embed: launch");
 }
@@ -399,9 +418,10 @@ int Backend::matvec(const Buffer &weights, const Matrix &m, const Buffer &input,
     job.enc = m.encoding; job.layout = m.layout; job.columns = (uint32_t)m.columns; job.tokens = 1; job.in = in; job.in_stride = m.columns;
     job.count = 1; job.mode = ACT_NONE;
     job.seg[0] = {w, stride, (uint32_t)m.rows, out, m.rows};
-    job.partials = partials_; job.partials_floats = partials_floats_; job.counters = counters_; job.counters_len = counters_len_; job.sm_count = sm_count_;
+    job.serial = written(weights); job.partials = partials_; job.partials_floats = partials_floats_; job.counters = counters_; job.counters_len = counters_len_; job.sm_count = sm_count_;
     if (!generic_only && fast_supported(job)) launches_ += launch_fast(stream_, job);
     else launches_ += launch_matmul_generic(stream_, m.encoding, m.layout, w, stride, (uint32_t)m.rows, (uint32_t)m.columns, in, false, m.columns, out, m.rows, 1);
+    wrote(output);
     opBoundary();
     return cuda(cudaGetLastError(), "matvec: launch");
 }
@@ -441,10 +461,11 @@ int Backend::matvecRows(const Buffer &weights, const Matrix &m, const Buffer &in
     job.enc = m.encoding; job.layout = m.layout; job.columns = (uint32_t)m.columns; job.tokens = (uint32_t)tokens; job.in = in; job.in_stride = in_stride;
     job.count = 1; job.mode = ACT_NONE;
     job.seg[0] = {w, stride, (uint32_t)m.rows, out, out_stride};
-    job.partials = partials_; job.partials_floats = partials_floats_; job.counters = counters_; job.counters_len = counters_len_; job.sm_count = sm_count_;
+    job.serial = written(weights); job.partials = partials_; job.partials_floats = partials_floats_; job.counters = counters_; job.counters_len = counters_len_; job.sm_count = sm_count_;
     if (!generic_only && fast_supported(job)) launches_ += launch_fast(stream_, job);
     else if (!generic_only && decodePasses(job, in, in_stride, out, out_stride, (uint32_t)tokens)) {}
     else launches_ += launch_matmul_generic(stream_, m.encoding, m.layout, w, stride, (uint32_t)m.rows, (uint32_t)m.columns, in, false, in_stride, out, out_stride, (uint32_t)tokens);
+    wrote(output);
     opBoundary();
     return cuda(cudaGetLastError(), "matvec_rows: launch");
 }
@@ -472,7 +493,7 @@ int Backend::matmul(const Buffer &weights, const Matrix &m, const Buffer &input,
         // Up to 8 tokens in one pass of the weights; a few more in passes of 8.
         FastJob job{};
         job.enc = m.encoding; job.layout = m.layout; job.columns = (uint32_t)m.columns; job.count = 1; job.mode = ACT_NONE; job.in_stride = in_stride;
-        job.partials = partials_; job.partials_floats = partials_floats_; job.counters = counters_; job.counters_len = counters_len_; job.sm_count = sm_count_;
+        job.serial = written(weights); job.partials = partials_; job.partials_floats = partials_floats_; job.counters = counters_; job.counters_len = counters_len_; job.sm_count = sm_count_;
         job.tokens = (uint32_t)(tokens < 8 ? tokens : 8);
         job.in = (const float *)in;
         job.seg[0] = {w, stride, (uint32_t)m.rows, out, out_stride};
@@ -508,6 +529,7 @@ int Backend::matmul(const Buffer &weights, const Matrix &m, const Buffer &input,
     }
     if (!done)
         launches_ += launch_matmul_generic(stream_, m.encoding, m.layout, w, stride, (uint32_t)m.rows, (uint32_t)m.columns, in, in_dtype == NU_BF16, in_stride, out, out_stride, (uint32_t)tokens);
+    wrote(output);
     opBoundary();
     return cuda(cudaGetLastError(), "matmul: launch");
 }
@@ -526,7 +548,7 @@ int Backend::matvecSegments(const Segment *segments, size_t count, const Buffer 
     FastJob job{};
     job.enc = segments[0].matrix.encoding; job.layout = segments[0].matrix.layout; job.columns = (uint32_t)columns; job.tokens = 1; job.in = in; job.in_stride = columns;
     job.count = (uint32_t)count; job.mode = mode == NU_SEGMENTS_PLAIN ? ACT_NONE : (mode == NU_SEGMENTS_SILU_MUL_PAIR ? ACT_SILU : ACT_GELU);
-    job.partials = partials_; job.partials_floats = partials_floats_; job.counters = counters_; job.counters_len = counters_len_; job.sm_count = sm_count_;
+    for (size_t i = 0; i < count; ++i) job.serial = job.serial || written(segments[i].weights); job.partials = partials_; job.partials_floats = partials_floats_; job.counters = counters_; job.counters_len = counters_len_; job.sm_count = sm_count_;
     bool same_encoding = true;
     uint64_t total_rows = 0;
     for (size_t i = 0; i < count; ++i) {
@@ -556,6 +578,7 @@ int Backend::matvecSegments(const Segment *segments, size_t count, const Buffer 
     if (generic_only || !same_encoding || !fast_supported(job)) return fail(NU_ERR_MERGE_DECLINED, "segments: merge declined");
     if (int rc = needRecording()) return rc;
     launches_ += launch_fast(stream_, job);
+    for (size_t i = 0; i < count; ++i) wrote(segments[i].output);
     opBoundary();
     return cuda(cudaGetLastError(), "segments: launch");
 }
@@ -568,6 +591,7 @@ int Backend::actMul(uint32_t act, const Buffer &gate, const Buffer &up, size_t c
     if (!g || !u || gate.offset % 4 != 0 || up.offset % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "act_mul: buffer too short");
     if (int rc = needRecording()) return rc;
     launches_ += launch_act_mul_rows(stream_, act, g, u, g, (uint32_t)count, 1, count, count, count);
+    wrote(gate);
     opBoundary();
     return cuda(cudaGetLastError(), "act_mul: launch");
 }
@@ -581,6 +605,7 @@ int Backend::route(const Buffer &logits, size_t experts, size_t k, size_t rows, 
     if (!l || !idx || !w || logits.offset % 4 != 0 || indices.offset % 4 != 0 || weights.offset % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "route: buffer too short");
     if (int rc = needRecording()) return rc;
     launches_ += launch_route(stream_, l, (uint32_t)experts, (uint32_t)k, (uint32_t)rows, in_stride, idx, w);
+    wrote(indices); wrote(weights);
     opBoundary();
     return cuda(cudaGetLastError(), "route: launch");
 }
@@ -603,6 +628,7 @@ int Backend::matvecExpertsGrouped(const Buffer &weights, const ExpertMatrix &t, 
     if (int rc = needRecording()) return rc;
     launches_ += launch_matvec_experts_generic(stream_, t.encoding, w, stride, per_expert, (uint32_t)t.experts, (uint32_t)t.rows, (uint32_t)t.columns,
                                                idx, (uint32_t)slots, in, in_stride, (uint32_t)in_group, out, out_stride);
+    wrote(output);
     opBoundary();
     return cuda(cudaGetLastError(), "experts: launch");
 }
@@ -619,6 +645,7 @@ int Backend::geluMulRows(const Buffer &gate, const Buffer &up, const Buffer &out
     if (overlaps(output, o_len, gate, g_len) || overlaps(output, o_len, up, u_len)) return fail(NU_ERR_INVALID_SHAPE, "gelu_mul_rows: output overlaps an input");
     if (int rc = needRecording()) return rc;
     launches_ += launch_act_mul_rows(stream_, ACT_GELU, g, u, o, (uint32_t)width, (uint32_t)rows, gate_stride, up_stride, out_stride);
+    wrote(output);
     opBoundary();
     return cuda(cudaGetLastError(), "gelu_mul_rows: launch");
 }
@@ -641,6 +668,7 @@ int Backend::combineExperts(const Buffer &values, const Buffer &weights, const B
     }
     if (int rc = needRecording()) return rc;
     launches_ += launch_combine_experts(stream_, v, w, idx, sc, out, (uint32_t)s.columns, (uint32_t)s.slots, (uint32_t)s.rows, s.in_stride, s.out_stride, (uint32_t)s.experts);
+    wrote(output);
     opBoundary();
     return cuda(cudaGetLastError(), "combine: launch");
 }
@@ -712,10 +740,62 @@ int Backend::commInit(const uint8_t *id, int ranks, int rank) {
     return NU_OK;
 }
 
+// The inbox of the one-shot allreduce, as an interprocess handle the other ranks open.
+int Backend::peerHandle(uint8_t *out) {
+    if (!out) return fail(NU_ERR_INVALID_SHAPE, "peer_handle: null result");
+    if (recording_) return fail(NU_ERR_ALREADY_RECORDING, "peer_handle: a recording is open");
+    cudaSetDevice(device_);
+    if (!inbox_) {
+        if (int rc = cuda(cudaMalloc(&inbox_, kPushBytes), "peer_handle: cudaMalloc", NU_ERR_BUFFER)) return rc;
+        if (int rc = cuda(cudaMemset(inbox_, 0, kPushBytes), "peer_handle: memset", NU_ERR_BUFFER)) return rc;
+    }
+    cudaIpcMemHandle_t h;
+    if (int rc = cuda(cudaIpcGetMemHandle(&h, inbox_), "peer_handle: cudaIpcGetMemHandle", NU_ERR_COMM)) return rc;
+    static_assert(sizeof(h) == 64, "interprocess memory handles are 64 bytes");
+    memcpy(out, &h, 64);
+    return NU_OK;
+}
+
+int Backend::attachPeers(const uint8_t *handles, int ranks, int rank) {
+    if (!handles || ranks < 2 || ranks > PUSH_MAX_RANKS || rank < 0 || rank >= ranks) return fail(NU_ERR_INVALID_SHAPE, "attach_peers: 2..8 ranks");
+    if (!inbox_ || peers_attached_) return fail(NU_ERR_COMM, "attach_peers: call peer_handle first, attach once");
+    if (recording_) return fail(NU_ERR_ALREADY_RECORDING, "attach_peers: a recording is open");
+    cudaSetDevice(device_);
+    for (int r = 0; r < ranks; ++r) {
+        if (r == rank) { peer_base_[r] = inbox_; continue; }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handles + (size_t)r * 64, 64);
+        if (int rc = cuda(cudaIpcOpenMemHandle(&peer_base_[r], h, cudaIpcMemLazyEnablePeerAccess), "attach_peers: cudaIpcOpenMemHandle", NU_ERR_COMM)) {
+            for (int q = 0; q < r; ++q) if (q != rank && peer_base_[q]) cudaIpcCloseMemHandle(peer_base_[q]);
+            memset(peer_base_, 0, sizeof peer_base_);
+            return rc;
+        }
+    }
+    peer_ranks_ = ranks;
+    peer_rank_ = rank;
+    peers_attached_ = true;
+    return NU_OK;
+}
+
 int Backend::allreduceSumF32(const Buffer &buffer, size_t count) {
     if (count == 0) return fail(NU_ERR_INVALID_SHAPE, "allreduce: empty");
     float *p = (float *)resolve(buffer, count * 4);
-    if (!p || buffer.offset % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "allreduce: buffer too short");
+    if (!p || buffer.offset % 16 != 0) return fail(NU_ERR_INVALID_SHAPE, "allreduce: buffer too short or not 16-byte aligned");
+    if (peers_attached_ && count <= kPushCapacity) {
+        if (int rc = needRecording()) return rc;
+        PushParams pp{};
+        pp.buf = p; pp.count = (uint32_t)count; pp.ranks = (uint32_t)peer_ranks_; pp.rank = (uint32_t)peer_rank_; pp.capacity = (uint32_t)kPushCapacity;
+        for (int r = 0; r < peer_ranks_; ++r) {
+            pp.inbox[r] = (float *)peer_base_[r];
+            pp.flags[r] = (uint32_t *)((uint8_t *)peer_base_[r] + kPushFloatBytes);
+        }
+        pp.seq = (uint32_t *)(inbox_ + kPushFloatBytes + kPushFlagBytes);
+        pp.status = counters_ + counters_len_;
+        launches_ += launch_push_allreduce(stream_, pp);
+        wrote(buffer);
+        opBoundary();
+        return cuda(cudaGetLastError(), "allreduce: launch");
+    }
     if (!comm_) return fail(NU_ERR_COMM, "allreduce: no group joined");
     if (int rc = needRecording()) return rc;
     const int rc = g_nccl.AllReduce(p, p, count, kNcclFloat, kNcclSum, comm_, stream_);
@@ -723,11 +803,20 @@ int Backend::allreduceSumF32(const Buffer &buffer, size_t count) {
         error_ = std::string("allreduce: ") + (g_nccl.GetErrorString ? g_nccl.GetErrorString(rc) : "NCCL error");
         return NU_ERR_COMM;
     }
+    wrote(buffer);
     opBoundary();  // a library collective: not counted among this library's own kernel launches
     return NU_OK;
 }
 
 int Backend::commDestroy() {
+    if (peers_attached_) {
+        cudaSetDevice(device_);
+        cudaStreamSynchronize(stream_);
+        for (int r = 0; r < peer_ranks_; ++r)
+            if (r != peer_rank_ && peer_base_[r]) cudaIpcCloseMemHandle(peer_base_[r]);
+        memset(peer_base_, 0, sizeof peer_base_);
+        peers_attached_ = false;
+    }
     if (!comm_) return NU_OK;
     if (recording_) return fail(NU_ERR_ALREADY_RECORDING, "comm_destroy: a recording is open");
     // A retained graph that holds a collective keeps the communicator busy: NCCL waits for it.
@@ -878,5 +967,7 @@ int nu_cuda_comm_unique_id(uint8_t id[NU_COMM_ID_BYTES]) { return id ? nu::uniqu
 int nu_cuda_comm_init(nu_cuda *h, const uint8_t id[NU_COMM_ID_BYTES], int ranks, int rank) { NU_H(h); return h->b->commInit(id, ranks, rank); }
 int nu_cuda_allreduce_sum_f32(nu_cuda *h, const nu_buffer *buffer, size_t count) { NU_H(h); NU_P(buffer); return h->b->allreduceSumF32(*buffer, count); }
 int nu_cuda_comm_destroy(nu_cuda *h) { NU_H(h); return h->b->commDestroy(); }
+int nu_cuda_comm_peer_handle(nu_cuda *h, uint8_t handle[NU_PEER_HANDLE_BYTES]) { NU_H(h); return h->b->peerHandle(handle); }
+int nu_cuda_comm_attach_peers(nu_cuda *h, const uint8_t *handles, int ranks, int rank) { NU_H(h); return h->b->attachPeers(handles, ranks, rank); }
 
 }  // extern "C"

@@ -80,6 +80,8 @@ public:
     int commInit(const uint8_t *id, int ranks, int rank);
     int allreduceSumF32(const Buffer &buffer, size_t count);
     int commDestroy();
+    int peerHandle(uint8_t *out);
+    int attachPeers(const uint8_t *handles, int ranks, int rank);
 
     const char *lastError() const { return error_.c_str(); }
 
@@ -99,6 +101,8 @@ private:
     static bool overlaps(const Buffer &a, size_t a_len, const Buffer &b, size_t b_len);
     int needRecording();
     void opBoundary();
+    void wrote(const Buffer &b);
+    bool written(const Buffer &b) const;
     int finishCapture(cudaGraphExec_t *exec);
     int runGraph(cudaGraphExec_t exec, uint32_t count, float *elapsed_ms);
     int checkKernelStatus();
@@ -114,6 +118,7 @@ private:
     uint32_t next_graph_ = 1;
     uint64_t created_bytes_ = 0;
     bool recording_ = false;
+    std::vector<uint32_t> written_;  // ids of buffers written in the open recording
     double gpu_seconds_ = 0;
     uint64_t launches_ = 0;
     std::string error_;
@@ -131,6 +136,11 @@ private:
     // collective
     void *comm_ = nullptr;  // ncclComm_t
     int ranks_ = 1, rank_ = 0;
+    // one-shot allreduce over peer memory: this rank's inbox (floats, then flags, then sequence numbers)
+    uint8_t *inbox_ = nullptr;
+    void *peer_base_[8] = {};
+    bool peers_attached_ = false;
+    int peer_ranks_ = 0, peer_rank_ = 0;
 };
 
 }  // namespace nu

@@ -5,6 +5,7 @@
 // that fetches it, the place of each activation in the staged layout, and the
 // mma loop over one task. See gemv_q4k_decode.cu for the description of the scheme.
 #pragma once
+#include <cstdlib>
 #include <cuda.h>
 #include <cuda_fp16.h>
 
@@ -184,6 +185,11 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
 #else
 #define NU_TRACE(i)
 #endif
+    // Programmatic dependent launch: the next kernel of the stream may take an SM as soon as this
+    // block leaves it, and this kernel starts its weight stream (weights are constant) while the
+    // previous kernel is still finishing elsewhere. Everything that reads the previous kernel's
+    // output or writes global memory comes after grid_dependency_wait() below.
+    asm volatile("griddepcontrol.launch_dependents;");
     if (tid == 0) {
         for (int i = 0; i < WARPS * STAGES; ++i) mbar_init(smem_u32(bars + i), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -217,6 +223,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
     };
     for (int i = 0; i < STAGES - 1; ++i)
         if (prod.u < u_end) issue();
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // the previous kernel has ended; its writes are visible
 
     // ---- stage the activation row: scale, split into fp16 pieces, group sums ----
     // The row is read from global memory once and kept in registers between the two passes.
@@ -263,6 +270,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
         }
     }
     __syncthreads();
+    NU_TRACE(0);
 
     // Lanes whose B column is not theirs (column n = lane >> 2 belongs to quad lane n >> 1) read zeros.
     const bool mine = (g >> 1) == t;
@@ -381,7 +389,11 @@ static size_t smem_bytes(uint32_t win_sb, int stages) {
            ROUND_STEPS * SLOTS * 4 + 128 + WARPS * stages * 8 + 128;
 }
 
+#ifdef NU_DEC_TRACE
+constexpr size_t kSmemMax = 226 * 1024;  // the trace keeps a few words of static shared memory
+#else
 constexpr size_t kSmemMax = 227 * 1024;
+#endif
 constexpr int kMaxColumns = 20480;  // the staging pass keeps the activation row in registers
 
 // Deepest ring of task stages that fits beside the staged activations: the copies in flight hide HBM latency.
@@ -468,18 +480,35 @@ static bool fill_common(const FastJob &job, Params &p) {
     return true;
 }
 
+// NUCLIS_NO_OVERLAP=1 in the environment launches every kernel fully serialised (for measurements).
+inline bool overlap_launches() {
+    static const bool on = [] { const char *e = getenv("NUCLIS_NO_OVERLAP"); return !(e && e[0] == '1'); }();
+    return on;
+}
+
 template <class E>
 static int launch(cudaStream_t s, const FastJob &job, const Params &p) {
     const uint32_t units = p.nks * p.total_tiles;
     const uint32_t grid = units < (uint32_t)job.sm_count ? units : (uint32_t)job.sm_count;
     const int stages = pick_stages<E>(p.win_sb);
     const size_t bytes = smem_bytes<E>(p.win_sb, stages);
+    // launched so that it may overlap the tail of the kernel before it (see the kernel's prologue)
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = bytes;
+    cfg.stream = s;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap_launches() && !job.serial ? 1 : 0;
     switch (stages) {
-    case 6: decode_kernel<E, 6><<<grid, THREADS, bytes, s>>>(p); break;
-    case 5: decode_kernel<E, 5><<<grid, THREADS, bytes, s>>>(p); break;
-    case 4: decode_kernel<E, 4><<<grid, THREADS, bytes, s>>>(p); break;
-    case 3: decode_kernel<E, 3><<<grid, THREADS, bytes, s>>>(p); break;
-    default: decode_kernel<E, 2><<<grid, THREADS, bytes, s>>>(p); break;
+    case 6: cudaLaunchKernelEx(&cfg, decode_kernel<E, 6>, p); break;
+    case 5: cudaLaunchKernelEx(&cfg, decode_kernel<E, 5>, p); break;
+    case 4: cudaLaunchKernelEx(&cfg, decode_kernel<E, 4>, p); break;
+    case 3: cudaLaunchKernelEx(&cfg, decode_kernel<E, 3>, p); break;
+    default: cudaLaunchKernelEx(&cfg, decode_kernel<E, 2>, p); break;
     }
     return 1;
 }

@@ -62,6 +62,7 @@ struct FastJob {
     uint32_t *counters;
     size_t counters_len;
     int sm_count;
+    bool serial;  // a weights buffer was written earlier in the same recording: no early start of the weight stream
 };
 // Opts every variant into its dynamic shared memory size; once per device, outside any capture.
 bool fast_configure();
@@ -97,6 +98,20 @@ bool prefill_configure();
 bool prefill_supported(const PrefillJob &job);
 int launch_prefill(cudaStream_t s, const PrefillJob &job);
 int launch_f32_to_bf16_rows(cudaStream_t s, const float *in, size_t in_stride, void *out, size_t out_stride, uint32_t columns, uint32_t tokens);
+
+// ---- one-shot allreduce over peer memory (push_allreduce.cu) ------------------------
+constexpr int PUSH_MAX_RANKS = 8;
+constexpr int PUSH_MAX_BLOCKS = 32;
+struct PushParams {
+    float *buf;                         // this rank's vector, summed in place
+    uint32_t count, ranks, rank;
+    uint32_t capacity;                  // floats per inbox slot
+    float *inbox[PUSH_MAX_RANKS];       // every rank's inbox [2][ranks][capacity]; inbox[rank] is local
+    uint32_t *flags[PUSH_MAX_RANKS];    // every rank's flags [2][ranks][PUSH_MAX_BLOCKS]
+    uint32_t *seq;                      // local: sequence number, finished blocks, sticky failure
+    uint32_t *status;
+};
+int launch_push_allreduce(cudaStream_t s, const PushParams &p);
 
 // ---- planar re-layout of a matrix for the specialized kernels ---------------------
 // Layout the matrix takes after preparation: 0 when the specialized kernels read the GGUF rows as they are.
