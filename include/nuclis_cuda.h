@@ -270,11 +270,10 @@ enum { NU_COMM_ID_BYTES = 128 };
 int nu_cuda_comm_unique_id(uint8_t id[NU_COMM_ID_BYTES]);
 /* Joins this handle to a group of `ranks` handles (one per GPU). Collective. */
 int nu_cuda_comm_init(nu_cuda *h, const uint8_t id[NU_COMM_ID_BYTES], int ranks, int rank);
-/* In-place sum over the group of `count` floats at `buffer` (16-byte aligned); recorded like an
- * operator. */
+/* In-place sum over the group of `count` floats at `buffer`; recorded like an operator. */
 int nu_cuda_allreduce_sum_f32(nu_cuda *h, const nu_buffer *buffer, size_t count);
 /* One-shot allreduce over peer memory for short vectors (at most 65,536 floats): at 20 KB a
- * collective is pure latency, and this path costs a peer store, a flag and a local sum instead of
+ * collective is pure latency, and this path costs one peer store and a local sum instead of
  * a library call. Each rank calls nu_cuda_comm_peer_handle (it allocates the rank's inbox and
  * returns a 64-byte interprocess handle), the handles travel to every rank by any means, ordered by
  * rank, and each rank calls nu_cuda_comm_attach_peers with all of them. From then on

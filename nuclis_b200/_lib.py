@@ -93,9 +93,10 @@ def load() -> ctypes.CDLL:
     """The loaded library; raises if it has not been built."""
     global _lib
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
-            raise RuntimeError(f"{LIB_PATH} is missing: run `python -m nuclis_b200.build` (there is no CPU fallback)")
-        lib = ctypes.CDLL(LIB_PATH)
+        path = os.environ.get("NUCLIS_CUDA_LIB", LIB_PATH)  # another build of the same library, e.g. a tuning variant
+        if not os.path.exists(path):
+            raise RuntimeError(f"{path} is missing: run `python -m nuclis_b200.build` (there is no CPU fallback)")
+        lib = ctypes.CDLL(path)
         for name, (restype, argtypes) in SIGNATURES.items():
             fn = getattr(lib, name)
             fn.restype = restype

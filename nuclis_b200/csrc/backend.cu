@@ -20,9 +20,8 @@ constexpr size_t kPad = 256;                       // slack after every allocati
 constexpr size_t kPartialsFloats = 4u << 20;       // 16 MiB of split-K partial sums
 constexpr size_t kCounters = 1u << 16;             // row-block arrival counters
 constexpr size_t kPushCapacity = 8 * 8192;         // floats per inbox slot: 8 token rows of up to 8192 values
-constexpr size_t kPushFloatBytes = 2 * PUSH_MAX_RANKS * kPushCapacity * sizeof(float);
-constexpr size_t kPushFlagBytes = 2 * PUSH_MAX_RANKS * PUSH_MAX_BLOCKS * sizeof(uint32_t);
-constexpr size_t kPushBytes = kPushFloatBytes + kPushFlagBytes + PUSH_MAX_BLOCKS * sizeof(uint32_t);
+constexpr size_t kPushWordBytes = 2 * PUSH_MAX_RANKS * kPushCapacity * 8;   // (value, tag) words
+constexpr size_t kPushBytes = kPushWordBytes + 64;                          // then sequence number, finished blocks, sticky failure
 
 // quant.validateRow, inference/src/quant/decode.zig:108-120.
 int validateRow(uint32_t enc, size_t byte_count, size_t element_count) {
@@ -780,16 +779,13 @@ int Backend::attachPeers(const uint8_t *handles, int ranks, int rank) {
 int Backend::allreduceSumF32(const Buffer &buffer, size_t count) {
     if (count == 0) return fail(NU_ERR_INVALID_SHAPE, "allreduce: empty");
     float *p = (float *)resolve(buffer, count * 4);
-    if (!p || buffer.offset % 16 != 0) return fail(NU_ERR_INVALID_SHAPE, "allreduce: buffer too short or not 16-byte aligned");
+    if (!p || buffer.offset % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "allreduce: buffer too short");
     if (peers_attached_ && count <= kPushCapacity) {
         if (int rc = needRecording()) return rc;
         PushParams pp{};
         pp.buf = p; pp.count = (uint32_t)count; pp.ranks = (uint32_t)peer_ranks_; pp.rank = (uint32_t)peer_rank_; pp.capacity = (uint32_t)kPushCapacity;
-        for (int r = 0; r < peer_ranks_; ++r) {
-            pp.inbox[r] = (float *)peer_base_[r];
-            pp.flags[r] = (uint32_t *)((uint8_t *)peer_base_[r] + kPushFloatBytes);
-        }
-        pp.seq = (uint32_t *)(inbox_ + kPushFloatBytes + kPushFlagBytes);
+        for (int r = 0; r < peer_ranks_; ++r) pp.inbox[r] = (uint2 *)peer_base_[r];
+        pp.seq = (uint32_t *)(inbox_ + kPushWordBytes);
         pp.status = counters_ + counters_len_;
         launches_ += launch_push_allreduce(stream_, pp);
         wrote(buffer);

@@ -21,6 +21,9 @@ namespace dec {
 #ifndef NU_DEC_WARPS
 #define NU_DEC_WARPS 16
 #endif
+#ifndef NU_DEC_PRE
+#define NU_DEC_PRE 1
+#endif
 constexpr int WARPS = NU_DEC_WARPS;
 constexpr int THREADS = WARPS * 32;
 constexpr int SLOTS = WARPS / 4;   // units in work at once
@@ -181,7 +184,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
 #ifdef NU_DEC_TRACE
     unsigned long long t_start; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_start));
     __shared__ unsigned long long trace_ns[8];
-#define NU_TRACE(i) do { if (tid == 0) { unsigned long long tt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tt)); trace_ns[(i)] = tt - t_start; } } while (0)
+#define NU_TRACE(i) do { if (tid == 0) { unsigned long long tt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tt)); trace_ns[(i)] = tt; } } while (0)
 #else
 #define NU_TRACE(i)
 #endif
@@ -221,9 +224,13 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
         ++issued;
         walk_next(p, prod, u_end, part);
     };
-    for (int i = 0; i < STAGES - 1; ++i)
+    // Only a part of the ring is requested before the activations: loads are served in order, and
+    // the activation row queued behind a full ring of weights would arrive microseconds late.
+    constexpr int PRE = NU_DEC_PRE < STAGES - 1 ? NU_DEC_PRE : STAGES - 1;
+    for (int i = 0; i < PRE; ++i)
         if (prod.u < u_end) issue();
     asm volatile("griddepcontrol.wait;" ::: "memory");  // the previous kernel has ended; its writes are visible
+    NU_TRACE(4);
 
     // ---- stage the activation row: scale, split into fp16 pieces, group sums ----
     // The row is read from global memory once and kept in registers between the two passes.
@@ -234,8 +241,11 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
     for (int j = 0; j < XV; ++j) {
         const uint32_t i = tid + j * THREADS;
         xv[j] = i < win_n * 64 ? ((const float4 *)p.in)[win0 * 64 + i] : make_float4(0.f, 0.f, 0.f, 0.f);
-        mx = fmaxf(mx, fmaxf(fmaxf(fabsf(xv[j].x), fabsf(xv[j].y)), fmaxf(fabsf(xv[j].z), fabsf(xv[j].w))));
     }
+    for (int i = PRE; i < STAGES - 1; ++i)  // the loads above are in flight; the rest of the ring follows them
+        if (prod.u < u_end) issue();
+#pragma unroll
+    for (int j = 0; j < XV; ++j) mx = fmaxf(mx, fmaxf(fmaxf(fabsf(xv[j].x), fabsf(xv[j].y)), fmaxf(fabsf(xv[j].z), fabsf(xv[j].w))));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     if (lane == 0) red[warp] = mx;
@@ -374,7 +384,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
     }
 #ifdef NU_DEC_TRACE
     if (tid == 0 && (blockIdx.x == 0 || blockIdx.x == 77 || blockIdx.x == 147))
-        printf("block %u: staged %llu ns, tasks done %llu, barrier %llu, reduced %llu; units %u..%u\n", blockIdx.x, trace_ns[0], trace_ns[1], trace_ns[2], trace_ns[3], u_begin, u_end);
+        printf("TR tiles %u ksb %u block %u start %llu waited %llu staged %llu tasks %llu reduced %llu\n", p.total_tiles, p.ksb, blockIdx.x, t_start, trace_ns[4], trace_ns[0], trace_ns[1], trace_ns[3]);
 #endif
     if (failed) {
         if (lane == 0) atomicExch(p.status, 1u);

@@ -209,6 +209,7 @@ extern "C" int nu_cuda_matvec_q4k_static(const void *weights, size_t stride, uin
     job.partials = d.scratch->partials; job.partials_floats = kStaticPartialFloats;
     job.counters = d.scratch->counters; job.counters_len = kStaticCounters;
     job.sm_count = d.sm_count;
+    job.serial = true;  // the caller's stream may hold a kernel that writes these weights: no early start of the weight stream
     dec::Params p;
     if (!dec::fill(job, p, true))
         return fail(NU_ERR_TOO_LARGE, "matvec_q4k_static: beyond the built-in scratch (65,536 rows, 20,480 columns, 1 MiB of partial sums) or pointers not 16-byte aligned");

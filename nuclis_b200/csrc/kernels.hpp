@@ -105,9 +105,8 @@ constexpr int PUSH_MAX_BLOCKS = 32;
 struct PushParams {
     float *buf;                         // this rank's vector, summed in place
     uint32_t count, ranks, rank;
-    uint32_t capacity;                  // floats per inbox slot
-    float *inbox[PUSH_MAX_RANKS];       // every rank's inbox [2][ranks][capacity]; inbox[rank] is local
-    uint32_t *flags[PUSH_MAX_RANKS];    // every rank's flags [2][ranks][PUSH_MAX_BLOCKS]
+    uint32_t capacity;                  // 8-byte words per inbox slot
+    uint2 *inbox[PUSH_MAX_RANKS];       // every rank's inbox [2][ranks][capacity] of (value, tag); inbox[rank] is local
     uint32_t *seq;                      // local: sequence number, finished blocks, sticky failure
     uint32_t *status;
 };

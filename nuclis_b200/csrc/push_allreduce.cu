@@ -1,21 +1,23 @@
 // One-shot allreduce of a short F32 vector over NVLink peer memory (no reference analogue: the
 // reference is single-device). A decode step of the row-split layer stack sums a 20 KB vector over
 // the ranks 128 times per token; at that size a collective is pure latency, and a library call
-// costs ~20-30 us. This kernel costs a peer store, a flag and a local sum.
+// costs ~20 us. This kernel costs one peer store and a local sum.
 //
-// Every rank owns an inbox in its own memory: [2 parities][ranks][capacity] floats and, per block
-// of the grid, a flag per (parity, source rank). A call with sequence number s uses parity s & 1:
-//   1. each rank stores its vector into slot [parity][my rank] of every peer's inbox (plain peer
-//      stores: remote data is always written into the consumer's own memory, never loaded from a peer);
-//   2. after a system-scope fence it stores s + 1 into its flag in every peer's inbox;
-//   3. it waits, with a bound, until the flags of all peers in its own inbox show s + 1;
-//   4. it adds the slots in rank order (every rank adds the same numbers in the same order, so all
-//      ranks hold bit-identical sums) and writes the result over its vector.
+// Every rank owns an inbox in its own memory: [2 parities][ranks][capacity] words of 8 bytes, each
+// a float beside a 32-bit tag. A call with sequence number s uses parity s & 1 and tag s + 1:
+//   1. each rank stores (value, tag) for every element into slot [parity][its rank] of every
+//      peer's inbox: plain peer stores, so remote data is always written into the consumer's own
+//      memory and never loaded from a peer. An 8-byte store is single-copy atomic, so a reader
+//      that sees the tag sees the value: no fence and no separate flag are needed;
+//   2. it polls its own inbox, with a bound, until every peer's word carries the tag;
+//   3. it adds the values in rank order (every rank adds the same numbers in the same order, so
+//      all ranks hold bit-identical sums) and writes the result over its vector.
 // Two parities suffice: a rank can be at most one call ahead of a peer, because finishing call
-// s + 1 needs the peer's flags for s + 1, which the peer sends only after its kernel for call s has
-// ended. Blocks of the grid work on disjoint slices with their own flags; no block waits on
-// another block of the same grid. The sequence number lives in device memory (a replayed graph
-// cannot change kernel arguments); the last block to finish advances it.
+// s + 1 needs the peer's words for s + 1, which the peer sends only after its kernel for call s
+// has ended; so words of call s + 2 (same parity as s) never land on words a peer still reads.
+// The sequence number lives in device memory (a replayed graph cannot change kernel arguments);
+// the last block to finish advances it. Threads work on disjoint elements; nothing waits on
+// another thread of the same grid.
 // A wait is bounded both by iterations and by the global timer (about two seconds: ranks replay
 // their graphs from separate processes, so a peer may legitimately arrive late by a host hiccup).
 // When it runs out the block raises the backend's status word, sets a sticky local word that makes
@@ -32,75 +34,80 @@ __device__ __forceinline__ unsigned long long global_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
+__device__ __forceinline__ void store_words(uint4 *dst, uint4 v) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 load_words(const uint4 *src) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src) : "memory");
+    return v;
+}
 
 __global__ void __launch_bounds__(256) push_allreduce_kernel(PushParams p) {
-    const uint32_t b = blockIdx.x, tid = threadIdx.x;
-    const uint32_t per = ((p.count + gridDim.x - 1) / gridDim.x + 3u) & ~3u;  // slice, a multiple of 4 floats
-    const uint32_t c0 = min(b * per, p.count), c1 = min(c0 + per, p.count);
+    // The kernel after this one may start its prologue now; this one reads the vector only after
+    // the kernel before it has ended.
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t tid = threadIdx.x;
     // p.seq: [0] sequence number, [1] blocks finished in this call, [2] sticky failure
-    if (*(volatile uint32_t *)(p.seq + 2) != 0) {
+    __shared__ uint32_t head[2];
+    if (tid == 0) {
+        head[0] = *(volatile uint32_t *)(p.seq + 2);
+        head[1] = *(volatile uint32_t *)p.seq;
+    }
+    __syncthreads();
+    if (head[0] != 0) {  // uniform over the block
         if (tid == 0) atomicExch(p.status, 2u);
         return;
     }
-    const uint32_t seq = *(volatile uint32_t *)p.seq;
-    const uint32_t parity = seq & 1u;
-    const size_t slot_floats = p.capacity;
-    // ---- 1. push my slice into every peer's inbox (and my own) ----
-    for (uint32_t r = 0; r < p.ranks; ++r) {
-        float *dst = p.inbox[r] + ((size_t)parity * p.ranks + p.rank) * slot_floats;
-        for (uint32_t i = c0 + tid * 4; i < c1; i += blockDim.x * 4) {
-            if (i + 4 <= c1) *(float4 *)(dst + i) = *(const float4 *)(p.buf + i);
-            else for (uint32_t j = i; j < c1; ++j) dst[j] = p.buf[j];
+    const uint32_t seq = head[1];
+    const uint32_t parity = seq & 1u, tag = seq + 1;
+    const uint32_t pairs = (p.count + 1) / 2;  // a thread moves two elements: one 16-byte word pair
+    const uint32_t first = blockIdx.x * blockDim.x + tid, step = gridDim.x * blockDim.x;
+    // ---- 1. push ----
+    for (uint32_t i = first; i < pairs; i += step) {
+        const float a = p.buf[2 * i], b = 2 * i + 1 < p.count ? p.buf[2 * i + 1] : 0.0f;
+        const uint4 w = make_uint4(__float_as_uint(a), tag, __float_as_uint(b), tag);
+        for (uint32_t r = 0; r < p.ranks; ++r)
+            if (r != p.rank) store_words((uint4 *)(p.inbox[r] + ((size_t)parity * p.ranks + p.rank) * p.capacity) + i, w);
+    }
+    // ---- 2, 3. poll my inbox and add in rank order ----
+    const unsigned long long t0 = global_ns();
+    bool failed = false;
+    for (uint32_t i = first; i < pairs && !failed; i += step) {
+        float s0 = 0.0f, s1 = 0.0f;
+        for (uint32_t r = 0; r < p.ranks; ++r) {
+            float a, b;
+            if (r == p.rank) {
+                a = p.buf[2 * i];
+                b = 2 * i + 1 < p.count ? p.buf[2 * i + 1] : 0.0f;
+            } else {
+                const uint4 *src = (const uint4 *)(p.inbox[p.rank] + ((size_t)parity * p.ranks + r) * p.capacity) + i;
+                uint4 w = load_words(src);
+                uint32_t n = 0;
+                while ((w.y != tag || w.w != tag) && ++n < kPushSpinLimit) {
+                    if ((n & 255u) == 0 && global_ns() - t0 > kPushWaitNs) break;
+                    w = load_words(src);
+                }
+                if (w.y != tag || w.w != tag) { failed = true; break; }
+                a = __uint_as_float(w.x);
+                b = __uint_as_float(w.z);
+            }
+            if (r == 0) { s0 = a; s1 = b; }
+            else { s0 += a; s1 += b; }
+        }
+        if (!failed) {
+            p.buf[2 * i] = s0;
+            if (2 * i + 1 < p.count) p.buf[2 * i + 1] = s1;
         }
     }
-    __threadfence_system();
-    __syncthreads();
-    // ---- 2. flags ----
-    if (tid < p.ranks) {
-        volatile uint32_t *flag = p.flags[tid] + ((size_t)parity * p.ranks + p.rank) * PUSH_MAX_BLOCKS + b;
-        *flag = seq + 1;
-    }
-    // ---- 3. wait for every rank's flag in my inbox ----
-    __shared__ uint32_t failed;
-    if (tid == 0) failed = 0;
-    __syncthreads();
-    if (tid < p.ranks) {
-        volatile uint32_t *flag = p.flags[p.rank] + ((size_t)parity * p.ranks + tid) * PUSH_MAX_BLOCKS + b;
-        const unsigned long long t0 = global_ns();
-        uint32_t i = 0;
-        bool ok = false;
-        while (!(ok = (*flag == seq + 1)) && ++i < kPushSpinLimit)
-            if ((i & 1023u) == 0 && global_ns() - t0 > kPushWaitNs) break;
-        if (!ok) failed = 1;
-    }
-    __syncthreads();
-    if (failed) {
+    if (__syncthreads_or(failed)) {
         if (tid == 0) {
             atomicExch(p.status, 2u);
             atomicExch(p.seq + 2, 1u);
         }
         return;
     }
-    __threadfence_system();
-    // ---- 4. add the slots in rank order ----
-    const float *mine = p.inbox[p.rank] + (size_t)parity * p.ranks * slot_floats;
-    for (uint32_t i = c0 + tid * 4; i < c1; i += blockDim.x * 4) {
-        if (i + 4 <= c1) {
-            float4 s = __ldcg((const float4 *)(mine + i));
-            for (uint32_t r = 1; r < p.ranks; ++r) {
-                const float4 v = __ldcg((const float4 *)(mine + r * slot_floats + i));
-                s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
-            }
-            *(float4 *)(p.buf + i) = s;
-        } else {
-            for (uint32_t j = i; j < c1; ++j) {
-                float s = __ldcg(mine + j);
-                for (uint32_t r = 1; r < p.ranks; ++r) s += __ldcg(mine + r * slot_floats + j);
-                p.buf[j] = s;
-            }
-        }
-    }
-    __syncthreads();
     if (tid == 0) {
         __threadfence();
         if (atomicAdd(p.seq + 1, 1u) == gridDim.x - 1) {
@@ -112,10 +119,20 @@ __global__ void __launch_bounds__(256) push_allreduce_kernel(PushParams p) {
 }
 
 int launch_push_allreduce(cudaStream_t s, const PushParams &p) {
-    uint32_t blocks = (p.count + 2047) / 2048;
+    const uint32_t pairs = (p.count + 1) / 2;
+    uint32_t blocks = (pairs + 255) / 256;
     if (blocks > PUSH_MAX_BLOCKS) blocks = PUSH_MAX_BLOCKS;
     if (blocks == 0) blocks = 1;
-    push_allreduce_kernel<<<blocks, 256, 0, s>>>(p);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = s;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, push_allreduce_kernel, p);
     return 1;
 }
 
