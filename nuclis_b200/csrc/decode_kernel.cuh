@@ -22,14 +22,14 @@ namespace dec {
 #define NU_DEC_WARPS 16
 #endif
 #ifndef NU_DEC_PRE
-#define NU_DEC_PRE 1
+#define NU_DEC_PRE 8
 #endif
 constexpr int WARPS = NU_DEC_WARPS;
 constexpr int THREADS = WARPS * 32;
 constexpr int SLOTS = WARPS / 4;   // units in work at once
 constexpr int PARTS = 4;           // warps sharing a unit's superblocks
 constexpr int PAIR_PITCH = 136;    // bytes per 64 staged activations (128 of halves + 8 of bank skew)
-constexpr int ROUND_STEPS = 8;     // steps between two reductions: 32 units, 8 KiB of slots
+constexpr int MAX_SLICES = 32;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
 struct Params {
@@ -40,11 +40,11 @@ struct Params {
     uint32_t tile_begin[5];  // first 16-row tile of each segment in the tile list
     uint32_t count, mode;
     uint32_t ksb, ksl, nks;  // superblocks per row, per slice; slices
-    uint32_t total_tiles;    // tiles per slice (pair mode: gate and up tiles interleaved)
-    uint32_t win_sb;         // superblocks of activations the widest block window holds
+    uint32_t units;          // units per slice: 16-row tiles (pair mode: a gate tile with its up tile)
+    uint32_t blk_first[MAX_SLICES + 1];  // blocks blk_first[s] .. blk_first[s+1]-1 work on slice s
     const float *in;
-    float *partials;         // [slice][tile][16]
-    uint32_t *counters;      // per output tile (pair mode: per gate/up tile pair)
+    float *partials;         // [slice][unit][32]
+    uint32_t *counters;      // per unit
     uint32_t *status;        // set to 1 if a bounded wait ran out
 };
 
@@ -95,84 +95,55 @@ __device__ __forceinline__ void mma16816_first(float d[4], const uint32_t a[4], 
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
 }
 
-__host__ __device__ __forceinline__ uint32_t slice_sbs(const Params &p, uint32_t ks) { const uint32_t left = p.ksb - ks * p.ksl; return p.ksl < left ? p.ksl : left; }
-
-// Tile `tile` of the list -> segment and first row. Pair mode interleaves the
-// tiles of the gate (even) and up (odd) segments.
-__device__ __forceinline__ void tile_rows(const Params &p, uint32_t tile, uint32_t &seg, uint32_t &row0) {
-    if (p.mode != ACT_NONE) {
-        seg = tile & 1u;
-        row0 = (tile >> 1) * 16;
-    } else {
-        seg = 0;
+// Unit `unit` of a plain list -> segment and first row.
+__device__ __forceinline__ void unit_rows(const Params &p, uint32_t unit, uint32_t &seg, uint32_t &row0) {
+    seg = 0;
 #pragma unroll
-        for (int s = 1; s < 4; ++s)
-            if ((uint32_t)s < p.count && tile >= p.tile_begin[s]) seg = s;
-        row0 = (tile - p.tile_begin[seg]) * 16;
+    for (int s = 1; s < 4; ++s)
+        if ((uint32_t)s < p.count && unit >= p.tile_begin[s]) seg = s;
+    row0 = (unit - p.tile_begin[seg]) * 16;
+}
+__device__ __forceinline__ void named_barrier(uint32_t id, uint32_t threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// Writes the finished sums of rows g and g+8 of a unit: v = plain sums (pair mode: gate), w = up sums.
+__device__ __forceinline__ void write_unit(const Params &p, uint32_t unit, uint32_t g, float v0, float v1, float w0, float w1) {
+    if (p.mode != ACT_NONE) {
+        const uint32_t row = unit * 16 + g;
+        if (row < p.rows[0]) p.out[0][row] = (p.mode == ACT_SILU ? silu_f32(v0) : gelu_f32(v0)) * w0;
+        if (row + 8 < p.rows[0]) p.out[0][row + 8] = (p.mode == ACT_SILU ? silu_f32(v1) : gelu_f32(v1)) * w1;
+    } else {
+        uint32_t seg, row0;
+        unit_rows(p, unit, seg, row0);
+        if (row0 + g < p.rows[seg]) p.out[seg][row0 + g] = v0;
+        if (row0 + g + 8 < p.rows[seg]) p.out[seg][row0 + g + 8] = v1;
     }
 }
 
-// First unit whose tasks start at or after `target` tasks into the slice-major unit list.
-__host__ __device__ __forceinline__ uint32_t unit_at(const Params &p, unsigned long long target) {
-    const unsigned long long full = (unsigned long long)p.total_tiles * p.ksl;  // tasks of a full slice
-    uint32_t ks = (uint32_t)(target / full);
-    if (ks >= p.nks) ks = p.nks - 1;
-    const unsigned long long rem = target - (unsigned long long)ks * full;
-    const uint32_t n = slice_sbs(p, ks);
-    uint32_t tile = (uint32_t)((rem + n - 1) / n);
-    if (tile > p.total_tiles) tile = p.total_tiles;
-    return ks * p.total_tiles + tile;
-}
-
-// A warp's walk over its tasks: units u_begin + slot, + 4, ... and in each the superblocks part, part + 4, ...
-struct Walk {
-    uint32_t u;        // unit
-    uint32_t sb;       // superblock within the unit's slice
-    uint32_t n;        // superblocks of the unit's slice
-    uint32_t sb0;      // first superblock of the unit's slice
-    uint32_t seg, row0;
-};
-__device__ __forceinline__ void walk_enter(const Params &p, Walk &w, uint32_t u_end, uint32_t part) {
-    // settle on the next unit (at or after w.u) that has a superblock for this part
-    while (w.u < u_end) {
-        const uint32_t ks = w.u / p.total_tiles;
-        w.n = slice_sbs(p, ks);
-        if (part < w.n) {
-            w.sb = part;
-            w.sb0 = ks * p.ksl;
-            tile_rows(p, w.u - ks * p.total_tiles, w.seg, w.row0);
-            return;
-        }
-        w.u += SLOTS;
-    }
-}
-__device__ __forceinline__ void walk_next(const Params &p, Walk &w, uint32_t u_end, uint32_t part) {
-    w.sb += PARTS;
-    if (w.sb >= w.n) {
-        w.u += SLOTS;
-        walk_enter(p, w, u_end, part);
-    }
-}
-
+// Work split. K is cut into `nks` slices and every slice owns a range of blocks (sized by the host
+// so that all blocks finish together); the blocks of a slice split its units evenly, so a block
+// stages the activations of one slice only. A block's 16 warps are 4 unit slots x 4 K parts: warp
+// (slot, part) takes units first + slot, + 4, ... of the block and in each the superblocks part,
+// part + 4, ... of the slice. The four warps of a slot meet at a named barrier of their own after
+// each unit and the first adds the parts in order; there is no block-wide barrier after staging.
 template <class E, int STAGES>
 __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constant__ Params p) {
     constexpr int TASK_BYTES = E::TASK_BYTES;
     extern __shared__ __align__(128) uint8_t smem[];
-    const uint32_t K = p.win_sb * 256;  // columns the staging area holds: the widest window of any block
-    // [task stages][hi pieces][lo pieces][128 B of zeros][group sums K/32 floats][slots][flags, scratch][barriers]
-    // A piece array holds K halves, the 128 bytes of each group pair (64 columns) padded to PAIR_PITCH = 136:
-    // the four quad lanes then read four different pairs of banks, and the lo array starts 32 bytes
-    // further round the banks than the hi array, so the eight loading lanes of a warp never collide.
+    // [task stages][hi pieces][lo pieces][128 B of zeros][group sums][part sums][max scratch][barriers]
+    // A piece array holds the slice's columns as halves, the 128 bytes of each group pair (64 columns) padded
+    // to PAIR_PITCH = 136: the four quad lanes then read four different pairs of banks, and the lo array starts
+    // 32 bytes further round the banks than the hi array, so the eight loading lanes of a warp never collide.
     uint8_t *stages = smem;
     uint8_t *xhi = stages + WARPS * STAGES * TASK_BYTES;
-    const uint32_t piece_bytes = (K / 64) * PAIR_PITCH;  // a multiple of 128 when K is a multiple of 1024; see lo_skew
+    const uint32_t piece_bytes = (p.ksl * 4) * PAIR_PITCH;
     const uint32_t lo_skew = (128u - piece_bytes % 128u) % 128u + 32u;
     uint8_t *xlo = xhi + piece_bytes + lo_skew;
     uint8_t *zero = xlo + piece_bytes + (128u - (piece_bytes + lo_skew + piece_bytes) % 128u) % 128u;
     float *gsum = (float *)(zero + 128);
-    float *slots = gsum + p.win_sb * E::GSUMS;
-    uint32_t *last_flag = (uint32_t *)(slots + ROUND_STEPS * SLOTS * PARTS * 16);  // one per unit of the round
-    float *red = (float *)(last_flag + ROUND_STEPS * SLOTS);
+    float *parts = gsum + p.ksl * E::GSUMS;           // SLOTS x 2 x 3 x 32 floats
+    float *red = parts + SLOTS * 2 * 3 * 32;
     uint64_t *bars = (uint64_t *)(red + 32);
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t g = lane >> 2, t = lane & 3;
@@ -182,68 +153,76 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
     const uint32_t stage0 = smem_u32(my_stage), bar0 = smem_u32(bars + warp * STAGES);
 
 #ifdef NU_DEC_TRACE
-    unsigned long long t_start; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_start));
-    __shared__ unsigned long long trace_ns[8];
-#define NU_TRACE(i) do { if (tid == 0) { unsigned long long tt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tt)); trace_ns[(i)] = tt; } } while (0)
+    unsigned long long tr[5];
+#define NU_TRACE(i) do { asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tr[i])); } while (0)
 #else
 #define NU_TRACE(i)
 #endif
+    NU_TRACE(0);
     // Programmatic dependent launch: the next kernel of the stream may take an SM as soon as this
     // block leaves it, and this kernel starts its weight stream (weights are constant) while the
     // previous kernel is still finishing elsewhere. Everything that reads the previous kernel's
-    // output or writes global memory comes after grid_dependency_wait() below.
+    // output or writes global memory comes after the griddepcontrol.wait below.
     asm volatile("griddepcontrol.launch_dependents;");
-    if (tid == 0) {
-        for (int i = 0; i < WARPS * STAGES; ++i) mbar_init(smem_u32(bars + i), 1);
+    // every warp owns its ring: it initialises its own barriers and nobody else touches them
+    if (lane == 0) {
+        for (int i = 0; i < STAGES; ++i) mbar_init(bar0 + i * 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    __syncthreads();
+    __syncwarp();
 
-    // ---- this block's units: contiguous, equal task count; pair mode keeps a gate tile with its up tile ----
-    const unsigned long long total_tasks = (unsigned long long)p.total_tiles * p.ksb;
-    uint32_t u_begin = unit_at(p, total_tasks * blockIdx.x / gridDim.x);
-    uint32_t u_end = blockIdx.x + 1 == gridDim.x ? p.nks * p.total_tiles : unit_at(p, total_tasks * (blockIdx.x + 1) / gridDim.x);
-    if (p.mode != ACT_NONE) { u_begin &= ~1u; u_end &= ~1u; }
+    // ---- this block's slice and units ----
+    const bool pair = p.mode != ACT_NONE;
+    uint32_t ks = 0;
+    while (ks + 1 < p.nks && blockIdx.x >= p.blk_first[ks + 1]) ++ks;
+    const uint32_t sb0 = ks * p.ksl, n = min(p.ksl, p.ksb - sb0);
+    const uint32_t nblk = p.blk_first[ks + 1] - p.blk_first[ks], jblk = blockIdx.x - p.blk_first[ks];
+    const uint32_t u_lo = (uint32_t)((unsigned long long)p.units * jblk / nblk);
+    const uint32_t u_hi = (uint32_t)((unsigned long long)p.units * (jblk + 1) / nblk);
+    const uint32_t np = min((uint32_t)PARTS, n);                          // warps that share a unit
+    const uint32_t m = part < n ? (n - part + PARTS - 1) / PARTS : 0;     // this warp's superblocks per unit
+    const uint32_t first_unit = u_lo + slot;
+    const uint32_t my_units = first_unit < u_hi ? (u_hi - first_unit + SLOTS - 1) / SLOTS : 0;
+    const uint32_t total = my_units * m * (pair ? 2u : 1u);
     const uint64_t policy = evict_first_policy();
-    // The activations this block needs: the columns of the slices its units lie in.
-    const uint32_t ks_first = u_begin < u_end ? u_begin / p.total_tiles : 0, ks_last = u_begin < u_end ? (u_end - 1) / p.total_tiles : 0;
-    const uint32_t win0 = ks_first * p.ksl;                                                  // first superblock of the window
-    const uint32_t win_n = u_begin < u_end ? min(p.ksb, (ks_last + 1) * p.ksl) - win0 : 0;   // superblocks in the window
 
-    // ---- start the weight stream before anything else ----
-    Walk prod;
-    prod.u = u_begin + slot;
-    walk_enter(p, prod, u_end, part);
-    Walk cons = prod;
-    uint32_t issued = 0, consumed = 0;
+    // ---- the weight stream: this warp's tasks in order (pair mode: gate then up of each superblock) ----
+    uint32_t issued = 0, p_stage = 0, p_unit = first_unit, p_j = 0, p_seg = 0, p_row0 = 0;
+    if (total) {
+        if (pair) p_row0 = p_unit * 16;
+        else unit_rows(p, p_unit, p_seg, p_row0);
+    }
     auto issue = [&]() {
-        if (lane == 0) {
-            const uint32_t st = issued % STAGES;
-            E::issue(p, prod.seg, prod.sb0 + prod.sb, prod.row0, stage0 + st * TASK_BYTES, bar0 + st * 8, policy);
-        }
+        if (lane == 0) E::issue(p, p_seg, sb0 + part + PARTS * p_j, p_row0, stage0 + p_stage * TASK_BYTES, bar0 + p_stage * 8, policy);
         ++issued;
-        walk_next(p, prod, u_end, part);
+        p_stage = p_stage + 1 == STAGES ? 0 : p_stage + 1;
+        if (pair && p_seg == 0) { p_seg = 1; return; }
+        if (pair) p_seg = 0;
+        if (++p_j == m) {
+            p_j = 0;
+            p_unit += SLOTS;
+            if (pair) p_row0 = p_unit * 16;
+            else if (issued < total) unit_rows(p, p_unit, p_seg, p_row0);
+        }
     };
-    // Only a part of the ring is requested before the activations: loads are served in order, and
-    // the activation row queued behind a full ring of weights would arrive microseconds late.
     constexpr int PRE = NU_DEC_PRE < STAGES - 1 ? NU_DEC_PRE : STAGES - 1;
     for (int i = 0; i < PRE; ++i)
-        if (prod.u < u_end) issue();
+        if (issued < total) issue();
     asm volatile("griddepcontrol.wait;" ::: "memory");  // the previous kernel has ended; its writes are visible
-    NU_TRACE(4);
+    NU_TRACE(1);
 
-    // ---- stage the activation row: scale, split into fp16 pieces, group sums ----
-    // The row is read from global memory once and kept in registers between the two passes.
-    constexpr int XV = (20480 / 4 + THREADS - 1) / THREADS;  // float4 per thread: rows of up to 20480 columns
+    // ---- stage the slice's activations: scale, split into fp16 pieces, group sums ----
+    // The window is read from global memory once and kept in registers between the two passes.
+    constexpr int XV = (20480 / 4 + THREADS - 1) / THREADS;  // float4 per thread: slices of up to 20480 columns
     float4 xv[XV];
     float mx = 0.0f;
 #pragma unroll
     for (int j = 0; j < XV; ++j) {
         const uint32_t i = tid + j * THREADS;
-        xv[j] = i < win_n * 64 ? ((const float4 *)p.in)[win0 * 64 + i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        xv[j] = i < n * 64 ? ((const float4 *)p.in)[sb0 * 64 + i] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     for (int i = PRE; i < STAGES - 1; ++i)  // the loads above are in flight; the rest of the ring follows them
-        if (prod.u < u_end) issue();
+        if (issued < total) issue();
 #pragma unroll
     for (int j = 0; j < XV; ++j) mx = fmaxf(mx, fmaxf(fmaxf(fabsf(xv[j].x), fabsf(xv[j].y)), fmaxf(fabsf(xv[j].z), fabsf(xv[j].w))));
 #pragma unroll
@@ -262,7 +241,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
 #pragma unroll
     for (int j = 0; j < XV; ++j) {
         const uint32_t i = tid + j * THREADS;
-        if (i < win_n * 64) {  // uniform per warp: a multiple of 32
+        if (i < n * 64) {  // uniform per warp: a multiple of 32
             const float x0 = xv[j].x * scale, x1 = xv[j].y * scale, x2 = xv[j].z * scale, x3 = xv[j].w * scale;
             const __half h0 = __float2half_rn(x0), h1 = __float2half_rn(x1), h2 = __float2half_rn(x2), h3 = __float2half_rn(x3);
             const __half l0 = __float2half_rn(x0 - __half2float(h0)), l1 = __float2half_rn(x1 - __half2float(h1));
@@ -280,137 +259,145 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
         }
     }
     __syncthreads();
-    NU_TRACE(0);
+    NU_TRACE(2);
 
+    // ---- the task loop ----
     // Lanes whose B column is not theirs (column n = lane >> 2 belongs to quad lane n >> 1) read zeros.
     const bool mine = (g >> 1) == t;
     const uint8_t *piece = (g & 1u) ? xlo : xhi;
+    const uint8_t *xlane = mine ? piece + t * PAIR_PITCH : zero;  // this lane's 64 columns of superblock 0: 128 B of halves
+    const uint32_t xstep = mine ? 4 * PAIR_PITCH : 0;
+    uint32_t c_stage = 0, c_phase = 0, consumed = 0;
     bool failed = false;
-
-    for (uint32_t round_begin = u_begin; round_begin < u_end && !failed; round_begin += ROUND_STEPS * SLOTS) {
-        const uint32_t round_end = min(u_end, round_begin + ROUND_STEPS * SLOTS);
-        // ---- this warp's units of the round: round_begin + slot, + 4, ... ----
-        while (cons.u < round_end && !failed) {
-            const uint32_t unit = cons.u;
-            float acc[2] = {0.0f, 0.0f};  // rows g, g+8: this lane's group pair, summed over the warp's superblocks
-            while (cons.u == unit) {
-                if (prod.u < u_end) issue();  // keep STAGES - 1 tasks in flight
-                const uint32_t st = consumed % STAGES;
-                if (!mbar_wait(bar0 + st * 8, (consumed / STAGES) & 1u)) { failed = true; break; }
-                const uint8_t *task = my_stage + st * TASK_BYTES;
-                const uint32_t sb_win = cons.sb0 + cons.sb - win0;
-                const uint8_t *xb = mine ? piece + (sb_win * 4 + t) * PAIR_PITCH : zero;  // this lane's 64 columns: 128 B of halves
-                E::task(task, xb, gsum + sb_win * E::GSUMS, g, t, acc);
-                __syncwarp();  // all lanes are done reading this stage before it is refilled
-                ++consumed;
-                walk_next(p, cons, u_end, part);
-            }
-            if (failed) break;
-            // the four lanes of a quad hold the four group pairs of the superblock
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                acc[h] += __shfl_xor_sync(0xffffffffu, acc[h], 1);
-                acc[h] += __shfl_xor_sync(0xffffffffu, acc[h], 2);
-            }
-            if (t == 0) {
-                float *dst = slots + ((unit - round_begin) * PARTS + part) * 16;
-                dst[g] = acc[0];
-                dst[g + 8] = acc[1];
-            }
-        }
-        NU_TRACE(1);
-        __syncthreads();
-        NU_TRACE(2);
-        // ---- add each unit's parts in part order: one thread per (unit, row); pair mode: per (gate unit, row) ----
-        const bool pair = p.mode != ACT_NONE;
-        for (uint32_t idx = tid; idx < (round_end - round_begin) * 16; idx += THREADS) {
-            const uint32_t ul = idx >> 4, r = idx & 15, u = round_begin + ul;
-            if (pair && (ul & 1u)) continue;
-            const uint32_t ks = u / p.total_tiles, tile = u - ks * p.total_tiles;
-            const uint32_t parts = min((uint32_t)PARTS, slice_sbs(p, ks));
-            float sum = 0.0f, up = 0.0f;
-            for (uint32_t k = 0; k < parts; ++k) sum += slots[(ul * PARTS + k) * 16 + r];
-            sum *= inv_scale;
+    uint32_t uidx = 0;
+    for (uint32_t unit = first_unit; unit < u_hi; unit += SLOTS, ++uidx) {
+        float acc[2] = {0.0f, 0.0f}, acc2[2] = {0.0f, 0.0f};  // rows g, g+8: this lane's groups, summed over the warp's superblocks
+        // After a wait has run out the warp stops computing but still walks its units, so that the
+        // warps it shares them with are not left at the barrier below.
+        for (uint32_t j = 0; j < m && !failed; ++j) {
+            const uint32_t sbw = part + PARTS * j;  // superblock within the slice
+            if (issued < total) issue();  // keep STAGES - 1 tasks in flight
+            if (!mbar_wait(bar0 + c_stage * 8, c_phase)) { failed = true; break; }
+            E::task(my_stage + c_stage * TASK_BYTES, xlane + sbw * xstep, gsum + sbw * E::GSUMS, g, t, acc);
+            __syncwarp();  // all lanes are done reading this stage before it is refilled
+            ++consumed;
+            if (++c_stage == STAGES) { c_stage = 0; c_phase ^= 1u; }
             if (pair) {
-                for (uint32_t k = 0; k < parts; ++k) up += slots[((ul + 1) * PARTS + k) * 16 + r];
-                up *= inv_scale;
-            }
-            uint32_t seg, row0;
-            tile_rows(p, tile, seg, row0);
-            if (p.nks == 1) {
-                if (row0 + r < p.rows[seg]) {
-                    if (pair) sum = (p.mode == ACT_SILU ? silu_f32(sum) : gelu_f32(sum)) * up;
-                    p.out[seg][row0 + r] = sum;
-                }
-            } else {
-                p.partials[((size_t)ks * p.total_tiles + tile) * 16 + r] = sum;
-                if (pair) p.partials[((size_t)ks * p.total_tiles + tile + 1) * 16 + r] = up;
-                __threadfence();
+                if (issued < total) issue();
+                if (!mbar_wait(bar0 + c_stage * 8, c_phase)) { failed = true; break; }
+                E::task(my_stage + c_stage * TASK_BYTES, xlane + sbw * xstep, gsum + sbw * E::GSUMS, g, t, acc2);
+                __syncwarp();
+                ++consumed;
+                if (++c_stage == STAGES) { c_stage = 0; c_phase ^= 1u; }
             }
         }
+        if (part >= np) continue;  // this warp has no superblocks in this slice
+        // the four lanes of a quad hold the four group pairs of the superblock
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            acc[h] += __shfl_xor_sync(0xffffffffu, acc[h], 1);
+            acc[h] += __shfl_xor_sync(0xffffffffu, acc[h], 2);
+            if (pair) {
+                acc2[h] += __shfl_xor_sync(0xffffffffu, acc2[h], 1);
+                acc2[h] += __shfl_xor_sync(0xffffffffu, acc2[h], 2);
+            }
+        }
+        // ---- the parts of the unit meet; part 0 adds them in part order ----
+        float *buf = parts + ((slot * 2 + (uidx & 1u)) * 3) * 32;
+        if (part > 0 && t == 0) {
+            float *dst = buf + (part - 1) * 32;
+            dst[g] = acc[0];
+            dst[g + 8] = acc[1];
+            if (pair) { dst[16 + g] = acc2[0]; dst[24 + g] = acc2[1]; }
+        }
+        if (np > 1) named_barrier(1 + slot, 32 * np);
+        if (part != 0 || t != 0) continue;
+        for (uint32_t k = 1; k < np; ++k) {
+            const float *src = buf + (k - 1) * 32;
+            acc[0] += src[g];
+            acc[1] += src[g + 8];
+            if (pair) { acc2[0] += src[16 + g]; acc2[1] += src[24 + g]; }
+        }
+        acc[0] *= inv_scale; acc[1] *= inv_scale; acc2[0] *= inv_scale; acc2[1] *= inv_scale;
         if (p.nks > 1) {
-            // the last block to arrive for an output tile adds its slices in order
-            __syncthreads();
-            for (uint32_t ul = tid; ul < round_end - round_begin; ul += THREADS) {
-                uint32_t flag = 0;
-                if (!(pair && (ul & 1u))) {
-                    const uint32_t u = round_begin + ul, tile = u % p.total_tiles;
-                    const uint32_t arrived = atomicAdd(p.counters + (pair ? tile >> 1 : tile), 1u);
-                    flag = arrived == p.nks - 1;
+            // several slices: leave the partial sums; they are published after the loop with one fence
+            float *dst = p.partials + ((size_t)ks * p.units + unit) * 32;
+            dst[g] = acc[0];
+            dst[g + 8] = acc[1];
+            if (pair) { dst[16 + g] = acc2[0]; dst[24 + g] = acc2[1]; }
+        } else {
+            write_unit(p, unit, g, acc[0], acc[1], acc2[0], acc2[1]);
+        }
+    }
+    NU_TRACE(3);
+    if (p.nks > 1 && part == 0 && my_units) {
+        // The last block to arrive for a unit adds the slices in order. Lanes announce 32 units at a
+        // time (one round trip for all of them), then the warp finishes those it was last for.
+        __threadfence();
+        __syncwarp();
+        for (uint32_t base = 0; base < my_units; base += 32) {
+            const uint32_t mine_u = base + lane;
+            uint32_t last = 0;
+            if (mine_u < my_units) last = atomicAdd(p.counters + first_unit + mine_u * SLOTS, 1u) == p.nks - 1;
+            uint32_t mask = __ballot_sync(0xffffffffu, last != 0);
+            if (mask) __threadfence();
+            while (mask) {
+                const uint32_t u = base + (uint32_t)__ffs((int)mask) - 1;
+                mask &= mask - 1;
+                const uint32_t unit = first_unit + u * SLOTS;
+                // lane = row of the unit's 32 partial sums (pair mode: 16 gate, 16 up)
+                float sum = 0.0f;
+                if (lane < 16 || pair)
+                    for (uint32_t k = 0; k < p.nks; ++k) sum += __ldcg(p.partials + ((size_t)k * p.units + unit) * 32 + lane);
+                const float up = __shfl_down_sync(0xffffffffu, sum, 16);
+                if (lane < 16) {
+                    if (pair) {
+                        const uint32_t row = unit * 16 + lane;
+                        if (row < p.rows[0]) p.out[0][row] = (p.mode == ACT_SILU ? silu_f32(sum) : gelu_f32(sum)) * up;
+                    } else {
+                        uint32_t seg, row0;
+                        unit_rows(p, unit, seg, row0);
+                        if (row0 + lane < p.rows[seg]) p.out[seg][row0 + lane] = sum;
+                    }
                 }
-                last_flag[ul] = flag;
-            }
-            __syncthreads();
-            for (uint32_t idx = tid; idx < (round_end - round_begin) * 16; idx += THREADS) {
-                const uint32_t ul = idx >> 4, r = idx & 15;
-                if (!last_flag[ul]) continue;
-                __threadfence();
-                const uint32_t tile = (round_begin + ul) % p.total_tiles;
-                float sum = 0.0f, up = 0.0f;
-                for (uint32_t k = 0; k < p.nks; ++k) sum += __ldcg(p.partials + ((size_t)k * p.total_tiles + tile) * 16 + r);
-                if (pair)
-                    for (uint32_t k = 0; k < p.nks; ++k) up += __ldcg(p.partials + ((size_t)k * p.total_tiles + tile + 1) * 16 + r);
-                uint32_t seg, row0;
-                tile_rows(p, tile, seg, row0);
-                if (row0 + r < p.rows[seg]) {
-                    if (pair) sum = (p.mode == ACT_SILU ? silu_f32(sum) : gelu_f32(sum)) * up;
-                    p.out[seg][row0 + r] = sum;
-                }
-                if (r == 0) p.counters[pair ? tile >> 1 : tile] = 0;  // leave the scratch as it was found
+                if (lane == 0) p.counters[unit] = 0;  // leave the scratch as it was found
             }
         }
-        __syncthreads();  // slots and flags are free for the next round
-        NU_TRACE(3);
     }
+    NU_TRACE(4);
 #ifdef NU_DEC_TRACE
-    if (tid == 0 && (blockIdx.x == 0 || blockIdx.x == 77 || blockIdx.x == 147))
-        printf("TR tiles %u ksb %u block %u start %llu waited %llu staged %llu tasks %llu reduced %llu\n", p.total_tiles, p.ksb, blockIdx.x, t_start, trace_ns[4], trace_ns[0], trace_ns[1], trace_ns[3]);
+    if (lane == 0 && (warp == 0 || warp == 7) && (blockIdx.x == 0 || blockIdx.x == gridDim.x / 2 || blockIdx.x == gridDim.x - 1))
+        printf("TR block %u/%u warp %u ks %u n %u units %u..%u mine %u m %u: waited %llu staged %llu loop %llu end %llu\n", blockIdx.x, gridDim.x, warp, ks, n, u_lo, u_hi, my_units,
+               m, tr[1] - tr[0], tr[2] - tr[0], tr[3] - tr[0], tr[4] - tr[0]);
 #endif
     if (failed) {
         if (lane == 0) atomicExch(p.status, 1u);
         // let this warp's copies still in flight land before the block's shared memory is released
-        for (; consumed < issued; ++consumed) mbar_wait(bar0 + (consumed % STAGES) * 8, (consumed / STAGES) & 1u);
+        for (; consumed < issued; ++consumed) {
+            mbar_wait(bar0 + c_stage * 8, c_phase);
+            if (++c_stage == STAGES) { c_stage = 0; c_phase ^= 1u; }
+        }
     }
 }
 
 template <class E>
-static size_t smem_bytes(uint32_t win_sb, int stages) {
-    return (size_t)WARPS * stages * E::TASK_BYTES + (size_t)(win_sb * 4) * PAIR_PITCH * 2 + 512 + (size_t)win_sb * E::GSUMS * 4 + ROUND_STEPS * SLOTS * PARTS * 64 +
-           ROUND_STEPS * SLOTS * 4 + 128 + WARPS * stages * 8 + 128;
+static size_t smem_bytes(uint32_t ksl, int stages) {
+    return (size_t)WARPS * stages * E::TASK_BYTES + (size_t)(ksl * 4) * PAIR_PITCH * 2 + 512 + (size_t)ksl * E::GSUMS * 4 + SLOTS * 2 * 3 * 32 * 4 + 128 +
+           WARPS * stages * 8 + 128;
 }
 
 #ifdef NU_DEC_TRACE
-constexpr size_t kSmemMax = 226 * 1024;  // the trace keeps a few words of static shared memory
+constexpr size_t kSmemMax = 226 * 1024;
 #else
 constexpr size_t kSmemMax = 227 * 1024;
 #endif
-constexpr int kMaxColumns = 20480;  // the staging pass keeps the activation row in registers
+constexpr uint32_t kMaxSliceSbs = 80;  // the staging pass keeps a slice of up to 20480 columns in registers
 
 // Deepest ring of task stages that fits beside the staged activations: the copies in flight hide HBM latency.
 template <class E>
-static int pick_stages(uint32_t win_sb) {
+static int pick_stages(uint32_t ksl) {
     for (int st = 6; st >= 2; --st)
-        if (smem_bytes<E>(win_sb, st) <= kSmemMax) return st;
+        if (smem_bytes<E>(ksl, st) <= kSmemMax) return st;
     return 0;
 }
 
@@ -422,11 +409,12 @@ template <class E>
 static bool configure() { return configure_one<E, 2>() && configure_one<E, 3>() && configure_one<E, 4>() && configure_one<E, 5>() && configure_one<E, 6>(); }
 
 // Fills everything of Params that does not depend on the encoding's planes; the caller adds the tensor maps.
+// Picks the K slices and the blocks of each slice: every candidate slice length is costed in task
+// steps of the slowest block (units over unit slots, superblocks over K parts).
 template <class E>
 static bool fill_common(const FastJob &job, Params &p) {
     if (job.tokens != 1 || job.count < 1 || job.count > 4) return false;
     if (job.columns == 0 || job.columns % 256 != 0) return false;
-    if (job.columns > kMaxColumns) return false;
     if ((uintptr_t)job.in % 16 != 0) return false;
     if (job.mode != ACT_NONE && (job.count != 2 || job.seg[0].rows != job.seg[1].rows)) return false;
     memset(&p, 0, sizeof p);
@@ -435,7 +423,6 @@ static bool fill_common(const FastJob &job, Params &p) {
     p.ksb = job.columns / 256;
     p.in = job.in;
     uint32_t tiles = 0;
-    uint64_t rows_total = 0;
     for (uint32_t s = 0; s < job.count; ++s) {
         const FastSegment &g = job.seg[s];
         if (g.rows == 0 || (uintptr_t)g.w % 16 != 0 || (uintptr_t)g.out % 4 != 0) return false;
@@ -443,49 +430,53 @@ static bool fill_common(const FastJob &job, Params &p) {
         p.rows[s] = g.rows;
         p.tile_begin[s] = tiles;
         tiles += (g.rows + 15) / 16;
-        rows_total += g.rows;
     }
     for (uint32_t s = job.count; s < 5; ++s) p.tile_begin[s] = tiles;
-    p.total_tiles = tiles;  // pair mode: gate tile i and up tile i are tiles 2i and 2i+1
-    // Slices: one if that fills the machine evenly, else the count that wastes least: whole steps of
-    // unit slots per block, four superblock parts per unit, against the partial sums and fences of a split.
-    double best = -1.0;
-    const double weight_bytes = (double)p.ksb * E::ROW_BYTES * rows_total;
-    for (uint32_t nks = 1; nks <= p.ksb && nks <= 32; ++nks) {
-        const uint32_t ksl = (p.ksb + nks - 1) / nks;
-        const uint32_t slices = (p.ksb + ksl - 1) / ksl;
-        const double units = (double)slices * tiles;
-        const double blocks = units < job.sm_count ? units : job.sm_count;
-        const double per_block = units / blocks;
-        const double steps = (double)(uint64_t)((per_block + SLOTS - 1) / SLOTS);
-        double eff = per_block / (steps * SLOTS);                                  // idle unit slots in the last step
-        eff *= (double)ksl / ((double)((ksl + PARTS - 1) / PARTS) * PARTS);        // idle parts
-        if (slices > 1) eff /= 1.2 + 2.0 * slices * tiles * 64.0 / weight_bytes;   // partial sums, fences and a second reduction
-        if (eff > best + 1e-9) { best = eff; p.ksl = ksl; p.nks = slices; }
-    }
-    // The widest activation window of any block sizes the staging area (and so the depth of the task ring).
-    {
-        const uint32_t units = p.nks * tiles;
-        const uint32_t grid = units < (uint32_t)job.sm_count ? units : (uint32_t)job.sm_count;
-        const unsigned long long total_tasks = (unsigned long long)tiles * p.ksb;
-        p.win_sb = 0;
-        for (uint32_t b = 0; b < grid; ++b) {
-            uint32_t ub = unit_at(p, total_tasks * b / grid);
-            uint32_t ue = b + 1 == grid ? units : unit_at(p, total_tasks * (b + 1) / grid);
-            if (job.mode != ACT_NONE) { ub &= ~1u; ue &= ~1u; }
-            if (ub >= ue) continue;
-            const uint32_t k0 = ub / tiles, k1 = (ue - 1) / tiles;
-            const uint32_t hi = (k1 + 1) * p.ksl < p.ksb ? (k1 + 1) * p.ksl : p.ksb;
-            if (hi - k0 * p.ksl > p.win_sb) p.win_sb = hi - k0 * p.ksl;
+    const bool pair = job.mode != ACT_NONE;
+    const uint32_t units = pair ? tiles / 2 : tiles;
+    const double per_sb = pair ? 2.0 : 1.0;  // tasks per superblock of a unit
+    p.units = units;
+    const uint32_t sms = (uint32_t)job.sm_count;
+    double best = 1e30;
+    uint32_t blocks[MAX_SLICES];
+    for (uint32_t ksl = 1; ksl <= p.ksb && ksl <= kMaxSliceSbs; ++ksl) {
+        const uint32_t nks = (p.ksb + ksl - 1) / ksl;
+        if (nks > MAX_SLICES || nks > sms) continue;
+        const int st = pick_stages<E>(ksl);
+        if (st < 2) continue;
+        auto cost = [&](uint32_t s, uint32_t b) {
+            const uint32_t n = s + 1 == nks ? p.ksb - s * ksl : ksl;
+            const uint32_t units_blk = (units + b - 1) / b;
+            return (double)((units_blk + SLOTS - 1) / SLOTS) * ((double)((n + PARTS - 1) / PARTS) * per_sb + 0.35);
+        };
+        for (uint32_t s = 0; s < nks; ++s) blocks[s] = 1;
+        for (uint32_t left = sms - nks; left > 0; --left) {
+            uint32_t worst = 0;
+            for (uint32_t s = 1; s < nks; ++s)
+                if (cost(s, blocks[s]) > cost(worst, blocks[worst])) worst = s;
+            if (blocks[worst] >= units) break;
+            ++blocks[worst];
         }
-        if (p.win_sb == 0 || pick_stages<E>(p.win_sb) == 0) return false;
+        double est = 0;
+        for (uint32_t s = 0; s < nks; ++s) est = cost(s, blocks[s]) > est ? cost(s, blocks[s]) : est;
+        est *= st >= 4 ? 1.0 : st == 3 ? 1.06 : 1.2;  // a shallow ring hides less latency
+        est += (nks > 1 ? 1.5 : 0.0) + 0.01 * ksl;   // partial sums; staging of the slice
+        if (est < best - 1e-9) {
+            best = est;
+            p.ksl = ksl;
+            p.nks = nks;
+            uint32_t first = 0;
+            for (uint32_t s = 0; s < nks; ++s) { p.blk_first[s] = first; first += blocks[s]; }
+            for (uint32_t s = nks; s <= MAX_SLICES; ++s) p.blk_first[s] = first;
+        }
     }
+    if (best >= 1e30) return false;
     p.partials = job.partials;
     p.counters = job.counters;
     p.status = job.counters + job.counters_len;
     if (p.nks > 1) {
-        if ((size_t)p.nks * tiles * 16 > job.partials_floats) return false;
-        if (tiles > job.counters_len) return false;
+        if ((size_t)p.nks * units * 32 > job.partials_floats) return false;
+        if (units > job.counters_len) return false;
     }
     return true;
 }
@@ -498,10 +489,9 @@ inline bool overlap_launches() {
 
 template <class E>
 static int launch(cudaStream_t s, const FastJob &job, const Params &p) {
-    const uint32_t units = p.nks * p.total_tiles;
-    const uint32_t grid = units < (uint32_t)job.sm_count ? units : (uint32_t)job.sm_count;
-    const int stages = pick_stages<E>(p.win_sb);
-    const size_t bytes = smem_bytes<E>(p.win_sb, stages);
+    const uint32_t grid = p.blk_first[p.nks];
+    const int stages = pick_stages<E>(p.ksl);
+    const size_t bytes = smem_bytes<E>(p.ksl, stages);
     // launched so that it may overlap the tail of the kernel before it (see the kernel's prologue)
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

@@ -187,6 +187,8 @@ extern "C" int nu_cuda_matvec_q4k_static(const void *weights, size_t stride, uin
     };
     if (!weights || !input || !output || rows == 0 || columns == 0) return fail(NU_ERR_INVALID_SHAPE, "matvec_q4k_static: null pointer or empty shape");
     if (columns % 256 != 0 || stride != (size_t)columns / 256 * 144) return fail(NU_ERR_INVALID_SHAPE, "matvec_q4k_static: rows must be whole, contiguous Q4_K superblocks");
+    if (rows > 65536u || columns > 20480u)
+        return fail(NU_ERR_TOO_LARGE, "matvec_q4k_static: beyond the built-in scratch (65,536 rows, 20,480 columns, 1 MiB of partial sums)");
     int device = -1;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return fail(NU_ERR_INIT, "matvec_q4k_static: no current CUDA device");
     StaticDevice &d = g_static_devices[device];
