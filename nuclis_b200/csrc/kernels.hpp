@@ -79,6 +79,10 @@ bool q4k_rows_configure();
 bool q4k_rows_one_token();
 bool q4k_rows_supported(const FastJob &job);
 int launch_q4k_rows(cudaStream_t s, const FastJob &job);
+// 2..8 token rows on planar Q6_K (gemv_q6k_rows.cu)
+bool q6k_rows_configure();
+bool q6k_rows_supported(const FastJob &job);
+int launch_q6k_rows(cudaStream_t s, const FastJob &job);
 bool q6k_decode_configure();
 bool q6k_decode_supported(const FastJob &job);
 int launch_q6k_decode(cudaStream_t s, const FastJob &job);
