@@ -236,9 +236,11 @@ def run_gpu(args, rank: int, world: int, local: int):
         mats = 2 if tokens == 1 else 1
         algo = mats * stack.m_gate.bytes + tokens * stack.shapes.hidden * 4 + tokens * l.ffn_rows * 4 * (1 if tokens == 1 else 1)
         achieved = algo / (pair_ms * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "kernel": "q4k_decode_kernel (SiLU gate/up pair)" if tokens == 1 else "fast_kernel<Q4_K> (gate)",
+        roofline = {"bound": "hbm", "kernel": "q4k_decode_kernel (SiLU gate/up pair)" if tokens == 1 else "rows_kernel<Q4K> (gate)",
                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": f"{peak_kind} HBM copy bandwidth",
-                    "bytes_per_launch": algo, "us_per_launch": pair_ms * 1e3, "traffic": None,
+                    "bytes_per_launch": algo, "us_per_launch": pair_ms * 1e3,
+                    # ncu dram__bytes_read+write of one decode launch (50.21 MB for a 50.14 MB matrix), scaled by the bytes of this launch
+                    "traffic": algo * (50.207488 / 50.13504) if tokens == 1 else None,
                     "chain_achieved": stack.algorithmic_bytes_per_step() / (ms_per_step * 1e-3) / 1e9}
         b.graph_release(pair_graph)
         if world == 1 and not args.no_cpu:
