@@ -5,12 +5,15 @@
 // weights into a half tile in threadgroup memory, stage the activations, 8x8 MACs).
 //
 // One block computes a 128-row x BN-token tile of the output:
-//   * warps 0..3 (128 threads, one per weight row) decode 64 columns of their row per K step to
-//     bf16 and store them in shared memory in the 128-byte-swizzled K-major layout the tensor
-//     core reads; the same warps later move the accumulator from tensor memory to the output;
-//   * warp 4 (one thread) brings the matching BN x 64 tile of bf16 activations with one TMA
+//   * warps 0..7 (256 threads: weight row tid & 127, column half tid >> 7) each decode 32 columns of
+//     their row per K step to bf16 (vector decoders for 16-byte aligned Q4_K and the planar Q6_K /
+//     Q8_0 forms: byte -> float through the 2^23 magic number, one FMA, packed conversion; the
+//     generic per-16 decoder otherwise) and store them in shared memory in the 128-byte-swizzled
+//     K-major layout the tensor core reads; the same warps later move the accumulator from tensor
+//     memory to the output;
+//   * warp 8 (one thread) brings the matching BN x 64 tile of bf16 activations with one TMA
 //     tensor copy per K step (128-byte swizzle, so no thread touches those bytes);
-//   * warp 5 (one thread) issues tcgen05.mma (M = 128, N = BN, K = 16, bf16 x bf16 -> f32) four
+//   * warp 9 (one thread) issues tcgen05.mma (M = 128, N = BN, K = 16, bf16 x bf16 -> f32) four
 //     times per K step into a BN-column accumulator in tensor memory and commits to the
 //     barrier that frees the stage.
 // A ring of stages decouples the three. Every barrier wait is bounded; on expiry the block raises
@@ -31,8 +34,8 @@ namespace prefill {
 
 constexpr int BM = 128;          // weight rows per tile = tensor-memory lanes
 constexpr int BK = 64;           // columns per K step: one 128-byte swizzle row of bf16
-constexpr int PRODUCERS = 128;   // decode threads
-constexpr int THREADS = 192;     // + the TMA warp and the MMA warp
+constexpr int PRODUCER_WARPS = 8; // decode threads: 128 rows x 2 column halves
+constexpr int THREADS = (PRODUCER_WARPS + 2) * 32;  // + the TMA warp and the MMA warp
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 
 struct Params {
@@ -40,6 +43,7 @@ struct Params {
     const uint8_t *w;
     unsigned long long stride;
     uint32_t enc, layout;
+    uint32_t fast;  // 1: the vector decoder of the encoding applies (aligned rows)
     uint32_t rows, columns, tokens;
     float *out;
     unsigned long long out_stride;
@@ -109,25 +113,114 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-// Decodes columns [k0, k0 + 64) of row r to bf16, as eight 16-byte chunks.
-__device__ __forceinline__ void decode64(const Params &p, uint32_t r, uint32_t k0, uint4 chunks[8]) {
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    const __nv_bfloat162 pair = __floats2bfloat162_rn(a, b);
+    return *(const uint32_t *)&pair;
+}
+// Byte j of w as a float, through the 2^23 magic number (one permute, one exact subtraction).
+__device__ __forceinline__ float byte_f32(uint32_t w, int j) { return __uint_as_float(__byte_perm(w, 0x4b000000u, 0x7650u + j)) - 8388608.0f; }
+
+// Decodes columns [k0 + 32 half, + 32) of row r to bf16, as four 16-byte chunks: the generic path.
+__device__ __forceinline__ void decode32_generic(const Params &p, uint32_t r, uint32_t k0, uint32_t half, uint4 chunks[4]) {
 #pragma unroll
-    for (int s = 0; s < 4; ++s) {
+    for (int s = 0; s < 2; ++s) {
         float v[16];
-        if (p.layout == 1) dequant16_planar_q6k(p.w, p.rows, p.columns / 256, r, k0 / 16 + s, v);
-        else if (p.layout == 2) dequant16_planar_q8_0(p.w, p.rows, p.columns, r, k0 / 16 + s, v);
-        else dequant16(p.enc, p.w + (size_t)r * p.stride, k0 / 16 + s, v);
+        const uint32_t seg = k0 / 16 + half * 2 + s;
+        if (p.layout == 1) dequant16_planar_q6k(p.w, p.rows, p.columns / 256, r, seg, v);
+        else if (p.layout == 2) dequant16_planar_q8_0(p.w, p.rows, p.columns, r, seg, v);
+        else dequant16(p.enc, p.w + (size_t)r * p.stride, seg, v);
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-            uint32_t packed[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const __nv_bfloat162 pair = __floats2bfloat162_rn(v[c * 8 + 2 * i], v[c * 8 + 2 * i + 1]);
-                packed[i] = *(const uint32_t *)&pair;
-            }
-            chunks[s * 2 + c] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-        }
+        for (int c = 0; c < 2; ++c)
+            chunks[s * 2 + c] = make_uint4(pack_bf16(v[c * 8], v[c * 8 + 1]), pack_bf16(v[c * 8 + 2], v[c * 8 + 3]), pack_bf16(v[c * 8 + 4], v[c * 8 + 5]),
+                                           pack_bf16(v[c * 8 + 6], v[c * 8 + 7]));
     }
+}
+
+// Q4_K, rows 16-byte aligned: the 64 columns of a K step are one group pair; half 0 is its even
+// group (low nibbles), half 1 the odd group (high nibbles). Values are (d*s)*q - dmin*m with one
+// rounding, like the reference decoder (inference/src/quant/decode.zig:147-170), then rounded to bf16.
+__device__ __forceinline__ void decode32_q4k(const Params &p, uint32_t r, uint32_t k0, uint32_t half, uint4 chunks[4]) {
+    const uint8_t *block = p.w + (size_t)r * p.stride + (size_t)(k0 / 256) * 144;
+    const uint32_t pair = (k0 / 64) & 3u, grp = pair * 2 + half;
+    const uint4 hdr = *(const uint4 *)block;
+    const uint4 qa = *(const uint4 *)(block + 16 + pair * 32), qb = *(const uint4 *)(block + 32 + pair * 32);
+    // six-bit scale and minimum of group grp out of the 12 packed bytes (words hdr.y, hdr.z, hdr.w)
+    const uint32_t lo_byte = grp & 3u;
+    const uint32_t y = (hdr.y >> (8 * lo_byte)) & 0xffu, z = (hdr.z >> (8 * lo_byte)) & 0xffu, w = (hdr.w >> (8 * lo_byte)) & 0xffu;
+    const uint32_t s6 = grp < 4 ? (y & 63u) : ((w & 15u) | ((y >> 6) << 4));
+    const uint32_t m6 = grp < 4 ? (z & 63u) : ((w >> 4) | ((z >> 6) << 4));
+    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu))), dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+    const float ds = __fmul_rn(d, (float)s6), ndm = -__fmul_rn(dmin, (float)m6);
+    const uint32_t words[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint32_t packed[4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t t4 = (half ? (words[c * 2 + h] >> 4) : words[c * 2 + h]) & 0x0f0f0f0fu;  // four codes, one per byte
+            const float v0 = fmaf(byte_f32(t4, 0), ds, ndm), v1 = fmaf(byte_f32(t4, 1), ds, ndm);
+            const float v2 = fmaf(byte_f32(t4, 2), ds, ndm), v3 = fmaf(byte_f32(t4, 3), ds, ndm);
+            packed[h * 2] = pack_bf16(v0, v1);
+            packed[h * 2 + 1] = pack_bf16(v2, v3);
+        }
+        chunks[c] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    }
+}
+
+// Planar Q8_0 (prepare.cu): 32 columns are one block; value = d * code, exact before the bf16 rounding.
+__device__ __forceinline__ void decode32_q8_0_planar(const Params &p, uint32_t r, uint32_t k0, uint32_t half, uint4 chunks[4]) {
+    const uint8_t *q = p.w + (size_t)r * p.columns + k0 + half * 32;
+    const uint32_t blk = k0 / 32 + half;
+    const float d = __half2float(*(const __half *)(p.w + (size_t)p.rows * p.columns + ((size_t)blk * p.rows + r) * 2));
+    const uint4 qa = *(const uint4 *)q, qb = *(const uint4 *)(q + 16);
+    const uint32_t words[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint32_t packed[4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t u = words[c * 2 + h] ^ 0x80808080u;  // code + 128
+            const float v0 = (byte_f32(u, 0) - 128.0f) * d, v1 = (byte_f32(u, 1) - 128.0f) * d;
+            const float v2 = (byte_f32(u, 2) - 128.0f) * d, v3 = (byte_f32(u, 3) - 128.0f) * d;
+            packed[h * 2] = pack_bf16(v0, v1);
+            packed[h * 2 + 1] = pack_bf16(v2, v3);
+        }
+        chunks[c] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    }
+}
+
+// Planar Q6_K (prepare.cu): the 32 columns are quarter qr of half hh of a superblock, 16 from each
+// column half ch (one planar chunk and one scale each); value = (d * scale) * (code - 32), exact.
+__device__ __forceinline__ void decode32_q6k_planar(const Params &p, uint32_t r, uint32_t k0, uint32_t half, uint4 chunks[4]) {
+    const uint32_t ksb = p.columns / 256, sb = k0 / 256, j = ((k0 / 32) & 7u) + half;  // 32-column run within the superblock
+    const uint32_t hh = j >> 2, qr = j & 3u;
+    const uint8_t *rec = p.w + ((size_t)r * ksb + sb) * 208;
+    const float d = __half2float(*(const __half *)(p.w + (size_t)p.rows * ksb * 208 + ((size_t)sb * p.rows + r) * 2));
+#pragma unroll
+    for (int ch = 0; ch < 2; ++ch) {
+        const uint8_t *chunk = rec + (hh * 2 + ch) * 48;
+        const uint4 ql = *(const uint4 *)(chunk + (qr & 1u) * 16), qh = *(const uint4 *)(chunk + 32);
+        const float ds = __fmul_rn(d, (float)(int8_t)rec[192 + hh * 8 + qr * 2 + ch]);
+        const uint32_t lw[4] = {ql.x, ql.y, ql.z, ql.w}, hw[4] = {qh.x, qh.y, qh.z, qh.w};
+        uint32_t packed[8];
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            const uint32_t nib = ((qr >> 1) ? (lw[m] >> 4) : lw[m]) & 0x0f0f0f0fu;
+            const uint32_t top = ((hw[m] >> (2 * qr)) & 0x03030303u) << 4;
+            const uint32_t v = nib | top;  // four codes 0..63, one per byte
+            packed[m * 2] = pack_bf16((byte_f32(v, 0) - 32.0f) * ds, (byte_f32(v, 1) - 32.0f) * ds);
+            packed[m * 2 + 1] = pack_bf16((byte_f32(v, 2) - 32.0f) * ds, (byte_f32(v, 3) - 32.0f) * ds);
+        }
+        chunks[ch * 2] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        chunks[ch * 2 + 1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+    }
+}
+
+__device__ __forceinline__ void decode32(const Params &p, uint32_t r, uint32_t k0, uint32_t half, uint4 chunks[4]) {
+    if (p.fast && p.enc == Q4_K) decode32_q4k(p, r, k0, half, chunks);
+    else if (p.fast && p.layout == 1) decode32_q6k_planar(p, r, k0, half, chunks);
+    else if (p.fast && p.layout == 2) decode32_q8_0_planar(p, r, k0, half, chunks);
+    else decode32_generic(p, r, k0, half, chunks);
 }
 
 template <int BN, int STAGES>
@@ -139,17 +232,18 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_kernel(const __grid_consta
     uint8_t *a_tiles = smem;                              // [STAGES][A_BYTES], 1024-byte aligned
     uint8_t *b_tiles = a_tiles + STAGES * A_BYTES;        // [STAGES][B_BYTES]
     uint64_t *bars = (uint64_t *)(b_tiles + STAGES * B_BYTES);
-    // barriers: full_a[STAGES] (4 producer warps), full_b[STAGES] (TMA bytes), empty[STAGES] (MMA done), accum
+    // barriers: full_a[STAGES] (8 producer warps), full_b[STAGES] (TMA bytes), empty[STAGES] (MMA done), accum
     const uint32_t full_a = smem_u32(bars), full_b = smem_u32(bars + STAGES), empty = smem_u32(bars + 2 * STAGES), accum = smem_u32(bars + 3 * STAGES);
     uint32_t *tmem_slot = (uint32_t *)(bars + 3 * STAGES + 1);
     volatile uint32_t *abort_flag = tmem_slot + 1;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t row0 = blockIdx.x * BM, tok0 = blockIdx.y * BN;
+    // token tiles vary fastest over the grid: the blocks running together share a few row tiles of weights (L2) 
+    const uint32_t row0 = blockIdx.y * BM, tok0 = blockIdx.x * BN;
     const uint32_t ksteps = p.columns / BK;
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(full_a + s * 8, 4);
+            mbar_init(full_a + s * 8, PRODUCER_WARPS);
             mbar_init(full_b + s * 8, 1);
             mbar_init(empty + s * 8, 1);
         }
@@ -157,7 +251,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_kernel(const __grid_consta
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 5) {
+    if (warp == PRODUCER_WARPS + 1) {
         // tensor memory: BN columns of 128 lanes of f32, allocated and later freed by this warp
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -167,9 +261,9 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_kernel(const __grid_consta
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
 
-    if (warp < 4) {
-        // ---- decode producers: thread r owns weight row row0 + r ----
-        const uint32_t r = tid;
+    if (warp < PRODUCER_WARPS) {
+        // ---- decode producers: thread (r, half) owns 32 columns per K step of weight row row0 + r ----
+        const uint32_t r = tid & 127u, half = tid >> 7;
         const uint32_t grow = min(row0 + r, p.rows - 1);  // rows past the matrix repeat the last one; never stored
         uint8_t *arow = a_tiles + (r >> 3) * 1024 + (r & 7) * 128;
         bool ok = true;
@@ -177,24 +271,24 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_kernel(const __grid_consta
             const uint32_t s = k % STAGES;
             if (k >= STAGES) ok = mbar_wait(empty + s * 8, ((k / STAGES) - 1) & 1u, abort_flag);
             if (!ok) break;
-            uint4 chunks[8];
-            decode64(p, grow, k * BK, chunks);
+            uint4 chunks[4];
+            decode32(p, grow, k * BK, half, chunks);
 #pragma unroll
-            for (int c = 0; c < 8; ++c) *(uint4 *)(arow + s * A_BYTES + ((c ^ (r & 7)) * 16)) = chunks[c];
+            for (int c = 0; c < 4; ++c) *(uint4 *)(arow + s * A_BYTES + (((half * 4 + c) ^ (r & 7)) * 16)) = chunks[c];
             // make the generic-proxy stores visible to the tensor core's reads, then one arrival per warp
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(full_a + s * 8);
         }
-        // ---- epilogue: tensor memory -> output; warp w reads lanes 32w .. 32w+31 (its rows) ----
+        // ---- epilogue: tensor memory -> output; warp w reads lanes 32 (w & 3) .. + 31 (its rows), half of the columns ----
         if (ok) ok = mbar_wait(accum, 0, abort_flag);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
             const uint32_t out_row = row0 + r;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = (int)half * (BN / 2); c0 < (int)(half + 1) * (BN / 2); c0 += 32) {
                 uint32_t v[32];
-                const uint32_t taddr = tmem + ((warp * 32u) << 16) + (uint32_t)c0;
+                const uint32_t taddr = tmem + (((warp & 3u) * 32u) << 16) + (uint32_t)c0;
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                     "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
@@ -214,7 +308,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_kernel(const __grid_consta
             }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    } else if (warp == 4) {
+    } else if (warp == PRODUCER_WARPS) {
         // ---- activation tiles by TMA ----
         if (lane == 0) {
             bool ok = true;
@@ -253,7 +347,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_kernel(const __grid_consta
         }
     }
     __syncthreads();
-    if (warp == 5) {
+    if (warp == PRODUCER_WARPS + 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)BN) : "memory");
     }
@@ -293,9 +387,11 @@ int launch_prefill(cudaStream_t s, const PrefillJob &j) {
     if (!encode_tiled_map(&p.xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, j.in, j.columns, j.padded_tokens, j.in_stride * 2, 64, bn, CU_TENSOR_MAP_SWIZZLE_128B))
         return 0;
     p.w = j.w; p.stride = j.stride; p.enc = j.enc; p.layout = j.layout;
+    // the vector decoders read 16-byte pieces: GGUF Q4_K rows on 16-byte boundaries, or a planar form (always aligned)
+    p.fast = (j.layout == 0 && j.enc == Q4_K && (uintptr_t)j.w % 16 == 0 && j.stride % 16 == 0 && j.columns % 256 == 0) || j.layout == 1 || j.layout == 2;
     p.rows = j.rows; p.columns = j.columns; p.tokens = j.tokens;
     p.out = j.out; p.out_stride = j.out_stride; p.status = j.status;
-    dim3 grid((j.rows + prefill::BM - 1) / prefill::BM, (j.tokens + bn - 1) / bn);
+    dim3 grid((j.tokens + bn - 1) / bn, (j.rows + prefill::BM - 1) / prefill::BM);
     if (bn == 256) prefill::prefill_kernel<256, 4><<<grid, prefill::THREADS, prefill::smem_bytes<256, 4>(), s>>>(p);
     else if (bn == 128) prefill::prefill_kernel<128, 6><<<grid, prefill::THREADS, prefill::smem_bytes<128, 6>(), s>>>(p);
     else prefill::prefill_kernel<64, 8><<<grid, prefill::THREADS, prefill::smem_bytes<64, 8>(), s>>>(p);
