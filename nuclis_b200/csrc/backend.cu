@@ -514,7 +514,7 @@ int Backend::matmul(const Buffer &weights, const Matrix &m, const Buffer &input,
         PrefillJob pj{};
         pj.enc = m.encoding; pj.layout = m.layout; pj.w = w; pj.stride = stride; pj.rows = (uint32_t)m.rows; pj.columns = (uint32_t)m.columns;
         pj.tokens = (uint32_t)tokens; pj.padded_tokens = (uint32_t)padded; pj.out = out; pj.out_stride = out_stride;
-        pj.status = counters_ + counters_len_;
+        pj.status = counters_ + counters_len_; pj.sm_count = sm_count_;
         if (in_dtype == NU_BF16) {
             pj.in = in; pj.in_stride = in_stride;
         } else if (padded * m.columns * 2 <= partials_floats_ * sizeof(float)) {

@@ -102,6 +102,7 @@ struct PrefillJob {
     float *out;              // [tokens][out_stride]
     size_t out_stride;
     uint32_t *status;
+    int sm_count;
 };
 bool prefill_configure();
 bool prefill_supported(const PrefillJob &job);

@@ -5,15 +5,15 @@
 // weights into a half tile in threadgroup memory, stage the activations, 8x8 MACs).
 //
 // One block computes a 128-row x BN-token tile of the output:
-//   * warps 0..7 (256 threads: weight row tid & 127, column half tid >> 7) each decode 32 columns of
+//   * warps 0..15 (512 threads: weight row tid & 127, column quarter tid >> 7) each decode 16 columns of
 //     their row per K step to bf16 (vector decoders for 16-byte aligned Q4_K and the planar Q6_K /
 //     Q8_0 forms: byte -> float through the 2^23 magic number, one FMA, packed conversion; the
 //     generic per-16 decoder otherwise) and store them in shared memory in the 128-byte-swizzled
 //     K-major layout the tensor core reads; the same warps later move the accumulator from tensor
 //     memory to the output;
-//   * warp 8 (one thread) brings the matching BN x 64 tile of bf16 activations with one TMA
+//   * warp 16 (one thread) brings the matching BN x 64 tile of bf16 activations with one TMA
 //     tensor copy per K step (128-byte swizzle, so no thread touches those bytes);
-//   * warp 9 (one thread) issues tcgen05.mma (M = 128, N = BN, K = 16, bf16 x bf16 -> f32) four
+//   * warp 17 (one thread) issues tcgen05.mma (M = 128, N = BN, K = 16, bf16 x bf16 -> f32) four
 //     times per K step into a BN-column accumulator in tensor memory and commits to the
 //     barrier that frees the stage.
 // A ring of stages decouples the three. Every barrier wait is bounded; on expiry the block raises
@@ -34,7 +34,7 @@ namespace prefill {
 
 constexpr int BM = 128;          // weight rows per tile = tensor-memory lanes
 constexpr int BK = 64;           // columns per K step: one 128-byte swizzle row of bf16
-constexpr int PRODUCER_WARPS = 8; // decode threads: 128 rows x 2 column halves
+constexpr int PRODUCER_WARPS = 16; // decode threads: 128 rows x 4 column quarters of a K step
 constexpr int THREADS = (PRODUCER_WARPS + 2) * 32;  // + the TMA warp and the MMA warp
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 
@@ -120,30 +120,39 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 // Byte j of w as a float, through the 2^23 magic number (one permute, one exact subtraction).
 __device__ __forceinline__ float byte_f32(uint32_t w, int j) { return __uint_as_float(__byte_perm(w, 0x4b000000u, 0x7650u + j)) - 8388608.0f; }
 
-// Decodes columns [k0 + 32 half, + 32) of row r to bf16, as four 16-byte chunks: the generic path.
-__device__ __forceinline__ void decode32_generic(const Params &p, uint32_t r, uint32_t k0, uint32_t half, uint4 chunks[4]) {
+// Decodes columns [k0 + 16 q, + 16) of row r to bf16, as two 16-byte chunks: the generic path.
+__device__ __forceinline__ void decode16_generic(const Params &p, uint32_t r, uint32_t k0, uint32_t q, uint4 chunks[2]) {
+    float v[16];
+    const uint32_t seg = k0 / 16 + q;
+    if (p.layout == 1) dequant16_planar_q6k(p.w, p.rows, p.columns / 256, r, seg, v);
+    else if (p.layout == 2) dequant16_planar_q8_0(p.w, p.rows, p.columns, r, seg, v);
+    else dequant16(p.enc, p.w + (size_t)r * p.stride, seg, v);
 #pragma unroll
-    for (int s = 0; s < 2; ++s) {
-        float v[16];
-        const uint32_t seg = k0 / 16 + half * 2 + s;
-        if (p.layout == 1) dequant16_planar_q6k(p.w, p.rows, p.columns / 256, r, seg, v);
-        else if (p.layout == 2) dequant16_planar_q8_0(p.w, p.rows, p.columns, r, seg, v);
-        else dequant16(p.enc, p.w + (size_t)r * p.stride, seg, v);
-#pragma unroll
-        for (int c = 0; c < 2; ++c)
-            chunks[s * 2 + c] = make_uint4(pack_bf16(v[c * 8], v[c * 8 + 1]), pack_bf16(v[c * 8 + 2], v[c * 8 + 3]), pack_bf16(v[c * 8 + 4], v[c * 8 + 5]),
-                                           pack_bf16(v[c * 8 + 6], v[c * 8 + 7]));
-    }
+    for (int c = 0; c < 2; ++c)
+        chunks[c] = make_uint4(pack_bf16(v[c * 8], v[c * 8 + 1]), pack_bf16(v[c * 8 + 2], v[c * 8 + 3]), pack_bf16(v[c * 8 + 4], v[c * 8 + 5]),
+                               pack_bf16(v[c * 8 + 6], v[c * 8 + 7]));
 }
 
-// Q4_K, rows 16-byte aligned: the 64 columns of a K step are one group pair; half 0 is its even
-// group (low nibbles), half 1 the odd group (high nibbles). Values are (d*s)*q - dmin*m with one
-// rounding, like the reference decoder (inference/src/quant/decode.zig:147-170), then rounded to bf16.
-__device__ __forceinline__ void decode32_q4k(const Params &p, uint32_t r, uint32_t k0, uint32_t half, uint4 chunks[4]) {
+// The bytes a producer thread needs for one K step, requested one step ahead of their use so that
+// the latency of the loads hides behind the decoding of the step before.
+struct Raw {
+    uint4 v[2];
+    uint32_t s;  // scale bytes / f16 scale bits, by encoding
+};
+
+// Q4_K, rows 16-byte aligned: the 64 columns of a K step are one group pair; quarters 0, 1 are its
+// even group (low nibbles of bytes 0..15, 16..31), quarters 2, 3 the odd group (high nibbles).
+// Values are (d*s)*q - dmin*m with one rounding, like the reference decoder
+// (inference/src/quant/decode.zig:147-170), then rounded to bf16.
+__device__ __forceinline__ void load16_q4k(const Params &p, uint32_t r, uint32_t k0, uint32_t q, Raw &raw) {
     const uint8_t *block = p.w + (size_t)r * p.stride + (size_t)(k0 / 256) * 144;
-    const uint32_t pair = (k0 / 64) & 3u, grp = pair * 2 + half;
-    const uint4 hdr = *(const uint4 *)block;
-    const uint4 qa = *(const uint4 *)(block + 16 + pair * 32), qb = *(const uint4 *)(block + 32 + pair * 32);
+    const uint32_t pair = (k0 / 64) & 3u;
+    raw.v[0] = *(const uint4 *)block;
+    raw.v[1] = *(const uint4 *)(block + 16 + pair * 32 + (q & 1u) * 16);
+}
+__device__ __forceinline__ void convert16_q4k(const Raw &raw, uint32_t k0, uint32_t q, uint4 chunks[2]) {
+    const uint32_t pair = (k0 / 64) & 3u, half = q >> 1, grp = pair * 2 + half;
+    const uint4 hdr = raw.v[0], qq = raw.v[1];
     // six-bit scale and minimum of group grp out of the 12 packed bytes (words hdr.y, hdr.z, hdr.w)
     const uint32_t lo_byte = grp & 3u;
     const uint32_t y = (hdr.y >> (8 * lo_byte)) & 0xffu, z = (hdr.z >> (8 * lo_byte)) & 0xffu, w = (hdr.w >> (8 * lo_byte)) & 0xffu;
@@ -151,9 +160,9 @@ __device__ __forceinline__ void decode32_q4k(const Params &p, uint32_t r, uint32
     const uint32_t m6 = grp < 4 ? (z & 63u) : ((w >> 4) | ((z >> 6) << 4));
     const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu))), dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
     const float ds = __fmul_rn(d, (float)s6), ndm = -__fmul_rn(dmin, (float)m6);
-    const uint32_t words[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+    const uint32_t words[4] = {qq.x, qq.y, qq.z, qq.w};
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < 2; ++c) {
         uint32_t packed[4];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -167,15 +176,17 @@ __device__ __forceinline__ void decode32_q4k(const Params &p, uint32_t r, uint32
     }
 }
 
-// Planar Q8_0 (prepare.cu): 32 columns are one block; value = d * code, exact before the bf16 rounding.
-__device__ __forceinline__ void decode32_q8_0_planar(const Params &p, uint32_t r, uint32_t k0, uint32_t half, uint4 chunks[4]) {
-    const uint8_t *q = p.w + (size_t)r * p.columns + k0 + half * 32;
-    const uint32_t blk = k0 / 32 + half;
-    const float d = __half2float(*(const __half *)(p.w + (size_t)p.rows * p.columns + ((size_t)blk * p.rows + r) * 2));
-    const uint4 qa = *(const uint4 *)q, qb = *(const uint4 *)(q + 16);
-    const uint32_t words[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+// Planar Q8_0 (prepare.cu): 16 columns are half a block; value = d * code, exact before the bf16 rounding.
+__device__ __forceinline__ void load16_q8_0_planar(const Params &p, uint32_t r, uint32_t k0, uint32_t q, Raw &raw) {
+    const uint32_t blk = k0 / 32 + (q >> 1);
+    raw.v[0] = *(const uint4 *)(p.w + (size_t)r * p.columns + k0 + q * 16);
+    raw.s = *(const unsigned short *)(p.w + (size_t)p.rows * p.columns + ((size_t)blk * p.rows + r) * 2);
+}
+__device__ __forceinline__ void convert16_q8_0_planar(const Raw &raw, uint4 chunks[2]) {
+    const float d = __half2float(__ushort_as_half((unsigned short)raw.s));
+    const uint32_t words[4] = {raw.v[0].x, raw.v[0].y, raw.v[0].z, raw.v[0].w};
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < 2; ++c) {
         uint32_t packed[4];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -189,38 +200,50 @@ __device__ __forceinline__ void decode32_q8_0_planar(const Params &p, uint32_t r
     }
 }
 
-// Planar Q6_K (prepare.cu): the 32 columns are quarter qr of half hh of a superblock, 16 from each
-// column half ch (one planar chunk and one scale each); value = (d * scale) * (code - 32), exact.
-__device__ __forceinline__ void decode32_q6k_planar(const Params &p, uint32_t r, uint32_t k0, uint32_t half, uint4 chunks[4]) {
-    const uint32_t ksb = p.columns / 256, sb = k0 / 256, j = ((k0 / 32) & 7u) + half;  // 32-column run within the superblock
+// Planar Q6_K (prepare.cu): the 16 columns are column half ch of quarter qr of half hh of a
+// superblock: one planar chunk and one scale; value = (d * scale) * (code - 32), exact.
+__device__ __forceinline__ void load16_q6k_planar(const Params &p, uint32_t r, uint32_t k0, uint32_t q, Raw &raw) {
+    const uint32_t ksb = p.columns / 256, sb = k0 / 256, j = ((k0 / 32) & 7u) + (q >> 1), ch = q & 1u;  // 32-column run j, its half ch
     const uint32_t hh = j >> 2, qr = j & 3u;
     const uint8_t *rec = p.w + ((size_t)r * ksb + sb) * 208;
-    const float d = __half2float(*(const __half *)(p.w + (size_t)p.rows * ksb * 208 + ((size_t)sb * p.rows + r) * 2));
+    const uint8_t *chunk = rec + (hh * 2 + ch) * 48;
+    raw.v[0] = *(const uint4 *)(chunk + (qr & 1u) * 16);
+    raw.v[1] = *(const uint4 *)(chunk + 32);
+    const uint32_t scale = rec[192 + hh * 8 + qr * 2 + ch];
+    const uint32_t dbits = *(const unsigned short *)(p.w + (size_t)p.rows * ksb * 208 + ((size_t)sb * p.rows + r) * 2);
+    raw.s = scale | (dbits << 16);
+}
+__device__ __forceinline__ void convert16_q6k_planar(const Raw &raw, uint32_t k0, uint32_t q, uint4 chunks[2]) {
+    const uint32_t qr = (((k0 / 32) & 7u) + (q >> 1)) & 3u;
+    const float d = __half2float(__ushort_as_half((unsigned short)(raw.s >> 16)));
+    const float ds = __fmul_rn(d, (float)(int8_t)(raw.s & 0xffu));
+    const uint4 ql = raw.v[0], qh = raw.v[1];
+    const uint32_t lw[4] = {ql.x, ql.y, ql.z, ql.w}, hw[4] = {qh.x, qh.y, qh.z, qh.w};
+    uint32_t packed[8];
 #pragma unroll
-    for (int ch = 0; ch < 2; ++ch) {
-        const uint8_t *chunk = rec + (hh * 2 + ch) * 48;
-        const uint4 ql = *(const uint4 *)(chunk + (qr & 1u) * 16), qh = *(const uint4 *)(chunk + 32);
-        const float ds = __fmul_rn(d, (float)(int8_t)rec[192 + hh * 8 + qr * 2 + ch]);
-        const uint32_t lw[4] = {ql.x, ql.y, ql.z, ql.w}, hw[4] = {qh.x, qh.y, qh.z, qh.w};
-        uint32_t packed[8];
-#pragma unroll
-        for (int m = 0; m < 4; ++m) {
-            const uint32_t nib = ((qr >> 1) ? (lw[m] >> 4) : lw[m]) & 0x0f0f0f0fu;
-            const uint32_t top = ((hw[m] >> (2 * qr)) & 0x03030303u) << 4;
-            const uint32_t v = nib | top;  // four codes 0..63, one per byte
-            packed[m * 2] = pack_bf16((byte_f32(v, 0) - 32.0f) * ds, (byte_f32(v, 1) - 32.0f) * ds);
-            packed[m * 2 + 1] = pack_bf16((byte_f32(v, 2) - 32.0f) * ds, (byte_f32(v, 3) - 32.0f) * ds);
-        }
-        chunks[ch * 2] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-        chunks[ch * 2 + 1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+    for (int m = 0; m < 4; ++m) {
+        const uint32_t nib = ((qr >> 1) ? (lw[m] >> 4) : lw[m]) & 0x0f0f0f0fu;
+        const uint32_t top = ((hw[m] >> (2 * qr)) & 0x03030303u) << 4;
+        const uint32_t v = nib | top;  // four codes 0..63, one per byte
+        packed[m * 2] = pack_bf16((byte_f32(v, 0) - 32.0f) * ds, (byte_f32(v, 1) - 32.0f) * ds);
+        packed[m * 2 + 1] = pack_bf16((byte_f32(v, 2) - 32.0f) * ds, (byte_f32(v, 3) - 32.0f) * ds);
     }
+    chunks[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    chunks[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
 }
 
-__device__ __forceinline__ void decode32(const Params &p, uint32_t r, uint32_t k0, uint32_t half, uint4 chunks[4]) {
-    if (p.fast && p.enc == Q4_K) decode32_q4k(p, r, k0, half, chunks);
-    else if (p.fast && p.layout == 1) decode32_q6k_planar(p, r, k0, half, chunks);
-    else if (p.fast && p.layout == 2) decode32_q8_0_planar(p, r, k0, half, chunks);
-    else decode32_generic(p, r, k0, half, chunks);
+// mode: 0 generic, 1 Q4_K, 2 planar Q6_K, 3 planar Q8_0
+__device__ __forceinline__ uint32_t decode_mode(const Params &p) { return !p.fast ? 0u : p.enc == Q4_K ? 1u : p.layout == 1 ? 2u : 3u; }
+__device__ __forceinline__ void load16(const Params &p, uint32_t mode, uint32_t r, uint32_t k0, uint32_t q, Raw &raw) {
+    if (mode == 1) load16_q4k(p, r, k0, q, raw);
+    else if (mode == 2) load16_q6k_planar(p, r, k0, q, raw);
+    else if (mode == 3) load16_q8_0_planar(p, r, k0, q, raw);
+}
+__device__ __forceinline__ void convert16(const Params &p, uint32_t mode, const Raw &raw, uint32_t r, uint32_t k0, uint32_t q, uint4 chunks[2]) {
+    if (mode == 1) convert16_q4k(raw, k0, q, chunks);
+    else if (mode == 2) convert16_q6k_planar(raw, k0, q, chunks);
+    else if (mode == 3) convert16_q8_0_planar(raw, chunks);
+    else decode16_generic(p, r, k0, q, chunks);
 }
 
 template <int BN, int STAGES>
@@ -232,7 +255,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_kernel(const __grid_consta
     uint8_t *a_tiles = smem;                              // [STAGES][A_BYTES], 1024-byte aligned
     uint8_t *b_tiles = a_tiles + STAGES * A_BYTES;        // [STAGES][B_BYTES]
     uint64_t *bars = (uint64_t *)(b_tiles + STAGES * B_BYTES);
-    // barriers: full_a[STAGES] (8 producer warps), full_b[STAGES] (TMA bytes), empty[STAGES] (MMA done), accum
+    // barriers: full_a[STAGES] (16 producer warps), full_b[STAGES] (TMA bytes), empty[STAGES] (MMA done), accum
     const uint32_t full_a = smem_u32(bars), full_b = smem_u32(bars + STAGES), empty = smem_u32(bars + 2 * STAGES), accum = smem_u32(bars + 3 * STAGES);
     uint32_t *tmem_slot = (uint32_t *)(bars + 3 * STAGES + 1);
     volatile uint32_t *abort_flag = tmem_slot + 1;
@@ -262,28 +285,34 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_kernel(const __grid_consta
     const uint32_t tmem = *tmem_slot;
 
     if (warp < PRODUCER_WARPS) {
-        // ---- decode producers: thread (r, half) owns 32 columns per K step of weight row row0 + r ----
-        const uint32_t r = tid & 127u, half = tid >> 7;
+        // ---- decode producers: thread (r, q) owns 16 columns per K step of weight row row0 + r ----
+        const uint32_t r = tid & 127u, q = tid >> 7;
         const uint32_t grow = min(row0 + r, p.rows - 1);  // rows past the matrix repeat the last one; never stored
         uint8_t *arow = a_tiles + (r >> 3) * 1024 + (r & 7) * 128;
         bool ok = true;
+        const uint32_t mode = decode_mode(p);
+        Raw raw;
+        load16(p, mode, grow, 0, q, raw);
         for (uint32_t k = 0; k < ksteps && ok; ++k) {
             const uint32_t s = k % STAGES;
+            const Raw cur = raw;
+            if (k + 1 < ksteps) load16(p, mode, grow, (k + 1) * BK, q, raw);  // in flight while this step is decoded
             if (k >= STAGES) ok = mbar_wait(empty + s * 8, ((k / STAGES) - 1) & 1u, abort_flag);
             if (!ok) break;
-            uint4 chunks[4];
-            decode32(p, grow, k * BK, half, chunks);
+            uint4 chunks[2];
+            convert16(p, mode, cur, grow, k * BK, q, chunks);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) *(uint4 *)(arow + s * A_BYTES + (((half * 4 + c) ^ (r & 7)) * 16)) = chunks[c];
+            for (int c = 0; c < 2; ++c) *(uint4 *)(arow + s * A_BYTES + (((q * 2 + c) ^ (r & 7)) * 16)) = chunks[c];
             // make the generic-proxy stores visible to the tensor core's reads, then one arrival per warp
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(full_a + s * 8);
         }
-        // ---- epilogue: tensor memory -> output; warp w reads lanes 32 (w & 3) .. + 31 (its rows), half of the columns ----
-        if (ok) ok = mbar_wait(accum, 0, abort_flag);
+        // ---- epilogue: tensor memory -> output; warps 0..7: warp w reads lanes 32 (w & 3) .. + 31 (its rows), half of the columns ----
+        const uint32_t half = q & 1u;
+        if (ok && q < 2) ok = mbar_wait(accum, 0, abort_flag);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok) {
+        if (ok && q < 2) {
             const uint32_t out_row = row0 + r;
 #pragma unroll 1
             for (int c0 = (int)half * (BN / 2); c0 < (int)(half + 1) * (BN / 2); c0 += 32) {
@@ -366,9 +395,15 @@ static bool configure_bn() {
     return cudaFuncSetAttribute(prefill::prefill_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, prefill::smem_bytes<BN, STAGES>()) == cudaSuccess;
 }
 
-bool prefill_configure() { return configure_bn<256, 4>() && configure_bn<128, 6>() && configure_bn<64, 8>(); }
+#ifndef NU_PREFILL_STAGES256
+#define NU_PREFILL_STAGES256 4
+#endif
+#ifndef NU_PREFILL_MAXBN
+#define NU_PREFILL_MAXBN 256
+#endif
+bool prefill_configure() { return configure_bn<256, NU_PREFILL_STAGES256>() && configure_bn<128, 6>() && configure_bn<64, 8>(); }
 
-static uint32_t pick_bn(uint32_t tokens) { return tokens > 128 ? 256 : tokens > 64 ? 128 : 64; }
+static uint32_t pick_bn(uint32_t tokens) { return tokens > 128 && NU_PREFILL_MAXBN >= 256 ? 256 : tokens > 64 ? 128 : 64; }
 
 bool prefill_supported(const PrefillJob &j) {
     if (layout(j.enc).elements == 0 || j.rows == 0 || j.tokens == 0) return false;
@@ -392,7 +427,7 @@ int launch_prefill(cudaStream_t s, const PrefillJob &j) {
     p.rows = j.rows; p.columns = j.columns; p.tokens = j.tokens;
     p.out = j.out; p.out_stride = j.out_stride; p.status = j.status;
     dim3 grid((j.tokens + bn - 1) / bn, (j.rows + prefill::BM - 1) / prefill::BM);
-    if (bn == 256) prefill::prefill_kernel<256, 4><<<grid, prefill::THREADS, prefill::smem_bytes<256, 4>(), s>>>(p);
+    if (bn == 256) prefill::prefill_kernel<256, NU_PREFILL_STAGES256><<<grid, prefill::THREADS, prefill::smem_bytes<256, NU_PREFILL_STAGES256>(), s>>>(p);
     else if (bn == 128) prefill::prefill_kernel<128, 6><<<grid, prefill::THREADS, prefill::smem_bytes<128, 6>(), s>>>(p);
     else prefill::prefill_kernel<64, 8><<<grid, prefill::THREADS, prefill::smem_bytes<64, 8>(), s>>>(p);
     return 1;
