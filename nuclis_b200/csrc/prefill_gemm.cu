@@ -5,15 +5,15 @@
 // weights into a half tile in threadgroup memory, stage the activations, 8x8 MACs).
 //
 // One block computes a 128-row x BN-token tile of the output:
-//   * warps 0..15 (512 threads: weight row tid & 127, column quarter tid >> 7) each decode 16 columns of
+//   * warps 0..7 (256 threads: weight row tid & 127, column half tid >> 7) each decode 32 columns of
 //     their row per K step to bf16 (vector decoders for 16-byte aligned Q4_K and the planar Q6_K /
 //     Q8_0 forms: byte -> float through the 2^23 magic number, one FMA, packed conversion; the
 //     generic per-16 decoder otherwise) and store them in shared memory in the 128-byte-swizzled
 //     K-major layout the tensor core reads; the same warps later move the accumulator from tensor
 //     memory to the output;
-//   * warp 16 (one thread) brings the matching BN x 64 tile of bf16 activations with one TMA
+//   * warp 8 (one thread) brings the matching BN x 64 tile of bf16 activations with one TMA
 //     tensor copy per K step (128-byte swizzle, so no thread touches those bytes);
-//   * warp 17 (one thread) issues tcgen05.mma (M = 128, N = BN, K = 16, bf16 x bf16 -> f32) four
+//   * warp 9 (one thread) issues tcgen05.mma (M = 128, N = BN, K = 16, bf16 x bf16 -> f32) four
 //     times per K step into a BN-column accumulator in tensor memory and commits to the
 //     barrier that frees the stage.
 // A ring of stages decouples the three. Every barrier wait is bounded; on expiry the block raises
@@ -34,7 +34,7 @@ namespace prefill {
 
 constexpr int BM = 128;          // weight rows per tile = tensor-memory lanes
 constexpr int BK = 64;           // columns per K step: one 128-byte swizzle row of bf16
-constexpr int PRODUCER_WARPS = 16; // decode threads: 128 rows x 4 column quarters of a K step
+constexpr int PRODUCER_WARPS = 8;  // decode threads: 128 rows x 2 column halves of a K step
 constexpr int THREADS = (PRODUCER_WARPS + 2) * 32;  // + the TMA warp and the MMA warp
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 
@@ -133,120 +133,15 @@ __device__ __forceinline__ void decode16_generic(const Params &p, uint32_t r, ui
                                pack_bf16(v[c * 8 + 6], v[c * 8 + 7]));
 }
 
-// The bytes a producer thread needs for one K step, requested one step ahead of their use so that
-// the latency of the loads hides behind the decoding of the step before.
-struct Raw {
-    uint4 v[2];
-    uint32_t s;  // scale bytes / f16 scale bits, by encoding
-};
+// Four bytes of codes (one per byte of t4) -> four values (code * mul + add) as two packed bf16 pairs.
+__device__ __forceinline__ void codes4_fma(uint32_t t4, float mul, float add, uint32_t &lo, uint32_t &hi) {
+    lo = pack_bf16(fmaf(byte_f32(t4, 0), mul, add), fmaf(byte_f32(t4, 1), mul, add));
+    hi = pack_bf16(fmaf(byte_f32(t4, 2), mul, add), fmaf(byte_f32(t4, 3), mul, add));
+}
+__device__ __forceinline__ uint4 ldg16(const uint8_t *ptr) { return __ldg((const uint4 *)ptr); }
 
-// Q4_K, rows 16-byte aligned: the 64 columns of a K step are one group pair; quarters 0, 1 are its
-// even group (low nibbles of bytes 0..15, 16..31), quarters 2, 3 the odd group (high nibbles).
-// Values are (d*s)*q - dmin*m with one rounding, like the reference decoder
-// (inference/src/quant/decode.zig:147-170), then rounded to bf16.
-__device__ __forceinline__ void load16_q4k(const Params &p, uint32_t r, uint32_t k0, uint32_t q, Raw &raw) {
-    const uint8_t *block = p.w + (size_t)r * p.stride + (size_t)(k0 / 256) * 144;
-    const uint32_t pair = (k0 / 64) & 3u;
-    raw.v[0] = *(const uint4 *)block;
-    raw.v[1] = *(const uint4 *)(block + 16 + pair * 32 + (q & 1u) * 16);
-}
-__device__ __forceinline__ void convert16_q4k(const Raw &raw, uint32_t k0, uint32_t q, uint4 chunks[2]) {
-    const uint32_t pair = (k0 / 64) & 3u, half = q >> 1, grp = pair * 2 + half;
-    const uint4 hdr = raw.v[0], qq = raw.v[1];
-    // six-bit scale and minimum of group grp out of the 12 packed bytes (words hdr.y, hdr.z, hdr.w)
-    const uint32_t lo_byte = grp & 3u;
-    const uint32_t y = (hdr.y >> (8 * lo_byte)) & 0xffu, z = (hdr.z >> (8 * lo_byte)) & 0xffu, w = (hdr.w >> (8 * lo_byte)) & 0xffu;
-    const uint32_t s6 = grp < 4 ? (y & 63u) : ((w & 15u) | ((y >> 6) << 4));
-    const uint32_t m6 = grp < 4 ? (z & 63u) : ((w >> 4) | ((z >> 6) << 4));
-    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu))), dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
-    const float ds = __fmul_rn(d, (float)s6), ndm = -__fmul_rn(dmin, (float)m6);
-    const uint32_t words[4] = {qq.x, qq.y, qq.z, qq.w};
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-        uint32_t packed[4];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const uint32_t t4 = (half ? (words[c * 2 + h] >> 4) : words[c * 2 + h]) & 0x0f0f0f0fu;  // four codes, one per byte
-            const float v0 = fmaf(byte_f32(t4, 0), ds, ndm), v1 = fmaf(byte_f32(t4, 1), ds, ndm);
-            const float v2 = fmaf(byte_f32(t4, 2), ds, ndm), v3 = fmaf(byte_f32(t4, 3), ds, ndm);
-            packed[h * 2] = pack_bf16(v0, v1);
-            packed[h * 2 + 1] = pack_bf16(v2, v3);
-        }
-        chunks[c] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-    }
-}
-
-// Planar Q8_0 (prepare.cu): 16 columns are half a block; value = d * code, exact before the bf16 rounding.
-__device__ __forceinline__ void load16_q8_0_planar(const Params &p, uint32_t r, uint32_t k0, uint32_t q, Raw &raw) {
-    const uint32_t blk = k0 / 32 + (q >> 1);
-    raw.v[0] = *(const uint4 *)(p.w + (size_t)r * p.columns + k0 + q * 16);
-    raw.s = *(const unsigned short *)(p.w + (size_t)p.rows * p.columns + ((size_t)blk * p.rows + r) * 2);
-}
-__device__ __forceinline__ void convert16_q8_0_planar(const Raw &raw, uint4 chunks[2]) {
-    const float d = __half2float(__ushort_as_half((unsigned short)raw.s));
-    const uint32_t words[4] = {raw.v[0].x, raw.v[0].y, raw.v[0].z, raw.v[0].w};
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-        uint32_t packed[4];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const uint32_t u = words[c * 2 + h] ^ 0x80808080u;  // code + 128
-            const float v0 = (byte_f32(u, 0) - 128.0f) * d, v1 = (byte_f32(u, 1) - 128.0f) * d;
-            const float v2 = (byte_f32(u, 2) - 128.0f) * d, v3 = (byte_f32(u, 3) - 128.0f) * d;
-            packed[h * 2] = pack_bf16(v0, v1);
-            packed[h * 2 + 1] = pack_bf16(v2, v3);
-        }
-        chunks[c] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-    }
-}
-
-// Planar Q6_K (prepare.cu): the 16 columns are column half ch of quarter qr of half hh of a
-// superblock: one planar chunk and one scale; value = (d * scale) * (code - 32), exact.
-__device__ __forceinline__ void load16_q6k_planar(const Params &p, uint32_t r, uint32_t k0, uint32_t q, Raw &raw) {
-    const uint32_t ksb = p.columns / 256, sb = k0 / 256, j = ((k0 / 32) & 7u) + (q >> 1), ch = q & 1u;  // 32-column run j, its half ch
-    const uint32_t hh = j >> 2, qr = j & 3u;
-    const uint8_t *rec = p.w + ((size_t)r * ksb + sb) * 208;
-    const uint8_t *chunk = rec + (hh * 2 + ch) * 48;
-    raw.v[0] = *(const uint4 *)(chunk + (qr & 1u) * 16);
-    raw.v[1] = *(const uint4 *)(chunk + 32);
-    const uint32_t scale = rec[192 + hh * 8 + qr * 2 + ch];
-    const uint32_t dbits = *(const unsigned short *)(p.w + (size_t)p.rows * ksb * 208 + ((size_t)sb * p.rows + r) * 2);
-    raw.s = scale | (dbits << 16);
-}
-__device__ __forceinline__ void convert16_q6k_planar(const Raw &raw, uint32_t k0, uint32_t q, uint4 chunks[2]) {
-    const uint32_t qr = (((k0 / 32) & 7u) + (q >> 1)) & 3u;
-    const float d = __half2float(__ushort_as_half((unsigned short)(raw.s >> 16)));
-    const float ds = __fmul_rn(d, (float)(int8_t)(raw.s & 0xffu));
-    const uint4 ql = raw.v[0], qh = raw.v[1];
-    const uint32_t lw[4] = {ql.x, ql.y, ql.z, ql.w}, hw[4] = {qh.x, qh.y, qh.z, qh.w};
-    uint32_t packed[8];
-#pragma unroll
-    for (int m = 0; m < 4; ++m) {
-        const uint32_t nib = ((qr >> 1) ? (lw[m] >> 4) : lw[m]) & 0x0f0f0f0fu;
-        const uint32_t top = ((hw[m] >> (2 * qr)) & 0x03030303u) << 4;
-        const uint32_t v = nib | top;  // four codes 0..63, one per byte
-        packed[m * 2] = pack_bf16((byte_f32(v, 0) - 32.0f) * ds, (byte_f32(v, 1) - 32.0f) * ds);
-        packed[m * 2 + 1] = pack_bf16((byte_f32(v, 2) - 32.0f) * ds, (byte_f32(v, 3) - 32.0f) * ds);
-    }
-    chunks[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-    chunks[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-}
-
-// mode: 0 generic, 1 Q4_K, 2 planar Q6_K, 3 planar Q8_0
-__device__ __forceinline__ uint32_t decode_mode(const Params &p) { return !p.fast ? 0u : p.enc == Q4_K ? 1u : p.layout == 1 ? 2u : 3u; }
-__device__ __forceinline__ void load16(const Params &p, uint32_t mode, uint32_t r, uint32_t k0, uint32_t q, Raw &raw) {
-    if (mode == 1) load16_q4k(p, r, k0, q, raw);
-    else if (mode == 2) load16_q6k_planar(p, r, k0, q, raw);
-    else if (mode == 3) load16_q8_0_planar(p, r, k0, q, raw);
-}
-__device__ __forceinline__ void convert16(const Params &p, uint32_t mode, const Raw &raw, uint32_t r, uint32_t k0, uint32_t q, uint4 chunks[2]) {
-    if (mode == 1) convert16_q4k(raw, k0, q, chunks);
-    else if (mode == 2) convert16_q6k_planar(raw, k0, q, chunks);
-    else if (mode == 3) convert16_q8_0_planar(raw, chunks);
-    else decode16_generic(p, r, k0, q, chunks);
-}
-
-template <int BN, int STAGES>
+// MODE: 0 the generic decoders (any encoding and layout), 1 Q4_K with 16-byte aligned rows, 2 planar Q6_K, 3 planar Q8_0.
+template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(THREADS, 1) prefill_kernel(const __grid_constant__ Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // swizzled tiles sit on 1024-byte boundaries
@@ -255,7 +150,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_kernel(const __grid_consta
     uint8_t *a_tiles = smem;                              // [STAGES][A_BYTES], 1024-byte aligned
     uint8_t *b_tiles = a_tiles + STAGES * A_BYTES;        // [STAGES][B_BYTES]
     uint64_t *bars = (uint64_t *)(b_tiles + STAGES * B_BYTES);
-    // barriers: full_a[STAGES] (16 producer warps), full_b[STAGES] (TMA bytes), empty[STAGES] (MMA done), accum
+    // barriers: full_a[STAGES] (8 producer warps), full_b[STAGES] (TMA bytes), empty[STAGES] (MMA done), accum
     const uint32_t full_a = smem_u32(bars), full_b = smem_u32(bars + STAGES), empty = smem_u32(bars + 2 * STAGES), accum = smem_u32(bars + 3 * STAGES);
     uint32_t *tmem_slot = (uint32_t *)(bars + 3 * STAGES + 1);
     volatile uint32_t *abort_flag = tmem_slot + 1;
@@ -285,35 +180,171 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_kernel(const __grid_consta
     const uint32_t tmem = *tmem_slot;
 
     if (warp < PRODUCER_WARPS) {
-        // ---- decode producers: thread (r, q) owns 16 columns per K step of weight row row0 + r ----
-        const uint32_t r = tid & 127u, q = tid >> 7;
+        // ---- decode producers: warp w owns weight rows 16 w .. 16 w + 15 of the tile, lane l row l & 15 and
+        // piece l >> 4: the two lanes of a row read adjacent bytes (a warp-wide load touches 16 short runs
+        // instead of 32 scattered 16-byte pieces: the load/store unit, not arithmetic, bounds this warp).
+        // The bytes of a step are requested one step ahead of their use, so that the latency of the loads
+        // hides behind the decoding of the step before; pointers advance, nothing is recomputed per step.
+        const uint32_t r = warp * 16 + (lane & 15u), piece = lane >> 4;
         const uint32_t grow = min(row0 + r, p.rows - 1);  // rows past the matrix repeat the last one; never stored
         uint8_t *arow = a_tiles + (r >> 3) * 1024 + (r & 7) * 128;
         bool ok = true;
-        const uint32_t mode = decode_mode(p);
-        Raw raw;
-        load16(p, mode, grow, 0, q, raw);
-        for (uint32_t k = 0; k < ksteps && ok; ++k) {
-            const uint32_t s = k % STAGES;
-            const Raw cur = raw;
-            if (k + 1 < ksteps) load16(p, mode, grow, (k + 1) * BK, q, raw);  // in flight while this step is decoded
-            if (k >= STAGES) ok = mbar_wait(empty + s * 8, ((k / STAGES) - 1) & 1u, abort_flag);
-            if (!ok) break;
-            uint4 chunks[2];
-            convert16(p, mode, cur, grow, k * BK, q, chunks);
-#pragma unroll
-            for (int c = 0; c < 2; ++c) *(uint4 *)(arow + s * A_BYTES + (((q * 2 + c) ^ (r & 7)) * 16)) = chunks[c];
+        uint32_t s = 0, round = 0;
+        // Stores four 16-byte chunks of a step (chunk positions pos[0..3] of the row's eight) into the
+        // stage's swizzled tile and hands the stage over.
+        auto put = [&](const uint4 (&chunks)[4], uint32_t pos0, uint32_t pos1) -> bool {
+            if (round && !mbar_wait(empty + s * 8, (round - 1) & 1u, abort_flag)) return false;
+            uint8_t *dst = arow + s * A_BYTES;
+            *(uint4 *)(dst + ((pos0 ^ (r & 7)) * 16)) = chunks[0];
+            *(uint4 *)(dst + (((pos0 + 1) ^ (r & 7)) * 16)) = chunks[1];
+            *(uint4 *)(dst + ((pos1 ^ (r & 7)) * 16)) = chunks[2];
+            *(uint4 *)(dst + (((pos1 + 1) ^ (r & 7)) * 16)) = chunks[3];
             // make the generic-proxy stores visible to the tensor core's reads, then one arrival per warp
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(full_a + s * 8);
+            if (++s == STAGES) { s = 0; ++round; }
+            return true;
+        };
+        if (MODE == 1) {
+            // Q4_K: a K step is one group pair of a superblock: 32 quant bytes whose low nibbles are the even
+            // group (columns 0..31 of the step) and high nibbles the odd group (columns 32..63). Piece p holds
+            // bytes 16 p .. 16 p + 15: columns 16 p .. + 15 of both groups. Values are (d*s)*q - dmin*m with one
+            // rounding, like the reference decoder (inference/src/quant/decode.zig:147-170), then rounded to bf16.
+            const uint8_t *blk = p.w + (size_t)grow * p.stride;
+            const uint32_t nsb = p.columns / 256;
+            uint4 hdr_n = ldg16(blk), q_n = ldg16(blk + 16 + piece * 16);
+            for (uint32_t sb = 0; sb < nsb && ok; ++sb, blk += 144) {
+                const uint4 hdr = hdr_n;
+                const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu))), dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint4 qq = q_n;
+                    if (j < 3) {
+                        q_n = ldg16(blk + 16 + (j + 1) * 32 + piece * 16);
+                    } else if (sb + 1 < nsb) {
+                        hdr_n = ldg16(blk + 144);
+                        q_n = ldg16(blk + 160 + piece * 16);
+                    }
+                    // six-bit scales and minima of groups 2j and 2j+1 out of the 12 packed bytes (words hdr.y, hdr.z, hdr.w)
+                    float ds[2], ndm[2];
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int sh = 8 * (2 * (j & 1) + e);
+                        const uint32_t y = (hdr.y >> sh) & 0xffu, z = (hdr.z >> sh) & 0xffu, w = (hdr.w >> sh) & 0xffu;
+                        const uint32_t s6 = j < 2 ? (y & 63u) : ((w & 15u) | ((y >> 6) << 4));
+                        const uint32_t m6 = j < 2 ? (z & 63u) : ((w >> 4) | ((z >> 6) << 4));
+                        ds[e] = __fmul_rn(d, (float)s6);
+                        ndm[e] = -__fmul_rn(dmin, (float)m6);
+                    }
+                    const uint32_t words[4] = {qq.x, qq.y, qq.z, qq.w};
+                    uint4 chunks[4];  // 0, 1: the even group's 16 columns; 2, 3: the odd group's
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        codes4_fma(words[c * 2] & 0x0f0f0f0fu, ds[0], ndm[0], chunks[c].x, chunks[c].y);
+                        codes4_fma(words[c * 2 + 1] & 0x0f0f0f0fu, ds[0], ndm[0], chunks[c].z, chunks[c].w);
+                        codes4_fma((words[c * 2] >> 4) & 0x0f0f0f0fu, ds[1], ndm[1], chunks[2 + c].x, chunks[2 + c].y);
+                        codes4_fma((words[c * 2 + 1] >> 4) & 0x0f0f0f0fu, ds[1], ndm[1], chunks[2 + c].z, chunks[2 + c].w);
+                    }
+                    ok = put(chunks, piece * 2, 4 + piece * 2);
+                    if (!ok) break;
+                }
+            }
+        } else if (MODE == 2) {
+            // Planar Q6_K (prepare.cu): K step j of a superblock holds 32-column runs 2j and 2j+1: quarters
+            // 2 (j & 1) and 2 (j & 1) + 1 of half j >> 1. Piece ch is the planar chunk of column half ch: 16
+            // columns of each run, one scale each; its 48 bytes serve two K steps (low nibbles: quarters 0, 1;
+            // high nibbles: quarters 2, 3). Value = (d * scale) * (code - 32), exact.
+            const uint32_t nsb = p.columns / 256;
+            const uint8_t *rec = p.w + (size_t)grow * nsb * 208;
+            const uint8_t *dp = p.w + (size_t)p.rows * nsb * 208 + (size_t)grow * 2;
+            const size_t dstep = (size_t)p.rows * 2;
+            uint4 raw_n[3];
+            uint2 sc_n;  // the 8 scales of a half: bytes qr * 2 + ch
+            auto fetch = [&](const uint8_t *record, int hh) {
+                const uint8_t *chunk = record + (hh * 2 + piece) * 48;
+                raw_n[0] = ldg16(chunk);
+                raw_n[1] = ldg16(chunk + 16);
+                raw_n[2] = ldg16(chunk + 32);
+                sc_n = *(const uint2 *)(record + 192 + hh * 8);
+            };
+            fetch(rec, 0);
+            float d_n = __half2float(*(const __half *)dp);
+            for (uint32_t sb = 0; sb < nsb && ok; ++sb, rec += 208) {
+                const float d = d_n;
+                if (sb + 1 < nsb) { dp += dstep; d_n = __half2float(*(const __half *)dp); }
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const uint4 qla = raw_n[0], qlb = raw_n[1], qh = raw_n[2];
+                    const uint2 scs = sc_n;
+                    if (hh == 0) fetch(rec, 1);
+                    else if (sb + 1 < nsb) fetch(rec + 208, 0);
+                    const uint32_t hw[4] = {qh.x, qh.y, qh.z, qh.w};
+#pragma unroll
+                    for (int jj = 0; jj < 2; ++jj) {  // K step 2 hh + jj: quarters 2 jj and 2 jj + 1
+                        uint4 chunks[4];
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const int qr = 2 * jj + e;
+                            const uint4 ql = e ? qlb : qla;
+                            const uint32_t scw = qr < 2 ? scs.x : scs.y;
+                            const float ds = __fmul_rn(d, (float)(int8_t)((scw >> (8 * ((qr & 1) * 2 + (int)piece))) & 0xffu));
+                            const float bias = -32.0f * ds;  // exact: a power of two times ds
+                            const uint32_t lw[4] = {ql.x, ql.y, ql.z, ql.w};
+                            uint32_t packed[8];
+#pragma unroll
+                            for (int m = 0; m < 4; ++m) {
+                                const uint32_t nib = (jj ? (lw[m] >> 4) : lw[m]) & 0x0f0f0f0fu;  // quarters 2, 3: high nibbles
+                                const uint32_t top = ((hw[m] >> (2 * qr)) & 0x03030303u) << 4;
+                                codes4_fma(nib | top, ds, bias, packed[m * 2], packed[m * 2 + 1]);
+                            }
+                            chunks[e * 2] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                            chunks[e * 2 + 1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                        }
+                        ok = put(chunks, piece * 2, 4 + piece * 2);
+                        if (!ok) break;
+                    }
+                    if (!ok) break;
+                }
+            }
+        } else if (MODE == 3) {
+            // Planar Q8_0 (prepare.cu): 32 columns are one block; value = d * code, exact before the bf16 rounding.
+            const uint8_t *q = p.w + (size_t)grow * p.columns + piece * 32;
+            const uint8_t *dp = p.w + (size_t)p.rows * p.columns + ((size_t)piece * p.rows + grow) * 2;
+            const size_t dstep = (size_t)p.rows * 4;  // two blocks per K step
+            uint4 qa_n = ldg16(q), qb_n = ldg16(q + 16);
+            float d_n = __half2float(*(const __half *)dp);
+            for (uint32_t k = 0; k < ksteps && ok; ++k) {
+                const uint4 qa = qa_n, qb = qb_n;
+                const float d = d_n, bias = -128.0f * d_n;
+                if (k + 1 < ksteps) {
+                    q += BK; dp += dstep;
+                    qa_n = ldg16(q); qb_n = ldg16(q + 16);
+                    d_n = __half2float(*(const __half *)dp);
+                }
+                const uint32_t words[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+                uint4 chunks[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    codes4_fma(words[c * 2] ^ 0x80808080u, d, bias, chunks[c].x, chunks[c].y);  // (code + 128) * d - 128 d
+                    codes4_fma(words[c * 2 + 1] ^ 0x80808080u, d, bias, chunks[c].z, chunks[c].w);
+                }
+                ok = put(chunks, piece * 4, piece * 4 + 2);
+            }
+        } else {
+            for (uint32_t k = 0; k < ksteps && ok; ++k) {
+                uint4 chunks[4];
+                decode16_generic(p, grow, k * BK, piece * 2, &chunks[0]);
+                decode16_generic(p, grow, k * BK, piece * 2 + 1, &chunks[2]);
+                ok = put(chunks, piece * 4, piece * 4 + 2);
+            }
         }
-        // ---- epilogue: tensor memory -> output; warps 0..7: warp w reads lanes 32 (w & 3) .. + 31 (its rows), half of the columns ----
-        const uint32_t half = q & 1u;
-        if (ok && q < 2) ok = mbar_wait(accum, 0, abort_flag);
+        // ---- epilogue: tensor memory -> output; warp w reads lanes 32 (w & 3) .. + 31 (its rows), half of the columns ----
+        if (ok) ok = mbar_wait(accum, 0, abort_flag);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok && q < 2) {
-            const uint32_t out_row = row0 + r;
+        if (ok) {
+            const uint32_t half = warp >> 2;
+            const uint32_t out_row = row0 + (warp & 3u) * 32 + lane;
 #pragma unroll 1
             for (int c0 = (int)half * (BN / 2); c0 < (int)(half + 1) * (BN / 2); c0 += 32) {
                 uint32_t v[32];
@@ -390,20 +421,29 @@ template <int BN, int STAGES> constexpr int smem_bytes() { return STAGES * (BM *
 bool encode_tiled_map(CUtensorMap *map, CUtensorMapDataType type, uint32_t elem_bytes, const void *base, uint64_t inner, uint64_t outer,
                       uint64_t stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle);
 
+template <int BN, int STAGES, int MODE>
+static bool configure_one() {
+    return cudaFuncSetAttribute(prefill::prefill_kernel<BN, STAGES, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, prefill::smem_bytes<BN, STAGES>()) == cudaSuccess;
+}
 template <int BN, int STAGES>
 static bool configure_bn() {
-    return cudaFuncSetAttribute(prefill::prefill_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, prefill::smem_bytes<BN, STAGES>()) == cudaSuccess;
+    return configure_one<BN, STAGES, 0>() && configure_one<BN, STAGES, 1>() && configure_one<BN, STAGES, 2>() && configure_one<BN, STAGES, 3>();
 }
 
-#ifndef NU_PREFILL_STAGES256
-#define NU_PREFILL_STAGES256 4
-#endif
-#ifndef NU_PREFILL_MAXBN
-#define NU_PREFILL_MAXBN 256
-#endif
-bool prefill_configure() { return configure_bn<256, NU_PREFILL_STAGES256>() && configure_bn<128, 6>() && configure_bn<64, 8>(); }
+bool prefill_configure() { return configure_bn<256, 4>() && configure_bn<128, 6>() && configure_bn<64, 8>(); }
 
-static uint32_t pick_bn(uint32_t tokens) { return tokens > 128 && NU_PREFILL_MAXBN >= 256 ? 256 : tokens > 64 ? 128 : 64; }
+static uint32_t pick_bn(uint32_t tokens) { return tokens > 128 ? 256 : tokens > 64 ? 128 : 64; }
+
+template <int BN, int STAGES>
+static void launch_bn(dim3 grid, cudaStream_t s, const prefill::Params &p, int mode) {
+    const int bytes = prefill::smem_bytes<BN, STAGES>();
+    switch (mode) {
+    case 1: prefill::prefill_kernel<BN, STAGES, 1><<<grid, prefill::THREADS, bytes, s>>>(p); break;
+    case 2: prefill::prefill_kernel<BN, STAGES, 2><<<grid, prefill::THREADS, bytes, s>>>(p); break;
+    case 3: prefill::prefill_kernel<BN, STAGES, 3><<<grid, prefill::THREADS, bytes, s>>>(p); break;
+    default: prefill::prefill_kernel<BN, STAGES, 0><<<grid, prefill::THREADS, bytes, s>>>(p); break;
+    }
+}
 
 bool prefill_supported(const PrefillJob &j) {
     if (layout(j.enc).elements == 0 || j.rows == 0 || j.tokens == 0) return false;
@@ -427,9 +467,10 @@ int launch_prefill(cudaStream_t s, const PrefillJob &j) {
     p.rows = j.rows; p.columns = j.columns; p.tokens = j.tokens;
     p.out = j.out; p.out_stride = j.out_stride; p.status = j.status;
     dim3 grid((j.tokens + bn - 1) / bn, (j.rows + prefill::BM - 1) / prefill::BM);
-    if (bn == 256) prefill::prefill_kernel<256, NU_PREFILL_STAGES256><<<grid, prefill::THREADS, prefill::smem_bytes<256, NU_PREFILL_STAGES256>(), s>>>(p);
-    else if (bn == 128) prefill::prefill_kernel<128, 6><<<grid, prefill::THREADS, prefill::smem_bytes<128, 6>(), s>>>(p);
-    else prefill::prefill_kernel<64, 8><<<grid, prefill::THREADS, prefill::smem_bytes<64, 8>(), s>>>(p);
+    const int mode = !p.fast ? 0 : j.enc == Q4_K ? 1 : j.layout == 1 ? 2 : 3;
+    if (bn == 256) launch_bn<256, 4>(grid, s, p, mode);
+    else if (bn == 128) launch_bn<128, 6>(grid, s, p, mode);
+    else launch_bn<64, 8>(grid, s, p, mode);
     return 1;
 }
 
