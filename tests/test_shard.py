@@ -92,3 +92,52 @@ def test_two_gloo_ranks_reproduce_the_unsharded_chain(tmp_path):
     outs = [p.communicate(timeout=180)[0] for p in procs]
     assert all(p.returncode == 0 for p in procs), outs
     assert "TP-OK" in outs[0]
+
+
+JOIN_SCRIPT = r'''
+import os, sys
+import torch.distributed as dist
+sys.path.insert(0, os.environ["NU_ROOT"])
+from nuclis_b200.group import join, torch_all_gather
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo", rank=rank, world_size=world)
+
+class FakeBackend:
+    """Records what join() asks of a backend; stands in for the CUDA library on a CPU box."""
+    calls = []
+    @staticmethod
+    def comm_unique_id():
+        return bytes([7]) * 128
+    def comm_init(self, uid, ranks, rank):
+        self.calls.append(("init", uid, ranks, rank))
+    def comm_peer_handle(self):
+        return bytes([rank + 1]) * 64
+    def comm_attach_peers(self, handles, rank):
+        self.calls.append(("attach", tuple(handles), rank))
+
+b = FakeBackend()
+join(b, rank, world, torch_all_gather())
+assert b.calls[0] == ("init", bytes([7]) * 128, world, rank), b.calls[0]
+assert b.calls[1] == ("attach", tuple(bytes([r + 1]) * 64 for r in range(world)), rank), b.calls[1]
+b2 = FakeBackend(); b2.calls = []
+join(b2, rank, world, torch_all_gather(), peer_memory=False)
+assert [c[0] for c in b2.calls] == ["init"]
+try:
+    join(b2, world, world, torch_all_gather())
+    raise SystemExit("rank outside the group was accepted")
+except ValueError:
+    pass
+print("JOIN-OK")
+dist.destroy_process_group()
+'''
+
+
+def test_group_join_exchanges_id_and_inbox_handles_in_rank_order(tmp_path):
+    script = tmp_path / "join.py"
+    script.write_text(JOIN_SCRIPT)
+    env = dict(os.environ, NU_ROOT=ROOT, MASTER_ADDR="127.0.0.1", MASTER_PORT="29643", WORLD_SIZE="2")
+    procs = [subprocess.Popen([sys.executable, str(script)], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+             for r in range(2)]
+    outs = [p.communicate(timeout=180)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
+    assert all("JOIN-OK" in o for o in outs)
