@@ -248,7 +248,7 @@ def run_gpu(args, rank: int, world: int, local: int):
             oracle.build()
             lps, cores, dt = cpu_layers_per_second(tokens, args.cpu_layers)
             cpu = {"value": tokens * lps / LAYERS, "unit": "tok/s", "cores": cores, "kind": "port",
-                   "sample": f"{args.cpu_layers} of {LAYERS} layers of the same stack on the CPU oracle ({dt:.1f} s), extrapolated to {LAYERS}"}
+                   "sample": f"{args.cpu_layers} layer passes of the same stack on the CPU oracle ({dt:.1f} s), scaled to the {LAYERS} layers of a token"}
 
     if rank == 0:
         line = {
@@ -276,7 +276,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=1)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--cpu-layers", type=int, default=4)
+    ap.add_argument("--cpu-layers", type=int, default=192, help="layer passes timed on the CPU oracle for cpu_baseline (about 10 s)")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--nccl-only", action="store_true", help="sum the short vectors with NCCL instead of the peer-memory allreduce")
     args = ap.parse_args()

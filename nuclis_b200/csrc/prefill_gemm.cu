@@ -213,19 +213,24 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_kernel(const __grid_consta
             // rounding, like the reference decoder (inference/src/quant/decode.zig:147-170), then rounded to bf16.
             const uint8_t *blk = p.w + (size_t)grow * p.stride;
             const uint32_t nsb = p.columns / 256;
-            uint4 hdr_n = ldg16(blk), q_n = ldg16(blk + 16 + piece * 16);
+            // the five 16-byte loads of a superblock are requested a whole superblock (four K steps) ahead
+            uint4 hdr_n = ldg16(blk), q_n[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) q_n[j] = ldg16(blk + 16 + j * 32 + piece * 16);
             for (uint32_t sb = 0; sb < nsb && ok; ++sb, blk += 144) {
                 const uint4 hdr = hdr_n;
+                uint4 q_c[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) q_c[j] = q_n[j];
+                if (sb + 1 < nsb) {
+                    hdr_n = ldg16(blk + 144);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) q_n[j] = ldg16(blk + 160 + j * 32 + piece * 16);
+                }
                 const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu))), dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const uint4 qq = q_n;
-                    if (j < 3) {
-                        q_n = ldg16(blk + 16 + (j + 1) * 32 + piece * 16);
-                    } else if (sb + 1 < nsb) {
-                        hdr_n = ldg16(blk + 144);
-                        q_n = ldg16(blk + 160 + piece * 16);
-                    }
+                    const uint4 qq = q_c[j];
                     // six-bit scales and minima of groups 2j and 2j+1 out of the 12 packed bytes (words hdr.y, hdr.z, hdr.w)
                     float ds[2], ndm[2];
 #pragma unroll
@@ -259,26 +264,40 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_kernel(const __grid_consta
             const uint8_t *rec = p.w + (size_t)grow * nsb * 208;
             const uint8_t *dp = p.w + (size_t)p.rows * nsb * 208 + (size_t)grow * 2;
             const size_t dstep = (size_t)p.rows * 2;
-            uint4 raw_n[3];
-            uint2 sc_n;  // the 8 scales of a half: bytes qr * 2 + ch
-            auto fetch = [&](const uint8_t *record, int hh) {
-                const uint8_t *chunk = record + (hh * 2 + piece) * 48;
-                raw_n[0] = ldg16(chunk);
-                raw_n[1] = ldg16(chunk + 16);
-                raw_n[2] = ldg16(chunk + 32);
-                sc_n = *(const uint2 *)(record + 192 + hh * 8);
+            // the loads of a superblock (two chunks of 48 bytes, 16 scale bytes, the super-scale) are requested a
+            // whole superblock (four K steps) ahead
+            uint4 raw_n[2][3];
+            uint2 sc_n[2];  // the 8 scales of each half: bytes qr * 2 + ch
+            auto fetch = [&](const uint8_t *record) {
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const uint8_t *chunk = record + (hh * 2 + piece) * 48;
+                    raw_n[hh][0] = ldg16(chunk);
+                    raw_n[hh][1] = ldg16(chunk + 16);
+                    raw_n[hh][2] = ldg16(chunk + 32);
+                    sc_n[hh] = *(const uint2 *)(record + 192 + hh * 8);
+                }
             };
-            fetch(rec, 0);
+            fetch(rec);
             float d_n = __half2float(*(const __half *)dp);
             for (uint32_t sb = 0; sb < nsb && ok; ++sb, rec += 208) {
                 const float d = d_n;
-                if (sb + 1 < nsb) { dp += dstep; d_n = __half2float(*(const __half *)dp); }
+                uint4 raw_c[2][3];
+                uint2 sc_c[2];
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
-                    const uint4 qla = raw_n[0], qlb = raw_n[1], qh = raw_n[2];
-                    const uint2 scs = sc_n;
-                    if (hh == 0) fetch(rec, 1);
-                    else if (sb + 1 < nsb) fetch(rec + 208, 0);
+                    raw_c[hh][0] = raw_n[hh][0]; raw_c[hh][1] = raw_n[hh][1]; raw_c[hh][2] = raw_n[hh][2];
+                    sc_c[hh] = sc_n[hh];
+                }
+                if (sb + 1 < nsb) {
+                    dp += dstep;
+                    d_n = __half2float(*(const __half *)dp);
+                    fetch(rec + 208);
+                }
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const uint4 qla = raw_c[hh][0], qlb = raw_c[hh][1], qh = raw_c[hh][2];
+                    const uint2 scs = sc_c[hh];
                     const uint32_t hw[4] = {qh.x, qh.y, qh.z, qh.w};
 #pragma unroll
                     for (int jj = 0; jj < 2; ++jj) {  // K step 2 hh + jj: quarters 2 jj and 2 jj + 1
