@@ -221,6 +221,14 @@ int nu_cuda_gelu_mul(nu_cuda *h, const nu_buffer *gate, const nu_buffer *up, siz
 int nu_cuda_route(nu_cuda *h, const nu_buffer *logits, size_t experts, size_t k, size_t rows, size_t in_stride,
                   const nu_buffer *indices, const nu_buffer *weights);
 
+/* Expert parallelism (no counterpart in the reference, which is single-device): a rank that holds
+ * experts [first_expert, first_expert + local_experts) turns the routed slots into its own view:
+ * slots it owns keep their weight and get the expert's local index, the others get index 0 and
+ * weight 0. The grouped operators then run unchanged on the rank's slice of the expert tensors and
+ * the partial outputs of all ranks add up (nu_cuda_allreduce_sum_f32) to the full result. */
+int nu_cuda_route_local(nu_cuda *h, const nu_buffer *indices, const nu_buffer *weights, size_t count, size_t first_expert, size_t local_experts,
+                        const nu_buffer *local_indices, const nu_buffer *local_weights);
+
 /* `Backend.matvecExperts` / `matvecExpertsGrouped` (ops/experts.zig:44-77). */
 int nu_cuda_matvec_experts(nu_cuda *h, const nu_buffer *weights, const nu_expert_matrix *tensor,
                            const nu_buffer *indices, size_t slots,

@@ -282,6 +282,12 @@ class Backend:
     def route(self, logits: Buffer, experts: int, k: int, rows: int, in_stride: int, indices: Buffer, weights: Buffer) -> None:
         self._check(self._lib.nu_cuda_route(self._h, logits._c(), experts, k, rows, in_stride, indices._c(), weights._c()))
 
+    def route_local(self, indices: Buffer, weights: Buffer, count: int, first_expert: int, local_experts: int, local_indices: Buffer,
+                    local_weights: Buffer) -> None:
+        """Expert parallelism: the routed slots this rank owns (local index, same weight), the others silenced (index 0, weight 0)."""
+        self._check(self._lib.nu_cuda_route_local(self._h, indices._c(), weights._c(), count, first_expert, local_experts, local_indices._c(),
+                                                  local_weights._c()))
+
     def matvec_experts(self, weights: Buffer, tensor: ExpertMatrix, indices: Buffer, slots: int, input: Buffer, in_stride: int,
                        output: Buffer, out_stride: int) -> None:
         self.matvec_experts_grouped(weights, tensor, indices, slots, input, in_stride, 1, output, out_stride)

@@ -609,6 +609,23 @@ int Backend::route(const Buffer &logits, size_t experts, size_t k, size_t rows, 
     return cuda(cudaGetLastError(), "route: launch");
 }
 
+// Expert parallelism (no reference analogue): the routed slots this rank owns, the others silenced.
+int Backend::routeLocal(const Buffer &indices, const Buffer &weights, size_t count, size_t first, size_t local, const Buffer &local_indices,
+                        const Buffer &local_weights) {
+    if (count == 0 || local == 0 || !fits_u32(count) || !fits_u32(first) || !fits_u32(local)) return fail(NU_ERR_INVALID_SHAPE, "route_local: shape");
+    const uint32_t *idx = (const uint32_t *)resolve(indices, count * 4);
+    const float *w = (const float *)resolve(weights, count * 4);
+    uint32_t *lidx = (uint32_t *)resolve(local_indices, count * 4);
+    float *lw = (float *)resolve(local_weights, count * 4);
+    if (!idx || !w || !lidx || !lw || indices.offset % 4 != 0 || weights.offset % 4 != 0 || local_indices.offset % 4 != 0 || local_weights.offset % 4 != 0)
+        return fail(NU_ERR_INVALID_SHAPE, "route_local: buffer too short");
+    if (int rc = needRecording()) return rc;
+    launches_ += launch_route_local(stream_, idx, w, (uint32_t)count, (uint32_t)first, (uint32_t)local, lidx, lw);
+    wrote(local_indices); wrote(local_weights);
+    opBoundary();
+    return cuda(cudaGetLastError(), "route_local: launch");
+}
+
 // ops/experts.zig:50-77 (expertBytes: backends/cpu/experts.zig:29-37).
 int Backend::matvecExpertsGrouped(const Buffer &weights, const ExpertMatrix &t, const Buffer &indices, size_t slots,
                                   const Buffer &input, size_t in_stride, size_t in_group, const Buffer &output, size_t out_stride) {
@@ -937,6 +954,12 @@ int nu_cuda_silu_mul(nu_cuda *h, const nu_buffer *gate, const nu_buffer *up, siz
 int nu_cuda_gelu_mul(nu_cuda *h, const nu_buffer *gate, const nu_buffer *up, size_t count) {
     NU_H(h); NU_P(gate && up);
     return h->b->actMul(nu::ACT_GELU, *gate, *up, count);
+}
+int nu_cuda_route_local(nu_cuda *h, const nu_buffer *indices, const nu_buffer *weights, size_t count, size_t first_expert, size_t local_experts,
+                        const nu_buffer *local_indices, const nu_buffer *local_weights) {
+    NU_H(h);
+    if (!indices || !weights || !local_indices || !local_weights) return NU_ERR_INVALID_SHAPE;
+    return h->b->routeLocal(*indices, *weights, count, first_expert, local_experts, *local_indices, *local_weights);
 }
 int nu_cuda_route(nu_cuda *h, const nu_buffer *logits, size_t experts, size_t k, size_t rows, size_t in_stride,
                   const nu_buffer *indices, const nu_buffer *weights) {

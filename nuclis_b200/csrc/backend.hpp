@@ -69,6 +69,7 @@ public:
     int matvecSegments(const Segment *segments, size_t count, const Buffer &input, uint32_t mode);
     int actMul(uint32_t act, const Buffer &gate, const Buffer &up, size_t count);
     int route(const Buffer &logits, size_t experts, size_t k, size_t rows, size_t in_stride, const Buffer &indices, const Buffer &weights);
+    int routeLocal(const Buffer &indices, const Buffer &weights, size_t count, size_t first, size_t local, const Buffer &local_indices, const Buffer &local_weights);
     int matvecExpertsGrouped(const Buffer &weights, const ExpertMatrix &tensor, const Buffer &indices, size_t slots,
                              const Buffer &input, size_t in_stride, size_t in_group, const Buffer &output, size_t out_stride);
     int geluMulRows(const Buffer &gate, const Buffer &up, const Buffer &output, size_t width, size_t rows,

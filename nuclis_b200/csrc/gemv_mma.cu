@@ -798,7 +798,7 @@ static bool fill_params(const FastJob &job, fast::Params &p) {
 }
 
 bool fast_supported(const FastJob &job) {
-    if (q4k_decode_supported(job) || q6k_decode_supported(job) || q8_0_decode_supported(job) || q4k_rows_supported(job) || q6k_rows_supported(job)) return true;
+    if (q4k_decode_supported(job) || q6k_decode_supported(job) || q8_0_decode_supported(job) || q4k_rows_supported(job) || q6k_rows_supported(job) || q8_0_rows_supported(job)) return true;
     fast::Params p;
     return fill_params(job, p);
 }
@@ -810,7 +810,7 @@ static bool configure_variant() {
 }
 
 bool fast_configure() {
-    return q4k_decode_configure() && q4k_rows_configure() && q6k_rows_configure() && q6k_decode_configure() && q8_0_decode_configure() && prefill_configure() && configure_variant<Q4_K, 1>() && configure_variant<Q4_K, 2>() && configure_variant<Q4_K, 4>() && configure_variant<Q4_K, 8>();
+    return q4k_decode_configure() && q4k_rows_configure() && q6k_rows_configure() && q8_0_rows_configure() && q6k_decode_configure() && q8_0_decode_configure() && prefill_configure() && configure_variant<Q4_K, 1>() && configure_variant<Q4_K, 2>() && configure_variant<Q4_K, 4>() && configure_variant<Q4_K, 8>();
 }
 
 template <int ENC, int TS>
@@ -829,6 +829,7 @@ int launch_fast(cudaStream_t s, const FastJob &job) {
     if (q8_0_decode_supported(job)) return launch_q8_0_decode(s, job);
     if (q4k_rows_supported(job)) return launch_q4k_rows(s, job);
     if (q6k_rows_supported(job)) return launch_q6k_rows(s, job);
+    if (q8_0_rows_supported(job)) return launch_q8_0_rows(s, job);
     fast::Params p;
     if (!fill_params(job, p)) return 0;
     // The status word lives at the end of the counters array.

@@ -55,9 +55,11 @@ __device__ __forceinline__ RowScales row_scales(const uint4 &hdr, uint32_t t) {
 struct Q4K {
     static constexpr int ROW_BYTES = 144;
     static constexpr int TASK_BYTES = 16 * ROW_BYTES;
+    static constexpr bool SWIZZLED = false;  // whether the task's TMA boxes use a shared-memory swizzle
+    static constexpr int AUX_BYTES = 0;
     static constexpr int GS_BYTES = 16;  // staged group sums per (B column, superblock): eight fp16
 
-    __device__ static __forceinline__ void issue(const Params &p, uint32_t seg, uint32_t sb, uint32_t row0, uint32_t dst, uint32_t bar, uint64_t policy) {
+    __device__ static __forceinline__ void issue(const Params &p, uint32_t seg, uint32_t sb, uint32_t row0, uint32_t dst, uint32_t, uint32_t bar, uint64_t policy) {
         mbar_expect_tx(bar, TASK_BYTES);
         tma_load_2d(dst, &p.map[seg], sb * ROW_BYTES, row0, bar, policy);
     }
@@ -78,7 +80,7 @@ struct Q4K {
     }
 
 template <bool WIDE>
-__device__ static __forceinline__ void task(const uint8_t *task, const uint8_t *xb, uint32_t lo_off, const uint8_t *gsb, uint32_t gs_lo_off, uint32_t g,
+__device__ static __forceinline__ void task(const uint8_t *task, const uint8_t *, const uint8_t *xb, uint32_t lo_off, const uint8_t *gsb, uint32_t gs_lo_off, uint32_t g,
                                      uint32_t t, float o[4]) {
     uint4 hdr[2], q0[2], q1[2];
 #pragma unroll

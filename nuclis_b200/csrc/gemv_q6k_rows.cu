@@ -20,9 +20,11 @@ struct Q6K {
     static constexpr int ROW_BYTES = 208;               // one planar record
     static constexpr int MAIN_BYTES = 16 * ROW_BYTES;   // 3328
     static constexpr int TASK_BYTES = MAIN_BYTES + 128; // + the 16 super-scales (32 bytes), padded to a multiple of 128
+    static constexpr bool SWIZZLED = false;  // whether the task's TMA boxes use a shared-memory swizzle
+    static constexpr int AUX_BYTES = 0;
     static constexpr int GS_BYTES = 32;                 // staged group sums per (B column, superblock): sixteen fp16
 
-    __device__ static __forceinline__ void issue(const Params &p, uint32_t seg, uint32_t sb, uint32_t row0, uint32_t dst, uint32_t bar, uint64_t policy) {
+    __device__ static __forceinline__ void issue(const Params &p, uint32_t seg, uint32_t sb, uint32_t row0, uint32_t dst, uint32_t, uint32_t bar, uint64_t policy) {
         mbar_expect_tx(bar, MAIN_BYTES + 32);
         tma_load_2d(dst, &p.map[seg], sb * ROW_BYTES, row0, bar, policy);
         tma_load_2d(dst + MAIN_BYTES, &p.map2[seg], row0 * 2, sb, bar, policy);
@@ -51,7 +53,7 @@ struct Q6K {
 
     // One task: rows g and g+8 of the tile against every token column; see rows_kernel.cuh for the arguments.
     template <bool WIDE>
-    __device__ static __forceinline__ void task(const uint8_t *task, const uint8_t *xb, uint32_t lo_off, const uint8_t *gsb, uint32_t gs_lo_off, uint32_t g,
+    __device__ static __forceinline__ void task(const uint8_t *task, const uint8_t *, const uint8_t *xb, uint32_t lo_off, const uint8_t *gsb, uint32_t gs_lo_off, uint32_t g,
                                                 uint32_t t, float o[4]) {
         const uint8_t *row[2] = {task + g * ROW_BYTES, task + (g + 8) * ROW_BYTES};
         uint4 sc[2];

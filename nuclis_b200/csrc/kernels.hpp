@@ -33,6 +33,8 @@ int launch_act_mul_rows(cudaStream_t s, uint32_t act, const float *gate, const f
                         uint32_t width, uint32_t rows, size_t gate_stride, size_t up_stride, size_t out_stride);
 int launch_route(cudaStream_t s, const float *logits, uint32_t experts, uint32_t k, uint32_t rows, size_t in_stride,
                  uint32_t *indices, float *weights);
+int launch_route_local(cudaStream_t s, const uint32_t *indices, const float *weights, uint32_t n, uint32_t first, uint32_t count, uint32_t *local_indices,
+                       float *local_weights);
 int launch_combine_experts(cudaStream_t s, const float *values, const float *weights, const uint32_t *indices, const float *scales,
                            float *out, uint32_t columns, uint32_t slots, uint32_t rows, size_t in_stride, size_t out_stride, uint32_t experts);
 
@@ -83,6 +85,10 @@ int launch_q4k_rows(cudaStream_t s, const FastJob &job);
 bool q6k_rows_configure();
 bool q6k_rows_supported(const FastJob &job);
 int launch_q6k_rows(cudaStream_t s, const FastJob &job);
+// 2..8 token rows on planar Q8_0 (gemv_q8_0_rows.cu)
+bool q8_0_rows_configure();
+bool q8_0_rows_supported(const FastJob &job);
+int launch_q8_0_rows(cudaStream_t s, const FastJob &job);
 bool q6k_decode_configure();
 bool q6k_decode_supported(const FastJob &job);
 int launch_q6k_decode(cudaStream_t s, const FastJob &job);

@@ -238,6 +238,25 @@ __global__ void combine_experts_kernel(const float *values, const float *weights
     out[(size_t)row * out_stride + c] = acc;
 }
 
+// Expert parallelism: a rank that holds experts [first, first + count) keeps the routed slots it
+// owns (index made local) and silences the others (index 0, weight 0), so that the grouped
+// operators run unchanged and the partial outputs of the ranks add up to the full result.
+__global__ void route_local_kernel(const uint32_t *indices, const float *weights, uint32_t n, uint32_t first, uint32_t count, uint32_t *local_indices,
+                                   float *local_weights) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint32_t e = indices[i];
+    const bool mine = e >= first && e - first < count;
+    local_indices[i] = mine ? e - first : 0u;
+    local_weights[i] = mine ? weights[i] : 0.0f;
+}
+
+int launch_route_local(cudaStream_t s, const uint32_t *indices, const float *weights, uint32_t n, uint32_t first, uint32_t count, uint32_t *local_indices,
+                       float *local_weights) {
+    route_local_kernel<<<(n + 127) / 128, 128, 0, s>>>(indices, weights, n, first, count, local_indices, local_weights);
+    return 1;
+}
+
 int launch_combine_experts(cudaStream_t s, const float *values, const float *weights, const uint32_t *indices, const float *scales,
                            float *out, uint32_t columns, uint32_t slots, uint32_t rows, size_t in_stride, size_t out_stride, uint32_t experts) {
     const size_t n = (size_t)columns * rows;

@@ -100,16 +100,20 @@ __host__ __device__ constexpr int columns() { return WIDE ? 16 : 8; }
 // [per-token 1/scale: 8 floats][per-token max bits: 8 words][part sums: SLOTS x 2 x 3 x 512 B][barriers]
 template <class E, bool WIDE>
 static size_t smem_bytes(uint32_t arr_stride, uint32_t gs_stride, int stages) {
-    return (size_t)WARPS * stages * E::TASK_BYTES + (size_t)columns<WIDE>() * (arr_stride + gs_stride) + 64 + SLOTS * 2 * 3 * 512 + WARPS * stages * 8 + 128;
+    // a swizzled TMA box needs the ring on a 1024-byte boundary: room to round the base up
+    return (E::SWIZZLED ? 1024 : 0) + (size_t)WARPS * stages * (E::TASK_BYTES + E::AUX_BYTES) + (size_t)columns<WIDE>() * (arr_stride + gs_stride) + 64 + SLOTS * 2 * 3 * 512 + WARPS * stages * 8 + 128;
 }
 
 template <class E, bool WIDE, int STAGES>
 __global__ void __launch_bounds__(THREADS, 1) rows_kernel(const __grid_constant__ Params p) {
     constexpr int NCOL = columns<WIDE>();
     constexpr int TASK_BYTES = E::TASK_BYTES;
-    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int AUX_BYTES = E::AUX_BYTES;  // a second, small part of a task kept apart so that TASK_BYTES can stay a multiple of 1024
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    uint8_t *smem = E::SWIZZLED ? (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023) : smem_raw;
     uint8_t *stages = smem;
-    uint8_t *xarr = stages + WARPS * STAGES * TASK_BYTES;
+    uint8_t *aux = stages + WARPS * STAGES * TASK_BYTES;
+    uint8_t *xarr = aux + WARPS * STAGES * AUX_BYTES;
     uint8_t *gsarr = xarr + NCOL * p.arr_stride;
     float *inv = (float *)(gsarr + NCOL * p.gs_stride);
     uint32_t *maxbits = (uint32_t *)(inv + 8);
@@ -119,6 +123,8 @@ __global__ void __launch_bounds__(THREADS, 1) rows_kernel(const __grid_constant_
     const uint32_t g = lane >> 2, t = lane & 3;
     const uint32_t slot = warp >> 2, part = warp & 3;
     const uint8_t *my_stage = stages + warp * STAGES * TASK_BYTES;
+    const uint8_t *my_aux = aux + warp * STAGES * AUX_BYTES;
+    const uint32_t aux0 = smem_u32(my_aux);
     const uint32_t stage0 = smem_u32(my_stage), bar0 = smem_u32(bars + warp * STAGES);
 
     // See decode_kernel.cuh: dependents may start now; this kernel reads its activations and writes
@@ -158,7 +164,7 @@ __global__ void __launch_bounds__(THREADS, 1) rows_kernel(const __grid_constant_
     if (total) tile_rows(p, p_tile, p_seg, p_row0);
     auto issue = [&]() {
         if (lane == 0) {
-            E::issue(p, p_seg, sb0 + part + PARTS * p_j, p_row0, stage0 + p_stage * TASK_BYTES, bar0 + p_stage * 8, policy);
+            E::issue(p, p_seg, sb0 + part + PARTS * p_j, p_row0, stage0 + p_stage * TASK_BYTES, aux0 + p_stage * AUX_BYTES, bar0 + p_stage * 8, policy);
         }
         ++issued;
         p_stage = p_stage + 1 == STAGES ? 0 : p_stage + 1;
@@ -258,7 +264,7 @@ __global__ void __launch_bounds__(THREADS, 1) rows_kernel(const __grid_constant_
             if (issued < total) issue();  // keep STAGES - 1 tasks in flight
             if (!mbar_wait(bar0 + c_stage * 8, c_phase)) { failed = true; break; }
             const uint32_t sbw = part + PARTS * j;  // superblock within the window
-            E::template task<WIDE>(my_stage + c_stage * TASK_BYTES, xlane + sbw * 4 * PITCH, lo_off, gslane + sbw * E::GS_BYTES, gs_lo_off, g, t, o);
+            E::template task<WIDE>(my_stage + c_stage * TASK_BYTES, my_aux + c_stage * AUX_BYTES, xlane + sbw * 4 * PITCH, lo_off, gslane + sbw * E::GS_BYTES, gs_lo_off, g, t, o);
             __syncwarp();  // all lanes are done reading this stage before it is refilled
             ++consumed;
             if (++c_stage == STAGES) { c_stage = 0; c_phase ^= 1u; }

@@ -26,6 +26,13 @@ def split_ranges(total: int, parts: int) -> list[tuple[int, int]]:
     return [(i * total // parts, (i + 1) * total // parts) for i in range(parts)]
 
 
+def expert_range(experts: int, ranks: int, rank: int) -> tuple[int, int]:
+    """Experts [first, end) a rank holds under expert parallelism: contiguous, as even as the count allows."""
+    if not 0 <= rank < ranks or experts < ranks:
+        raise ValueError(f"{experts} experts over {ranks} ranks, rank {rank}")
+    return split_ranges(experts, ranks)[rank]
+
+
 @dataclass(frozen=True)
 class LayerShapes:
     """Full (unsharded) shapes of the synthetic dense decoder layer."""

@@ -10,7 +10,7 @@ import numpy as np
 import pytest
 
 import oracle
-from nuclis_b200 import Backend, CombineShape, ExpertMatrix, NuclisError, encoding as enc, synth
+from nuclis_b200 import Backend, CombineShape, ExpertMatrix, NuclisError, encoding as enc, shard, synth
 
 pytestmark = pytest.mark.gpu
 
@@ -98,6 +98,59 @@ def test_expert_chain_matches_cpu_ffn(backend, tensors, tokens):
         assert np.max(np.abs(got[t] - want)) <= bound, (t, np.max(np.abs(got[t] - want)), bound)
     backend.unwrap(gate_up); backend.unwrap(down)
     for buf in (xb, lb, sb, ib, wb, gu_out, hid, y, out):
+        backend.release(buf)
+
+
+@pytest.mark.parametrize("tokens", [1, 8])
+def test_expert_parallel_partials_add_up_to_the_full_result(backend, tensors, tokens):
+    """Eight ranks of 16 experts each, run one after the other on this GPU: every rank sees only its slice of
+    the expert tensors and its own view of the routing (route_local); the partial outputs add up to the
+    CPU oracle's full result (what the allreduce over the ranks would hold)."""
+    gate_up, down = tensors
+    ranks = 8
+    rng = np.random.default_rng(31 + tokens)
+    x = rng.standard_normal((tokens, HIDDEN)).astype(np.float32)
+    logits = rng.standard_normal((tokens, EXPERTS)).astype(np.float32)
+    scales = (0.5 + rng.random(EXPERTS)).astype(np.float32)
+    slots = tokens * K
+    gu_bytes, dn_bytes = gate_up.size // EXPERTS, down.size // EXPERTS
+    xb = backend.create(x.nbytes); lb = backend.create(logits.nbytes)
+    ib = backend.create(slots * 4); wb = backend.create(slots * 4)
+    lib_ = backend.create(slots * 4); lwb = backend.create(slots * 4)
+    gu_out = backend.create(slots * 2 * FF * 4); hid = backend.create(slots * FF * 4)
+    y = backend.create(slots * HIDDEN * 4); out = backend.create(tokens * HIDDEN * 4)
+    xb.write(x); lb.write(logits)
+    total = np.zeros((tokens, HIDDEN), dtype=np.float64)
+    owners = 0
+    for r in range(ranks):
+        e0, e1 = shard.expert_range(EXPERTS, ranks, r)
+        n = e1 - e0
+        gub = backend.create(n * gu_bytes); gub.write(gate_up[e0 * gu_bytes:e1 * gu_bytes])
+        dnb = backend.create(n * dn_bytes); dnb.write(down[e0 * dn_bytes:e1 * dn_bytes])
+        sb = backend.create(n * 4); sb.write(scales[e0:e1])
+        gu_t = ExpertMatrix(enc.Q4_K, n, 2 * FF, HIDDEN, n * gu_bytes)
+        dn_t = ExpertMatrix(enc.Q8_0, n, HIDDEN, FF, n * dn_bytes)
+        backend.begin()
+        backend.route(lb, EXPERTS, K, tokens, EXPERTS, ib, wb)
+        backend.route_local(ib, wb, slots, e0, n, lib_, lwb)
+        backend.matvec_experts_grouped(gub, gu_t, lib_, slots, xb, HIDDEN if tokens > 1 else 0, K if tokens > 1 else 1, gu_out, 2 * FF)
+        backend.gelu_mul_rows(gu_out, gu_out.slice(FF * 4, gu_out.len - FF * 4), hid, FF, slots, 2 * FF, 2 * FF, FF)
+        backend.matvec_experts(dnb, dn_t, lib_, slots, hid, FF, y, HIDDEN)
+        backend.combine_experts(y, lwb, lib_, sb, out, CombineShape(columns=HIDDEN, slots=K, experts=n, in_stride=HIDDEN, out_stride=HIDDEN, rows=tokens))
+        backend.commit()
+        total += out.floats().reshape(tokens, HIDDEN).astype(np.float64)
+        owners += int(np.count_nonzero(lwb.floats()[:slots]))
+        idx = ib.read(np.uint32)[:slots]
+        assert np.array_equal(lib_.read(np.uint32)[:slots], np.where((idx >= e0) & (idx < e1), idx - e0, 0))
+        for buf in (gub, dnb, sb):
+            backend.release(buf)
+    assert owners == slots  # every routed slot has exactly one owner (weights are positive)
+    for t in range(tokens):
+        idx, w = oracle.route(logits[t], K)
+        want = oracle.ffn((enc.Q4_K, EXPERTS, 2 * FF, HIDDEN, gate_up), (enc.Q8_0, EXPERTS, HIDDEN, FF, down), x[t], idx, w, down_scale=scales)
+        bound = 2e-5 * (1 + np.max(np.abs(want)))
+        assert np.max(np.abs(total[t] - want)) <= bound, (t, np.max(np.abs(total[t] - want)), bound)
+    for buf in (xb, lb, ib, wb, lib_, lwb, gu_out, hid, y, out):
         backend.release(buf)
 
 

@@ -31,6 +31,19 @@ def test_split_tables_cover_everything_at_superblock_granularity():
         shard.rank_shapes(shard.LayerShapes(kv=1001), 8, 0)
 
 
+def test_expert_ranges_partition_the_experts():
+    for ranks in (1, 2, 4, 8):
+        spans = [shard.expert_range(128, ranks, r) for r in range(ranks)]
+        assert spans[0][0] == 0 and spans[-1][1] == 128
+        assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+        assert all(e1 - e0 == 128 // ranks for e0, e1 in spans)
+    assert [shard.expert_range(10, 4, r) for r in range(4)] == [(0, 2), (2, 5), (5, 7), (7, 10)]
+    with pytest.raises(ValueError):
+        shard.expert_range(4, 8, 0)
+    with pytest.raises(ValueError):
+        shard.expert_range(128, 8, 8)
+
+
 @pytest.mark.parametrize("encoding", [enc.Q4_K, enc.Q6_K, enc.Q8_0])
 def test_column_shards_sum_to_the_full_product(encoding):
     rows, columns = 48, 2048
