@@ -346,9 +346,19 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
                 mask &= mask - 1;
                 const uint32_t unit = first_unit + u * SLOTS;
                 // lane = row of the unit's 32 partial sums (pair mode: 16 gate, 16 up)
+                // (eight loads in flight at a time; added in slice order)
                 float sum = 0.0f;
-                if (lane < 16 || pair)
-                    for (uint32_t k = 0; k < p.nks; ++k) sum += __ldcg(p.partials + ((size_t)k * p.units + unit) * 32 + lane);
+                if (lane < 16 || pair) {
+                    const float *src = p.partials + (size_t)unit * 32 + lane;
+                    const size_t step = (size_t)p.units * 32;
+                    for (uint32_t k0 = 0; k0 < p.nks; k0 += 8) {
+                        float v[8];
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) v[k] = k0 + k < p.nks ? __ldcg(src + (k0 + k) * step) : 0.0f;
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) sum += v[k];
+                    }
+                }
                 const float up = __shfl_down_sync(0xffffffffu, sum, 16);
                 if (lane < 16) {
                     if (pair) {
@@ -439,7 +449,9 @@ static bool fill_common(const FastJob &job, Params &p) {
     const uint32_t sms = (uint32_t)job.sm_count;
     double best = 1e30;
     uint32_t blocks[MAX_SLICES];
+    static const uint32_t forced_ksl = [] { const char *e = getenv("NUCLIS_DEC_KSL"); return e ? (uint32_t)atoi(e) : 0u; }();  // measurements only
     for (uint32_t ksl = 1; ksl <= p.ksb && ksl <= kMaxSliceSbs; ++ksl) {
+        if (forced_ksl && ksl != forced_ksl && forced_ksl <= p.ksb) continue;
         const uint32_t nks = (p.ksb + ksl - 1) / ksl;
         if (nks > MAX_SLICES || nks > sms) continue;
         const int st = pick_stages<E>(ksl);
@@ -460,7 +472,7 @@ static bool fill_common(const FastJob &job, Params &p) {
         double est = 0;
         for (uint32_t s = 0; s < nks; ++s) est = cost(s, blocks[s]) > est ? cost(s, blocks[s]) : est;
         est *= st >= 4 ? 1.0 : st == 3 ? 1.06 : 1.2;  // a shallow ring hides less latency
-        est += (nks > 1 ? 1.5 : 0.0) + 0.01 * ksl;   // partial sums; staging of the slice
+        est += (nks > 1 ? 5.0 + 0.3 * nks : 0.0) + 0.01 * ksl;  // partial sums, their fence and the last arriver's pass (measured: 4-6 us); staging of the slice
         if (est < best - 1e-9) {
             best = est;
             p.ksl = ksl;

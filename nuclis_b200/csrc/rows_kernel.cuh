@@ -309,10 +309,16 @@ __global__ void __launch_bounds__(THREADS, 1) rows_kernel(const __grid_constant_
                 const uint32_t u = base + (uint32_t)__ffs((int)mask) - 1;
                 mask &= mask - 1;
                 const uint32_t tile = first_tile + u * SLOTS;
+                // (four loads in flight at a time; added in slice order)
                 float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (uint32_t k = 0; k < p.nks; ++k) {
-                    const float4 v = __ldcg((const float4 *)(p.partials + ((size_t)k * p.total_tiles + tile) * PARTIAL_FLOATS + lane * 4));
-                    s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+                const float *src = p.partials + (size_t)tile * PARTIAL_FLOATS + lane * 4;
+                const size_t step = (size_t)p.total_tiles * PARTIAL_FLOATS;
+                for (uint32_t k0 = 0; k0 < p.nks; k0 += 4) {
+                    float4 v[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) v[k] = k0 + k < p.nks ? __ldcg((const float4 *)(src + (k0 + k) * step)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) { s.x += v[k].x; s.y += v[k].y; s.z += v[k].z; s.w += v[k].w; }
                 }
                 const float val[4] = {s.x, s.y, s.z, s.w};
                 write_tile<WIDE>(p, tile, g, t, val);
@@ -405,7 +411,7 @@ static bool fill_common(const FastJob &job, Params &p, Plan &plan) {
         double est = 0;
         for (uint32_t s = 0; s < nks; ++s) est = cost(s, blocks[s]) > est ? cost(s, blocks[s]) : est;
         est *= st >= 4 ? 1.0 : st == 3 ? 1.06 : 1.2;            // a shallow ring hides less latency
-        est += (nks > 1 ? 0.6 : 0.0) + 0.005 * job.tokens * ksl;  // partial sums; staging of the window
+        est += (nks > 1 ? 3.0 + 0.3 * nks : 0.0) + 0.005 * job.tokens * ksl;  // partial sums and the last arriver's pass; staging of the window
         if (est < best - 1e-9) {
             best = est;
             p.ksl = ksl;
