@@ -131,7 +131,7 @@ template <class E, int STAGES>
 __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constant__ Params p) {
     constexpr int TASK_BYTES = E::TASK_BYTES;
     extern __shared__ __align__(128) uint8_t smem[];
-    // [task stages][hi pieces][lo pieces][128 B of zeros][group sums][part sums][max scratch][barriers]
+    // [task stages][hi pieces][lo pieces][128 B of zeros][group sums][per-superblock 1/scale][staged flags][part sums][barriers]
     // A piece array holds the slice's columns as halves, the 128 bytes of each group pair (64 columns) padded
     // to PAIR_PITCH = 136: the four quad lanes then read four different pairs of banks, and the lo array starts
     // 32 bytes further round the banks than the hi array, so the eight loading lanes of a warp never collide.
@@ -142,9 +142,10 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
     uint8_t *xlo = xhi + piece_bytes + lo_skew;
     uint8_t *zero = xlo + piece_bytes + (128u - (piece_bytes + lo_skew + piece_bytes) % 128u) % 128u;
     float *gsum = (float *)(zero + 128);
-    float *parts = gsum + p.ksl * E::GSUMS;           // SLOTS x 2 x 3 x 32 floats
-    float *red = parts + SLOTS * 2 * 3 * 32;
-    uint64_t *bars = (uint64_t *)(red + 32);
+    float *inv_sb = gsum + p.ksl * E::GSUMS;           // per superblock of the slice: 1 / its activation scale
+    volatile uint32_t *ready = (volatile uint32_t *)(inv_sb + p.ksl);  // per superblock: staged
+    float *parts = (float *)(ready + p.ksl);           // SLOTS x 2 x 3 x 32 floats
+    uint64_t *bars = (uint64_t *)(parts + SLOTS * 2 * 3 * 32);
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t g = lane >> 2, t = lane & 3;
     const uint32_t slot = warp >> 2, part = warp & 3;
@@ -205,60 +206,67 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
             else if (issued < total) unit_rows(p, p_unit, p_seg, p_row0);
         }
     };
-    constexpr int PRE = NU_DEC_PRE < STAGES - 1 ? NU_DEC_PRE : STAGES - 1;
-    for (int i = 0; i < PRE; ++i)
+    for (int i = 0; i < STAGES - 1; ++i)
         if (issued < total) issue();
+    for (uint32_t i = tid; i < p.ksl; i += THREADS) ready[i] = 0;
+    if (tid < 32) ((uint32_t *)zero)[tid] = 0;
+    __syncthreads();  // still under the tail of the previous kernel
     asm volatile("griddepcontrol.wait;" ::: "memory");  // the previous kernel has ended; its writes are visible
     NU_TRACE(1);
 
-    // ---- stage the slice's activations: scale, split into fp16 pieces, group sums ----
-    // The window is read from global memory once and kept in registers between the two passes.
-    constexpr int XV = (20480 / 4 + THREADS - 1) / THREADS;  // float4 per thread: slices of up to 20480 columns
-    float4 xv[XV];
-    float mx = 0.0f;
+    // ---- stage the slice's activations, a superblock per warp at a time: scale, fp16 pieces, group sums ----
+    // Warp w stages superblocks w, w + 16, ... of the slice (two float4 per lane each), with the
+    // superblock's own power-of-two scale, and raises the superblock's flag; a task waits for the flag
+    // of its superblock only, so the first tasks start while later superblocks are still being staged.
+    {
+        constexpr int SBW = (80 + WARPS - 1) / WARPS;  // superblocks per warp at most
+        float4 xa[SBW], xb2[SBW];
 #pragma unroll
-    for (int j = 0; j < XV; ++j) {
-        const uint32_t i = tid + j * THREADS;
-        xv[j] = i < n * 64 ? ((const float4 *)p.in)[sb0 * 64 + i] : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    for (int i = PRE; i < STAGES - 1; ++i)  // the loads above are in flight; the rest of the ring follows them
-        if (issued < total) issue();
+        for (int j = 0; j < SBW; ++j) {
+            const uint32_t sb = warp + j * WARPS;
+            if (sb < n) {
+                xa[j] = ((const float4 *)p.in)[(sb0 + sb) * 64 + lane];
+                xb2[j] = ((const float4 *)p.in)[(sb0 + sb) * 64 + 32 + lane];
+            }
+        }
 #pragma unroll
-    for (int j = 0; j < XV; ++j) mx = fmaxf(mx, fmaxf(fmaxf(fabsf(xv[j].x), fabsf(xv[j].y)), fmaxf(fabsf(xv[j].z), fabsf(xv[j].w))));
+        for (int j = 0; j < SBW; ++j) {
+            const uint32_t sb = warp + j * WARPS;
+            if (sb < n) {  // uniform per warp
+                float mx = fmaxf(fmaxf(fmaxf(fabsf(xa[j].x), fabsf(xa[j].y)), fmaxf(fabsf(xa[j].z), fabsf(xa[j].w))),
+                                 fmaxf(fmaxf(fabsf(xb2[j].x), fabsf(xb2[j].y)), fmaxf(fabsf(xb2[j].z), fabsf(xb2[j].w))));
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if (lane == 0) red[warp] = mx;
-    if (tid < 32) ((uint32_t *)zero)[tid] = 0;
-    __syncthreads();
-    mx = red[0];
+                for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                // 2^e puts the largest |x| in [2^13, 2^14): hi cannot overflow fp16, lo keeps 11 bits down to 2^-25 of the largest value
+                const uint32_t e = (__float_as_uint(mx) >> 23) & 0xffu;
+                const bool ok = e >= 40u && e < 255u;
+                const float scale = ok ? __uint_as_float((267u - e) << 23) : 1.0f;
 #pragma unroll
-    for (int w = 1; w < WARPS; ++w) mx = fmaxf(mx, red[w]);
-    // 2^e puts the largest |x| in [2^13, 2^14): hi cannot overflow fp16, lo keeps 11 bits down to 2^-25 of the largest value
-    const uint32_t e = (__float_as_uint(mx) >> 23) & 0xffu;
-    const bool ok = e >= 40u && e < 255u;
-    const float scale = ok ? __uint_as_float((267u - e) << 23) : 1.0f;
-    const float inv_scale = ok ? __uint_as_float((e - 13u) << 23) : 1.0f;
-#pragma unroll
-    for (int j = 0; j < XV; ++j) {
-        const uint32_t i = tid + j * THREADS;
-        if (i < n * 64) {  // uniform per warp: a multiple of 32
-            const float x0 = xv[j].x * scale, x1 = xv[j].y * scale, x2 = xv[j].z * scale, x3 = xv[j].w * scale;
-            const __half h0 = __float2half_rn(x0), h1 = __float2half_rn(x1), h2 = __float2half_rn(x2), h3 = __float2half_rn(x3);
-            const __half l0 = __float2half_rn(x0 - __half2float(h0)), l1 = __float2half_rn(x1 - __half2float(h1));
-            const __half l2 = __float2half_rn(x2 - __half2float(h2)), l3 = __float2half_rn(x3 - __half2float(h3));
-            // k order of the A operand built below: columns +0, +2 in the first register, +1, +3 in the second
-            uint2 hi, lo;
-            hi.x = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h2) << 16);
-            hi.y = (uint32_t)__half_as_ushort(h1) | ((uint32_t)__half_as_ushort(h3) << 16);
-            lo.x = (uint32_t)__half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l2) << 16);
-            lo.y = (uint32_t)__half_as_ushort(l1) | ((uint32_t)__half_as_ushort(l3) << 16);
-            const uint32_t off = E::x_offset(i);
-            *(uint2 *)(xhi + off) = hi;
-            *(uint2 *)(xlo + off) = lo;
-            E::group_sum(gsum, i, (x0 + x1) + (x2 + x3), lane);
+                for (int hf = 0; hf < 2; ++hf) {
+                    const float4 v = hf ? xb2[j] : xa[j];
+                    const uint32_t i = sb * 64 + hf * 32 + lane;  // float4 index within the slice
+                    const float x0 = v.x * scale, x1 = v.y * scale, x2 = v.z * scale, x3 = v.w * scale;
+                    const __half h0 = __float2half_rn(x0), h1 = __float2half_rn(x1), h2 = __float2half_rn(x2), h3 = __float2half_rn(x3);
+                    const __half l0 = __float2half_rn(x0 - __half2float(h0)), l1 = __float2half_rn(x1 - __half2float(h1));
+                    const __half l2 = __float2half_rn(x2 - __half2float(h2)), l3 = __float2half_rn(x3 - __half2float(h3));
+                    // k order of the A operand built below: columns +0, +2 in the first register, +1, +3 in the second
+                    uint2 hi, lo;
+                    hi.x = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h2) << 16);
+                    hi.y = (uint32_t)__half_as_ushort(h1) | ((uint32_t)__half_as_ushort(h3) << 16);
+                    lo.x = (uint32_t)__half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l2) << 16);
+                    lo.y = (uint32_t)__half_as_ushort(l1) | ((uint32_t)__half_as_ushort(l3) << 16);
+                    const uint32_t off = E::x_offset(i);
+                    *(uint2 *)(xhi + off) = hi;
+                    *(uint2 *)(xlo + off) = lo;
+                    E::group_sum(gsum, i, (x0 + x1) + (x2 + x3), lane);
+                }
+                if (lane == 0) inv_sb[sb] = ok ? __uint_as_float((e - 13u) << 23) : 1.0f;
+                __threadfence_block();
+                __syncwarp();
+                if (lane == 0) ready[sb] = 1;
+            }
         }
     }
-    __syncthreads();
     NU_TRACE(2);
 
     // ---- the task loop ----
@@ -277,15 +285,29 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
         for (uint32_t j = 0; j < m && !failed; ++j) {
             const uint32_t sbw = part + PARTS * j;  // superblock within the slice
             if (issued < total) issue();  // keep STAGES - 1 tasks in flight
+            if (uidx == 0) {
+                // the first unit may run ahead of the staging of its superblocks
+                uint32_t spins = 0;
+                while (ready[sbw] == 0 && ++spins < SPIN_LIMIT) {}
+                if (ready[sbw] == 0) { failed = true; break; }
+                __threadfence_block();
+            }
             if (!mbar_wait(bar0 + c_stage * 8, c_phase)) { failed = true; break; }
-            E::task(my_stage + c_stage * TASK_BYTES, xlane + sbw * xstep, gsum + sbw * E::GSUMS, g, t, acc);
+            const float inv = inv_sb[sbw];
+            float tmp[2] = {0.0f, 0.0f};
+            E::task(my_stage + c_stage * TASK_BYTES, xlane + sbw * xstep, gsum + sbw * E::GSUMS, g, t, tmp);
+            acc[0] = fmaf(inv, tmp[0], acc[0]);
+            acc[1] = fmaf(inv, tmp[1], acc[1]);
             __syncwarp();  // all lanes are done reading this stage before it is refilled
             ++consumed;
             if (++c_stage == STAGES) { c_stage = 0; c_phase ^= 1u; }
             if (pair) {
                 if (issued < total) issue();
                 if (!mbar_wait(bar0 + c_stage * 8, c_phase)) { failed = true; break; }
-                E::task(my_stage + c_stage * TASK_BYTES, xlane + sbw * xstep, gsum + sbw * E::GSUMS, g, t, acc2);
+                float tmp2[2] = {0.0f, 0.0f};
+                E::task(my_stage + c_stage * TASK_BYTES, xlane + sbw * xstep, gsum + sbw * E::GSUMS, g, t, tmp2);
+                acc2[0] = fmaf(inv, tmp2[0], acc2[0]);
+                acc2[1] = fmaf(inv, tmp2[1], acc2[1]);
                 __syncwarp();
                 ++consumed;
                 if (++c_stage == STAGES) { c_stage = 0; c_phase ^= 1u; }
@@ -318,7 +340,6 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
             acc[1] += src[g + 8];
             if (pair) { acc2[0] += src[16 + g]; acc2[1] += src[24 + g]; }
         }
-        acc[0] *= inv_scale; acc[1] *= inv_scale; acc2[0] *= inv_scale; acc2[1] *= inv_scale;
         if (p.nks > 1) {
             // several slices: leave the partial sums; they are published after the loop with one fence
             float *dst = p.partials + ((size_t)ks * p.units + unit) * 32;
@@ -392,7 +413,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
 
 template <class E>
 static size_t smem_bytes(uint32_t ksl, int stages) {
-    return (size_t)WARPS * stages * E::TASK_BYTES + (size_t)(ksl * 4) * PAIR_PITCH * 2 + 512 + (size_t)ksl * E::GSUMS * 4 + SLOTS * 2 * 3 * 32 * 4 + 128 +
+    return (size_t)WARPS * stages * E::TASK_BYTES + (size_t)(ksl * 4) * PAIR_PITCH * 2 + 512 + (size_t)ksl * E::GSUMS * 4 + (size_t)ksl * 8 + SLOTS * 2 * 3 * 32 * 4 + 128 +
            WARPS * stages * 8 + 128;
 }
 
