@@ -221,6 +221,19 @@ int nu_cuda_gelu_mul(nu_cuda *h, const nu_buffer *gate, const nu_buffer *up, siz
 int nu_cuda_route(nu_cuda *h, const nu_buffer *logits, size_t experts, size_t k, size_t rows, size_t in_stride,
                   const nu_buffer *indices, const nu_buffer *weights);
 
+/* `Backend.expertLists` (ops/experts.zig:137-146): groups the rows * k slot rows of `indices` ([row][k], as
+ * route writes them) by expert into `lists`, nu_cuda_expert_lists_words(rows * k, experts) 32-bit words in
+ * the reference's layout: the tile count, n, experts + 1 exclusive prefix offsets, the tiles of at most 32
+ * slot rows as (expert, first, count), and the n slot rows grouped by expert. At most 256 experts. */
+size_t nu_cuda_expert_lists_words(size_t slot_rows, size_t experts);
+int nu_cuda_expert_lists(nu_cuda *h, const nu_buffer *indices, size_t rows, size_t k, size_t experts, const nu_buffer *lists);
+/* `Backend.matmulExperts` (ops/experts.zig:162-202): for each slot row s of the lists,
+ * output[s * out_stride + r] = W[e_s][r] . input[(s / in_group) * in_stride]; weights are read once per
+ * tile of an expert's slot rows; exactly rows * k output rows are written. Same shape rules as matmul
+ * (columns % 64, rows % 8, 16-byte aligned input). */
+int nu_cuda_matmul_experts(nu_cuda *h, const nu_buffer *weights, const nu_expert_matrix *tensor, const nu_buffer *lists, size_t rows, size_t k,
+                           const nu_buffer *input, size_t in_stride, size_t in_group, const nu_buffer *output, size_t out_stride);
+
 /* Expert parallelism (no counterpart in the reference, which is single-device): a rank that holds
  * experts [first_expert, first_expert + local_experts) turns the routed slots into its own view:
  * slots it owns keep their weight and get the expert's local index, the others get index 0 and

@@ -74,6 +74,9 @@ SIGNATURES = {
     "nu_cuda_silu_mul": (cint, [vp, BP, BP, sz]),
     "nu_cuda_gelu_mul": (cint, [vp, BP, BP, sz]),
     "nu_cuda_route": (cint, [vp, BP, sz, sz, sz, sz, BP, BP]),
+    "nu_cuda_expert_lists_words": (sz, [sz, sz]),
+    "nu_cuda_expert_lists": (cint, [vp, BP, sz, sz, sz, BP]),
+    "nu_cuda_matmul_experts": (cint, [vp, BP, ctypes.POINTER(CExpertMatrix), BP, sz, sz, BP, sz, sz, BP, sz]),
     "nu_cuda_route_local": (cint, [vp, BP, BP, sz, sz, sz, BP, BP]),
     "nu_cuda_matvec_experts": (cint, [vp, BP, EP, BP, sz, BP, sz, sz, BP, sz]),
     "nu_cuda_gelu_mul_rows": (cint, [vp, BP, BP, BP, sz, sz, sz, sz, sz]),

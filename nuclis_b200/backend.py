@@ -282,6 +282,19 @@ class Backend:
     def route(self, logits: Buffer, experts: int, k: int, rows: int, in_stride: int, indices: Buffer, weights: Buffer) -> None:
         self._check(self._lib.nu_cuda_route(self._h, logits._c(), experts, k, rows, in_stride, indices._c(), weights._c()))
 
+    @staticmethod
+    def expert_lists_words(slot_rows: int, experts: int) -> int:
+        """32-bit words of the lists buffer `expert_lists` fills (the reference's `expertListsLayout`)."""
+        return _lib.load().nu_cuda_expert_lists_words(slot_rows, experts)
+
+    def expert_lists(self, indices: Buffer, rows: int, k: int, experts: int, lists: Buffer) -> None:
+        self._check(self._lib.nu_cuda_expert_lists(self._h, indices._c(), rows, k, experts, lists._c()))
+
+    def matmul_experts(self, weights: Buffer, tensor: ExpertMatrix, lists: Buffer, rows: int, k: int, input: Buffer, in_stride: int, in_group: int,
+                       output: Buffer, out_stride: int) -> None:
+        self._check(self._lib.nu_cuda_matmul_experts(self._h, weights._c(), tensor._c(), lists._c(), rows, k, input._c(), in_stride, in_group,
+                                                     output._c(), out_stride))
+
     def route_local(self, indices: Buffer, weights: Buffer, count: int, first_expert: int, local_experts: int, local_indices: Buffer,
                     local_weights: Buffer) -> None:
         """Expert parallelism: the routed slots this rank owns (local index, same weight), the others silenced (index 0, weight 0)."""

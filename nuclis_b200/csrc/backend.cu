@@ -649,6 +649,51 @@ int Backend::matvecExpertsGrouped(const Buffer &weights, const ExpertMatrix &t, 
     return cuda(cudaGetLastError(), "experts: launch");
 }
 
+// ops/experts.zig:119-146: the lists buffer layout is the reference's (expertListsLayout).
+static size_t expertTileBound(size_t n, size_t experts) { return (n + 31) / 32 + experts; }
+static size_t expertListsWords(size_t n, size_t experts) { return experts + 3 + 3 * expertTileBound(n, experts) + n; }
+
+int Backend::expertLists(const Buffer &indices, size_t rows, size_t k, size_t experts, const Buffer &lists) {
+    if (rows == 0 || k == 0 || experts == 0 || experts > 256) return fail(NU_ERR_INVALID_SHAPE, "expert_lists: shape");
+    if (rows > 0x3fffffffull / k) return fail(NU_ERR_INVALID_SHAPE, "expert_lists: too many slot rows");
+    const size_t n = rows * k;
+    const uint32_t *idx = (const uint32_t *)resolve(indices, n * 4);
+    uint32_t *l = (uint32_t *)resolve(lists, expertListsWords(n, experts) * 4);
+    if (!idx || !l || indices.offset % 4 != 0 || lists.offset % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "expert_lists: buffer too short");
+    if (int rc = needRecording()) return rc;
+    launches_ += launch_expert_lists(stream_, idx, (uint32_t)n, (uint32_t)experts, (uint32_t)expertTileBound(n, experts), l);
+    wrote(lists);
+    opBoundary();
+    return cuda(cudaGetLastError(), "expert_lists: launch");
+}
+
+// ops/experts.zig:148-202.
+int Backend::matmulExperts(const Buffer &weights, const ExpertMatrix &t, const Buffer &lists, size_t rows, size_t k, const Buffer &input, size_t in_stride,
+                           size_t in_group, const Buffer &output, size_t out_stride) {
+    if (t.experts == 0 || t.experts > 256 || t.rows == 0 || t.columns == 0 || t.bytes % t.experts != 0 || (t.bytes / t.experts) % t.rows != 0)
+        return fail(NU_ERR_INVALID_SHAPE, "matmul_experts: tensor shape");
+    const size_t per_expert = t.bytes / t.experts;
+    const size_t stride = per_expert / t.rows;
+    if (validateRow(t.encoding, stride, t.columns) != NU_OK) return fail(NU_ERR_INVALID_SHAPE, "matmul_experts: row layout");
+    if (t.rows % 8 != 0 || t.columns % 64 != 0 || t.rows > 0xffffffffull / 4 || !fits_u32(t.columns)) return fail(NU_ERR_INVALID_SHAPE, "matmul_experts: sizes");
+    if (rows == 0 || k == 0 || in_group == 0 || in_stride < t.columns || out_stride < t.rows || in_stride % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "matmul_experts: rows or strides");
+    if (rows > 0x3fffffffull / k) return fail(NU_ERR_INVALID_SHAPE, "matmul_experts: too many slot rows");
+    const size_t n = rows * k, input_rows = (n + in_group - 1) / in_group;
+    const uint8_t *w = resolve(weights, t.bytes);
+    const uint32_t *l = (const uint32_t *)resolve(lists, expertListsWords(n, t.experts) * 4);
+    const float *in = (const float *)resolve(input, ((input_rows - 1) * in_stride + t.columns) * 4);
+    float *out = (float *)resolve(output, ((n - 1) * out_stride + t.rows) * 4);
+    if (!w || !l || !in || !out || lists.offset % 4 != 0 || input.offset % 16 != 0 || output.offset % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "matmul_experts: buffer too short");
+    const size_t bound = expertTileBound(n, t.experts);
+    if (bound > 65535) return fail(NU_ERR_TOO_LARGE, "matmul_experts: more than 65,535 tiles");
+    if (int rc = needRecording()) return rc;
+    launches_ += launch_matmul_experts_generic(stream_, t.encoding, w, stride, per_expert, (uint32_t)t.experts, (uint32_t)t.rows, (uint32_t)t.columns, l,
+                                               (uint32_t)bound, in, in_stride, (uint32_t)in_group, out, out_stride);
+    wrote(output);
+    opBoundary();
+    return cuda(cudaGetLastError(), "matmul_experts: launch");
+}
+
 // ops/experts.zig:106-117.
 int Backend::geluMulRows(const Buffer &gate, const Buffer &up, const Buffer &output, size_t width, size_t rows,
                          size_t gate_stride, size_t up_stride, size_t out_stride) {
@@ -954,6 +999,18 @@ int nu_cuda_silu_mul(nu_cuda *h, const nu_buffer *gate, const nu_buffer *up, siz
 int nu_cuda_gelu_mul(nu_cuda *h, const nu_buffer *gate, const nu_buffer *up, size_t count) {
     NU_H(h); NU_P(gate && up);
     return h->b->actMul(nu::ACT_GELU, *gate, *up, count);
+}
+int nu_cuda_expert_lists(nu_cuda *h, const nu_buffer *indices, size_t rows, size_t k, size_t experts, const nu_buffer *lists) {
+    NU_H(h);
+    if (!indices || !lists) return NU_ERR_INVALID_SHAPE;
+    return h->b->expertLists(*indices, rows, k, experts, *lists);
+}
+size_t nu_cuda_expert_lists_words(size_t slot_rows, size_t experts) { return experts + 3 + 3 * ((slot_rows + 31) / 32 + experts) + slot_rows; }
+int nu_cuda_matmul_experts(nu_cuda *h, const nu_buffer *weights, const nu_expert_matrix *tensor, const nu_buffer *lists, size_t rows, size_t k,
+                           const nu_buffer *input, size_t in_stride, size_t in_group, const nu_buffer *output, size_t out_stride) {
+    NU_H(h);
+    if (!weights || !tensor || !lists || !input || !output) return NU_ERR_INVALID_SHAPE;
+    return h->b->matmulExperts(*weights, *tensor, *lists, rows, k, *input, in_stride, in_group, *output, out_stride);
 }
 int nu_cuda_route_local(nu_cuda *h, const nu_buffer *indices, const nu_buffer *weights, size_t count, size_t first_expert, size_t local_experts,
                         const nu_buffer *local_indices, const nu_buffer *local_weights) {

@@ -33,6 +33,10 @@ int launch_act_mul_rows(cudaStream_t s, uint32_t act, const float *gate, const f
                         uint32_t width, uint32_t rows, size_t gate_stride, size_t up_stride, size_t out_stride);
 int launch_route(cudaStream_t s, const float *logits, uint32_t experts, uint32_t k, uint32_t rows, size_t in_stride,
                  uint32_t *indices, float *weights);
+int launch_expert_lists(cudaStream_t s, const uint32_t *indices, uint32_t n, uint32_t experts, uint32_t bound, uint32_t *lists);
+int launch_matmul_experts_generic(cudaStream_t s, uint32_t enc, const uint8_t *w, size_t stride, size_t expert_bytes, uint32_t experts, uint32_t rows,
+                                  uint32_t columns, const uint32_t *lists, uint32_t bound, const float *in, size_t in_stride, uint32_t in_group,
+                                  float *out, size_t out_stride);
 int launch_route_local(cudaStream_t s, const uint32_t *indices, const float *weights, uint32_t n, uint32_t first, uint32_t count, uint32_t *local_indices,
                        float *local_weights);
 int launch_combine_experts(cudaStream_t s, const float *values, const float *weights, const uint32_t *indices, const float *scales,

@@ -129,6 +129,109 @@ int launch_matvec_experts_generic(cudaStream_t s, uint32_t enc, const uint8_t *w
     return 1;
 }
 
+// ---- prefill expert path: slot rows grouped by expert, then gathered tiles ------------------
+// (inference/src/backends/metal/ops/experts.zig:119-202). The lists buffer holds, in 32-bit words:
+// [0] tile count, [1] n, [2 .. 2 + experts] exclusive prefix offsets, then `bound` tiles of
+// (expert, first, count), then the n slot rows grouped by expert, in slot order within an expert.
+
+constexpr int EXPERT_TILE = 32;
+
+__global__ void expert_lists_kernel(const uint32_t *indices, uint32_t n, uint32_t experts, uint32_t bound, uint32_t *lists) {
+    __shared__ uint32_t counts[256], offsets[257];
+    const uint32_t tid = threadIdx.x;
+    uint32_t *tiles = lists + experts + 3, *rows = tiles + 3 * (size_t)bound;
+    // one thread per expert walks the slot rows in order: counts first, stable placement after the prefix
+    uint32_t mine = 0;
+    if (tid < experts)
+        for (uint32_t i = 0; i < n; ++i) mine += min(indices[i], experts - 1) == tid;
+    counts[tid] = tid < experts ? mine : 0;
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t at = 0, ntiles = 0;
+        for (uint32_t e = 0; e < experts; ++e) {
+            offsets[e] = at;
+            for (uint32_t first = 0; first < counts[e]; first += EXPERT_TILE) {
+                tiles[3 * ntiles] = e;
+                tiles[3 * ntiles + 1] = at + first;
+                tiles[3 * ntiles + 2] = min((uint32_t)EXPERT_TILE, counts[e] - first);
+                ++ntiles;
+            }
+            at += counts[e];
+        }
+        offsets[experts] = at;
+        lists[0] = ntiles;
+        lists[1] = n;
+    }
+    __syncthreads();
+    if (tid <= experts) lists[2 + tid] = offsets[tid];
+    if (tid < experts) {
+        uint32_t at = offsets[tid];
+        for (uint32_t i = 0; i < n; ++i)
+            if (min(indices[i], experts - 1) == tid) rows[at++] = i;
+    }
+}
+
+int launch_expert_lists(cudaStream_t s, const uint32_t *indices, uint32_t n, uint32_t experts, uint32_t bound, uint32_t *lists) {
+    expert_lists_kernel<<<1, 256, 0, s>>>(indices, n, experts, bound, lists);
+    return 1;
+}
+
+// One block per (tile of up to 32 slot rows of one expert, group of GENERIC_WARPS weight rows); a warp
+// takes one weight row and the tile's slot rows eight at a time: the expert's weights are decoded once per
+// eight slot rows instead of once per slot row.
+__global__ void matmul_experts_generic_kernel(uint32_t enc, const uint8_t *w, size_t stride, size_t expert_bytes, uint32_t experts, uint32_t rows,
+                                              uint32_t columns, const uint32_t *lists, uint32_t bound, const float *in, size_t in_stride,
+                                              uint32_t in_group, float *out, size_t out_stride) {
+    const uint32_t tile = blockIdx.y;
+    if (tile >= lists[0]) return;
+    const uint32_t *tiles = lists + experts + 3, *slot_rows = tiles + 3 * (size_t)bound;
+    const uint32_t expert = min(tiles[3 * tile], experts - 1), first = tiles[3 * tile + 1], count = tiles[3 * tile + 2];
+    const uint32_t r = blockIdx.x * GENERIC_WARPS + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint8_t *we = w + (size_t)expert * expert_bytes;
+    for (uint32_t c0 = 0; c0 < count; c0 += GENERIC_TOKENS) {
+        const uint32_t nt = min(count - c0, (uint32_t)GENERIC_TOKENS);
+        const float *x[GENERIC_TOKENS];
+        uint32_t slot[GENERIC_TOKENS];
+#pragma unroll
+        for (int t = 0; t < GENERIC_TOKENS; ++t) {
+            slot[t] = slot_rows[first + c0 + min((uint32_t)t, nt - 1)];
+            x[t] = in + (size_t)(slot[t] / in_group) * in_stride;
+        }
+        float acc[GENERIC_TOKENS];
+#pragma unroll
+        for (int t = 0; t < GENERIC_TOKENS; ++t) acc[t] = 0.0f;
+        for (uint32_t seg = lane; seg < columns / 16; seg += 32) {
+            float v[16];
+            decode16(enc, 0, we, stride, rows, columns, r, seg, v);
+#pragma unroll
+            for (int t = 0; t < GENERIC_TOKENS; ++t) {
+                if ((uint32_t)t < nt) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) acc[t] = fmaf(v[i], x[t][seg * 16 + i], acc[t]);
+                }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < GENERIC_TOKENS; ++t) {
+            float a = acc[t];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+            if (lane == 0 && (uint32_t)t < nt) out[(size_t)slot[t] * out_stride + r] = a;
+        }
+    }
+}
+
+int launch_matmul_experts_generic(cudaStream_t s, uint32_t enc, const uint8_t *w, size_t stride, size_t expert_bytes, uint32_t experts, uint32_t rows,
+                                  uint32_t columns, const uint32_t *lists, uint32_t bound, const float *in, size_t in_stride, uint32_t in_group,
+                                  float *out, size_t out_stride) {
+    dim3 grid((rows + GENERIC_WARPS - 1) / GENERIC_WARPS, bound);
+    matmul_experts_generic_kernel<<<grid, GENERIC_WARPS * 32, 0, s>>>(enc, w, stride, expert_bytes, experts, rows, columns, lists, bound, in, in_stride,
+                                                                      in_group, out, out_stride);
+    return 1;
+}
+
 // ---- act(gate) * up ----------------------------------------------------------
 
 __global__ void act_mul_rows_kernel(uint32_t act, const float *gate, const float *up, float *out, uint32_t width, uint32_t rows,

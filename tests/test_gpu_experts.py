@@ -154,6 +154,86 @@ def test_expert_parallel_partials_add_up_to_the_full_result(backend, tensors, to
         backend.release(buf)
 
 
+def test_expert_lists_group_slot_rows_by_expert(backend):
+    rows, experts = 37, 128
+    rng = np.random.default_rng(77)
+    idx = np.stack([rng.choice(experts, K, replace=False) for _ in range(rows)]).astype(np.uint32)
+    idx[0, 0] = 4000  # a corrupt index is clamped to the last expert, as in the other expert operators
+    n = rows * K
+    words = Backend.expert_lists_words(n, experts)
+    bound = (n + 31) // 32 + experts
+    assert words == experts + 3 + 3 * bound + n
+    ib = backend.create(idx.nbytes); lb = backend.create(words * 4)
+    ib.write(idx)
+    backend.begin(); backend.expert_lists(ib, rows, K, experts, lb); backend.commit()
+    lists = lb.read(np.uint32)[:words]
+    flat = np.minimum(idx.reshape(-1), experts - 1)
+    counts = np.bincount(flat, minlength=experts)
+    assert lists[1] == n
+    assert np.array_equal(lists[2:2 + experts + 1], np.concatenate([[0], np.cumsum(counts)]))
+    tiles = lists[experts + 3:experts + 3 + 3 * lists[0]].reshape(-1, 3)
+    assert lists[0] == sum((c + 31) // 32 for c in counts)
+    slot_rows = lists[experts + 3 + 3 * bound:]
+    order = np.argsort(flat, kind="stable")
+    assert np.array_equal(slot_rows, order)
+    at = 0
+    for e, first, count in tiles:
+        assert first == at and 1 <= count <= 32 and np.all(flat[slot_rows[first:first + count]] == e)
+        at += count
+    assert at == n
+    with pytest.raises(NuclisError):
+        backend.begin()
+        try:
+            backend.expert_lists(ib, rows, K, 300, lb)
+        finally:
+            backend.discard()
+    backend.release(ib); backend.release(lb)
+
+
+def test_gathered_matmul_over_expert_lists_matches_cpu_ffn(backend, tensors):
+    """The prefill form of the expert chain (rows > 8): slot rows grouped by expert, weights read once per
+    tile of an expert's rows, against the CPU oracle token by token."""
+    gate_up, down = tensors
+    tokens = 24
+    rng = np.random.default_rng(41)
+    x = rng.standard_normal((tokens, HIDDEN)).astype(np.float32)
+    logits = rng.standard_normal((tokens, EXPERTS)).astype(np.float32)
+    scales = (0.5 + rng.random(EXPERTS)).astype(np.float32)
+    gu_t = ExpertMatrix(enc.Q4_K, EXPERTS, 2 * FF, HIDDEN, gate_up.size)
+    dn_t = ExpertMatrix(enc.Q8_0, EXPERTS, HIDDEN, FF, down.size)
+    slots = tokens * K
+    gub, dnb = backend.wrap(gate_up), backend.wrap(down)
+    xb = backend.create(x.nbytes); lb = backend.create(logits.nbytes); sb = backend.create(scales.nbytes)
+    ib = backend.create(slots * 4); wb = backend.create(slots * 4)
+    lists = backend.create(Backend.expert_lists_words(slots, EXPERTS) * 4)
+    gu_out = backend.create(slots * 2 * FF * 4); hid = backend.create(slots * FF * 4)
+    y = backend.create(slots * HIDDEN * 4); out = backend.create(tokens * HIDDEN * 4)
+    xb.write(x); lb.write(logits); sb.write(scales)
+    backend.begin()
+    backend.route(lb, EXPERTS, K, tokens, EXPERTS, ib, wb)
+    backend.expert_lists(ib, tokens, K, EXPERTS, lists)
+    backend.matmul_experts(gub, gu_t, lists, tokens, K, xb, HIDDEN, K, gu_out, 2 * FF)
+    backend.gelu_mul_rows(gu_out, gu_out.slice(FF * 4, gu_out.len - FF * 4), hid, FF, slots, 2 * FF, 2 * FF, FF)
+    backend.matmul_experts(dnb, dn_t, lists, tokens, K, hid, FF, 1, y, HIDDEN)
+    backend.combine_experts(y, wb, ib, sb, out, CombineShape(columns=HIDDEN, slots=K, experts=EXPERTS, in_stride=HIDDEN, out_stride=HIDDEN, rows=tokens))
+    backend.commit()
+    got = out.floats().reshape(tokens, HIDDEN)
+    for t in range(tokens):
+        idx, w = oracle.route(logits[t], K)
+        want = oracle.ffn((enc.Q4_K, EXPERTS, 2 * FF, HIDDEN, gate_up), (enc.Q8_0, EXPERTS, HIDDEN, FF, down), x[t], idx, w, down_scale=scales)
+        bound = 2e-5 * (1 + np.max(np.abs(want)))
+        assert np.max(np.abs(got[t] - want)) <= bound, (t, np.max(np.abs(got[t] - want)), bound)
+    with pytest.raises(NuclisError):  # the shape rules of matmul: rows % 8, columns % 64
+        backend.begin()
+        try:
+            backend.matmul_experts(gub, ExpertMatrix(enc.Q4_K, EXPERTS, 2 * FF, HIDDEN, gate_up.size), lists, tokens, K, xb, HIDDEN - 4, K, gu_out, 2 * FF)
+        finally:
+            backend.discard()
+    backend.unwrap(gate_up); backend.unwrap(down)
+    for buf in (xb, lb, sb, ib, wb, lists, gu_out, hid, y, out):
+        backend.release(buf)
+
+
 def test_gathered_matvec_reads_only_selected_experts(backend):
     # unselected experts hold NaN-decoding bytes (scale 0x7e00): a stray read poisons the output
     experts, rows, cols = 6, 32, 256
