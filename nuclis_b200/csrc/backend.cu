@@ -14,6 +14,8 @@
 
 namespace nu {
 
+struct FastJobBox { FastJob job; };
+
 namespace {
 
 constexpr size_t kPad = 256;                       // slack after every allocation: bulk copies may read up to 15 bytes past a row
@@ -90,6 +92,7 @@ Backend::~Backend() {
     for (auto &g : graphs_) cudaGraphExecDestroy(g.second);
     for (auto &a : buffers_) if (a.ptr) cudaFree(a.ptr);
     for (auto &ev : profile_events_) cudaEventDestroy(ev);
+    delete pending_job_;
     if (inbox_) cudaFree(inbox_);
     if (partials_) cudaFree(partials_);
     if (counters_) cudaFree(counters_);
@@ -238,7 +241,16 @@ int Backend::begin() {
 int Backend::needRecording() {
     if (!recording_) return fail(NU_ERR_NOT_RECORDING, "no recording is open (call begin first)");
     cudaSetDevice(device_);
-    return NU_OK;
+    return flushPending();  // every operator but the allreduce that may fuse with it launches a held-back matvec first
+}
+
+// Launches the matvec that was held back to see whether an allreduce of its output follows.
+int Backend::flushPending() {
+    if (!pending_) return NU_OK;
+    pending_ = false;
+    launches_ += launch_fast(stream_, pending_job_->job);
+    opBoundary();
+    return cuda(cudaGetLastError(), "matvec: launch");
 }
 
 // Buffers an operator of the open recording has written. A decode kernel starts reading its
@@ -299,6 +311,7 @@ int Backend::runGraph(cudaGraphExec_t exec, uint32_t count, float *elapsed_ms) {
 int Backend::commit() {
     if (!recording_) return fail(NU_ERR_NOT_RECORDING, "commit: no recording is open");
     cudaSetDevice(device_);
+    if (int rc = flushPending()) return rc;
     if (profiling_) {
         recording_ = false;
         if (int rc = cuda(cudaStreamSynchronize(stream_), "commit: wait")) return rc;
@@ -323,6 +336,7 @@ int Backend::commitRetain(uint32_t *graph) {
     if (!recording_) return fail(NU_ERR_NOT_RECORDING, "commit_retain: no recording is open");
     if (profiling_) return fail(NU_ERR_INVALID_SHAPE, "commit_retain: not available while profiling");
     cudaSetDevice(device_);
+    if (int rc = flushPending()) return rc;
     cudaGraphExec_t exec = nullptr;
     if (int rc = finishCapture(&exec)) return rc;
     if (int rc = runGraph(exec, 1, nullptr)) { cudaGraphExecDestroy(exec); return rc; }
@@ -351,6 +365,7 @@ int Backend::discard() {
     if (!recording_) return NU_OK;
     cudaSetDevice(device_);
     recording_ = false;
+    pending_ = false;
     if (profiling_) {
         // Profiling runs operators as they are recorded; there is nothing left to drop.
         cudaStreamSynchronize(stream_);
@@ -418,8 +433,20 @@ int Backend::matvec(const Buffer &weights, const Matrix &m, const Buffer &input,
     job.count = 1; job.mode = ACT_NONE;
     job.seg[0] = {w, stride, (uint32_t)m.rows, out, m.rows};
     job.serial = written(weights); job.partials = partials_; job.partials_floats = partials_floats_; job.counters = counters_; job.counters_len = counters_len_; job.sm_count = sm_count_;
-    if (!generic_only && fast_supported(job)) launches_ += launch_fast(stream_, job);
-    else launches_ += launch_matmul_generic(stream_, m.encoding, m.layout, w, stride, (uint32_t)m.rows, (uint32_t)m.columns, in, false, m.columns, out, m.rows, 1);
+    if (!generic_only && fast_supported(job)) {
+        if (peers_attached_ && !profiling_ && m.rows <= kPushCapacity) {
+            // held back: an allreduce of this output may follow and fuse with it (allreduceSumF32)
+            if (!pending_job_) pending_job_ = new FastJobBox;
+            pending_job_->job = job;
+            pending_out_ = output;
+            pending_ = true;
+            wrote(output);
+            return NU_OK;
+        }
+        launches_ += launch_fast(stream_, job);
+    } else {
+        launches_ += launch_matmul_generic(stream_, m.encoding, m.layout, w, stride, (uint32_t)m.rows, (uint32_t)m.columns, in, false, m.columns, out, m.rows, 1);
+    }
     wrote(output);
     opBoundary();
     return cuda(cudaGetLastError(), "matvec: launch");
@@ -843,12 +870,32 @@ int Backend::allreduceSumF32(const Buffer &buffer, size_t count) {
     float *p = (float *)resolve(buffer, count * 4);
     if (!p || buffer.offset % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "allreduce: buffer too short");
     if (peers_attached_ && count <= kPushCapacity) {
-        if (int rc = needRecording()) return rc;
+        // A one-token matvec whose whole output is this vector was held back: it becomes one kernel that
+        // computes and pushes its rows into every rank's inbox, and the sum only gathers.
+        const bool fuse = recording_ && pending_ && pending_out_.id == buffer.id && pending_out_.offset == buffer.offset &&
+                          pending_job_->job.seg[0].rows == count;
         PushParams pp{};
         pp.buf = p; pp.count = (uint32_t)count; pp.ranks = (uint32_t)peer_ranks_; pp.rank = (uint32_t)peer_rank_; pp.capacity = (uint32_t)kPushCapacity;
         for (int r = 0; r < peer_ranks_; ++r) pp.inbox[r] = (uint2 *)peer_base_[r];
         pp.seq = (uint32_t *)(inbox_ + kPushWordBytes);
         pp.status = counters_ + counters_len_;
+        if (fuse) {
+            cudaSetDevice(device_);
+            FastJob &job = pending_job_->job;
+            job.push.ranks = pp.ranks; job.push.rank = pp.rank; job.push.capacity = pp.capacity; job.push.seq = pp.seq;
+            for (int r = 0; r < peer_ranks_; ++r) job.push.inbox[r] = pp.inbox[r];
+            if (fast_supported(job)) {
+                pending_ = false;
+                launches_ += launch_fast(stream_, job);
+                opBoundary();
+                launches_ += launch_gather_sum(stream_, pp);
+                wrote(buffer);
+                opBoundary();
+                return cuda(cudaGetLastError(), "allreduce: launch");
+            }
+            job.push.ranks = 0;
+        }
+        if (int rc = needRecording()) return rc;
         launches_ += launch_push_allreduce(stream_, pp);
         wrote(buffer);
         opBoundary();

@@ -21,6 +21,7 @@
 namespace nu {
 
 struct FastJob;
+struct FastJobBox;
 
 using Buffer = nu_buffer;
 using Matrix = nu_matrix;
@@ -110,6 +111,7 @@ private:
     int finishCapture(cudaGraphExec_t *exec);
     int runGraph(cudaGraphExec_t exec, uint32_t count, float *elapsed_ms);
     int checkKernelStatus();
+    int flushPending();
     bool decodePasses(FastJob job, const float *in, size_t in_stride, float *out, size_t out_stride, uint32_t tokens);
 
     int device_ = 0;
@@ -144,6 +146,10 @@ private:
     uint8_t *inbox_ = nullptr;
     void *peer_base_[8] = {};
     bool peers_attached_ = false;
+    // a one-token plain matvec held back for one operator: if an allreduce of its output follows, the two are fused
+    bool pending_ = false;
+    FastJobBox *pending_job_ = nullptr;
+    Buffer pending_out_{};
     int peer_ranks_ = 0, peer_rank_ = 0;
 };
 

@@ -46,6 +46,7 @@ struct Params {
     float *partials;         // [slice][unit][32]
     uint32_t *counters;      // per unit
     uint32_t *status;        // set to 1 if a bounded wait ran out
+    PushTarget push;         // ranks > 0: output rows go to the ranks' inboxes instead of `out`
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -107,12 +108,29 @@ __device__ __forceinline__ void named_barrier(uint32_t id, uint32_t threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+__device__ __forceinline__ void push_word(uint2 *dst, float v, uint32_t tag) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+}
+
 // Writes the finished sums of rows g and g+8 of a unit: v = plain sums (pair mode: gate), w = up sums.
 __device__ __forceinline__ void write_unit(const Params &p, uint32_t unit, uint32_t g, float v0, float v1, float w0, float w1) {
     if (p.mode != ACT_NONE) {
         const uint32_t row = unit * 16 + g;
         if (row < p.rows[0]) p.out[0][row] = (p.mode == ACT_SILU ? silu_f32(v0) : gelu_f32(v0)) * w0;
         if (row + 8 < p.rows[0]) p.out[0][row + 8] = (p.mode == ACT_SILU ? silu_f32(v1) : gelu_f32(v1)) * w1;
+    } else if (p.push.ranks) {
+        // fused with the allreduce that follows: the rows travel to every rank's inbox as (value, tag)
+        uint32_t seg, row0;
+        unit_rows(p, unit, seg, row0);
+        const uint32_t seq = *(volatile const uint32_t *)p.push.seq;
+        const uint32_t tag = seq + 1;
+        const size_t slot = ((size_t)(seq & 1u) * p.push.ranks + p.push.rank) * p.push.capacity;
+#pragma unroll 1
+        for (uint32_t r = 0; r < p.push.ranks; ++r) {
+            uint2 *dst = p.push.inbox[r] + slot + row0 + g;
+            if (row0 + g < p.rows[seg]) push_word(dst, v0, tag);
+            if (row0 + g + 8 < p.rows[seg]) push_word(dst + 8, v1, tag);
+        }
     } else {
         uint32_t seg, row0;
         unit_rows(p, unit, seg, row0);
@@ -388,7 +406,15 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
                     } else {
                         uint32_t seg, row0;
                         unit_rows(p, unit, seg, row0);
-                        if (row0 + lane < p.rows[seg]) p.out[seg][row0 + lane] = sum;
+                        if (row0 + lane < p.rows[seg]) {
+                            if (p.push.ranks) {
+                                const uint32_t seq = *(volatile const uint32_t *)p.push.seq;
+                                const size_t slot = ((size_t)(seq & 1u) * p.push.ranks + p.push.rank) * p.push.capacity;
+                                for (uint32_t r = 0; r < p.push.ranks; ++r) push_word(p.push.inbox[r] + slot + row0 + lane, sum, seq + 1);
+                            } else {
+                                p.out[seg][row0 + lane] = sum;
+                            }
+                        }
                     }
                 }
                 if (lane == 0) p.counters[unit] = 0;  // leave the scratch as it was found
@@ -507,6 +533,8 @@ static bool fill_common(const FastJob &job, Params &p) {
     p.partials = job.partials;
     p.counters = job.counters;
     p.status = job.counters + job.counters_len;
+    p.push = job.push;
+    if (p.push.ranks && (job.mode != ACT_NONE || job.count != 1)) return false;  // one plain matrix only
     if (p.nks > 1) {
         if ((size_t)p.nks * units * 32 > job.partials_floats) return false;
         if (units > job.counters_len) return false;

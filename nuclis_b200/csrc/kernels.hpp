@@ -44,6 +44,14 @@ int launch_combine_experts(cudaStream_t s, const float *values, const float *wei
 
 // ---- fused dequant tensor-core GEMV / small-M GEMM (1..8 token rows) ------
 
+// Where a one-token GEMV sends its output rows when an allreduce over peer memory follows it: slot
+// [parity][rank] of every rank's inbox (push_allreduce.cu), as (value, tag) words.
+struct PushTarget {
+    uint2 *inbox[8];
+    uint32_t ranks, rank;   // ranks == 0: no push, the output goes to `out`
+    uint32_t capacity;      // words per inbox slot
+    const uint32_t *seq;    // the allreduce's sequence number in this rank's memory
+};
 struct FastSegment {
     const uint8_t *w;  // first row of the (expert's) matrix
     size_t stride;     // bytes per weight row
@@ -69,6 +77,7 @@ struct FastJob {
     size_t counters_len;
     int sm_count;
     bool serial;  // a weights buffer was written earlier in the same recording: no early start of the weight stream
+    PushTarget push;
 };
 // Opts every variant into its dynamic shared memory size; once per device, outside any capture.
 bool fast_configure();
@@ -131,6 +140,8 @@ struct PushParams {
     uint32_t *status;
 };
 int launch_push_allreduce(cudaStream_t s, const PushParams &p);
+// The second half alone: the vector was already pushed (by the GEMV that produced it) into every inbox, this rank's included.
+int launch_gather_sum(cudaStream_t s, const PushParams &p);
 
 // ---- planar re-layout of a matrix for the specialized kernels ---------------------
 // Layout the matrix takes after preparation: 0 when the specialized kernels read the GGUF rows as they are.

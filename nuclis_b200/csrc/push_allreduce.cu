@@ -43,6 +43,7 @@ __device__ __forceinline__ uint4 load_words(const uint4 *src) {
     return v;
 }
 
+template <bool PUSH>
 __global__ void __launch_bounds__(256) push_allreduce_kernel(PushParams p) {
     // The kernel after this one may start its prologue now; this one reads the vector only after
     // the kernel before it has ended.
@@ -64,8 +65,8 @@ __global__ void __launch_bounds__(256) push_allreduce_kernel(PushParams p) {
     const uint32_t parity = seq & 1u, tag = seq + 1;
     const uint32_t pairs = (p.count + 1) / 2;  // a thread moves two elements: one 16-byte word pair
     const uint32_t first = blockIdx.x * blockDim.x + tid, step = gridDim.x * blockDim.x;
-    // ---- 1. push ----
-    for (uint32_t i = first; i < pairs; i += step) {
+    // ---- 1. push (not when the producer of the vector pushed it already, into this rank's inbox too) ----
+    for (uint32_t i = first; PUSH && i < pairs; i += step) {
         const float a = p.buf[2 * i], b = 2 * i + 1 < p.count ? p.buf[2 * i + 1] : 0.0f;
         const uint4 w = make_uint4(__float_as_uint(a), tag, __float_as_uint(b), tag);
         for (uint32_t r = 0; r < p.ranks; ++r)
@@ -78,20 +79,21 @@ __global__ void __launch_bounds__(256) push_allreduce_kernel(PushParams p) {
         float s0 = 0.0f, s1 = 0.0f;
         for (uint32_t r = 0; r < p.ranks; ++r) {
             float a, b;
-            if (r == p.rank) {
+            if (PUSH && r == p.rank) {
                 a = p.buf[2 * i];
                 b = 2 * i + 1 < p.count ? p.buf[2 * i + 1] : 0.0f;
             } else {
                 const uint4 *src = (const uint4 *)(p.inbox[p.rank] + ((size_t)parity * p.ranks + r) * p.capacity) + i;
+                const bool both = 2 * i + 1 < p.count;  // the last word pair of an odd count has one element
                 uint4 w = load_words(src);
                 uint32_t n = 0;
-                while ((w.y != tag || w.w != tag) && ++n < kPushSpinLimit) {
+                while ((w.y != tag || (both && w.w != tag)) && ++n < kPushSpinLimit) {
                     if ((n & 255u) == 0 && global_ns() - t0 > kPushWaitNs) break;
                     w = load_words(src);
                 }
-                if (w.y != tag || w.w != tag) { failed = true; break; }
+                if (w.y != tag || (both && w.w != tag)) { failed = true; break; }
                 a = __uint_as_float(w.x);
-                b = __uint_as_float(w.z);
+                b = both ? __uint_as_float(w.z) : 0.0f;
             }
             if (r == 0) { s0 = a; s1 = b; }
             else { s0 += a; s1 += b; }
@@ -132,7 +134,25 @@ int launch_push_allreduce(cudaStream_t s, const PushParams &p) {
     cfg.stream = s;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaLaunchKernelEx(&cfg, push_allreduce_kernel, p);
+    cudaLaunchKernelEx(&cfg, push_allreduce_kernel<true>, p);
+    return 1;
+}
+
+int launch_gather_sum(cudaStream_t s, const PushParams &p) {
+    const uint32_t pairs = (p.count + 1) / 2;
+    uint32_t blocks = (pairs + 255) / 256;
+    if (blocks > PUSH_MAX_BLOCKS) blocks = PUSH_MAX_BLOCKS;
+    if (blocks == 0) blocks = 1;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = s;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, push_allreduce_kernel<false>, p);
     return 1;
 }
 
