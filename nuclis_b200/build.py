@@ -39,7 +39,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not stale():
         return LIB
     nvcc = os.environ.get("NVCC", "nvcc")
-    extra = os.environ.get("NUCLIS_NVCC_FLAGS", "").split()  # e.g. -DNU_FAST_WARPS=16 for tuning experiments
+    extra = os.environ.get("NUCLIS_NVCC_FLAGS", "").split()  # e.g. -DNU_DEC_WARPS=20 for tuning experiments
     objs = []
     procs = []
     os.makedirs(os.path.join(HERE, "build"), exist_ok=True)
