@@ -2,13 +2,14 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens M] [--impl reference]
 
-Workload (BASELINE.json config 2): the synthetic dense 27B-shape decode layer
+Workload (the benchmark's config 2): the synthetic dense 27B-shape decode layer
 stack, 64 layers of QKV (Q4_K) -> O (Q4_K) -> SiLU gate/up pair (Q4_K) -> down
 (Q6_K), hidden 5120, intermediate 17408, random-init weights drawn on the
 device, hidden state N(0,1). A step is one decode pass of all 64 layers for M
 tokens (M = 1: decode; M = 8: the speculative-verify batch). With N GPUs the
-layers are row-split over the ranks (strong scaling) with an NCCL allreduce
-after every O and down projection.
+layers are row-split over the ranks (strong scaling) with a sum over the ranks
+after every O and down projection (over NVLink peer memory, fused with the
+GEMV that produces the vector; ``--nccl-only`` uses NCCL instead).
 
 One JSON line is printed by rank 0:
   value     tokens per second, whole job, device-timed (CUDA events on the

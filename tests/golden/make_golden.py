@@ -2,7 +2,7 @@
 
 Run once where the reference tree is mounted:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path to the nuclis source tree>
 
 It reads inference/src/quant/fixtures/{k-affine,k-signed,simple}.json (the rows the
 reference's own tests require an exact match on, inference/src/quant/decode.zig:587-592),
@@ -46,4 +46,6 @@ def main(root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit(__doc__)
+    main(sys.argv[1])
