@@ -1,0 +1,170 @@
+"""GPU parity of the operators a decode layer is built from, at the shapes of the 27B-shape stack:
+merged projections (`matvecSegments`: plain, SiLU pair, GELU pair; inference/metal-check.zig:4596-4680
+checks the reference's merged matvec the same way), the verify batch on the planar forms at both
+config-1 shapes, and one whole layer (QKV -> O -> gate/up -> down) for one and eight tokens against
+the CPU oracle."""
+import numpy as np
+import pytest
+
+import oracle
+from nuclis_b200 import Backend, Matrix, NuclisError, Segment, SegmentMode, encoding as enc, synth
+from parity import assert_matvec_close, expect, make_case, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def backend():
+    b = Backend(0)
+    yield b
+    b.deinit()
+
+
+def upload(b, data):
+    buf = b.create(data.nbytes)
+    buf.write(data)
+    return buf
+
+
+def weights(b, encoding, rows, columns, seed, prepare):
+    """A matrix on the device (planar when `prepare`), its descriptor and its GGUF bytes on the host."""
+    w = synth.matrix(encoding, rows, columns, seed)
+    m = Matrix(encoding, rows, columns, w.size)
+    wb = upload(b, w)
+    if prepare:
+        pb, m = b.prepare(wb, m)
+        b.release(wb)
+        wb = pb
+    return wb, m, w
+
+
+@pytest.mark.parametrize("encoding,prepare", [(enc.Q4_K, False), (enc.Q6_K, True), (enc.Q8_0, True)])
+def test_plain_segments_share_one_input(backend, encoding, prepare):
+    b = backend
+    columns, rows = 1280, [512, 256, 272]
+    x = synth.activations(1, columns, 7)[0]
+    xb = upload(b, x)
+    segs, wants, bufs = [], [], [xb]
+    for i, r in enumerate(rows):
+        wb, m, w = weights(b, encoding, r, columns, 20 + i, prepare)
+        out = b.create(r * 4)
+        segs.append(Segment(wb, m, out))
+        wants.append((oracle.matvec(encoding, r, columns, w, x), oracle.matvec_abs(encoding, r, columns, w, x)))
+        bufs += [wb, out]
+    b.begin()
+    b.matvec_segments(segs, xb, SegmentMode.plain)
+    b.commit()
+    for seg, (want, mag) in zip(segs, wants):
+        assert_matvec_close(seg.output.floats()[: seg.matrix.rows], want, mag, f"segment of {seg.matrix.rows} rows, enc {encoding}")
+    for buf in bufs:
+        b.release(buf)
+
+
+@pytest.mark.parametrize("mode", [SegmentMode.silu_mul_pair, SegmentMode.gelu_mul_pair])
+@pytest.mark.parametrize("shape", [(1056, 1280), (17408, 5120)])
+def test_gate_up_pair_writes_the_activated_product(backend, mode, shape):
+    b = backend
+    rows, columns = shape
+    x = synth.activations(1, columns, 11)[0]
+    xb = upload(b, x)
+    gb, m, wg = weights(b, enc.Q4_K, rows, columns, 31, False)
+    ub, _, wu = weights(b, enc.Q4_K, rows, columns, 32, False)
+    out = b.create(rows * 4)
+    b.begin()
+    b.matvec_segments([Segment(gb, m, out), Segment(ub, m, out)], xb, mode)
+    b.commit()
+    g = oracle.matvec(enc.Q4_K, rows, columns, wg, x)
+    u = oracle.matvec(enc.Q4_K, rows, columns, wu, x)
+    act = oracle.silu(g) if mode == SegmentMode.silu_mul_pair else oracle.gelu(g)
+    want = act.astype(np.float64) * u.astype(np.float64)
+    got = out.floats()[:rows]
+    # the product of two sums each within the matvec bound: compare on the whole vector
+    assert rel_l2(got, want) <= 1e-5
+    for buf in (xb, gb, ub, out):
+        b.release(buf)
+
+
+def test_merge_is_declined_before_anything_is_recorded(backend):
+    b = backend
+    columns = 1280
+    xb = upload(b, synth.activations(1, columns, 3)[0])
+    a, ma, _ = weights(b, enc.Q4_K, 256, columns, 41, False)
+    c, mc, _ = weights(b, enc.Q6_K, 256, columns, 42, True)
+    o1, o2 = b.create(256 * 4), b.create(256 * 4)
+    b.begin()
+    try:
+        with pytest.raises(NuclisError) as e:
+            b.matvec_segments([Segment(a, ma, o1), Segment(c, mc, o2)], xb, SegmentMode.plain)  # two encodings
+        assert e.value.status == 5  # MergeDeclined: the caller falls back to separate matvecs
+        with pytest.raises(NuclisError):
+            b.matvec_segments([Segment(a, ma, o1), Segment(a, ma, o2)], xb, SegmentMode.silu_mul_pair)  # a pair names one output
+    finally:
+        b.discard()
+    for buf in (xb, a, c, o1, o2):
+        b.release(buf)
+
+
+@pytest.mark.parametrize("encoding", [enc.Q6_K, enc.Q8_0])
+@pytest.mark.parametrize("shape", [(17408, 5120), (5120, 17408)])
+@pytest.mark.parametrize("tokens", [2, 4, 8])
+def test_verify_batch_on_the_planar_forms(backend, encoding, shape, tokens):
+    b = backend
+    rows, columns = shape
+    w, x, m = make_case(encoding, rows, columns, tokens, seed=300 + tokens)
+    want, mag = expect(encoding, rows, columns, w, x)
+    wb = upload(b, w)
+    pb, pm = b.prepare(wb, m)
+    xb = upload(b, x)
+    yb = b.create(tokens * rows * 4)
+    b.begin()
+    b.matvec_rows(pb, pm, xb, columns, yb, rows, tokens)
+    b.commit()
+    assert_matvec_close(yb.floats().reshape(tokens, rows), want, mag, f"planar enc {encoding} {rows}x{columns} tokens {tokens}")
+    for buf in (wb, pb, xb, yb):
+        b.release(buf)
+
+
+@pytest.mark.parametrize("tokens", [1, 8])
+def test_one_layer_of_the_stack_matches_the_oracle(backend, tokens):
+    """QKV (three merged projections) -> O -> gate/up -> down at the 27B shapes, the way the benchmark records a layer."""
+    b = backend
+    hidden, kv, ffn = 5120, 1024, 17408
+    h = synth.activations(tokens, hidden, 5)
+    wq, mq, hq = weights(b, enc.Q4_K, hidden, hidden, 51, False)
+    wk, mk, hk = weights(b, enc.Q4_K, kv, hidden, 52, False)
+    wv, mv, hv = weights(b, enc.Q4_K, kv, hidden, 53, False)
+    wo, mo, ho = weights(b, enc.Q4_K, hidden, hidden, 54, False)
+    wg, mg, hg = weights(b, enc.Q4_K, ffn, hidden, 55, False)
+    wu, mu, hu = weights(b, enc.Q4_K, ffn, hidden, 56, False)
+    wd, md, hd = weights(b, enc.Q6_K, hidden, ffn, 57, True)
+    hb = upload(b, h)
+    q = b.create(tokens * hidden * 4); k = b.create(tokens * kv * 4); v = b.create(tokens * kv * 4)
+    o = b.create(tokens * hidden * 4); g = b.create(tokens * ffn * 4); u = b.create(tokens * ffn * 4); d = b.create(tokens * hidden * 4)
+    b.begin()
+    if tokens == 1:
+        b.matvec_segments([Segment(wq, mq, q), Segment(wk, mk, k), Segment(wv, mv, v)], hb, SegmentMode.plain)
+        b.matvec(wo, mo, q, o)
+        b.matvec_segments([Segment(wg, mg, g), Segment(wu, mg, g)], o, SegmentMode.silu_mul_pair)
+        b.matvec(wd, md, g, d)
+    else:
+        b.matvec_rows(wq, mq, hb, hidden, q, hidden, tokens)
+        b.matvec_rows(wk, mk, hb, hidden, k, kv, tokens)
+        b.matvec_rows(wo, mo, q, hidden, o, hidden, tokens)
+        b.matvec_rows(wg, mg, o, hidden, g, ffn, tokens)
+        b.matvec_rows(wu, mu, o, hidden, u, ffn, tokens)
+        b.silu_mul(g, u, tokens * ffn)
+        b.matvec_rows(wd, md, g, ffn, d, hidden, tokens)
+    b.commit()
+    got = d.floats()[: tokens * hidden].reshape(tokens, hidden)
+    for t in range(tokens):
+        qq = oracle.matvec(enc.Q4_K, hidden, hidden, hq, h[t])
+        oo = oracle.matvec(enc.Q4_K, hidden, hidden, ho, qq)
+        act = (oracle.silu(oracle.matvec(enc.Q4_K, ffn, hidden, hg, oo)) * oracle.matvec(enc.Q4_K, ffn, hidden, hu, oo)).astype(np.float32)
+        want = oracle.matvec(enc.Q6_K, hidden, ffn, hd, act)
+        # four chained products: each within 1e-5, their errors add up
+        assert rel_l2(got[t], want) <= 4e-5, (t, rel_l2(got[t], want))
+    if tokens == 1:
+        assert_matvec_close(k.floats()[:kv], oracle.matvec(enc.Q4_K, kv, hidden, hk, h[0]), oracle.matvec_abs(enc.Q4_K, kv, hidden, hk, h[0]), "K rows")
+        assert_matvec_close(v.floats()[:kv], oracle.matvec(enc.Q4_K, kv, hidden, hv, h[0]), oracle.matvec_abs(enc.Q4_K, kv, hidden, hv, h[0]), "V rows")
+    for buf in (wq, wk, wv, wo, wg, wu, wd, hb, q, k, v, o, g, u, d):
+        b.release(buf)
