@@ -283,6 +283,17 @@ int Backend::finishCapture(cudaGraphExec_t *exec) {
     return cuda(e, "commit: instantiate");
 }
 
+#ifdef NU_DEC_TRACE
+int Backend::debugTrace(unsigned long long *out, size_t words, int reset) {
+    cudaSetDevice(device_);
+    cudaStreamSynchronize(stream_);
+    unsigned long long *log = (unsigned long long *)(partials_ + (3u << 20));
+    if (out && words) cudaMemcpy(out, log, words * 8, cudaMemcpyDeviceToHost);
+    if (reset) cudaMemset(log, 0, 8 * (8 + 4000 * 8));
+    return NU_OK;
+}
+#endif
+
 int Backend::checkKernelStatus() {
     uint32_t status = 0;
     if (int rc = cuda(cudaMemcpyAsync(&status, counters_ + counters_len_, sizeof status, cudaMemcpyDeviceToHost, stream_), "status read")) return rc;
@@ -1089,6 +1100,13 @@ int nu_cuda_combine_experts(nu_cuda *h, const nu_buffer *values, const nu_buffer
 int nu_cuda_comm_unique_id(uint8_t id[NU_COMM_ID_BYTES]) { return id ? nu::unique_id(id) : NU_ERR_INVALID_SHAPE; }
 int nu_cuda_comm_init(nu_cuda *h, const uint8_t id[NU_COMM_ID_BYTES], int ranks, int rank) { NU_H(h); return h->b->commInit(id, ranks, rank); }
 int nu_cuda_allreduce_sum_f32(nu_cuda *h, const nu_buffer *buffer, size_t count) { NU_H(h); NU_P(buffer); return h->b->allreduceSumF32(*buffer, count); }
+#ifdef NU_DEC_TRACE
+// Trace builds only: the log the decode kernels append to (count word, then 8-word entries).
+extern "C" int nu_cuda_debug_trace(nu_cuda *h, unsigned long long *out, size_t words, int reset) {
+    NU_H(h);
+    return h->b->debugTrace(out, words, reset);
+}
+#endif
 int nu_cuda_comm_destroy(nu_cuda *h) { NU_H(h); return h->b->commDestroy(); }
 int nu_cuda_comm_peer_handle(nu_cuda *h, uint8_t handle[NU_PEER_HANDLE_BYTES]) { NU_H(h); return h->b->peerHandle(handle); }
 int nu_cuda_comm_attach_peers(nu_cuda *h, const uint8_t *handles, int ranks, int rank) { NU_H(h); return h->b->attachPeers(handles, ranks, rank); }

@@ -196,8 +196,12 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
     while (ks + 1 < p.nks && blockIdx.x >= p.blk_first[ks + 1]) ++ks;
     const uint32_t sb0 = ks * p.ksl, n = min(p.ksl, p.ksb - sb0);
     const uint32_t nblk = p.blk_first[ks + 1] - p.blk_first[ks], jblk = blockIdx.x - p.blk_first[ks];
-    const uint32_t u_lo = (uint32_t)((unsigned long long)p.units * jblk / nblk);
-    const uint32_t u_hi = (uint32_t)((unsigned long long)p.units * (jblk + 1) / nblk);
+    // The first blocks of a slice take the units that do not divide evenly: blocks are dispatched in index
+    // order onto the SMs as the kernel before frees them, so the SMs that were done early (the light ones
+    // of that kernel) get the heavy blocks of this one, and the block that starts last has the least to do.
+    const uint32_t per_blk = p.units / nblk, extra = p.units - per_blk * nblk;
+    const uint32_t u_lo = jblk * per_blk + min(jblk, extra);
+    const uint32_t u_hi = u_lo + per_blk + (jblk < extra ? 1u : 0u);
     const uint32_t np = min((uint32_t)PARTS, n);                          // warps that share a unit
     const uint32_t m = part < n ? (n - part + PARTS - 1) / PARTS : 0;     // this warp's superblocks per unit
     const uint32_t first_unit = u_lo + slot;
@@ -423,9 +427,16 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
     }
     NU_TRACE(4);
 #ifdef NU_DEC_TRACE
-    if (lane == 0 && (warp == 0 || warp == 7) && (blockIdx.x == 0 || blockIdx.x == gridDim.x / 2 || blockIdx.x == gridDim.x - 1))
-        printf("TR block %u/%u warp %u ks %u n %u units %u..%u mine %u m %u: waited %llu staged %llu loop %llu end %llu\n", blockIdx.x, gridDim.x, warp, ks, n, u_lo, u_hi, my_units,
-               m, tr[1] - tr[0], tr[2] - tr[0], tr[3] - tr[0], tr[4] - tr[0]);
+    // absolute stamps of warp 0 of three blocks, appended to a log at the far end of the partial-sum scratch
+    if (lane == 0 && warp == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x / 2 || blockIdx.x == gridDim.x - 1)) {
+        unsigned long long *log = (unsigned long long *)(p.partials + (3u << 20));
+        const unsigned long long slot = atomicAdd(log, 1ull);
+        if (slot < 4000) {
+            unsigned long long *e = log + 8 + slot * 8;
+            e[0] = ((unsigned long long)p.units << 32) | blockIdx.x;
+            e[1] = tr[0]; e[2] = tr[1]; e[3] = tr[2]; e[4] = tr[3]; e[5] = tr[4];
+        }
+    }
 #endif
     if (failed) {
         if (lane == 0) atomicExch(p.status, 1u);

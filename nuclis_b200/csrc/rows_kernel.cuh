@@ -150,8 +150,10 @@ __global__ void __launch_bounds__(THREADS, 1) rows_kernel(const __grid_constant_
     while (ks + 1 < p.nks && blockIdx.x >= p.blk_first[ks + 1]) ++ks;
     const uint32_t sb0 = ks * p.ksl, n = min(p.ksl, p.ksb - sb0);
     const uint32_t nblk = p.blk_first[ks + 1] - p.blk_first[ks], jblk = blockIdx.x - p.blk_first[ks];
-    const uint32_t tile_lo = (uint32_t)((unsigned long long)p.total_tiles * jblk / nblk);
-    const uint32_t tile_hi = (uint32_t)((unsigned long long)p.total_tiles * (jblk + 1) / nblk);
+    // the first blocks of a slice take the tiles that do not divide evenly (see decode_kernel.cuh)
+    const uint32_t per_blk = p.total_tiles / nblk, extra = p.total_tiles - per_blk * nblk;
+    const uint32_t tile_lo = jblk * per_blk + min(jblk, extra);
+    const uint32_t tile_hi = tile_lo + per_blk + (jblk < extra ? 1u : 0u);
     const uint32_t np = min((uint32_t)PARTS, n);                 // warps that share a unit
     const uint32_t m = part < n ? (n - part + PARTS - 1) / PARTS : 0;  // this warp's tasks per unit
     const uint32_t first_tile = tile_lo + slot;
