@@ -22,7 +22,7 @@ namespace dec {
 #define NU_DEC_WARPS 16
 #endif
 #ifndef NU_DEC_PRE
-#define NU_DEC_PRE 8
+#define NU_DEC_PRE 3
 #endif
 constexpr int WARPS = NU_DEC_WARPS;
 constexpr int THREADS = WARPS * 32;
@@ -228,7 +228,10 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
             else if (issued < total) unit_rows(p, p_unit, p_seg, p_row0);
         }
     };
-    for (int i = 0; i < STAGES - 1; ++i)
+    // A part of the ring is requested before the wait (it streams under the tail of the kernel before),
+    // the rest after the activation loads have left, so that those do not queue behind the whole ring.
+    constexpr int PRE = NU_DEC_PRE < STAGES - 1 ? NU_DEC_PRE : STAGES - 1;
+    for (int i = 0; i < PRE; ++i)
         if (issued < total) issue();
     for (uint32_t i = tid; i < p.ksl; i += THREADS) ready[i] = 0;
     if (tid < 32) ((uint32_t *)zero)[tid] = 0;
@@ -251,6 +254,8 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
                 xb2[j] = ((const float4 *)p.in)[(sb0 + sb) * 64 + 32 + lane];
             }
         }
+        for (int i = PRE; i < STAGES - 1; ++i)
+            if (issued < total) issue();
 #pragma unroll
         for (int j = 0; j < SBW; ++j) {
             const uint32_t sb = warp + j * WARPS;
