@@ -18,16 +18,19 @@
 namespace nu {
 namespace dec {
 
-#ifndef NU_DEC_WARPS
-#define NU_DEC_WARPS 16
-#endif
 #ifndef NU_DEC_PRE
 #define NU_DEC_PRE 3
 #endif
-constexpr int WARPS = NU_DEC_WARPS;
-constexpr int THREADS = WARPS * 32;
-constexpr int SLOTS = WARPS / 4;   // units in work at once
-constexpr int PARTS = 4;           // warps sharing a unit's superblocks
+// A block's warps are unit slots x K parts. Plain GEMVs run 20 warps as 4 slots x 5 parts (a 20-superblock
+// row is 4 tasks per warp and unit; measured 5 to 10 % faster alone than 16 warps); gate/up pairs measured
+// better with 16 warps as 4 x 4 and a deeper ring.
+template <int W, int P>
+struct Geometry {
+    static constexpr int WARPS = W, PARTS = P, SLOTS = W / P, THREADS = W * 32;
+    static_assert(W % P == 0 && W <= 32 && W / P <= 8, "warps are unit slots x K parts; a named barrier per slot");
+};
+using Plain = Geometry<20, 5>;
+using Pairs = Geometry<16, 4>;
 constexpr int PAIR_PITCH = 136;    // bytes per 64 staged activations (128 of halves + 8 of bank skew)
 constexpr int MAX_SLICES = 32;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
@@ -141,13 +144,14 @@ __device__ __forceinline__ void write_unit(const Params &p, uint32_t unit, uint3
 
 // Work split. K is cut into `nks` slices and every slice owns a range of blocks (sized by the host
 // so that all blocks finish together); the blocks of a slice split its units evenly, so a block
-// stages the activations of one slice only. A block's 16 warps are 4 unit slots x 4 K parts: warp
-// (slot, part) takes units first + slot, + 4, ... of the block and in each the superblocks part,
-// part + 4, ... of the slice. The four warps of a slot meet at a named barrier of their own after
+// stages the activations of one slice only. A block's warps are unit slots x K parts (4 x 4 or 4 x 5): warp
+// (slot, part) takes units first + slot, + SLOTS, ... of the block and in each the superblocks part,
+// part + PARTS, ... of the slice. The warps of a slot meet at a named barrier of their own after
 // each unit and the first adds the parts in order; there is no block-wide barrier after staging.
-template <class E, int STAGES>
-__global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constant__ Params p) {
+template <class E, class G, int STAGES>
+__global__ void __launch_bounds__(G::THREADS, 1) decode_kernel(const __grid_constant__ Params p) {
     constexpr int TASK_BYTES = E::TASK_BYTES;
+    constexpr int WARPS = G::WARPS, THREADS = G::THREADS, SLOTS = G::SLOTS, PARTS = G::PARTS;
     extern __shared__ __align__(128) uint8_t smem[];
     // [task stages][hi pieces][lo pieces][128 B of zeros][group sums][per-superblock 1/scale][staged flags][part sums][barriers]
     // A piece array holds the slice's columns as halves, the 128 bytes of each group pair (64 columns) padded
@@ -162,12 +166,11 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
     float *gsum = (float *)(zero + 128);
     float *inv_sb = gsum + p.ksl * E::GSUMS;           // per superblock of the slice: 1 / its activation scale
     volatile uint32_t *ready = (volatile uint32_t *)(inv_sb + p.ksl);  // per superblock: staged
-    float *parts = (float *)(ready + p.ksl);           // SLOTS x 2 x 3 x 32 floats
-    uint64_t *bars = (uint64_t *)(parts + SLOTS * 2 * 3 * 32);
+    float *parts = (float *)(ready + p.ksl);           // SLOTS x 2 x (PARTS - 1) x 32 floats
+    uint64_t *bars = (uint64_t *)(parts + SLOTS * 2 * (PARTS - 1) * 32);
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t g = lane >> 2, t = lane & 3;
-    const uint32_t slot = warp >> 2, part = warp & 3;
-    static_assert(WARPS % 4 == 0 && WARPS <= 32, "warps are unit slots x four K parts");
+    const uint32_t slot = warp / PARTS, part = warp % PARTS;
     const uint8_t *my_stage = stages + warp * STAGES * TASK_BYTES;
     const uint32_t stage0 = smem_u32(my_stage), bar0 = smem_u32(bars + warp * STAGES);
 
@@ -240,7 +243,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
     NU_TRACE(1);
 
     // ---- stage the slice's activations, a superblock per warp at a time: scale, fp16 pieces, group sums ----
-    // Warp w stages superblocks w, w + 16, ... of the slice (two float4 per lane each), with the
+    // Warp w stages superblocks w, w + WARPS, ... of the slice (two float4 per lane each), with the
     // superblock's own power-of-two scale, and raises the superblock's flag; a task waits for the flag
     // of its superblock only, so the first tasks start while later superblocks are still being staged.
     {
@@ -352,7 +355,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
             }
         }
         // ---- the parts of the unit meet; part 0 adds them in part order ----
-        float *buf = parts + ((slot * 2 + (uidx & 1u)) * 3) * 32;
+        float *buf = parts + ((slot * 2 + (uidx & 1u)) * (PARTS - 1)) * 32;
         if (part > 0 && t == 0) {
             float *dst = buf + (part - 1) * 32;
             dst[g] = acc[0];
@@ -453,9 +456,10 @@ __global__ void __launch_bounds__(THREADS, 1) decode_kernel(const __grid_constan
     }
 }
 
-template <class E>
+template <class E, class G>
 static size_t smem_bytes(uint32_t ksl, int stages) {
-    return (size_t)WARPS * stages * E::TASK_BYTES + (size_t)(ksl * 4) * PAIR_PITCH * 2 + 512 + (size_t)ksl * E::GSUMS * 4 + (size_t)ksl * 8 + SLOTS * 2 * 3 * 32 * 4 + 128 +
+    constexpr int WARPS = G::WARPS, SLOTS = G::SLOTS, PARTS = G::PARTS;
+    return (size_t)WARPS * stages * E::TASK_BYTES + (size_t)(ksl * 4) * PAIR_PITCH * 2 + 512 + (size_t)ksl * E::GSUMS * 4 + (size_t)ksl * 8 + SLOTS * 2 * (PARTS - 1) * 32 * 4 + 128 +
            WARPS * stages * 8 + 128;
 }
 
@@ -467,25 +471,30 @@ constexpr size_t kSmemMax = 227 * 1024;
 constexpr uint32_t kMaxSliceSbs = 80;  // the staging pass keeps a slice of up to 20480 columns in registers
 
 // Deepest ring of task stages that fits beside the staged activations: the copies in flight hide HBM latency.
-template <class E>
+template <class E, class G>
 static int pick_stages(uint32_t ksl) {
     for (int st = 6; st >= 2; --st)
-        if (smem_bytes<E>(ksl, st) <= kSmemMax) return st;
+        if (smem_bytes<E, G>(ksl, st) <= kSmemMax) return st;
     return 0;
 }
 
-template <class E, int STAGES>
+template <class E, class G, int STAGES>
 static bool configure_one() {
-    return cudaFuncSetAttribute(decode_kernel<E, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax) == cudaSuccess;
+    return cudaFuncSetAttribute(decode_kernel<E, G, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax) == cudaSuccess;
+}
+template <class E, class G>
+static bool configure_geometry() {
+    return configure_one<E, G, 2>() && configure_one<E, G, 3>() && configure_one<E, G, 4>() && configure_one<E, G, 5>() && configure_one<E, G, 6>();
 }
 template <class E>
-static bool configure() { return configure_one<E, 2>() && configure_one<E, 3>() && configure_one<E, 4>() && configure_one<E, 5>() && configure_one<E, 6>(); }
+static bool configure() { return configure_geometry<E, Plain>() && configure_geometry<E, Pairs>(); }
 
 // Fills everything of Params that does not depend on the encoding's planes; the caller adds the tensor maps.
 // Picks the K slices and the blocks of each slice: every candidate slice length is costed in task
 // steps of the slowest block (units over unit slots, superblocks over K parts).
-template <class E>
-static bool fill_common(const FastJob &job, Params &p) {
+template <class E, class G>
+static bool fill_geometry(const FastJob &job, Params &p) {
+    constexpr int SLOTS = G::SLOTS, PARTS = G::PARTS;
     if (job.tokens != 1 || job.count < 1 || job.count > 4) return false;
     if (job.columns == 0 || job.columns % 256 != 0) return false;
     if ((uintptr_t)job.in % 16 != 0) return false;
@@ -517,7 +526,7 @@ static bool fill_common(const FastJob &job, Params &p) {
         if (forced_ksl && ksl != forced_ksl && forced_ksl <= p.ksb) continue;
         const uint32_t nks = (p.ksb + ksl - 1) / ksl;
         if (nks > MAX_SLICES || nks > sms) continue;
-        const int st = pick_stages<E>(ksl);
+        const int st = pick_stages<E, G>(ksl);
         if (st < 2) continue;
         auto cost = [&](uint32_t s, uint32_t b) {
             const uint32_t n = s + 1 == nks ? p.ksb - s * ksl : ksl;
@@ -564,30 +573,40 @@ inline bool overlap_launches() {
     return on;
 }
 
-template <class E>
-static int launch(cudaStream_t s, const FastJob &job, const Params &p) {
+template <class E, class G>
+static int launch_geometry(cudaStream_t s, const FastJob &job, const Params &p) {
     const uint32_t grid = p.blk_first[p.nks];
-    const int stages = pick_stages<E>(p.ksl);
-    const size_t bytes = smem_bytes<E>(p.ksl, stages);
+    const int stages = pick_stages<E, G>(p.ksl);
+    const size_t bytes = smem_bytes<E, G>(p.ksl, stages);
     // launched so that it may overlap the tail of the kernel before it (see the kernel's prologue)
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(THREADS);
+    cfg.blockDim = dim3(G::THREADS);
     cfg.dynamicSmemBytes = bytes;
     cfg.stream = s;
     cfg.attrs = attr;
     cfg.numAttrs = overlap_launches() && !job.serial ? 1 : 0;
     switch (stages) {
-    case 6: cudaLaunchKernelEx(&cfg, decode_kernel<E, 6>, p); break;
-    case 5: cudaLaunchKernelEx(&cfg, decode_kernel<E, 5>, p); break;
-    case 4: cudaLaunchKernelEx(&cfg, decode_kernel<E, 4>, p); break;
-    case 3: cudaLaunchKernelEx(&cfg, decode_kernel<E, 3>, p); break;
-    default: cudaLaunchKernelEx(&cfg, decode_kernel<E, 2>, p); break;
+    case 6: cudaLaunchKernelEx(&cfg, decode_kernel<E, G, 6>, p); break;
+    case 5: cudaLaunchKernelEx(&cfg, decode_kernel<E, G, 5>, p); break;
+    case 4: cudaLaunchKernelEx(&cfg, decode_kernel<E, G, 4>, p); break;
+    case 3: cudaLaunchKernelEx(&cfg, decode_kernel<E, G, 3>, p); break;
+    default: cudaLaunchKernelEx(&cfg, decode_kernel<E, G, 2>, p); break;
     }
     return 1;
+}
+
+// The geometry follows the job: gate/up pairs on Pairs, everything else on Plain.
+template <class E>
+static bool fill_common(const FastJob &job, Params &p) {
+    return job.mode != ACT_NONE ? fill_geometry<E, Pairs>(job, p) : fill_geometry<E, Plain>(job, p);
+}
+template <class E>
+static int launch(cudaStream_t s, const FastJob &job, const Params &p) {
+    return job.mode != ACT_NONE ? launch_geometry<E, Pairs>(s, job, p) : launch_geometry<E, Plain>(s, job, p);
 }
 
 }  // namespace dec

@@ -6,8 +6,8 @@
 // The HBM stream is the only large traffic: every weight byte is read once.
 // A task is 16 weight rows by one superblock (2304 bytes); one TMA tensor copy
 // (cp.async.bulk.tensor.2d + mbarrier) brings it to shared memory, each warp
-// keeps its own ring of stages filled a few tasks ahead, and 16 warps per SM
-// keep about 100 KB of copies in flight. The lanes then read their 16-byte
+// keeps its own ring of stages filled a few tasks ahead, and the 16 or 20 warps
+// of an SM keep about 100 KB of copies in flight. The lanes then read their 16-byte
 // pieces with 128-bit shared loads (a quad of lanes reads the 128 contiguous
 // quant bytes of a superblock row).
 //
@@ -28,11 +28,12 @@
 //
 // Work split. K is cut into `nks` slices; a unit is a 16-row tile by one slice,
 // a task one superblock of a unit. Units are dealt to persistent blocks (one per
-// SM) in contiguous, slice-major ranges of equal task count. A block's 16 warps
-// are 4 unit slots x 4 K parts: in each step four units are in work, warp
-// (slot, part) takes superblocks part, part+4, ... of its unit, keeps the sums
-// in registers and leaves 16 row sums in a shared-memory slot. After a
-// block-wide barrier the four parts of a unit are added in part order. With
+// SM) in contiguous, slice-major ranges of equal task count. A block's warps
+// are 4 unit slots x P K parts (20 warps, P = 5; gate/up pairs 16 warps, P = 4):
+// in each step four units are in work, warp (slot, part) takes superblocks
+// part, part+P, ... of its unit, keeps the sums in registers and leaves 16 row
+// sums in a shared-memory slot. The warps of a slot meet at a named barrier of
+// their own and the parts of the unit are added in part order. With
 // several slices those sums go to a global scratch array and the last block to
 // arrive for a row tile adds them in slice order. No sum depends on timing.
 #include "decode_kernel.cuh"
