@@ -26,6 +26,13 @@ One JSON line is printed by rank 0:
   clocks    SM clock and throttle reasons sampled during the timed region.
 
 ``--impl reference`` times that CPU path alone on the same metric.
+
+``--workload experts`` times the mixture-of-experts decode chain instead (the
+benchmark's config 4: 128 experts, top-8, hidden 2816, expert width 704; router,
+Q4_K gate_up GEMV of the routed slots, GELU gate, Q8_0 down GEMV, weighted
+combine) for M = ``--tokens`` tokens on one GPU and prints one line of its own.
+Several chains with different router logits are recorded into the replayed
+graph, so that a replay touches more expert bytes than L2 holds.
 """
 from __future__ import annotations
 
@@ -269,6 +276,73 @@ def run_gpu(args, rank: int, world: int, local: int):
     b.deinit()
 
 
+def run_experts(args):
+    """Config 4 on one GPU: microseconds per expert chain and the bandwidth over the distinct experts' bytes."""
+    import oracle
+    from nuclis_b200 import Backend, CombineShape, ExpertMatrix, encoding as enc, synth
+    experts, k, hidden, ff = 128, 8, 2816, 704
+    tokens = args.tokens
+    chains = 16 if tokens == 1 else 6
+    b = Backend(0)
+    gate_up = synth.matrix(enc.Q4_K, experts * 2 * ff, hidden, seed=args.seed + 901)
+    down = synth.matrix(enc.Q8_0, experts * hidden, ff, seed=args.seed + 902)
+    gu_t = ExpertMatrix(enc.Q4_K, experts, 2 * ff, hidden, gate_up.size)
+    dn_t = ExpertMatrix(enc.Q8_0, experts, hidden, ff, down.size)
+    gub, dnb = b.wrap(gate_up), b.wrap(down)
+    rng = np.random.default_rng(args.seed)
+    slots = tokens * k
+    x = rng.standard_normal((tokens, hidden)).astype(np.float32)
+    xb = b.create(x.nbytes); xb.write(x)
+    ib = b.create(slots * 4); wb = b.create(slots * 4)
+    gu_out = b.create(slots * 2 * ff * 4); hid = b.create(slots * ff * 4)
+    y = b.create(slots * hidden * 4); out = b.create(tokens * hidden * 4)
+    distinct = 0
+    lbs = []
+    for c in range(chains):
+        logits = rng.standard_normal((tokens, experts)).astype(np.float32)
+        lb = b.create(logits.nbytes); lb.write(logits)
+        lbs.append(lb)
+        distinct += len({int(e) for t in range(tokens) for e in oracle.route(logits[t], k)[0]})
+    b.begin()
+    for lb in lbs:
+        b.route(lb, experts, k, tokens, experts, ib, wb)
+        b.matvec_experts_grouped(gub, gu_t, ib, slots, xb, hidden if tokens > 1 else 0, k if tokens > 1 else 1, gu_out, 2 * ff)
+        b.gelu_mul_rows(gu_out, gu_out.slice(ff * 4, gu_out.len - ff * 4), hid, ff, slots, 2 * ff, 2 * ff, ff)
+        b.matvec_experts(dnb, dn_t, ib, slots, hid, ff, y, hidden)
+        b.combine_experts(y, wb, ib, None, out, CombineShape(columns=hidden, slots=k, experts=experts, in_stride=hidden, out_stride=hidden, rows=tokens))
+    graph = b.commit_retain()
+    launches = b.launch_count
+    b.graph_launch(graph, max(args.warmup, 3))
+    us = b.graph_launch(graph, args.steps) / (args.steps * chains) * 1e3
+    # where a chain's time goes: the same operators once more with an event after each (adds the events' own cost)
+    names = ["route", "gate_up", "gelu_mul", "down", "combine"]
+    b.enable_profiling(len(names) * chains)
+    b.begin()
+    for lb in lbs:
+        b.route(lb, experts, k, tokens, experts, ib, wb)
+        b.matvec_experts_grouped(gub, gu_t, ib, slots, xb, hidden if tokens > 1 else 0, k if tokens > 1 else 1, gu_out, 2 * ff)
+        b.gelu_mul_rows(gu_out, gu_out.slice(ff * 4, gu_out.len - ff * 4), hid, ff, slots, 2 * ff, 2 * ff, ff)
+        b.matvec_experts(dnb, dn_t, ib, slots, hid, ff, y, hidden)
+        b.combine_experts(y, wb, ib, None, out, CombineShape(columns=hidden, slots=k, experts=experts, in_stride=hidden, out_stride=hidden, rows=tokens))
+    b.commit()
+    per_op = b.profile_read().reshape(chains, len(names))[1:].mean(axis=0) * 1e6
+    per_expert = gate_up.size // experts + down.size // experts
+    algo = distinct / chains * per_expert
+    peak, source = measured_peak()
+    print(json.dumps({
+        "metric": "config 4 expert decode chain", "value": us, "unit": "us per chain", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "higher_is_better": False, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "config 4: 128 experts, top-8, hidden 2816, width 704", "tokens": tokens, "chains_per_replay": chains,
+                   "l2": f"{distinct * per_expert / 1e6:.0f} MB of distinct expert bytes per replay, larger than L2",
+                   "kernels": "generic" if os.environ.get("NUCLIS_EXPERTS_GENERIC") == "1" else "specialized"},
+        "gpu_launches": launches * args.steps,
+        "per_operator_us": {n: round(float(v), 2) for n, v in zip(names, per_op)},
+        "roofline": {"bound": "hbm", "achieved": algo / (us * 1e-6) / 1e9, "peak": peak, "unit": "GB/s", "frac": algo / (us * 1e-6) / 1e9 / peak,
+                     "peak_source": source + " HBM copy bandwidth", "bytes_per_chain": algo, "traffic": None},
+    }), flush=True)
+    b.deinit()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -280,8 +354,14 @@ def main():
     ap.add_argument("--cpu-layers", type=int, default=192, help="layer passes timed on the CPU oracle for cpu_baseline (about 10 s)")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--nccl-only", action="store_true", help="sum the short vectors with NCCL instead of the peer-memory allreduce")
+    ap.add_argument("--workload", default="stack", choices=["stack", "experts"])
     args = ap.parse_args()
     rank, world, local = dist_env()
+    if args.workload == "experts":
+        if world > 1 or args.impl != "ours":
+            raise SystemExit("--workload experts runs on one GPU, this library only")
+        run_experts(args)
+        return
     if args.impl == "reference":
         if args.steps == 20:
             args.steps = 5

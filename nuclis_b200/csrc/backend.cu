@@ -680,8 +680,12 @@ int Backend::matvecExpertsGrouped(const Buffer &weights, const ExpertMatrix &t, 
     float *out = (float *)resolve(output, ((slots - 1) * out_stride + t.rows) * 4);
     if (!w || !idx || !in || !out || indices.offset % 4 != 0 || output.offset % 4 != 0 || input.offset % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "experts: buffer too short");
     if (int rc = needRecording()) return rc;
-    launches_ += launch_matvec_experts_generic(stream_, t.encoding, w, stride, per_expert, (uint32_t)t.experts, (uint32_t)t.rows, (uint32_t)t.columns,
-                                               idx, (uint32_t)slots, in, in_stride, (uint32_t)in_group, out, out_stride);
+    int launched = launch_matvec_experts_fast(stream_, t.encoding, w, stride, per_expert, (uint32_t)t.experts, (uint32_t)t.rows, (uint32_t)t.columns, idx,
+                                              (uint32_t)slots, in, in_stride, (uint32_t)in_group, out, out_stride);
+    if (!launched)
+        launched = launch_matvec_experts_generic(stream_, t.encoding, w, stride, per_expert, (uint32_t)t.experts, (uint32_t)t.rows, (uint32_t)t.columns,
+                                                 idx, (uint32_t)slots, in, in_stride, (uint32_t)in_group, out, out_stride);
+    launches_ += launched;
     wrote(output);
     opBoundary();
     return cuda(cudaGetLastError(), "experts: launch");

@@ -21,6 +21,10 @@ int launch_matmul_generic(cudaStream_t s, uint32_t enc, uint32_t layout, const u
                           const void *in, bool in_bf16, size_t in_stride, float *out, size_t out_stride, uint32_t tokens);
 
 // Gathered form: slot s uses matrix `indices[s]` (clamped) and input row s / in_group.
+// 0 when the shape is not one of the specialized forms (expert_gemv.cu); the caller then uses the generic kernel.
+int launch_matvec_experts_fast(cudaStream_t s, uint32_t enc, const uint8_t *w, size_t stride, size_t expert_bytes, uint32_t experts, uint32_t rows,
+                               uint32_t columns, const uint32_t *indices, uint32_t slots, const float *in, size_t in_stride, uint32_t in_group,
+                               float *out, size_t out_stride);
 int launch_matvec_experts_generic(cudaStream_t s, uint32_t enc, const uint8_t *w, size_t stride, size_t expert_bytes,
                                   uint32_t experts, uint32_t rows, uint32_t columns, const uint32_t *indices, uint32_t slots,
                                   const float *in, size_t in_stride, uint32_t in_group, float *out, size_t out_stride);

@@ -266,3 +266,38 @@ def test_gathered_matvec_reads_only_selected_experts(backend):
     backend.unwrap(data)
     for buf in (xb, ib, yb):
         backend.release(buf)
+
+
+@pytest.mark.parametrize("encoding,rows,cols", [(enc.Q4_K, 50, 768), (enc.Q4_K, 32, 256), (enc.Q8_0, 37, 96), (enc.Q8_0, 8, 704), (enc.Q6_K, 24, 512)])
+@pytest.mark.parametrize("in_group", [1, 3])
+def test_expert_gemv_ragged_shapes(backend, encoding, rows, cols, in_group):
+    """Row counts that do not fill a block, one to a few blocks per row, slots sharing an input row in groups
+    (ops/experts.zig:36-77: slot s reads input row s / in_group) — Q4_K and Q8_0 on the specialized kernels,
+    Q6_K on the generic one, each against the oracle's matvec of the selected expert."""
+    experts, slots = 5, 7
+    data = synth.matrix(encoding, experts * rows, cols, seed=40 + rows)
+    per = data.size // experts
+    t = ExpertMatrix(encoding, experts, rows, cols, data.size)
+    rng = np.random.default_rng(rows + cols + in_group)
+    groups = (slots + in_group - 1) // in_group
+    in_stride = cols + 8
+    x = rng.standard_normal((groups, in_stride)).astype(np.float32)
+    idx = rng.integers(0, experts, size=slots).astype(np.uint32)
+    out_stride = rows + 3
+    wb = backend.wrap(data)
+    xb = backend.create(x.nbytes); xb.write(x)
+    ib = backend.create(slots * 4); ib.write(idx)
+    yb = backend.create(slots * out_stride * 4)
+    backend.begin()
+    backend.matvec_experts_grouped(wb, t, ib, slots, xb, in_stride, in_group, yb, out_stride)
+    backend.commit()
+    got = yb.floats().reshape(slots, out_stride)[:, :rows]
+    for s in range(slots):
+        e = int(idx[s])
+        xs = x[s // in_group, :cols]
+        want = oracle.matvec(encoding, rows, cols, data[e * per:(e + 1) * per], xs)
+        scale = oracle.matvec_abs(encoding, rows, cols, data[e * per:(e + 1) * per], xs)
+        assert np.max(np.abs(got[s] - want) / np.maximum(scale, 1e-30)) <= 2e-6, (s, e)
+    backend.unwrap(data)
+    for buf in (xb, ib, yb):
+        backend.release(buf)
