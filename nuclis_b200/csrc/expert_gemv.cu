@@ -8,15 +8,24 @@
 //
 // The work is a few to a few hundred megabytes spread over up to 64 small matrices picked by
 // device-side indices, so the kernels use plain loads instead of tensor maps (an expert's address is
-// known only on the device) and aim at keeping enough 16-byte loads in flight:
+// known only on the device). A first version decoded every code to F32 (permute, subtract, FMA: six
+// instructions per weight and lane all told) and was bound by instruction issue at 2.1 TB/s. This
+// one keeps the codes as the bytes they are and multiplies them on the integer dot-product unit:
+//
+//  * The block turns its slot's input row into fixed point once: per chunk of columns (16 for Q4_K,
+//    32 for Q8_0) X = round(x * 2^k), k chosen from the chunk's largest exponent so that |X| < 2^20,
+//    split into three signed digits X = p2 * 2^14 + p1 * 2^7 + p0 with |p| <= 64, kept as three
+//    byte planes in shared memory. An element is off by at most 2^-21 of its chunk's largest value.
+//  * dp4a (four byte products added into an int32) then gives sum(code * p) exactly, for four
+//    weights per instruction and digit; the three digit sums are recombined in int32 (a digit sum is
+//    at most 16 * 15 * 64 for Q4_K and 8 * 128 * 64 = 2^16 for Q8_0, times 2^14: below 2^31),
+//    converted once and scaled by 2^-k and the block's scales in F32.
 //  * Q4_K: 8 lanes per weight row, 4 rows per warp, 32 rows per block. Lane p of a row takes the
 //    16-byte piece p of each superblock's 128 quant bytes: 16 low nibbles of group 2(p/2) and 16 high
-//    nibbles of group 2(p/2)+1, columns 16(p&1).. of each. Bytes become floats through the 2^23 magic
-//    number (one permute, one subtract), products accumulate in F32; the group's d*scale and dmin*min
-//    are applied once per piece, the minimum against a sum of x that the block prepares once per
-//    16 columns. The slot's input row is staged in shared memory once per block.
-//  * Q8_0: a warp per weight row; a lane takes 8-code quarters of the 34-byte blocks (2-byte aligned,
-//    so 16-bit loads), x comes through the read-only cache.
+//    nibbles of group 2(p/2)+1, columns 16(p&1).. of each; `w & 0x0f0f0f0f` is four codes ready for
+//    dp4a. The minima multiply exact F32 sums of x prepared once per chunk.
+//  * Q8_0: a warp per weight row, 8 rows per warp; a lane takes 8-code quarters of the 34-byte blocks
+//    (2-byte aligned, so 16-bit loads); the int8 codes go to dp4a as they are.
 // Sums run in a fixed order: results do not depend on timing.
 #include "kernels.hpp"
 #include "nu_device.cuh"
@@ -25,15 +34,23 @@ namespace nu {
 namespace {
 
 constexpr int XQ_THREADS = 256;
-constexpr int XQ_ROWS = 32;  // weight rows per block: 8 lanes each
+constexpr int XQ_ROWS = 32;  // Q4_K: weight rows per block, 8 lanes each
 
 __device__ __forceinline__ uint4 ldg_stream16(const void *p) {
     uint4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
-// byte b of w as a float: 0x4b0000bb is 2^23 + b
-__device__ __forceinline__ float byte_f32(uint32_t w, int b, float bias = 8388608.0f) { return __uint_as_float(__byte_perm(w, 0x4b000000u, 0x7650u + b)) - bias; }
+__device__ __forceinline__ int dp4a_us(uint32_t codes, uint32_t digits, int c) {  // unsigned codes x signed digits
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(codes), "r"(digits), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp4a_ss(uint32_t codes, uint32_t digits, int c) {  // signed codes x signed digits
+    int d;
+    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(codes), "r"(digits), "r"(c));
+    return d;
+}
 
 // 6-bit scale and minimum of group g of a Q4_K superblock; y, z, w are scale bytes 0..3, 4..7, 8..11.
 __device__ __forceinline__ void q4k_scale_min(uint32_t y, uint32_t z, uint32_t w, uint32_t g, float &s, float &m) {
@@ -48,85 +65,114 @@ __device__ __forceinline__ void q4k_scale_min(uint32_t y, uint32_t z, uint32_t w
     }
 }
 
-#ifndef NU_XQ_BATCH
-#define NU_XQ_BATCH 1
-#endif
-constexpr int XQ_BATCH = NU_XQ_BATCH;  // superblocks whose bytes a lane requests before it uses any
-
-// One piece (16 quant bytes, this lane's two half groups) of one superblock against the staged input.
-__device__ __forceinline__ float q4k_piece(const uint4 &hdr, const uint4 &q, const float *xs, const float *sums, uint32_t sb, uint32_t p) {
-    const uint32_t g_lo = 2 * (p >> 1), g_hi = g_lo + 1;
-    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
-    const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
-    float s_lo, m_lo, s_hi, m_hi;
-    q4k_scale_min(hdr.y, hdr.z, hdr.w, g_lo, s_lo, m_lo);
-    q4k_scale_min(hdr.y, hdr.z, hdr.w, g_hi, s_hi, m_hi);
-    const float *x_lo = xs + sb * 272 + (p >> 1) * 68 + (p & 1u) * 16, *x_hi = x_lo + 32;
-    float a_lo = 0.0f, a_hi = 0.0f;
-    const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const uint32_t lo = qw[i] & 0x0f0f0f0fu, hi = (qw[i] >> 4) & 0x0f0f0f0fu;
-        const float4 xl = *(const float4 *)(x_lo + 4 * i), xh = *(const float4 *)(x_hi + 4 * i);
-        a_lo = fmaf(byte_f32(lo, 0), xl.x, a_lo); a_lo = fmaf(byte_f32(lo, 1), xl.y, a_lo);
-        a_lo = fmaf(byte_f32(lo, 2), xl.z, a_lo); a_lo = fmaf(byte_f32(lo, 3), xl.w, a_lo);
-        a_hi = fmaf(byte_f32(hi, 0), xh.x, a_hi); a_hi = fmaf(byte_f32(hi, 1), xh.y, a_hi);
-        a_hi = fmaf(byte_f32(hi, 2), xh.z, a_hi); a_hi = fmaf(byte_f32(hi, 3), xh.w, a_hi);
-    }
-    const float sum_lo = sums[sb * 16 + g_lo * 2 + (p & 1u)], sum_hi = sums[sb * 16 + g_hi * 2 + (p & 1u)];
-    float acc = d * s_lo * a_lo;
-    acc = fmaf(d * s_hi, a_hi, acc);
-    acc = fmaf(-(dmin * m_lo), sum_lo, acc);
-    return fmaf(-(dmin * m_hi), sum_hi, acc);
+// Power of two that brings a chunk whose largest magnitude is `mx` below 2^20, and its inverse. A chunk that
+// is all zero (or too small to matter) is left as it is; one that holds an infinity or a NaN gets a NaN
+// inverse so that the row's result is NaN, as the F32 arithmetic would give.
+__device__ __forceinline__ void chunk_scale(float mx, float &scale, float &inv) {
+    const uint32_t e = (__float_as_uint(mx) >> 23) & 0xffu;
+    if (e == 255u) { scale = 0.0f; inv = __uint_as_float(0x7fc00000u); return; }
+    if (e < 40u) { scale = 1.0f; inv = 1.0f; return; }
+    scale = __uint_as_float((273u - e) << 23);  // 2^(146 - e): mx < 2^(e - 126) becomes < 2^20
+    inv = __uint_as_float((e - 19u) << 23);     // 2^(e - 146)
 }
+// Three signed digits of X = p2 * 2^14 + p1 * 2^7 + p0, |X| <= 2^20: p0, p1 in [-64, 63], p2 in [-64, 64].
+__device__ __forceinline__ void digits(float x, float scale, int &p0, int &p1, int &p2) {
+    const int X = __float2int_rn(x * scale);
+    p0 = ((X + 64) & 127) - 64;
+    const int X1 = (X - p0) >> 7;
+    p1 = ((X1 + 64) & 127) - 64;
+    p2 = (X1 - p1) >> 7;
+}
+// Byte planes are padded by 32 bytes per 128 so that the eight lanes of a weight row, which read 16-byte
+// chunks 0, 1, 4, 5, 8, 9, 12, 13 (or those + 2) of a superblock's 16, hit eight different groups of banks.
+__device__ __forceinline__ uint32_t plane_offset(uint32_t byte) { return byte + (byte >> 7) * 32; }
 
 __global__ void __launch_bounds__(XQ_THREADS) expert_gemv_q4k_kernel(const uint8_t *w, size_t stride, size_t expert_bytes, uint32_t experts, uint32_t rows,
                                                                      uint32_t ksb, const uint32_t *indices, const float *in, size_t in_stride,
                                                                      uint32_t in_group, float *out, size_t out_stride) {
-    // [ksb * 272] the slot's input row, every 64 columns followed by 4 floats of padding (the eight lanes of a
-    // weight row then read from eight different groups of banks), then [ksb * 16] sums of 16 columns
-    extern __shared__ __align__(16) float xs[];
-    float *sums = xs + ksb * 272;
+    // [3 planes of digits, ksb * 320 bytes each][ksb * 16 inverse scales][ksb * 16 sums of x]: one entry per 16 columns
+    extern __shared__ __align__(16) uint8_t smem[];
+    const uint32_t plane = ksb * 320;
+    float *inv_scale = (float *)(smem + 3 * plane);
+    float *sums = inv_scale + ksb * 16;
     // launched so that its blocks may be placed while the operator before it drains; nothing is read before this
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;");
     const uint32_t slot = blockIdx.y;
+    const float *x = in + (size_t)(slot / in_group) * in_stride;
+    for (uint32_t c = threadIdx.x; c < ksb * 16; c += XQ_THREADS) {
+        float v[16];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float4 f = __ldg((const float4 *)x + c * 4 + i);
+            v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+        }
+        float mx = 0.0f, bad = 0.0f;  // bad: 0 * x is NaN for an infinity or a NaN, which fmaxf would drop
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            mx = fmaxf(mx, fabsf(v[i]));
+            bad += 0.0f * v[i];
+        }
+        mx += bad;
+        float scale, inv;
+        chunk_scale(mx, scale, inv);
+        uint32_t d0[4], d1[4], d2[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            d0[i] = d1[i] = d2[i] = 0;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                int p0, p1, p2;
+                digits(v[4 * i + b], scale, p0, p1, p2);
+                d0[i] |= (uint32_t)(p0 & 0xff) << (8 * b);
+                d1[i] |= (uint32_t)(p1 & 0xff) << (8 * b);
+                d2[i] |= (uint32_t)(p2 & 0xff) << (8 * b);
+            }
+        }
+        const uint32_t off = plane_offset(c * 16);
+        *(uint4 *)(smem + off) = make_uint4(d0[0], d0[1], d0[2], d0[3]);
+        *(uint4 *)(smem + plane + off) = make_uint4(d1[0], d1[1], d1[2], d1[3]);
+        *(uint4 *)(smem + 2 * plane + off) = make_uint4(d2[0], d2[1], d2[2], d2[3]);
+        inv_scale[c] = inv;
+        sums[c] = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7])) + (((v[8] + v[9]) + (v[10] + v[11])) + ((v[12] + v[13]) + (v[14] + v[15])));
+    }
+    __syncthreads();
     const uint32_t r = blockIdx.x * XQ_ROWS + (threadIdx.x >> 3), p = threadIdx.x & 7;
     const bool live = r < rows;
     // A corrupt routing buffer can never read past the tensor (experts.metal:25).
     const uint32_t expert = min(indices[slot], experts - 1);
-    const uint8_t *row = w + (size_t)expert * expert_bytes + (size_t)(live ? r : 0) * stride;
-    // the first batch of weight bytes is requested before the input row is staged
-    uint4 hdr[XQ_BATCH], q[XQ_BATCH];
-#pragma unroll
-    for (int j = 0; j < XQ_BATCH; ++j)
-        if (live && (uint32_t)j < ksb) {
-            hdr[j] = ldg_stream16(row + (size_t)j * 144);
-            q[j] = ldg_stream16(row + (size_t)j * 144 + 16 + p * 16);
-        }
-    const float *x = in + (size_t)(slot / in_group) * in_stride;
-    for (uint32_t i = threadIdx.x; i < ksb * 64; i += XQ_THREADS) ((float4 *)xs)[i + (i >> 4)] = __ldg((const float4 *)x + i);
-    __syncthreads();
-    for (uint32_t i = threadIdx.x; i < ksb * 16; i += XQ_THREADS) {
-        const float4 *src = (const float4 *)xs + i * 4 + (i >> 2);
-        const float4 a = src[0], b = src[1], c = src[2], d = src[3];
-        sums[i] = ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w)) + (((c.x + c.y) + (c.z + c.w)) + ((d.x + d.y) + (d.z + d.w)));
-    }
-    __syncthreads();
     float acc = 0.0f;
     if (live) {
-        for (uint32_t sb0 = 0; sb0 < ksb; sb0 += XQ_BATCH) {
-            if (sb0) {
-#pragma unroll
-                for (int j = 0; j < XQ_BATCH; ++j)
-                    if (sb0 + j < ksb) {
-                        hdr[j] = ldg_stream16(row + (size_t)(sb0 + j) * 144);
-                        q[j] = ldg_stream16(row + (size_t)(sb0 + j) * 144 + 16 + p * 16);
-                    }
-            }
-#pragma unroll
-            for (int j = 0; j < XQ_BATCH; ++j)
-                if (sb0 + j < ksb) acc += q4k_piece(hdr[j], q[j], xs, sums, sb0 + j, p);
+        const uint8_t *row = w + (size_t)expert * expert_bytes + (size_t)r * stride;
+        const uint32_t g_lo = 2 * (p >> 1), g_hi = g_lo + 1;
+        const uint32_t c_lo = 4 * (p >> 1) + (p & 1u), c_hi = c_lo + 2;  // this lane's 16-column chunks of a superblock
+#pragma unroll 2
+        for (uint32_t sb = 0; sb < ksb; ++sb) {
+            const uint4 hdr = ldg_stream16(row + (size_t)sb * 144);
+            const uint4 q = ldg_stream16(row + (size_t)sb * 144 + 16 + p * 16);
+            const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
+            const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+            float s_lo, m_lo, s_hi, m_hi;
+            q4k_scale_min(hdr.y, hdr.z, hdr.w, g_lo, s_lo, m_lo);
+            q4k_scale_min(hdr.y, hdr.z, hdr.w, g_hi, s_hi, m_hi);
+            const uint32_t o_lo = plane_offset((sb * 16 + c_lo) * 16), o_hi = plane_offset((sb * 16 + c_hi) * 16);
+            const uint4 l0 = *(const uint4 *)(smem + o_lo), l1 = *(const uint4 *)(smem + plane + o_lo), l2 = *(const uint4 *)(smem + 2 * plane + o_lo);
+            const uint4 h0 = *(const uint4 *)(smem + o_hi), h1 = *(const uint4 *)(smem + plane + o_hi), h2 = *(const uint4 *)(smem + 2 * plane + o_hi);
+            const uint32_t ql[4] = {q.x & 0x0f0f0f0fu, q.y & 0x0f0f0f0fu, q.z & 0x0f0f0f0fu, q.w & 0x0f0f0f0fu};
+            const uint32_t qh[4] = {(q.x >> 4) & 0x0f0f0f0fu, (q.y >> 4) & 0x0f0f0f0fu, (q.z >> 4) & 0x0f0f0f0fu, (q.w >> 4) & 0x0f0f0f0fu};
+            int a0 = 0, a1 = 0, a2 = 0, b0 = 0, b1 = 0, b2 = 0;
+            a0 = dp4a_us(ql[0], l0.x, a0); a0 = dp4a_us(ql[1], l0.y, a0); a0 = dp4a_us(ql[2], l0.z, a0); a0 = dp4a_us(ql[3], l0.w, a0);
+            a1 = dp4a_us(ql[0], l1.x, a1); a1 = dp4a_us(ql[1], l1.y, a1); a1 = dp4a_us(ql[2], l1.z, a1); a1 = dp4a_us(ql[3], l1.w, a1);
+            a2 = dp4a_us(ql[0], l2.x, a2); a2 = dp4a_us(ql[1], l2.y, a2); a2 = dp4a_us(ql[2], l2.z, a2); a2 = dp4a_us(ql[3], l2.w, a2);
+            b0 = dp4a_us(qh[0], h0.x, b0); b0 = dp4a_us(qh[1], h0.y, b0); b0 = dp4a_us(qh[2], h0.z, b0); b0 = dp4a_us(qh[3], h0.w, b0);
+            b1 = dp4a_us(qh[0], h1.x, b1); b1 = dp4a_us(qh[1], h1.y, b1); b1 = dp4a_us(qh[2], h1.z, b1); b1 = dp4a_us(qh[3], h1.w, b1);
+            b2 = dp4a_us(qh[0], h2.x, b2); b2 = dp4a_us(qh[1], h2.y, b2); b2 = dp4a_us(qh[2], h2.z, b2); b2 = dp4a_us(qh[3], h2.w, b2);
+            const float f_lo = (float)(a2 * 16384 + a1 * 128 + a0) * inv_scale[sb * 16 + c_lo];
+            const float f_hi = (float)(b2 * 16384 + b1 * 128 + b0) * inv_scale[sb * 16 + c_hi];
+            acc = fmaf(d * s_lo, f_lo, acc);
+            acc = fmaf(d * s_hi, f_hi, acc);
+            acc = fmaf(-(dmin * m_lo), sums[sb * 16 + c_lo], acc);
+            acc = fmaf(-(dmin * m_hi), sums[sb * 16 + c_hi], acc);
         }
     }
     acc += __shfl_xor_sync(0xffffffffu, acc, 1);
@@ -135,59 +181,65 @@ __global__ void __launch_bounds__(XQ_THREADS) expert_gemv_q4k_kernel(const uint8
     if (p == 0 && live) out[(size_t)slot * out_stride + r] = acc;
 }
 
-constexpr int X8_WARPS = 8;  // weight rows per block
-#ifndef NU_X8_BATCH
-#define NU_X8_BATCH 1
-#endif
-constexpr int X8_BATCH = NU_X8_BATCH;  // quarters whose bytes a lane requests before it uses any (a 704-column row: 88 quarters, 3 per lane)
+constexpr int X8_WARPS = 8;
+constexpr int X8_ROWS = 64;  // Q8_0: weight rows per block, 8 per warp
 
 __global__ void __launch_bounds__(X8_WARPS * 32) expert_gemv_q8_0_kernel(const uint8_t *w, size_t stride, size_t expert_bytes, uint32_t experts, uint32_t rows,
                                                                          uint32_t blocks, const uint32_t *indices, const float *in, size_t in_stride,
                                                                          uint32_t in_group, float *out, size_t out_stride) {
+    // [3 planes of digits, blocks * 32 bytes each][blocks inverse scales]: one scale per 32-column block
+    extern __shared__ __align__(16) uint8_t smem[];
+    const uint32_t plane = blocks * 32;
+    float *inv_scale = (float *)(smem + 3 * plane);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;");
-    const uint32_t slot = blockIdx.y, lane = threadIdx.x & 31;
-    const uint32_t r = blockIdx.x * X8_WARPS + (threadIdx.x >> 5);
-    if (r >= rows) return;
-    const uint32_t expert = min(indices[slot], experts - 1);
-    const uint8_t *row = w + (size_t)expert * expert_bytes + (size_t)r * stride;
+    const uint32_t slot = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float *x = in + (size_t)(slot / in_group) * in_stride;
-    float acc = 0.0f;
-    // quarter qi of the row: block qi / 4, codes 8 (qi & 3) .. +7
-    for (uint32_t q0 = lane; q0 < blocks * 4; q0 += 32 * X8_BATCH) {
-        unsigned short dh[X8_BATCH], c[X8_BATCH][4];
-        float4 xa[X8_BATCH], xb[X8_BATCH];
+    // a warp per block of 32 columns, a lane per column
+    for (uint32_t b = warp; b < blocks; b += X8_WARPS) {
+        const float v = __ldg(x + b * 32 + lane);
+        float mx = fabsf(v), bad = 0.0f * v;  // bad: NaN for an infinity or a NaN, which fmaxf would drop
 #pragma unroll
-        for (int j = 0; j < X8_BATCH; ++j) {
-            const uint32_t qi = q0 + 32 * j;
-            if (qi < blocks * 4) {
-                const uint8_t *blk = row + (size_t)(qi >> 2) * 34;
-                const unsigned short *codes = (const unsigned short *)(blk + 2 + (qi & 3u) * 8);
-                dh[j] = __ldg((const unsigned short *)blk);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) c[j][i] = __ldg(codes + i);
-                const float *xp = x + (qi >> 2) * 32 + (qi & 3u) * 8;
-                xa[j] = __ldg((const float4 *)xp);
-                xb[j] = __ldg((const float4 *)xp + 1);
-            }
+        for (int o = 16; o > 0; o >>= 1) {
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            bad += __shfl_xor_sync(0xffffffffu, bad, o);
         }
-#pragma unroll
-        for (int j = 0; j < X8_BATCH; ++j) {
-            if (q0 + 32 * j < blocks * 4) {
-                const uint32_t w0 = ((uint32_t)c[j][0] | ((uint32_t)c[j][1] << 16)) ^ 0x80808080u;  // code + 128
-                const uint32_t w1 = ((uint32_t)c[j][2] | ((uint32_t)c[j][3] << 16)) ^ 0x80808080u;
-                float a = 0.0f;
-                a = fmaf(byte_f32(w0, 0, 8388736.0f), xa[j].x, a); a = fmaf(byte_f32(w0, 1, 8388736.0f), xa[j].y, a);
-                a = fmaf(byte_f32(w0, 2, 8388736.0f), xa[j].z, a); a = fmaf(byte_f32(w0, 3, 8388736.0f), xa[j].w, a);
-                a = fmaf(byte_f32(w1, 0, 8388736.0f), xb[j].x, a); a = fmaf(byte_f32(w1, 1, 8388736.0f), xb[j].y, a);
-                a = fmaf(byte_f32(w1, 2, 8388736.0f), xb[j].z, a); a = fmaf(byte_f32(w1, 3, 8388736.0f), xb[j].w, a);
-                acc = fmaf(__half2float(__ushort_as_half(dh[j])), a, acc);
-            }
-        }
+        mx += bad;
+        float scale, inv;
+        chunk_scale(mx, scale, inv);
+        int p0, p1, p2;
+        digits(v, scale, p0, p1, p2);
+        smem[b * 32 + lane] = (uint8_t)p0;
+        smem[plane + b * 32 + lane] = (uint8_t)p1;
+        smem[2 * plane + b * 32 + lane] = (uint8_t)p2;
+        if (lane == 0) inv_scale[b] = inv;
     }
+    __syncthreads();
+    const uint32_t expert = min(indices[slot], experts - 1);
+    const uint8_t *base = w + (size_t)expert * expert_bytes;
+    for (uint32_t k = 0; k < X8_ROWS / X8_WARPS; ++k) {
+        const uint32_t r = blockIdx.x * X8_ROWS + k * X8_WARPS + warp;
+        if (r >= rows) break;
+        const uint8_t *row = base + (size_t)r * stride;
+        float acc = 0.0f;
+        // quarter qi of the row: block qi / 4, codes 8 (qi & 3) .. +7
+        for (uint32_t qi = lane; qi < blocks * 4; qi += 32) {
+            const uint8_t *blk = row + (size_t)(qi >> 2) * 34;
+            const unsigned short *codes = (const unsigned short *)(blk + 2 + (qi & 3u) * 8);
+            const float d = __half2float(__ushort_as_half(__ldg((const unsigned short *)blk)));
+            const uint32_t w0 = (uint32_t)__ldg(codes) | ((uint32_t)__ldg(codes + 1) << 16);
+            const uint32_t w1 = (uint32_t)__ldg(codes + 2) | ((uint32_t)__ldg(codes + 3) << 16);
+            const uint32_t off = qi * 8;
+            const uint2 d0 = *(const uint2 *)(smem + off), d1 = *(const uint2 *)(smem + plane + off), d2 = *(const uint2 *)(smem + 2 * plane + off);
+            const int a0 = dp4a_ss(w1, d0.y, dp4a_ss(w0, d0.x, 0));
+            const int a1 = dp4a_ss(w1, d1.y, dp4a_ss(w0, d1.x, 0));
+            const int a2 = dp4a_ss(w1, d2.y, dp4a_ss(w0, d2.x, 0));
+            acc = fmaf(d * inv_scale[qi >> 2], (float)(a2 * 16384 + a1 * 128 + a0), acc);
+        }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) out[(size_t)slot * out_stride + r] = acc;
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) out[(size_t)slot * out_stride + r] = acc;
+    }
 }
 
 // NUCLIS_EXPERTS_GENERIC=1 keeps every expert GEMV on the generic kernel (for measurements and tests).
@@ -208,38 +260,39 @@ int launch_matvec_experts_fast(cudaStream_t s, uint32_t enc, const uint8_t *w, s
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.stream = s;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    constexpr uint32_t kMaxColumns = 16384;  // shared memory: about 4 bytes a column
     if (enc == Q4_K) {
-        if (columns % 256 != 0 || columns > 10240) return 0;  // the staged row and its sums: 4.5 bytes a column of shared memory
+        if (columns % 256 != 0 || columns > kMaxColumns) return 0;
         if ((uintptr_t)w % 16 != 0 || stride % 16 != 0 || expert_bytes % 16 != 0) return 0;
         const uint32_t ksb = columns / 256;
-        const size_t smem = (size_t)ksb * (272 + 16) * 4;
         static bool configured = false;
         if (!configured) {
-            if (cudaFuncSetAttribute(expert_gemv_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 10240 / 256 * (272 + 16) * 4) != cudaSuccess) return 0;
+            if (cudaFuncSetAttribute(expert_gemv_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kMaxColumns / 256 * (3 * 320 + 128))) != cudaSuccess) return 0;
             configured = true;
         }
-        dim3 grid((rows + XQ_ROWS - 1) / XQ_ROWS, slots);
-        cudaLaunchConfig_t cfg{};
-        cfg.gridDim = grid;
+        cfg.gridDim = dim3((rows + XQ_ROWS - 1) / XQ_ROWS, slots);
         cfg.blockDim = dim3(XQ_THREADS);
-        cfg.dynamicSmemBytes = smem;
-        cfg.stream = s;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        cfg.dynamicSmemBytes = (size_t)ksb * (3 * 320 + 128);
         cudaLaunchKernelEx(&cfg, expert_gemv_q4k_kernel, w, stride, expert_bytes, experts, rows, ksb, indices, in, in_stride, in_group, out, out_stride);
         return 1;
     }
     if (enc == Q8_0) {
-        if (columns % 32 != 0) return 0;
+        if (columns % 32 != 0 || columns > kMaxColumns) return 0;
         if ((uintptr_t)w % 2 != 0 || stride % 2 != 0 || expert_bytes % 2 != 0) return 0;
-        dim3 grid((rows + X8_WARPS - 1) / X8_WARPS, slots);
-        cudaLaunchConfig_t cfg{};
-        cfg.gridDim = grid;
+        const uint32_t blocks = columns / 32;
+        static bool configured = false;
+        if (!configured) {
+            if (cudaFuncSetAttribute(expert_gemv_q8_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kMaxColumns / 32 * (3 * 32 + 4))) != cudaSuccess) return 0;
+            configured = true;
+        }
+        cfg.gridDim = dim3((rows + X8_ROWS - 1) / X8_ROWS, slots);
         cfg.blockDim = dim3(X8_WARPS * 32);
-        cfg.stream = s;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        cudaLaunchKernelEx(&cfg, expert_gemv_q8_0_kernel, w, stride, expert_bytes, experts, rows, columns / 32, indices, in, in_stride, in_group, out, out_stride);
+        cfg.dynamicSmemBytes = (size_t)blocks * (3 * 32 + 4);
+        cudaLaunchKernelEx(&cfg, expert_gemv_q8_0_kernel, w, stride, expert_bytes, experts, rows, blocks, indices, in, in_stride, in_group, out, out_stride);
         return 1;
     }
     return 0;

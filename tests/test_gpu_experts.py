@@ -301,3 +301,45 @@ def test_expert_gemv_ragged_shapes(backend, encoding, rows, cols, in_group):
     backend.unwrap(data)
     for buf in (xb, ib, yb):
         backend.release(buf)
+
+
+@pytest.mark.parametrize("encoding,cols", [(enc.Q4_K, 512), (enc.Q8_0, 96)])
+def test_expert_gemv_extreme_inputs(backend, encoding, cols):
+    """The specialized expert kernels turn the input row into fixed point per chunk of columns: rows scaled by
+    1e+-20, a chunk of zeros and a chunk 2^40 times larger than its neighbours stay within the acceptance
+    bound; an infinity in the input gives a non-finite output as the F32 arithmetic would."""
+    experts, rows, slots = 3, 40, 3
+    data = synth.matrix(encoding, experts * rows, cols, seed=77)
+    per = data.size // experts
+    t = ExpertMatrix(encoding, experts, rows, cols, data.size)
+    rng = np.random.default_rng(cols)
+    x = rng.standard_normal((slots, cols)).astype(np.float32)
+    x[0] *= np.float32(1e20)
+    x[1] *= np.float32(1e-20)
+    x[2, :32] = 0.0
+    x[2, 32:64] *= np.float32(2.0 ** 40)
+    idx = np.array([2, 0, 1], dtype=np.uint32)
+    wb = backend.wrap(data)
+    xb = backend.create(x.nbytes); xb.write(x)
+    ib = backend.create(slots * 4); ib.write(idx)
+    yb = backend.create(slots * rows * 4)
+    backend.begin()
+    backend.matvec_experts(wb, t, ib, slots, xb, cols, yb, rows)
+    backend.commit()
+    got = yb.floats().reshape(slots, rows)
+    for s in range(slots):
+        e = int(idx[s])
+        want = oracle.matvec(encoding, rows, cols, data[e * per:(e + 1) * per], x[s])
+        scale = oracle.matvec_abs(encoding, rows, cols, data[e * per:(e + 1) * per], x[s])
+        assert np.max(np.abs(got[s] - want) / np.maximum(scale, 1e-30)) <= 2e-6, s
+    x[1, 5] = np.inf
+    xb.write(x)
+    backend.begin()
+    backend.matvec_experts(wb, t, ib, slots, xb, cols, yb, rows)
+    backend.commit()
+    got = yb.floats().reshape(slots, rows)
+    assert not np.isfinite(got[1]).any()
+    assert np.isfinite(got[0]).all() and np.isfinite(got[2]).all()
+    backend.unwrap(data)
+    for buf in (xb, ib, yb):
+        backend.release(buf)
