@@ -24,8 +24,11 @@
 //    16-byte piece p of each superblock's 128 quant bytes: 16 low nibbles of group 2(p/2) and 16 high
 //    nibbles of group 2(p/2)+1, columns 16(p&1).. of each; `w & 0x0f0f0f0f` is four codes ready for
 //    dp4a. The minima multiply exact F32 sums of x prepared once per chunk.
-//  * Q8_0: a warp per weight row, 8 rows per warp; a lane takes 8-code quarters of the 34-byte blocks
-//    (2-byte aligned, so 16-bit loads); the int8 codes go to dp4a as they are.
+//  * Q8_0: a warp per weight row, up to 8 rows per warp; a lane takes 8-code quarters of the 34-byte
+//    blocks; the int8 codes go to dp4a as they are.
+//  * The weight bytes travel with cp.async into small rings in shared memory, several superblocks (Q4_K)
+//    or rows (Q8_0, as 4-byte copies: its blocks are only 2-byte aligned) ahead of their use: the first
+//    versions held one 16-byte load per lane in flight and were bound by memory latency at 2.4 TB/s.
 // Sums run in a fixed order: results do not depend on timing.
 #include "kernels.hpp"
 #include "nu_device.cuh"
@@ -36,11 +39,6 @@ namespace {
 constexpr int XQ_THREADS = 256;
 constexpr int XQ_ROWS = 32;  // Q4_K: weight rows per block, 8 lanes each
 
-__device__ __forceinline__ uint4 ldg_stream16(const void *p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
 __device__ __forceinline__ int dp4a_us(uint32_t codes, uint32_t digits, int c) {  // unsigned codes x signed digits
     int d;
     asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(codes), "r"(digits), "r"(c));
@@ -52,18 +50,19 @@ __device__ __forceinline__ int dp4a_ss(uint32_t codes, uint32_t digits, int c) {
     return d;
 }
 
-// 6-bit scale and minimum of group g of a Q4_K superblock; y, z, w are scale bytes 0..3, 4..7, 8..11.
-__device__ __forceinline__ void q4k_scale_min(uint32_t y, uint32_t z, uint32_t w, uint32_t g, float &s, float &m) {
-    const uint32_t sh = (g & 3u) * 8;
-    const uint32_t by = (y >> sh) & 0xffu, bz = (z >> sh) & 0xffu, bw = (w >> sh) & 0xffu;
-    if (g < 4) {
-        s = (float)(by & 63u);
-        m = (float)(bz & 63u);
-    } else {
-        s = (float)((bw & 15u) | ((by >> 6) << 4));
-        m = (float)((bw >> 4) | ((bz >> 6) << 4));
-    }
+// 6-bit scales and minima of groups 2j and 2j+1 of a Q4_K superblock, as two bytes each (group 2j in the low
+// byte); y, z, w are scale bytes 0..3, 4..7, 8..11. No branch: the lanes of a warp hold different j.
+__device__ __forceinline__ void q4k_pair_scales(uint32_t y, uint32_t z, uint32_t w, uint32_t j, uint32_t &s2, uint32_t &m2) {
+    const uint32_t shift = (j & 1u) * 16;
+    const uint32_t hy = (y >> shift) & 0xffffu, hz = (z >> shift) & 0xffffu, hw = (w >> shift) & 0xffffu;
+    // groups 0..3: low six bits of bytes 0..3 / 4..7; groups 4..7: nibbles of bytes 8..11 plus the top two bits of bytes 0..7
+    const uint32_t s_lo = hy & 0x3f3fu, m_lo = hz & 0x3f3fu;
+    const uint32_t s_hi = (hw & 0x0f0fu) | ((hy >> 2) & 0x3030u), m_hi = ((hw >> 4) & 0x0f0fu) | ((hz >> 2) & 0x3030u);
+    s2 = j < 2 ? s_lo : s_hi;
+    m2 = j < 2 ? m_lo : m_hi;
 }
+// byte b of w as a float: 0x4b0000bb is 2^23 + b
+__device__ __forceinline__ float byte_f32(uint32_t w, int b) { return __uint_as_float(__byte_perm(w, 0x4b000000u, 0x7650u + b)) - 8388608.0f; }
 
 // Power of two that brings a chunk whose largest magnitude is `mx` below 2^20, and its inverse. A chunk that
 // is all zero (or too small to matter) is left as it is; one that holds an infinity or a NaN gets a NaN
@@ -87,18 +86,57 @@ __device__ __forceinline__ void digits(float x, float scale, int &p0, int &p1, i
 // chunks 0, 1, 4, 5, 8, 9, 12, 13 (or those + 2) of a superblock's 16, hit eight different groups of banks.
 __device__ __forceinline__ uint32_t plane_offset(uint32_t byte) { return byte + (byte >> 7) * 32; }
 
+constexpr int XQ_STAGES = 6;                        // superblocks in flight per lane
+constexpr int XQ_RING = XQ_STAGES * XQ_ROWS * 144;  // bytes: a stage holds one superblock of each of the block's rows
+
+__device__ __forceinline__ void cp_async16(void *dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void *dst, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 __global__ void __launch_bounds__(XQ_THREADS) expert_gemv_q4k_kernel(const uint8_t *w, size_t stride, size_t expert_bytes, uint32_t experts, uint32_t rows,
                                                                      uint32_t ksb, const uint32_t *indices, const float *in, size_t in_stride,
                                                                      uint32_t in_group, float *out, size_t out_stride) {
-    // [3 planes of digits, ksb * 320 bytes each][ksb * 16 inverse scales][ksb * 16 sums of x]: one entry per 16 columns
+    // [ring of weight stages][3 planes of digits, ksb * 320 bytes each][ksb * 16 pairs (inverse scale, sum of x)]
+    // (one pair per 16 columns)
     extern __shared__ __align__(16) uint8_t smem[];
+    uint8_t *ring = smem;
+    uint8_t *planes = smem + XQ_RING;
     const uint32_t plane = ksb * 320;
-    float *inv_scale = (float *)(smem + 3 * plane);
-    float *sums = inv_scale + ksb * 16;
+    float2 *chunk = (float2 *)(planes + 3 * plane);
     // launched so that its blocks may be placed while the operator before it drains; nothing is read before this
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;");
     const uint32_t slot = blockIdx.y;
+    const uint32_t rl = threadIdx.x >> 3, p = threadIdx.x & 7;
+    const uint32_t r = blockIdx.x * XQ_ROWS + rl;
+    const bool live = r < rows;
+    // A corrupt routing buffer can never read past the tensor (experts.metal:25).
+    const uint32_t expert = min(indices[slot], experts - 1);
+    const uint8_t *row = w + (size_t)expert * expert_bytes + (size_t)(live ? r : 0) * stride;
+    // The weight stream: lane p copies its 16-byte piece of the row's superblock (lane 0 also the 16-byte header)
+    // into the stage, XQ_STAGES - 1 superblocks ahead of its use, without holding them in registers.
+    uint8_t *const my_ring = ring + rl * 144;
+    const uint8_t *src_next = row;
+    uint32_t stage_next = 0, sb_next = 0;
+    auto request = [&]() {
+        if (live && sb_next < ksb) {
+            uint8_t *dst = my_ring + stage_next * (XQ_ROWS * 144);
+            cp_async16(dst + 16 + p * 16, src_next + 16 + p * 16);
+            if (p == 0) cp_async16(dst, src_next);
+        }
+        cp_async_commit();
+        ++sb_next;
+        src_next += 144;
+        stage_next = stage_next + 1 == XQ_STAGES ? 0 : stage_next + 1;
+    };
+    for (int i = 0; i < XQ_STAGES - 1; ++i) request();  // in flight while the input row is prepared
+
     const float *x = in + (size_t)(slot / in_group) * in_stride;
     for (uint32_t c = threadIdx.x; c < ksb * 16; c += XQ_THREADS) {
         float v[16];
@@ -130,34 +168,34 @@ __global__ void __launch_bounds__(XQ_THREADS) expert_gemv_q4k_kernel(const uint8
             }
         }
         const uint32_t off = plane_offset(c * 16);
-        *(uint4 *)(smem + off) = make_uint4(d0[0], d0[1], d0[2], d0[3]);
-        *(uint4 *)(smem + plane + off) = make_uint4(d1[0], d1[1], d1[2], d1[3]);
-        *(uint4 *)(smem + 2 * plane + off) = make_uint4(d2[0], d2[1], d2[2], d2[3]);
-        inv_scale[c] = inv;
-        sums[c] = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7])) + (((v[8] + v[9]) + (v[10] + v[11])) + ((v[12] + v[13]) + (v[14] + v[15])));
+        *(uint4 *)(planes + off) = make_uint4(d0[0], d0[1], d0[2], d0[3]);
+        *(uint4 *)(planes + plane + off) = make_uint4(d1[0], d1[1], d1[2], d1[3]);
+        *(uint4 *)(planes + 2 * plane + off) = make_uint4(d2[0], d2[1], d2[2], d2[3]);
+        chunk[c] = make_float2(inv, ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7])) + (((v[8] + v[9]) + (v[10] + v[11])) + ((v[12] + v[13]) + (v[14] + v[15]))));
     }
     __syncthreads();
-    const uint32_t r = blockIdx.x * XQ_ROWS + (threadIdx.x >> 3), p = threadIdx.x & 7;
-    const bool live = r < rows;
-    // A corrupt routing buffer can never read past the tensor (experts.metal:25).
-    const uint32_t expert = min(indices[slot], experts - 1);
     float acc = 0.0f;
-    if (live) {
-        const uint8_t *row = w + (size_t)expert * expert_bytes + (size_t)r * stride;
-        const uint32_t g_lo = 2 * (p >> 1), g_hi = g_lo + 1;
-        const uint32_t c_lo = 4 * (p >> 1) + (p & 1u), c_hi = c_lo + 2;  // this lane's 16-column chunks of a superblock
-#pragma unroll 2
-        for (uint32_t sb = 0; sb < ksb; ++sb) {
-            const uint4 hdr = ldg_stream16(row + (size_t)sb * 144);
-            const uint4 q = ldg_stream16(row + (size_t)sb * 144 + 16 + p * 16);
+    const uint32_t c_lo = 4 * (p >> 1) + (p & 1u);  // this lane's 16-column chunks of a superblock: c_lo (low nibbles) and c_lo + 2
+    // this lane's places, advanced by one superblock per turn: digits of chunk c_lo (those of c_lo + 2 sit 32 bytes on), the chunk pairs
+    const uint8_t *dig = planes + plane_offset(c_lo * 16);
+    const float2 *ch = chunk + c_lo;
+    uint32_t stage = 0;
+    for (uint32_t sb = 0; sb < ksb; ++sb) {
+        request();
+        cp_async_wait<XQ_STAGES - 1>();  // this lane's copies of superblock sb have landed
+        __syncwarp();                    // and so have lane 0's (the header)
+        if (live) {
+            const uint8_t *src = my_ring + stage * (XQ_ROWS * 144);
+            const uint4 hdr = *(const uint4 *)src;
+            const uint4 q = *(const uint4 *)(src + 16 + p * 16);
             const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
             const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
-            float s_lo, m_lo, s_hi, m_hi;
-            q4k_scale_min(hdr.y, hdr.z, hdr.w, g_lo, s_lo, m_lo);
-            q4k_scale_min(hdr.y, hdr.z, hdr.w, g_hi, s_hi, m_hi);
-            const uint32_t o_lo = plane_offset((sb * 16 + c_lo) * 16), o_hi = plane_offset((sb * 16 + c_hi) * 16);
-            const uint4 l0 = *(const uint4 *)(smem + o_lo), l1 = *(const uint4 *)(smem + plane + o_lo), l2 = *(const uint4 *)(smem + 2 * plane + o_lo);
-            const uint4 h0 = *(const uint4 *)(smem + o_hi), h1 = *(const uint4 *)(smem + plane + o_hi), h2 = *(const uint4 *)(smem + 2 * plane + o_hi);
+            uint32_t s2, m2;
+            q4k_pair_scales(hdr.y, hdr.z, hdr.w, p >> 1, s2, m2);
+            const float s_lo = byte_f32(s2, 0), s_hi = byte_f32(s2, 1), m_lo = byte_f32(m2, 0), m_hi = byte_f32(m2, 1);
+            const uint4 l0 = *(const uint4 *)dig, l1 = *(const uint4 *)(dig + plane), l2 = *(const uint4 *)(dig + 2 * plane);
+            const uint4 h0 = *(const uint4 *)(dig + 32), h1 = *(const uint4 *)(dig + plane + 32), h2 = *(const uint4 *)(dig + 2 * plane + 32);
+            const float2 k_lo = ch[0], k_hi = ch[2];
             const uint32_t ql[4] = {q.x & 0x0f0f0f0fu, q.y & 0x0f0f0f0fu, q.z & 0x0f0f0f0fu, q.w & 0x0f0f0f0fu};
             const uint32_t qh[4] = {(q.x >> 4) & 0x0f0f0f0fu, (q.y >> 4) & 0x0f0f0f0fu, (q.z >> 4) & 0x0f0f0f0fu, (q.w >> 4) & 0x0f0f0f0fu};
             int a0 = 0, a1 = 0, a2 = 0, b0 = 0, b1 = 0, b2 = 0;
@@ -167,14 +205,19 @@ __global__ void __launch_bounds__(XQ_THREADS) expert_gemv_q4k_kernel(const uint8
             b0 = dp4a_us(qh[0], h0.x, b0); b0 = dp4a_us(qh[1], h0.y, b0); b0 = dp4a_us(qh[2], h0.z, b0); b0 = dp4a_us(qh[3], h0.w, b0);
             b1 = dp4a_us(qh[0], h1.x, b1); b1 = dp4a_us(qh[1], h1.y, b1); b1 = dp4a_us(qh[2], h1.z, b1); b1 = dp4a_us(qh[3], h1.w, b1);
             b2 = dp4a_us(qh[0], h2.x, b2); b2 = dp4a_us(qh[1], h2.y, b2); b2 = dp4a_us(qh[2], h2.z, b2); b2 = dp4a_us(qh[3], h2.w, b2);
-            const float f_lo = (float)(a2 * 16384 + a1 * 128 + a0) * inv_scale[sb * 16 + c_lo];
-            const float f_hi = (float)(b2 * 16384 + b1 * 128 + b0) * inv_scale[sb * 16 + c_hi];
+            const float f_lo = (float)(a2 * 16384 + a1 * 128 + a0) * k_lo.x;
+            const float f_hi = (float)(b2 * 16384 + b1 * 128 + b0) * k_hi.x;
             acc = fmaf(d * s_lo, f_lo, acc);
             acc = fmaf(d * s_hi, f_hi, acc);
-            acc = fmaf(-(dmin * m_lo), sums[sb * 16 + c_lo], acc);
-            acc = fmaf(-(dmin * m_hi), sums[sb * 16 + c_hi], acc);
+            acc = fmaf(-(dmin * m_lo), k_lo.y, acc);
+            acc = fmaf(-(dmin * m_hi), k_hi.y, acc);
         }
+        dig += 320;
+        ch += 16;
+        stage = stage + 1 == XQ_STAGES ? 0 : stage + 1;
+        __syncwarp();  // every lane is done with this stage before lane 0 refills its header
     }
+    cp_async_wait<0>();
     acc += __shfl_xor_sync(0xffffffffu, acc, 1);
     acc += __shfl_xor_sync(0xffffffffu, acc, 2);
     acc += __shfl_xor_sync(0xffffffffu, acc, 4);
@@ -182,18 +225,37 @@ __global__ void __launch_bounds__(XQ_THREADS) expert_gemv_q4k_kernel(const uint8
 }
 
 constexpr int X8_WARPS = 8;
-constexpr int X8_ROWS = 64;  // Q8_0: weight rows per block, 8 per warp
+constexpr int X8_STAGES = 4;  // rows in flight per warp
 
 __global__ void __launch_bounds__(X8_WARPS * 32) expert_gemv_q8_0_kernel(const uint8_t *w, size_t stride, size_t expert_bytes, uint32_t experts, uint32_t rows,
-                                                                         uint32_t blocks, const uint32_t *indices, const float *in, size_t in_stride,
-                                                                         uint32_t in_group, float *out, size_t out_stride) {
-    // [3 planes of digits, blocks * 32 bytes each][blocks inverse scales]: one scale per 32-column block
+                                                                         uint32_t blocks, uint32_t rows_per_warp, const uint32_t *indices, const float *in,
+                                                                         size_t in_stride, uint32_t in_group, float *out, size_t out_stride) {
+    // [per warp: ring of X8_STAGES rows, `pitch` bytes each][3 planes of digits, blocks * 32 bytes each][blocks inverse scales]
     extern __shared__ __align__(16) uint8_t smem[];
+    const uint32_t words = blocks * 34 / 4;  // the launcher takes an even number of blocks only: rows are whole 4-byte words
+    const uint32_t pitch = (words * 4 + 15) & ~15u;
+    uint8_t *planes = smem + X8_WARPS * X8_STAGES * pitch;
     const uint32_t plane = blocks * 32;
-    float *inv_scale = (float *)(smem + 3 * plane);
+    float *inv_scale = (float *)(planes + 3 * plane);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;");
     const uint32_t slot = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t expert = min(indices[slot], experts - 1);
+    const uint8_t *base = w + (size_t)expert * expert_bytes;
+    // rows of this warp: r0, r0 + 1, ...; a row travels to the warp's ring as 4-byte copies, X8_STAGES - 1 rows ahead
+    const uint32_t r0 = (blockIdx.x * X8_WARPS + warp) * rows_per_warp;
+    const uint32_t nrows = r0 < rows ? min(rows_per_warp, rows - r0) : 0;
+    uint8_t *ring = smem + warp * X8_STAGES * pitch;
+    auto request = [&](uint32_t k) {
+        if (k < nrows) {
+            const uint8_t *src = base + (size_t)(r0 + k) * stride;
+            uint8_t *dst = ring + (k % X8_STAGES) * pitch;
+            for (uint32_t i = lane; i < words; i += 32) cp_async4(dst + i * 4, src + i * 4);
+        }
+        cp_async_commit();
+    };
+    for (uint32_t k = 0; k < X8_STAGES - 1; ++k) request(k);  // in flight while the input row is prepared
+
     const float *x = in + (size_t)(slot / in_group) * in_stride;
     // a warp per block of 32 columns, a lane per column
     for (uint32_t b = warp; b < blocks; b += X8_WARPS) {
@@ -209,37 +271,37 @@ __global__ void __launch_bounds__(X8_WARPS * 32) expert_gemv_q8_0_kernel(const u
         chunk_scale(mx, scale, inv);
         int p0, p1, p2;
         digits(v, scale, p0, p1, p2);
-        smem[b * 32 + lane] = (uint8_t)p0;
-        smem[plane + b * 32 + lane] = (uint8_t)p1;
-        smem[2 * plane + b * 32 + lane] = (uint8_t)p2;
+        planes[b * 32 + lane] = (uint8_t)p0;
+        planes[plane + b * 32 + lane] = (uint8_t)p1;
+        planes[2 * plane + b * 32 + lane] = (uint8_t)p2;
         if (lane == 0) inv_scale[b] = inv;
     }
     __syncthreads();
-    const uint32_t expert = min(indices[slot], experts - 1);
-    const uint8_t *base = w + (size_t)expert * expert_bytes;
-    for (uint32_t k = 0; k < X8_ROWS / X8_WARPS; ++k) {
-        const uint32_t r = blockIdx.x * X8_ROWS + k * X8_WARPS + warp;
-        if (r >= rows) break;
-        const uint8_t *row = base + (size_t)r * stride;
+    for (uint32_t k = 0; k < nrows; ++k) {
+        request(k + X8_STAGES - 1);
+        cp_async_wait<X8_STAGES - 1>();
+        __syncwarp();  // the whole row has landed: every lane's copies
+        const uint8_t *row = ring + (k % X8_STAGES) * pitch;
         float acc = 0.0f;
         // quarter qi of the row: block qi / 4, codes 8 (qi & 3) .. +7
         for (uint32_t qi = lane; qi < blocks * 4; qi += 32) {
-            const uint8_t *blk = row + (size_t)(qi >> 2) * 34;
+            const uint8_t *blk = row + (qi >> 2) * 34;
             const unsigned short *codes = (const unsigned short *)(blk + 2 + (qi & 3u) * 8);
-            const float d = __half2float(__ushort_as_half(__ldg((const unsigned short *)blk)));
-            const uint32_t w0 = (uint32_t)__ldg(codes) | ((uint32_t)__ldg(codes + 1) << 16);
-            const uint32_t w1 = (uint32_t)__ldg(codes + 2) | ((uint32_t)__ldg(codes + 3) << 16);
+            const float d = __half2float(__ushort_as_half(*(const unsigned short *)blk));
+            const uint32_t w0 = (uint32_t)codes[0] | ((uint32_t)codes[1] << 16);
+            const uint32_t w1 = (uint32_t)codes[2] | ((uint32_t)codes[3] << 16);
             const uint32_t off = qi * 8;
-            const uint2 d0 = *(const uint2 *)(smem + off), d1 = *(const uint2 *)(smem + plane + off), d2 = *(const uint2 *)(smem + 2 * plane + off);
+            const uint2 d0 = *(const uint2 *)(planes + off), d1 = *(const uint2 *)(planes + plane + off), d2 = *(const uint2 *)(planes + 2 * plane + off);
             const int a0 = dp4a_ss(w1, d0.y, dp4a_ss(w0, d0.x, 0));
             const int a1 = dp4a_ss(w1, d1.y, dp4a_ss(w0, d1.x, 0));
             const int a2 = dp4a_ss(w1, d2.y, dp4a_ss(w0, d2.x, 0));
             acc = fmaf(d * inv_scale[qi >> 2], (float)(a2 * 16384 + a1 * 128 + a0), acc);
         }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (lane == 0) out[(size_t)slot * out_stride + r] = acc;
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);  // also: every lane is done with the stage before it is refilled
+        if (lane == 0) out[(size_t)slot * out_stride + r0 + k] = acc;
     }
+    cp_async_wait<0>();
 }
 
 // NUCLIS_EXPERTS_GENERIC=1 keeps every expert GEMV on the generic kernel (for measurements and tests).
@@ -271,28 +333,36 @@ int launch_matvec_experts_fast(cudaStream_t s, uint32_t enc, const uint8_t *w, s
         const uint32_t ksb = columns / 256;
         static bool configured = false;
         if (!configured) {
-            if (cudaFuncSetAttribute(expert_gemv_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kMaxColumns / 256 * (3 * 320 + 128))) != cudaSuccess) return 0;
+            if (cudaFuncSetAttribute(expert_gemv_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(XQ_RING + kMaxColumns / 256 * (3 * 320 + 128))) != cudaSuccess) return 0;
             configured = true;
         }
         cfg.gridDim = dim3((rows + XQ_ROWS - 1) / XQ_ROWS, slots);
         cfg.blockDim = dim3(XQ_THREADS);
-        cfg.dynamicSmemBytes = (size_t)ksb * (3 * 320 + 128);
+        cfg.dynamicSmemBytes = XQ_RING + (size_t)ksb * (3 * 320 + 128);
         cudaLaunchKernelEx(&cfg, expert_gemv_q4k_kernel, w, stride, expert_bytes, experts, rows, ksb, indices, in, in_stride, in_group, out, out_stride);
         return 1;
     }
     if (enc == Q8_0) {
-        if (columns % 32 != 0 || columns > kMaxColumns) return 0;
-        if ((uintptr_t)w % 2 != 0 || stride % 2 != 0 || expert_bytes % 2 != 0) return 0;
+        // rows travel as 4-byte copies: an even number of 34-byte blocks, rows and experts on 4-byte boundaries
+        if (columns % 64 != 0 || columns > kMaxColumns) return 0;
+        if ((uintptr_t)w % 4 != 0 || stride % 4 != 0 || expert_bytes % 4 != 0) return 0;
         const uint32_t blocks = columns / 32;
+        const uint32_t pitch = (blocks * 34 + 15) & ~15u;
+        const size_t smem = (size_t)X8_WARPS * X8_STAGES * pitch + (size_t)blocks * (3 * 32 + 4);
+        if (smem > 200 * 1024) return 0;
         static bool configured = false;
         if (!configured) {
-            if (cudaFuncSetAttribute(expert_gemv_q8_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kMaxColumns / 32 * (3 * 32 + 4))) != cudaSuccess) return 0;
+            if (cudaFuncSetAttribute(expert_gemv_q8_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return 0;
             configured = true;
         }
-        cfg.gridDim = dim3((rows + X8_ROWS - 1) / X8_ROWS, slots);
+        // enough blocks to fill the machine a few times over, up to eight rows per warp
+        uint32_t rows_per_warp = (uint32_t)(((uint64_t)rows * slots) / (X8_WARPS * 148ull * 4));
+        rows_per_warp = rows_per_warp < 1 ? 1 : rows_per_warp > 8 ? 8 : rows_per_warp;
+        const uint32_t rows_per_block = rows_per_warp * X8_WARPS;
+        cfg.gridDim = dim3((rows + rows_per_block - 1) / rows_per_block, slots);
         cfg.blockDim = dim3(X8_WARPS * 32);
-        cfg.dynamicSmemBytes = (size_t)blocks * (3 * 32 + 4);
-        cudaLaunchKernelEx(&cfg, expert_gemv_q8_0_kernel, w, stride, expert_bytes, experts, rows, blocks, indices, in, in_stride, in_group, out, out_stride);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchKernelEx(&cfg, expert_gemv_q8_0_kernel, w, stride, expert_bytes, experts, rows, blocks, rows_per_warp, indices, in, in_stride, in_group, out, out_stride);
         return 1;
     }
     return 0;
