@@ -8,7 +8,7 @@
 
 namespace nu {
 
-enum Encoding : uint32_t { F32 = 0, F16 = 1, Q8_0 = 8, Q4_K = 12, Q6_K = 14, BF16 = 30 };
+enum Encoding : uint32_t { F32 = 0, F16 = 1, Q4_0 = 2, Q5_0 = 6, Q5_1 = 7, Q8_0 = 8, Q4_K = 12, Q5_K = 13, Q6_K = 14, BF16 = 30 };
 
 struct Layout { uint32_t elements, bytes; };
 
@@ -17,8 +17,12 @@ __host__ __device__ inline Layout layout(uint32_t id) {
     switch (id) {
     case F32: return {1, 4};
     case F16: return {1, 2};
+    case Q4_0: return {32, 18};
+    case Q5_0: return {32, 22};
+    case Q5_1: return {32, 24};
     case Q8_0: return {32, 34};
     case Q4_K: return {256, 144};
+    case Q5_K: return {256, 176};
     case Q6_K: return {256, 210};
     case BF16: return {1, 2};
     default: return {0, 0};
@@ -63,8 +67,37 @@ __device__ __forceinline__ void dequant16(uint32_t enc, const uint8_t *row, uint
         for (int i = 0; i < 16; ++i) out[i] = __fmul_rn(d, (float)(int8_t)q[i]);
         break;
     }
-    case Q4_K: {
-        const uint8_t *block = row + (size_t)(first / 256) * 144;
+    case Q4_0: {
+        // decode.zig:46-53: low nibbles are the first half of the block, high nibbles the second; code - 8
+        const uint8_t *block = row + (size_t)(first / 32) * 18;
+        const float d = half_at(block);
+        const uint32_t shift = ((first % 32) / 16) * 4;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) out[i] = __fmul_rn(d, (float)((int)((block[2 + i] >> shift) & 15u) - 8));
+        break;
+    }
+    case Q5_0:
+    case Q5_1: {
+        // decode.zig:125-143: Q4_0's nibble order, each code completed by its bit of the 32-bit plane
+        const bool offset = enc == Q5_1;
+        const uint8_t *block = row + (size_t)(first / 32) * (offset ? 24 : 22);
+        const float d = half_at(block);
+        const float m = offset ? half_at(block + 2) : 0.0f;
+        const uint8_t *plane = block + (offset ? 4 : 2);
+        const uint32_t qh = (uint32_t)plane[0] | ((uint32_t)plane[1] << 8) | ((uint32_t)plane[2] << 16) | ((uint32_t)plane[3] << 24);
+        const uint32_t hi = (first % 32) / 16;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int q = (int)(((plane[4 + i] >> (hi * 4)) & 15u) | (((qh >> (i + hi * 16)) & 1u) << 4));
+            out[i] = offset ? __fadd_rn(__fmul_rn(d, (float)q), m) : __fmul_rn(d, (float)(q - 16));
+        }
+        break;
+    }
+    case Q4_K:
+    case Q5_K: {
+        // decode.zig:147-170; Q5_K: 32 bytes of high bits at 16 (bit g of byte c belongs to group g), the nibbles after them
+        const bool fifth = enc == Q5_K;
+        const uint8_t *block = row + (size_t)(first / 256) * (fifth ? 176 : 144);
         const uint32_t in_block = first % 256;
         const uint32_t g = in_block / 32, c0 = in_block % 32;
         const uint8_t *sc = block + 4;
@@ -78,10 +111,14 @@ __device__ __forceinline__ void dequant16(uint32_t enc, const uint8_t *row, uint
         }
         const float multiplier = __fmul_rn(half_at(block), (float)s);
         const float offset = __fmul_rn(half_at(block + 2), (float)m);
-        const uint8_t *qs = block + 16 + (g / 2) * 32 + c0;
+        const uint8_t *qs = block + (fifth ? 48 : 16) + (g / 2) * 32 + c0;
         const uint32_t shift = (g & 1u) * 4;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) out[i] = __fsub_rn(__fmul_rn(multiplier, (float)((qs[i] >> shift) & 15u)), offset);
+        for (int i = 0; i < 16; ++i) {
+            uint32_t q = (qs[i] >> shift) & 15u;
+            if (fifth) q |= (((uint32_t)block[16 + c0 + i] >> g) & 1u) << 4;
+            out[i] = __fsub_rn(__fmul_rn(multiplier, (float)q), offset);
+        }
         break;
     }
     case Q6_K: {

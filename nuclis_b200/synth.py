@@ -57,7 +57,45 @@ def q8_0(rng: np.random.Generator, rows: int, columns: int) -> np.ndarray:
     return out.reshape(-1)
 
 
-GENERATORS = {enc.Q4_K: q4_k, enc.Q6_K: q6_k, enc.Q8_0: q8_0}
+def q4_0(rng: np.random.Generator, rows: int, columns: int) -> np.ndarray:
+    """[rows * columns/32 * 18] bytes. Draw order: d, nibbles."""
+    blocks = rows * (columns // 32)
+    out = np.empty((blocks, 18), dtype=np.uint8)
+    out[:, 0:2] = _abs_normal_f16(rng, blocks, 2e-2)
+    out[:, 2:18] = rng.integers(0, 256, size=(blocks, 16), dtype=np.uint8)
+    return out.reshape(-1)
+
+
+def q5_0(rng: np.random.Generator, rows: int, columns: int) -> np.ndarray:
+    """[rows * columns/32 * 22] bytes. Draw order: d, the plane of fifth bits, nibbles."""
+    blocks = rows * (columns // 32)
+    out = np.empty((blocks, 22), dtype=np.uint8)
+    out[:, 0:2] = _abs_normal_f16(rng, blocks, 1e-2)
+    out[:, 2:22] = rng.integers(0, 256, size=(blocks, 20), dtype=np.uint8)
+    return out.reshape(-1)
+
+
+def q5_1(rng: np.random.Generator, rows: int, columns: int) -> np.ndarray:
+    """[rows * columns/32 * 24] bytes. Draw order: d, m, the plane of fifth bits, nibbles."""
+    blocks = rows * (columns // 32)
+    out = np.empty((blocks, 24), dtype=np.uint8)
+    out[:, 0:2] = _abs_normal_f16(rng, blocks, 1e-2)
+    out[:, 2:4] = _abs_normal_f16(rng, blocks, 1e-1)
+    out[:, 4:24] = rng.integers(0, 256, size=(blocks, 20), dtype=np.uint8)
+    return out.reshape(-1)
+
+
+def q5_k(rng: np.random.Generator, rows: int, columns: int) -> np.ndarray:
+    """[rows * columns/256 * 176] bytes. Draw order: d, dmin, scale bytes, fifth bits and nibbles."""
+    blocks = rows * (columns // 256)
+    out = np.empty((blocks, 176), dtype=np.uint8)
+    out[:, 0:2] = _abs_normal_f16(rng, blocks, 5e-4)
+    out[:, 2:4] = _abs_normal_f16(rng, blocks, 5e-4)
+    out[:, 4:176] = rng.integers(0, 256, size=(blocks, 172), dtype=np.uint8)
+    return out.reshape(-1)
+
+
+GENERATORS = {enc.Q4_K: q4_k, enc.Q6_K: q6_k, enc.Q8_0: q8_0, enc.Q4_0: q4_0, enc.Q5_0: q5_0, enc.Q5_1: q5_1, enc.Q5_K: q5_k}
 
 
 def matrix(encoding: int, rows: int, columns: int, seed: int) -> np.ndarray:

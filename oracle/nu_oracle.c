@@ -17,7 +17,7 @@
  * What each function follows (paths inside the reference tree):
  *   nu_ref_layout        inference/src/tensor/encoding.zig:29-56
  *   nu_ref_validate_row  inference/src/quant/decode.zig:108-120
- *   nu_ref_row           inference/src/quant/decode.zig:30-103 (ids 0,1,8,12,14,30),
+ *   nu_ref_row           inference/src/quant/decode.zig:30-103 (ids 0,1,2,6,7,8,12,13,14,30),
  *                        :147-170 (Q4_K), :198-211 (Q6_K), :432-435 (half)
  *   nu_ref_matvec        inference/src/backends/cpu/root.zig:112-152
  *   nu_ref_gelu/silu     inference/src/backends/cpu/vector.zig:94-98, 178-196
@@ -49,8 +49,12 @@ int nu_ref_layout(uint32_t id, uint32_t *elements, uint32_t *bytes) {
     switch (id) {
     case 0: e = 1; b = 4; break;      /* F32  */
     case 1: e = 1; b = 2; break;      /* F16  */
+    case 2: e = 32; b = 18; break;    /* Q4_0 */
+    case 6: e = 32; b = 22; break;    /* Q5_0 */
+    case 7: e = 32; b = 24; break;    /* Q5_1 */
     case 8: e = 32; b = 34; break;    /* Q8_0 */
     case 12: e = 256; b = 144; break; /* Q4_K */
+    case 13: e = 256; b = 176; break; /* Q5_K */
     case 14: e = 256; b = 210; break; /* Q6_K */
     case 30: e = 1; b = 2; break;     /* BF16 */
     default: return NU_REF_UNSUPPORTED_ENCODING;
@@ -95,12 +99,34 @@ static float half_at(const uint8_t *p) {
     return f;
 }
 
-/* decode.zig:147-170 with fifth_bit = false. */
-static void q4k_block(const uint8_t *block, float *out) {
+/* decode.zig:125-143: Q5_0 (offset = 0: d * (q - 16)) and Q5_1 (d * q + m). Q4_0's nibble order,
+ * each code completed by its bit of the 32-bit plane (bit j for value j). */
+static void five_block(int offset, const uint8_t *block, float *out) {
+    const float d = half_at(block);
+    const float m = offset ? half_at(block + 2) : 0.0f;
+    const uint8_t *plane = block + (offset ? 4 : 2);
+    const uint32_t qh = (uint32_t)plane[0] | ((uint32_t)plane[1] << 8) | ((uint32_t)plane[2] << 16) | ((uint32_t)plane[3] << 24);
+    const uint8_t *qs = plane + 4;
+    for (int j = 0; j < 16; ++j) {
+        const int low = (int)((qs[j] & 15u) | (((qh >> j) & 1u) << 4));
+        const int high = (int)((uint32_t)(qs[j] >> 4) | (((qh >> (j + 16)) & 1u) << 4));
+        if (offset) {
+            out[j] = d * (float)low + m;
+            out[j + 16] = d * (float)high + m;
+        } else {
+            out[j] = d * (float)(low - 16);
+            out[j + 16] = d * (float)(high - 16);
+        }
+    }
+}
+
+/* decode.zig:147-170: Q4_K (fifth_bit = 0) and Q5_K (fifth_bit = 1: 32 bytes of high bits at 16, one bit per
+ * group in each, the nibbles after them). */
+static void q4k_block(int fifth_bit, const uint8_t *block, float *out) {
     const float d = half_at(block);
     const float dmin = half_at(block + 2);
     const uint8_t *sc = block + 4;
-    const uint8_t *qs = block + 16;
+    const uint8_t *qs = block + (fifth_bit ? 48 : 16);
     for (int g = 0; g < 8; ++g) {
         uint32_t s, m;
         if (g < 4) {
@@ -114,7 +140,8 @@ static void q4k_block(const uint8_t *block, float *out) {
         const float offset = dmin * (float)m;
         for (int c = 0; c < 32; ++c) {
             const uint8_t byte = qs[(g / 2) * 32 + c];
-            const uint32_t q = (g % 2 == 0) ? (byte & 15u) : (uint32_t)(byte >> 4);
+            uint32_t q = (g % 2 == 0) ? (byte & 15u) : (uint32_t)(byte >> 4);
+            if (fifth_bit) q |= (((uint32_t)block[16 + c] >> g) & 1u) << 4;
             out[g * 32 + c] = multiplier * (float)q - offset;
         }
     }
@@ -136,7 +163,7 @@ static void q6k_block(const uint8_t *block, float *out) {
     }
 }
 
-/* decode.zig:30-103, the arms for ids 0, 1, 8, 12, 14, 30. All validation
+/* decode.zig:30-103, the arms for ids 0, 1, 2, 6, 7, 8, 12, 13, 14, 30. All validation
  * happens before the first write. */
 int nu_ref_row(uint32_t id, const uint8_t *bytes, size_t byte_count, float *out, size_t element_count) {
     int rc = nu_ref_validate_row(id, byte_count, element_count);
@@ -153,12 +180,24 @@ int nu_ref_row(uint32_t id, const uint8_t *bytes, size_t byte_count, float *out,
             break;
         }
         case 1: out[o] = half_at(block); break;
+        case 2: {
+            /* Q4_0: low nibbles are the first half of the block, high nibbles the second; code - 8 */
+            const float scale = half_at(block);
+            for (int j = 0; j < 16; ++j) {
+                out[o + j] = scale * (float)((int)(block[2 + j] & 15u) - 8);
+                out[o + j + 16] = scale * (float)((int)(block[2 + j] >> 4) - 8);
+            }
+            break;
+        }
+        case 6: five_block(0, block, out + o); break;
+        case 7: five_block(1, block, out + o); break;
         case 8: {
             const float scale = half_at(block);
             for (int j = 0; j < 32; ++j) out[o + j] = scale * (float)(int8_t)block[2 + j];
             break;
         }
-        case 12: q4k_block(block, out + o); break;
+        case 12: q4k_block(0, block, out + o); break;
+        case 13: q4k_block(1, block, out + o); break;
         case 14: q6k_block(block, out + o); break;
         case 30: {
             uint32_t bits = ((uint32_t)block[0] | ((uint32_t)block[1] << 8)) << 16;
