@@ -57,7 +57,7 @@ typedef enum nu_status {
 } nu_status;
 
 /* GGML encoding ids served (inference/src/tensor/encoding.zig:29-56). */
-enum { NU_F32 = 0, NU_F16 = 1, NU_Q4_0 = 2, NU_Q5_0 = 6, NU_Q5_1 = 7, NU_Q8_0 = 8, NU_Q4_K = 12, NU_Q5_K = 13, NU_Q6_K = 14, NU_BF16 = 30 };
+enum { NU_F32 = 0, NU_F16 = 1, NU_Q4_0 = 2, NU_Q5_0 = 6, NU_Q5_1 = 7, NU_Q8_0 = 8, NU_Q2_K = 10, NU_Q3_K = 11, NU_Q4_K = 12, NU_Q5_K = 13, NU_Q6_K = 14, NU_BF16 = 30 };
 
 /* `Buffer` of backends/metal/root.zig:62-86 without the host pointer: device
  * memory is not host-addressable here; use upload/download. */

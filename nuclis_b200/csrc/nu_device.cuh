@@ -8,7 +8,7 @@
 
 namespace nu {
 
-enum Encoding : uint32_t { F32 = 0, F16 = 1, Q4_0 = 2, Q5_0 = 6, Q5_1 = 7, Q8_0 = 8, Q4_K = 12, Q5_K = 13, Q6_K = 14, BF16 = 30 };
+enum Encoding : uint32_t { F32 = 0, F16 = 1, Q4_0 = 2, Q5_0 = 6, Q5_1 = 7, Q8_0 = 8, Q2_K = 10, Q3_K = 11, Q4_K = 12, Q5_K = 13, Q6_K = 14, BF16 = 30 };
 
 struct Layout { uint32_t elements, bytes; };
 
@@ -21,6 +21,8 @@ __host__ __device__ inline Layout layout(uint32_t id) {
     case Q5_0: return {32, 22};
     case Q5_1: return {32, 24};
     case Q8_0: return {32, 34};
+    case Q2_K: return {256, 84};
+    case Q3_K: return {256, 110};
     case Q4_K: return {256, 144};
     case Q5_K: return {256, 176};
     case Q6_K: return {256, 210};
@@ -90,6 +92,36 @@ __device__ __forceinline__ void dequant16(uint32_t enc, const uint8_t *row, uint
         for (int i = 0; i < 16; ++i) {
             const int q = (int)(((plane[4 + i] >> (hi * 4)) & 15u) | (((qh >> (i + hi * 16)) & 1u) << 4));
             out[i] = offset ? __fadd_rn(__fmul_rn(d, (float)q), m) : __fmul_rn(d, (float)(q - 16));
+        }
+        break;
+    }
+    case Q2_K: {
+        // decode.zig:260-275: the 16 values are one group: a four-bit scale and minimum, two-bit codes in bit planes
+        const uint8_t *block = row + (size_t)(first / 256) * 84;
+        const uint32_t i0 = first % 256, g = i0 / 16;
+        const float multiplier = __fmul_rn(half_at(block + 80), (float)(block[g] & 15u));
+        const float offset = __fmul_rn(half_at(block + 82), (float)(block[g] >> 4));
+        const uint8_t *q = block + 16 + (i0 / 128) * 32 + i0 % 32;
+        const uint32_t shift = 2 * ((i0 % 128) / 32);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) out[i] = __fsub_rn(__fmul_rn(multiplier, (float)((q[i] >> shift) & 3u)), offset);
+        break;
+    }
+    case Q3_K: {
+        // decode.zig:174-196: biased six-bit scales; a clear high-mask bit means subtract four
+        const uint8_t *block = row + (size_t)(first / 256) * 110;
+        const uint32_t i0 = first % 256, g = i0 / 16;
+        const uint8_t *scales = block + 96;
+        const uint32_t nibble = g < 8 ? (scales[g] & 15u) : (uint32_t)(scales[g - 8] >> 4);
+        const uint32_t upper = ((uint32_t)scales[8 + g % 4] >> (2 * (g / 4))) & 3u;
+        const float multiplier = __fmul_rn(half_at(block + 108), (float)((int)(nibble | (upper << 4)) - 32));
+        const uint8_t *q = block + 32 + (i0 / 128) * 32 + i0 % 32;
+        const uint8_t *mask = block + i0 % 32;
+        const uint32_t low_shift = 2 * ((i0 % 128) / 32), sign_shift = i0 / 32;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int low = (int)((q[i] >> low_shift) & 3u);
+            out[i] = __fmul_rn(multiplier, (float)(low - (((mask[i] >> sign_shift) & 1u) ? 0 : 4)));
         }
         break;
     }

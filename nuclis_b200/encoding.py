@@ -7,7 +7,7 @@ descriptors can be sized before any device call.
 from __future__ import annotations
 
 F32, F16, Q8_0, Q4_K, Q6_K, BF16 = 0, 1, 8, 12, 14, 30
-Q4_0, Q5_0, Q5_1, Q5_K = 2, 6, 7, 13  # served by the generic kernels (bit-exact decode, any alignment)
+Q4_0, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K = 2, 6, 7, 10, 11, 13  # served by the generic kernels (bit-exact decode, any alignment)
 
 LAYOUTS = {
     F32: ("F32", 1, 4),
@@ -15,6 +15,8 @@ LAYOUTS = {
     Q4_0: ("Q4_0", 32, 18),
     Q5_0: ("Q5_0", 32, 22),
     Q5_1: ("Q5_1", 32, 24),
+    Q2_K: ("Q2_K", 256, 84),
+    Q3_K: ("Q3_K", 256, 110),
     Q5_K: ("Q5_K", 256, 176),
     Q8_0: ("Q8_0", 32, 34),
     Q4_K: ("Q4_K", 256, 144),

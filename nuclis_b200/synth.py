@@ -95,7 +95,26 @@ def q5_k(rng: np.random.Generator, rows: int, columns: int) -> np.ndarray:
     return out.reshape(-1)
 
 
-GENERATORS = {enc.Q4_K: q4_k, enc.Q6_K: q6_k, enc.Q8_0: q8_0, enc.Q4_0: q4_0, enc.Q5_0: q5_0, enc.Q5_1: q5_1, enc.Q5_K: q5_k}
+def q2_k(rng: np.random.Generator, rows: int, columns: int) -> np.ndarray:
+    """[rows * columns/256 * 84] bytes. Draw order: scale bytes and codes, d, dmin."""
+    blocks = rows * (columns // 256)
+    out = np.empty((blocks, 84), dtype=np.uint8)
+    out[:, 0:80] = rng.integers(0, 256, size=(blocks, 80), dtype=np.uint8)
+    out[:, 80:82] = _abs_normal_f16(rng, blocks, 5e-3)
+    out[:, 82:84] = _abs_normal_f16(rng, blocks, 5e-3)
+    return out.reshape(-1)
+
+
+def q3_k(rng: np.random.Generator, rows: int, columns: int) -> np.ndarray:
+    """[rows * columns/256 * 110] bytes. Draw order: high-bit mask, codes and scale bytes, d."""
+    blocks = rows * (columns // 256)
+    out = np.empty((blocks, 110), dtype=np.uint8)
+    out[:, 0:108] = rng.integers(0, 256, size=(blocks, 108), dtype=np.uint8)
+    out[:, 108:110] = _abs_normal_f16(rng, blocks, 1e-3)
+    return out.reshape(-1)
+
+
+GENERATORS = {enc.Q2_K: q2_k, enc.Q3_K: q3_k, enc.Q4_K: q4_k, enc.Q6_K: q6_k, enc.Q8_0: q8_0, enc.Q4_0: q4_0, enc.Q5_0: q5_0, enc.Q5_1: q5_1, enc.Q5_K: q5_k}
 
 
 def matrix(encoding: int, rows: int, columns: int, seed: int) -> np.ndarray:

@@ -17,7 +17,7 @@
  * What each function follows (paths inside the reference tree):
  *   nu_ref_layout        inference/src/tensor/encoding.zig:29-56
  *   nu_ref_validate_row  inference/src/quant/decode.zig:108-120
- *   nu_ref_row           inference/src/quant/decode.zig:30-103 (ids 0,1,2,6,7,8,12,13,14,30),
+ *   nu_ref_row           inference/src/quant/decode.zig:30-103 (ids 0,1,2,6,7,8,10,11,12,13,14,30),
  *                        :147-170 (Q4_K), :198-211 (Q6_K), :432-435 (half)
  *   nu_ref_matvec        inference/src/backends/cpu/root.zig:112-152
  *   nu_ref_gelu/silu     inference/src/backends/cpu/vector.zig:94-98, 178-196
@@ -53,6 +53,8 @@ int nu_ref_layout(uint32_t id, uint32_t *elements, uint32_t *bytes) {
     case 6: e = 32; b = 22; break;    /* Q5_0 */
     case 7: e = 32; b = 24; break;    /* Q5_1 */
     case 8: e = 32; b = 34; break;    /* Q8_0 */
+    case 10: e = 256; b = 84; break;  /* Q2_K */
+    case 11: e = 256; b = 110; break; /* Q3_K */
     case 12: e = 256; b = 144; break; /* Q4_K */
     case 13: e = 256; b = 176; break; /* Q5_K */
     case 14: e = 256; b = 210; break; /* Q6_K */
@@ -147,6 +149,42 @@ static void q4k_block(int fifth_bit, const uint8_t *block, float *out) {
     }
 }
 
+/* decode.zig:260-275: Q2_K, sixteen groups of 16 two-bit codes, a four-bit scale (low nibble) and a four-bit
+ * minimum (high nibble) each under two block scales; each 128-value half packs four bit planes of 32 bytes. */
+static void q2k_block(const uint8_t *block, float *out) {
+    const float d = half_at(block + 80);
+    const float dmin = half_at(block + 82);
+    for (int g = 0; g < 16; ++g) {
+        const float multiplier = d * (float)(block[g] & 15u);
+        const float offset = dmin * (float)(block[g] >> 4);
+        for (int c = 0; c < 16; ++c) {
+            const int i = g * 16 + c;
+            const int shift = 2 * ((i % 128) / 32);
+            const uint32_t code = ((uint32_t)block[16 + (i / 128) * 32 + i % 32] >> shift) & 3u;
+            out[i] = multiplier * (float)code - offset;
+        }
+    }
+}
+
+/* decode.zig:174-196: Q3_K, biased six-bit scales and an inverted high bit per code (clear means subtract four). */
+static void q3k_block(const uint8_t *block, float *out) {
+    const float d = half_at(block + 108);
+    const uint8_t *scales = block + 96;
+    for (int g = 0; g < 16; ++g) {
+        const uint32_t nibble = g < 8 ? (scales[g] & 15u) : (uint32_t)(scales[g - 8] >> 4);
+        const uint32_t upper = ((uint32_t)scales[8 + g % 4] >> (2 * (g / 4))) & 3u;
+        const int scale = (int)(nibble | (upper << 4)) - 32;
+        const float multiplier = d * (float)scale;
+        for (int c = 0; c < 16; ++c) {
+            const int i = g * 16 + c;
+            const int low_shift = 2 * ((i % 128) / 32);
+            const int low = (int)(((uint32_t)block[32 + (i / 128) * 32 + i % 32] >> low_shift) & 3u);
+            const uint32_t nonnegative = ((uint32_t)block[i % 32] >> (i / 32)) & 1u;
+            out[i] = multiplier * (float)(low - (nonnegative ? 0 : 4));
+        }
+    }
+}
+
 /* decode.zig:198-211. */
 static void q6k_block(const uint8_t *block, float *out) {
     const float d = half_at(block + 208);
@@ -163,7 +201,7 @@ static void q6k_block(const uint8_t *block, float *out) {
     }
 }
 
-/* decode.zig:30-103, the arms for ids 0, 1, 2, 6, 7, 8, 12, 13, 14, 30. All validation
+/* decode.zig:30-103, the arms for ids 0, 1, 2, 6, 7, 8, 10, 11, 12, 13, 14, 30. All validation
  * happens before the first write. */
 int nu_ref_row(uint32_t id, const uint8_t *bytes, size_t byte_count, float *out, size_t element_count) {
     int rc = nu_ref_validate_row(id, byte_count, element_count);
@@ -196,6 +234,8 @@ int nu_ref_row(uint32_t id, const uint8_t *bytes, size_t byte_count, float *out,
             for (int j = 0; j < 32; ++j) out[o + j] = scale * (float)(int8_t)block[2 + j];
             break;
         }
+        case 10: q2k_block(block, out + o); break;
+        case 11: q3k_block(block, out + o); break;
         case 12: q4k_block(0, block, out + o); break;
         case 13: q4k_block(1, block, out + o); break;
         case 14: q6k_block(block, out + o); break;

@@ -1,7 +1,7 @@
-"""GPU parity of the encodings served by the generic kernels: Q4_0, Q5_0, Q5_1, Q5_K.
+"""GPU parity of the encodings served by the generic kernels: Q4_0, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K.
 
-The reference decodes them in inference/src/quant/decode.zig:46-56, 125-143, 147-170 and pins them
-with the rows of its fixtures simple.json, five-bit.json and k-affine.json, which
+The reference decodes them in inference/src/quant/decode.zig:46-56, 125-143, 147-196, 260-275 and pins
+them with the rows of its fixtures simple, five-bit, codebook, k-affine and k-signed.json, which
 tests/golden/quant_rows.json carries; the golden-row tests of test_gpu_matvec.py decode those on the
 device bit for bit. Here: random matrices through every operator entry point (row decode, one-token
 GEMV, 2..8 token rows, prefill tiles) against the CPU oracle, all through the C ABI.
@@ -15,7 +15,7 @@ from parity import assert_matvec_close, expect, make_case, rel_l2
 
 pytestmark = pytest.mark.gpu
 
-ENCODINGS = [enc.Q4_0, enc.Q5_0, enc.Q5_1, enc.Q5_K]
+ENCODINGS = [enc.Q4_0, enc.Q5_0, enc.Q5_1, enc.Q2_K, enc.Q3_K, enc.Q5_K]
 
 
 @pytest.fixture(scope="module")
