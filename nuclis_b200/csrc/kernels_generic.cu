@@ -7,10 +7,33 @@
 // specialized kernels are checked against on the device.
 #include <cuda_bf16.h>
 
+#include <utility>
+
 #include "kernels.hpp"
 #include "nu_device.cuh"
 
 namespace nu {
+
+// The small kernels of the expert chain are launched so that their blocks may be placed while the operator
+// before them drains; each starts with griddepcontrol.wait, after which the earlier operator's writes are
+// visible, so nothing else changes. Saves part of the launch latency between short dependent kernels.
+template <typename... KArgs, typename... Args>
+static void launch_after_previous(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t s, Args &&...args) {
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.stream = s;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+__device__ __forceinline__ void wait_for_previous_operator() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
+}
 
 // ---- row decode ------------------------------------------------------------
 
@@ -236,6 +259,7 @@ int launch_matmul_experts_generic(cudaStream_t s, uint32_t enc, const uint8_t *w
 
 __global__ void act_mul_rows_kernel(uint32_t act, const float *gate, const float *up, float *out, uint32_t width, uint32_t rows,
                                     size_t gate_stride, size_t up_stride, size_t out_stride) {
+    wait_for_previous_operator();
     const size_t id = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (id >= (size_t)width * rows) return;
     const size_t r = id / width, i = id % width;
@@ -247,7 +271,7 @@ __global__ void act_mul_rows_kernel(uint32_t act, const float *gate, const float
 int launch_act_mul_rows(cudaStream_t s, uint32_t act, const float *gate, const float *up, float *out,
                         uint32_t width, uint32_t rows, size_t gate_stride, size_t up_stride, size_t out_stride) {
     const size_t n = (size_t)width * rows;
-    act_mul_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(act, gate, up, out, width, rows, gate_stride, up_stride, out_stride);
+    launch_after_previous(act_mul_rows_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), s, act, gate, up, out, width, rows, gate_stride, up_stride, out_stride);
     return 1;
 }
 
@@ -264,6 +288,7 @@ __global__ void route_kernel(const float *logits, uint32_t experts, uint32_t k, 
     __shared__ float part_v[8];
     __shared__ uint32_t part_i[8];
     __shared__ float selected[ROUTE_MAX_K];
+    wait_for_previous_operator();
     const uint32_t row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const bool live = tid < experts;
     const float logit = live ? logits[(size_t)row * in_stride + tid] : -INFINITY;
@@ -319,7 +344,7 @@ __global__ void route_kernel(const float *logits, uint32_t experts, uint32_t k, 
 
 int launch_route(cudaStream_t s, const float *logits, uint32_t experts, uint32_t k, uint32_t rows, size_t in_stride,
                  uint32_t *indices, float *weights) {
-    route_kernel<<<rows, ROUTE_THREADS, 0, s>>>(logits, experts, k, in_stride, indices, weights);
+    launch_after_previous(route_kernel, dim3(rows), dim3(ROUTE_THREADS), s, logits, experts, k, in_stride, indices, weights);
     return 1;
 }
 
@@ -328,6 +353,7 @@ int launch_route(cudaStream_t s, const float *logits, uint32_t experts, uint32_t
 __global__ void combine_experts_kernel(const float *values, const float *weights, const uint32_t *indices, const float *scales,
                                        float *out, uint32_t columns, uint32_t slots, uint32_t rows, size_t in_stride, size_t out_stride,
                                        uint32_t experts) {
+    wait_for_previous_operator();
     const size_t id = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (id >= (size_t)columns * rows) return;
     const uint32_t row = (uint32_t)(id / columns), c = (uint32_t)(id % columns);
@@ -363,8 +389,8 @@ int launch_route_local(cudaStream_t s, const uint32_t *indices, const float *wei
 int launch_combine_experts(cudaStream_t s, const float *values, const float *weights, const uint32_t *indices, const float *scales,
                            float *out, uint32_t columns, uint32_t slots, uint32_t rows, size_t in_stride, size_t out_stride, uint32_t experts) {
     const size_t n = (size_t)columns * rows;
-    combine_experts_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(values, weights, indices, scales, out, columns, slots, rows,
-                                                                       in_stride, out_stride, experts);
+    launch_after_previous(combine_experts_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), s, values, weights, indices, scales, out, columns, slots, rows,
+                                                      in_stride, out_stride, experts);
     return 1;
 }
 
