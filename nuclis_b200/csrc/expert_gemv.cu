@@ -24,11 +24,12 @@
 //    16-byte piece p of each superblock's 128 quant bytes: 16 low nibbles of group 2(p/2) and 16 high
 //    nibbles of group 2(p/2)+1, columns 16(p&1).. of each; `w & 0x0f0f0f0f` is four codes ready for
 //    dp4a. The minima multiply exact F32 sums of x prepared once per chunk.
-//  * Q8_0: a warp per weight row, up to 8 rows per warp; a lane takes 8-code quarters of the 34-byte
-//    blocks; the int8 codes go to dp4a as they are.
-//  * The weight bytes travel with cp.async into small rings in shared memory, several superblocks (Q4_K)
-//    or rows (Q8_0, as 4-byte copies: its blocks are only 2-byte aligned) ahead of their use: the first
-//    versions held one 16-byte load per lane in flight and were bound by memory latency at 2.4 TB/s.
+//  * Q8_0: a block copies 32 weight rows into shared memory, then a lane per row and a warp per 32-column
+//    block: the digits of a block are one broadcast address for the warp, the int8 codes go to dp4a as
+//    they are (an earlier version gave a lane 8 codes at a time: twelve instructions per code all told).
+//  * The weight bytes travel with cp.async into shared memory (Q4_K: a ring, six superblocks ahead; Q8_0:
+//    the block's 32 rows at once, as 4-byte copies since its blocks are only 2-byte aligned) instead of
+//    being held in registers: the first versions had one 16-byte load per lane in flight.
 // Sums run in a fixed order: results do not depend on timing.
 #include "kernels.hpp"
 #include "nu_device.cuh"
@@ -225,36 +226,38 @@ __global__ void __launch_bounds__(XQ_THREADS) expert_gemv_q4k_kernel(const uint8
 }
 
 constexpr int X8_WARPS = 8;
-constexpr int X8_STAGES = 4;  // rows in flight per warp
+constexpr int X8_ROWS = 32;  // weight rows per block: a lane per row
 
 __global__ void __launch_bounds__(X8_WARPS * 32) expert_gemv_q8_0_kernel(const uint8_t *w, size_t stride, size_t expert_bytes, uint32_t experts, uint32_t rows,
-                                                                         uint32_t blocks, uint32_t rows_per_warp, const uint32_t *indices, const float *in,
-                                                                         size_t in_stride, uint32_t in_group, float *out, size_t out_stride) {
-    // [per warp: ring of X8_STAGES rows, `pitch` bytes each][3 planes of digits, blocks * 32 bytes each][blocks inverse scales]
+                                                                         uint32_t blocks, const uint32_t *indices, const float *in, size_t in_stride,
+                                                                         uint32_t in_group, float *out, size_t out_stride) {
+    // [32 weight rows, `pitch` words each][3 planes of digits, blocks * 32 bytes each][blocks inverse scales][8 x 32 part sums]
+    // A row is blocks * 34 / 4 whole words (the launcher takes an even number of blocks); the pitch is odd so that
+    // the 32 lanes of a warp, one row each, read 32 different banks.
     extern __shared__ __align__(16) uint8_t smem[];
-    const uint32_t words = blocks * 34 / 4;  // the launcher takes an even number of blocks only: rows are whole 4-byte words
-    const uint32_t pitch = (words * 4 + 15) & ~15u;
-    uint8_t *planes = smem + X8_WARPS * X8_STAGES * pitch;
+    const uint32_t words = blocks * 34 / 4;
+    const uint32_t pitch = words | 1u;
+    uint32_t *tile = (uint32_t *)smem;
+    uint8_t *planes = smem + (((size_t)X8_ROWS * pitch * 4 + 15) & ~(size_t)15);
     const uint32_t plane = blocks * 32;
     float *inv_scale = (float *)(planes + 3 * plane);
+    float *parts = inv_scale + blocks;
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;");
     const uint32_t slot = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t expert = min(indices[slot], experts - 1);
-    const uint8_t *base = w + (size_t)expert * expert_bytes;
-    // rows of this warp: r0, r0 + 1, ...; a row travels to the warp's ring as 4-byte copies, X8_STAGES - 1 rows ahead
-    const uint32_t r0 = (blockIdx.x * X8_WARPS + warp) * rows_per_warp;
-    const uint32_t nrows = r0 < rows ? min(rows_per_warp, rows - r0) : 0;
-    uint8_t *ring = smem + warp * X8_STAGES * pitch;
-    auto request = [&](uint32_t k) {
-        if (k < nrows) {
-            const uint8_t *src = base + (size_t)(r0 + k) * stride;
-            uint8_t *dst = ring + (k % X8_STAGES) * pitch;
-            for (uint32_t i = lane; i < words; i += 32) cp_async4(dst + i * 4, src + i * 4);
-        }
-        cp_async_commit();
-    };
-    for (uint32_t k = 0; k < X8_STAGES - 1; ++k) request(k);  // in flight while the input row is prepared
+    const uint32_t r0 = blockIdx.x * X8_ROWS;
+    const uint32_t nrows = min((uint32_t)X8_ROWS, rows - r0);
+    const uint8_t *base = w + (size_t)expert * expert_bytes + (size_t)r0 * stride;
+    // the block's rows travel to shared memory as 4-byte copies (the 34-byte blocks are only 2-byte aligned),
+    // consecutive threads on consecutive words of a row; all of them are in flight while the input row is prepared
+    // (warp w takes rows w, w + 8, ...; its lanes consecutive words: no division in the loop)
+    for (uint32_t r = warp; r < nrows; r += X8_WARPS) {
+        const uint8_t *src = base + (size_t)r * stride;
+        uint32_t *dst = tile + r * pitch;
+        for (uint32_t c = lane; c < words; c += 32) cp_async4(dst + c, src + c * 4);
+    }
+    cp_async_commit();
 
     const float *x = in + (size_t)(slot / in_group) * in_stride;
     // a warp per block of 32 columns, a lane per column
@@ -276,32 +279,54 @@ __global__ void __launch_bounds__(X8_WARPS * 32) expert_gemv_q8_0_kernel(const u
         planes[2 * plane + b * 32 + lane] = (uint8_t)p2;
         if (lane == 0) inv_scale[b] = inv;
     }
-    __syncthreads();
-    for (uint32_t k = 0; k < nrows; ++k) {
-        request(k + X8_STAGES - 1);
-        cp_async_wait<X8_STAGES - 1>();
-        __syncwarp();  // the whole row has landed: every lane's copies
-        const uint8_t *row = ring + (k % X8_STAGES) * pitch;
-        float acc = 0.0f;
-        // quarter qi of the row: block qi / 4, codes 8 (qi & 3) .. +7
-        for (uint32_t qi = lane; qi < blocks * 4; qi += 32) {
-            const uint8_t *blk = row + (qi >> 2) * 34;
-            const unsigned short *codes = (const unsigned short *)(blk + 2 + (qi & 3u) * 8);
-            const float d = __half2float(__ushort_as_half(*(const unsigned short *)blk));
-            const uint32_t w0 = (uint32_t)codes[0] | ((uint32_t)codes[1] << 16);
-            const uint32_t w1 = (uint32_t)codes[2] | ((uint32_t)codes[3] << 16);
-            const uint32_t off = qi * 8;
-            const uint2 d0 = *(const uint2 *)(planes + off), d1 = *(const uint2 *)(planes + plane + off), d2 = *(const uint2 *)(planes + 2 * plane + off);
-            const int a0 = dp4a_ss(w1, d0.y, dp4a_ss(w0, d0.x, 0));
-            const int a1 = dp4a_ss(w1, d1.y, dp4a_ss(w0, d1.x, 0));
-            const int a2 = dp4a_ss(w1, d2.y, dp4a_ss(w0, d2.x, 0));
-            acc = fmaf(d * inv_scale[qi >> 2], (float)(a2 * 16384 + a1 * 128 + a0), acc);
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);  // also: every lane is done with the stage before it is refilled
-        if (lane == 0) out[(size_t)slot * out_stride + r0 + k] = acc;
-    }
     cp_async_wait<0>();
+    __syncthreads();
+    // lane = row of the tile; warp w takes blocks w, w + 8, ...: the digits of a block are one address for the
+    // whole warp (a broadcast), the codes 32 different banks
+    float acc = 0.0f;
+    if (lane < nrows) {
+        const uint32_t *row = tile + lane * pitch;
+        for (uint32_t b = warp; b < blocks; b += X8_WARPS) {
+            // the block starts at byte 34 b of the row: scale in the low or high half of word 17 b / 2, codes after it
+            const uint32_t first = (b * 34) >> 2;
+            uint32_t c[8];
+            float d;
+            if (b & 1u) {  // bytes 34 b .. start in the middle of a word: scale high half, codes word-aligned
+                d = __half2float(__ushort_as_half((unsigned short)(row[first] >> 16)));
+#pragma unroll
+                for (int i = 0; i < 8; ++i) c[i] = row[first + 1 + i];
+            } else {       // scale low half, codes straddle words
+                uint32_t wv[9];
+#pragma unroll
+                for (int i = 0; i < 9; ++i) wv[i] = row[first + i];
+                d = __half2float(__ushort_as_half((unsigned short)(wv[0] & 0xffffu)));
+#pragma unroll
+                for (int i = 0; i < 8; ++i) c[i] = __funnelshift_r(wv[i], wv[i + 1], 16);
+            }
+            const uint4 *dg = (const uint4 *)(planes + b * 32);
+            const uint4 *dg1 = (const uint4 *)(planes + plane + b * 32), *dg2 = (const uint4 *)(planes + 2 * plane + b * 32);
+            int a0 = 0, a1 = 0, a2 = 0;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint4 q0 = dg[h], q1 = dg1[h], q2 = dg2[h];
+                a0 = dp4a_ss(c[4 * h], q0.x, a0); a0 = dp4a_ss(c[4 * h + 1], q0.y, a0); a0 = dp4a_ss(c[4 * h + 2], q0.z, a0); a0 = dp4a_ss(c[4 * h + 3], q0.w, a0);
+                a1 = dp4a_ss(c[4 * h], q1.x, a1); a1 = dp4a_ss(c[4 * h + 1], q1.y, a1); a1 = dp4a_ss(c[4 * h + 2], q1.z, a1); a1 = dp4a_ss(c[4 * h + 3], q1.w, a1);
+                a2 = dp4a_ss(c[4 * h], q2.x, a2); a2 = dp4a_ss(c[4 * h + 1], q2.y, a2); a2 = dp4a_ss(c[4 * h + 2], q2.z, a2); a2 = dp4a_ss(c[4 * h + 3], q2.w, a2);
+            }
+            // a digit sum is at most 32 * 128 * 64 = 2^18; times 2^14 it would not fit an int32: recombine in F32
+            // (each term is below 2^24 in magnitude and a multiple of its power of two, so the sum is exact to 2^-24 relative)
+            const float v = (float)a2 * 16384.0f + ((float)a1 * 128.0f + (float)a0);
+            acc = fmaf(d * inv_scale[b], v, acc);
+        }
+    }
+    parts[warp * 32 + lane] = acc;
+    __syncthreads();
+    if (warp == 0 && lane < nrows) {
+        float sum = 0.0f;
+#pragma unroll
+        for (int k = 0; k < X8_WARPS; ++k) sum += parts[k * 32 + lane];
+        out[(size_t)slot * out_stride + r0 + lane] = sum;
+    }
 }
 
 // NUCLIS_EXPERTS_GENERIC=1 keeps every expert GEMV on the generic kernel (for measurements and tests).
@@ -347,22 +372,18 @@ int launch_matvec_experts_fast(cudaStream_t s, uint32_t enc, const uint8_t *w, s
         if (columns % 64 != 0 || columns > kMaxColumns) return 0;
         if ((uintptr_t)w % 4 != 0 || stride % 4 != 0 || expert_bytes % 4 != 0) return 0;
         const uint32_t blocks = columns / 32;
-        const uint32_t pitch = (blocks * 34 + 15) & ~15u;
-        const size_t smem = (size_t)X8_WARPS * X8_STAGES * pitch + (size_t)blocks * (3 * 32 + 4);
+        const uint32_t pitch = (blocks * 34 / 4) | 1u;
+        const size_t smem = (((size_t)X8_ROWS * pitch * 4 + 15) & ~(size_t)15) + (size_t)blocks * (3 * 32 + 4) + X8_WARPS * 32 * 4;
         if (smem > 200 * 1024) return 0;
         static bool configured = false;
         if (!configured) {
             if (cudaFuncSetAttribute(expert_gemv_q8_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return 0;
             configured = true;
         }
-        // enough blocks to fill the machine a few times over, up to eight rows per warp
-        uint32_t rows_per_warp = (uint32_t)(((uint64_t)rows * slots) / (X8_WARPS * 148ull * 4));
-        rows_per_warp = rows_per_warp < 1 ? 1 : rows_per_warp > 8 ? 8 : rows_per_warp;
-        const uint32_t rows_per_block = rows_per_warp * X8_WARPS;
-        cfg.gridDim = dim3((rows + rows_per_block - 1) / rows_per_block, slots);
+        cfg.gridDim = dim3((rows + X8_ROWS - 1) / X8_ROWS, slots);
         cfg.blockDim = dim3(X8_WARPS * 32);
         cfg.dynamicSmemBytes = smem;
-        cudaLaunchKernelEx(&cfg, expert_gemv_q8_0_kernel, w, stride, expert_bytes, experts, rows, blocks, rows_per_warp, indices, in, in_stride, in_group, out, out_stride);
+        cudaLaunchKernelEx(&cfg, expert_gemv_q8_0_kernel, w, stride, expert_bytes, experts, rows, blocks, indices, in, in_stride, in_group, out, out_stride);
         return 1;
     }
     return 0;
