@@ -17,9 +17,9 @@
 //    split into three signed digits X = p2 * 2^14 + p1 * 2^7 + p0 with |p| <= 64, kept as three
 //    byte planes in shared memory. An element is off by at most 2^-21 of its chunk's largest value.
 //  * dp4a (four byte products added into an int32) then gives sum(code * p) exactly, for four
-//    weights per instruction and digit; the three digit sums are recombined in int32 (a digit sum is
-//    at most 16 * 15 * 64 for Q4_K and 8 * 128 * 64 = 2^16 for Q8_0, times 2^14: below 2^31),
-//    converted once and scaled by 2^-k and the block's scales in F32.
+//    weights per instruction and digit; the three digit sums are recombined (Q4_K: in int32, a digit
+//    sum is at most 16 * 15 * 64 and times 2^14 stays below 2^31; Q8_0: in F32, where 32 * 128 * 64 =
+//    2^18 times 2^14 would not fit) and scaled by 2^-k and the block's scales in F32.
 //  * Q4_K: 8 lanes per weight row, 4 rows per warp, 32 rows per block. Lane p of a row takes the
 //    16-byte piece p of each superblock's 128 quant bytes: 16 low nibbles of group 2(p/2) and 16 high
 //    nibbles of group 2(p/2)+1, columns 16(p&1).. of each; `w & 0x0f0f0f0f` is four codes ready for
