@@ -600,13 +600,18 @@ static int launch_geometry(cudaStream_t s, const FastJob &job, const Params &p) 
 }
 
 // The geometry follows the job: gate/up pairs on Pairs, everything else on Plain.
+// NUCLIS_DEC_PAIRS_COLUMNS=n in the environment also sends plain jobs of more than n columns to Pairs (for measurements).
+inline bool on_pairs(const FastJob &job) {
+    static const uint32_t wide = [] { const char *e = getenv("NUCLIS_DEC_PAIRS_COLUMNS"); return e ? (uint32_t)atoi(e) : 0u; }();
+    return job.mode != ACT_NONE || (wide && job.columns > wide);
+}
 template <class E>
 static bool fill_common(const FastJob &job, Params &p) {
-    return job.mode != ACT_NONE ? fill_geometry<E, Pairs>(job, p) : fill_geometry<E, Plain>(job, p);
+    return on_pairs(job) ? fill_geometry<E, Pairs>(job, p) : fill_geometry<E, Plain>(job, p);
 }
 template <class E>
 static int launch(cudaStream_t s, const FastJob &job, const Params &p) {
-    return job.mode != ACT_NONE ? launch_geometry<E, Pairs>(s, job, p) : launch_geometry<E, Plain>(s, job, p);
+    return on_pairs(job) ? launch_geometry<E, Pairs>(s, job, p) : launch_geometry<E, Plain>(s, job, p);
 }
 
 }  // namespace dec
