@@ -281,6 +281,14 @@ int nu_cuda_combine_experts(nu_cuda *h, const nu_buffer *values, const nu_buffer
  * Results are those of nu_cuda_matvec on the same data. */
 int nu_cuda_matvec_q4k_static(const void *weights, size_t stride, uint32_t rows, uint32_t columns,
                               const float *input, float *output, void *stream, char *err, size_t err_cap);
+/* Two helpers of the entry point above (no counterpart in the reference either; neither allocates).
+ * `_plan` is host arithmetic only: how many K slices and blocks a call of that shape would use on a
+ * GPU of `sm_count` multiprocessors (more than one slice means the built-in array is used), or
+ * NU_ERR_TOO_LARGE when no way to cut the shape fits the array. `_status` waits for `stream` and
+ * reads the word the kernel raises when one of its bounded waits ran out (0: all calls so far on
+ * this device completed their copies); the entry point itself only enqueues and cannot report that. */
+int nu_cuda_matvec_q4k_static_plan(uint32_t rows, uint32_t columns, uint32_t sm_count, uint32_t *slices, uint32_t *blocks);
+int nu_cuda_matvec_q4k_static_status(void *stream, uint32_t *status);
 
 /* ---- tensor-parallel collective (no reference analogue: the reference is
  * single-device) ---------------------------------------------------------- */

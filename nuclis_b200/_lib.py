@@ -82,6 +82,8 @@ SIGNATURES = {
     "nu_cuda_gelu_mul_rows": (cint, [vp, BP, BP, BP, sz, sz, sz, sz, sz]),
     "nu_cuda_combine_experts": (cint, [vp, BP, BP, BP, BP, BP, ctypes.POINTER(CCombineShape)]),
     "nu_cuda_matvec_q4k_static": (cint, [vp, sz, u32, u32, vp, vp, vp, ctypes.c_char_p, sz]),
+    "nu_cuda_matvec_q4k_static_plan": (cint, [u32, u32, u32, ctypes.POINTER(u32), ctypes.POINTER(u32)]),
+    "nu_cuda_matvec_q4k_static_status": (cint, [vp, ctypes.POINTER(u32)]),
     "nu_cuda_comm_unique_id": (cint, [u8p]),
     "nu_cuda_comm_init": (cint, [vp, u8p, cint, cint]),
     "nu_cuda_allreduce_sum_f32": (cint, [vp, BP, sz]),

@@ -283,17 +283,6 @@ int Backend::finishCapture(cudaGraphExec_t *exec) {
     return cuda(e, "commit: instantiate");
 }
 
-#ifdef NU_DEC_TRACE
-int Backend::debugTrace(unsigned long long *out, size_t words, int reset) {
-    cudaSetDevice(device_);
-    cudaStreamSynchronize(stream_);
-    unsigned long long *log = (unsigned long long *)(partials_ + (3u << 20));
-    if (out && words) cudaMemcpy(out, log, words * 8, cudaMemcpyDeviceToHost);
-    if (reset) cudaMemset(log, 0, 8 * (8 + 4000 * 8));
-    return NU_OK;
-}
-#endif
-
 int Backend::checkKernelStatus() {
     uint32_t status = 0;
     if (int rc = cuda(cudaMemcpyAsync(&status, counters_ + counters_len_, sizeof status, cudaMemcpyDeviceToHost, stream_), "status read")) return rc;
@@ -680,7 +669,7 @@ int Backend::matvecExpertsGrouped(const Buffer &weights, const ExpertMatrix &t, 
     float *out = (float *)resolve(output, ((slots - 1) * out_stride + t.rows) * 4);
     if (!w || !idx || !in || !out || indices.offset % 4 != 0 || output.offset % 4 != 0 || input.offset % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "experts: buffer too short");
     if (int rc = needRecording()) return rc;
-    int launched = launch_matvec_experts_fast(stream_, t.encoding, w, stride, per_expert, (uint32_t)t.experts, (uint32_t)t.rows, (uint32_t)t.columns, idx,
+    int launched = generic_only ? 0 : launch_matvec_experts_fast(stream_, t.encoding, w, stride, per_expert, (uint32_t)t.experts, (uint32_t)t.rows, (uint32_t)t.columns, idx,
                                               (uint32_t)slots, in, in_stride, (uint32_t)in_group, out, out_stride);
     if (!launched)
         launched = launch_matvec_experts_generic(stream_, t.encoding, w, stride, per_expert, (uint32_t)t.experts, (uint32_t)t.rows, (uint32_t)t.columns,
@@ -929,24 +918,27 @@ int Backend::allreduceSumF32(const Buffer &buffer, size_t count) {
 }
 
 int Backend::commDestroy() {
+    if (!peers_attached_ && !comm_) return NU_OK;
+    if (recording_) return fail(NU_ERR_ALREADY_RECORDING, "comm_destroy: a recording is open");
+    // A retained graph may hold kernels with the peers' inbox addresses baked in, or a collective that
+    // keeps the communicator busy. Retained graphs are therefore dropped with the group they may refer
+    // to, before the peer mappings are closed: a later graph_launch finds no graph instead of storing
+    // into unmapped memory.
+    cudaSetDevice(device_);
+    cudaStreamSynchronize(stream_);
+    for (auto &g : graphs_) cudaGraphExecDestroy(g.second);
+    graphs_.clear();
+    pending_ = false;
     if (peers_attached_) {
-        cudaSetDevice(device_);
-        cudaStreamSynchronize(stream_);
         for (int r = 0; r < peer_ranks_; ++r)
             if (r != peer_rank_ && peer_base_[r]) cudaIpcCloseMemHandle(peer_base_[r]);
         memset(peer_base_, 0, sizeof peer_base_);
         peers_attached_ = false;
     }
-    if (!comm_) return NU_OK;
-    if (recording_) return fail(NU_ERR_ALREADY_RECORDING, "comm_destroy: a recording is open");
-    // A retained graph that holds a collective keeps the communicator busy: NCCL waits for it.
-    // Retained graphs are therefore dropped with the group they may refer to.
-    cudaSetDevice(device_);
-    cudaStreamSynchronize(stream_);
-    for (auto &g : graphs_) cudaGraphExecDestroy(g.second);
-    graphs_.clear();
-    g_nccl.CommDestroy(comm_);
-    comm_ = nullptr;
+    if (comm_) {
+        g_nccl.CommDestroy(comm_);
+        comm_ = nullptr;
+    }
     ranks_ = 1;
     rank_ = 0;
     return NU_OK;
@@ -1104,13 +1096,6 @@ int nu_cuda_combine_experts(nu_cuda *h, const nu_buffer *values, const nu_buffer
 int nu_cuda_comm_unique_id(uint8_t id[NU_COMM_ID_BYTES]) { return id ? nu::unique_id(id) : NU_ERR_INVALID_SHAPE; }
 int nu_cuda_comm_init(nu_cuda *h, const uint8_t id[NU_COMM_ID_BYTES], int ranks, int rank) { NU_H(h); return h->b->commInit(id, ranks, rank); }
 int nu_cuda_allreduce_sum_f32(nu_cuda *h, const nu_buffer *buffer, size_t count) { NU_H(h); NU_P(buffer); return h->b->allreduceSumF32(*buffer, count); }
-#ifdef NU_DEC_TRACE
-// Trace builds only: the log the decode kernels append to (count word, then 8-word entries).
-extern "C" int nu_cuda_debug_trace(nu_cuda *h, unsigned long long *out, size_t words, int reset) {
-    NU_H(h);
-    return h->b->debugTrace(out, words, reset);
-}
-#endif
 int nu_cuda_comm_destroy(nu_cuda *h) { NU_H(h); return h->b->commDestroy(); }
 int nu_cuda_comm_peer_handle(nu_cuda *h, uint8_t handle[NU_PEER_HANDLE_BYTES]) { NU_H(h); return h->b->peerHandle(handle); }
 int nu_cuda_comm_attach_peers(nu_cuda *h, const uint8_t *handles, int ranks, int rank) { NU_H(h); return h->b->attachPeers(handles, ranks, rank); }

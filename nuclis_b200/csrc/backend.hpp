@@ -88,9 +88,6 @@ public:
     int peerHandle(uint8_t *out);
     int attachPeers(const uint8_t *handles, int ranks, int rank);
 
-#ifdef NU_DEC_TRACE
-    int debugTrace(unsigned long long *out, size_t words, int reset);
-#endif
     const char *lastError() const { return error_.c_str(); }
 
     static size_t matmulPadded(size_t tokens) { return (tokens + 63) / 64 * 64; }

@@ -126,7 +126,7 @@ __device__ __forceinline__ void write_unit(const Params &p, uint32_t unit, uint3
         uint32_t seg, row0;
         unit_rows(p, unit, seg, row0);
         const uint32_t seq = *(volatile const uint32_t *)p.push.seq;
-        const uint32_t tag = seq + 1;
+        const uint32_t tag = push_tag(seq);
         const size_t slot = ((size_t)(seq & 1u) * p.push.ranks + p.push.rank) * p.push.capacity;
 #pragma unroll 1
         for (uint32_t r = 0; r < p.push.ranks; ++r) {
@@ -174,13 +174,6 @@ __global__ void __launch_bounds__(G::THREADS, 1) decode_kernel(const __grid_cons
     const uint8_t *my_stage = stages + warp * STAGES * TASK_BYTES;
     const uint32_t stage0 = smem_u32(my_stage), bar0 = smem_u32(bars + warp * STAGES);
 
-#ifdef NU_DEC_TRACE
-    unsigned long long tr[5];
-#define NU_TRACE(i) do { asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tr[i])); } while (0)
-#else
-#define NU_TRACE(i)
-#endif
-    NU_TRACE(0);
     // Programmatic dependent launch: the next kernel of the stream may take an SM as soon as this
     // block leaves it, and this kernel starts its weight stream (weights are constant) while the
     // previous kernel is still finishing elsewhere. Everything that reads the previous kernel's
@@ -240,7 +233,6 @@ __global__ void __launch_bounds__(G::THREADS, 1) decode_kernel(const __grid_cons
     if (tid < 32) ((uint32_t *)zero)[tid] = 0;
     __syncthreads();  // still under the tail of the previous kernel
     asm volatile("griddepcontrol.wait;" ::: "memory");  // the previous kernel has ended; its writes are visible
-    NU_TRACE(1);
 
     // ---- stage the slice's activations, a superblock per warp at a time: scale, fp16 pieces, group sums ----
     // Warp w stages superblocks w, w + WARPS, ... of the slice (two float4 per lane each), with the
@@ -297,7 +289,6 @@ __global__ void __launch_bounds__(G::THREADS, 1) decode_kernel(const __grid_cons
             }
         }
     }
-    NU_TRACE(2);
 
     // ---- the task loop ----
     // Lanes whose B column is not theirs (column n = lane >> 2 belongs to quad lane n >> 1) read zeros.
@@ -380,7 +371,6 @@ __global__ void __launch_bounds__(G::THREADS, 1) decode_kernel(const __grid_cons
             write_unit(p, unit, g, acc[0], acc[1], acc2[0], acc2[1]);
         }
     }
-    NU_TRACE(3);
     if (p.nks > 1 && part == 0 && my_units) {
         // The last block to arrive for a unit adds the slices in order. Lanes announce 32 units at a
         // time (one round trip for all of them), then the warp finishes those it was last for.
@@ -422,7 +412,7 @@ __global__ void __launch_bounds__(G::THREADS, 1) decode_kernel(const __grid_cons
                             if (p.push.ranks) {
                                 const uint32_t seq = *(volatile const uint32_t *)p.push.seq;
                                 const size_t slot = ((size_t)(seq & 1u) * p.push.ranks + p.push.rank) * p.push.capacity;
-                                for (uint32_t r = 0; r < p.push.ranks; ++r) push_word(p.push.inbox[r] + slot + row0 + lane, sum, seq + 1);
+                                for (uint32_t r = 0; r < p.push.ranks; ++r) push_word(p.push.inbox[r] + slot + row0 + lane, sum, push_tag(seq));
                             } else {
                                 p.out[seg][row0 + lane] = sum;
                             }
@@ -433,19 +423,6 @@ __global__ void __launch_bounds__(G::THREADS, 1) decode_kernel(const __grid_cons
             }
         }
     }
-    NU_TRACE(4);
-#ifdef NU_DEC_TRACE
-    // absolute stamps of warp 0 of three blocks, appended to a log at the far end of the partial-sum scratch
-    if (lane == 0 && warp == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x / 2 || blockIdx.x == gridDim.x - 1)) {
-        unsigned long long *log = (unsigned long long *)(p.partials + (3u << 20));
-        const unsigned long long slot = atomicAdd(log, 1ull);
-        if (slot < 4000) {
-            unsigned long long *e = log + 8 + slot * 8;
-            e[0] = ((unsigned long long)p.units << 32) | blockIdx.x;
-            e[1] = tr[0]; e[2] = tr[1]; e[3] = tr[2]; e[4] = tr[3]; e[5] = tr[4];
-        }
-    }
-#endif
     if (failed) {
         if (lane == 0) atomicExch(p.status, 1u);
         // let this warp's copies still in flight land before the block's shared memory is released
@@ -463,11 +440,7 @@ static size_t smem_bytes(uint32_t ksl, int stages) {
            WARPS * stages * 8 + 128;
 }
 
-#ifdef NU_DEC_TRACE
-constexpr size_t kSmemMax = 226 * 1024;
-#else
 constexpr size_t kSmemMax = 227 * 1024;
-#endif
 constexpr uint32_t kMaxSliceSbs = 80;  // the staging pass keeps a slice of up to 20480 columns in registers
 
 // Deepest ring of task stages that fits beside the staged activations: the copies in flight hide HBM latency.
@@ -521,11 +494,11 @@ static bool fill_geometry(const FastJob &job, Params &p) {
     const uint32_t sms = (uint32_t)job.sm_count;
     double best = 1e30;
     uint32_t blocks[MAX_SLICES];
-    static const uint32_t forced_ksl = [] { const char *e = getenv("NUCLIS_DEC_KSL"); return e ? (uint32_t)atoi(e) : 0u; }();  // measurements only
     for (uint32_t ksl = 1; ksl <= p.ksb && ksl <= kMaxSliceSbs; ++ksl) {
-        if (forced_ksl && ksl != forced_ksl && forced_ksl <= p.ksb) continue;
         const uint32_t nks = (p.ksb + ksl - 1) / ksl;
         if (nks > MAX_SLICES || nks > sms) continue;
+        // a slicing whose partial sums or arrival counters do not fit the caller's scratch is no candidate
+        if (nks > 1 && ((size_t)nks * units * 32 > job.partials_floats || units > job.counters_len)) continue;
         const int st = pick_stages<E, G>(ksl);
         if (st < 2) continue;
         auto cost = [&](uint32_t s, uint32_t b) {
@@ -560,17 +533,7 @@ static bool fill_geometry(const FastJob &job, Params &p) {
     p.status = job.counters + job.counters_len;
     p.push = job.push;
     if (p.push.ranks && (job.mode != ACT_NONE || job.count != 1)) return false;  // one plain matrix only
-    if (p.nks > 1) {
-        if ((size_t)p.nks * units * 32 > job.partials_floats) return false;
-        if (units > job.counters_len) return false;
-    }
     return true;
-}
-
-// NUCLIS_NO_OVERLAP=1 in the environment launches every kernel fully serialised (for measurements).
-inline bool overlap_launches() {
-    static const bool on = [] { const char *e = getenv("NUCLIS_NO_OVERLAP"); return !(e && e[0] == '1'); }();
-    return on;
 }
 
 template <class E, class G>
@@ -588,7 +551,7 @@ static int launch_geometry(cudaStream_t s, const FastJob &job, const Params &p) 
     cfg.dynamicSmemBytes = bytes;
     cfg.stream = s;
     cfg.attrs = attr;
-    cfg.numAttrs = overlap_launches() && !job.serial ? 1 : 0;
+    cfg.numAttrs = job.serial ? 0 : 1;
     switch (stages) {
     case 6: cudaLaunchKernelEx(&cfg, decode_kernel<E, G, 6>, p); break;
     case 5: cudaLaunchKernelEx(&cfg, decode_kernel<E, G, 5>, p); break;
@@ -600,11 +563,7 @@ static int launch_geometry(cudaStream_t s, const FastJob &job, const Params &p) 
 }
 
 // The geometry follows the job: gate/up pairs on Pairs, everything else on Plain.
-// NUCLIS_DEC_PAIRS_COLUMNS=n in the environment also sends plain jobs of more than n columns to Pairs (for measurements).
-inline bool on_pairs(const FastJob &job) {
-    static const uint32_t wide = [] { const char *e = getenv("NUCLIS_DEC_PAIRS_COLUMNS"); return e ? (uint32_t)atoi(e) : 0u; }();
-    return job.mode != ACT_NONE || (wide && job.columns > wide);
-}
+inline bool on_pairs(const FastJob &job) { return job.mode != ACT_NONE; }
 template <class E>
 static bool fill_common(const FastJob &job, Params &p) {
     return on_pairs(job) ? fill_geometry<E, Pairs>(job, p) : fill_geometry<E, Plain>(job, p);

@@ -329,19 +329,22 @@ __global__ void __launch_bounds__(X8_WARPS * 32) expert_gemv_q8_0_kernel(const u
     }
 }
 
-// NUCLIS_EXPERTS_GENERIC=1 keeps every expert GEMV on the generic kernel (for measurements and tests).
-bool experts_generic_only() {
-    static const bool on = [] { const char *e = getenv("NUCLIS_EXPERTS_GENERIC"); return e && e[0] == '1'; }();
-    return on;
-}
-
 }  // namespace
+
+constexpr uint32_t kMaxColumns = 16384;  // shared memory: about 4 bytes a column
+
+// Opts both kernels into their dynamic shared memory sizes. The attribute belongs to the device that
+// is current, so this runs once per handle, with the handle's device current (fast_configure).
+bool expert_gemv_configure() {
+    return cudaFuncSetAttribute(expert_gemv_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(XQ_RING + kMaxColumns / 256 * (3 * 320 + 128))) == cudaSuccess &&
+           cudaFuncSetAttribute(expert_gemv_q8_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) == cudaSuccess;
+}
 
 // Returns the number of kernels launched: 0 when the shape is not one of the specialized forms.
 int launch_matvec_experts_fast(cudaStream_t s, uint32_t enc, const uint8_t *w, size_t stride, size_t expert_bytes, uint32_t experts, uint32_t rows,
                                uint32_t columns, const uint32_t *indices, uint32_t slots, const float *in, size_t in_stride, uint32_t in_group,
                                float *out, size_t out_stride) {
-    if (experts_generic_only() || slots > 65535) return 0;
+    if (slots > 65535) return 0;
     if ((uintptr_t)in % 16 != 0 || in_stride % 4 != 0) return 0;
     // The blocks may be placed while the operator before drains (the kernels wait for it before they read anything).
     cudaLaunchAttribute attr[1];
@@ -351,16 +354,10 @@ int launch_matvec_experts_fast(cudaStream_t s, uint32_t enc, const uint8_t *w, s
     cfg.stream = s;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    constexpr uint32_t kMaxColumns = 16384;  // shared memory: about 4 bytes a column
     if (enc == Q4_K) {
         if (columns % 256 != 0 || columns > kMaxColumns) return 0;
         if ((uintptr_t)w % 16 != 0 || stride % 16 != 0 || expert_bytes % 16 != 0) return 0;
         const uint32_t ksb = columns / 256;
-        static bool configured = false;
-        if (!configured) {
-            if (cudaFuncSetAttribute(expert_gemv_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(XQ_RING + kMaxColumns / 256 * (3 * 320 + 128))) != cudaSuccess) return 0;
-            configured = true;
-        }
         cfg.gridDim = dim3((rows + XQ_ROWS - 1) / XQ_ROWS, slots);
         cfg.blockDim = dim3(XQ_THREADS);
         cfg.dynamicSmemBytes = XQ_RING + (size_t)ksb * (3 * 320 + 128);
@@ -375,11 +372,6 @@ int launch_matvec_experts_fast(cudaStream_t s, uint32_t enc, const uint8_t *w, s
         const uint32_t pitch = (blocks * 34 / 4) | 1u;
         const size_t smem = (((size_t)X8_ROWS * pitch * 4 + 15) & ~(size_t)15) + (size_t)blocks * (3 * 32 + 4) + X8_WARPS * 32 * 4;
         if (smem > 200 * 1024) return 0;
-        static bool configured = false;
-        if (!configured) {
-            if (cudaFuncSetAttribute(expert_gemv_q8_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return 0;
-            configured = true;
-        }
         cfg.gridDim = dim3((rows + X8_ROWS - 1) / X8_ROWS, slots);
         cfg.blockDim = dim3(X8_WARPS * 32);
         cfg.dynamicSmemBytes = smem;

@@ -1,0 +1,265 @@
+// Q4_K GEMV and small-batch GEMM (1..8 activation rows) for sm_100a on the integer tensor path: the
+// kernel behind Backend.matvec, matvecRows, small matmul and matvecSegments on Q4_K weights
+// (inference/src/backends/metal/ops/matvec.zig:85-188, 268-343; the reference's kernels for this are
+// nu_matvec_q4_k, kernels/matvec.metal:161-209, and nu_matvec_rows_q4_k, kernels/matvec_rows.metal:34-128).
+//
+// The HBM stream is the only large traffic: every weight byte is read once, whatever the number of
+// activation rows. A task is 16 weight rows by one superblock (2304 bytes); one TMA tensor copy
+// (cp.async.bulk.tensor.2d + mbarrier) brings it to shared memory, each warp keeps its own ring of
+// stages filled a few tasks ahead.
+//
+// Arithmetic (i8_kernel.cuh has the scheme). A Q4_K superblock row holds 128 quant bytes: byte j of
+// the 32-byte chunk c carries element j of group 2c in its low nibble and of group 2c + 1 in its high
+// nibble. A word masked with 0x0f0f0f0f is four codes of the even group as bytes; masked with
+// 0xf0f0f0f0 it is four codes of the odd group times 16, still bytes (at most 240), so no shift is
+// spent: the odd groups get an accumulator of their own and the factor 16 is undone once per
+// superblock. One m16n8k32 mma covers one 32-column scale group of 16 rows: lane t of a quad supplies
+// the group's columns 8t..8t+7 (eight consecutive quant bytes, one 64-bit shared load per row), and
+// the 6-bit group scale multiplies the int32 sums afterwards. Per superblock and row:
+//   out += d * inv * sum_g s_g * sum_k(q * X)  -  dmin * inv * sum_g m_g * sum_k(X),
+// the factored form of kernels/matvec.metal:197 with X the fixed-point activations and inv the power
+// of two that scaled them. The minima go through the tensor core too: an m16n8k8 f16 step whose A
+// holds a row's eight 6-bit minima and whose B holds the eight group sums of X (as fp16 pieces hi + lo).
+#include "i8_kernel.cuh"
+
+#include "../../include/nuclis_cuda.h"
+
+namespace nu {
+namespace i8 {
+
+// The integer scales of one superblock row, its minima as an f16 pair for this lane's k slots, d and dmin.
+struct RowInts {
+    int s[8];
+    uint32_t mm;
+    float d, dmin;
+};
+__device__ __forceinline__ RowInts row_ints(const uint4 &hdr, uint32_t t) {
+    const uint32_t y = hdr.y, z = hdr.z, w = hdr.w;
+    // groups 0..3: low six bits of bytes 0..3 / 4..7; groups 4..7: nibbles of bytes 8..11 plus the top two bits of bytes 0..7
+    const uint32_t s_lo = y & 0x3f3f3f3fu, s_hi = (w & 0x0f0f0f0fu) | ((y >> 2) & 0x30303030u);
+    const uint32_t m_lo = z & 0x3f3f3f3fu, m_hi = ((w >> 4) & 0x0f0f0f0fu) | ((z >> 2) & 0x30303030u);
+    RowInts r;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        r.s[i] = (int)((s_lo >> (8 * i)) & 0xffu);
+        r.s[4 + i] = (int)((s_hi >> (8 * i)) & 0xffu);
+    }
+    // minima of groups 2t, 2t + 1: a byte b under the exponent byte 0x64 is the fp16 1024 + b
+    const uint32_t m4 = t < 2 ? m_lo : m_hi;
+    r.mm = hsub2(__byte_perm(m4, 0x64646464u, (t & 1u) ? 0x4342 : 0x4140), 0x64006400u);
+    r.d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
+    r.dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+    return r;
+}
+
+struct Q4K {
+    static constexpr int ROW_BYTES = 144;              // one superblock of one row
+    static constexpr int TASK_BYTES = 16 * ROW_BYTES;  // 2304, a multiple of 128
+
+    __device__ static __forceinline__ void issue(const Params &p, uint32_t seg, uint32_t sb, uint32_t row0, uint32_t dst, uint32_t bar, uint64_t policy) {
+        mbar_expect_tx(bar, TASK_BYTES);
+        tma_load_2d(dst, &p.map[seg], sb * ROW_BYTES, row0, bar, policy);
+    }
+
+    // One task: task rows gr and gr + 8 against every B column. xb: this lane's digit row at the task's
+    // superblock (its 8 bytes of group 0); the digit rows of the next mma (wide) lie 8 * pitch further.
+    // gsb: this lane's word of the group sums. iv: 1 / the activation scale of the lane's two tokens.
+    // acc: (row gr, token a), (gr, a + 1), (gr + 8, a), (gr + 8, a + 1).
+    template <bool WIDE>
+    __device__ static __forceinline__ void task(const uint8_t *task, const uint8_t *xb, uint32_t pitch, const uint8_t *gsb, uint32_t gs_step, float2 iv, float wl,
+                                                uint32_t gr, uint32_t t, float acc[4]) {
+        constexpr int NC = WIDE ? 3 : 1;
+        const uint8_t *r0 = task + gr * ROW_BYTES, *r1 = r0 + 8 * ROW_BYTES;
+        const uint4 h0 = *(const uint4 *)r0, h1 = *(const uint4 *)r1;
+        const RowInts a = row_ints(h0, t), b = row_ints(h1, t);
+        int ie[NC][4], io[NC][4];
+#pragma unroll
+        for (int j = 0; j < NC; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) ie[j][i] = io[j][i] = 0;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const uint2 q0 = *(const uint2 *)(r0 + 16 + c * 32 + t * 8), q1 = *(const uint2 *)(r1 + 16 + c * 32 + t * 8);
+            const uint32_t ae[4] = {q0.x & 0x0f0f0f0fu, q1.x & 0x0f0f0f0fu, q0.y & 0x0f0f0f0fu, q1.y & 0x0f0f0f0fu};
+            const uint32_t ao[4] = {q0.x & 0xf0f0f0f0u, q1.x & 0xf0f0f0f0u, q0.y & 0xf0f0f0f0u, q1.y & 0xf0f0f0f0u};
+#pragma unroll
+            for (int j = 0; j < NC; ++j) {
+                const uint2 be = *(const uint2 *)(xb + (size_t)j * 8 * pitch + (2 * c) * 32);
+                const uint2 bo = *(const uint2 *)(xb + (size_t)j * 8 * pitch + (2 * c + 1) * 32);
+                int ce[4], co[4];
+                imma_u8(ce, ae, be.x, be.y);
+                imma_u8(co, ao, bo.x, bo.y);
+                ie[j][0] += a.s[2 * c] * ce[0]; ie[j][1] += a.s[2 * c] * ce[1];
+                ie[j][2] += b.s[2 * c] * ce[2]; ie[j][3] += b.s[2 * c] * ce[3];
+                io[j][0] += a.s[2 * c + 1] * co[0]; io[j][1] += a.s[2 * c + 1] * co[1];
+                io[j][2] += b.s[2 * c + 1] * co[2]; io[j][3] += b.s[2 * c + 1] * co[3];
+            }
+        }
+        // 16 * sum_g s_g * sum(q * digit) per plane (below 2^29); wide: the planes recombined in F32
+        float f[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[i] = (float)((ie[0][i] << 4) + io[0][i]);
+            if (WIDE) f[i] = fmaf((float)((ie[2][i] << 4) + io[2][i]), 65536.0f, fmaf((float)((ie[1][i] << 4) + io[1][i]), 256.0f, f[i]));
+        }
+        const float iw0 = iv.x * wl, iw1 = iv.y * wl;
+        acc[0] = fmaf(f[0], a.d * iw0, acc[0]);
+        acc[1] = fmaf(f[1], a.d * iw1, acc[1]);
+        acc[2] = fmaf(f[2], b.d * iw0, acc[2]);
+        acc[3] = fmaf(f[3], b.d * iw1, acc[3]);
+        // the minima: sum_g m_g * (group sum of X * 2^-12), pieces hi + lo
+        float cm[4] = {0.f, 0.f, 0.f, 0.f};
+        hmma_k8(cm, a.mm, b.mm, *(const uint32_t *)gsb);
+        if (WIDE) hmma_k8(cm, a.mm, b.mm, *(const uint32_t *)(gsb + gs_step));
+        const float m0 = -4096.0f * a.dmin, m1 = -4096.0f * b.dmin;
+        acc[0] = fmaf(cm[0], m0 * iv.x, acc[0]);
+        acc[1] = fmaf(cm[1], m0 * iv.y, acc[1]);
+        acc[2] = fmaf(cm[2], m1 * iv.x, acc[2]);
+        acc[3] = fmaf(cm[3], m1 * iv.y, acc[3]);
+    }
+};
+
+// Plain one- and two-token jobs run 20 warps as 4 unit slots x 5 K parts (a 20-superblock row is then exactly
+// 4 tasks per warp and unit); gate/up pairs and the wide form run 16 warps as 4 x 4, which leaves more
+// shared memory to the digit rows and the ring.
+using Plain = Geometry<20, 5>;
+using Dense = Geometry<16, 4>;
+
+static bool on_dense(const FastJob &job) { return job.mode != ACT_NONE || job.tokens > 2; }
+
+static bool fill(const FastJob &job, Params &p, Plan &plan, bool maps) {
+    if (job.enc != Q4_K || job.layout != 0) return false;
+    if (!(on_dense(job) ? fill_geometry<Q4K, Dense>(job, p, plan) : fill_geometry<Q4K, Plain>(job, p, plan))) return false;
+    for (uint32_t s = 0; s < job.count; ++s) {
+        const FastSegment &g = job.seg[s];
+        if (g.stride % 16 != 0) return false;
+        if (maps && !encode_weight_map(&p.map[s], g.w, (uint64_t)p.ksb * 144, g.rows, g.stride, 144, 16)) return false;
+    }
+    return true;
+}
+
+static int launch(cudaStream_t s, const FastJob &job, const Params &p, const Plan &plan) {
+    return on_dense(job) ? launch_geometry<Q4K, Dense>(s, job, p, plan) : launch_geometry<Q4K, Plain>(s, job, p, plan);
+}
+
+}  // namespace i8
+
+bool q4k_i8_configure() { return i8::configure_wide<i8::Q4K, i8::Plain, false>() && i8::configure_geometry<i8::Q4K, i8::Dense>(); }
+
+bool q4k_i8_supported(const FastJob &job) {
+    i8::Params p;
+    i8::Plan plan;
+    return i8::fill(job, p, plan, false);
+}
+
+int launch_q4k_i8(cudaStream_t s, const FastJob &job) {
+    i8::Params p;
+    i8::Plan plan;
+    if (!i8::fill(job, p, plan, true)) return 0;
+    return i8::launch(s, job, p, plan);
+}
+
+bool q4k_i8_plan(const FastJob &job, uint32_t *slices, uint32_t *blocks) {
+    i8::Params p;
+    i8::Plan plan;
+    if (!i8::fill(job, p, plan, false)) return false;
+    if (slices) *slices = p.nks;
+    if (blocks) *blocks = plan.grid;
+    return true;
+}
+
+// ---- the entry point that allocates nothing ------------------------------------------------------
+// The split-K sums and arrival counters of the kernel normally live in memory the handle
+// allocated at creation. Here they live in an array that is part of the loaded library image.
+
+namespace {
+constexpr size_t kStaticPartialFloats = 256 * 1024;  // 1 MiB of partial sums
+constexpr size_t kStaticCounters = 4096;             // output tiles of 16 rows: matrices of up to 65,536 rows
+struct StaticScratch {
+    float partials[kStaticPartialFloats];
+    uint32_t counters[kStaticCounters + 1];  // + the status word the kernel raises when a bounded wait runs out
+};
+static __device__ __align__(256) StaticScratch g_static_scratch;
+
+struct StaticDevice {
+    bool ready = false;
+    StaticScratch *scratch = nullptr;  // the device address of g_static_scratch on this device
+    int sm_count = 0;
+};
+StaticDevice g_static_devices[64];
+
+FastJob static_job(const void *weights, size_t stride, uint32_t rows, uint32_t columns, const float *input, float *output, float *partials, uint32_t *counters,
+                   int sm_count) {
+    FastJob job{};
+    job.enc = Q4_K; job.layout = 0; job.columns = columns; job.tokens = 1; job.in = input; job.in_stride = columns;
+    job.count = 1; job.mode = ACT_NONE;
+    job.seg[0] = {(const uint8_t *)weights, stride, rows, output, rows};
+    job.partials = partials; job.partials_floats = kStaticPartialFloats;
+    job.counters = counters; job.counters_len = kStaticCounters;
+    job.sm_count = sm_count;
+    job.serial = true;  // the caller's stream may hold a kernel that writes these weights: no early start of the weight stream
+    return job;
+}
+}  // namespace
+
+}  // namespace nu
+
+extern "C" int nu_cuda_matvec_q4k_static_plan(uint32_t rows, uint32_t columns, uint32_t sm_count, uint32_t *slices, uint32_t *blocks) {
+    using namespace nu;
+    if (rows == 0 || columns == 0 || columns % 256 != 0 || sm_count == 0) return NU_ERR_INVALID_SHAPE;
+    if (rows > 65536u || columns > 20480u) return NU_ERR_TOO_LARGE;
+    // no device is touched: the pointers only have to look aligned
+    const FastJob job = static_job((const void *)256, (size_t)columns / 256 * 144, rows, columns, (const float *)256, (float *)256, (float *)256, (uint32_t *)256, (int)sm_count);
+    return q4k_i8_plan(job, slices, blocks) ? NU_OK : NU_ERR_TOO_LARGE;
+}
+
+extern "C" int nu_cuda_matvec_q4k_static(const void *weights, size_t stride, uint32_t rows, uint32_t columns, const float *input, float *output,
+                                         void *stream, char *err, size_t err_cap) {
+    using namespace nu;
+    auto fail = [&](int status, const char *what) {
+        if (err && err_cap) snprintf(err, err_cap, "%s", what);
+        return status;
+    };
+    if (!weights || !input || !output || rows == 0 || columns == 0) return fail(NU_ERR_INVALID_SHAPE, "matvec_q4k_static: null pointer or empty shape");
+    if (columns % 256 != 0 || stride != (size_t)columns / 256 * 144) return fail(NU_ERR_INVALID_SHAPE, "matvec_q4k_static: rows must be whole, contiguous Q4_K superblocks");
+    if ((uintptr_t)weights % 16 != 0 || (uintptr_t)input % 16 != 0 || (uintptr_t)output % 4 != 0)
+        return fail(NU_ERR_INVALID_SHAPE, "matvec_q4k_static: weights and input must be 16-byte aligned, output 4-byte aligned");
+    if (rows > 65536u || columns > 20480u)
+        return fail(NU_ERR_TOO_LARGE, "matvec_q4k_static: beyond the built-in scratch (65,536 rows, 20,480 columns, 1 MiB of partial sums)");
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return fail(NU_ERR_INIT, "matvec_q4k_static: no current CUDA device");
+    StaticDevice &d = g_static_devices[device];
+    if (!d.ready) {
+        // Once per device, with that device current: in host code the array's name is only a stand-in,
+        // the kernel needs the address the symbol has on this device.
+        void *ptr = nullptr;
+        cudaDeviceProp prop{};
+        if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || !ptr) return fail(NU_ERR_INIT, "matvec_q4k_static: cudaGetSymbolAddress failed");
+        if (cudaGetDeviceProperties(&prop, device) != cudaSuccess || prop.major != 10) return fail(NU_ERR_INIT, "matvec_q4k_static: needs an sm_100 device");
+        if (!q4k_i8_configure()) return fail(NU_ERR_INIT, "matvec_q4k_static: kernel set-up failed");
+        d.scratch = (StaticScratch *)ptr;
+        d.sm_count = prop.multiProcessorCount;
+        d.ready = true;
+    }
+    const FastJob job = static_job(weights, stride, rows, columns, input, output, d.scratch->partials, d.scratch->counters, d.sm_count);
+    i8::Params p;
+    i8::Plan plan;
+    if (!i8::fill(job, p, plan, true)) return fail(NU_ERR_TOO_LARGE, "matvec_q4k_static: no way to cut this shape fits the built-in scratch");
+    cudaStream_t s = (cudaStream_t)stream;
+    // The array keeps whatever the last call left: the counters and the status word must start at zero.
+    if (cudaMemsetAsync(d.scratch->counters, 0, sizeof d.scratch->counters, s) != cudaSuccess) return fail(NU_ERR_EXECUTION, "matvec_q4k_static: clearing the counters failed");
+    i8::launch(s, job, p, plan);
+    if (cudaGetLastError() != cudaSuccess) return fail(NU_ERR_EXECUTION, "matvec_q4k_static: launch failed");
+    return NU_OK;
+}
+
+extern "C" int nu_cuda_matvec_q4k_static_status(void *stream, uint32_t *status) {
+    using namespace nu;
+    int device = -1;
+    if (!status || cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return NU_ERR_INVALID_SHAPE;
+    StaticDevice &d = g_static_devices[device];
+    if (!d.ready) { *status = 0; return NU_OK; }
+    cudaStream_t s = (cudaStream_t)stream;
+    if (cudaMemcpyAsync(status, d.scratch->counters + kStaticCounters, sizeof *status, cudaMemcpyDeviceToHost, s) != cudaSuccess) return NU_ERR_EXECUTION;
+    return cudaStreamSynchronize(s) == cudaSuccess ? NU_OK : NU_ERR_EXECUTION;
+}

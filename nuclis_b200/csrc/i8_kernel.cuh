@@ -1,0 +1,609 @@
+// GEMV / small-batch GEMM skeleton on the integer tensor path (1..8 activation rows) shared by the
+// block encodings. The activation rows are turned into fixed point once per block: per token row and
+// superblock a power of two puts the largest |x| in [2^21, 2^22), X = round(x * 2^k), and X is cut into
+// three balanced base-256 digits X = d2*2^16 + d1*2^8 + d0, each in [-128, 127], kept as three planes of
+// bytes in shared memory. The weight codes stay what they are, bytes, so
+// mma.sync.m16n8k32.s32.u8.s8 gives sum(code * digit) exactly, 512 weights per instruction, and the
+// products need no conversion at all: one mask per four codes. The three digit sums are recombined
+// once per superblock (exactly in F32 up to the last bit), scaled by the superblock's F32 factors and
+// accumulated in F32. An element of x is off by at most 2^-22 of its superblock's largest value.
+//
+// The B operand's 8 columns hold (digit plane, token): with one or two tokens one mma serves all
+// three planes (column = plane * 2 + token); with three to eight tokens each plane takes an mma of its
+// own (column = token). The k index of an mma is a column within one scale group, so the group's
+// integer scale multiplies the int32 sums after the mma (one IMAD per accumulator register).
+//
+// An encoding supplies a policy class E: the bytes of a task (16 weight rows x one superblock), the
+// copy that fetches it, and the mma loop over one task. Work split, task ring, programmatic dependent
+// launch and the sums across K parts and K slices are those of the earlier fp16 skeleton
+// (decode_kernel.cuh), whose helpers this file uses.
+#pragma once
+#include "decode_kernel.cuh"
+
+namespace nu {
+namespace i8 {
+
+using dec::evict_first_policy;
+using dec::mbar_expect_tx;
+using dec::mbar_init;
+using dec::mbar_wait;
+using dec::named_barrier;
+using dec::push_word;
+using dec::smem_u32;
+using dec::tma_load_2d;
+
+constexpr int MAX_SLICES = 32;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+constexpr int SBW = 5;  // (token, superblock) pairs a warp stages at most: the staging pass keeps them in registers
+
+template <int W, int P>
+struct Geometry {
+    static constexpr int WARPS = W, PARTS = P, SLOTS = W / P, THREADS = W * 32;
+    static_assert(W % P == 0 && W <= 32 && W / P <= 8, "warps are unit slots x K parts; a named barrier per slot");
+};
+
+struct Params {
+    CUtensorMap map[4];   // per segment: uint8 [rows][row bytes], box 16 rows x one superblock
+    CUtensorMap map2[4];  // per segment: a second plane of the encoding, if it has one
+    float *out[4];
+    uint32_t out_stride[4];
+    uint32_t rows[4];
+    uint32_t tile_begin[5];  // first 16-row tile of each segment in the tile list
+    uint32_t count, mode, tokens;
+    uint32_t ksb, ksl, nks;  // superblocks per row, per slice; slices
+    uint32_t units;          // units per slice: 16-row tiles (pair mode: a gate tile with its up tile)
+    uint32_t blk_first[MAX_SLICES + 1];  // blocks blk_first[s] .. blk_first[s+1]-1 work on slice s
+    uint32_t plane_pitch;    // bytes between the digit rows of two B columns (32 mod 128: the eight rows a warp reads hit different banks)
+    uint32_t gs_pitch;       // bytes between the group-sum rows of two B columns (16 mod 128)
+    const float *in;
+    uint32_t in_stride;
+    float *partials;         // [slice][unit][pair half][record]
+    uint32_t *counters;      // per unit
+    uint32_t *status;        // set to 1 if a bounded wait ran out
+    PushTarget push;         // ranks > 0: output rows go to the ranks' inboxes instead of `out`
+};
+
+// C = A(16 x 32, unsigned bytes) x B(32 x 8, signed bytes), int32, starting from zero.
+__device__ __forceinline__ void imma_u8(int c[4], const uint32_t a[4], uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
+}
+// The same with signed codes.
+__device__ __forceinline__ void imma_s8(int c[4], const uint32_t a[4], uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
+}
+// C += A(16 x 8, f16) x B(8 x 8, f16): the minima (or biases) of a row against the group sums of x.
+__device__ __forceinline__ void hmma_k8(float c[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(b0));
+}
+__device__ __forceinline__ uint32_t hsub2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
+// Row of the task a lane's mma row g (0..7) stands for. Task rows are 144 bytes = 36 words apart, so the
+// eight-byte pieces the lanes of a half-warp (g = 0..3 or 4..7) read hit distinct banks only when their
+// rows are two apart: 0, 2, 4, 6 and 1, 3, 5, 7. Row g + 8 of the mma is task row row_of(g) + 8.
+__device__ __forceinline__ uint32_t row_of(uint32_t g) { return g < 4 ? 2 * g : 2 * g - 7; }
+
+template <bool WIDE>
+__host__ __device__ constexpr int plane_columns() { return WIDE ? 24 : 6; }  // digit rows staged: planes x tokens
+template <bool WIDE>
+__host__ __device__ constexpr int gs_columns() { return WIDE ? 16 : 4; }     // group-sum rows staged: (hi, lo) x tokens
+template <bool WIDE>
+__host__ __device__ constexpr int record_lanes() { return WIDE ? 32 : 8; }   // float4 a unit's sums take (narrow: quad lane 0 of each quad)
+
+__device__ __forceinline__ void unit_rows(const Params &p, uint32_t unit, uint32_t &seg, uint32_t &row0) {
+    seg = 0;
+#pragma unroll
+    for (int s = 1; s < 4; ++s)
+        if ((uint32_t)s < p.count && unit >= p.tile_begin[s]) seg = s;
+    row0 = (unit - p.tile_begin[seg]) * 16;
+}
+
+// Writes the finished sums a lane holds for a unit. v: (row r, token a), (row r, token a + 1), (row r + 8, a), (row r + 8, a + 1)
+// with r = row_of(g); narrow: a = 0 and only quad lane 0 holds sums; wide: a = 2t. w: the up sums in pair mode.
+template <bool WIDE>
+__device__ __forceinline__ void write_unit(const Params &p, uint32_t unit, uint32_t g, uint32_t t, const float v[4], const float w[4]) {
+    if (!WIDE && t != 0) return;
+    const uint32_t r = row_of(g), tok0 = WIDE ? 2 * t : 0;
+    if (p.mode != ACT_NONE) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t row = unit * 16 + r + 8 * h;
+            if (row >= p.rows[0]) continue;
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+                if (tok0 + c < p.tokens) {
+                    const float gate = v[2 * h + c];
+                    p.out[0][(size_t)(tok0 + c) * p.out_stride[0] + row] = (p.mode == ACT_SILU ? silu_f32(gate) : gelu_f32(gate)) * w[2 * h + c];
+                }
+        }
+        return;
+    }
+    uint32_t seg, row0;
+    unit_rows(p, unit, seg, row0);
+    if (p.push.ranks) {
+        // fused with the allreduce that follows (one token): the rows travel to every rank's inbox as (value, tag)
+        const uint32_t seq = *(volatile const uint32_t *)p.push.seq;
+        const uint32_t tag = push_tag(seq);
+        const size_t slot = ((size_t)(seq & 1u) * p.push.ranks + p.push.rank) * p.push.capacity;
+#pragma unroll 1
+        for (uint32_t k = 0; k < p.push.ranks; ++k) {
+            uint2 *dst = p.push.inbox[k] + slot + row0 + r;
+            if (row0 + r < p.rows[seg]) push_word(dst, v[0], tag);
+            if (row0 + r + 8 < p.rows[seg]) push_word(dst + 8, v[2], tag);
+        }
+        return;
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t row = row0 + r + 8 * h;
+        if (row >= p.rows[seg]) continue;
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+            if (tok0 + c < p.tokens) p.out[seg][(size_t)(tok0 + c) * p.out_stride[seg] + row] = v[2 * h + c];
+    }
+}
+
+// Shared memory: [task stages][digit rows][group-sum rows][16 zero bytes... see the kernel][1/scale per (superblock, token)]
+// [staged counts per superblock][part sums][barriers]
+template <class E, class G, bool WIDE>
+static size_t smem_bytes(uint32_t ksl, bool pair, int stages) {
+    const size_t plane_pitch = (size_t)ksl * 256 + 32;
+    const size_t gs_pitch = (size_t)ksl * 16 + (16 + 128 - ((size_t)ksl * 16) % 128) % 128;
+    const size_t parts = (size_t)G::SLOTS * 2 * (G::PARTS - 1) * (pair ? 2 : 1) * record_lanes<WIDE>() * 16;
+    return (size_t)G::WARPS * stages * E::TASK_BYTES + plane_columns<WIDE>() * plane_pitch + gs_columns<WIDE>() * gs_pitch + 128 + (size_t)ksl * 8 * 4 + (size_t)ksl * 4 +
+           parts + G::WARPS * stages * 8 + 256;
+}
+
+template <class E, class G, bool WIDE, int STAGES>
+__global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant__ Params p) {
+    constexpr int TASK_BYTES = E::TASK_BYTES;
+    constexpr int WARPS = G::WARPS, THREADS = G::THREADS, SLOTS = G::SLOTS, PARTS = G::PARTS;
+    constexpr int REC = record_lanes<WIDE>();
+    extern __shared__ __align__(128) uint8_t smem[];
+    const bool pair = p.mode != ACT_NONE;
+    uint8_t *stages = smem;
+    uint8_t *planes = stages + WARPS * STAGES * TASK_BYTES;
+    uint8_t *gs = planes + plane_columns<WIDE>() * p.plane_pitch;
+    uint8_t *zero = gs + gs_columns<WIDE>() * p.gs_pitch;      // 128 bytes of zeros (group sums of the B columns no token uses)
+    zero += (128u - (uint32_t)(zero - smem) % 128u) % 128u;
+    float *inv = (float *)(zero + 128);                        // [superblock of the slice][8 tokens]: 1 / the activation scale
+    uint32_t *ready = (uint32_t *)(inv + p.ksl * 8);           // per superblock: token rows staged
+    float4 *parts = (float4 *)(((uintptr_t)(ready + p.ksl) + 15) & ~(uintptr_t)15);
+    uint64_t *bars = (uint64_t *)(parts + SLOTS * 2 * (PARTS - 1) * (pair ? 2 : 1) * REC);
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t g = lane >> 2, t = lane & 3;
+    const uint32_t slot = warp / PARTS, part = warp % PARTS;
+    const uint8_t *my_stage = stages + warp * STAGES * TASK_BYTES;
+    const uint32_t stage0 = smem_u32(my_stage), bar0 = smem_u32(bars + warp * STAGES);
+
+    // Programmatic dependent launch: the next kernel of the stream may take an SM as soon as this
+    // block leaves it, and this kernel starts its weight stream (weights are constant) while the
+    // previous kernel is still finishing elsewhere. Everything that reads the previous kernel's
+    // output or writes global memory comes after the griddepcontrol.wait below.
+    asm volatile("griddepcontrol.launch_dependents;");
+    if (lane == 0) {
+        for (int i = 0; i < STAGES; ++i) mbar_init(bar0 + i * 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+
+    // ---- this block's slice and units ----
+    uint32_t ks = 0;
+    while (ks + 1 < p.nks && blockIdx.x >= p.blk_first[ks + 1]) ++ks;
+    const uint32_t sb0 = ks * p.ksl, n = min(p.ksl, p.ksb - sb0);
+    const uint32_t nblk = p.blk_first[ks + 1] - p.blk_first[ks], jblk = blockIdx.x - p.blk_first[ks];
+    // The first blocks of a slice take the units that do not divide evenly: blocks are dispatched in index
+    // order onto the SMs as the kernel before frees them, so the block that starts last has the least to do.
+    const uint32_t per_blk = p.units / nblk, extra = p.units - per_blk * nblk;
+    const uint32_t u_lo = jblk * per_blk + min(jblk, extra);
+    const uint32_t u_hi = u_lo + per_blk + (jblk < extra ? 1u : 0u);
+    const uint32_t np = min((uint32_t)PARTS, n);                          // warps that share a unit
+    const uint32_t m = part < n ? (n - part + PARTS - 1) / PARTS : 0;     // this warp's superblocks per unit
+    const uint32_t first_unit = u_lo + slot;
+    const uint32_t my_units = first_unit < u_hi ? (u_hi - first_unit + SLOTS - 1) / SLOTS : 0;
+    const uint32_t total = my_units * m * (pair ? 2u : 1u);
+    const uint64_t policy = evict_first_policy();
+
+    // ---- the weight stream: this warp's tasks in order (pair mode: gate then up of each superblock) ----
+    uint32_t issued = 0, p_stage = 0, p_unit = first_unit, p_j = 0, p_seg = 0, p_row0 = 0;
+    if (total) {
+        if (pair) p_row0 = p_unit * 16;
+        else unit_rows(p, p_unit, p_seg, p_row0);
+    }
+    auto issue = [&]() {
+        if (lane == 0) E::issue(p, p_seg, sb0 + part + PARTS * p_j, p_row0, stage0 + p_stage * TASK_BYTES, bar0 + p_stage * 8, policy);
+        ++issued;
+        p_stage = p_stage + 1 == STAGES ? 0 : p_stage + 1;
+        if (pair && p_seg == 0) { p_seg = 1; return; }
+        if (pair) p_seg = 0;
+        if (++p_j == m) {
+            p_j = 0;
+            p_unit += SLOTS;
+            if (pair) p_row0 = p_unit * 16;
+            else if (issued < total) unit_rows(p, p_unit, p_seg, p_row0);
+        }
+    };
+    for (int i = 0; i < STAGES - 1; ++i)
+        if (issued < total) issue();
+    for (uint32_t i = tid; i < p.ksl; i += THREADS) ready[i] = 0;
+    if (tid < 32) ((uint32_t *)zero)[tid] = 0;
+    __syncthreads();  // still under the tail of the previous kernel
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // the previous kernel has ended; its writes are visible
+
+    // ---- stage the slice's activations: a warp takes one (superblock, token) pair at a time ----
+    // Pairs are dealt superblock-major, so the first superblocks are complete first; a task waits for the
+    // count of its own superblock only and the first tasks start while later superblocks are still staged.
+    {
+        const uint32_t pairs = n * p.tokens;
+        float4 xa[SBW], xb2[SBW];
+#pragma unroll
+        for (int j = 0; j < SBW; ++j) {
+            const uint32_t q = warp + j * WARPS;
+            if (q < pairs) {
+                const uint32_t sb = q / p.tokens, tok = q - sb * p.tokens;
+                const float4 *src = (const float4 *)(p.in + (size_t)tok * p.in_stride) + (size_t)(sb0 + sb) * 64;
+                xa[j] = src[lane];
+                xb2[j] = src[32 + lane];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < SBW; ++j) {
+            const uint32_t q = warp + j * WARPS;
+            if (q < pairs) {  // uniform per warp
+                const uint32_t sb = q / p.tokens, tok = q - sb * p.tokens;
+                float mx = fmaxf(fmaxf(fmaxf(fabsf(xa[j].x), fabsf(xa[j].y)), fmaxf(fabsf(xa[j].z), fabsf(xa[j].w))),
+                                 fmaxf(fmaxf(fabsf(xb2[j].x), fabsf(xb2[j].y)), fmaxf(fabsf(xb2[j].z), fabsf(xb2[j].w))));
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                // 2^k puts the largest |x| in [2^21, 2^22). A row of zeros or of values below 2^-105 is staged as
+                // zeros; an infinity or a NaN makes the superblock's factor a NaN, as F32 arithmetic would the sums.
+                const uint32_t e = (__float_as_uint(mx) >> 23) & 0xffu;
+                const bool ok = e >= 22u && e < 255u;
+                const float scale = ok ? __uint_as_float((275u - e) << 23) : 0.0f;
+                // the digit rows of this token: B column of plane d is (narrow) d * 2 + token, (wide) d * 8 + token
+                uint8_t *row0 = planes + (size_t)tok * p.plane_pitch + sb * 256 + lane * 4;
+                const uint32_t plane_step = (WIDE ? 8u : 2u) * p.plane_pitch;
+                int gsum[2];
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf) {
+                    const float4 v = hf ? xb2[j] : xa[j];
+                    int x0 = ok ? __float2int_rn(v.x * scale) : 0, x1 = ok ? __float2int_rn(v.y * scale) : 0;
+                    int x2 = ok ? __float2int_rn(v.z * scale) : 0, x3 = ok ? __float2int_rn(v.w * scale) : 0;
+                    gsum[hf] = (x0 + x1) + (x2 + x3);
+#pragma unroll
+                    for (int d = 0; d < 3; ++d) {
+                        // the low bytes are the balanced digits; what is left is (x + 128) >> 8
+                        const uint32_t lo = __byte_perm((uint32_t)x0, (uint32_t)x1, 0x0040), hi = __byte_perm((uint32_t)x2, (uint32_t)x3, 0x0040);
+                        *(uint32_t *)(row0 + d * plane_step + hf * 128) = __byte_perm(lo, hi, 0x5410);
+                        x0 = (x0 + 128) >> 8; x1 = (x1 + 128) >> 8; x2 = (x2 + 128) >> 8; x3 = (x3 + 128) >> 8;
+                    }
+                }
+                // 32-column group sums of X (exact integers below 2^27), times 2^-12, as fp16 pieces hi + lo
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf) {
+                    int s = gsum[hf];
+                    s += __shfl_xor_sync(0xffffffffu, s, 1);
+                    s += __shfl_xor_sync(0xffffffffu, s, 2);
+                    s += __shfl_xor_sync(0xffffffffu, s, 4);
+                    if ((lane & 7u) == 0) {
+                        const float f = (float)s * 0.000244140625f;
+                        const __half sh = __float2half_rn(f), sl = __float2half_rn(f - __half2float(sh));
+                        const uint32_t grp = sb * 8 + hf * 4 + (lane >> 3);
+                        *(__half *)(gs + (size_t)tok * p.gs_pitch + grp * 2) = sh;
+                        *(__half *)(gs + (size_t)((WIDE ? 8u : 2u) + tok) * p.gs_pitch + grp * 2) = sl;
+                    }
+                }
+                if (lane == 0) inv[sb * 8 + tok] = ok ? __uint_as_float((e - 21u) << 23) : (e == 255u ? __uint_as_float(0x7fc00000u) : 0.0f);
+                __threadfence_block();
+                __syncwarp();
+                if (lane == 0) atomicAdd(ready + sb, 1u);
+            }
+        }
+    }
+
+    // ---- the task loop ----
+    // This lane's B column n = g. Narrow: column = plane * 2 + token, columns 6 and 7 and the columns of a
+    // token that is not there read column 0 (finite integers; their sums are never used). Wide: plane d is
+    // the mma d, column = token.
+    const uint32_t gr = row_of(g);
+    const uint8_t *xlane;
+    const uint8_t *gslane;
+    uint32_t gs_step;   // bytes from a lane's hi group sums to its lo group sums
+    if (WIDE) {
+        xlane = planes + (size_t)(g < p.tokens ? g : 0u) * p.plane_pitch + t * 8;
+        gslane = g < p.tokens ? gs + (size_t)g * p.gs_pitch + t * 4 : zero;
+        gs_step = g < p.tokens ? 8u * p.gs_pitch : 0u;
+    } else {
+        const bool used = g < 6 && (g & 1u) < p.tokens;
+        xlane = planes + (size_t)(used ? g : 0u) * p.plane_pitch + t * 8;
+        // the mma of the minima has columns (piece, token): 0, 1 hi; 2, 3 lo
+        const bool gs_used = g < 4 && (g & 1u) < p.tokens;
+        gslane = gs_used ? gs + (size_t)g * p.gs_pitch + t * 4 : zero;
+        gs_step = 0;
+    }
+    const uint32_t gs_sb = (gslane == zero) ? 0u : 16u;
+    // narrow: lane t holds the sums of digit plane t (weights 1, 2^8, 2^16; quad lane 3 holds nothing); 1/16 undoes
+    // the high nibbles left in place
+    const float wl = WIDE ? 0.0625f : (t == 0 ? 0.0625f : t == 1 ? 16.0f : t == 2 ? 4096.0f : 0.0f);
+    const uint32_t tok_a = WIDE ? 2 * t : 0;  // the token of a lane's accumulator columns 0 and 2 (1 and 3: the next one)
+    uint32_t c_stage = 0, c_phase = 0, consumed = 0;
+    bool failed = false;
+    uint32_t uidx = 0;
+    for (uint32_t unit = first_unit; unit < u_hi; unit += SLOTS, ++uidx) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
+        // After a wait has run out the warp stops computing but still walks its units, so that the
+        // warps it shares them with are not left at the barrier below.
+        for (uint32_t j = 0; j < m && !failed; ++j) {
+            const uint32_t sbw = part + PARTS * j;  // superblock within the slice
+            if (issued < total) issue();  // keep STAGES - 1 tasks in flight
+            if (uidx == 0) {
+                // the first unit may run ahead of the staging of its superblocks
+                uint32_t spins = 0;
+                while (*(volatile uint32_t *)(ready + sbw) < p.tokens && ++spins < SPIN_LIMIT) {}
+                if (*(volatile uint32_t *)(ready + sbw) < p.tokens) { failed = true; break; }
+                __threadfence_block();
+            }
+            if (!mbar_wait(bar0 + c_stage * 8, c_phase)) { failed = true; break; }
+            const float2 iv = *(const float2 *)(inv + sbw * 8 + tok_a);
+            E::template task<WIDE>(my_stage + c_stage * TASK_BYTES, xlane + sbw * 256, p.plane_pitch, gslane + sbw * gs_sb, gs_step, iv, wl, gr, t, acc);
+            __syncwarp();  // all lanes are done reading this stage before it is refilled
+            ++consumed;
+            if (++c_stage == STAGES) { c_stage = 0; c_phase ^= 1u; }
+            if (pair) {
+                if (issued < total) issue();
+                if (!mbar_wait(bar0 + c_stage * 8, c_phase)) { failed = true; break; }
+                E::template task<WIDE>(my_stage + c_stage * TASK_BYTES, xlane + sbw * 256, p.plane_pitch, gslane + sbw * gs_sb, gs_step, iv, wl, gr, t, acc2);
+                __syncwarp();
+                ++consumed;
+                if (++c_stage == STAGES) { c_stage = 0; c_phase ^= 1u; }
+            }
+        }
+        if (part >= np) continue;  // this warp has no superblocks in this slice
+        if (!WIDE) {
+            // the quad's lanes hold the three digit planes (and the two pieces of the minima): add them
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 1);
+                acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 2);
+                if (pair) {
+                    acc2[i] += __shfl_xor_sync(0xffffffffu, acc2[i], 1);
+                    acc2[i] += __shfl_xor_sync(0xffffffffu, acc2[i], 2);
+                }
+            }
+        }
+        // ---- the parts of the unit meet; part 0 adds them in part order ----
+        const bool holds = WIDE || t == 0;
+        const uint32_t rec = WIDE ? lane : g;
+        float4 *buf = parts + (size_t)((slot * 2 + (uidx & 1u)) * (PARTS - 1)) * (pair ? 2 : 1) * REC;
+        if (part > 0 && holds) {
+            float4 *dst = buf + (size_t)(part - 1) * (pair ? 2 : 1) * REC;
+            dst[rec] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            if (pair) dst[REC + rec] = make_float4(acc2[0], acc2[1], acc2[2], acc2[3]);
+        }
+        if (np > 1) named_barrier(1 + slot, 32 * np);
+        if (part != 0 || !holds) continue;
+        for (uint32_t k = 1; k < np; ++k) {
+            const float4 *src = buf + (size_t)(k - 1) * (pair ? 2 : 1) * REC;
+            const float4 v = src[rec];
+            acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+            if (pair) {
+                const float4 w = src[REC + rec];
+                acc2[0] += w.x; acc2[1] += w.y; acc2[2] += w.z; acc2[3] += w.w;
+            }
+        }
+        if (p.nks > 1) {
+            // several slices: leave the partial sums; they are published after the loop with one fence
+            float4 *dst = (float4 *)p.partials + ((size_t)ks * p.units + unit) * (pair ? 2 : 1) * REC;
+            dst[rec] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            if (pair) dst[REC + rec] = make_float4(acc2[0], acc2[1], acc2[2], acc2[3]);
+        } else {
+            write_unit<WIDE>(p, unit, g, t, acc, acc2);
+        }
+    }
+    if (p.nks > 1 && part == 0 && my_units) {
+        // The last block to arrive for a unit adds the slices in order. Lanes announce 32 units at a
+        // time (one round trip for all of them), then the warp finishes those it was last for.
+        __threadfence();
+        __syncwarp();
+        const bool holds = WIDE || t == 0;
+        const uint32_t rec = WIDE ? lane : g;
+        for (uint32_t base = 0; base < my_units; base += 32) {
+            const uint32_t mine_u = base + lane;
+            uint32_t last = 0;
+            if (mine_u < my_units) last = atomicAdd(p.counters + first_unit + mine_u * SLOTS, 1u) == p.nks - 1;
+            uint32_t mask = __ballot_sync(0xffffffffu, last != 0);
+            if (mask) __threadfence();
+            while (mask) {
+                const uint32_t u = base + (uint32_t)__ffs((int)mask) - 1;
+                mask &= mask - 1;
+                const uint32_t unit = first_unit + u * SLOTS;
+                if (holds) {
+                    const size_t per = (size_t)(pair ? 2 : 1) * REC;
+                    const float4 *src = (const float4 *)p.partials + (size_t)unit * per + rec;
+                    const size_t step = (size_t)p.units * per;
+                    float4 s = make_float4(0.f, 0.f, 0.f, 0.f), s2 = make_float4(0.f, 0.f, 0.f, 0.f);
+                    // (four loads in flight at a time; added in slice order)
+                    for (uint32_t k0 = 0; k0 < p.nks; k0 += 4) {
+                        float4 v[4], w[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            v[k] = k0 + k < p.nks ? __ldcg(src + (k0 + k) * step) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            w[k] = pair && k0 + k < p.nks ? __ldcg(src + (k0 + k) * step + REC) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            s.x += v[k].x; s.y += v[k].y; s.z += v[k].z; s.w += v[k].w;
+                            s2.x += w[k].x; s2.y += w[k].y; s2.z += w[k].z; s2.w += w[k].w;
+                        }
+                    }
+                    const float v4[4] = {s.x, s.y, s.z, s.w}, w4[4] = {s2.x, s2.y, s2.z, s2.w};
+                    write_unit<WIDE>(p, unit, g, t, v4, w4);
+                }
+                if (lane == 0) p.counters[unit] = 0;  // leave the scratch as it was found
+            }
+        }
+    }
+    if (failed) {
+        if (lane == 0) atomicExch(p.status, 1u);
+        // let this warp's copies still in flight land before the block's shared memory is released
+        for (; consumed < issued; ++consumed) {
+            mbar_wait(bar0 + c_stage * 8, c_phase);
+            if (++c_stage == STAGES) { c_stage = 0; c_phase ^= 1u; }
+        }
+    }
+}
+
+constexpr size_t kSmemMax = 227 * 1024;
+constexpr int kMaxStages = 6;
+
+struct Plan {
+    bool wide;
+    int stages;
+    uint32_t grid;
+    size_t smem;
+};
+
+template <class E, class G, bool WIDE>
+static int pick_stages(uint32_t ksl, bool pair) {
+    for (int st = kMaxStages; st >= 2; --st)
+        if (smem_bytes<E, G, WIDE>(ksl, pair, st) <= kSmemMax) return st;
+    return 0;
+}
+
+// Fills everything of Params that does not depend on the encoding's planes; the caller adds the tensor maps.
+// Picks the K slices and the blocks of each slice: every candidate slice length is costed in task
+// steps of the slowest block (units over unit slots, superblocks over K parts).
+template <class E, class G>
+static bool fill_geometry(const FastJob &job, Params &p, Plan &plan) {
+    constexpr int SLOTS = G::SLOTS, PARTS = G::PARTS;
+    if (job.tokens < 1 || job.tokens > 8 || job.count < 1 || job.count > 4) return false;
+    if (job.columns == 0 || job.columns % 256 != 0) return false;
+    if ((uintptr_t)job.in % 16 != 0 || job.in_stride % 4 != 0 || job.in_stride > 0xffffffffull) return false;
+    if (job.mode != ACT_NONE && (job.count != 2 || job.seg[0].rows != job.seg[1].rows)) return false;
+    memset(&p, 0, sizeof p);
+    p.count = job.count;
+    p.mode = job.mode;
+    p.tokens = job.tokens;
+    p.ksb = job.columns / 256;
+    p.in = job.in;
+    p.in_stride = (uint32_t)job.in_stride;
+    uint32_t tiles = 0;
+    for (uint32_t s = 0; s < job.count; ++s) {
+        const FastSegment &g = job.seg[s];
+        if (g.rows == 0 || (uintptr_t)g.w % 16 != 0 || (uintptr_t)g.out % 4 != 0 || g.out_stride > 0xffffffffull) return false;
+        p.out[s] = g.out;
+        p.out_stride[s] = (uint32_t)g.out_stride;
+        p.rows[s] = g.rows;
+        p.tile_begin[s] = tiles;
+        tiles += (g.rows + 15) / 16;
+    }
+    for (uint32_t s = job.count; s < 5; ++s) p.tile_begin[s] = tiles;
+    const bool pair = job.mode != ACT_NONE;
+    const uint32_t units = pair ? tiles / 2 : tiles;
+    const double per_sb = pair ? 2.0 : 1.0;  // tasks per superblock of a unit
+    p.units = units;
+    plan.wide = job.tokens > 2;
+    const size_t rec_floats = (size_t)(pair ? 2 : 1) * (plan.wide ? 32 : 8) * 4;  // partial sums a (slice, unit) leaves
+    const uint32_t sms = (uint32_t)job.sm_count;
+    double best = 1e30;
+    uint32_t blocks[MAX_SLICES];
+    for (uint32_t ksl = 1; ksl <= p.ksb; ++ksl) {
+        const uint32_t nks = (p.ksb + ksl - 1) / ksl;
+        if (nks > MAX_SLICES || nks > sms) continue;
+        if ((size_t)ksl * job.tokens > (size_t)SBW * G::WARPS) continue;  // the staging pass keeps the slice in registers
+        // a slicing whose partial sums or arrival counters do not fit the caller's scratch is no candidate
+        if (nks > 1 && ((size_t)nks * units * rec_floats > job.partials_floats || units > job.counters_len)) continue;
+        const int st = plan.wide ? pick_stages<E, G, true>(ksl, pair) : pick_stages<E, G, false>(ksl, pair);
+        if (st < 2) continue;
+        auto cost = [&](uint32_t s, uint32_t b) {
+            const uint32_t n = s + 1 == nks ? p.ksb - s * ksl : ksl;
+            const uint32_t units_blk = (units + b - 1) / b;
+            return (double)((units_blk + SLOTS - 1) / SLOTS) * ((double)((n + PARTS - 1) / PARTS) * per_sb + 0.35);
+        };
+        for (uint32_t s = 0; s < nks; ++s) blocks[s] = 1;
+        for (uint32_t left = sms - nks; left > 0; --left) {
+            uint32_t worst = 0;
+            for (uint32_t s = 1; s < nks; ++s)
+                if (cost(s, blocks[s]) > cost(worst, blocks[worst])) worst = s;
+            if (blocks[worst] >= units) break;
+            ++blocks[worst];
+        }
+        double est = 0;
+        for (uint32_t s = 0; s < nks; ++s) est = cost(s, blocks[s]) > est ? cost(s, blocks[s]) : est;
+        est *= st >= 4 ? 1.0 : st == 3 ? 1.06 : 1.2;  // a shallow ring hides less latency
+        est += (nks > 1 ? 5.0 + 0.3 * nks : 0.0) + 0.01 * ksl * job.tokens;  // partial sums, their fence and the last arriver's pass; staging of the slice
+        if (est < best - 1e-9) {
+            best = est;
+            p.ksl = ksl;
+            p.nks = nks;
+            plan.stages = st;
+            uint32_t first = 0;
+            for (uint32_t s = 0; s < nks; ++s) { p.blk_first[s] = first; first += blocks[s]; }
+            for (uint32_t s = nks; s <= MAX_SLICES; ++s) p.blk_first[s] = first;
+            plan.grid = first;
+        }
+    }
+    if (best >= 1e30) return false;
+    p.plane_pitch = p.ksl * 256 + 32;
+    p.gs_pitch = p.ksl * 16 + (16 + 128 - (p.ksl * 16) % 128) % 128;
+    plan.smem = plan.wide ? smem_bytes<E, G, true>(p.ksl, pair, plan.stages) : smem_bytes<E, G, false>(p.ksl, pair, plan.stages);
+    p.partials = job.partials;
+    p.counters = job.counters;
+    p.status = job.counters + job.counters_len;
+    p.push = job.push;
+    if (p.push.ranks && (job.mode != ACT_NONE || job.count != 1 || job.tokens != 1)) return false;  // one plain matrix, one token only
+    return true;
+}
+
+template <class E, class G, bool WIDE, int STAGES>
+static bool configure_one() {
+    return cudaFuncSetAttribute(i8_kernel<E, G, WIDE, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax) == cudaSuccess;
+}
+template <class E, class G, bool WIDE>
+static bool configure_wide() {
+    return configure_one<E, G, WIDE, 2>() && configure_one<E, G, WIDE, 3>() && configure_one<E, G, WIDE, 4>() && configure_one<E, G, WIDE, 5>() &&
+           configure_one<E, G, WIDE, 6>();
+}
+template <class E, class G>
+static bool configure_geometry() { return configure_wide<E, G, false>() && configure_wide<E, G, true>(); }
+
+template <class E, class G, bool WIDE>
+static void launch_stages(const cudaLaunchConfig_t &cfg, int stages, const Params &p) {
+    switch (stages) {
+    case 6: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, WIDE, 6>, p); break;
+    case 5: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, WIDE, 5>, p); break;
+    case 4: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, WIDE, 4>, p); break;
+    case 3: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, WIDE, 3>, p); break;
+    default: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, WIDE, 2>, p); break;
+    }
+}
+
+template <class E, class G>
+static int launch_geometry(cudaStream_t s, const FastJob &job, const Params &p, const Plan &plan) {
+    // launched so that it may overlap the tail of the kernel before it (see the kernel's prologue)
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(plan.grid);
+    cfg.blockDim = dim3(G::THREADS);
+    cfg.dynamicSmemBytes = plan.smem;
+    cfg.stream = s;
+    cfg.attrs = attr;
+    cfg.numAttrs = job.serial ? 0 : 1;
+    if (plan.wide) launch_stages<E, G, true>(cfg, plan.stages, p);
+    else launch_stages<E, G, false>(cfg, plan.stages, p);
+    return 1;
+}
+
+}  // namespace i8
+}  // namespace nu

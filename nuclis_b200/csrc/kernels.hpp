@@ -25,6 +25,7 @@ int launch_matmul_generic(cudaStream_t s, uint32_t enc, uint32_t layout, const u
 int launch_matvec_experts_fast(cudaStream_t s, uint32_t enc, const uint8_t *w, size_t stride, size_t expert_bytes, uint32_t experts, uint32_t rows,
                                uint32_t columns, const uint32_t *indices, uint32_t slots, const float *in, size_t in_stride, uint32_t in_group,
                                float *out, size_t out_stride);
+bool expert_gemv_configure();
 int launch_matvec_experts_generic(cudaStream_t s, uint32_t enc, const uint8_t *w, size_t stride, size_t expert_bytes,
                                   uint32_t experts, uint32_t rows, uint32_t columns, const uint32_t *indices, uint32_t slots,
                                   const float *in, size_t in_stride, uint32_t in_group, float *out, size_t out_stride);
@@ -56,6 +57,8 @@ struct PushTarget {
     uint32_t capacity;      // words per inbox slot
     const uint32_t *seq;    // the allreduce's sequence number in this rank's memory
 };
+// Tag of the words of call `seq`: never 0, which is what an inbox word holds before anything was pushed to it.
+__host__ __device__ inline uint32_t push_tag(uint32_t seq) { return seq + 1u ? seq + 1u : 1u; }
 struct FastSegment {
     const uint8_t *w;  // first row of the (expert's) matrix
     size_t stride;     // bytes per weight row
@@ -89,15 +92,13 @@ bool fast_configure();
 bool fast_supported(const FastJob &job);
 int launch_fast(cudaStream_t s, const FastJob &job);
 
-// ---- decode GEMV (one activation row) per encoding --------------------------------
-bool q4k_decode_configure();
-bool q4k_decode_supported(const FastJob &job);
-int launch_q4k_decode(cudaStream_t s, const FastJob &job);
-// 2..8 token rows on Q4_K (gemv_q4k_rows.cu)
-bool q4k_rows_configure();
-bool q4k_rows_one_token();
-bool q4k_rows_supported(const FastJob &job);
-int launch_q4k_rows(cudaStream_t s, const FastJob &job);
+// ---- 1..8 activation rows on Q4_K, integer tensor path (gemv_q4k_i8.cu) ------------
+bool q4k_i8_configure();
+bool q4k_i8_supported(const FastJob &job);
+int launch_q4k_i8(cudaStream_t s, const FastJob &job);
+// The K slices and blocks the launch would use (host arithmetic only).
+bool q4k_i8_plan(const FastJob &job, uint32_t *slices, uint32_t *blocks);
+// ---- decode GEMV (one activation row) on the planar forms --------------------------
 // 2..8 token rows on planar Q6_K (gemv_q6k_rows.cu)
 bool q6k_rows_configure();
 bool q6k_rows_supported(const FastJob &job);

@@ -4,7 +4,7 @@
 // costs ~20 us. This kernel costs one peer store and a local sum.
 //
 // Every rank owns an inbox in its own memory: [2 parities][ranks][capacity] words of 8 bytes, each
-// a float beside a 32-bit tag. A call with sequence number s uses parity s & 1 and tag s + 1:
+// a float beside a 32-bit tag. A call with sequence number s uses parity s & 1 and tag s + 1 (never 0):
 //   1. each rank stores (value, tag) for every element into slot [parity][its rank] of every
 //      peer's inbox: plain peer stores, so remote data is always written into the consumer's own
 //      memory and never loaded from a peer. An 8-byte store is single-copy atomic, so a reader
@@ -62,9 +62,20 @@ __global__ void __launch_bounds__(256) push_allreduce_kernel(PushParams p) {
         return;
     }
     const uint32_t seq = head[1];
-    const uint32_t parity = seq & 1u, tag = seq + 1;
+    const uint32_t parity = seq & 1u, tag = push_tag(seq);
     const uint32_t pairs = (p.count + 1) / 2;  // a thread moves two elements: one 16-byte word pair
     const uint32_t first = blockIdx.x * blockDim.x + tid, step = gridDim.x * blockDim.x;
+    // The sequence number is 32 bits wide and wraps after some 23 hours of decoding. A word that no call has
+    // rewritten for a whole period (the tail of a slot, beyond the longest vector summed lately) could then
+    // carry the tag of a new call. So twice per 2^30 calls (once per parity) a rank clears the tails of its
+    // own slots of this parity: no peer writes there during this call (a peer is at most one call ahead, on
+    // the other parity), and afterwards no word of the inbox is older than 2^30 calls.
+    if (((seq >> 1) & 0x1fffffffu) == 0u) {
+        const uint32_t cap_pairs = p.capacity / 2;
+        for (uint32_t r = 0; r < p.ranks; ++r)
+            for (uint32_t i = pairs + first; i < cap_pairs; i += step)
+                store_words((uint4 *)(p.inbox[p.rank] + ((size_t)parity * p.ranks + r) * p.capacity) + i, make_uint4(0u, 0u, 0u, 0u));
+    }
     // ---- 1. push (not when the producer of the vector pushed it already, into this rank's inbox too) ----
     for (uint32_t i = first; PUSH && i < pairs; i += step) {
         const float a = p.buf[2 * i], b = 2 * i + 1 < p.count ? p.buf[2 * i + 1] : 0.0f;

@@ -130,13 +130,6 @@ __global__ void __launch_bounds__(THREADS, 1) rows_kernel(const __grid_constant_
     // See decode_kernel.cuh: dependents may start now; this kernel reads its activations and writes
     // global memory only after the wait below, its weights (constants) before it.
     asm volatile("griddepcontrol.launch_dependents;");
-#ifdef NU_DEC_TRACE
-    unsigned long long tr[5];
-#define NU_RTRACE(i) do { asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tr[i])); } while (0)
-#else
-#define NU_RTRACE(i)
-#endif
-    NU_RTRACE(0);
     // every warp owns its ring: it initialises its own barriers and nobody else touches them
     if (lane == 0) {
         for (int i = 0; i < STAGES; ++i) mbar_init(bar0 + i * 8, 1);
@@ -179,7 +172,6 @@ __global__ void __launch_bounds__(THREADS, 1) rows_kernel(const __grid_constant_
     for (int i = 0; i < STAGES - 1; ++i)
         if (issued < total) issue();
     asm volatile("griddepcontrol.wait;" ::: "memory");  // the previous kernel has ended; its writes are visible
-    NU_RTRACE(1);
 
     // ---- stage the token rows of this slice: per-token scale, fp16 pieces in mma B order, group sums ----
     // Every thread requests all its float4 at once (the window is read from global memory once and kept
@@ -249,7 +241,6 @@ __global__ void __launch_bounds__(THREADS, 1) rows_kernel(const __grid_constant_
         }
     }
     __syncthreads();
-    NU_RTRACE(2);
 
     // ---- the task loop ----
     const uint8_t *xlane = xarr + g * p.arr_stride + t * PITCH;  // B column g, pair t of superblock 0 of the window
@@ -295,7 +286,6 @@ __global__ void __launch_bounds__(THREADS, 1) rows_kernel(const __grid_constant_
             write_tile<WIDE>(p, tile, g, t, val);
         }
     }
-    NU_RTRACE(3);
     if (p.nks > 1 && part == 0 && units) {
         // The last block to arrive for a row tile adds the slices in order. Lanes announce 32 tiles
         // at a time (one round trip for all of them), then the warp finishes those it was last for.
@@ -328,12 +318,6 @@ __global__ void __launch_bounds__(THREADS, 1) rows_kernel(const __grid_constant_
             }
         }
     }
-    NU_RTRACE(4);
-#ifdef NU_DEC_TRACE
-    if (lane == 0 && (warp == 0 || warp == 7) && (blockIdx.x == 0 || blockIdx.x == gridDim.x / 2 || blockIdx.x == gridDim.x - 1))
-        printf("RT block %u/%u warp %u ks %u n %u tiles %u..%u units %u m %u: waited %llu staged %llu loop %llu end %llu\n", blockIdx.x, gridDim.x, warp, ks, n, tile_lo, tile_hi,
-               units, m, tr[1] - tr[0], tr[2] - tr[0], tr[3] - tr[0], tr[4] - tr[0]);
-#endif
     if (failed) {
         if (lane == 0) atomicExch(p.status, 1u);
         // let this warp's copies still in flight land before the block's shared memory is released
@@ -392,6 +376,7 @@ static bool fill_common(const FastJob &job, Params &p, Plan &plan) {
     for (uint32_t ksl = 1; ksl <= p.ksb; ++ksl) {
         const uint32_t nks = (p.ksb + ksl - 1) / ksl;
         if (nks > MAX_SLICES || nks > sms) continue;
+        if (nks > 1 && ((size_t)nks * tiles * PARTIAL_FLOATS > job.partials_floats || tiles > job.counters_len)) continue;  // the scratch must hold it
         if ((size_t)job.tokens * ksl * 64 > (size_t)XV * THREADS) continue;  // the staging pass keeps the window in registers
         const uint32_t arr = ksl * 4 * PITCH + ((ksl * 4 * PITCH) % 128 == 64 ? 0 : 64);  // columns 64 bytes apart round the banks
         const uint32_t gs = ksl * E::GS_BYTES + (16 + 128 - (ksl * E::GS_BYTES) % 128) % 128;  // columns 16 bytes apart round the banks
@@ -431,10 +416,6 @@ static bool fill_common(const FastJob &job, Params &p, Plan &plan) {
     p.partials = job.partials;
     p.counters = job.counters;
     p.status = job.counters + job.counters_len;
-    if (p.nks > 1) {
-        if ((size_t)p.nks * tiles * PARTIAL_FLOATS > job.partials_floats) return false;
-        if (tiles > job.counters_len) return false;
-    }
     return true;
 }
 
@@ -470,7 +451,7 @@ static int launch(cudaStream_t s, const FastJob &job, const Params &p, const Pla
     cfg.dynamicSmemBytes = plan.wide ? smem_bytes<E, true>(p.arr_stride, p.gs_stride, plan.stages) : smem_bytes<E, false>(p.arr_stride, p.gs_stride, plan.stages);
     cfg.stream = s;
     cfg.attrs = attr;
-    cfg.numAttrs = dec::overlap_launches() && !job.serial ? 1 : 0;
+    cfg.numAttrs = job.serial ? 0 : 1;
     if (plan.wide) launch_wide<E, true>(cfg, plan.stages, p);
     else launch_wide<E, false>(cfg, plan.stages, p);
     return 1;

@@ -168,3 +168,43 @@ def test_one_layer_of_the_stack_matches_the_oracle(backend, tokens):
         assert_matvec_close(v.floats()[:kv], oracle.matvec(enc.Q4_K, kv, hidden, hv, h[0]), oracle.matvec_abs(enc.Q4_K, kv, hidden, hv, h[0]), "V rows")
     for buf in (wq, wk, wv, wo, wg, wu, wd, hb, q, k, v, o, g, u, d):
         b.release(buf)
+
+
+@pytest.mark.parametrize("name", ["silu_mul", "gelu_mul"])
+@pytest.mark.parametrize("count", [1, 33, 704, 17408])
+def test_gate_activations_match_the_oracle(backend, name, count):
+    """`siluMul` / `geluMul` alone (ops/rowwise.zig:209-233): gate[i] = act(gate[i]) * up[i] in place, against the
+    CPU forms (vector.zig:94-98, 178-181: evaluated in F64, rounded once). F32 `exp` / `tanh` on the device:
+    1 + tanh(u) cancels for negative gates, so the bound is absolute in the gate's size:
+    |error| <= 1e-6 * max(1, |gate|) * |up| + 1e-7; large |gate| values take the saturated branches."""
+    b = backend
+    rng = np.random.default_rng(count)
+    gate = (rng.standard_normal(count) * 4).astype(np.float32)
+    gate[:1] = 0.0
+    if count > 8:
+        gate[1:7] = [30.0, -30.0, 88.0, -88.0, 1e-8, -1e-8]
+    up = rng.standard_normal(count).astype(np.float32)
+    gb, ub = upload(b, gate), upload(b, up)
+    b.begin()
+    getattr(b, name)(gb, ub, count)
+    b.commit()
+    got = gb.floats()
+    act = oracle.silu(gate) if name == "silu_mul" else oracle.gelu(gate)
+    want = act.astype(np.float64) * up.astype(np.float64)
+    assert np.all(np.isfinite(got))
+    bound = 1e-6 * np.maximum(1.0, np.abs(gate)) * np.abs(up) + 1e-7
+    assert np.all(np.abs(got - want) <= bound), float(np.max(np.abs(got - want) / bound))
+    assert np.array_equal(ub.floats(), up)  # `up` is only read
+    b.release(gb); b.release(ub)
+
+
+def test_gate_activations_refuse_bad_calls(backend):
+    b = backend
+    gb, ub = b.create(64), b.create(64)
+    b.begin()
+    with pytest.raises(NuclisError):
+        b.gelu_mul(gb, ub, 17)   # 17 floats do not fit 64 bytes
+    with pytest.raises(NuclisError):
+        b.silu_mul(gb, ub, 0)
+    b.discard()
+    b.release(gb); b.release(ub)

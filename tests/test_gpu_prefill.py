@@ -99,6 +99,30 @@ def test_prefill_config_shapes_at_512_tokens(backend, case):
     run_matmul(backend, w, Matrix(encoding, rows, columns, w.size), x, BF16, check_tokens=[0, 1, 255, 256, 511], prepare=prepare)
 
 
+@pytest.mark.parametrize("tokens", [4096, 16384])
+@pytest.mark.parametrize("case", [(enc.Q4_K, 17408, 5120, False), (enc.Q6_K, 5120, 17408, True)])
+def test_prefill_config_shapes_at_the_large_token_counts(backend, case, tokens):
+    """The two large sizes of the prefill configuration. The oracle costs about 0.1 s per token row at these
+    shapes, so it checks a stated sample: 16 token rows spread over the first, a middle and the last token
+    tile (all weight rows of each), plus 256 random (token, weight row) pairs over the whole output; every
+    output element must be finite. Relative L2 <= 2e-2 per checked token row, per element 4e-3 * sum|w*x| + 1e-6."""
+    encoding, rows, columns, prepare = case
+    w = synth.matrix(encoding, rows, columns, seed=82)
+    rng = np.random.default_rng(83 + tokens)
+    x = rng.standard_normal((tokens, columns), dtype=np.float32)
+    mid = (tokens // 2 // 256) * 256
+    sample = [0, 1, 63, 64, 255, mid, mid + 1, mid + 127, mid + 128, mid + 255, tokens - 256, tokens - 129, tokens - 128, tokens - 65, tokens - 2, tokens - 1]
+    got = run_matmul(backend, w, Matrix(encoding, rows, columns, w.size), x, BF16, check_tokens=sample, prepare=prepare)
+    assert np.all(np.isfinite(got)), "non-finite output element"
+    stride = w.size // rows
+    xr = from_bf16_bits(to_bf16_bits(x))
+    for t, r in zip(rng.integers(0, tokens, 256), rng.integers(0, rows, 256)):
+        row = w[r * stride:(r + 1) * stride]
+        want = oracle.matvec(encoding, 1, columns, row, xr[t])[0]
+        mag = oracle.matvec_abs(encoding, 1, columns, row, xr[t])[0]
+        assert abs(got[t, r] - want) <= 4e-3 * mag + 1e-6, f"token {t} row {r}: {got[t, r]} against {want}"
+
+
 def test_prefill_contract(backend):
     rows, columns = 128, 512
     w = synth.matrix(enc.Q4_K, rows, columns, seed=1)

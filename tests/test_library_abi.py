@@ -65,3 +65,17 @@ def test_synthetic_blocks_decode_to_finite_values_and_are_seeded():
     assert sub.min() >= -32 and sub.max() <= 31
     q8 = synth.matrix(enc.Q8_0, 4, 256, seed=1).reshape(-1, 34)
     assert q8[:, 2:].view(np.int8).min() >= -127
+
+
+def test_static_entry_point_plans_its_whole_documented_range():
+    """The planner (host arithmetic) finds a cut that fits the built-in array up to the documented limits."""
+    lib = _lib.load()
+    slices, blocks = ctypes.c_uint32(), ctypes.c_uint32()
+    for rows, columns in ((65536, 20480), (50000, 20480), (65536, 256), (16, 20480), (5120, 17408)):
+        assert lib.nu_cuda_matvec_q4k_static_plan(rows, columns, 148, ctypes.byref(slices), ctypes.byref(blocks)) == 0, (rows, columns)
+        assert 1 <= slices.value <= 32 and 1 <= blocks.value <= 148
+        # partial sums of a cut: slices x 16-row tiles x 32 floats, inside 256 Ki floats
+        assert slices.value == 1 or slices.value * ((rows + 15) // 16) * 32 <= 256 * 1024
+    assert lib.nu_cuda_matvec_q4k_static_plan(65537, 256, 148, ctypes.byref(slices), ctypes.byref(blocks)) == 12
+    assert lib.nu_cuda_matvec_q4k_static_plan(16, 20736, 148, ctypes.byref(slices), ctypes.byref(blocks)) == 12
+    assert lib.nu_cuda_matvec_q4k_static_plan(16, 100, 148, ctypes.byref(slices), ctypes.byref(blocks)) == 4

@@ -23,11 +23,23 @@ def call_static(b, wb, m, xb, yb):
     return b._lib.nu_cuda_matvec_q4k_static(wb.device_ptr, stride, m.rows, m.columns, xb.device_ptr, yb.device_ptr, b.stream, err, len(err)), err.value.decode()
 
 
-@pytest.mark.parametrize("shape", [(5120, 5120), (1024, 2048), (80, 256)])
-def test_static_scratch_matvec_matches_the_ordinary_entry_point(shape):
+def planned_slices(b, rows, columns):
+    """K slices the entry point will cut this shape into on this GPU (more than one: the built-in array is used)."""
+    import torch
+    slices, blocks = ctypes.c_uint32(), ctypes.c_uint32()
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert b._lib.nu_cuda_matvec_q4k_static_plan(rows, columns, sms, ctypes.byref(slices), ctypes.byref(blocks)) == 0
+    return slices.value
+
+
+# (5120, 17408) and (2048, 20480) are cut along K, so their partial sums and arrival counters go through the
+# built-in array; the others fit one slice and never touch it.
+@pytest.mark.parametrize("shape,split", [((5120, 17408), True), ((2048, 20480), True), ((5120, 5120), False), ((1024, 2048), False), ((80, 256), False)])
+def test_static_scratch_matvec_matches_the_ordinary_entry_point(shape, split):
     rows, columns = shape
     b = Backend(0)
     try:
+        assert (planned_slices(b, rows, columns) > 1) == split
         w, x, m = make_case(enc.Q4_K, rows, columns, 1, seed=41)
         want, mag = expect(enc.Q4_K, rows, columns, w, x)
         wb = b.wrap(w)
@@ -46,6 +58,8 @@ def test_static_scratch_matvec_matches_the_ordinary_entry_point(shape):
             got = y_new.floats()  # the download waits for the backend's stream, on which the kernel ran
             assert_matvec_close(got, want[0], mag[0], f"static scratch {shape} call {call}")
             assert np.allclose(got, ref, rtol=1e-5, atol=1e-6), f"call {call} differs from nu_cuda_matvec"
+            word = ctypes.c_uint32(7)
+            assert b._lib.nu_cuda_matvec_q4k_static_status(b.stream, ctypes.byref(word)) == 0 and word.value == 0
     finally:
         b.deinit()
 
