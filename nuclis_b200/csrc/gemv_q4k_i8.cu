@@ -4,9 +4,9 @@
 // nu_matvec_q4_k, kernels/matvec.metal:161-209, and nu_matvec_rows_q4_k, kernels/matvec_rows.metal:34-128).
 //
 // The HBM stream is the only large traffic: every weight byte is read once, whatever the number of
-// activation rows. A task is 16 weight rows by one superblock (2304 bytes); one TMA tensor copy
-// (cp.async.bulk.tensor.2d + mbarrier) brings it to shared memory, each warp keeps its own ring of
-// stages filled a few tasks ahead.
+// activation rows. A task is 16 weight rows by one superblock (2304 bytes). The five warps of a unit slot
+// share a ring of stages; one TMA tensor copy (cp.async.bulk.tensor.2d + mbarrier) brings 16 rows by five
+// superblocks (11,520 bytes, 720 contiguous bytes per row) into a stage, one task for each of the five.
 //
 // Arithmetic (i8_kernel.cuh has the scheme). A Q4_K superblock row holds 128 quant bytes: byte j of
 // the 32-byte chunk c carries element j of group 2c in its low nibble and of group 2c + 1 in its high
@@ -41,8 +41,8 @@ __device__ __forceinline__ RowInts row_ints(const uint4 &hdr, uint32_t t) {
     RowInts r;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        r.s[i] = (int)((s_lo >> (8 * i)) & 0xffu);
-        r.s[4 + i] = (int)((s_hi >> (8 * i)) & 0xffu);
+        r.s[i] = (int)__byte_perm(s_lo, 0u, 0x4440 + i);      // byte i alone: one permute
+        r.s[4 + i] = (int)__byte_perm(s_hi, 0u, 0x4440 + i);
     }
     // minima of groups 2t, 2t + 1: a byte b under the exponent byte 0x64 is the fp16 1024 + b
     const uint32_t m4 = t < 2 ? m_lo : m_hi;
@@ -53,23 +53,31 @@ __device__ __forceinline__ RowInts row_ints(const uint4 &hdr, uint32_t t) {
 }
 
 struct Q4K {
-    static constexpr int ROW_BYTES = 144;              // one superblock of one row
-    static constexpr int TASK_BYTES = 16 * ROW_BYTES;  // 2304, a multiple of 128
+    static constexpr int ROW_BYTES = 144;                 // one superblock of one row
+    static constexpr int STAGE_SBS = 5;                   // superblocks of a row a stage holds: one per warp of a slot
+    static constexpr int ROW_PITCH = STAGE_SBS * ROW_BYTES;  // 720 bytes = 180 words between the rows of a stage: rows two apart
+                                                          // lie 8 banks apart, which the lanes' 8-byte loads need (row_of)
+    static constexpr int STAGE_BYTES = 16 * ROW_PITCH;    // 11520, a multiple of 128
 
+    // One box of 16 rows x 720 bytes. Measured on B200: boxes of 16 x 144 bytes stream at 3.3 TB/s however many are
+    // in flight (the copy engine's cost is per row of a box), 16 x 720 bytes at 6.2 TB/s. The tensor map counts in
+    // 4-byte elements (a box side is at most 256 elements). Superblocks past the row are filled with zeros.
     __device__ static __forceinline__ void issue(const Params &p, uint32_t seg, uint32_t sb, uint32_t row0, uint32_t dst, uint32_t bar, uint64_t policy) {
-        mbar_expect_tx(bar, TASK_BYTES);
-        tma_load_2d(dst, &p.map[seg], sb * ROW_BYTES, row0, bar, policy);
+        mbar_expect_tx(bar, STAGE_BYTES);
+        tma_load_2d(dst, &p.map[seg], sb * (ROW_BYTES / 4), row0, bar, policy);
     }
 
     // One task: task rows gr and gr + 8 against every B column. xb: this lane's digit row at the task's
     // superblock (its 8 bytes of group 0); the digit rows of the next mma (wide) lie 8 * pitch further.
-    // gsb: this lane's word of the group sums. iv: 1 / the activation scale of the lane's two tokens.
-    // acc: (row gr, token a), (gr, a + 1), (gr + 8, a), (gr + 8, a + 1).
-    template <bool WIDE>
-    __device__ static __forceinline__ void task(const uint8_t *task, const uint8_t *xb, uint32_t pitch, const uint8_t *gsb, uint32_t gs_step, float2 iv, float wl,
+    // gsb: this lane's word of the group sums. iv: 1 / the activation scale of the lane's token(s) at this superblock.
+    // acc: (row gr, token a), (gr, a + 1), (gr + 8, a), (gr + 8, a + 1); with one token the odd entries stay untouched.
+    template <int NT>
+    __device__ static __forceinline__ void task(const uint8_t *task, const uint8_t *xb, uint32_t pitch, const uint8_t *gsb, uint32_t gs_step, const float *iv, float wl,
                                                 uint32_t gr, uint32_t t, float acc[4]) {
+        constexpr bool WIDE = NT == 8;
         constexpr int NC = WIDE ? 3 : 1;
-        const uint8_t *r0 = task + gr * ROW_BYTES, *r1 = r0 + 8 * ROW_BYTES;
+        constexpr int STEP = NT == 1 ? 2 : 1;  // one token: accumulator columns 0 and 2 only
+        const uint8_t *r0 = task + gr * ROW_PITCH, *r1 = r0 + 8 * ROW_PITCH;
         const uint4 h0 = *(const uint4 *)r0, h1 = *(const uint4 *)r1;
         const RowInts a = row_ints(h0, t), b = row_ints(h1, t);
         int ie[NC][4], io[NC][4];
@@ -89,62 +97,58 @@ struct Q4K {
                 int ce[4], co[4];
                 imma_u8(ce, ae, be.x, be.y);
                 imma_u8(co, ao, bo.x, bo.y);
-                ie[j][0] += a.s[2 * c] * ce[0]; ie[j][1] += a.s[2 * c] * ce[1];
-                ie[j][2] += b.s[2 * c] * ce[2]; ie[j][3] += b.s[2 * c] * ce[3];
-                io[j][0] += a.s[2 * c + 1] * co[0]; io[j][1] += a.s[2 * c + 1] * co[1];
-                io[j][2] += b.s[2 * c + 1] * co[2]; io[j][3] += b.s[2 * c + 1] * co[3];
+#pragma unroll
+                for (int i = 0; i < 4; i += STEP) {
+                    ie[j][i] += (i < 2 ? a.s[2 * c] : b.s[2 * c]) * ce[i];
+                    io[j][i] += (i < 2 ? a.s[2 * c + 1] : b.s[2 * c + 1]) * co[i];
+                }
             }
         }
-        // 16 * sum_g s_g * sum(q * digit) per plane (below 2^29); wide: the planes recombined in F32
-        float f[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            f[i] = (float)((ie[0][i] << 4) + io[0][i]);
-            if (WIDE) f[i] = fmaf((float)((ie[2][i] << 4) + io[2][i]), 65536.0f, fmaf((float)((ie[1][i] << 4) + io[1][i]), 256.0f, f[i]));
-        }
-        const float iw0 = iv.x * wl, iw1 = iv.y * wl;
-        acc[0] = fmaf(f[0], a.d * iw0, acc[0]);
-        acc[1] = fmaf(f[1], a.d * iw1, acc[1]);
-        acc[2] = fmaf(f[2], b.d * iw0, acc[2]);
-        acc[3] = fmaf(f[3], b.d * iw1, acc[3]);
         // the minima: sum_g m_g * (group sum of X * 2^-12), pieces hi + lo
         float cm[4] = {0.f, 0.f, 0.f, 0.f};
         hmma_k8(cm, a.mm, b.mm, *(const uint32_t *)gsb);
         if (WIDE) hmma_k8(cm, a.mm, b.mm, *(const uint32_t *)(gsb + gs_step));
-        const float m0 = -4096.0f * a.dmin, m1 = -4096.0f * b.dmin;
-        acc[0] = fmaf(cm[0], m0 * iv.x, acc[0]);
-        acc[1] = fmaf(cm[1], m0 * iv.y, acc[1]);
-        acc[2] = fmaf(cm[2], m1 * iv.x, acc[2]);
-        acc[3] = fmaf(cm[3], m1 * iv.y, acc[3]);
+        const float iv0 = iv[0], iv1 = NT == 1 ? 0.0f : iv[1];
+        const float dm0 = -4096.0f * a.dmin, dm1 = -4096.0f * b.dmin;
+#pragma unroll
+        for (int i = 0; i < 4; i += STEP) {
+            // 16 * sum_g s_g * sum(q * digit) per plane (below 2^29); wide: the planes recombined in F32
+            float f = (float)((ie[0][i] << 4) + io[0][i]);
+            if (WIDE) f = fmaf((float)((ie[2][i] << 4) + io[2][i]), 65536.0f, fmaf((float)((ie[1][i] << 4) + io[1][i]), 256.0f, f));
+            const float ivi = (i & 1) ? iv1 : iv0;
+            acc[i] = fmaf(f, (i < 2 ? a.d : b.d) * (ivi * wl), acc[i]);
+            acc[i] = fmaf(cm[i], (i < 2 ? dm0 : dm1) * ivi, acc[i]);
+        }
     }
 };
 
-// Plain one- and two-token jobs run 20 warps as 4 unit slots x 5 K parts (a 20-superblock row is then exactly
-// 4 tasks per warp and unit); gate/up pairs and the wide form run 16 warps as 4 x 4, which leaves more
-// shared memory to the digit rows and the ring.
+// One- and two-token jobs (plain or gate/up pairs) run 20 warps as 4 unit slots x 5 K parts; the wide form
+// (three to eight tokens, 128 registers a thread) runs 15 warps as 3 x 5.
 using Plain = Geometry<20, 5>;
-using Dense = Geometry<16, 4>;
+using Dense = Geometry<15, 5>;
 
-static bool on_dense(const FastJob &job) { return job.mode != ACT_NONE || job.tokens > 2; }
 
 static bool fill(const FastJob &job, Params &p, Plan &plan, bool maps) {
     if (job.enc != Q4_K || job.layout != 0) return false;
-    if (!(on_dense(job) ? fill_geometry<Q4K, Dense>(job, p, plan) : fill_geometry<Q4K, Plain>(job, p, plan))) return false;
+    const bool ok = job.tokens == 1 ? fill_geometry<Q4K, Plain, 1>(job, p, plan) : job.tokens == 2 ? fill_geometry<Q4K, Plain, 2>(job, p, plan) : fill_geometry<Q4K, Dense, 8>(job, p, plan);
+    if (!ok) return false;
     for (uint32_t s = 0; s < job.count; ++s) {
         const FastSegment &g = job.seg[s];
         if (g.stride % 16 != 0) return false;
-        if (maps && !encode_weight_map(&p.map[s], g.w, (uint64_t)p.ksb * 144, g.rows, g.stride, 144, 16)) return false;
+        if (maps && !encode_tiled_map(&p.map[s], CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, g.w, (uint64_t)p.ksb * 36, g.rows, g.stride, Q4K::ROW_PITCH / 4, 16, CU_TENSOR_MAP_SWIZZLE_NONE)) return false;
     }
     return true;
 }
 
 static int launch(cudaStream_t s, const FastJob &job, const Params &p, const Plan &plan) {
-    return on_dense(job) ? launch_geometry<Q4K, Dense>(s, job, p, plan) : launch_geometry<Q4K, Plain>(s, job, p, plan);
+    return plan.nt == 1 ? launch_geometry<Q4K, Plain, 1>(s, job, p, plan) : plan.nt == 2 ? launch_geometry<Q4K, Plain, 2>(s, job, p, plan) : launch_geometry<Q4K, Dense, 8>(s, job, p, plan);
 }
 
 }  // namespace i8
 
-bool q4k_i8_configure() { return i8::configure_wide<i8::Q4K, i8::Plain, false>() && i8::configure_geometry<i8::Q4K, i8::Dense>(); }
+bool q4k_i8_configure() {
+    return i8::configure_geometry<i8::Q4K, i8::Plain, 1>() && i8::configure_geometry<i8::Q4K, i8::Plain, 2>() && i8::configure_geometry<i8::Q4K, i8::Dense, 8>();
+}
 
 bool q4k_i8_supported(const FastJob &job) {
     i8::Params p;

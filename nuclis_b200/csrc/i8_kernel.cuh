@@ -34,7 +34,7 @@ using dec::tma_load_2d;
 
 constexpr int MAX_SLICES = 32;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
-constexpr int SBW = 5;  // (token, superblock) pairs a warp stages at most: the staging pass keeps them in registers
+constexpr int SBW = 4;  // (token, superblock) pairs a warp stages per pass: a pass keeps them in registers
 
 template <int W, int P>
 struct Geometry {
@@ -81,6 +81,9 @@ __device__ __forceinline__ void hmma_k8(float c[4], uint32_t a0, uint32_t a1, ui
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(b0));
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ uint32_t hsub2(uint32_t a, uint32_t b) {
     uint32_t d;
     asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
@@ -92,12 +95,14 @@ __device__ __forceinline__ uint32_t hsub2(uint32_t a, uint32_t b) {
 // rows are two apart: 0, 2, 4, 6 and 1, 3, 5, 7. Row g + 8 of the mma is task row row_of(g) + 8.
 __device__ __forceinline__ uint32_t row_of(uint32_t g) { return g < 4 ? 2 * g : 2 * g - 7; }
 
-template <bool WIDE>
-__host__ __device__ constexpr int plane_columns() { return WIDE ? 24 : 6; }  // digit rows staged: planes x tokens
-template <bool WIDE>
-__host__ __device__ constexpr int gs_columns() { return WIDE ? 16 : 4; }     // group-sum rows staged: (hi, lo) x tokens
-template <bool WIDE>
-__host__ __device__ constexpr int record_lanes() { return WIDE ? 32 : 8; }   // float4 a unit's sums take (narrow: quad lane 0 of each quad)
+// NT is the number of token columns a kernel instance is built for: 1, 2 (narrow: one mma serves the three
+// digit planes) or 8 (wide: three to eight tokens, an mma per plane).
+template <int NT>
+__host__ __device__ constexpr int plane_columns() { return NT == 8 ? 24 : 6; }  // digit rows staged: planes x tokens
+template <int NT>
+__host__ __device__ constexpr int gs_columns() { return NT == 8 ? 16 : 4; }     // group-sum rows staged: (hi, lo) x tokens
+template <int NT>
+__host__ __device__ constexpr int record_lanes() { return NT == 8 ? 32 : 8; }   // float4 a unit's sums take (narrow: quad lane 0 of each quad)
 
 __device__ __forceinline__ void unit_rows(const Params &p, uint32_t unit, uint32_t &seg, uint32_t &row0) {
     seg = 0;
@@ -109,8 +114,9 @@ __device__ __forceinline__ void unit_rows(const Params &p, uint32_t unit, uint32
 
 // Writes the finished sums a lane holds for a unit. v: (row r, token a), (row r, token a + 1), (row r + 8, a), (row r + 8, a + 1)
 // with r = row_of(g); narrow: a = 0 and only quad lane 0 holds sums; wide: a = 2t. w: the up sums in pair mode.
-template <bool WIDE>
+template <int NT>
 __device__ __forceinline__ void write_unit(const Params &p, uint32_t unit, uint32_t g, uint32_t t, const float v[4], const float w[4]) {
+    constexpr bool WIDE = NT == 8;
     if (!WIDE && t != 0) return;
     const uint32_t r = row_of(g), tok0 = WIDE ? 2 * t : 0;
     if (p.mode != ACT_NONE) {
@@ -152,49 +158,54 @@ __device__ __forceinline__ void write_unit(const Params &p, uint32_t unit, uint3
     }
 }
 
-// Shared memory: [task stages][digit rows][group-sum rows][16 zero bytes... see the kernel][1/scale per (superblock, token)]
-// [staged counts per superblock][part sums][barriers]
-template <class E, class G, bool WIDE>
+
+// Shared memory: [stages][digit rows][group-sum rows][128 zero bytes][1/scale per (superblock, token)][part sums][barriers]
+template <class E, class G, int NT>
 static size_t smem_bytes(uint32_t ksl, bool pair, int stages) {
     const size_t plane_pitch = (size_t)ksl * 256 + 32;
     const size_t gs_pitch = (size_t)ksl * 16 + (16 + 128 - ((size_t)ksl * 16) % 128) % 128;
-    const size_t parts = (size_t)G::SLOTS * 2 * (G::PARTS - 1) * (pair ? 2 : 1) * record_lanes<WIDE>() * 16;
-    return (size_t)G::WARPS * stages * E::TASK_BYTES + plane_columns<WIDE>() * plane_pitch + gs_columns<WIDE>() * gs_pitch + 128 + (size_t)ksl * 8 * 4 + (size_t)ksl * 4 +
-           parts + G::WARPS * stages * 8 + 256;
+    const size_t parts = (size_t)G::SLOTS * 2 * (G::PARTS - 1) * (pair ? 2 : 1) * record_lanes<NT>() * 16;
+    return (size_t)G::SLOTS * stages * E::STAGE_BYTES + plane_columns<NT>() * plane_pitch + gs_columns<NT>() * gs_pitch + 128 + (size_t)ksl * 8 * 4 + parts +
+           G::SLOTS * stages * 16 + 256;
 }
 
-template <class E, class G, bool WIDE, int STAGES>
+template <class E, class G, int NT, int STAGES>
 __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant__ Params p) {
-    constexpr int TASK_BYTES = E::TASK_BYTES;
-    constexpr int WARPS = G::WARPS, THREADS = G::THREADS, SLOTS = G::SLOTS, PARTS = G::PARTS;
-    constexpr int REC = record_lanes<WIDE>();
+    constexpr bool WIDE = NT == 8;
+    constexpr int STAGE_BYTES = E::STAGE_BYTES;  // 16 weight rows x PARTS superblocks: one TMA box, one task per warp of the slot
+    constexpr int WARPS = G::WARPS, SLOTS = G::SLOTS, PARTS = G::PARTS;
+    static_assert(PARTS == E::STAGE_SBS, "a stage holds one superblock per K part");
+    constexpr int REC = record_lanes<NT>();
     extern __shared__ __align__(128) uint8_t smem[];
     const bool pair = p.mode != ACT_NONE;
     uint8_t *stages = smem;
-    uint8_t *planes = stages + WARPS * STAGES * TASK_BYTES;
-    uint8_t *gs = planes + plane_columns<WIDE>() * p.plane_pitch;
-    uint8_t *zero = gs + gs_columns<WIDE>() * p.gs_pitch;      // 128 bytes of zeros (group sums of the B columns no token uses)
+    uint8_t *planes = stages + SLOTS * STAGES * STAGE_BYTES;
+    uint8_t *gs = planes + plane_columns<NT>() * p.plane_pitch;
+    uint8_t *zero = gs + gs_columns<NT>() * p.gs_pitch;        // 128 bytes of zeros (group sums of the B columns no token uses)
     zero += (128u - (uint32_t)(zero - smem) % 128u) % 128u;
     float *inv = (float *)(zero + 128);                        // [superblock of the slice][8 tokens]: 1 / the activation scale
-    uint32_t *ready = (uint32_t *)(inv + p.ksl * 8);           // per superblock: token rows staged
-    float4 *parts = (float4 *)(((uintptr_t)(ready + p.ksl) + 15) & ~(uintptr_t)15);
+    float4 *parts = (float4 *)(((uintptr_t)(inv + p.ksl * 8) + 15) & ~(uintptr_t)15);
     uint64_t *bars = (uint64_t *)(parts + SLOTS * 2 * (PARTS - 1) * (pair ? 2 : 1) * REC);
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t g = lane >> 2, t = lane & 3;
     const uint32_t slot = warp / PARTS, part = warp % PARTS;
-    const uint8_t *my_stage = stages + warp * STAGES * TASK_BYTES;
-    const uint32_t stage0 = smem_u32(my_stage), bar0 = smem_u32(bars + warp * STAGES);
+    // A slot's warps share one ring of stages. full[i]: the copy into stage i has landed (all of them wait on it);
+    // empty[i]: all of them have read stage i (the slot's first warp waits on it before it refills the stage).
+    const uint8_t *my_stage = stages + slot * STAGES * STAGE_BYTES;
+    const uint32_t stage0 = smem_u32(my_stage), full0 = smem_u32(bars + slot * 2 * STAGES), empty0 = full0 + STAGES * 8;
 
     // Programmatic dependent launch: the next kernel of the stream may take an SM as soon as this
     // block leaves it, and this kernel starts its weight stream (weights are constant) while the
     // previous kernel is still finishing elsewhere. Everything that reads the previous kernel's
     // output or writes global memory comes after the griddepcontrol.wait below.
     asm volatile("griddepcontrol.launch_dependents;");
-    if (lane == 0) {
-        for (int i = 0; i < STAGES; ++i) mbar_init(bar0 + i * 8, 1);
+    if (part == 0 && lane == 0) {
+        for (int i = 0; i < STAGES; ++i) {
+            mbar_init(full0 + i * 8, 1);
+            mbar_init(empty0 + i * 8, PARTS);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    __syncwarp();
 
     // ---- this block's slice and units ----
     uint32_t ks = 0;
@@ -206,23 +217,28 @@ __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant
     const uint32_t per_blk = p.units / nblk, extra = p.units - per_blk * nblk;
     const uint32_t u_lo = jblk * per_blk + min(jblk, extra);
     const uint32_t u_hi = u_lo + per_blk + (jblk < extra ? 1u : 0u);
-    const uint32_t np = min((uint32_t)PARTS, n);                          // warps that share a unit
-    const uint32_t m = part < n ? (n - part + PARTS - 1) / PARTS : 0;     // this warp's superblocks per unit
+    const uint32_t np = min((uint32_t)PARTS, n);   // warps of a slot that have superblocks in this slice
+    const uint32_t m = (n + PARTS - 1) / PARTS;    // stages per unit (pair mode: per matrix of the unit)
     const uint32_t first_unit = u_lo + slot;
     const uint32_t my_units = first_unit < u_hi ? (u_hi - first_unit + SLOTS - 1) / SLOTS : 0;
-    const uint32_t total = my_units * m * (pair ? 2u : 1u);
-    const uint64_t policy = evict_first_policy();
+    const uint32_t total = my_units * m * (pair ? 2u : 1u);  // stages the slot streams
 
-    // ---- the weight stream: this warp's tasks in order (pair mode: gate then up of each superblock) ----
-    uint32_t issued = 0, p_stage = 0, p_unit = first_unit, p_j = 0, p_seg = 0, p_row0 = 0;
+    // ---- the weight stream: the slot's stages in order (pair mode: gate then up of each group of superblocks). Only
+    // the slot's first warp keeps this state; it refills a stage once all warps of the slot have left it.
+    uint32_t issued = 0, p_stage = 0, p_phase = 0, p_unit = first_unit, p_j = 0, p_seg = 0, p_row0 = 0;
+    bool stuck = false;
+    const uint64_t policy = evict_first_policy();
     if (total) {
         if (pair) p_row0 = p_unit * 16;
         else unit_rows(p, p_unit, p_seg, p_row0);
     }
     auto issue = [&]() {
-        if (lane == 0) E::issue(p, p_seg, sb0 + part + PARTS * p_j, p_row0, stage0 + p_stage * TASK_BYTES, bar0 + p_stage * 8, policy);
+        if (lane == 0 && !stuck) {
+            if (issued >= (uint32_t)STAGES && !mbar_wait(empty0 + p_stage * 8, p_phase ^ 1u)) stuck = true;
+            else E::issue(p, p_seg, sb0 + PARTS * p_j, p_row0, stage0 + p_stage * STAGE_BYTES, full0 + p_stage * 8, policy);
+        }
         ++issued;
-        p_stage = p_stage + 1 == STAGES ? 0 : p_stage + 1;
+        if (++p_stage == STAGES) { p_stage = 0; p_phase ^= 1u; }
         if (pair && p_seg == 0) { p_seg = 1; return; }
         if (pair) p_seg = 0;
         if (++p_j == m) {
@@ -232,22 +248,22 @@ __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant
             else if (issued < total) unit_rows(p, p_unit, p_seg, p_row0);
         }
     };
-    for (int i = 0; i < STAGES - 1; ++i)
-        if (issued < total) issue();
-    for (uint32_t i = tid; i < p.ksl; i += THREADS) ready[i] = 0;
+    if (part == 0) {
+        __syncwarp();
+        for (int i = 0; i < STAGES - 1; ++i)
+            if (issued < total) issue();
+    }
     if (tid < 32) ((uint32_t *)zero)[tid] = 0;
-    __syncthreads();  // still under the tail of the previous kernel
     asm volatile("griddepcontrol.wait;" ::: "memory");  // the previous kernel has ended; its writes are visible
 
     // ---- stage the slice's activations: a warp takes one (superblock, token) pair at a time ----
-    // Pairs are dealt superblock-major, so the first superblocks are complete first; a task waits for the
-    // count of its own superblock only and the first tasks start while later superblocks are still staged.
-    {
-        const uint32_t pairs = n * p.tokens;
+    // A pass keeps up to SBW pairs of a warp in registers between the loads and the conversion.
+    const uint32_t pairs = n * p.tokens;
+    for (uint32_t pass0 = 0; pass0 < pairs; pass0 += SBW * WARPS) {
         float4 xa[SBW], xb2[SBW];
 #pragma unroll
         for (int j = 0; j < SBW; ++j) {
-            const uint32_t q = warp + j * WARPS;
+            const uint32_t q = pass0 + warp + j * WARPS;
             if (q < pairs) {
                 const uint32_t sb = q / p.tokens, tok = q - sb * p.tokens;
                 const float4 *src = (const float4 *)(p.in + (size_t)tok * p.in_stride) + (size_t)(sb0 + sb) * 64;
@@ -257,7 +273,7 @@ __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant
         }
 #pragma unroll
         for (int j = 0; j < SBW; ++j) {
-            const uint32_t q = warp + j * WARPS;
+            const uint32_t q = pass0 + warp + j * WARPS;
             if (q < pairs) {  // uniform per warp
                 const uint32_t sb = q / p.tokens, tok = q - sb * p.tokens;
                 float mx = fmaxf(fmaxf(fmaxf(fabsf(xa[j].x), fabsf(xa[j].y)), fmaxf(fabsf(xa[j].z), fabsf(xa[j].w))),
@@ -303,12 +319,10 @@ __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant
                     }
                 }
                 if (lane == 0) inv[sb * 8 + tok] = ok ? __uint_as_float((e - 21u) << 23) : (e == 255u ? __uint_as_float(0x7fc00000u) : 0.0f);
-                __threadfence_block();
-                __syncwarp();
-                if (lane == 0) atomicAdd(ready + sb, 1u);
             }
         }
     }
+    __syncthreads();  // the staged rows, the zero block and the slots' barriers are visible to every warp
 
     // ---- the task loop ----
     // This lane's B column n = g. Narrow: column = plane * 2 + token, columns 6 and 7 and the columns of a
@@ -317,16 +331,16 @@ __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant
     const uint32_t gr = row_of(g);
     const uint8_t *xlane;
     const uint8_t *gslane;
-    uint32_t gs_step;   // bytes from a lane's hi group sums to its lo group sums
+    uint32_t gs_step;   // bytes from a lane's hi group sums to its lo group sums (wide)
     if (WIDE) {
         xlane = planes + (size_t)(g < p.tokens ? g : 0u) * p.plane_pitch + t * 8;
         gslane = g < p.tokens ? gs + (size_t)g * p.gs_pitch + t * 4 : zero;
         gs_step = g < p.tokens ? 8u * p.gs_pitch : 0u;
     } else {
-        const bool used = g < 6 && (g & 1u) < p.tokens;
+        const bool used = g < 6 && (g & 1u) < (uint32_t)NT;
         xlane = planes + (size_t)(used ? g : 0u) * p.plane_pitch + t * 8;
         // the mma of the minima has columns (piece, token): 0, 1 hi; 2, 3 lo
-        const bool gs_used = g < 4 && (g & 1u) < p.tokens;
+        const bool gs_used = g < 4 && (g & 1u) < (uint32_t)NT;
         gslane = gs_used ? gs + (size_t)g * p.gs_pitch + t * 4 : zero;
         gs_step = 0;
     }
@@ -334,7 +348,7 @@ __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant
     // narrow: lane t holds the sums of digit plane t (weights 1, 2^8, 2^16; quad lane 3 holds nothing); 1/16 undoes
     // the high nibbles left in place
     const float wl = WIDE ? 0.0625f : (t == 0 ? 0.0625f : t == 1 ? 16.0f : t == 2 ? 4096.0f : 0.0f);
-    const uint32_t tok_a = WIDE ? 2 * t : 0;  // the token of a lane's accumulator columns 0 and 2 (1 and 3: the next one)
+    const float *ivlane = inv + (WIDE ? 2 * t : 0);  // 1 / scale of the lane's token(s), per superblock
     uint32_t c_stage = 0, c_phase = 0, consumed = 0;
     bool failed = false;
     uint32_t uidx = 0;
@@ -343,26 +357,23 @@ __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant
         // After a wait has run out the warp stops computing but still walks its units, so that the
         // warps it shares them with are not left at the barrier below.
         for (uint32_t j = 0; j < m && !failed; ++j) {
-            const uint32_t sbw = part + PARTS * j;  // superblock within the slice
-            if (issued < total) issue();  // keep STAGES - 1 tasks in flight
-            if (uidx == 0) {
-                // the first unit may run ahead of the staging of its superblocks
-                uint32_t spins = 0;
-                while (*(volatile uint32_t *)(ready + sbw) < p.tokens && ++spins < SPIN_LIMIT) {}
-                if (*(volatile uint32_t *)(ready + sbw) < p.tokens) { failed = true; break; }
-                __threadfence_block();
-            }
-            if (!mbar_wait(bar0 + c_stage * 8, c_phase)) { failed = true; break; }
-            const float2 iv = *(const float2 *)(inv + sbw * 8 + tok_a);
-            E::template task<WIDE>(my_stage + c_stage * TASK_BYTES, xlane + sbw * 256, p.plane_pitch, gslane + sbw * gs_sb, gs_step, iv, wl, gr, t, acc);
-            __syncwarp();  // all lanes are done reading this stage before it is refilled
+            const uint32_t sbw = part + PARTS * j;  // superblock within the slice: this warp's task of the stage
+            const bool live = sbw < n;              // the last stage of a row may reach past the slice
+            if (part == 0 && issued < total) issue();  // keep STAGES - 1 stages in flight
+            if (!mbar_wait(full0 + c_stage * 8, c_phase)) { failed = true; break; }
+            if (live)
+                E::template task<NT>(my_stage + c_stage * STAGE_BYTES + part * E::ROW_BYTES, xlane + sbw * 256, p.plane_pitch, gslane + sbw * gs_sb, gs_step, ivlane + sbw * 8, wl, gr, t, acc);
+            __syncwarp();  // all lanes are done reading this stage
+            if (lane == 0) mbar_arrive(empty0 + c_stage * 8);
             ++consumed;
             if (++c_stage == STAGES) { c_stage = 0; c_phase ^= 1u; }
             if (pair) {
-                if (issued < total) issue();
-                if (!mbar_wait(bar0 + c_stage * 8, c_phase)) { failed = true; break; }
-                E::template task<WIDE>(my_stage + c_stage * TASK_BYTES, xlane + sbw * 256, p.plane_pitch, gslane + sbw * gs_sb, gs_step, iv, wl, gr, t, acc2);
+                if (part == 0 && issued < total) issue();
+                if (!mbar_wait(full0 + c_stage * 8, c_phase)) { failed = true; break; }
+                if (live)
+                    E::template task<NT>(my_stage + c_stage * STAGE_BYTES + part * E::ROW_BYTES, xlane + sbw * 256, p.plane_pitch, gslane + sbw * gs_sb, gs_step, ivlane + sbw * 8, wl, gr, t, acc2);
                 __syncwarp();
+                if (lane == 0) mbar_arrive(empty0 + c_stage * 8);
                 ++consumed;
                 if (++c_stage == STAGES) { c_stage = 0; c_phase ^= 1u; }
             }
@@ -372,6 +383,7 @@ __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant
             // the quad's lanes hold the three digit planes (and the two pieces of the minima): add them
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
+                if (NT == 1 && (i & 1)) continue;
                 acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 1);
                 acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 2);
                 if (pair) {
@@ -406,7 +418,7 @@ __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant
             dst[rec] = make_float4(acc[0], acc[1], acc[2], acc[3]);
             if (pair) dst[REC + rec] = make_float4(acc2[0], acc2[1], acc2[2], acc2[3]);
         } else {
-            write_unit<WIDE>(p, unit, g, t, acc, acc2);
+            write_unit<NT>(p, unit, g, t, acc, acc2);
         }
     }
     if (p.nks > 1 && part == 0 && my_units) {
@@ -446,46 +458,48 @@ __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant
                         }
                     }
                     const float v4[4] = {s.x, s.y, s.z, s.w}, w4[4] = {s2.x, s2.y, s2.z, s2.w};
-                    write_unit<WIDE>(p, unit, g, t, v4, w4);
+                    write_unit<NT>(p, unit, g, t, v4, w4);
                 }
                 if (lane == 0) p.counters[unit] = 0;  // leave the scratch as it was found
             }
         }
     }
-    if (failed) {
+    if (__any_sync(0xffffffffu, failed || stuck)) {
         if (lane == 0) atomicExch(p.status, 1u);
-        // let this warp's copies still in flight land before the block's shared memory is released
-        for (; consumed < issued; ++consumed) {
-            mbar_wait(bar0 + c_stage * 8, c_phase);
-            if (++c_stage == STAGES) { c_stage = 0; c_phase ^= 1u; }
-        }
+        // the slot's first warp lets the copies still in flight land before the block's shared memory is released
+        if (part == 0)
+            for (; consumed < issued; ++consumed) {
+                mbar_wait(full0 + c_stage * 8, c_phase);
+                if (++c_stage == STAGES) { c_stage = 0; c_phase ^= 1u; }
+            }
     }
 }
 
 constexpr size_t kSmemMax = 227 * 1024;
-constexpr int kMaxStages = 6;
+constexpr int kMaxStages = 5;
 
 struct Plan {
-    bool wide;
+    int nt;       // the kernel instance: 1, 2 or 8 token columns
     int stages;
     uint32_t grid;
     size_t smem;
 };
 
-template <class E, class G, bool WIDE>
+template <class E, class G, int NT>
 static int pick_stages(uint32_t ksl, bool pair) {
     for (int st = kMaxStages; st >= 2; --st)
-        if (smem_bytes<E, G, WIDE>(ksl, pair, st) <= kSmemMax) return st;
+        if (smem_bytes<E, G, NT>(ksl, pair, st) <= kSmemMax) return st;
     return 0;
 }
 
 // Fills everything of Params that does not depend on the encoding's planes; the caller adds the tensor maps.
-// Picks the K slices and the blocks of each slice: every candidate slice length is costed in task
+// Picks the K slices and the blocks of each slice: every candidate slice length is costed in stage
 // steps of the slowest block (units over unit slots, superblocks over K parts).
-template <class E, class G>
+template <class E, class G, int NT>
 static bool fill_geometry(const FastJob &job, Params &p, Plan &plan) {
     constexpr int SLOTS = G::SLOTS, PARTS = G::PARTS;
     if (job.tokens < 1 || job.tokens > 8 || job.count < 1 || job.count > 4) return false;
+    if (NT == 8 ? job.tokens < 3 : job.tokens != (uint32_t)NT) return false;
     if (job.columns == 0 || job.columns % 256 != 0) return false;
     if ((uintptr_t)job.in % 16 != 0 || job.in_stride % 4 != 0 || job.in_stride > 0xffffffffull) return false;
     if (job.mode != ACT_NONE && (job.count != 2 || job.seg[0].rows != job.seg[1].rows)) return false;
@@ -509,20 +523,20 @@ static bool fill_geometry(const FastJob &job, Params &p, Plan &plan) {
     for (uint32_t s = job.count; s < 5; ++s) p.tile_begin[s] = tiles;
     const bool pair = job.mode != ACT_NONE;
     const uint32_t units = pair ? tiles / 2 : tiles;
-    const double per_sb = pair ? 2.0 : 1.0;  // tasks per superblock of a unit
+    const double per_sb = pair ? 2.0 : 1.0;  // stages per group of superblocks of a unit
     p.units = units;
-    plan.wide = job.tokens > 2;
-    const size_t rec_floats = (size_t)(pair ? 2 : 1) * (plan.wide ? 32 : 8) * 4;  // partial sums a (slice, unit) leaves
+    plan.nt = NT;
+    const size_t rec_floats = (size_t)(pair ? 2 : 1) * record_lanes<NT>() * 4;  // partial sums a (slice, unit) leaves
     const uint32_t sms = (uint32_t)job.sm_count;
     double best = 1e30;
     uint32_t blocks[MAX_SLICES];
     for (uint32_t ksl = 1; ksl <= p.ksb; ++ksl) {
         const uint32_t nks = (p.ksb + ksl - 1) / ksl;
         if (nks > MAX_SLICES || nks > sms) continue;
-        if ((size_t)ksl * job.tokens > (size_t)SBW * G::WARPS) continue;  // the staging pass keeps the slice in registers
+        if (nks > 1 && ksl % PARTS != 0) continue;                        // a stage never spans two slices
         // a slicing whose partial sums or arrival counters do not fit the caller's scratch is no candidate
         if (nks > 1 && ((size_t)nks * units * rec_floats > job.partials_floats || units > job.counters_len)) continue;
-        const int st = plan.wide ? pick_stages<E, G, true>(ksl, pair) : pick_stages<E, G, false>(ksl, pair);
+        const int st = pick_stages<E, G, NT>(ksl, pair);
         if (st < 2) continue;
         auto cost = [&](uint32_t s, uint32_t b) {
             const uint32_t n = s + 1 == nks ? p.ksb - s * ksl : ksl;
@@ -539,7 +553,9 @@ static bool fill_geometry(const FastJob &job, Params &p, Plan &plan) {
         }
         double est = 0;
         for (uint32_t s = 0; s < nks; ++s) est = cost(s, blocks[s]) > est ? cost(s, blocks[s]) : est;
-        est *= st >= 4 ? 1.0 : st == 3 ? 1.06 : 1.2;  // a shallow ring hides less latency
+        // a shallow ring cannot keep the memory system busy: about 110 KB of copies in flight per multiprocessor saturate it
+        const double in_flight = (double)SLOTS * (st - 1) * E::STAGE_BYTES;
+        if (in_flight < 110.0 * 1024) est *= 110.0 * 1024 / in_flight;
         est += (nks > 1 ? 5.0 + 0.3 * nks : 0.0) + 0.01 * ksl * job.tokens;  // partial sums, their fence and the last arriver's pass; staging of the slice
         if (est < best - 1e-9) {
             best = est;
@@ -555,7 +571,7 @@ static bool fill_geometry(const FastJob &job, Params &p, Plan &plan) {
     if (best >= 1e30) return false;
     p.plane_pitch = p.ksl * 256 + 32;
     p.gs_pitch = p.ksl * 16 + (16 + 128 - (p.ksl * 16) % 128) % 128;
-    plan.smem = plan.wide ? smem_bytes<E, G, true>(p.ksl, pair, plan.stages) : smem_bytes<E, G, false>(p.ksl, pair, plan.stages);
+    plan.smem = smem_bytes<E, G, NT>(p.ksl, pair, plan.stages);
     p.partials = job.partials;
     p.counters = job.counters;
     p.status = job.counters + job.counters_len;
@@ -564,30 +580,16 @@ static bool fill_geometry(const FastJob &job, Params &p, Plan &plan) {
     return true;
 }
 
-template <class E, class G, bool WIDE, int STAGES>
+template <class E, class G, int NT, int STAGES>
 static bool configure_one() {
-    return cudaFuncSetAttribute(i8_kernel<E, G, WIDE, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax) == cudaSuccess;
+    return cudaFuncSetAttribute(i8_kernel<E, G, NT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax) == cudaSuccess;
 }
-template <class E, class G, bool WIDE>
-static bool configure_wide() {
-    return configure_one<E, G, WIDE, 2>() && configure_one<E, G, WIDE, 3>() && configure_one<E, G, WIDE, 4>() && configure_one<E, G, WIDE, 5>() &&
-           configure_one<E, G, WIDE, 6>();
-}
-template <class E, class G>
-static bool configure_geometry() { return configure_wide<E, G, false>() && configure_wide<E, G, true>(); }
-
-template <class E, class G, bool WIDE>
-static void launch_stages(const cudaLaunchConfig_t &cfg, int stages, const Params &p) {
-    switch (stages) {
-    case 6: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, WIDE, 6>, p); break;
-    case 5: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, WIDE, 5>, p); break;
-    case 4: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, WIDE, 4>, p); break;
-    case 3: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, WIDE, 3>, p); break;
-    default: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, WIDE, 2>, p); break;
-    }
+template <class E, class G, int NT>
+static bool configure_geometry() {
+    return configure_one<E, G, NT, 2>() && configure_one<E, G, NT, 3>() && configure_one<E, G, NT, 4>() && configure_one<E, G, NT, 5>();
 }
 
-template <class E, class G>
+template <class E, class G, int NT>
 static int launch_geometry(cudaStream_t s, const FastJob &job, const Params &p, const Plan &plan) {
     // launched so that it may overlap the tail of the kernel before it (see the kernel's prologue)
     cudaLaunchAttribute attr[1];
@@ -600,10 +602,18 @@ static int launch_geometry(cudaStream_t s, const FastJob &job, const Params &p, 
     cfg.stream = s;
     cfg.attrs = attr;
     cfg.numAttrs = job.serial ? 0 : 1;
-    if (plan.wide) launch_stages<E, G, true>(cfg, plan.stages, p);
-    else launch_stages<E, G, false>(cfg, plan.stages, p);
+    switch (plan.stages) {
+    case 5: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, NT, 5>, p); break;
+    case 4: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, NT, 4>, p); break;
+    case 3: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, NT, 3>, p); break;
+    default: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, NT, 2>, p); break;
+    }
     return 1;
 }
 
 }  // namespace i8
+
+bool encode_tiled_map(CUtensorMap *map, CUtensorMapDataType type, uint32_t elem_bytes, const void *base, uint64_t inner, uint64_t outer,
+                      uint64_t stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle);
+
 }  // namespace nu
