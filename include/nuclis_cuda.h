@@ -311,6 +311,11 @@ int nu_cuda_allreduce_sum_f32(nu_cuda *h, const nu_buffer *buffer, size_t count)
 enum { NU_PEER_HANDLE_BYTES = 64 };
 int nu_cuda_comm_peer_handle(nu_cuda *h, uint8_t handle[NU_PEER_HANDLE_BYTES]);
 int nu_cuda_comm_attach_peers(nu_cuda *h, const uint8_t *handles, int ranks, int rank);
+/* How long a rank's kernel polls its inbox for the peers' words before it gives up (default 2,000 ms;
+ * 1..60,000). When the limit runs out the kernel returns, the next commit / graph_launch reports
+ * NU_ERR_EXECUTION, and the peer-memory path of this handle stays closed (every later sum over it fails
+ * at once) until the group is destroyed. Applies to operators recorded after the call. */
+int nu_cuda_comm_set_wait_ms(nu_cuda *h, uint32_t ms);
 /* Leaves the group. Every retained graph of the handle is released first (a graph
  * that holds a collective keeps the communicator alive). */
 int nu_cuda_comm_destroy(nu_cuda *h);

@@ -90,6 +90,7 @@ SIGNATURES = {
     "nu_cuda_comm_destroy": (cint, [vp]),
     "nu_cuda_comm_peer_handle": (cint, [vp, u8p]),
     "nu_cuda_comm_attach_peers": (cint, [vp, u8p, cint, cint]),
+    "nu_cuda_comm_set_wait_ms": (cint, [vp, u32]),
 }
 
 _lib = None

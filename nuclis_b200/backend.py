@@ -346,5 +346,9 @@ class Backend:
         flat = (ctypes.c_uint8 * (64 * len(handles))).from_buffer_copy(b"".join(handles))
         self._check(self._lib.nu_cuda_comm_attach_peers(self._h, flat, len(handles), rank))
 
+    def comm_set_wait_ms(self, ms: int) -> None:
+        """How long a kernel of the peer-memory allreduce waits for the peers' words before it gives up."""
+        self._check(self._lib.nu_cuda_comm_set_wait_ms(self._h, ms))
+
     def comm_destroy(self) -> None:
         self._check(self._lib.nu_cuda_comm_destroy(self._h))

@@ -747,6 +747,7 @@ int Backend::combineExperts(const Buffer &values, const Buffer &weights, const B
                             const Buffer &output, const nu_combine_shape &s) {
     if (s.columns == 0 || s.slots == 0 || s.rows == 0 || s.experts == 0 || s.in_stride < s.columns || s.out_stride < s.columns) return fail(NU_ERR_INVALID_SHAPE, "combine: shape");
     if (!fits_u32(s.columns) || !fits_u32(s.rows) || !fits_u32(s.slots) || !fits_u32(s.experts)) return fail(NU_ERR_INVALID_SHAPE, "combine: too large");
+    if (s.rows > 65535) return fail(NU_ERR_TOO_LARGE, "combine: more than 65,535 token rows in one call");
     const size_t slot_rows = s.rows * s.slots;
     const float *v = (const float *)resolve(values, ((slot_rows - 1) * s.in_stride + s.columns) * 4);
     const float *w = (const float *)resolve(weights, slot_rows * 4);
@@ -869,6 +870,13 @@ int Backend::attachPeers(const uint8_t *handles, int ranks, int rank) {
     return NU_OK;
 }
 
+int Backend::setPeerWaitMs(uint32_t ms) {
+    if (ms == 0 || ms > 60000) return fail(NU_ERR_INVALID_SHAPE, "comm_set_wait_ms: 1..60000 ms");
+    if (recording_) return fail(NU_ERR_ALREADY_RECORDING, "comm_set_wait_ms: a recording is open");
+    peer_wait_ns_ = (unsigned long long)ms * 1000000ull;  // recorded graphs keep the limit they were recorded with
+    return NU_OK;
+}
+
 int Backend::allreduceSumF32(const Buffer &buffer, size_t count) {
     if (count == 0) return fail(NU_ERR_INVALID_SHAPE, "allreduce: empty");
     float *p = (float *)resolve(buffer, count * 4);
@@ -883,6 +891,7 @@ int Backend::allreduceSumF32(const Buffer &buffer, size_t count) {
         for (int r = 0; r < peer_ranks_; ++r) pp.inbox[r] = (uint2 *)peer_base_[r];
         pp.seq = (uint32_t *)(inbox_ + kPushWordBytes);
         pp.status = counters_ + counters_len_;
+        pp.wait_ns = peer_wait_ns_;
         if (fuse) {
             cudaSetDevice(device_);
             FastJob &job = pending_job_->job;
@@ -1099,5 +1108,6 @@ int nu_cuda_allreduce_sum_f32(nu_cuda *h, const nu_buffer *buffer, size_t count)
 int nu_cuda_comm_destroy(nu_cuda *h) { NU_H(h); return h->b->commDestroy(); }
 int nu_cuda_comm_peer_handle(nu_cuda *h, uint8_t handle[NU_PEER_HANDLE_BYTES]) { NU_H(h); return h->b->peerHandle(handle); }
 int nu_cuda_comm_attach_peers(nu_cuda *h, const uint8_t *handles, int ranks, int rank) { NU_H(h); return h->b->attachPeers(handles, ranks, rank); }
+int nu_cuda_comm_set_wait_ms(nu_cuda *h, uint32_t ms) { NU_H(h); return h->b->setPeerWaitMs(ms); }
 
 }  // extern "C"

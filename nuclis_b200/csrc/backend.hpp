@@ -87,6 +87,7 @@ public:
     int commDestroy();
     int peerHandle(uint8_t *out);
     int attachPeers(const uint8_t *handles, int ranks, int rank);
+    int setPeerWaitMs(uint32_t ms);
 
     const char *lastError() const { return error_.c_str(); }
 
@@ -151,6 +152,7 @@ private:
     FastJobBox *pending_job_ = nullptr;
     Buffer pending_out_{};
     int peer_ranks_ = 0, peer_rank_ = 0;
+    unsigned long long peer_wait_ns_ = 2000000000ull;
 };
 
 }  // namespace nu

@@ -143,6 +143,7 @@ struct PushParams {
     uint2 *inbox[PUSH_MAX_RANKS];       // every rank's inbox [2][ranks][capacity] of (value, tag); inbox[rank] is local
     uint32_t *seq;                      // local: sequence number, finished blocks, sticky failure
     uint32_t *status;
+    unsigned long long wait_ns;         // how long a rank polls for its peers' words before it gives up
 };
 int launch_push_allreduce(cudaStream_t s, const PushParams &p);
 // The second half alone: the vector was already pushed (by the GEMV that produced it) into every inbox, this rank's included.

@@ -276,95 +276,118 @@ int launch_act_mul_rows(cudaStream_t s, uint32_t act, const float *gate, const f
 }
 
 // ---- router -------------------------------------------------------------------
-// One 256-thread block per row of logits: softmax in F32, then k rounds of
-// arg-max by (logit desc, index asc) on the logits themselves, so that the
-// rounding of exp cannot reorder near ties; weights renormalized over the
-// selected experts with the sum clamped below at the smallest F16 normal.
+// `Backend.route` (ops/experts.zig:29-34; the arithmetic of cpu.experts.route, backends/cpu/experts.zig:50-79).
+// One warp per token row, the logits in registers (lane l holds experts l, l + 32, ...; at most 256 experts):
+// the maximum and the sum of exp by warp shuffles, then k rounds of a warp-wide arg-max by (logit descending,
+// index ascending) on the logits themselves, so that the rounding of exp cannot reorder near ties. Round r's
+// expert and probability stay in lane r mod 32 until the end; the selected probabilities are added in slot
+// order, as a serial loop would, and the weights are renormalized over them with the sum clamped below at
+// the smallest normal F16. No shared memory, no block barrier.
 
-constexpr int ROUTE_THREADS = 256;
+constexpr int ROUTE_WARPS = 4;
+constexpr int ROUTE_PER_LANE = 8;  // 256 experts at most
 constexpr int ROUTE_MAX_K = 64;
 
-__global__ void route_kernel(const float *logits, uint32_t experts, uint32_t k, size_t in_stride, uint32_t *indices, float *weights) {
-    __shared__ float part_v[8];
-    __shared__ uint32_t part_i[8];
-    __shared__ float selected[ROUTE_MAX_K];
+__global__ void __launch_bounds__(ROUTE_WARPS * 32) route_kernel(const float *logits, uint32_t experts, uint32_t k, uint32_t rows, size_t in_stride,
+                                                                  uint32_t *indices, float *weights) {
     wait_for_previous_operator();
-    const uint32_t row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const bool live = tid < experts;
-    const float logit = live ? logits[(size_t)row * in_stride + tid] : -INFINITY;
-    float m = logit;
+    const uint32_t lane = threadIdx.x & 31, row = blockIdx.x * ROUTE_WARPS + (threadIdx.x >> 5);
+    if (row >= rows) return;  // whole warps leave together
+    const float *src = logits + (size_t)row * in_stride;
+    float v[ROUTE_PER_LANE], top = -INFINITY;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    if (lane == 0) part_v[warp] = m;
-    __syncthreads();
-    m = part_v[0];
+    for (int j = 0; j < ROUTE_PER_LANE; ++j) {
+        const uint32_t e = lane + 32u * j;
+        v[j] = e < experts ? src[e] : -INFINITY;
+        top = fmaxf(top, v[j]);
+    }
 #pragma unroll
-    for (int i = 1; i < 8; ++i) m = fmaxf(m, part_v[i]);
-    __syncthreads();
-    const float e = live ? expf(logit - m) : 0.0f;
-    float total = e;
+    for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+    float prob[ROUTE_PER_LANE], total = 0.0f;
+#pragma unroll
+    for (int j = 0; j < ROUTE_PER_LANE; ++j) {
+        prob[j] = lane + 32u * j < experts ? expf(v[j] - top) : 0.0f;
+        total += prob[j];
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
-    if (lane == 0) part_v[warp] = total;
-    __syncthreads();
-    total = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) total += part_v[i];
-    const float probability = e / total;
-    bool taken = !live;
+    uint32_t used = 0, kept_index[ROUTE_MAX_K / 32] = {0u, 0u};
+    float kept_prob[ROUTE_MAX_K / 32] = {0.0f, 0.0f}, chosen = 0.0f;
     for (uint32_t r = 0; r < k; ++r) {
-        __syncthreads();
-        float v = taken ? -INFINITY : logit;
-        uint32_t idx = taken ? 0xffffffffu : tid;
+        // this lane's best unused expert: its experts ascend with j, so a strict comparison keeps the lowest index of a tie
+        float best = -INFINITY, best_prob = 0.0f;
+        uint32_t best_e = 0xffffffffu;
+#pragma unroll
+        for (int j = 0; j < ROUTE_PER_LANE; ++j) {
+            const uint32_t e = lane + 32u * j;
+            const bool open = e < experts && !((used >> j) & 1u);
+            if (open && (best_e == 0xffffffffu || v[j] > best)) { best = v[j]; best_e = e; best_prob = prob[j]; }
+        }
+        // the warp's best: larger logit first, lower index on equal logits
+        float win = best;
+        uint32_t win_e = best_e;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, v, o);
-            const uint32_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
-            if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+            const float other = __shfl_xor_sync(0xffffffffu, win, o);
+            const uint32_t other_e = __shfl_xor_sync(0xffffffffu, win_e, o);
+            if (other_e != 0xffffffffu && (win_e == 0xffffffffu || other > win || (other == win && other_e < win_e))) { win = other; win_e = other_e; }
         }
-        if (lane == 0) { part_v[warp] = v; part_i[warp] = idx; }
-        __syncthreads();
-        v = part_v[0];
-        idx = part_i[0];
-#pragma unroll
-        for (int i = 1; i < 8; ++i)
-            if (part_v[i] > v || (part_v[i] == v && part_i[i] < idx)) { v = part_v[i]; idx = part_i[i]; }
-        if (tid == idx) {
-            taken = true;
-            selected[r] = probability;
-            indices[(size_t)row * k + r] = idx;
+        const float p = __shfl_sync(0xffffffffu, best_prob, win_e & 31u) / total;  // the owner's lane holds it as its own best
+        if ((win_e & 31u) == lane) used |= 1u << (win_e >> 5);
+        chosen += p;
+        if ((r & 31u) == lane) {
+            if (r < 32) { kept_index[0] = win_e; kept_prob[0] = p; }
+            else { kept_index[1] = win_e; kept_prob[1] = p; }
         }
     }
-    __syncthreads();
-    // The selected probabilities summed in slot order, as a serial loop would.
-    float sum = 0.0f;
-    for (uint32_t r = 0; r < k; ++r) sum += selected[r];
-    if (tid < k) weights[(size_t)row * k + tid] = selected[tid] / fmaxf(sum, 6.103515625e-5f);
+    const float norm = fmaxf(chosen, 6.103515625e-5f);
+    if (lane < k) {
+        indices[(size_t)row * k + lane] = kept_index[0];
+        weights[(size_t)row * k + lane] = kept_prob[0] / norm;
+    }
+    if (lane + 32 < k) {
+        indices[(size_t)row * k + lane + 32] = kept_index[1];
+        weights[(size_t)row * k + lane + 32] = kept_prob[1] / norm;
+    }
 }
 
 int launch_route(cudaStream_t s, const float *logits, uint32_t experts, uint32_t k, uint32_t rows, size_t in_stride,
                  uint32_t *indices, float *weights) {
-    launch_after_previous(route_kernel, dim3(rows), dim3(ROUTE_THREADS), s, logits, experts, k, in_stride, indices, weights);
+    launch_after_previous(route_kernel, dim3((rows + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), s, logits, experts, k, rows, in_stride, indices, weights);
     return 1;
 }
 
 // ---- combine --------------------------------------------------------------------
+// `Backend.combineExperts` (ops/experts.zig:79-92): out[row] = sum over the row's slots, in slot order, of
+// weight * (scale of the slot's expert) * values[slot]. A thread owns VEC adjacent columns of one token row
+// and walks the slots once; the slot factors are the same address for a whole warp (one broadcast load).
 
-__global__ void combine_experts_kernel(const float *values, const float *weights, const uint32_t *indices, const float *scales,
-                                       float *out, uint32_t columns, uint32_t slots, uint32_t rows, size_t in_stride, size_t out_stride,
-                                       uint32_t experts) {
+template <int VEC>
+__global__ void __launch_bounds__(128) combine_experts_kernel(const float *values, const float *weights, const uint32_t *indices, const float *scales,
+                                                              float *out, uint32_t columns, uint32_t slots, size_t in_stride, size_t out_stride,
+                                                              uint32_t experts) {
     wait_for_previous_operator();
-    const size_t id = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (id >= (size_t)columns * rows) return;
-    const uint32_t row = (uint32_t)(id / columns), c = (uint32_t)(id % columns);
-    float acc = 0.0f;
+    const uint32_t row = blockIdx.y, c0 = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+    if (c0 >= columns) return;
+    float acc[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = 0.0f;
+    const size_t first = (size_t)row * slots;
     for (uint32_t s = 0; s < slots; ++s) {
-        const size_t slot = (size_t)row * slots + s;
-        float w = weights[slot];
-        if (scales) w *= scales[min(indices[slot], experts - 1)];
-        acc = fmaf(w, values[slot * in_stride + c], acc);
+        float factor = weights[first + s];
+        if (scales) factor *= scales[min(indices[first + s], experts - 1)];
+        const float *src = values + (first + s) * in_stride + c0;
+        if (VEC == 4) {
+            const float4 x = *(const float4 *)src;
+            acc[0] = fmaf(factor, x.x, acc[0]); acc[1] = fmaf(factor, x.y, acc[1]);
+            acc[2] = fmaf(factor, x.z, acc[2]); acc[3] = fmaf(factor, x.w, acc[3]);
+        } else {
+            acc[0] = fmaf(factor, src[0], acc[0]);
+        }
     }
-    out[(size_t)row * out_stride + c] = acc;
+    float *dst = out + (size_t)row * out_stride + c0;
+    if (VEC == 4) *(float4 *)dst = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    else dst[0] = acc[0];
 }
 
 // Expert parallelism: a rank that holds experts [first, first + count) keeps the routed slots it
@@ -388,9 +411,13 @@ int launch_route_local(cudaStream_t s, const uint32_t *indices, const float *wei
 
 int launch_combine_experts(cudaStream_t s, const float *values, const float *weights, const uint32_t *indices, const float *scales,
                            float *out, uint32_t columns, uint32_t slots, uint32_t rows, size_t in_stride, size_t out_stride, uint32_t experts) {
-    const size_t n = (size_t)columns * rows;
-    launch_after_previous(combine_experts_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), s, values, weights, indices, scales, out, columns, slots, rows,
-                                                      in_stride, out_stride, experts);
+    const bool vec = columns % 4 == 0 && in_stride % 4 == 0 && out_stride % 4 == 0 && (uintptr_t)values % 16 == 0 && (uintptr_t)out % 16 == 0;
+    if (vec)
+        launch_after_previous(combine_experts_kernel<4>, dim3((columns / 4 + 127) / 128, rows), dim3(128), s, values, weights, indices, scales, out, columns, slots,
+                              in_stride, out_stride, experts);
+    else
+        launch_after_previous(combine_experts_kernel<1>, dim3((columns + 127) / 128, rows), dim3(128), s, values, weights, indices, scales, out, columns, slots,
+                              in_stride, out_stride, experts);
     return 1;
 }
 

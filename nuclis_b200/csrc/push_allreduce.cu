@@ -18,8 +18,9 @@
 // The sequence number lives in device memory (a replayed graph cannot change kernel arguments);
 // the last block to finish advances it. Threads work on disjoint elements; nothing waits on
 // another thread of the same grid.
-// A wait is bounded both by iterations and by the global timer (about two seconds: ranks replay
-// their graphs from separate processes, so a peer may legitimately arrive late by a host hiccup).
+// A wait is bounded both by iterations and by the global timer (two seconds unless the host set another
+// limit: ranks replay their graphs from separate processes, so a peer may legitimately arrive late by a
+// host hiccup).
 // When it runs out the block raises the backend's status word, sets a sticky local word that makes
 // every later call return at once, and returns; the host reports the failure at commit.
 #include "kernels.hpp"
@@ -27,7 +28,6 @@
 namespace nu {
 
 constexpr uint32_t kPushSpinLimit = 1u << 24;
-constexpr unsigned long long kPushWaitNs = 2000000000ull;
 
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(256) push_allreduce_kernel(PushParams p) {
                 uint4 w = load_words(src);
                 uint32_t n = 0;
                 while ((w.y != tag || (both && w.w != tag)) && ++n < kPushSpinLimit) {
-                    if ((n & 255u) == 0 && global_ns() - t0 > kPushWaitNs) break;
+                    if ((n & 255u) == 0 && global_ns() - t0 > p.wait_ns) break;
                     w = load_words(src);
                 }
                 if (w.y != tag || (both && w.w != tag)) { failed = true; break; }

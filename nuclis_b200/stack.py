@@ -172,16 +172,3 @@ def make_stack(backend: Backend, tokens: int, layers: int, ranks: int = 1, rank:
             torch.cuda.synchronize()
             st.prepare_layer(w)
     return st
-
-
-def reference_layer(oracle, shapes: LayerShapes, w: dict, h: np.ndarray, tasks: int | None = None) -> np.ndarray:
-    """One layer on the CPU oracle (full, unsharded matrices as bytes in ``w``); h is [tokens][hidden]."""
-    out = []
-    for t in range(h.shape[0]):
-        qkv = oracle.matvec(shapes.qkv_encoding, shapes.qkv_rows, shapes.hidden, w["qkv"], h[t], tasks)
-        o = oracle.matvec(shapes.o_encoding, shapes.hidden, shapes.hidden, w["o"], qkv[: shapes.hidden], tasks)
-        g = oracle.matvec(shapes.gate_up_encoding, shapes.ffn, shapes.hidden, w["gate"], o, tasks)
-        u = oracle.matvec(shapes.gate_up_encoding, shapes.ffn, shapes.hidden, w["up"], o, tasks)
-        a = (oracle.silu(g) * u).astype(np.float32)
-        out.append(oracle.matvec(shapes.down_encoding, shapes.hidden, shapes.ffn, w["down"], a, tasks))
-    return np.stack(out)
