@@ -252,6 +252,11 @@ int nu_cuda_matvec_experts(nu_cuda *h, const nu_buffer *weights, const nu_expert
 int nu_cuda_gelu_mul_rows(nu_cuda *h, const nu_buffer *gate, const nu_buffer *up, const nu_buffer *output,
                           size_t width, size_t rows, size_t gate_stride, size_t up_stride, size_t out_stride);
 
+/* `Backend.argmax` (ops/sampling.zig:73-86): greedy selection over the output head's logits. `result` receives one
+ * uint32: the index of the largest of `count` F32 logits, the lowest index on ties, or 0xffffffff when any
+ * logit is NaN or infinite. The scratch of the reference's two passes belongs to the handle here. */
+int nu_cuda_argmax(nu_cuda *h, const nu_buffer *logits, size_t count, const nu_buffer *result);
+
 /* `Backend.combineExperts` (ops/experts.zig:79-92); `scales` may be NULL. */
 int nu_cuda_combine_experts(nu_cuda *h, const nu_buffer *values, const nu_buffer *weights, const nu_buffer *indices,
                             const nu_buffer *scales, const nu_buffer *output, const nu_combine_shape *shape);

@@ -73,6 +73,7 @@ SIGNATURES = {
     "nu_cuda_matvec_segments": (cint, [vp, SP, sz, BP, u32]),
     "nu_cuda_silu_mul": (cint, [vp, BP, BP, sz]),
     "nu_cuda_gelu_mul": (cint, [vp, BP, BP, sz]),
+    "nu_cuda_argmax": (cint, [vp, BP, sz, BP]),
     "nu_cuda_route": (cint, [vp, BP, sz, sz, sz, sz, BP, BP]),
     "nu_cuda_expert_lists_words": (sz, [sz, sz]),
     "nu_cuda_expert_lists": (cint, [vp, BP, sz, sz, sz, BP]),

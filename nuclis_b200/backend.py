@@ -279,6 +279,10 @@ class Backend:
     def gelu_mul(self, gate: Buffer, up: Buffer, count: int) -> None:
         self._check(self._lib.nu_cuda_gelu_mul(self._h, gate._c(), up._c(), count))
 
+    def argmax(self, logits: Buffer, count: int, result: Buffer) -> None:
+        """Index of the largest logit into `result` (one uint32; 0xffffffff if a logit is not finite)."""
+        self._check(self._lib.nu_cuda_argmax(self._h, logits._c(), count, result._c()))
+
     def route(self, logits: Buffer, experts: int, k: int, rows: int, in_stride: int, indices: Buffer, weights: Buffer) -> None:
         self._check(self._lib.nu_cuda_route(self._h, logits._c(), experts, k, rows, in_stride, indices._c(), weights._c()))
 

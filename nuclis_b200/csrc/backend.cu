@@ -68,6 +68,8 @@ Backend *Backend::create(int device, std::string &error) {
     ok = ok && cudaMalloc(&b->partials_, kPartialsFloats * sizeof(float)) == cudaSuccess;
     ok = ok && cudaMalloc(&b->counters_, (kCounters + 1) * sizeof(uint32_t)) == cudaSuccess;
     ok = ok && cudaMemset(b->counters_, 0, (kCounters + 1) * sizeof(uint32_t)) == cudaSuccess;
+    ok = ok && cudaMalloc(&b->argmax_records_, (128 * 4 + 4) * sizeof(float)) == cudaSuccess;
+    ok = ok && cudaMemset(b->argmax_records_, 0, (128 * 4 + 4) * sizeof(float)) == cudaSuccess;
     if (!ok) {
         error = std::string("CUDA set-up failed: ") + cudaGetErrorString(cudaGetLastError());
         delete b;
@@ -96,6 +98,7 @@ Backend::~Backend() {
     if (inbox_) cudaFree(inbox_);
     if (partials_) cudaFree(partials_);
     if (counters_) cudaFree(counters_);
+    if (argmax_records_) cudaFree(argmax_records_);
     if (ev_start_) cudaEventDestroy(ev_start_);
     if (ev_stop_) cudaEventDestroy(ev_stop_);
     if (stream_) cudaStreamDestroy(stream_);
@@ -622,6 +625,19 @@ int Backend::actMul(uint32_t act, const Buffer &gate, const Buffer &up, size_t c
     return cuda(cudaGetLastError(), "act_mul: launch");
 }
 
+// ops/sampling.zig:73-86: greedy selection over the head's logits; the scratch of the two passes is the handle's.
+int Backend::argmax(const Buffer &logits, size_t count, const Buffer &result) {
+    if (count == 0 || count >= 0xffffffffull) return fail(NU_ERR_INVALID_SHAPE, "argmax: count");
+    const float *l = (const float *)resolve(logits, count * 4);
+    uint32_t *r = (uint32_t *)resolve(result, 4);
+    if (!l || !r || logits.offset % 4 != 0 || result.offset % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "argmax: buffer too short");
+    if (int rc = needRecording()) return rc;
+    launches_ += launch_argmax(stream_, l, (uint32_t)count, argmax_records_, (uint32_t *)(argmax_records_ + 128 * 4), r);
+    wrote(result);
+    opBoundary();
+    return cuda(cudaGetLastError(), "argmax: launch");
+}
+
 // ops/experts.zig:29-34.
 int Backend::route(const Buffer &logits, size_t experts, size_t k, size_t rows, size_t in_stride, const Buffer &indices, const Buffer &weights) {
     if (experts == 0 || experts > 256 || k == 0 || k > experts || k > 64 || rows == 0 || in_stride < experts || !fits_u32(rows)) return fail(NU_ERR_INVALID_SHAPE, "route: shape");
@@ -1074,6 +1090,10 @@ int nu_cuda_matmul_experts(nu_cuda *h, const nu_buffer *weights, const nu_expert
     NU_H(h);
     if (!weights || !tensor || !lists || !input || !output) return NU_ERR_INVALID_SHAPE;
     return h->b->matmulExperts(*weights, *tensor, *lists, rows, k, *input, in_stride, in_group, *output, out_stride);
+}
+int nu_cuda_argmax(nu_cuda *h, const nu_buffer *logits, size_t count, const nu_buffer *result) {
+    NU_H(h); NU_P(logits && result);
+    return h->b->argmax(*logits, count, *result);
 }
 int nu_cuda_route_local(nu_cuda *h, const nu_buffer *indices, const nu_buffer *weights, size_t count, size_t first_expert, size_t local_experts,
                         const nu_buffer *local_indices, const nu_buffer *local_weights) {

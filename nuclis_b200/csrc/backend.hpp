@@ -69,6 +69,7 @@ public:
                const Buffer &output, size_t out_stride, size_t tokens);
     int matvecSegments(const Segment *segments, size_t count, const Buffer &input, uint32_t mode);
     int actMul(uint32_t act, const Buffer &gate, const Buffer &up, size_t count);
+    int argmax(const Buffer &logits, size_t count, const Buffer &result);
     int route(const Buffer &logits, size_t experts, size_t k, size_t rows, size_t in_stride, const Buffer &indices, const Buffer &weights);
     int routeLocal(const Buffer &indices, const Buffer &weights, size_t count, size_t first, size_t local, const Buffer &local_indices, const Buffer &local_weights);
     int matvecExpertsGrouped(const Buffer &weights, const ExpertMatrix &tensor, const Buffer &indices, size_t slots,
@@ -133,6 +134,7 @@ private:
     float *partials_ = nullptr;
     size_t partials_floats_ = 0;
     uint32_t *counters_ = nullptr;
+    float *argmax_records_ = nullptr;  // 128 x (value, index, non-finite) of the argmax blocks, then their arrival counter
     size_t counters_len_ = 0;
     // per-operator profile
     bool profiling_ = false;

@@ -38,6 +38,9 @@ int launch_act_mul_rows(cudaStream_t s, uint32_t act, const float *gate, const f
                         uint32_t width, uint32_t rows, size_t gate_stride, size_t up_stride, size_t out_stride);
 int launch_route(cudaStream_t s, const float *logits, uint32_t experts, uint32_t k, uint32_t rows, size_t in_stride,
                  uint32_t *indices, float *weights);
+// Index of the largest of `count` logits (lowest index on ties; 0xffffffff if any is not finite). `records`: 4 floats per block
+// of scratch (at most 128 blocks); `counter`: one zero word, left zero.
+int launch_argmax(cudaStream_t s, const float *logits, uint32_t count, float *records, uint32_t *counter, uint32_t *result);
 int launch_expert_lists(cudaStream_t s, const uint32_t *indices, uint32_t n, uint32_t experts, uint32_t bound, uint32_t *lists);
 int launch_matmul_experts_generic(cudaStream_t s, uint32_t enc, const uint8_t *w, size_t stride, size_t expert_bytes, uint32_t experts, uint32_t rows,
                                   uint32_t columns, const uint32_t *lists, uint32_t bound, const float *in, size_t in_stride, uint32_t in_group,

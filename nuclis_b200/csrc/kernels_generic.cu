@@ -390,6 +390,79 @@ __global__ void __launch_bounds__(128) combine_experts_kernel(const float *value
     else dst[0] = acc[0];
 }
 
+// ---- greedy selection over the output head's logits ---------------------------------------------
+// `Backend.argmax` (ops/sampling.zig:73-86): the index of the largest logit, the lowest index on ties,
+// 0xffffffff when any logit is NaN or infinite. One kernel: every block reduces a strided share to one
+// (value, index, non-finite) record in the scratch, and the block that arrives last (an arrival counter
+// that it leaves at zero) reduces the records in block order; nothing depends on timing.
+
+constexpr int ARGMAX_BLOCKS = 128;
+constexpr int ARGMAX_THREADS = 256;
+
+__device__ __forceinline__ void argmax_better(float &v, uint32_t &idx, float ov, uint32_t oi) {
+    if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+}
+
+__global__ void __launch_bounds__(ARGMAX_THREADS) argmax_kernel(const float *logits, uint32_t count, float *records, uint32_t *counter, uint32_t *result) {
+    __shared__ float sv[ARGMAX_THREADS / 32];
+    __shared__ uint32_t si[ARGMAX_THREADS / 32], sbad[ARGMAX_THREADS / 32], last_block;
+    wait_for_previous_operator();
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float v = -INFINITY;
+    uint32_t idx = 0xffffffffu, bad = 0;
+    for (uint32_t i = blockIdx.x * ARGMAX_THREADS + tid; i < count; i += gridDim.x * ARGMAX_THREADS) {
+        const float x = logits[i];
+        bad |= !isfinite(x);
+        argmax_better(v, idx, x, i);
+    }
+    auto block_reduce = [&]() {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            bad |= __shfl_xor_sync(0xffffffffu, bad, o);
+            argmax_better(v, idx, ov, oi);
+        }
+        if (lane == 0) { sv[warp] = v; si[warp] = idx; sbad[warp] = bad; }
+        __syncthreads();
+        if (tid == 0)
+            for (int w = 1; w < ARGMAX_THREADS / 32; ++w) {
+                bad |= sbad[w];
+                argmax_better(v, idx, sv[w], si[w]);
+            }
+    };
+    block_reduce();
+    if (tid == 0) {
+        records[blockIdx.x * 4 + 0] = v;
+        records[blockIdx.x * 4 + 1] = __uint_as_float(idx);
+        records[blockIdx.x * 4 + 2] = __uint_as_float(bad);
+        __threadfence();
+        last_block = atomicAdd(counter, 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!last_block) return;
+    __threadfence();
+    v = -INFINITY; idx = 0xffffffffu; bad = 0;
+    if (tid < gridDim.x) {
+        v = __ldcg(records + tid * 4);
+        idx = __float_as_uint(__ldcg(records + tid * 4 + 1));
+        bad = __float_as_uint(__ldcg(records + tid * 4 + 2));
+    }
+    __syncthreads();
+    block_reduce();
+    if (tid == 0) {
+        *result = bad ? 0xffffffffu : idx;
+        *counter = 0;  // leave the scratch as it was found
+    }
+}
+
+int launch_argmax(cudaStream_t s, const float *logits, uint32_t count, float *records, uint32_t *counter, uint32_t *result) {
+    uint32_t blocks = (count + ARGMAX_THREADS - 1) / ARGMAX_THREADS;
+    if (blocks > ARGMAX_BLOCKS) blocks = ARGMAX_BLOCKS;
+    launch_after_previous(argmax_kernel, dim3(blocks), dim3(ARGMAX_THREADS), s, logits, count, records, counter, result);
+    return 1;
+}
+
 // Expert parallelism: a rank that holds experts [first, first + count) keeps the routed slots it
 // owns (index made local) and silences the others (index 0, weight 0), so that the grouped
 // operators run unchanged and the partial outputs of the ranks add up to the full result.
