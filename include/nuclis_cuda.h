@@ -252,6 +252,21 @@ int nu_cuda_matvec_experts(nu_cuda *h, const nu_buffer *weights, const nu_expert
 int nu_cuda_gelu_mul_rows(nu_cuda *h, const nu_buffer *gate, const nu_buffer *up, const nu_buffer *output,
                           size_t width, size_t rows, size_t gate_stride, size_t up_stride, size_t out_stride);
 
+/* The steps on either side of a projection in a decoder layer (models/qwen35_metal.zig:630-640).
+ * `Norm` of ops/rowwise.zig:24-35: `rows` rows of `width` floats, strides in floats, eps > 0. */
+typedef struct nu_norm {
+    size_t rows, width, in_stride, out_stride;
+    float eps;
+} nu_norm;
+/* `Backend.rmsNorm` (ops/rowwise.zig:37-51): output = input * rsqrt(mean(input^2) + eps) * weight, per row.
+ * `output` may alias `input` exactly. */
+int nu_cuda_rms_norm(nu_cuda *h, const nu_buffer *input, const nu_buffer *weight, const nu_buffer *output, const nu_norm *spec);
+/* `Backend.addRmsNorm` (ops/rowwise.zig:76-93): residual += input, then output = norm(residual) * weight, in
+ * one pass over the row. `input` shares the residual's stride and overlaps neither it nor `output`. */
+int nu_cuda_add_rms_norm(nu_cuda *h, const nu_buffer *residual, const nu_buffer *input, const nu_buffer *weight, const nu_buffer *output, const nu_norm *spec);
+/* `Backend.add` (ops/rowwise.zig:199-202): x[0..count) += y[0..count). */
+int nu_cuda_add(nu_cuda *h, const nu_buffer *x, const nu_buffer *y, size_t count);
+
 /* `Backend.argmax` (ops/sampling.zig:73-86): greedy selection over the output head's logits. `result` receives one
  * uint32: the index of the largest of `count` F32 logits, the lowest index on ties, or 0xffffffff when any
  * logit is NaN or infinite. The scratch of the reference's two passes belongs to the handle here. */

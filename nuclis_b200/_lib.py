@@ -36,6 +36,10 @@ class CCombineShape(ctypes.Structure):
     _fields_ = [("columns", u64), ("slots", u64), ("rows", u64), ("experts", u64), ("in_stride", u64), ("out_stride", u64)]
 
 
+class CNorm(ctypes.Structure):
+    _fields_ = [("rows", sz), ("width", sz), ("in_stride", sz), ("out_stride", sz), ("eps", ctypes.c_float)]
+
+
 BP, MP, EP, SP = ctypes.POINTER(CBuffer), ctypes.POINTER(CMatrix), ctypes.POINTER(CExpertMatrix), ctypes.POINTER(CSegment)
 
 # name -> (restype, argtypes); every function declared in include/nuclis_cuda.h
@@ -73,6 +77,9 @@ SIGNATURES = {
     "nu_cuda_matvec_segments": (cint, [vp, SP, sz, BP, u32]),
     "nu_cuda_silu_mul": (cint, [vp, BP, BP, sz]),
     "nu_cuda_gelu_mul": (cint, [vp, BP, BP, sz]),
+    "nu_cuda_rms_norm": (cint, [vp, BP, BP, BP, ctypes.POINTER(CNorm)]),
+    "nu_cuda_add_rms_norm": (cint, [vp, BP, BP, BP, BP, ctypes.POINTER(CNorm)]),
+    "nu_cuda_add": (cint, [vp, BP, BP, sz]),
     "nu_cuda_argmax": (cint, [vp, BP, sz, BP]),
     "nu_cuda_route": (cint, [vp, BP, sz, sz, sz, sz, BP, BP]),
     "nu_cuda_expert_lists_words": (sz, [sz, sz]),

@@ -279,6 +279,22 @@ class Backend:
     def gelu_mul(self, gate: Buffer, up: Buffer, count: int) -> None:
         self._check(self._lib.nu_cuda_gelu_mul(self._h, gate._c(), up._c(), count))
 
+    def rms_norm(self, input: Buffer, weight: Buffer, output: Buffer, rows: int, width: int, in_stride: int | None = None, out_stride: int | None = None,
+                 eps: float = 1e-6) -> None:
+        """``rmsNorm`` (ops/rowwise.zig:37-51): output = input * rsqrt(mean(input^2) + eps) * weight per row."""
+        n = _lib.CNorm(rows, width, in_stride or width, out_stride or width, eps)
+        self._check(self._lib.nu_cuda_rms_norm(self._h, input._c(), weight._c(), output._c(), ctypes.byref(n)))
+
+    def add_rms_norm(self, residual: Buffer, input: Buffer, weight: Buffer, output: Buffer, rows: int, width: int, in_stride: int | None = None,
+                     out_stride: int | None = None, eps: float = 1e-6) -> None:
+        """``addRmsNorm`` (ops/rowwise.zig:76-93): residual += input, output = norm(residual) * weight."""
+        n = _lib.CNorm(rows, width, in_stride or width, out_stride or width, eps)
+        self._check(self._lib.nu_cuda_add_rms_norm(self._h, residual._c(), input._c(), weight._c(), output._c(), ctypes.byref(n)))
+
+    def add(self, x: Buffer, y: Buffer, count: int) -> None:
+        """``add`` (ops/rowwise.zig:199-202): x += y."""
+        self._check(self._lib.nu_cuda_add(self._h, x._c(), y._c(), count))
+
     def argmax(self, logits: Buffer, count: int, result: Buffer) -> None:
         """Index of the largest logit into `result` (one uint32; 0xffffffff if a logit is not finite)."""
         self._check(self._lib.nu_cuda_argmax(self._h, logits._c(), count, result._c()))

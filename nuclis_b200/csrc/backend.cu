@@ -625,6 +625,55 @@ int Backend::actMul(uint32_t act, const Buffer &gate, const Buffer &up, size_t c
     return cuda(cudaGetLastError(), "act_mul: launch");
 }
 
+// ops/rowwise.zig:37-51 (without the optional SiLU multiplier, which no caller on this path uses).
+int Backend::rmsNorm(const Buffer &input, const Buffer &weight, const Buffer &output, const nu_norm &n) {
+    if (n.rows == 0 || n.width == 0 || n.in_stride < n.width || n.out_stride < n.width || !(n.eps > 0) || !fits_u32(n.rows) || !fits_u32(n.width)) return fail(NU_ERR_INVALID_SHAPE, "rms_norm: shape");
+    float *x = (float *)resolve(input, ((n.rows - 1) * n.in_stride + n.width) * 4);
+    float *y = (float *)resolve(output, ((n.rows - 1) * n.out_stride + n.width) * 4);
+    const float *w = (const float *)resolve(weight, n.width * 4);
+    if (!x || !y || !w || input.offset % 4 != 0 || output.offset % 4 != 0 || weight.offset % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "rms_norm: buffer too short");
+    // input and output may alias exactly (the same rows at the same stride); any other overlap is refused
+    const bool same = input.id == output.id && input.offset == output.offset && n.in_stride == n.out_stride;
+    if (!same && overlaps(input, ((n.rows - 1) * n.in_stride + n.width) * 4, output, ((n.rows - 1) * n.out_stride + n.width) * 4)) return fail(NU_ERR_INVALID_SHAPE, "rms_norm: output overlaps input");
+    if (int rc = needRecording()) return rc;
+    launches_ += launch_norm_rows(stream_, x, nullptr, w, y, (uint32_t)n.width, (uint32_t)n.rows, n.in_stride, n.out_stride, n.eps);
+    wrote(output);
+    opBoundary();
+    return cuda(cudaGetLastError(), "rms_norm: launch");
+}
+
+// ops/rowwise.zig:76-93: residual += input, output = norm(residual) * weight, in one pass.
+int Backend::addRmsNorm(const Buffer &residual, const Buffer &input, const Buffer &weight, const Buffer &output, const nu_norm &n) {
+    if (n.rows == 0 || n.width == 0 || n.in_stride < n.width || n.out_stride < n.width || !(n.eps > 0) || !fits_u32(n.rows) || !fits_u32(n.width)) return fail(NU_ERR_INVALID_SHAPE, "add_rms_norm: shape");
+    const size_t in_len = ((n.rows - 1) * n.in_stride + n.width) * 4, out_len = ((n.rows - 1) * n.out_stride + n.width) * 4;
+    float *x = (float *)resolve(residual, in_len);
+    const float *s = (const float *)resolve(input, in_len);
+    float *y = (float *)resolve(output, out_len);
+    const float *w = (const float *)resolve(weight, n.width * 4);
+    if (!x || !s || !y || !w || residual.offset % 4 != 0 || input.offset % 4 != 0 || output.offset % 4 != 0 || weight.offset % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "add_rms_norm: buffer too short");
+    if (overlaps(input, in_len, output, out_len) || overlaps(input, in_len, residual, in_len)) return fail(NU_ERR_INVALID_SHAPE, "add_rms_norm: input overlaps the residual or the output");
+    const bool same = residual.id == output.id && residual.offset == output.offset && n.in_stride == n.out_stride;
+    if (!same && overlaps(residual, in_len, output, out_len)) return fail(NU_ERR_INVALID_SHAPE, "add_rms_norm: output overlaps the residual");
+    if (int rc = needRecording()) return rc;
+    launches_ += launch_norm_rows(stream_, x, s, w, y, (uint32_t)n.width, (uint32_t)n.rows, n.in_stride, n.out_stride, n.eps);
+    wrote(residual); wrote(output);
+    opBoundary();
+    return cuda(cudaGetLastError(), "add_rms_norm: launch");
+}
+
+// ops/rowwise.zig:199-202.
+int Backend::add(const Buffer &xb, const Buffer &yb, size_t count) {
+    if (count == 0) return fail(NU_ERR_INVALID_SHAPE, "add: count");
+    float *x = (float *)resolve(xb, count * 4);
+    const float *y = (const float *)resolve(yb, count * 4);
+    if (!x || !y || xb.offset % 4 != 0 || yb.offset % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "add: buffer too short");
+    if (int rc = needRecording()) return rc;
+    launches_ += launch_add(stream_, x, y, count);
+    wrote(xb);
+    opBoundary();
+    return cuda(cudaGetLastError(), "add: launch");
+}
+
 // ops/sampling.zig:73-86: greedy selection over the head's logits; the scratch of the two passes is the handle's.
 int Backend::argmax(const Buffer &logits, size_t count, const Buffer &result) {
     if (count == 0 || count >= 0xffffffffull) return fail(NU_ERR_INVALID_SHAPE, "argmax: count");
@@ -1090,6 +1139,18 @@ int nu_cuda_matmul_experts(nu_cuda *h, const nu_buffer *weights, const nu_expert
     NU_H(h);
     if (!weights || !tensor || !lists || !input || !output) return NU_ERR_INVALID_SHAPE;
     return h->b->matmulExperts(*weights, *tensor, *lists, rows, k, *input, in_stride, in_group, *output, out_stride);
+}
+int nu_cuda_rms_norm(nu_cuda *h, const nu_buffer *input, const nu_buffer *weight, const nu_buffer *output, const nu_norm *spec) {
+    NU_H(h); NU_P(input && weight && output && spec);
+    return h->b->rmsNorm(*input, *weight, *output, *spec);
+}
+int nu_cuda_add_rms_norm(nu_cuda *h, const nu_buffer *residual, const nu_buffer *input, const nu_buffer *weight, const nu_buffer *output, const nu_norm *spec) {
+    NU_H(h); NU_P(residual && input && weight && output && spec);
+    return h->b->addRmsNorm(*residual, *input, *weight, *output, *spec);
+}
+int nu_cuda_add(nu_cuda *h, const nu_buffer *x, const nu_buffer *y, size_t count) {
+    NU_H(h); NU_P(x && y);
+    return h->b->add(*x, *y, count);
 }
 int nu_cuda_argmax(nu_cuda *h, const nu_buffer *logits, size_t count, const nu_buffer *result) {
     NU_H(h); NU_P(logits && result);

@@ -69,6 +69,9 @@ public:
                const Buffer &output, size_t out_stride, size_t tokens);
     int matvecSegments(const Segment *segments, size_t count, const Buffer &input, uint32_t mode);
     int actMul(uint32_t act, const Buffer &gate, const Buffer &up, size_t count);
+    int rmsNorm(const Buffer &input, const Buffer &weight, const Buffer &output, const nu_norm &spec);
+    int addRmsNorm(const Buffer &residual, const Buffer &input, const Buffer &weight, const Buffer &output, const nu_norm &spec);
+    int add(const Buffer &x, const Buffer &y, size_t count);
     int argmax(const Buffer &logits, size_t count, const Buffer &result);
     int route(const Buffer &logits, size_t experts, size_t k, size_t rows, size_t in_stride, const Buffer &indices, const Buffer &weights);
     int routeLocal(const Buffer &indices, const Buffer &weights, size_t count, size_t first, size_t local, const Buffer &local_indices, const Buffer &local_weights);

@@ -36,6 +36,10 @@ enum Act : uint32_t { ACT_NONE = 0, ACT_SILU = 1, ACT_GELU = 2 };
 // out[r][i] = act(gate[r][i]) * up[r][i]; out may alias gate exactly.
 int launch_act_mul_rows(cudaStream_t s, uint32_t act, const float *gate, const float *up, float *out,
                         uint32_t width, uint32_t rows, size_t gate_stride, size_t up_stride, size_t out_stride);
+// output[row] = rms_norm(residual[row] (+ input[row], stored back into residual)) * weight; input may be null.
+int launch_norm_rows(cudaStream_t s, float *residual, const float *input, const float *weight, float *output, uint32_t width, uint32_t rows, size_t in_stride,
+                     size_t out_stride, float eps);
+int launch_add(cudaStream_t s, float *x, const float *y, size_t count);
 int launch_route(cudaStream_t s, const float *logits, uint32_t experts, uint32_t k, uint32_t rows, size_t in_stride,
                  uint32_t *indices, float *weights);
 // Index of the largest of `count` logits (lowest index on ties; 0xffffffff if any is not finite). `records`: 4 floats per block

@@ -275,6 +275,105 @@ int launch_act_mul_rows(cudaStream_t s, uint32_t act, const float *gate, const f
     return 1;
 }
 
+// ---- weighted RMS norm, alone or with the residual add in front -----------------------------------
+// `Backend.rmsNorm` / `addRmsNorm` / `add` (ops/rowwise.zig:37-51, 76-93, 199-202; the arithmetic of cpu rmsNorm,
+// backends/cpu/vector.zig:53-64). A block per token row. The row is read once: every thread keeps its float4 pieces
+// (the summed residual, when an input is added) in registers between the sum of squares and the scaled write, so rows
+// of up to NORM_THREADS * 4 * NORM_KEEP floats cost one pass over memory; longer rows re-read what does not fit.
+// With ADD the updated residual is stored as well. `output` may alias the residual exactly.
+
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_KEEP = 8;  // float4 pieces a thread keeps: rows of up to 8192 floats in one pass
+
+template <bool ADD>
+__global__ void __launch_bounds__(NORM_THREADS) norm_rows_kernel(float *residual, const float *input, const float *weight, float *output, uint32_t width,
+                                                                  size_t in_stride, size_t out_stride, float eps) {
+    __shared__ float partial[NORM_THREADS / 32];
+    wait_for_previous_operator();
+    const uint32_t row = blockIdx.x, tid = threadIdx.x;
+    float *x = residual + (size_t)row * in_stride;
+    const float *s = ADD ? input + (size_t)row * in_stride : nullptr;
+    float *y = output + (size_t)row * out_stride;
+    const bool vec = width % 4 == 0 && in_stride % 4 == 0 && out_stride % 4 == 0 && ((uintptr_t)residual | (uintptr_t)output | (uintptr_t)weight | (ADD ? (uintptr_t)input : 0)) % 16 == 0;
+    float4 kept[NORM_KEEP];
+    float sum = 0.0f;
+    if (vec) {
+        const uint32_t pieces = width / 4;
+#pragma unroll
+        for (int k = 0; k < NORM_KEEP; ++k) {
+            const uint32_t i = tid + k * NORM_THREADS;
+            if (i < pieces) {
+                float4 v = ((const float4 *)x)[i];
+                if (ADD) {
+                    const float4 a = ((const float4 *)s)[i];
+                    v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+                    ((float4 *)x)[i] = v;
+                }
+                kept[k] = v;
+                sum += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+        }
+        for (uint32_t i = tid + NORM_KEEP * NORM_THREADS; i < pieces; i += NORM_THREADS) {
+            float4 v = ((const float4 *)x)[i];
+            if (ADD) {
+                const float4 a = ((const float4 *)s)[i];
+                v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+                ((float4 *)x)[i] = v;
+            }
+            sum += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    } else {
+        for (uint32_t i = tid; i < width; i += NORM_THREADS) {
+            float v = x[i];
+            if (ADD) { v += s[i]; x[i] = v; }
+            sum += v * v;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if ((tid & 31) == 0) partial[tid >> 5] = sum;
+    __syncthreads();  // every thread has read (and, with ADD, written back) its part of the row
+    float total = 0.0f;
+#pragma unroll
+    for (int w = 0; w < NORM_THREADS / 32; ++w) total += partial[w];
+    const float scale = rsqrtf(total / (float)width + eps);
+    if (vec) {
+        const uint32_t pieces = width / 4;
+#pragma unroll
+        for (int k = 0; k < NORM_KEEP; ++k) {
+            const uint32_t i = tid + k * NORM_THREADS;
+            if (i < pieces) {
+                const float4 v = kept[k], g = ((const float4 *)weight)[i];
+                ((float4 *)y)[i] = make_float4(v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z, v.w * scale * g.w);
+            }
+        }
+        for (uint32_t i = tid + NORM_KEEP * NORM_THREADS; i < pieces; i += NORM_THREADS) {
+            const float4 v = ((const float4 *)x)[i], g = ((const float4 *)weight)[i];
+            ((float4 *)y)[i] = make_float4(v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z, v.w * scale * g.w);
+        }
+    } else {
+        for (uint32_t i = tid; i < width; i += NORM_THREADS) y[i] = x[i] * scale * weight[i];
+    }
+}
+
+int launch_norm_rows(cudaStream_t s, float *residual, const float *input, const float *weight, float *output, uint32_t width, uint32_t rows, size_t in_stride,
+                     size_t out_stride, float eps) {
+    if (input) launch_after_previous(norm_rows_kernel<true>, dim3(rows), dim3(NORM_THREADS), s, residual, input, weight, output, width, in_stride, out_stride, eps);
+    else launch_after_previous(norm_rows_kernel<false>, dim3(rows), dim3(NORM_THREADS), s, residual, input, weight, output, width, in_stride, out_stride, eps);
+    return 1;
+}
+
+__global__ void add_kernel(float *x, const float *y, size_t count) {
+    wait_for_previous_operator();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) x[i] += y[i];
+}
+
+int launch_add(cudaStream_t s, float *x, const float *y, size_t count) {
+    launch_after_previous(add_kernel, dim3((unsigned)((count + 255) / 256)), dim3(256), s, x, y, count);
+    return 1;
+}
+
 // ---- router -------------------------------------------------------------------
 // `Backend.route` (ops/experts.zig:29-34; the arithmetic of cpu.experts.route, backends/cpu/experts.zig:50-79).
 // One warp per token row, the logits in registers (lane l holds experts l, l + 32, ...; at most 256 experts):

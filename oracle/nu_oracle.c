@@ -21,6 +21,7 @@
  *                        :147-170 (Q4_K), :198-211 (Q6_K), :432-435 (half)
  *   nu_ref_matvec        inference/src/backends/cpu/root.zig:112-152
  *   nu_ref_gelu/silu     inference/src/backends/cpu/vector.zig:94-98, 178-196
+ *   nu_ref_rms_norm      inference/src/backends/cpu/vector.zig:53-64
  *   nu_ref_route         inference/src/backends/cpu/experts.zig:50-79
  *   nu_ref_ffn           inference/src/backends/cpu/experts.zig:107-133
  */
@@ -356,6 +357,20 @@ static double logistic(float x) {
 float nu_ref_silu(float x) {
     if (isinf(x) && x < 0) return -0.0f;
     return (float)((double)x * logistic(x));
+}
+
+/* ---- rmsNorm: backends/cpu/vector.zig:53-64 (F64 sum of squares, one division per element) ---- */
+
+int nu_ref_rms_norm(const float *input, float *output, size_t n, float epsilon) {
+    if (n == 0 || !isfinite(epsilon) || epsilon <= 0) return NU_REF_INVALID_SHAPE;
+    double squares = 0;
+    for (size_t i = 0; i < n; ++i) {
+        if (!isfinite(input[i])) return NU_REF_INVALID_SHAPE;
+        squares += (double)input[i] * (double)input[i];
+    }
+    const double denominator = sqrt(squares / (double)n + (double)epsilon);
+    for (size_t i = 0; i < n; ++i) output[i] = (float)((double)input[i] / denominator);
+    return NU_REF_OK;
 }
 
 /* ---- routing: experts.zig:50-79 ------------------------------------------ */

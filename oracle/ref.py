@@ -148,6 +148,16 @@ def silu(x) -> np.ndarray:
     return np.array([f(float(v)) for v in np.asarray(x, dtype=np.float32).ravel()], dtype=np.float32).reshape(np.shape(x))
 
 
+def rms_norm(x: np.ndarray, eps: float = 1e-6) -> np.ndarray:
+    """cpu rmsNorm (vector.zig:53-64): x / sqrt(mean(x^2) + eps), the sum of squares in F64; no weight."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty_like(x)
+    f = _load().nu_ref_rms_norm
+    f.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float]
+    _check(f(_ptr(x), _ptr(out), x.size, eps))
+    return out
+
+
 def route(logits: np.ndarray, k: int) -> tuple[np.ndarray, np.ndarray]:
     """cpu.experts.route for one token: (indices u32[k], weights f32[k])."""
     logits = np.ascontiguousarray(logits, dtype=np.float32)

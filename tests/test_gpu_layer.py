@@ -208,3 +208,51 @@ def test_gate_activations_refuse_bad_calls(backend):
         b.silu_mul(gb, ub, 0)
     b.discard()
     b.release(gb); b.release(ub)
+
+
+@pytest.mark.parametrize("rows,width,pad", [(1, 5120, 0), (8, 5120, 64), (3, 2816, 0), (2, 17408, 0), (4, 100, 3), (1, 16, 0)])
+def test_norms_around_the_projections_match_the_oracle(backend, rows, width, pad):
+    """`rmsNorm`, `addRmsNorm` and `add` (ops/rowwise.zig:37-51, 76-93, 199-202) against the CPU forms (vector.zig:53-64:
+    F64 sum of squares, one division per element) times the weight: within 4e-6 relative + 1e-7. `addRmsNorm` also
+    leaves residual + input in the residual, bit for bit what `add` gives; rows wider than a thread keeps in
+    registers (17408), odd widths and padded strides take the other paths of the kernel."""
+    b = backend
+    rng = np.random.default_rng(rows * 1000 + width)
+    stride = width + pad
+    x = (rng.standard_normal((rows, stride)) * 3).astype(np.float32)
+    s = rng.standard_normal((rows, stride)).astype(np.float32)
+    w = (1.0 + 0.1 * rng.standard_normal(width)).astype(np.float32)
+    xb, sb, wb, yb = upload(b, x), upload(b, s), upload(b, w), b.create(rows * stride * 4)
+    x2 = upload(b, x)
+    b.begin()
+    b.rms_norm(xb, wb, yb, rows, width, stride, stride)
+    b.commit()
+    got = yb.floats().reshape(rows, stride)[:, :width]
+    for r in range(rows):
+        want = oracle.rms_norm(x[r, :width]).astype(np.float64) * w
+        assert np.all(np.abs(got[r] - want) <= 4e-6 * np.abs(want) + 1e-7), (r, float(np.max(np.abs(got[r] - want))))
+    b.begin()
+    b.add_rms_norm(xb, sb, wb, yb, rows, width, stride, stride)
+    b.add(x2, sb, rows * stride)
+    b.commit()
+    got = yb.floats().reshape(rows, stride)[:, :width]
+    summed = xb.floats().reshape(rows, stride)
+    assert np.array_equal(summed[:, :width], (x + s)[:, :width]) and np.array_equal(x2.floats().reshape(rows, stride), x + s)
+    assert np.array_equal(summed[:, width:], x[:, width:])          # the padding between rows is not touched
+    for r in range(rows):
+        want = oracle.rms_norm((x + s)[r, :width]).astype(np.float64) * w
+        assert np.all(np.abs(got[r] - want) <= 4e-6 * np.abs(want) + 1e-7), r
+    # in place, and the refusals
+    b.begin()
+    b.rms_norm(xb, wb, xb, rows, width, stride, stride)
+    with pytest.raises(NuclisError):
+        b.rms_norm(xb, wb, yb, rows, width, width - 1 if width > 1 else 0, stride)
+    with pytest.raises(NuclisError):
+        b.add_rms_norm(xb, xb, wb, yb, rows, width, stride, stride)   # input is the residual
+    with pytest.raises(NuclisError):
+        b.rms_norm(xb, wb, yb, rows, width, stride, stride, eps=0.0)
+    b.commit()
+    inplace = xb.floats().reshape(rows, stride)[:, :width]
+    assert np.array_equal(inplace, got)
+    for buf in (xb, sb, wb, yb, x2):
+        b.release(buf)
