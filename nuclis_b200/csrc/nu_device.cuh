@@ -8,7 +8,7 @@
 
 namespace nu {
 
-enum Encoding : uint32_t { F32 = 0, F16 = 1, Q4_0 = 2, Q5_0 = 6, Q5_1 = 7, Q8_0 = 8, Q2_K = 10, Q3_K = 11, Q4_K = 12, Q5_K = 13, Q6_K = 14, BF16 = 30 };
+enum Encoding : uint32_t { F32 = 0, F16 = 1, Q4_0 = 2, Q5_0 = 6, Q5_1 = 7, Q8_0 = 8, Q2_K = 10, Q3_K = 11, Q4_K = 12, Q5_K = 13, Q6_K = 14, IQ4_NL = 20, IQ4_XS = 23, BF16 = 30 };
 
 struct Layout { uint32_t elements, bytes; };
 
@@ -26,6 +26,8 @@ __host__ __device__ inline Layout layout(uint32_t id) {
     case Q4_K: return {256, 144};
     case Q5_K: return {256, 176};
     case Q6_K: return {256, 210};
+    case IQ4_NL: return {32, 18};
+    case IQ4_XS: return {256, 136};
     case BF16: return {1, 2};
     default: return {0, 0};
     }
@@ -35,6 +37,13 @@ __host__ __device__ inline Layout layout(uint32_t id) {
 __device__ __forceinline__ float half_at(const uint8_t *p) {
     const unsigned short bits = (unsigned short)p[0] | ((unsigned short)p[1] << 8);
     return __half2float(__ushort_as_half(bits));
+}
+
+// The sixteen values a four-bit IQ4 code selects (decode.zig:437), packed four to a word so that the
+// lookup is a shift and a sign extension instead of a table in local memory.
+__device__ __forceinline__ int iq4_value(uint32_t code) {
+    const uint32_t w = code < 8 ? (code < 4 ? 0xbfad9881u : 0xf6eaddcfu) : (code < 12 ? 0x26190d01u : 0x71594535u);
+    return (int)(int8_t)(w >> ((code & 3u) * 8));
 }
 
 // Decodes the 16 consecutive values [16*seg, 16*seg+16) of one row.
@@ -93,6 +102,29 @@ __device__ __forceinline__ void dequant16(uint32_t enc, const uint8_t *row, uint
             const int q = (int)(((plane[4 + i] >> (hi * 4)) & 15u) | (((qh >> (i + hi * 16)) & 1u) << 4));
             out[i] = offset ? __fadd_rn(__fmul_rn(d, (float)q), m) : __fmul_rn(d, (float)(q - 16));
         }
+        break;
+    }
+    case IQ4_NL: {
+        // decode.zig:73-81: d * table[code]; low nibbles are the first 16 values of the block, high nibbles the next 16
+        const uint8_t *block = row + (size_t)(first / 32) * 18;
+        const float d = half_at(block);
+        const uint32_t shift = ((first % 32) / 16) * 4;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) out[i] = __fmul_rn(d, (float)iq4_value((block[2 + i] >> shift) & 15u));
+        break;
+    }
+    case IQ4_XS: {
+        // decode.zig:214-228: eight groups of 32 under a six-bit scale biased by 32; the 16 values are half a group
+        const uint8_t *block = row + (size_t)(first / 256) * 136;
+        const uint32_t i0 = first % 256, g = i0 / 32;
+        const uint32_t high = (uint32_t)block[2] | ((uint32_t)block[3] << 8);
+        const uint32_t low = (block[4 + g / 2] >> (4 * (g % 2))) & 15u;
+        const int scale = (int)(low | (((high >> (2 * g)) & 3u) << 4)) - 32;
+        const float multiplier = __fmul_rn(half_at(block), (float)scale);
+        const uint8_t *q = block + 8 + g * 16;
+        const uint32_t shift = ((i0 % 32) / 16) * 4;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) out[i] = __fmul_rn(multiplier, (float)iq4_value((q[i] >> shift) & 15u));
         break;
     }
     case Q2_K: {

@@ -7,7 +7,7 @@ descriptors can be sized before any device call.
 from __future__ import annotations
 
 F32, F16, Q8_0, Q4_K, Q6_K, BF16 = 0, 1, 8, 12, 14, 30
-Q4_0, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K = 2, 6, 7, 10, 11, 13  # served by the generic kernels (bit-exact decode, any alignment)
+Q4_0, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K, IQ4_NL, IQ4_XS = 2, 6, 7, 10, 11, 13, 20, 23  # served by the generic kernels (bit-exact decode, any alignment)
 
 LAYOUTS = {
     F32: ("F32", 1, 4),
@@ -21,6 +21,8 @@ LAYOUTS = {
     Q8_0: ("Q8_0", 32, 34),
     Q4_K: ("Q4_K", 256, 144),
     Q6_K: ("Q6_K", 256, 210),
+    IQ4_NL: ("IQ4_NL", 32, 18),
+    IQ4_XS: ("IQ4_XS", 256, 136),
     BF16: ("BF16", 1, 2),
 }
 

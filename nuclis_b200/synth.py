@@ -114,7 +114,25 @@ def q3_k(rng: np.random.Generator, rows: int, columns: int) -> np.ndarray:
     return out.reshape(-1)
 
 
-GENERATORS = {enc.Q2_K: q2_k, enc.Q3_K: q3_k, enc.Q4_K: q4_k, enc.Q6_K: q6_k, enc.Q8_0: q8_0, enc.Q4_0: q4_0, enc.Q5_0: q5_0, enc.Q5_1: q5_1, enc.Q5_K: q5_k}
+def iq4_nl(rng: np.random.Generator, rows: int, columns: int) -> np.ndarray:
+    """[rows * columns/32 * 18] bytes. Draw order: d, codes."""
+    blocks = rows * (columns // 32)
+    out = np.empty((blocks, 18), dtype=np.uint8)
+    out[:, 0:2] = _abs_normal_f16(rng, blocks, 2e-4)
+    out[:, 2:18] = rng.integers(0, 256, size=(blocks, 16), dtype=np.uint8)
+    return out.reshape(-1)
+
+
+def iq4_xs(rng: np.random.Generator, rows: int, columns: int) -> np.ndarray:
+    """[rows * columns/256 * 136] bytes. Draw order: d, scale bits and codes."""
+    blocks = rows * (columns // 256)
+    out = np.empty((blocks, 136), dtype=np.uint8)
+    out[:, 0:2] = _abs_normal_f16(rng, blocks, 1e-5)
+    out[:, 2:136] = rng.integers(0, 256, size=(blocks, 134), dtype=np.uint8)
+    return out.reshape(-1)
+
+
+GENERATORS = {enc.IQ4_NL: iq4_nl, enc.IQ4_XS: iq4_xs, enc.Q2_K: q2_k, enc.Q3_K: q3_k, enc.Q4_K: q4_k, enc.Q6_K: q6_k, enc.Q8_0: q8_0, enc.Q4_0: q4_0, enc.Q5_0: q5_0, enc.Q5_1: q5_1, enc.Q5_K: q5_k}
 
 
 def matrix(encoding: int, rows: int, columns: int, seed: int) -> np.ndarray:

@@ -59,12 +59,45 @@ int nu_ref_layout(uint32_t id, uint32_t *elements, uint32_t *bytes) {
     case 12: e = 256; b = 144; break; /* Q4_K */
     case 13: e = 256; b = 176; break; /* Q5_K */
     case 14: e = 256; b = 210; break; /* Q6_K */
+    case 20: e = 32; b = 18; break;   /* IQ4_NL */
+    case 23: e = 256; b = 136; break; /* IQ4_XS */
     case 30: e = 1; b = 2; break;     /* BF16 */
     default: return NU_REF_UNSUPPORTED_ENCODING;
     }
     if (elements) *elements = e;
     if (bytes) *bytes = b;
     return NU_REF_OK;
+}
+
+/* The sixteen values a four-bit IQ4 code selects (decode.zig:437): part of the storage format. */
+static const int8_t iq4_values[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+
+/* decode.zig:73-81: IQ4_NL, 18 bytes per 32 values: d, then 16 bytes whose low nibbles are the first
+ * half of the block and whose high nibbles are the second; value = d * table[code]. */
+static void iq4nl_block(const uint8_t *block, float *out) {
+    const float scale = half_at(block);
+    for (int j = 0; j < 16; ++j) {
+        out[j] = scale * (float)iq4_values[block[2 + j] & 15u];
+        out[j + 16] = scale * (float)iq4_values[block[2 + j] >> 4];
+    }
+}
+
+/* decode.zig:214-228: IQ4_XS, 136 bytes per 256 values: d, 16 bits of scale high parts, 4 bytes of scale
+ * low nibbles, 128 code bytes. Eight groups of 32 with a six-bit scale biased by 32; within a group the
+ * low nibbles are the first 16 values and the high nibbles the next 16. */
+static void iq4xs_block(const uint8_t *block, float *out) {
+    const float d = half_at(block);
+    const uint32_t high = (uint32_t)block[2] | ((uint32_t)block[3] << 8);
+    for (int g = 0; g < 8; ++g) {
+        const uint32_t low = (block[4 + g / 2] >> (4 * (g % 2))) & 15u;
+        const int scale = (int)(low | (((high >> (2 * g)) & 3u) << 4)) - 32;
+        const float multiplier = d * (float)scale;
+        const uint8_t *q = block + 8 + g * 16;
+        for (int j = 0; j < 16; ++j) {
+            out[g * 32 + j] = multiplier * (float)iq4_values[q[j] & 15u];
+            out[g * 32 + j + 16] = multiplier * (float)iq4_values[q[j] >> 4];
+        }
+    }
 }
 
 /* decode.zig:108-120: quotients are compared, nothing is multiplied. */
@@ -240,6 +273,8 @@ int nu_ref_row(uint32_t id, const uint8_t *bytes, size_t byte_count, float *out,
         case 12: q4k_block(0, block, out + o); break;
         case 13: q4k_block(1, block, out + o); break;
         case 14: q6k_block(block, out + o); break;
+        case 20: iq4nl_block(block, out + o); break;
+        case 23: iq4xs_block(block, out + o); break;
         case 30: {
             uint32_t bits = ((uint32_t)block[0] | ((uint32_t)block[1] << 8)) << 16;
             memcpy(out + o, &bits, 4);

@@ -48,8 +48,7 @@ _lib = None
 def _load():
     global _lib
     if _lib is None:
-        if not os.path.exists(_SO):
-            build()
+        build()  # compiles when the library is missing or older than its source
         lib = ctypes.CDLL(_SO)
         sz, u32, vp, f32 = ctypes.c_size_t, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_float
         lib.nu_ref_layout.argtypes = [u32, ctypes.POINTER(u32), ctypes.POINTER(u32)]

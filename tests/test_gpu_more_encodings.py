@@ -1,4 +1,4 @@
-"""GPU parity of the encodings served by the generic kernels: Q4_0, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K.
+"""GPU parity of the encodings served by the generic kernels: Q4_0, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K, IQ4_NL, IQ4_XS.
 
 The reference decodes them in inference/src/quant/decode.zig:46-56, 125-143, 147-196, 260-275 and pins
 them with the rows of its fixtures simple, five-bit, codebook, k-affine and k-signed.json, which
@@ -15,7 +15,7 @@ from parity import assert_matvec_close, expect, make_case, rel_l2
 
 pytestmark = pytest.mark.gpu
 
-ENCODINGS = [enc.Q4_0, enc.Q5_0, enc.Q5_1, enc.Q2_K, enc.Q3_K, enc.Q5_K]
+ENCODINGS = [enc.Q4_0, enc.Q5_0, enc.Q5_1, enc.Q2_K, enc.Q3_K, enc.Q5_K, enc.IQ4_NL, enc.IQ4_XS]
 
 
 @pytest.fixture(scope="module")

@@ -27,12 +27,13 @@ def test_layouts():
     assert oracle.layout(0) == (1, 4) and oracle.layout(1) == (1, 2) and oracle.layout(30) == (1, 2)
     assert oracle.layout(2) == (32, 18) and oracle.layout(6) == (32, 22) and oracle.layout(7) == (32, 24) and oracle.layout(13) == (256, 176)
     assert oracle.layout(10) == (256, 84) and oracle.layout(11) == (256, 110)
+    assert oracle.layout(20) == (32, 18) and oracle.layout(23) == (256, 136)
     with pytest.raises(oracle.OracleError):
         oracle.layout(999)
 
 
 def test_golden_rows_exact_on_unaligned_input(golden_rows):
-    assert {r["encoding"] for r in golden_rows} == {2, 6, 7, 8, 10, 11, 12, 13, 14}
+    assert {r["encoding"] for r in golden_rows} == {2, 6, 7, 8, 10, 11, 12, 13, 14, 20, 23}
     for r in golden_rows:
         shifted = np.empty(r["bytes"].size + 1, dtype=np.uint8)
         shifted[1:] = r["bytes"]
