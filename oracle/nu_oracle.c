@@ -69,6 +69,8 @@ int nu_ref_layout(uint32_t id, uint32_t *elements, uint32_t *bytes) {
     return NU_REF_OK;
 }
 
+static float half_at(const uint8_t *p);
+
 /* The sixteen values a four-bit IQ4 code selects (decode.zig:437): part of the storage format. */
 static const int8_t iq4_values[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
 
