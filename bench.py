@@ -373,6 +373,42 @@ class ExpertCase:
                 "distinct_expert_mb_per_replay": self.distinct * self.per_expert / 1e6, "parity_worst_over_bound": worst, "roofline": roof}
 
 
+def expert_prefill(b, tokens: int, seed: int, steps: int = 10) -> dict:
+    """The prefill form of config 4's layer: `tokens` token rows routed, their slot rows grouped by expert, both expert
+    GEMMs on the tensor-core tiles (router -> lists -> gate_up -> GELU gate -> down -> combine), microseconds per chain."""
+    from nuclis_b200 import Backend, CombineShape
+    case = ExpertCase(b, 1, seed, chains=1)
+    E, k, hidden, ff = case.experts, case.k, case.hidden, case.ff
+    slots = tokens * k
+    rng = np.random.default_rng(seed + tokens)
+    x = rng.standard_normal((tokens, hidden)).astype(np.float32)
+    logits = rng.standard_normal((tokens, E)).astype(np.float32)
+    xb, lb = b.create(x.nbytes), b.create(logits.nbytes)
+    xb.write(x); lb.write(logits)
+    ib, wb = b.create(slots * 4), b.create(slots * 4)
+    lists = b.create(Backend.expert_lists_words(slots, E) * 4)
+    gu_out, hid = b.create(slots * 2 * ff * 4), b.create(slots * ff * 4)
+    y, out = b.create(slots * hidden * 4), b.create(tokens * hidden * 4)
+    b.begin()
+    b.route(lb, E, k, tokens, E, ib, wb)
+    b.expert_lists(ib, tokens, k, E, lists)
+    b.matmul_experts(case.gub, case.gu_t, lists, tokens, k, xb, hidden, k, gu_out, 2 * ff)
+    b.gelu_mul_rows(gu_out, gu_out.slice(ff * 4, gu_out.len - ff * 4), hid, ff, slots, 2 * ff, 2 * ff, ff)
+    b.matmul_experts(case.dnb, case.dn_t, lists, tokens, k, hid, ff, 1, y, hidden)
+    b.combine_experts(y, wb, ib, None, out, CombineShape(columns=hidden, slots=k, experts=E, in_stride=hidden, out_stride=hidden, rows=tokens))
+    graph = b.commit_retain()
+    b.graph_launch(graph, 3)
+    us = b.graph_launch(graph, steps) / steps * 1e3
+    b.graph_release(graph)
+    flops = 2.0 * slots * (2 * ff * hidden + hidden * ff)
+    peaks, kind = measured_peaks()
+    for buf in (xb, lb, ib, wb, lists, gu_out, hid, y, out):
+        b.release(buf)
+    return {"us_per_chain": us, "tokens": tokens, "slot_rows": slots, "tflops": flops / us / 1e6,
+            "roofline": {"bound": "tensor", "achieved": flops / us / 1e6, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": flops / us / 1e6 / peaks["bf16_tflops"],
+                         "peak_source": f"{kind} cuBLAS bf16 (burst)"}}
+
+
 # ---- parity of one (sharded) layer of the recorded step, before anything is timed -------------------
 
 def layer_parity(b, tokens: int, rank: int, world: int, seed: int) -> dict:
@@ -472,6 +508,7 @@ def other_configs(b, args, stack8_value=None) -> dict:
     for tokens in (1, 8):
         case = ExpertCase(b, tokens, args.seed)
         ex[f"m{tokens}"] = case.measure(max(args.steps, 10), args.warmup)
+    ex["prefill_t512"] = expert_prefill(b, 512, args.seed)
     out["config4"] = {"workload": "expert decode chain: 128 experts, top-8, hidden 2816, width 704 (gate_up Q4_K, down Q8_0)", "cases": ex}
     return out
 

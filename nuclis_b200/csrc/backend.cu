@@ -19,7 +19,8 @@ struct FastJobBox { FastJob job; };
 namespace {
 
 constexpr size_t kPad = 256;                       // slack after every allocation: bulk copies may read up to 15 bytes past a row
-constexpr size_t kPartialsFloats = 4u << 20;       // 16 MiB of split-K partial sums
+constexpr size_t kPartialsFloats = 64u << 20;      // 256 MiB of scratch: split-K partial sums, the bf16 staging of F32 prefill activations,
+                                                   // the gathered rows of the grouped (expert) prefill
 constexpr size_t kCounters = 1u << 16;             // row-block arrival counters
 constexpr size_t kPushCapacity = 8 * 8192;         // floats per inbox slot: 8 token rows of up to 8192 values
 constexpr size_t kPushWordBytes = 2 * PUSH_MAX_RANKS * kPushCapacity * 8;   // (value, tag) words
@@ -783,8 +784,17 @@ int Backend::matmulExperts(const Buffer &weights, const ExpertMatrix &t, const B
     const size_t bound = expertTileBound(n, t.experts);
     if (bound > 65535) return fail(NU_ERR_TOO_LARGE, "matmul_experts: more than 65,535 tiles");
     if (int rc = needRecording()) return rc;
-    launches_ += launch_matmul_experts_generic(stream_, t.encoding, w, stride, per_expert, (uint32_t)t.experts, (uint32_t)t.rows, (uint32_t)t.columns, l,
-                                               (uint32_t)bound, in, in_stride, (uint32_t)in_group, out, out_stride);
+    // Many slot rows: the tensor-core tiles (bf16 operands, as the prefill of a dense matrix). A handful of rows per expert
+    // would leave the 64-row tiles mostly empty: those stay on the F32 kernel.
+    int launched = 0;
+    if (!generic_only && n >= 8 * t.experts && fits_u32(n))
+        launched = launch_matmul_experts_fast(stream_, t.encoding, w, stride, per_expert, (uint32_t)t.experts, (uint32_t)t.rows, (uint32_t)t.columns, l, (uint32_t)bound,
+                                              (uint32_t)n, in, in_stride, (uint32_t)in_group, out, out_stride, partials_, partials_floats_ * sizeof(float),
+                                              counters_ + counters_len_);
+    if (!launched)
+        launched = launch_matmul_experts_generic(stream_, t.encoding, w, stride, per_expert, (uint32_t)t.experts, (uint32_t)t.rows, (uint32_t)t.columns, l,
+                                                 (uint32_t)bound, in, in_stride, (uint32_t)in_group, out, out_stride);
+    launches_ += launched;
     wrote(output);
     opBoundary();
     return cuda(cudaGetLastError(), "matmul_experts: launch");

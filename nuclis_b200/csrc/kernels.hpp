@@ -138,6 +138,12 @@ struct PrefillJob {
 bool prefill_configure();
 bool prefill_supported(const PrefillJob &job);
 int launch_prefill(cudaStream_t s, const PrefillJob &job);
+// The prefill of a mixture-of-experts layer on the tensor cores: slot rows grouped by expert (`lists`, as launch_expert_lists
+// wrote them), gathered into whole 64-row tiles in `scratch`, one block per (tile, 128 weight rows). 0 when the form does not apply.
+size_t matmul_experts_scratch(uint32_t n, uint32_t experts, uint32_t columns);
+int launch_matmul_experts_fast(cudaStream_t s, uint32_t enc, const uint8_t *w, size_t stride, size_t expert_bytes, uint32_t experts, uint32_t rows, uint32_t columns,
+                               const uint32_t *lists, uint32_t bound, uint32_t n, const float *in, size_t in_stride, uint32_t in_group, float *out, size_t out_stride,
+                               void *scratch, size_t scratch_bytes, uint32_t *status);
 int launch_f32_to_bf16_rows(cudaStream_t s, const float *in, size_t in_stride, void *out, size_t out_stride, uint32_t columns, uint32_t tokens);
 
 // ---- one-shot allreduce over peer memory (push_allreduce.cu) ------------------------

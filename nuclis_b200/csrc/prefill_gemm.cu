@@ -48,6 +48,12 @@ struct Params {
     float *out;
     unsigned long long out_stride;
     uint32_t *status;
+    // Grouped form (expert tensors): a block's token tile is one record of `tiles` ([0] the tile count, then from word 4 on
+    // {expert, first gathered row, rows of the tile, first entry of the expert's slot-row list}), its weights are the
+    // expert's matrix, and its output rows are scattered to the slot rows `slot_rows` names. Null: the plain form.
+    const uint32_t *tiles;
+    const uint32_t *slot_rows;
+    unsigned long long expert_bytes;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -121,12 +127,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 __device__ __forceinline__ float byte_f32(uint32_t w, int j) { return __uint_as_float(__byte_perm(w, 0x4b000000u, 0x7650u + j)) - 8388608.0f; }
 
 // Decodes columns [k0 + 16 q, + 16) of row r to bf16, as two 16-byte chunks: the generic path.
-__device__ __forceinline__ void decode16_generic(const Params &p, uint32_t r, uint32_t k0, uint32_t q, uint4 chunks[2]) {
+__device__ __forceinline__ void decode16_generic(const Params &p, const uint8_t *w, uint32_t r, uint32_t k0, uint32_t q, uint4 chunks[2]) {
     float v[16];
     const uint32_t seg = k0 / 16 + q;
-    if (p.layout == 1) dequant16_planar_q6k(p.w, p.rows, p.columns / 256, r, seg, v);
-    else if (p.layout == 2) dequant16_planar_q8_0(p.w, p.rows, p.columns, r, seg, v);
-    else dequant16(p.enc, p.w + (size_t)r * p.stride, seg, v);
+    if (p.layout == 1) dequant16_planar_q6k(w, p.rows, p.columns / 256, r, seg, v);
+    else if (p.layout == 2) dequant16_planar_q8_0(w, p.rows, p.columns, r, seg, v);
+    else dequant16(p.enc, w + (size_t)r * p.stride, seg, v);
 #pragma unroll
     for (int c = 0; c < 2; ++c)
         chunks[c] = make_uint4(pack_bf16(v[c * 8], v[c * 8 + 1]), pack_bf16(v[c * 8 + 2], v[c * 8 + 3]), pack_bf16(v[c * 8 + 4], v[c * 8 + 5]),
@@ -158,7 +164,17 @@ __global__ void __launch_bounds__(THREADS, BPS) prefill_kernel(const __grid_cons
     volatile uint32_t *abort_flag = tmem_slot + 1;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // token tiles vary fastest over the grid: the blocks running together share a few row tiles of weights (L2) 
-    const uint32_t row0 = blockIdx.y * BM, tok0 = blockIdx.x * BN;
+    const uint32_t row0 = blockIdx.y * BM;
+    uint32_t tok0 = blockIdx.x * BN, tile_rows = 0, list_first = 0;
+    const uint8_t *wbase = p.w;
+    if (p.tiles) {
+        if (blockIdx.x >= p.tiles[0]) return;  // the grid is sized for the most tiles a routing can give; the whole block leaves
+        const uint32_t *t = p.tiles + 4 + 4 * (size_t)blockIdx.x;
+        wbase += (size_t)t[0] * p.expert_bytes;
+        tok0 = t[1];
+        tile_rows = t[2];
+        list_first = t[3];
+    }
     const uint32_t ksteps = p.columns / BK;
 
     if (tid == 0) {
@@ -213,7 +229,7 @@ __global__ void __launch_bounds__(THREADS, BPS) prefill_kernel(const __grid_cons
             // group (columns 0..31 of the step) and high nibbles the odd group (columns 32..63). Piece p holds
             // bytes 16 p .. 16 p + 15: columns 16 p .. + 15 of both groups. Values are (d*s)*q - dmin*m with one
             // rounding, like the reference decoder (inference/src/quant/decode.zig:147-170), then rounded to bf16.
-            const uint8_t *blk = p.w + (size_t)grow * p.stride;
+            const uint8_t *blk = wbase + (size_t)grow * p.stride;
             const uint32_t nsb = p.columns / 256;
             // the five 16-byte loads of a superblock are requested a whole superblock (four K steps) ahead
             uint4 hdr_n = ldg16(blk), q_n[4];
@@ -263,8 +279,8 @@ __global__ void __launch_bounds__(THREADS, BPS) prefill_kernel(const __grid_cons
             // columns of each run, one scale each; its 48 bytes serve two K steps (low nibbles: quarters 0, 1;
             // high nibbles: quarters 2, 3). Value = (d * scale) * (code - 32), exact.
             const uint32_t nsb = p.columns / 256;
-            const uint8_t *rec = p.w + (size_t)grow * nsb * 208;
-            const uint8_t *dp = p.w + (size_t)p.rows * nsb * 208 + (size_t)grow * 2;
+            const uint8_t *rec = wbase + (size_t)grow * nsb * 208;
+            const uint8_t *dp = wbase + (size_t)p.rows * nsb * 208 + (size_t)grow * 2;
             const size_t dstep = (size_t)p.rows * 2;
             // the loads of a superblock (two chunks of 48 bytes, 16 scale bytes, the super-scale) are requested a
             // whole superblock (four K steps) ahead
@@ -330,8 +346,8 @@ __global__ void __launch_bounds__(THREADS, BPS) prefill_kernel(const __grid_cons
             }
         } else if (MODE == 3) {
             // Planar Q8_0 (prepare.cu): 32 columns are one block; value = d * code, exact before the bf16 rounding.
-            const uint8_t *q = p.w + (size_t)grow * p.columns + piece * 32;
-            const uint8_t *dp = p.w + (size_t)p.rows * p.columns + ((size_t)piece * p.rows + grow) * 2;
+            const uint8_t *q = wbase + (size_t)grow * p.columns + piece * 32;
+            const uint8_t *dp = wbase + (size_t)p.rows * p.columns + ((size_t)piece * p.rows + grow) * 2;
             const size_t dstep = (size_t)p.rows * 4;  // two blocks per K step
             uint4 qa_n = ldg16(q), qb_n = ldg16(q + 16);
             float d_n = __half2float(*(const __half *)dp);
@@ -355,8 +371,8 @@ __global__ void __launch_bounds__(THREADS, BPS) prefill_kernel(const __grid_cons
         } else {
             for (uint32_t k = 0; k < ksteps && ok; ++k) {
                 uint4 chunks[4];
-                decode16_generic(p, grow, k * BK, piece * 2, &chunks[0]);
-                decode16_generic(p, grow, k * BK, piece * 2 + 1, &chunks[2]);
+                decode16_generic(p, wbase, grow, k * BK, piece * 2, &chunks[0]);
+                decode16_generic(p, wbase, grow, k * BK, piece * 2 + 1, &chunks[2]);
                 ok = put(chunks, piece * 4, piece * 4 + 2);
             }
         }
@@ -382,8 +398,12 @@ __global__ void __launch_bounds__(THREADS, BPS) prefill_kernel(const __grid_cons
                 if (out_row < p.rows) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const uint32_t tok = tok0 + c0 + j;
-                        if (tok < p.tokens) p.out[(size_t)tok * p.out_stride + out_row] = __uint_as_float(v[j]);
+                        if (p.tiles) {
+                            if ((uint32_t)(c0 + j) < tile_rows) p.out[(size_t)p.slot_rows[list_first + c0 + j] * p.out_stride + out_row] = __uint_as_float(v[j]);
+                        } else {
+                            const uint32_t tok = tok0 + c0 + j;
+                            if (tok < p.tokens) p.out[(size_t)tok * p.out_stride + out_row] = __uint_as_float(v[j]);
+                        }
                     }
                 }
             }
@@ -497,6 +517,85 @@ int launch_prefill(cudaStream_t s, const PrefillJob &j) {
     else if (bn == 128) launch_bn<128, 6, 1>(grid, s, p, mode);
     else launch_bn<64, 8, 1>(grid, s, p, mode);
     return 1;
+}
+
+// ---- grouped form: the prefill of a mixture-of-experts layer --------------------------------------
+// `Backend.matmulExperts` (ops/experts.zig:148-202; the reference's gathered tiles: kernels/matmul.metal:552-570,
+// kernels/experts.metal:179-213). The slot rows arrive grouped by expert (the lists `expertLists` wrote). A gather
+// pass copies each expert's input rows, rounded to bf16, into the scratch as whole tiles of 64 rows (the tail of an
+// expert's last tile is zero), and writes one record per tile; the tensor-core kernel above then runs one block per
+// (tile, 128 weight rows) on the expert's matrix and scatters its output rows through the list.
+
+constexpr int GROUP_BN = 64;
+
+// lists: [0] tile count of the reference's own tiling (unused here), [1] n, [2 .. 2 + experts] exclusive prefix offsets of
+// the experts' slot rows, then 3 * bound words, then the n slot rows grouped by expert.
+__global__ void __launch_bounds__(256) expert_gather_kernel(const uint32_t *lists, uint32_t experts, uint32_t bound, const float *in, size_t in_stride,
+                                                            uint32_t in_group, uint32_t columns, __nv_bfloat16 *gathered, uint32_t *table) {
+    __shared__ uint32_t found[4];  // expert, rows of this tile, first list entry, total tiles
+    const uint32_t *offsets = lists + 2, *slot_rows = lists + experts + 3 + 3 * (size_t)bound;
+    const uint32_t tile = blockIdx.x, tid = threadIdx.x;
+    if (tid == 0) {
+        uint32_t at = 0;
+        found[0] = 0xffffffffu;
+        for (uint32_t e = 0; e < experts; ++e) {
+            const uint32_t count = offsets[e + 1] - offsets[e], tiles = (count + GROUP_BN - 1) / GROUP_BN;
+            if (tile >= at && tile < at + tiles) {
+                found[0] = e;
+                found[1] = min((uint32_t)GROUP_BN, count - (tile - at) * GROUP_BN);
+                found[2] = offsets[e] + (tile - at) * GROUP_BN;
+            }
+            at += tiles;
+        }
+        found[3] = at;
+        if (tile == 0) table[0] = at;
+        if (found[0] != 0xffffffffu) {
+            uint32_t *rec = table + 4 + 4 * (size_t)tile;
+            rec[0] = found[0]; rec[1] = tile * GROUP_BN; rec[2] = found[1]; rec[3] = found[2];
+        }
+    }
+    __syncthreads();
+    if (found[0] == 0xffffffffu) return;
+    const uint32_t rows = found[1], first = found[2];
+    for (uint32_t i = 0; i < GROUP_BN; ++i) {
+        __nv_bfloat16 *dst = gathered + ((size_t)tile * GROUP_BN + i) * columns;
+        if (i < rows) {
+            const float *src = in + (size_t)(slot_rows[first + i] / in_group) * in_stride;
+            for (uint32_t c = tid; c < columns; c += 256) dst[c] = __float2bfloat16_rn(src[c]);
+        } else {
+            for (uint32_t c = tid; c < columns; c += 256) dst[c] = __float2bfloat16_rn(0.0f);
+        }
+    }
+}
+
+// Bytes of scratch the grouped form needs for `n` slot rows: the tile table, then the gathered bf16 rows.
+size_t matmul_experts_scratch(uint32_t n, uint32_t experts, uint32_t columns) {
+    const size_t tiles = (size_t)(n + GROUP_BN - 1) / GROUP_BN + (experts < n ? experts : n);
+    return ((4 + 4 * tiles) * 4 + 1023) / 1024 * 1024 + tiles * GROUP_BN * columns * 2;
+}
+
+int launch_matmul_experts_fast(cudaStream_t s, uint32_t enc, const uint8_t *w, size_t stride, size_t expert_bytes, uint32_t experts, uint32_t rows, uint32_t columns,
+                               const uint32_t *lists, uint32_t bound, uint32_t n, const float *in, size_t in_stride, uint32_t in_group, float *out, size_t out_stride,
+                               void *scratch, size_t scratch_bytes, uint32_t *status) {
+    if (layout(enc).elements == 0 || columns == 0 || columns % 64 != 0 || rows == 0 || n == 0) return 0;
+    if (matmul_experts_scratch(n, experts, columns) > scratch_bytes || (uintptr_t)scratch % 1024 != 0 || (uintptr_t)out % 4 != 0) return 0;
+    const size_t tiles = (size_t)(n + GROUP_BN - 1) / GROUP_BN + (experts < n ? experts : n);
+    if (tiles > 65535u * 32u) return 0;
+    uint32_t *table = (uint32_t *)scratch;
+    __nv_bfloat16 *gathered = (__nv_bfloat16 *)((uint8_t *)scratch + ((4 + 4 * tiles) * 4 + 1023) / 1024 * 1024);
+    prefill::Params p;
+    memset(&p, 0, sizeof p);
+    if (!encode_tiled_map(&p.xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, gathered, columns, tiles * GROUP_BN, (uint64_t)columns * 2, 64, GROUP_BN, CU_TENSOR_MAP_SWIZZLE_128B))
+        return 0;
+    expert_gather_kernel<<<(unsigned)tiles, 256, 0, s>>>(lists, experts, bound, in, in_stride, in_group, columns, gathered, table);
+    p.w = w; p.stride = stride; p.enc = enc; p.layout = 0;
+    p.fast = enc == Q4_K && (uintptr_t)w % 16 == 0 && stride % 16 == 0 && expert_bytes % 16 == 0 && columns % 256 == 0;
+    p.rows = rows; p.columns = columns; p.tokens = (uint32_t)(tiles * GROUP_BN);
+    p.out = out; p.out_stride = out_stride; p.status = status;
+    p.tiles = table; p.slot_rows = lists + experts + 3 + 3 * (size_t)bound; p.expert_bytes = expert_bytes;
+    dim3 grid((unsigned)tiles, (rows + prefill::BM - 1) / prefill::BM);
+    launch_bn<64, 8, 1>(grid, s, p, p.fast ? 1 : 0);
+    return 2;
 }
 
 // ---- F32 -> BF16 rows (the reference's matmul takes F32 activations) ------------------------------

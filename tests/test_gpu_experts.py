@@ -234,6 +234,73 @@ def test_gathered_matmul_over_expert_lists_matches_cpu_ffn(backend, tensors):
         backend.release(buf)
 
 
+@pytest.mark.parametrize("tokens", [256, 301])
+def test_grouped_prefill_on_the_tensor_cores_matches_cpu_ffn(backend, tensors, tokens):
+    """The prefill of the expert layer at a chunk of 256 token rows (2,048 slot rows, 16 per expert on average; 301: ragged
+    groups): `matmulExperts` takes the tensor-core tiles (bf16 operands, F32 accumulate). Each of the two grouped GEMMs is
+    checked alone, slot row by slot row for a sample of slots and every output row, against the oracle's matvec on the
+    bf16-rounded input: relative L2 <= 2e-2 and per element 4e-3 * sum|w*x| + 1e-6, the bounds of the dense prefill; then
+    the whole chain against cpu.experts.ffn at the bf16 tolerance, and the same call on the F32 kernel agrees with both."""
+    from test_gpu_prefill import from_bf16_bits, to_bf16_bits
+    gate_up, down = tensors
+    rng = np.random.default_rng(tokens)
+    x = rng.standard_normal((tokens, HIDDEN)).astype(np.float32)
+    logits = rng.standard_normal((tokens, EXPERTS)).astype(np.float32)
+    gu_t = ExpertMatrix(enc.Q4_K, EXPERTS, 2 * FF, HIDDEN, gate_up.size)
+    dn_t = ExpertMatrix(enc.Q8_0, EXPERTS, HIDDEN, FF, down.size)
+    slots = tokens * K
+    gub, dnb = backend.wrap(gate_up), backend.wrap(down)
+    xb = backend.create(x.nbytes); lb = backend.create(logits.nbytes)
+    ib = backend.create(slots * 4); wb = backend.create(slots * 4)
+    lists = backend.create(Backend.expert_lists_words(slots, EXPERTS) * 4)
+    gu_out = backend.create(slots * 2 * FF * 4); hid = backend.create(slots * FF * 4)
+    y = backend.create(slots * HIDDEN * 4); out = backend.create(tokens * HIDDEN * 4)
+    xb.write(x); lb.write(logits)
+    gu_out.write(np.full(slots * 2 * FF, np.nan, dtype=np.float32)); y.write(np.full(slots * HIDDEN, np.nan, dtype=np.float32))
+    launches = backend.launch_count
+    backend.begin()
+    backend.route(lb, EXPERTS, K, tokens, EXPERTS, ib, wb)
+    backend.expert_lists(ib, tokens, K, EXPERTS, lists)
+    backend.matmul_experts(gub, gu_t, lists, tokens, K, xb, HIDDEN, K, gu_out, 2 * FF)
+    backend.gelu_mul_rows(gu_out, gu_out.slice(FF * 4, gu_out.len - FF * 4), hid, FF, slots, 2 * FF, 2 * FF, FF)
+    backend.matmul_experts(dnb, dn_t, lists, tokens, K, hid, FF, 1, y, HIDDEN)
+    backend.combine_experts(y, wb, ib, None, out, CombineShape(columns=HIDDEN, slots=K, experts=EXPERTS, in_stride=HIDDEN, out_stride=HIDDEN, rows=tokens))
+    backend.commit()
+    assert backend.launch_count - launches == 8   # the two grouped GEMMs are a gather pass and the tile kernel each
+    picked = ib.read(np.uint32, slots)
+    gu, hidden_rows, yy = gu_out.floats().reshape(slots, 2 * FF), hid.floats().reshape(slots, FF), y.floats().reshape(slots, HIDDEN)
+    assert np.all(np.isfinite(gu)) and np.all(np.isfinite(yy))
+    gu_per, dn_per = gate_up.size // EXPERTS, down.size // EXPERTS
+    for s in list(range(0, slots, max(1, slots // 24))) + [slots - 1]:
+        e = int(picked[s])
+        xr = from_bf16_bits(to_bf16_bits(x[s // K]))
+        w_e = gate_up[e * gu_per:(e + 1) * gu_per]
+        want = oracle.matvec(enc.Q4_K, 2 * FF, HIDDEN, w_e, xr)
+        mag = oracle.matvec_abs(enc.Q4_K, 2 * FF, HIDDEN, w_e, xr)
+        assert np.max(np.abs(gu[s] - want) / (4e-3 * mag + 1e-6)) <= 1.0 and np.linalg.norm(gu[s] - want) <= 2e-2 * np.linalg.norm(want), ("gate_up", s)
+        hr = from_bf16_bits(to_bf16_bits(hidden_rows[s]))
+        d_e = down[e * dn_per:(e + 1) * dn_per]
+        want = oracle.matvec(enc.Q8_0, HIDDEN, FF, d_e, hr)
+        mag = oracle.matvec_abs(enc.Q8_0, HIDDEN, FF, d_e, hr)
+        assert np.max(np.abs(yy[s] - want) / (4e-3 * mag + 1e-6)) <= 1.0 and np.linalg.norm(yy[s] - want) <= 2e-2 * np.linalg.norm(want), ("down", s)
+    got = out.floats().reshape(tokens, HIDDEN)
+    for t in (0, tokens // 2, tokens - 1):
+        idx, w = oracle.route(logits[t], K)
+        want = oracle.ffn((enc.Q4_K, EXPERTS, 2 * FF, HIDDEN, gate_up), (enc.Q8_0, EXPERTS, HIDDEN, FF, down), x[t], idx, w)
+        assert np.linalg.norm(got[t] - want) <= 2e-2 * np.linalg.norm(want), t
+    # the F32 kernel on the same lists: the two forms agree at the bf16 tolerance
+    backend.generic_only = True
+    backend.begin()
+    backend.matmul_experts(gub, gu_t, lists, tokens, K, xb, HIDDEN, K, gu_out, 2 * FF)
+    backend.commit()
+    backend.generic_only = False
+    exact = gu_out.floats().reshape(slots, 2 * FF)
+    assert np.linalg.norm(gu - exact) <= 2e-2 * np.linalg.norm(exact)
+    backend.unwrap(gate_up); backend.unwrap(down)
+    for buf in (xb, lb, ib, wb, lists, gu_out, hid, y, out):
+        backend.release(buf)
+
+
 def test_gathered_matvec_reads_only_selected_experts(backend):
     # unselected experts hold NaN-decoding bytes (scale 0x7e00): a stray read poisons the output
     experts, rows, cols = 6, 32, 256
