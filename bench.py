@@ -565,7 +565,7 @@ def dominant_kernel(b, stack, tokens: int) -> dict:
     mats = 2 if tokens == 1 else 1
     algo = mats * stack.m_gate.bytes + tokens * stack.shapes.hidden * 4 + tokens * l.ffn_rows * 4
     # ncu dram__bytes_read + write of one launch of this kernel on a 50.1 MB matrix (profiles/), scaled by the bytes of this launch
-    traffic = algo * (50.221056 + 0.001536) / 50.13504 if tokens == 1 else None
+    traffic = algo * (50.221056 + 0.001024) / 50.13504 if tokens == 1 else None
     return hbm_roofline(algo, us, "i8_kernel<Q4K> (SiLU gate/up pair, one token)" if tokens == 1 else "i8_kernel<Q4K> (gate, token rows)", traffic)
 
 

@@ -53,16 +53,17 @@ bool encode_weight_map(CUtensorMap *map, const uint8_t *base, uint64_t row_bytes
 }
 
 bool fast_supported(const FastJob &job) {
-    return q4k_i8_supported(job) || q6k_decode_supported(job) || q8_0_decode_supported(job) || q6k_rows_supported(job) || q8_0_rows_supported(job);
+    return q4k_i8_supported(job) || q6k_i8_supported(job) || q6k_decode_supported(job) || q8_0_decode_supported(job) || q6k_rows_supported(job) || q8_0_rows_supported(job);
 }
 
 bool fast_configure() {
-    return q4k_i8_configure() && q6k_decode_configure() && q8_0_decode_configure() && q6k_rows_configure() &&
+    return q4k_i8_configure() && q6k_i8_configure() && q6k_decode_configure() && q8_0_decode_configure() && q6k_rows_configure() &&
            q8_0_rows_configure() && prefill_configure() && expert_gemv_configure();
 }
 
 int launch_fast(cudaStream_t s, const FastJob &job) {
     if (q4k_i8_supported(job)) return launch_q4k_i8(s, job);
+    if (q6k_i8_supported(job)) return launch_q6k_i8(s, job);
     if (q6k_decode_supported(job)) return launch_q6k_decode(s, job);
     if (q8_0_decode_supported(job)) return launch_q8_0_decode(s, job);
     if (q6k_rows_supported(job)) return launch_q6k_rows(s, job);

@@ -58,6 +58,12 @@ struct Q4K {
     static constexpr int ROW_PITCH = STAGE_SBS * ROW_BYTES;  // 720 bytes = 180 words between the rows of a stage: rows two apart
                                                           // lie 8 banks apart, which the lanes' 8-byte loads need (row_of)
     static constexpr int STAGE_BYTES = 16 * ROW_PITCH;    // 11520, a multiple of 128
+    static constexpr int GROUP = 32;                      // columns per scale group
+    static constexpr int GS_BYTES = 16;                   // staged group sums per superblock and B column: eight fp16
+    static constexpr float GS_SCALE = 0.000244140625f;    // 2^-12: a group sum of X (below 2^27) fits fp16
+    static constexpr int PLANE_SKEW = 32;                 // digit rows 32 bytes apart round the banks: 8-byte loads, 4 lanes a row
+    static constexpr int LANE_BYTES = 8;                  // digits a lane supplies per mma: columns 8t..8t+7 of the group
+    static constexpr float UNIT = 0.0625f;                // the integer sums carry 16 (high nibbles left in place)
 
     // One box of 16 rows x 720 bytes. Measured on B200: boxes of 16 x 144 bytes stream at 3.3 TB/s however many are
     // in flight (the copy engine's cost is per row of a box), 16 x 720 bytes at 6.2 TB/s. The tensor map counts in
@@ -67,13 +73,14 @@ struct Q4K {
         tma_load_2d(dst, &p.map[seg], sb * (ROW_BYTES / 4), row0, bar, policy);
     }
 
-    // One task: task rows gr and gr + 8 against every B column. xb: this lane's digit row at the task's
+    // One task (superblock `part` of the stage): task rows gr and gr + 8 against every B column. xb: this lane's digit row at the task's
     // superblock (its 8 bytes of group 0); the digit rows of the next mma (wide) lie 8 * pitch further.
     // gsb: this lane's word of the group sums. iv: 1 / the activation scale of the lane's token(s) at this superblock.
     // acc: (row gr, token a), (gr, a + 1), (gr + 8, a), (gr + 8, a + 1); with one token the odd entries stay untouched.
     template <int NT>
-    __device__ static __forceinline__ void task(const uint8_t *task, const uint8_t *xb, uint32_t pitch, const uint8_t *gsb, uint32_t gs_step, const float *iv, float wl,
-                                                uint32_t gr, uint32_t t, float acc[4]) {
+    __device__ static __forceinline__ void task(const uint8_t *stage, uint32_t part, const uint8_t *xb, uint32_t pitch, const uint8_t *gsb, uint32_t gs_step, const float *iv,
+                                                float wl, uint32_t gr, uint32_t t, float acc[4]) {
+        const uint8_t *task = stage + part * ROW_BYTES;
         constexpr bool WIDE = NT == 8;
         constexpr int NC = WIDE ? 3 : 1;
         constexpr int STEP = NT == 1 ? 2 : 1;  // one token: accumulator columns 0 and 2 only

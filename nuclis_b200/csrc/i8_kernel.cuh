@@ -53,7 +53,7 @@ struct Params {
     uint32_t ksb, ksl, nks;  // superblocks per row, per slice; slices
     uint32_t units;          // units per slice: 16-row tiles (pair mode: a gate tile with its up tile)
     uint32_t blk_first[MAX_SLICES + 1];  // blocks blk_first[s] .. blk_first[s+1]-1 work on slice s
-    uint32_t plane_pitch;    // bytes between the digit rows of two B columns (32 mod 128: the eight rows a warp reads hit different banks)
+    uint32_t plane_pitch;    // bytes between the digit rows of two B columns (32 or 16 mod 128: the eight rows a warp reads hit different banks)
     uint32_t gs_pitch;       // bytes between the group-sum rows of two B columns (16 mod 128)
     const float *in;
     uint32_t in_stride;
@@ -162,8 +162,8 @@ __device__ __forceinline__ void write_unit(const Params &p, uint32_t unit, uint3
 // Shared memory: [stages][digit rows][group-sum rows][128 zero bytes][1/scale per (superblock, token)][part sums][barriers]
 template <class E, class G, int NT>
 static size_t smem_bytes(uint32_t ksl, bool pair, int stages) {
-    const size_t plane_pitch = (size_t)ksl * 256 + 32;
-    const size_t gs_pitch = (size_t)ksl * 16 + (16 + 128 - ((size_t)ksl * 16) % 128) % 128;
+    const size_t plane_pitch = (size_t)ksl * 256 + E::PLANE_SKEW;
+    const size_t gs_pitch = (size_t)ksl * E::GS_BYTES + (16 + 128 - ((size_t)ksl * E::GS_BYTES) % 128) % 128;
     const size_t parts = (size_t)G::SLOTS * 2 * (G::PARTS - 1) * (pair ? 2 : 1) * record_lanes<NT>() * 16;
     return (size_t)G::SLOTS * stages * E::STAGE_BYTES + plane_columns<NT>() * plane_pitch + gs_columns<NT>() * gs_pitch + 128 + (size_t)ksl * 8 * 4 + parts +
            G::SLOTS * stages * 16 + 256;
@@ -172,7 +172,8 @@ static size_t smem_bytes(uint32_t ksl, bool pair, int stages) {
 template <class E, class G, int NT, int STAGES>
 __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant__ Params p) {
     constexpr bool WIDE = NT == 8;
-    constexpr int STAGE_BYTES = E::STAGE_BYTES;  // 16 weight rows x PARTS superblocks: one TMA box, one task per warp of the slot
+    constexpr int STAGE_BYTES = E::STAGE_BYTES;  // 16 weight rows x PARTS superblocks (one TMA box, one task per warp of the slot),
+                                                 // then whatever second plane the encoding's records need
     constexpr int WARPS = G::WARPS, SLOTS = G::SLOTS, PARTS = G::PARTS;
     static_assert(PARTS == E::STAGE_SBS, "a stage holds one superblock per K part");
     constexpr int REC = record_lanes<NT>();
@@ -286,7 +287,7 @@ __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant
                 const bool ok = e >= 22u && e < 255u;
                 const float scale = ok ? __uint_as_float((275u - e) << 23) : 0.0f;
                 // the digit rows of this token: B column of plane d is (narrow) d * 2 + token, (wide) d * 8 + token
-                uint8_t *row0 = planes + (size_t)tok * p.plane_pitch + sb * 256 + lane * 4;
+                uint8_t *row0 = planes + (size_t)tok * p.plane_pitch + sb * 256 + lane * 4;  // byte c of a superblock's 256 is column c
                 const uint32_t plane_step = (WIDE ? 8u : 2u) * p.plane_pitch;
                 int gsum[2];
 #pragma unroll
@@ -303,17 +304,19 @@ __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant
                         x0 = (x0 + 128) >> 8; x1 = (x1 + 128) >> 8; x2 = (x2 + 128) >> 8; x3 = (x3 + 128) >> 8;
                     }
                 }
-                // 32-column group sums of X (exact integers below 2^27), times 2^-12, as fp16 pieces hi + lo
+                // group sums of X over the encoding's scale groups (exact integers below 2^27; 32 columns: eight lanes,
+                // 16 columns: four), scaled to fit fp16, as pieces hi + lo
+                constexpr uint32_t GLANES = E::GROUP / 4, GPER = 128 / E::GROUP;  // lanes and groups per 128 columns
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
                     int s = gsum[hf];
                     s += __shfl_xor_sync(0xffffffffu, s, 1);
                     s += __shfl_xor_sync(0xffffffffu, s, 2);
-                    s += __shfl_xor_sync(0xffffffffu, s, 4);
-                    if ((lane & 7u) == 0) {
-                        const float f = (float)s * 0.000244140625f;
+                    if (GLANES == 8) s += __shfl_xor_sync(0xffffffffu, s, 4);
+                    if ((lane & (GLANES - 1)) == 0) {
+                        const float f = (float)s * E::GS_SCALE;
                         const __half sh = __float2half_rn(f), sl = __float2half_rn(f - __half2float(sh));
-                        const uint32_t grp = sb * 8 + hf * 4 + (lane >> 3);
+                        const uint32_t grp = sb * (2 * GPER) + hf * GPER + lane / GLANES;
                         *(__half *)(gs + (size_t)tok * p.gs_pitch + grp * 2) = sh;
                         *(__half *)(gs + (size_t)((WIDE ? 8u : 2u) + tok) * p.gs_pitch + grp * 2) = sl;
                     }
@@ -333,21 +336,21 @@ __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant
     const uint8_t *gslane;
     uint32_t gs_step;   // bytes from a lane's hi group sums to its lo group sums (wide)
     if (WIDE) {
-        xlane = planes + (size_t)(g < p.tokens ? g : 0u) * p.plane_pitch + t * 8;
+        xlane = planes + (size_t)(g < p.tokens ? g : 0u) * p.plane_pitch + t * E::LANE_BYTES;
         gslane = g < p.tokens ? gs + (size_t)g * p.gs_pitch + t * 4 : zero;
         gs_step = g < p.tokens ? 8u * p.gs_pitch : 0u;
     } else {
         const bool used = g < 6 && (g & 1u) < (uint32_t)NT;
-        xlane = planes + (size_t)(used ? g : 0u) * p.plane_pitch + t * 8;
+        xlane = planes + (size_t)(used ? g : 0u) * p.plane_pitch + t * E::LANE_BYTES;
         // the mma of the minima has columns (piece, token): 0, 1 hi; 2, 3 lo
         const bool gs_used = g < 4 && (g & 1u) < (uint32_t)NT;
         gslane = gs_used ? gs + (size_t)g * p.gs_pitch + t * 4 : zero;
         gs_step = 0;
     }
-    const uint32_t gs_sb = (gslane == zero) ? 0u : 16u;
-    // narrow: lane t holds the sums of digit plane t (weights 1, 2^8, 2^16; quad lane 3 holds nothing); 1/16 undoes
-    // the high nibbles left in place
-    const float wl = WIDE ? 0.0625f : (t == 0 ? 0.0625f : t == 1 ? 16.0f : t == 2 ? 4096.0f : 0.0f);
+    const uint32_t gs_sb = (gslane == zero) ? 0u : (uint32_t)E::GS_BYTES;
+    // narrow: lane t holds the sums of digit plane t (weights 1, 2^8, 2^16; quad lane 3 holds nothing); E::UNIT undoes
+    // a factor the encoding's integer sums carry (Q4_K: 16, the high nibbles left in place)
+    const float wl = E::UNIT * (WIDE ? 1.0f : (t == 0 ? 1.0f : t == 1 ? 256.0f : t == 2 ? 65536.0f : 0.0f));
     const float *ivlane = inv + (WIDE ? 2 * t : 0);  // 1 / scale of the lane's token(s), per superblock
     uint32_t c_stage = 0, c_phase = 0, consumed = 0;
     bool failed = false;
@@ -362,7 +365,7 @@ __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant
             if (part == 0 && issued < total) issue();  // keep STAGES - 1 stages in flight
             if (!mbar_wait(full0 + c_stage * 8, c_phase)) { failed = true; break; }
             if (live)
-                E::template task<NT>(my_stage + c_stage * STAGE_BYTES + part * E::ROW_BYTES, xlane + sbw * 256, p.plane_pitch, gslane + sbw * gs_sb, gs_step, ivlane + sbw * 8, wl, gr, t, acc);
+                E::template task<NT>(my_stage + c_stage * STAGE_BYTES, part, xlane + sbw * 256, p.plane_pitch, gslane + sbw * gs_sb, gs_step, ivlane + sbw * 8, wl, gr, t, acc);
             __syncwarp();  // all lanes are done reading this stage
             if (lane == 0) mbar_arrive(empty0 + c_stage * 8);
             ++consumed;
@@ -371,7 +374,7 @@ __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant
                 if (part == 0 && issued < total) issue();
                 if (!mbar_wait(full0 + c_stage * 8, c_phase)) { failed = true; break; }
                 if (live)
-                    E::template task<NT>(my_stage + c_stage * STAGE_BYTES + part * E::ROW_BYTES, xlane + sbw * 256, p.plane_pitch, gslane + sbw * gs_sb, gs_step, ivlane + sbw * 8, wl, gr, t, acc2);
+                    E::template task<NT>(my_stage + c_stage * STAGE_BYTES, part, xlane + sbw * 256, p.plane_pitch, gslane + sbw * gs_sb, gs_step, ivlane + sbw * 8, wl, gr, t, acc2);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty0 + c_stage * 8);
                 ++consumed;
@@ -569,8 +572,8 @@ static bool fill_geometry(const FastJob &job, Params &p, Plan &plan) {
         }
     }
     if (best >= 1e30) return false;
-    p.plane_pitch = p.ksl * 256 + 32;
-    p.gs_pitch = p.ksl * 16 + (16 + 128 - (p.ksl * 16) % 128) % 128;
+    p.plane_pitch = p.ksl * 256 + E::PLANE_SKEW;
+    p.gs_pitch = p.ksl * E::GS_BYTES + (16 + 128 - (p.ksl * E::GS_BYTES) % 128) % 128;
     plan.smem = smem_bytes<E, G, NT>(p.ksl, pair, plan.stages);
     p.partials = job.partials;
     p.counters = job.counters;

@@ -105,6 +105,10 @@ bool q4k_i8_supported(const FastJob &job);
 int launch_q4k_i8(cudaStream_t s, const FastJob &job);
 // The K slices and blocks the launch would use (host arithmetic only).
 bool q4k_i8_plan(const FastJob &job, uint32_t *slices, uint32_t *blocks);
+// ---- 1..8 activation rows on planar Q6_K, integer tensor path (gemv_q6k_i8.cu) -----
+bool q6k_i8_configure();
+bool q6k_i8_supported(const FastJob &job);
+int launch_q6k_i8(cudaStream_t s, const FastJob &job);
 // ---- decode GEMV (one activation row) on the planar forms --------------------------
 // 2..8 token rows on planar Q6_K (gemv_q6k_rows.cu)
 bool q6k_rows_configure();
