@@ -579,6 +579,7 @@ def run_gpu(args, rank: int, world: int, local: int):
     if world > 1:
         dist.init_process_group("gloo", rank=rank, world_size=world)
     b = Backend(local)
+    b.chaining = args.chain
     if world > 1:
         from nuclis_b200.group import join, torch_all_gather
         join(b, rank, world, torch_all_gather(), peer_memory=not args.nccl_only)
@@ -590,7 +591,7 @@ def run_gpu(args, rank: int, world: int, local: int):
 
     tokens = args.tokens
     parity = layer_parity(b, tokens, rank, world, args.seed)
-    stack = make_stack(b, tokens, LAYERS, ranks=world, rank=rank, seed=args.seed)
+    stack = make_stack(b, tokens, args.layers, ranks=world, rank=rank, seed=args.seed)
     torch.cuda.synchronize()
     sampler = ClockSampler(local)
     if rank == 0:
@@ -646,9 +647,10 @@ def run_gpu(args, rank: int, world: int, local: int):
         line = {
             "metric": "synthetic 27B-shape decode tok/s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "f32 out; int8 tensor-core products of 4-bit codes x 24-bit fixed-point activations (Q4_K), fp16 hi+lo products (Q6_K), f32 accumulate", "data": "synthetic",
-            "config": {"workload": f"config 2: 64-layer 27B-shape decode stack, M={tokens}", "tokens": tokens, "layers": LAYERS,
-                       "parallelism": f"tp{world}", "l2": "13.4 GB of weights per step, far larger than L2", "operators_per_step": ops},
+            "dtype": "f32 out; int8 tensor-core products of 4- and 6-bit codes x 24-bit fixed-point activations, f32 accumulate", "data": "synthetic",
+            "config": {"workload": f"config 2: {args.layers}-layer 27B-shape decode stack, M={tokens}" + ("" if args.layers == LAYERS else " (NOT the configuration: a profiler-sized stack)"),
+                       "tokens": tokens, "layers": args.layers, "parallelism": f"tp{world}", "l2": f"{13.4 * args.layers / LAYERS:.1f} GB of weights per step, far larger than L2",
+                       "operators_per_step": ops, "chained": args.chain},
             "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": up, "d2h_bytes_per_step": down},
             "gpu_launches": int(launches) * args.steps,
             "roofline": roofline, "parity": parity, "cpu_baseline": cpu, "clocks": clocks, "configs": configs,
@@ -698,6 +700,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="seconds of layer passes timed on the CPU oracle for cpu_baseline")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="the stack alone: skip the other configurations")
+    ap.add_argument("--layers", type=int, default=LAYERS, help="layers of the stack (the configuration has 64; fewer only for a profiler capture, and the line says so)")
+    ap.add_argument("--chain", action="store_true", help="runs of matvecs as one persistent kernel each instead of kernels of their own (measured slower; off by default)")
     ap.add_argument("--nccl-only", action="store_true", help="sum the short vectors with NCCL instead of the peer-memory allreduce")
     ap.add_argument("--workload", default="stack", choices=["stack", "gemv", "prefill", "experts"])
     ap.add_argument("--encoding", type=int, default=12, help="GGUF type id of the matrix of --workload gemv / prefill (12 Q4_K, 14 Q6_K, 8 Q8_0)")

@@ -116,6 +116,16 @@ const char *nu_cuda_status_name(int status);
 /* `Backend.generic_only` (root.zig:99-104): force the plain decode-and-FMA
  * kernels even where a specialized kernel applies. */
 int nu_cuda_set_generic_only(nu_cuda *h, int on);
+/* No counterpart in the reference. With `on` != 0, one-token matvecs on the
+ * specialized kernels that are recorded back to back (a decode layer's QKV, O,
+ * gate/up pair and down projections) are launched as ONE persistent kernel that
+ * walks them in order, a grid-wide barrier between two of them: the weight
+ * stream of an operator starts while other blocks still finish the one before.
+ * Same results bit for bit. Off by default: on a B200 the barrier and the
+ * per-operator set-up inside one resident block cost more than the launches
+ * they replace (225 against 289 tokens/s on the 64-layer stack). Takes effect
+ * at the next operator recorded. */
+int nu_cuda_set_chaining(nu_cuda *h, int on);
 
 /* ---- buffers (nu_metal_buffer_create / wrap / contents / release) -------- */
 

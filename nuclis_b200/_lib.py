@@ -49,6 +49,7 @@ SIGNATURES = {
     "nu_cuda_last_error": (ctypes.c_char_p, [vp]),
     "nu_cuda_status_name": (ctypes.c_char_p, [cint]),
     "nu_cuda_set_generic_only": (cint, [vp, cint]),
+    "nu_cuda_set_chaining": (cint, [vp, cint]),
     "nu_cuda_buffer_create": (cint, [vp, sz, ctypes.POINTER(u32)]),
     "nu_cuda_buffer_upload": (cint, [vp, u32, sz, vp, sz]),
     "nu_cuda_buffer_download": (cint, [vp, u32, sz, vp, sz]),

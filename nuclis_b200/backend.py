@@ -167,6 +167,17 @@ class Backend:
         self._check(self._lib.nu_cuda_set_generic_only(self._h, int(bool(on))))
         self._generic_only = bool(on)
 
+    @property
+    def chaining(self) -> bool:
+        """Back-to-back one-token matvecs run as one persistent kernel (off by default: measured slower than kernels of
+        their own; no counterpart in the reference)."""
+        return self._chaining if hasattr(self, "_chaining") else False
+
+    @chaining.setter
+    def chaining(self, on: bool) -> None:
+        self._check(self._lib.nu_cuda_set_chaining(self._h, int(bool(on))))
+        self._chaining = bool(on)
+
     # ---- buffers ----
     def create(self, len: int) -> Buffer:
         id = ctypes.c_uint32()

@@ -15,6 +15,7 @@
 namespace nu {
 
 struct FastJobBox { FastJob job; };
+struct FastChain { std::vector<FastJob> jobs; };
 
 namespace {
 
@@ -67,8 +68,8 @@ Backend *Backend::create(int device, std::string &error) {
     ok = ok && cudaStreamCreateWithFlags(&b->stream_, cudaStreamNonBlocking) == cudaSuccess;
     ok = ok && cudaEventCreate(&b->ev_start_) == cudaSuccess && cudaEventCreate(&b->ev_stop_) == cudaSuccess;
     ok = ok && cudaMalloc(&b->partials_, kPartialsFloats * sizeof(float)) == cudaSuccess;
-    ok = ok && cudaMalloc(&b->counters_, (kCounters + 1) * sizeof(uint32_t)) == cudaSuccess;
-    ok = ok && cudaMemset(b->counters_, 0, (kCounters + 1) * sizeof(uint32_t)) == cudaSuccess;
+    ok = ok && cudaMalloc(&b->counters_, (kCounters + 3) * sizeof(uint32_t)) == cudaSuccess;
+    ok = ok && cudaMemset(b->counters_, 0, (kCounters + 3) * sizeof(uint32_t)) == cudaSuccess;
     ok = ok && cudaMalloc(&b->argmax_records_, (128 * 4 + 4) * sizeof(float)) == cudaSuccess;
     ok = ok && cudaMemset(b->argmax_records_, 0, (128 * 4 + 4) * sizeof(float)) == cudaSuccess;
     if (!ok) {
@@ -96,6 +97,7 @@ Backend::~Backend() {
     for (auto &a : buffers_) if (a.ptr) cudaFree(a.ptr);
     for (auto &ev : profile_events_) cudaEventDestroy(ev);
     delete pending_job_;
+    delete chain_;
     if (inbox_) cudaFree(inbox_);
     if (partials_) cudaFree(partials_);
     if (counters_) cudaFree(counters_);
@@ -242,10 +244,41 @@ int Backend::begin() {
     return NU_OK;
 }
 
-int Backend::needRecording() {
+int Backend::needRecording(bool keep_chain) {
     if (!recording_) return fail(NU_ERR_NOT_RECORDING, "no recording is open (call begin first)");
     cudaSetDevice(device_);
+    if (!keep_chain)
+        if (int rc = flushChain()) return rc;  // every operator but another link ends a run of chained matvecs
     return flushPending();  // every operator but the allreduce that may fuse with it launches a held-back matvec first
+}
+
+// A one-token job on the specialized kernels: held as a link of the open chain if it can be one, else launched now.
+int Backend::chainOrLaunch(const FastJob &job) {
+    if (!chain_) chain_ = new FastChain;
+    if (chaining && !profiling_ && !peers_attached_ && chain_supported(job)) {
+        if (chain_->jobs.size() == (size_t)kChainMax)
+            if (int rc = flushChain()) return rc;
+        chain_->jobs.push_back(job);
+        return NU_OK;
+    }
+    if (int rc = flushChain()) return rc;
+    launches_ += launch_fast(stream_, job);
+    return NU_OK;
+}
+
+// Launches the held run: one job as its own kernel, two or more as one persistent kernel.
+int Backend::flushChain() {
+    if (!chain_ || chain_->jobs.empty()) return NU_OK;
+    std::vector<FastJob> &jobs = chain_->jobs;
+    int launched = 0;
+    if (jobs.size() >= 2) launched = launch_chain(stream_, jobs.data(), (uint32_t)jobs.size(), counters_ + counters_len_ + 1, sm_count_);
+    if (launched) {
+        launches_ += launched;
+    } else {
+        for (const FastJob &job : jobs) launches_ += launch_fast(stream_, job);
+    }
+    jobs.clear();
+    return cuda(cudaGetLastError(), "matvec chain: launch");
 }
 
 // Launches the matvec that was held back to see whether an allreduce of its output follows.
@@ -292,7 +325,7 @@ int Backend::checkKernelStatus() {
     if (int rc = cuda(cudaMemcpyAsync(&status, counters_ + counters_len_, sizeof status, cudaMemcpyDeviceToHost, stream_), "status read")) return rc;
     if (int rc = cuda(cudaStreamSynchronize(stream_), "status sync")) return rc;
     if (status != 0) {
-        cudaMemsetAsync(counters_, 0, (counters_len_ + 1) * sizeof(uint32_t), stream_);
+        cudaMemsetAsync(counters_, 0, (counters_len_ + 3) * sizeof(uint32_t), stream_);  // counters, status word, the chain kernel's two arrival counts
         cudaStreamSynchronize(stream_);
         return fail(NU_ERR_EXECUTION, status == 2 ? "allreduce over peer memory: a rank never arrived (bounded wait ran out); the path stays closed" : "a kernel gave up a bounded wait (copy never completed)");
     }
@@ -315,6 +348,7 @@ int Backend::runGraph(cudaGraphExec_t exec, uint32_t count, float *elapsed_ms) {
 int Backend::commit() {
     if (!recording_) return fail(NU_ERR_NOT_RECORDING, "commit: no recording is open");
     cudaSetDevice(device_);
+    if (int rc = flushChain()) return rc;
     if (int rc = flushPending()) return rc;
     if (profiling_) {
         recording_ = false;
@@ -340,6 +374,7 @@ int Backend::commitRetain(uint32_t *graph) {
     if (!recording_) return fail(NU_ERR_NOT_RECORDING, "commit_retain: no recording is open");
     if (profiling_) return fail(NU_ERR_INVALID_SHAPE, "commit_retain: not available while profiling");
     cudaSetDevice(device_);
+    if (int rc = flushChain()) return rc;
     if (int rc = flushPending()) return rc;
     cudaGraphExec_t exec = nullptr;
     if (int rc = finishCapture(&exec)) return rc;
@@ -370,6 +405,7 @@ int Backend::discard() {
     cudaSetDevice(device_);
     recording_ = false;
     pending_ = false;
+    if (chain_) chain_->jobs.clear();
     if (profiling_) {
         // Profiling runs operators as they are recorded; there is nothing left to drop.
         cudaStreamSynchronize(stream_);
@@ -431,7 +467,7 @@ int Backend::matvec(const Buffer &weights, const Matrix &m, const Buffer &input,
     const float *in = (const float *)resolve(input, m.columns * 4);
     float *out = (float *)resolve(output, m.rows * 4);
     if (!w || !in || !out || input.offset % 4 != 0 || output.offset % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "matvec: buffer too short");
-    if (int rc = needRecording()) return rc;
+    if (int rc = needRecording(true)) return rc;
     FastJob job{};
     job.enc = m.encoding; job.layout = m.layout; job.columns = (uint32_t)m.columns; job.tokens = 1; job.in = in; job.in_stride = m.columns;
     job.count = 1; job.mode = ACT_NONE;
@@ -447,8 +483,9 @@ int Backend::matvec(const Buffer &weights, const Matrix &m, const Buffer &input,
             wrote(output);
             return NU_OK;
         }
-        launches_ += launch_fast(stream_, job);
+        if (int rc = chainOrLaunch(job)) return rc;
     } else {
+        if (int rc = flushChain()) return rc;
         launches_ += launch_matmul_generic(stream_, m.encoding, m.layout, w, stride, (uint32_t)m.rows, (uint32_t)m.columns, in, false, m.columns, out, m.rows, 1);
     }
     wrote(output);
@@ -606,8 +643,8 @@ int Backend::matvecSegments(const Segment *segments, size_t count, const Buffer 
     // specialized kernel does not serve, is declined before anything is
     // recorded and the caller runs the segments alone (ops/matvec.zig:245-257).
     if (generic_only || !same_encoding || !fast_supported(job)) return fail(NU_ERR_MERGE_DECLINED, "segments: merge declined");
-    if (int rc = needRecording()) return rc;
-    launches_ += launch_fast(stream_, job);
+    if (int rc = needRecording(true)) return rc;
+    if (int rc = chainOrLaunch(job)) return rc;
     for (size_t i = 0; i < count; ++i) wrote(segments[i].output);
     opBoundary();
     return cuda(cudaGetLastError(), "segments: launch");
@@ -1081,6 +1118,7 @@ const char *nu_cuda_status_name(int status) {
 #define NU_P(p) if (!(p)) return NU_ERR_INVALID_SHAPE
 
 int nu_cuda_set_generic_only(nu_cuda *h, int on) { NU_H(h); h->b->generic_only = on != 0; return NU_OK; }
+int nu_cuda_set_chaining(nu_cuda *h, int on) { NU_H(h); h->b->chaining = on != 0; return NU_OK; }
 int nu_cuda_buffer_create(nu_cuda *h, size_t len, uint32_t *id) { NU_H(h); return h->b->createBuffer(len, id); }
 int nu_cuda_buffer_upload(nu_cuda *h, uint32_t id, size_t offset, const void *src, size_t len) { NU_H(h); return h->b->upload(id, offset, src, len); }
 int nu_cuda_buffer_download(nu_cuda *h, uint32_t id, size_t offset, void *dst, size_t len) { NU_H(h); return h->b->download(id, offset, dst, len); }

@@ -22,6 +22,8 @@ namespace nu {
 
 struct FastJob;
 struct FastJobBox;
+struct FastChain;
+struct FastJob;
 
 using Buffer = nu_buffer;
 using Matrix = nu_matrix;
@@ -35,6 +37,8 @@ public:
 
     // ---- knobs (root.zig:99-114) ----
     bool generic_only = false;
+    bool chaining = false;  // back-to-back one-token matvecs become one persistent launch (gemv_chain.cu); measured slower than
+                            // kernels of their own with programmatic dependent launch, so off unless asked for
 
     // ---- buffers ----
     int createBuffer(size_t len, uint32_t *id);
@@ -109,7 +113,7 @@ private:
     // Device address of a view after checking that `need` bytes fit in it and in its buffer.
     uint8_t *resolve(const Buffer &b, size_t need);
     static bool overlaps(const Buffer &a, size_t a_len, const Buffer &b, size_t b_len);
-    int needRecording();
+    int needRecording(bool keep_chain = false);
     void opBoundary();
     void wrote(const Buffer &b);
     bool written(const Buffer &b) const;
@@ -157,6 +161,11 @@ private:
     FastJobBox *pending_job_ = nullptr;
     Buffer pending_out_{};
     int peer_ranks_ = 0, peer_rank_ = 0;
+    // one-token integer-path matvecs recorded back to back, held until another operator (or the commit) ends the
+    // run: two or more of them become one persistent launch (gemv_chain.cu)
+    FastChain *chain_ = nullptr;
+    int flushChain();
+    int chainOrLaunch(const FastJob &job);
     unsigned long long peer_wait_ns_ = 2000000000ull;
 };
 

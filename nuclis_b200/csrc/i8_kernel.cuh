@@ -159,53 +159,91 @@ __device__ __forceinline__ void write_unit(const Params &p, uint32_t unit, uint3
 }
 
 
-// Shared memory: [stages][digit rows][group-sum rows][128 zero bytes][1/scale per (superblock, token)][part sums][barriers]
+// Shared memory: [barriers, 1 KB][stages][digit rows][group-sum rows][128 zero bytes][1/scale per (superblock, token)][part sums]
+// The barriers sit at a fixed place, a fixed distance apart per unit slot, so that the operators of a chain
+// (gemv_chain.cu), whose geometries differ, find the barriers the operator before them left.
+constexpr int kMaxStages = 5;
+constexpr int kBarBytes = 3584;               // 8 unit slots x (kMaxStages full + kMaxStages empty) x 8 bytes = 640, then room for two
+                                              // copies of an operator's Params (a chain keeps the current and the next one there)
+constexpr int kParamsAt = 768;                // the first copy; the second follows it
+static_assert(kParamsAt + 2 * sizeof(Params) <= kBarBytes && sizeof(Params) % 16 == 0, "the head of shared memory holds two Params");
+constexpr int kSlotBarBytes = 2 * kMaxStages * 8;
 template <class E, class G, int NT>
 static size_t smem_bytes(uint32_t ksl, bool pair, int stages) {
     const size_t plane_pitch = (size_t)ksl * 256 + E::PLANE_SKEW;
     const size_t gs_pitch = (size_t)ksl * E::GS_BYTES + (16 + 128 - ((size_t)ksl * E::GS_BYTES) % 128) % 128;
     const size_t parts = (size_t)G::SLOTS * 2 * (G::PARTS - 1) * (pair ? 2 : 1) * record_lanes<NT>() * 16;
-    return (size_t)G::SLOTS * stages * E::STAGE_BYTES + plane_columns<NT>() * plane_pitch + gs_columns<NT>() * gs_pitch + 128 + (size_t)ksl * 8 * 4 + parts +
-           G::SLOTS * stages * 16 + 256;
+    return kBarBytes + (size_t)G::SLOTS * stages * E::STAGE_BYTES + plane_columns<NT>() * plane_pitch + gs_columns<NT>() * gs_pitch + 128 + (size_t)ksl * 8 * 4 + parts + 256;
 }
 
-template <class E, class G, int NT, int STAGES>
-__global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant__ Params p) {
+// How an operator of a chain follows the one before it in the same launch. A kernel of its own has target 0.
+struct ChainLink {
+    uint32_t *arrivals;    // blocks that have finished an operator of the chain, counted over the whole launch
+    uint32_t target;       // the count at which every block has finished the operator before this one
+    uint32_t prev_slots;   // unit slots and stages of the operator before: its barriers are invalidated before this one's are made
+    uint32_t prev_stages;
+};
+constexpr uint32_t CHAIN_SPIN_LIMIT = 1u << 20;
+
+__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void mbar_inval(uint32_t bar) { asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar) : "memory"); }
+
+// One operator: 16-row units of the matrices of p against the staged activation rows. Every thread of the
+// first G::THREADS of the block calls it; STAGES is the depth of a slot's ring.
+// p: the operator's parameters where they are cheapest to read (the kernel's own parameter, or a copy in shared memory);
+// pm: where its tensor maps may be handed to the copy engine (the kernel's parameter space).
+template <class E, class G, int NT>
+__device__ __forceinline__ void run_op(const Params &p, const Params &pm, const int STAGES, uint8_t *smem, const ChainLink link) {
     constexpr bool WIDE = NT == 8;
     constexpr int STAGE_BYTES = E::STAGE_BYTES;  // 16 weight rows x PARTS superblocks (one TMA box, one task per warp of the slot),
                                                  // then whatever second plane the encoding's records need
     constexpr int WARPS = G::WARPS, SLOTS = G::SLOTS, PARTS = G::PARTS;
     static_assert(PARTS == E::STAGE_SBS, "a stage holds one superblock per K part");
     constexpr int REC = record_lanes<NT>();
-    extern __shared__ __align__(128) uint8_t smem[];
     const bool pair = p.mode != ACT_NONE;
-    uint8_t *stages = smem;
+    uint8_t *stages = smem + kBarBytes;
     uint8_t *planes = stages + SLOTS * STAGES * STAGE_BYTES;
     uint8_t *gs = planes + plane_columns<NT>() * p.plane_pitch;
     uint8_t *zero = gs + gs_columns<NT>() * p.gs_pitch;        // 128 bytes of zeros (group sums of the B columns no token uses)
     zero += (128u - (uint32_t)(zero - smem) % 128u) % 128u;
     float *inv = (float *)(zero + 128);                        // [superblock of the slice][8 tokens]: 1 / the activation scale
     float4 *parts = (float4 *)(((uintptr_t)(inv + p.ksl * 8) + 15) & ~(uintptr_t)15);
-    uint64_t *bars = (uint64_t *)(parts + SLOTS * 2 * (PARTS - 1) * (pair ? 2 : 1) * REC);
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t g = lane >> 2, t = lane & 3;
     const uint32_t slot = warp / PARTS, part = warp % PARTS;
     // A slot's warps share one ring of stages. full[i]: the copy into stage i has landed (all of them wait on it);
     // empty[i]: all of them have read stage i (the slot's first warp waits on it before it refills the stage).
     const uint8_t *my_stage = stages + slot * STAGES * STAGE_BYTES;
-    const uint32_t stage0 = smem_u32(my_stage), full0 = smem_u32(bars + slot * 2 * STAGES), empty0 = full0 + STAGES * 8;
+    const uint32_t stage0 = smem_u32(my_stage), full0 = smem_u32(smem) + slot * kSlotBarBytes, empty0 = full0 + kMaxStages * 8;
 
     // Programmatic dependent launch: the next kernel of the stream may take an SM as soon as this
     // block leaves it, and this kernel starts its weight stream (weights are constant) while the
     // previous kernel is still finishing elsewhere. Everything that reads the previous kernel's
-    // output or writes global memory comes after the griddepcontrol.wait below.
-    asm volatile("griddepcontrol.launch_dependents;");
+    // output or writes global memory comes after the griddepcontrol.wait below. In a chain the
+    // same holds between operators: the weight stream of this one starts while other blocks are
+    // still in the one before, and the wait is for the chain's arrival count.
+    if (!link.target) asm volatile("griddepcontrol.launch_dependents;");
     if (part == 0 && lane == 0) {
+        if (link.target) {
+            // the barriers the operator before left (this slot's; the last slot also takes those of slots this operator has not)
+            const uint32_t upto = slot == SLOTS - 1 ? max((uint32_t)SLOTS, link.prev_slots) : slot + 1;
+            for (uint32_t s2 = slot; s2 < upto && s2 < link.prev_slots; ++s2)
+                for (uint32_t i = 0; i < link.prev_stages; ++i) {
+                    mbar_inval(smem_u32(smem) + s2 * kSlotBarBytes + i * 8);
+                    mbar_inval(smem_u32(smem) + s2 * kSlotBarBytes + (kMaxStages + i) * 8);
+                }
+        }
         for (int i = 0; i < STAGES; ++i) {
             mbar_init(full0 + i * 8, 1);
             mbar_init(empty0 + i * 8, PARTS);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // shared memory the operator before wrote through the generic proxy is about to be written by copies
+        if (link.target) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
 
     // ---- this block's slice and units ----
@@ -236,7 +274,7 @@ __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant
     auto issue = [&]() {
         if (lane == 0 && !stuck) {
             if (issued >= (uint32_t)STAGES && !mbar_wait(empty0 + p_stage * 8, p_phase ^ 1u)) stuck = true;
-            else E::issue(p, p_seg, sb0 + PARTS * p_j, p_row0, stage0 + p_stage * STAGE_BYTES, full0 + p_stage * 8, policy);
+            else E::issue(pm, p_seg, sb0 + PARTS * p_j, p_row0, stage0 + p_stage * STAGE_BYTES, full0 + p_stage * 8, policy);
         }
         ++issued;
         if (++p_stage == STAGES) { p_stage = 0; p_phase ^= 1u; }
@@ -255,7 +293,20 @@ __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant
             if (issued < total) issue();
     }
     if (tid < 32) ((uint32_t *)zero)[tid] = 0;
-    asm volatile("griddepcontrol.wait;" ::: "memory");  // the previous kernel has ended; its writes are visible
+    if (link.target) {
+        // every block has finished the operator before (bounded: a block that never arrives raises the status word)
+        if (tid == 0) {
+            bool there = false;
+            for (uint32_t i = 0; i < CHAIN_SPIN_LIMIT && !there; ++i) {
+                there = ld_acquire_u32(link.arrivals) >= link.target;
+                if (!there) __nanosleep(64);
+            }
+            if (!there) atomicExch(p.status, 1u);
+        }
+        named_barrier(15, G::THREADS);
+    } else {
+        asm volatile("griddepcontrol.wait;" ::: "memory");  // the previous kernel has ended; its writes are visible
+    }
 
     // ---- stage the slice's activations: a warp takes one (superblock, token) pair at a time ----
     // A pass keeps up to SBW pairs of a warp in registers between the loads and the conversion.
@@ -268,8 +319,8 @@ __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant
             if (q < pairs) {
                 const uint32_t sb = q / p.tokens, tok = q - sb * p.tokens;
                 const float4 *src = (const float4 *)(p.in + (size_t)tok * p.in_stride) + (size_t)(sb0 + sb) * 64;
-                xa[j] = src[lane];
-                xb2[j] = src[32 + lane];
+                xa[j] = __ldcg(src + lane);  // L2: in a chain another block wrote them during this launch
+                xb2[j] = __ldcg(src + 32 + lane);
             }
         }
 #pragma unroll
@@ -325,7 +376,7 @@ __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant
             }
         }
     }
-    __syncthreads();  // the staged rows, the zero block and the slots' barriers are visible to every warp
+    named_barrier(15, G::THREADS);  // the staged rows, the zero block and the slots' barriers are visible to every warp
 
     // ---- the task loop ----
     // This lane's B column n = g. Narrow: column = plane * 2 + token, columns 6 and 7 and the columns of a
@@ -478,8 +529,14 @@ __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant
     }
 }
 
+// The operator as a kernel of its own.
+template <class E, class G, int NT, int STAGES>
+__global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant__ Params p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    run_op<E, G, NT>(p, p, STAGES, smem, ChainLink{nullptr, 0u, 0u, 0u});
+}
+
 constexpr size_t kSmemMax = 227 * 1024;
-constexpr int kMaxStages = 5;
 
 struct Plan {
     int nt;       // the kernel instance: 1, 2 or 8 token columns
@@ -615,6 +672,10 @@ static int launch_geometry(cudaStream_t s, const FastJob &job, const Params &p, 
 }
 
 }  // namespace i8
+
+// The parameters and launch plan of a job on the integer path (maps: also encode the tensor maps); false: not served.
+bool q4k_i8_fill(const FastJob &job, i8::Params &p, i8::Plan &plan, bool maps);
+bool q6k_i8_fill(const FastJob &job, i8::Params &p, i8::Plan &plan, bool maps);
 
 bool encode_tiled_map(CUtensorMap *map, CUtensorMapDataType type, uint32_t elem_bytes, const void *base, uint64_t inner, uint64_t outer,
                       uint64_t stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle);
