@@ -35,6 +35,8 @@ using dec::tma_load_2d;
 constexpr int MAX_SLICES = 32;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 constexpr int SBW = 4;  // (token, superblock) pairs a warp stages per pass: a pass keeps them in registers
+constexpr int SHARE_FROM_SLOTS = 5;  // geometries with at least this many unit slots share the units of a block's last round (see run_op);
+                                     // measured: with six slots (Q6_K) 17408x5120 goes from 19.8 to 17.4 us, with four (Q4_K) the extra code costs 3 %
 
 template <int W, int P>
 struct Geometry {
@@ -159,7 +161,7 @@ __device__ __forceinline__ void write_unit(const Params &p, uint32_t unit, uint3
 }
 
 
-// Shared memory: [barriers, 1 KB][stages][digit rows][group-sum rows][128 zero bytes][1/scale per (superblock, token)][part sums]
+// Shared memory: [barriers and parameter copies][stages][digit rows][group-sum rows][128 zero bytes][1/scale per (superblock, token)][part sums][slot sums]
 // The barriers sit at a fixed place, a fixed distance apart per unit slot, so that the operators of a chain
 // (gemv_chain.cu), whose geometries differ, find the barriers the operator before them left.
 constexpr int kMaxStages = 5;
@@ -172,7 +174,7 @@ template <class E, class G, int NT>
 static size_t smem_bytes(uint32_t ksl, bool pair, int stages) {
     const size_t plane_pitch = (size_t)ksl * 256 + E::PLANE_SKEW;
     const size_t gs_pitch = (size_t)ksl * E::GS_BYTES + (16 + 128 - ((size_t)ksl * E::GS_BYTES) % 128) % 128;
-    const size_t parts = (size_t)G::SLOTS * 2 * (G::PARTS - 1) * (pair ? 2 : 1) * record_lanes<NT>() * 16;
+    const size_t parts = (size_t)G::SLOTS * (2 * (G::PARTS - 1) + 1) * (pair ? 2 : 1) * record_lanes<NT>() * 16;  // part sums (two sets) and slot sums
     return kBarBytes + (size_t)G::SLOTS * stages * E::STAGE_BYTES + plane_columns<NT>() * plane_pitch + gs_columns<NT>() * gs_pitch + 128 + (size_t)ksl * 8 * 4 + parts + 256;
 }
 
@@ -212,6 +214,7 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
     zero += (128u - (uint32_t)(zero - smem) % 128u) % 128u;
     float *inv = (float *)(zero + 128);                        // [superblock of the slice][8 tokens]: 1 / the activation scale
     float4 *parts = (float4 *)(((uintptr_t)(inv + p.ksl * 8) + 15) & ~(uintptr_t)15);
+    float4 *coopbuf = parts + SLOTS * 2 * (PARTS - 1) * (pair ? 2 : 1) * REC;  // sums of the slots that share a unit
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t g = lane >> 2, t = lane & 3;
     const uint32_t slot = warp / PARTS, part = warp % PARTS;
@@ -258,13 +261,24 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
     const uint32_t u_hi = u_lo + per_blk + (jblk < extra ? 1u : 0u);
     const uint32_t np = min((uint32_t)PARTS, n);   // warps of a slot that have superblocks in this slice
     const uint32_t m = (n + PARTS - 1) / PARTS;    // stages per unit (pair mode: per matrix of the unit)
-    const uint32_t first_unit = u_lo + slot;
-    const uint32_t my_units = first_unit < u_hi ? (u_hi - first_unit + SLOTS - 1) / SLOTS : 0;
-    const uint32_t total = my_units * m * (pair ? 2u : 1u);  // stages the slot streams
+    // The block's units go to its slots in rounds of SLOTS. When the last round has units for at most half of the
+    // slots, `coop` slots share each of its units: slot i of a group streams the i-th part of the unit's stages, and
+    // the groups' first slots add the others' sums (in slot order) from shared memory. Otherwise a small matrix would
+    // leave most slots of every block idle for a whole unit.
+    const uint32_t nunits = u_hi - u_lo, full = nunits / SLOTS, rem = nunits - full * SLOTS;
+    const uint32_t coop = (SLOTS >= SHARE_FROM_SLOTS && rem && 2 * rem <= (uint32_t)SLOTS) ? min((uint32_t)SLOTS / rem, m) : 1u;
+    const bool in_last = slot < rem * coop;
+    const uint32_t ci = slot % coop, group = slot / coop;           // place in the group; the group's unit of the last round
+    const uint32_t last_unit = u_lo + full * SLOTS + group;
+    const uint32_t jb = in_last ? ci * m / coop : 0u, je = in_last ? (ci + 1) * m / coop : 0u;  // its stages of that unit
+    const uint32_t my_items = full + (in_last ? 1u : 0u);           // units (or shares of one) this slot works on
+    const uint32_t my_units = full + (in_last && ci == 0 ? 1u : 0u);  // units whose sums this slot finishes and writes
+    const uint32_t total = (full * m + (je - jb)) * (pair ? 2u : 1u);  // stages the slot streams
+    auto item_unit = [&](uint32_t i) { return i < full ? u_lo + i * SLOTS + slot : last_unit; };
 
     // ---- the weight stream: the slot's stages in order (pair mode: gate then up of each group of superblocks). Only
     // the slot's first warp keeps this state; it refills a stage once all warps of the slot have left it.
-    uint32_t issued = 0, p_stage = 0, p_phase = 0, p_unit = first_unit, p_j = 0, p_seg = 0, p_row0 = 0;
+    uint32_t issued = 0, p_stage = 0, p_phase = 0, p_item = 0, p_unit = item_unit(0), p_j = full ? 0u : jb, p_seg = 0, p_row0 = 0;
     bool stuck = false;
     const uint64_t policy = evict_first_policy();
     if (total) {
@@ -280,9 +294,10 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
         if (++p_stage == STAGES) { p_stage = 0; p_phase ^= 1u; }
         if (pair && p_seg == 0) { p_seg = 1; return; }
         if (pair) p_seg = 0;
-        if (++p_j == m) {
-            p_j = 0;
-            p_unit += SLOTS;
+        if (++p_j == (p_item < full ? m : je)) {
+            ++p_item;
+            p_j = p_item < full ? 0u : jb;
+            p_unit = item_unit(p_item);
             if (pair) p_row0 = p_unit * 16;
             else if (issued < total) unit_rows(p, p_unit, p_seg, p_row0);
         }
@@ -405,12 +420,13 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
     const float *ivlane = inv + (WIDE ? 2 * t : 0);  // 1 / scale of the lane's token(s), per superblock
     uint32_t c_stage = 0, c_phase = 0, consumed = 0;
     bool failed = false;
-    uint32_t uidx = 0;
-    for (uint32_t unit = first_unit; unit < u_hi; unit += SLOTS, ++uidx) {
+    for (uint32_t uidx = 0; uidx < my_items; ++uidx) {
+        const uint32_t unit = item_unit(uidx);
+        const bool shared_unit = SLOTS >= SHARE_FROM_SLOTS && uidx == full && coop > 1;  // this slot streams a share of the unit's stages
         float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
         // After a wait has run out the warp stops computing but still walks its units, so that the
         // warps it shares them with are not left at the barrier below.
-        for (uint32_t j = 0; j < m && !failed; ++j) {
+        for (uint32_t j = uidx < full ? 0u : jb; j < (uidx < full ? m : je) && !failed; ++j) {
             const uint32_t sbw = part + PARTS * j;  // superblock within the slice: this warp's task of the stage
             const bool live = sbw < n;              // the last stage of a row may reach past the slice
             if (part == 0 && issued < total) issue();  // keep STAGES - 1 stages in flight
@@ -456,16 +472,38 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
             if (pair) dst[REC + rec] = make_float4(acc2[0], acc2[1], acc2[2], acc2[3]);
         }
         if (np > 1) named_barrier(1 + slot, 32 * np);
-        if (part != 0 || !holds) continue;
-        for (uint32_t k = 1; k < np; ++k) {
-            const float4 *src = buf + (size_t)(k - 1) * (pair ? 2 : 1) * REC;
-            const float4 v = src[rec];
-            acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
-            if (pair) {
-                const float4 w = src[REC + rec];
-                acc2[0] += w.x; acc2[1] += w.y; acc2[2] += w.z; acc2[3] += w.w;
+        if (part != 0) continue;
+        if (holds)
+            for (uint32_t k = 1; k < np; ++k) {
+                const float4 *src = buf + (size_t)(k - 1) * (pair ? 2 : 1) * REC;
+                const float4 v = src[rec];
+                acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+                if (pair) {
+                    const float4 w = src[REC + rec];
+                    acc2[0] += w.x; acc2[1] += w.y; acc2[2] += w.z; acc2[3] += w.w;
+                }
             }
+        if (shared_unit) {
+            // ---- the slots that shared the unit meet (their first warps); the group's first slot adds them in slot order ----
+            float4 *mine = coopbuf + (size_t)slot * (pair ? 2 : 1) * REC;
+            if (ci > 0 && holds) {
+                mine[rec] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                if (pair) mine[REC + rec] = make_float4(acc2[0], acc2[1], acc2[2], acc2[3]);
+            }
+            named_barrier(9 + group, 32 * coop);
+            if (ci > 0) continue;
+            if (holds)
+                for (uint32_t k = 1; k < coop; ++k) {
+                    const float4 *src = mine + (size_t)k * (pair ? 2 : 1) * REC;
+                    const float4 v = src[rec];
+                    acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+                    if (pair) {
+                        const float4 w = src[REC + rec];
+                        acc2[0] += w.x; acc2[1] += w.y; acc2[2] += w.z; acc2[3] += w.w;
+                    }
+                }
         }
+        if (!holds) continue;
         if (p.nks > 1) {
             // several slices: leave the partial sums; they are published after the loop with one fence
             float4 *dst = (float4 *)p.partials + ((size_t)ks * p.units + unit) * (pair ? 2 : 1) * REC;
@@ -485,13 +523,13 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
         for (uint32_t base = 0; base < my_units; base += 32) {
             const uint32_t mine_u = base + lane;
             uint32_t last = 0;
-            if (mine_u < my_units) last = atomicAdd(p.counters + first_unit + mine_u * SLOTS, 1u) == p.nks - 1;
+            if (mine_u < my_units) last = atomicAdd(p.counters + item_unit(mine_u), 1u) == p.nks - 1;
             uint32_t mask = __ballot_sync(0xffffffffu, last != 0);
             if (mask) __threadfence();
             while (mask) {
                 const uint32_t u = base + (uint32_t)__ffs((int)mask) - 1;
                 mask &= mask - 1;
-                const uint32_t unit = first_unit + u * SLOTS;
+                const uint32_t unit = item_unit(u);
                 if (holds) {
                     const size_t per = (size_t)(pair ? 2 : 1) * REC;
                     const float4 *src = (const float4 *)p.partials + (size_t)unit * per + rec;
@@ -598,10 +636,21 @@ static bool fill_geometry(const FastJob &job, Params &p, Plan &plan) {
         if (nks > 1 && ((size_t)nks * units * rec_floats > job.partials_floats || units > job.counters_len)) continue;
         const int st = pick_stages<E, G, NT>(ksl, pair);
         if (st < 2) continue;
+        // stage steps of a block with `ub` units of `st` stages each: whole rounds of SLOTS units, then a last round whose
+        // units are shared by several slots each when there are few of them (the kernel's `coop`)
+        auto steps = [&](uint32_t ub, uint32_t st) {
+            const uint32_t whole = ub / SLOTS, rest = ub % SLOTS;
+            double c = whole * (st * per_sb + 0.35);
+            if (rest) {
+                const uint32_t share = SLOTS >= SHARE_FROM_SLOTS && 2 * rest <= (uint32_t)SLOTS ? ((uint32_t)SLOTS / rest < st ? (uint32_t)SLOTS / rest : st) : 1u;
+                c += (double)((st + share - 1) / share) * per_sb + 0.35 + (share > 1 ? 0.3 : 0.0);
+            }
+            return c;
+        };
         auto cost = [&](uint32_t s, uint32_t b) {
-            const uint32_t n = s + 1 == nks ? p.ksb - s * ksl : ksl;
-            const uint32_t units_blk = (units + b - 1) / b;
-            return (double)((units_blk + SLOTS - 1) / SLOTS) * ((double)((n + PARTS - 1) / PARTS) * per_sb + 0.35);
+            const uint32_t n = s + 1 == nks ? p.ksb - s * ksl : ksl, st = (n + PARTS - 1) / PARTS;
+            const double hi = steps((units + b - 1) / b, st), lo = steps(units / b, st);  // blocks take one or the other
+            return hi > lo ? hi : lo;
         };
         for (uint32_t s = 0; s < nks; ++s) blocks[s] = 1;
         for (uint32_t left = sms - nks; left > 0; --left) {
