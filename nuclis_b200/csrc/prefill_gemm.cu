@@ -54,6 +54,9 @@ struct Params {
     const uint32_t *tiles;
     const uint32_t *slot_rows;
     unsigned long long expert_bytes;
+    // Plain form with many token tiles: the grid is one-dimensional and walks `group` token tiles at a time through all
+    // row tiles before it moves to the next group, so that the group's activations stay in L2 (0: the two-dimensional grid).
+    uint32_t group, tok_tiles, row_tiles;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -164,8 +167,15 @@ __global__ void __launch_bounds__(THREADS, BPS) prefill_kernel(const __grid_cons
     volatile uint32_t *abort_flag = tmem_slot + 1;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // token tiles vary fastest over the grid: the blocks running together share a few row tiles of weights (L2) 
-    const uint32_t row0 = blockIdx.y * BM;
-    uint32_t tok0 = blockIdx.x * BN, tile_rows = 0, list_first = 0;
+    uint32_t bx = blockIdx.x, by = blockIdx.y;
+    if (p.group) {
+        const uint32_t per = p.group * p.row_tiles, grp = blockIdx.x / per, in = blockIdx.x - grp * per;
+        const uint32_t gsize = min(p.group, p.tok_tiles - grp * p.group);  // the last group may be short
+        by = in / gsize;
+        bx = grp * p.group + (in - by * gsize);
+    }
+    const uint32_t row0 = by * BM;
+    uint32_t tok0 = bx * BN, tile_rows = 0, list_first = 0;
     const uint8_t *wbase = p.w;
     if (p.tiles) {
         if (blockIdx.x >= p.tiles[0]) return;  // the grid is sized for the most tiles a routing can give; the whole block leaves
@@ -508,6 +518,17 @@ int launch_prefill(cudaStream_t s, const PrefillJob &j) {
     p.rows = j.rows; p.columns = j.columns; p.tokens = j.tokens;
     p.out = j.out; p.out_stride = j.out_stride; p.status = j.status;
     dim3 grid((j.tokens + bn - 1) / bn, (j.rows + prefill::BM - 1) / prefill::BM);
+    // Token tiles vary fastest over the grid, so the blocks running together share a few row tiles of weights. When the
+    // activations of all token tiles no longer fit in L2 beside them (16,384 rows of 5,120 columns are 168 MB), every row
+    // tile would stream them from HBM again: walk them in groups of about 48 MB instead.
+    const size_t tile_bytes = (size_t)bn * j.columns * 2;
+    if ((size_t)grid.x * tile_bytes > (size_t)(64u << 20) && (size_t)grid.x * grid.y < 0x7fffffffull) {
+        p.group = (uint32_t)((size_t)(48u << 20) / tile_bytes);
+        if (p.group < 1) p.group = 1;
+        p.tok_tiles = grid.x;
+        p.row_tiles = grid.y;
+        grid = dim3(grid.x * grid.y, 1);
+    }
     const int mode = !p.fast ? 0 : j.enc == Q4_K ? 1 : j.layout == 1 ? 2 : 3;
     // Two blocks per SM (two stages each) when there are more blocks than SMs and the decoder is light enough for the
     // smaller register budget (measured: Q4_K 933 -> 1,067 TFLOP/s; planar Q6_K loses a little).
