@@ -51,7 +51,7 @@ static_assert(sizeof(ChainParams) <= 32764, "kernel parameters are at most 32,76
 // parameter space never changes and would read it again after every wait); pm: the parameter space, for the tensor maps.
 template <class E, class G, int STAGES>
 __device__ __noinline__ void run_link(const Params *p, const Params *pm, uint8_t *smem, ChainLink link) {
-    run_op<E, G, 1>(*p, *pm, STAGES, smem, link);
+    run_op<E, G, 1, (G::SLOTS >= 5)>(*p, *pm, STAGES, smem, link);  // shared units where a block has many slots (the plan may assume either)
 }
 template <class E, class G>
 __device__ __forceinline__ void run_stages(const Params *p, const Params *pm, uint32_t stages, uint8_t *smem, const ChainLink &link) {

@@ -35,8 +35,6 @@ using dec::tma_load_2d;
 constexpr int MAX_SLICES = 32;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 constexpr int SBW = 4;  // (token, superblock) pairs a warp stages per pass: a pass keeps them in registers
-constexpr int SHARE_FROM_SLOTS = 5;  // geometries with at least this many unit slots share the units of a block's last round (see run_op);
-                                     // measured: with six slots (Q6_K) 17408x5120 goes from 19.8 to 17.4 us, with four (Q4_K) the extra code costs 3 %
 
 template <int W, int P>
 struct Geometry {
@@ -198,7 +196,9 @@ __device__ __forceinline__ void mbar_inval(uint32_t bar) { asm volatile("mbarrie
 // first G::THREADS of the block calls it; STAGES is the depth of a slot's ring.
 // p: the operator's parameters where they are cheapest to read (the kernel's own parameter, or a copy in shared memory);
 // pm: where its tensor maps may be handed to the copy engine (the kernel's parameter space).
-template <class E, class G, int NT>
+// SHARE: the instance whose slots share the units of a block's last round (below); the host picks it per geometry
+// (fill_geometry).
+template <class E, class G, int NT, bool SHARE>
 __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const int STAGES, uint8_t *smem, const ChainLink link) {
     constexpr bool WIDE = NT == 8;
     constexpr int STAGE_BYTES = E::STAGE_BYTES;  // 16 weight rows x PARTS superblocks (one TMA box, one task per warp of the slot),
@@ -266,7 +266,7 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
     // the groups' first slots add the others' sums (in slot order) from shared memory. Otherwise a small matrix would
     // leave most slots of every block idle for a whole unit.
     const uint32_t nunits = u_hi - u_lo, full = nunits / SLOTS, rem = nunits - full * SLOTS;
-    const uint32_t coop = (SLOTS >= SHARE_FROM_SLOTS && rem && 2 * rem <= (uint32_t)SLOTS) ? min((uint32_t)SLOTS / rem, m) : 1u;
+    const uint32_t coop = (SHARE && rem && 2 * rem <= (uint32_t)SLOTS) ? min((uint32_t)SLOTS / rem, m) : 1u;
     const bool in_last = slot < rem * coop;
     const uint32_t ci = slot % coop, group = slot / coop;           // place in the group; the group's unit of the last round
     const uint32_t last_unit = u_lo + full * SLOTS + group;
@@ -422,7 +422,7 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
     bool failed = false;
     for (uint32_t uidx = 0; uidx < my_items; ++uidx) {
         const uint32_t unit = item_unit(uidx);
-        const bool shared_unit = SLOTS >= SHARE_FROM_SLOTS && uidx == full && coop > 1;  // this slot streams a share of the unit's stages
+        const bool shared_unit = SHARE && uidx == full && coop > 1;  // this slot streams a share of the unit's stages
         float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
         // After a wait has run out the warp stops computing but still walks its units, so that the
         // warps it shares them with are not left at the barrier below.
@@ -568,10 +568,10 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
 }
 
 // The operator as a kernel of its own.
-template <class E, class G, int NT, int STAGES>
+template <class E, class G, int NT, int STAGES, bool SHARE>
 __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant__ Params p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    run_op<E, G, NT>(p, p, STAGES, smem, ChainLink{nullptr, 0u, 0u, 0u});
+    run_op<E, G, NT, SHARE>(p, p, STAGES, smem, ChainLink{nullptr, 0u, 0u, 0u});
 }
 
 constexpr size_t kSmemMax = 227 * 1024;
@@ -579,6 +579,7 @@ constexpr size_t kSmemMax = 227 * 1024;
 struct Plan {
     int nt;       // the kernel instance: 1, 2 or 8 token columns
     int stages;
+    bool share;   // the instance whose slots share the units of a block's last round
     uint32_t grid;
     size_t smem;
 };
@@ -624,10 +625,16 @@ static bool fill_geometry(const FastJob &job, Params &p, Plan &plan) {
     const double per_sb = pair ? 2.0 : 1.0;  // stages per group of superblocks of a unit
     p.units = units;
     plan.nt = NT;
+    plan.share = false;
     const size_t rec_floats = (size_t)(pair ? 2 : 1) * record_lanes<NT>() * 4;  // partial sums a (slice, unit) leaves
     const uint32_t sms = (uint32_t)job.sm_count;
     double best = 1e30;
     uint32_t blocks[MAX_SLICES];
+    // Measured: with six slots a block (Q6_K) sharing takes 17408 x 5120 from 19.8 to 17.4 us and the 64-layer stack from 289
+    // to 297 tok/s; with four (Q4_K) it never shortened a launch (small matrices are bound by the launch, not by stage
+    // steps) and its extra code cost the large ones 3 %.
+    constexpr bool sharing = SLOTS >= 5;
+    plan.share = sharing;
     for (uint32_t ksl = 1; ksl <= p.ksb; ++ksl) {
         const uint32_t nks = (p.ksb + ksl - 1) / ksl;
         if (nks > MAX_SLICES || nks > sms) continue;
@@ -642,7 +649,7 @@ static bool fill_geometry(const FastJob &job, Params &p, Plan &plan) {
             const uint32_t whole = ub / SLOTS, rest = ub % SLOTS;
             double c = whole * (st * per_sb + 0.35);
             if (rest) {
-                const uint32_t share = SLOTS >= SHARE_FROM_SLOTS && 2 * rest <= (uint32_t)SLOTS ? ((uint32_t)SLOTS / rest < st ? (uint32_t)SLOTS / rest : st) : 1u;
+                const uint32_t share = sharing && 2 * rest <= (uint32_t)SLOTS ? ((uint32_t)SLOTS / rest < st ? (uint32_t)SLOTS / rest : st) : 1u;
                 c += (double)((st + share - 1) / share) * per_sb + 0.35 + (share > 1 ? 0.3 : 0.0);
             }
             return c;
@@ -691,7 +698,8 @@ static bool fill_geometry(const FastJob &job, Params &p, Plan &plan) {
 
 template <class E, class G, int NT, int STAGES>
 static bool configure_one() {
-    return cudaFuncSetAttribute(i8_kernel<E, G, NT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax) == cudaSuccess;
+    return cudaFuncSetAttribute(i8_kernel<E, G, NT, STAGES, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax) == cudaSuccess &&
+           cudaFuncSetAttribute(i8_kernel<E, G, NT, STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax) == cudaSuccess;
 }
 template <class E, class G, int NT>
 static bool configure_geometry() {
@@ -711,11 +719,20 @@ static int launch_geometry(cudaStream_t s, const FastJob &job, const Params &p, 
     cfg.stream = s;
     cfg.attrs = attr;
     cfg.numAttrs = job.serial ? 0 : 1;
-    switch (plan.stages) {
-    case 5: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, NT, 5>, p); break;
-    case 4: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, NT, 4>, p); break;
-    case 3: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, NT, 3>, p); break;
-    default: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, NT, 2>, p); break;
+    if (plan.share) {
+        switch (plan.stages) {
+        case 5: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, NT, 5, true>, p); break;
+        case 4: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, NT, 4, true>, p); break;
+        case 3: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, NT, 3, true>, p); break;
+        default: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, NT, 2, true>, p); break;
+        }
+    } else {
+        switch (plan.stages) {
+        case 5: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, NT, 5, false>, p); break;
+        case 4: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, NT, 4, false>, p); break;
+        case 3: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, NT, 3, false>, p); break;
+        default: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, NT, 2, false>, p); break;
+        }
     }
     return 1;
 }
