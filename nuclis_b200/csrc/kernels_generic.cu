@@ -159,27 +159,42 @@ int launch_matvec_experts_generic(cudaStream_t s, uint32_t enc, const uint8_t *w
 
 constexpr int EXPERT_TILE = 32;
 
-__global__ void expert_lists_kernel(const uint32_t *indices, uint32_t n, uint32_t experts, uint32_t bound, uint32_t *lists) {
-    __shared__ uint32_t counts[256], offsets[257];
-    const uint32_t tid = threadIdx.x;
+// One block of 32 warps; warp w owns the w-th contiguous part of the slot rows. Pass 1 counts each part's rows per expert
+// (shared-memory atomics); a prefix over the parts, expert by expert, turns the counts into the place where each part's
+// rows of an expert start; pass 2 walks the parts again, 32 rows at a time: the lanes that hold the same expert find one
+// another with a match, take consecutive places in lane order (= slot order) and their first lane moves the expert's
+// place on. The order within an expert is the slot order, and the work is one pass over the rows, not rows x experts.
+constexpr int LISTS_WARPS = 32;
+
+__global__ void __launch_bounds__(LISTS_WARPS * 32) expert_lists_kernel(const uint32_t *indices, uint32_t n, uint32_t experts, uint32_t bound, uint32_t *lists) {
+    __shared__ uint32_t place[LISTS_WARPS][256];  // pass 1: rows of expert e in part w; then: where they start in the list
+    __shared__ uint32_t offsets[257];
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     uint32_t *tiles = lists + experts + 3, *rows = tiles + 3 * (size_t)bound;
-    // one thread per expert walks the slot rows in order: counts first, stable placement after the prefix
-    uint32_t mine = 0;
+    for (uint32_t i = tid; i < LISTS_WARPS * 256; i += LISTS_WARPS * 32) (&place[0][0])[i] = 0;
+    __syncthreads();
+    const uint32_t per = ((n + LISTS_WARPS - 1) / LISTS_WARPS + 31u) & ~31u;  // whole groups of 32 rows
+    const uint32_t lo = min(warp * per, n), hi = min(lo + per, n);
+    for (uint32_t i = lo + lane; i < hi; i += 32) atomicAdd(&place[warp][min(__ldg(indices + i), experts - 1)], 1u);
+    __syncthreads();
+    // per expert: its rows in all parts; then the experts' exclusive prefix (one thread: at most 256 steps) and the tiles
+    uint32_t total = 0;
     if (tid < experts)
-        for (uint32_t i = 0; i < n; ++i) mine += min(indices[i], experts - 1) == tid;
-    counts[tid] = tid < experts ? mine : 0;
+        for (int w = 0; w < LISTS_WARPS; ++w) total += place[w][tid];
+    if (tid < 256) offsets[tid] = tid < experts ? total : 0;
     __syncthreads();
     if (tid == 0) {
         uint32_t at = 0, ntiles = 0;
-        for (uint32_t e = 0; e < experts; ++e) {
-            offsets[e] = at;
-            for (uint32_t first = 0; first < counts[e]; first += EXPERT_TILE) {
-                tiles[3 * ntiles] = e;
+        for (uint32_t x = 0; x < experts; ++x) {
+            const uint32_t c = offsets[x];
+            offsets[x] = at;
+            for (uint32_t first = 0; first < c; first += EXPERT_TILE) {
+                tiles[3 * ntiles] = x;
                 tiles[3 * ntiles + 1] = at + first;
-                tiles[3 * ntiles + 2] = min((uint32_t)EXPERT_TILE, counts[e] - first);
+                tiles[3 * ntiles + 2] = min((uint32_t)EXPERT_TILE, c - first);
                 ++ntiles;
             }
-            at += counts[e];
+            at += c;
         }
         offsets[experts] = at;
         lists[0] = ntiles;
@@ -189,13 +204,31 @@ __global__ void expert_lists_kernel(const uint32_t *indices, uint32_t n, uint32_
     if (tid <= experts) lists[2 + tid] = offsets[tid];
     if (tid < experts) {
         uint32_t at = offsets[tid];
-        for (uint32_t i = 0; i < n; ++i)
-            if (min(indices[i], experts - 1) == tid) rows[at++] = i;
+        for (int w = 0; w < LISTS_WARPS; ++w) {
+            const uint32_t c = place[w][tid];
+            place[w][tid] = at;
+            at += c;
+        }
+    }
+    __syncthreads();
+    for (uint32_t i0 = lo; i0 < hi; i0 += 32) {
+        const uint32_t i = i0 + lane;
+        const bool live = i < hi;
+        const uint32_t e = live ? min(__ldg(indices + i), experts - 1) : 0xffffffffu;
+        const uint32_t same = __match_any_sync(0xffffffffu, e);
+        if (live) {
+            const uint32_t before = __popc(same & ((1u << lane) - 1u));
+            const uint32_t at = place[warp][e];
+            rows[at + before] = i;
+        }
+        __syncwarp();
+        if (live && lane == (uint32_t)__ffs((int)same) - 1u) place[warp][e] += __popc(same);
+        __syncwarp();
     }
 }
 
 int launch_expert_lists(cudaStream_t s, const uint32_t *indices, uint32_t n, uint32_t experts, uint32_t bound, uint32_t *lists) {
-    expert_lists_kernel<<<1, 256, 0, s>>>(indices, n, experts, bound, lists);
+    expert_lists_kernel<<<1, LISTS_WARPS * 32, 0, s>>>(indices, n, experts, bound, lists);
     return 1;
 }
 

@@ -149,7 +149,8 @@ __device__ __forceinline__ void codes4_fma(uint32_t t4, float mul, float add, ui
 }
 __device__ __forceinline__ uint4 ldg16(const uint8_t *ptr) { return __ldg((const uint4 *)ptr); }
 
-// MODE: 0 the generic decoders (any encoding and layout), 1 Q4_K with 16-byte aligned rows, 2 planar Q6_K, 3 planar Q8_0.
+// MODE: 0 the generic decoders (any encoding and layout), 1 Q4_K with 16-byte aligned rows, 2 planar Q6_K, 3 planar Q8_0,
+// 4 GGUF Q8_0 rows.
 // BPS: blocks per SM the instance is built for (registers capped accordingly). Two blocks of two stages share an SM's
 // shared and tensor memory: one block's epilogue and prologue run under the other's main loop.
 template <int BN, int STAGES, int MODE, int BPS>
@@ -378,6 +379,42 @@ __global__ void __launch_bounds__(THREADS, BPS) prefill_kernel(const __grid_cons
                 }
                 ok = put(chunks, piece * 4, piece * 4 + 2);
             }
+        } else if (MODE == 4) {
+            // GGUF Q8_0 rows (34-byte blocks: an f16 scale, 32 codes; blocks start on 2-byte boundaries only). Piece p takes
+            // block p of the K step. The codes are fetched as aligned 32-bit words around them and shifted into place
+            // (the offset within a word is 0 or 2 bytes); an aligned word never reaches past a buffer whose size is a multiple
+            // of four, and the word beyond the codes is only read when the shift needs it.
+            const uint8_t *blk = wbase + (size_t)grow * p.stride + piece * 34;
+            auto fetch = [&](const uint8_t *b, uint32_t (&w)[9], float &d) {
+                d = __half2float(*(const __half *)b);
+                const uintptr_t cp = (uintptr_t)(b + 2);
+                const uint32_t *base = (const uint32_t *)(cp & ~(uintptr_t)3);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) w[j] = __ldg(base + j);
+                w[8] = (cp & 2) ? __ldg(base + 8) : 0u;
+            };
+            uint32_t w_n[9];
+            float d_n;
+            fetch(blk, w_n, d_n);
+            for (uint32_t k = 0; k < ksteps && ok; ++k) {
+                uint32_t w_c[9];
+#pragma unroll
+                for (int j = 0; j < 9; ++j) w_c[j] = w_n[j];
+                const float d = d_n, bias = -128.0f * d_n;
+                const uint32_t sh = (((uintptr_t)(blk + 2)) & 2) ? 16u : 0u;
+                if (k + 1 < ksteps) {
+                    blk += 68;
+                    fetch(blk, w_n, d_n);
+                }
+                uint4 chunks[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint32_t c0 = __funnelshift_r(w_c[c * 2], w_c[c * 2 + 1], sh), c1 = __funnelshift_r(w_c[c * 2 + 1], w_c[c * 2 + 2], sh);
+                    codes4_fma(c0 ^ 0x80808080u, d, bias, chunks[c].x, chunks[c].y);  // (code + 128) * d - 128 d
+                    codes4_fma(c1 ^ 0x80808080u, d, bias, chunks[c].z, chunks[c].w);
+                }
+                ok = put(chunks, piece * 4, piece * 4 + 2);
+            }
         } else {
             for (uint32_t k = 0; k < ksteps && ok; ++k) {
                 uint4 chunks[4];
@@ -478,10 +515,11 @@ static bool configure_one() {
 }
 template <int BN, int STAGES, int BPS>
 static bool configure_bn() {
-    return configure_one<BN, STAGES, 0, BPS>() && configure_one<BN, STAGES, 1, BPS>() && configure_one<BN, STAGES, 2, BPS>() && configure_one<BN, STAGES, 3, BPS>();
+    return configure_one<BN, STAGES, 0, BPS>() && configure_one<BN, STAGES, 1, BPS>() && configure_one<BN, STAGES, 2, BPS>() && configure_one<BN, STAGES, 3, BPS>() &&
+           configure_one<BN, STAGES, 4, BPS>();
 }
 
-bool prefill_configure() { return configure_bn<256, 4, 1>() && configure_bn<256, 2, 2>() && configure_bn<128, 6, 1>() && configure_bn<64, 8, 1>(); }
+bool prefill_configure() { return configure_bn<256, 4, 1>() && configure_bn<256, 2, 2>() && configure_bn<128, 6, 1>() && configure_bn<64, 8, 1>() && configure_bn<64, 4, 2>(); }
 
 static uint32_t pick_bn(uint32_t tokens) { return tokens > 128 ? 256 : tokens > 64 ? 128 : 64; }
 
@@ -492,6 +530,7 @@ static void launch_bn(dim3 grid, cudaStream_t s, const prefill::Params &p, int m
     case 1: prefill::prefill_kernel<BN, STAGES, 1, BPS><<<grid, prefill::THREADS, bytes, s>>>(p); break;
     case 2: prefill::prefill_kernel<BN, STAGES, 2, BPS><<<grid, prefill::THREADS, bytes, s>>>(p); break;
     case 3: prefill::prefill_kernel<BN, STAGES, 3, BPS><<<grid, prefill::THREADS, bytes, s>>>(p); break;
+    case 4: prefill::prefill_kernel<BN, STAGES, 4, BPS><<<grid, prefill::THREADS, bytes, s>>>(p); break;
     default: prefill::prefill_kernel<BN, STAGES, 0, BPS><<<grid, prefill::THREADS, bytes, s>>>(p); break;
     }
 }
@@ -529,10 +568,11 @@ int launch_prefill(cudaStream_t s, const PrefillJob &j) {
         p.row_tiles = grid.y;
         grid = dim3(grid.x * grid.y, 1);
     }
-    const int mode = !p.fast ? 0 : j.enc == Q4_K ? 1 : j.layout == 1 ? 2 : 3;
+    const bool q8_rows = j.layout == 0 && j.enc == Q8_0 && (uintptr_t)j.w % 4 == 0 && j.stride % 2 == 0;
+    const int mode = q8_rows ? 4 : !p.fast ? 0 : j.enc == Q4_K ? 1 : j.layout == 1 ? 2 : 3;
     // Two blocks per SM (two stages each) when there are more blocks than SMs and the decoder is light enough for the
     // smaller register budget (measured: Q4_K 933 -> 1,067 TFLOP/s; planar Q6_K loses a little).
-    const bool two = bn == 256 && (mode == 1 || mode == 3) && (size_t)grid.x * grid.y > (size_t)j.sm_count;
+    const bool two = bn == 256 && (mode == 1 || mode == 3 || mode == 4) && (size_t)grid.x * grid.y > (size_t)j.sm_count;
     if (two) launch_bn<256, 2, 2>(grid, s, p, mode);
     else if (bn == 256) launch_bn<256, 4, 1>(grid, s, p, mode);
     else if (bn == 128) launch_bn<128, 6, 1>(grid, s, p, mode);
@@ -554,8 +594,11 @@ constexpr int GROUP_BN = 64;
 __global__ void __launch_bounds__(256) expert_gather_kernel(const uint32_t *lists, uint32_t experts, uint32_t bound, const float *in, size_t in_stride,
                                                             uint32_t in_group, uint32_t columns, __nv_bfloat16 *gathered, uint32_t *table) {
     __shared__ uint32_t found[4];  // expert, rows of this tile, first list entry, total tiles
-    const uint32_t *offsets = lists + 2, *slot_rows = lists + experts + 3 + 3 * (size_t)bound;
+    __shared__ uint32_t offsets[257];  // the experts' prefix offsets (at most 256 experts), read once by the block
+    const uint32_t *slot_rows = lists + experts + 3 + 3 * (size_t)bound;
     const uint32_t tile = blockIdx.x, tid = threadIdx.x;
+    for (uint32_t i = tid; i <= experts && i < 257; i += 256) offsets[i] = lists[2 + i];
+    __syncthreads();
     if (tid == 0) {
         uint32_t at = 0;
         found[0] = 0xffffffffu;
@@ -615,7 +658,10 @@ int launch_matmul_experts_fast(cudaStream_t s, uint32_t enc, const uint8_t *w, s
     p.out = out; p.out_stride = out_stride; p.status = status;
     p.tiles = table; p.slot_rows = lists + experts + 3 + 3 * (size_t)bound; p.expert_bytes = expert_bytes;
     dim3 grid((unsigned)tiles, (rows + prefill::BM - 1) / prefill::BM);
-    launch_bn<64, 8, 1>(grid, s, p, p.fast ? 1 : 0);
+    // Two blocks of four stages per SM: with 64-row tiles the block is bound by its eight decoding warps, not by the tensor
+    // core, and a second block doubles them (measured at 4,096 slot rows over 128 experts: the gate_up GEMM 425 -> see bench).
+    const bool q8_rows = enc == Q8_0 && (uintptr_t)w % 4 == 0 && stride % 2 == 0 && expert_bytes % 4 == 0;
+    launch_bn<64, 4, 2>(grid, s, p, p.fast ? 1 : q8_rows ? 4 : 0);
     return 2;
 }
 
