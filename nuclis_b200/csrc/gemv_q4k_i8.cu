@@ -29,10 +29,11 @@ namespace i8 {
 
 using Plain = Q4KPlain;
 using Dense = Q4KDense;
+using Quad = Q4KDense;  // three or four tokens: the 15-warp geometry (two mmas a group want the wide form's registers), no K cut forced by the digit rows
 
 static bool fill(const FastJob &job, Params &p, Plan &plan, bool maps) {
     if (job.enc != Q4_K || job.layout != 0) return false;
-    const bool ok = job.tokens == 1 ? fill_geometry<Q4K, Plain, 1>(job, p, plan) : job.tokens == 2 ? fill_geometry<Q4K, Plain, 2>(job, p, plan) : fill_geometry<Q4K, Dense, 8>(job, p, plan);
+    const bool ok = job.tokens == 1 ? fill_geometry<Q4K, Plain, 1>(job, p, plan) : job.tokens == 2 ? fill_geometry<Q4K, Plain, 2>(job, p, plan) : job.tokens <= 4 ? fill_geometry<Q4K, Quad, 4>(job, p, plan) : fill_geometry<Q4K, Dense, 8>(job, p, plan);
     if (!ok) return false;
     for (uint32_t s = 0; s < job.count; ++s) {
         const FastSegment &g = job.seg[s];
@@ -43,7 +44,7 @@ static bool fill(const FastJob &job, Params &p, Plan &plan, bool maps) {
 }
 
 static int launch(cudaStream_t s, const FastJob &job, const Params &p, const Plan &plan) {
-    return plan.nt == 1 ? launch_geometry<Q4K, Plain, 1>(s, job, p, plan) : plan.nt == 2 ? launch_geometry<Q4K, Plain, 2>(s, job, p, plan) : launch_geometry<Q4K, Dense, 8>(s, job, p, plan);
+    return plan.nt == 1 ? launch_geometry<Q4K, Plain, 1>(s, job, p, plan) : plan.nt == 2 ? launch_geometry<Q4K, Plain, 2>(s, job, p, plan) : plan.nt == 4 ? launch_geometry<Q4K, Quad, 4>(s, job, p, plan) : launch_geometry<Q4K, Dense, 8>(s, job, p, plan);
 }
 
 }  // namespace i8
@@ -51,7 +52,8 @@ static int launch(cudaStream_t s, const FastJob &job, const Params &p, const Pla
 bool q4k_i8_fill(const FastJob &job, i8::Params &p, i8::Plan &plan, bool maps) { return i8::fill(job, p, plan, maps); }
 
 bool q4k_i8_configure() {
-    return i8::configure_geometry<i8::Q4K, i8::Plain, 1>() && i8::configure_geometry<i8::Q4K, i8::Plain, 2>() && i8::configure_geometry<i8::Q4K, i8::Dense, 8>();
+    return i8::configure_geometry<i8::Q4K, i8::Plain, 1>() && i8::configure_geometry<i8::Q4K, i8::Plain, 2>() && i8::configure_geometry<i8::Q4K, i8::Quad, 4>() &&
+           i8::configure_geometry<i8::Q4K, i8::Dense, 8>();
 }
 
 bool q4k_i8_supported(const FastJob &job) {

@@ -24,10 +24,11 @@ namespace i8 {
 
 using Plain = Q6KPlain;
 using Dense = Q6KDense;
+using Quad = Q6KDense;  // three or four tokens: the 15-warp geometry (two mmas a group want the wide form's registers), no K cut forced by the digit rows
 
 static bool fill(const FastJob &job, Params &p, Plan &plan, bool maps) {
     if (job.enc != Q6_K || job.layout != 1) return false;
-    const bool ok = job.tokens == 1 ? fill_geometry<Q6K, Plain, 1>(job, p, plan) : job.tokens == 2 ? fill_geometry<Q6K, Plain, 2>(job, p, plan) : fill_geometry<Q6K, Dense, 8>(job, p, plan);
+    const bool ok = job.tokens == 1 ? fill_geometry<Q6K, Plain, 1>(job, p, plan) : job.tokens == 2 ? fill_geometry<Q6K, Plain, 2>(job, p, plan) : job.tokens <= 4 ? fill_geometry<Q6K, Quad, 4>(job, p, plan) : fill_geometry<Q6K, Dense, 8>(job, p, plan);
     if (!ok) return false;
     for (uint32_t s = 0; s < job.count; ++s) {
         const FastSegment &g = job.seg[s];
@@ -42,7 +43,7 @@ static bool fill(const FastJob &job, Params &p, Plan &plan, bool maps) {
 }
 
 static int launch(cudaStream_t s, const FastJob &job, const Params &p, const Plan &plan) {
-    return plan.nt == 1 ? launch_geometry<Q6K, Plain, 1>(s, job, p, plan) : plan.nt == 2 ? launch_geometry<Q6K, Plain, 2>(s, job, p, plan) : launch_geometry<Q6K, Dense, 8>(s, job, p, plan);
+    return plan.nt == 1 ? launch_geometry<Q6K, Plain, 1>(s, job, p, plan) : plan.nt == 2 ? launch_geometry<Q6K, Plain, 2>(s, job, p, plan) : plan.nt == 4 ? launch_geometry<Q6K, Quad, 4>(s, job, p, plan) : launch_geometry<Q6K, Dense, 8>(s, job, p, plan);
 }
 
 }  // namespace i8
@@ -50,7 +51,8 @@ static int launch(cudaStream_t s, const FastJob &job, const Params &p, const Pla
 bool q6k_i8_fill(const FastJob &job, i8::Params &p, i8::Plan &plan, bool maps) { return i8::fill(job, p, plan, maps); }
 
 bool q6k_i8_configure() {
-    return i8::configure_geometry<i8::Q6K, i8::Plain, 1>() && i8::configure_geometry<i8::Q6K, i8::Plain, 2>() && i8::configure_geometry<i8::Q6K, i8::Dense, 8>();
+    return i8::configure_geometry<i8::Q6K, i8::Plain, 1>() && i8::configure_geometry<i8::Q6K, i8::Plain, 2>() && i8::configure_geometry<i8::Q6K, i8::Quad, 4>() &&
+           i8::configure_geometry<i8::Q6K, i8::Dense, 8>();
 }
 
 bool q6k_i8_supported(const FastJob &job) {

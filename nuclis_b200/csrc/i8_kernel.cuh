@@ -96,13 +96,18 @@ __device__ __forceinline__ uint32_t hsub2(uint32_t a, uint32_t b) {
 __device__ __forceinline__ uint32_t row_of(uint32_t g) { return g < 4 ? 2 * g : 2 * g - 7; }
 
 // NT is the number of token columns a kernel instance is built for: 1, 2 (narrow: one mma serves the three
-// digit planes) or 8 (wide: three to eight tokens, an mma per plane).
+// digit planes), 4 (three or four tokens: two mmas, planes 0 and 1 in the first, plane 2 in half of the second) or
+// 8 (wide: five to eight tokens, an mma per plane).
 template <int NT>
-__host__ __device__ constexpr int plane_columns() { return NT == 8 ? 24 : 6; }  // digit rows staged: planes x tokens
+__host__ __device__ constexpr int token_stride() { return NT == 8 ? 8 : NT == 4 ? 4 : 2; }  // rows between two digit planes (and between the hi and lo group sums)
 template <int NT>
-__host__ __device__ constexpr int gs_columns() { return NT == 8 ? 16 : 4; }     // group-sum rows staged: (hi, lo) x tokens
+__host__ __device__ constexpr int plane_columns() { return 3 * token_stride<NT>(); }  // digit rows staged: planes x tokens
 template <int NT>
-__host__ __device__ constexpr int record_lanes() { return NT == 8 ? 32 : 8; }   // float4 a unit's sums take (narrow: quad lane 0 of each quad)
+__host__ __device__ constexpr int gs_columns() { return 2 * token_stride<NT>(); }     // group-sum rows staged: (hi, lo) x tokens
+template <int NT>
+__host__ __device__ constexpr int record_lanes() { return NT == 8 ? 32 : NT == 4 ? 16 : 8; }  // float4 a unit's sums take (the lanes that hold sums)
+template <int NT>
+__host__ __device__ constexpr int mma_count() { return NT == 8 ? 3 : NT == 4 ? 2 : 1; }  // integer mmas per scale group
 
 __device__ __forceinline__ void unit_rows(const Params &p, uint32_t unit, uint32_t &seg, uint32_t &row0) {
     seg = 0;
@@ -113,12 +118,13 @@ __device__ __forceinline__ void unit_rows(const Params &p, uint32_t unit, uint32
 }
 
 // Writes the finished sums a lane holds for a unit. v: (row r, token a), (row r, token a + 1), (row r + 8, a), (row r + 8, a + 1)
-// with r = row_of(g); narrow: a = 0 and only quad lane 0 holds sums; wide: a = 2t. w: the up sums in pair mode.
+// with r = row_of(g); narrow: a = 0 and only quad lane 0 holds sums; four tokens: a = 2t in quad lanes 0 and 1; wide: a = 2t.
+// w: the up sums in pair mode.
 template <int NT>
 __device__ __forceinline__ void write_unit(const Params &p, uint32_t unit, uint32_t g, uint32_t t, const float v[4], const float w[4]) {
-    constexpr bool WIDE = NT == 8;
-    if (!WIDE && t != 0) return;
-    const uint32_t r = row_of(g), tok0 = WIDE ? 2 * t : 0;
+    constexpr bool WIDE = NT == 8, QUAD = NT == 4;
+    if (QUAD ? t >= 2 : (!WIDE && t != 0)) return;
+    const uint32_t r = row_of(g), tok0 = (WIDE || QUAD) ? 2 * t : 0;
     if (p.mode != ACT_NONE) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -200,7 +206,8 @@ __device__ __forceinline__ void mbar_inval(uint32_t bar) { asm volatile("mbarrie
 // (fill_geometry).
 template <class E, class G, int NT, bool SHARE>
 __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const int STAGES, uint8_t *smem, const ChainLink link) {
-    constexpr bool WIDE = NT == 8;
+    constexpr bool WIDE = NT == 8, QUAD = NT == 4;
+    constexpr uint32_t TS = token_stride<NT>();
     constexpr int STAGE_BYTES = E::STAGE_BYTES;  // 16 weight rows x PARTS superblocks (one TMA box, one task per warp of the slot),
                                                  // then whatever second plane the encoding's records need
     constexpr int WARPS = G::WARPS, SLOTS = G::SLOTS, PARTS = G::PARTS;
@@ -352,9 +359,9 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
                 const uint32_t e = (__float_as_uint(mx) >> 23) & 0xffu;
                 const bool ok = e >= 22u && e < 255u;
                 const float scale = ok ? __uint_as_float((275u - e) << 23) : 0.0f;
-                // the digit rows of this token: B column of plane d is (narrow) d * 2 + token, (wide) d * 8 + token
+                // the digit rows of this token: plane d is row d * TS + token (TS = 2, 4 or 8 tokens a plane)
                 uint8_t *row0 = planes + (size_t)tok * p.plane_pitch + sb * 256 + lane * 4;  // byte c of a superblock's 256 is column c
-                const uint32_t plane_step = (WIDE ? 8u : 2u) * p.plane_pitch;
+                const uint32_t plane_step = TS * p.plane_pitch;
                 int gsum[2];
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
@@ -384,7 +391,7 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
                         const __half sh = __float2half_rn(f), sl = __float2half_rn(f - __half2float(sh));
                         const uint32_t grp = sb * (2 * GPER) + hf * GPER + lane / GLANES;
                         *(__half *)(gs + (size_t)tok * p.gs_pitch + grp * 2) = sh;
-                        *(__half *)(gs + (size_t)((WIDE ? 8u : 2u) + tok) * p.gs_pitch + grp * 2) = sl;
+                        *(__half *)(gs + (size_t)(TS + tok) * p.gs_pitch + grp * 2) = sl;
                     }
                 }
                 if (lane == 0) inv[sb * 8 + tok] = ok ? __uint_as_float((e - 21u) << 23) : (e == 255u ? __uint_as_float(0x7fc00000u) : 0.0f);
@@ -401,10 +408,21 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
     const uint8_t *xlane;
     const uint8_t *gslane;
     uint32_t gs_step;   // bytes from a lane's hi group sums to its lo group sums (wide)
+    uint32_t bstep = 0; // bytes from a lane's digit row of one mma to that of the next
     if (WIDE) {
         xlane = planes + (size_t)(g < p.tokens ? g : 0u) * p.plane_pitch + t * E::LANE_BYTES;
+        bstep = 8u * p.plane_pitch;
         gslane = g < p.tokens ? gs + (size_t)g * p.gs_pitch + t * 4 : zero;
         gs_step = g < p.tokens ? 8u * p.gs_pitch : 0u;
+    } else if (QUAD) {
+        // first mma: column g = (plane g >> 2, token g & 3); second: columns 0..3 = (plane 2, token), 4..7 unused. The
+        // mma of the minima has columns (piece g >> 2, token g & 3). Columns of tokens that are not there read row 0.
+        const bool there = (g & 3u) < p.tokens;
+        const uint32_t row_a = there ? g : 0u, row_b = (there && g < 4) ? 8u + g : 0u;
+        xlane = planes + (size_t)row_a * p.plane_pitch + t * E::LANE_BYTES;
+        bstep = (row_b - row_a) * p.plane_pitch;  // (modulo 2^32: added to a pointer)
+        gslane = there ? gs + (size_t)g * p.gs_pitch + t * 4 : zero;
+        gs_step = 0;
     } else {
         const bool used = g < 6 && (g & 1u) < (uint32_t)NT;
         xlane = planes + (size_t)(used ? g : 0u) * p.plane_pitch + t * E::LANE_BYTES;
@@ -416,8 +434,11 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
     const uint32_t gs_sb = (gslane == zero) ? 0u : (uint32_t)E::GS_BYTES;
     // narrow: lane t holds the sums of digit plane t (weights 1, 2^8, 2^16; quad lane 3 holds nothing); E::UNIT undoes
     // a factor the encoding's integer sums carry (Q4_K: 16, the high nibbles left in place)
-    const float wl = E::UNIT * (WIDE ? 1.0f : (t == 0 ? 1.0f : t == 1 ? 256.0f : t == 2 ? 65536.0f : 0.0f));
-    const float *ivlane = inv + (WIDE ? 2 * t : 0);  // 1 / scale of the lane's token(s), per superblock
+    // The weight of the digit plane each of the lane's mmas holds. Four tokens: quad lanes 0, 1 hold plane 0 (first mma)
+    // and plane 2 (second), lanes 2, 3 plane 1 and nothing; lanes t and t ^ 2 hold the same two tokens.
+    const float wl[3] = {E::UNIT * (WIDE ? 1.0f : QUAD ? (t < 2 ? 1.0f : 256.0f) : (t == 0 ? 1.0f : t == 1 ? 256.0f : t == 2 ? 65536.0f : 0.0f)),
+                         E::UNIT * (WIDE ? 256.0f : (QUAD && t < 2) ? 65536.0f : 0.0f), E::UNIT * (WIDE ? 65536.0f : 0.0f)};
+    const float *ivlane = inv + (WIDE ? 2 * t : QUAD ? 2 * (t & 1u) : 0);  // 1 / scale of the lane's token(s), per superblock
     uint32_t c_stage = 0, c_phase = 0, consumed = 0;
     bool failed = false;
     for (uint32_t uidx = 0; uidx < my_items; ++uidx) {
@@ -432,7 +453,7 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
             if (part == 0 && issued < total) issue();  // keep STAGES - 1 stages in flight
             if (!mbar_wait(full0 + c_stage * 8, c_phase)) { failed = true; break; }
             if (live)
-                E::template task<NT>(my_stage + c_stage * STAGE_BYTES, part, xlane + sbw * 256, p.plane_pitch, gslane + sbw * gs_sb, gs_step, ivlane + sbw * 8, wl, gr, t, acc);
+                E::template task<NT>(my_stage + c_stage * STAGE_BYTES, part, xlane + sbw * 256, bstep, gslane + sbw * gs_sb, gs_step, ivlane + sbw * 8, wl, gr, t, acc);
             __syncwarp();  // all lanes are done reading this stage
             if (lane == 0) mbar_arrive(empty0 + c_stage * 8);
             ++consumed;
@@ -441,7 +462,7 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
                 if (part == 0 && issued < total) issue();
                 if (!mbar_wait(full0 + c_stage * 8, c_phase)) { failed = true; break; }
                 if (live)
-                    E::template task<NT>(my_stage + c_stage * STAGE_BYTES, part, xlane + sbw * 256, p.plane_pitch, gslane + sbw * gs_sb, gs_step, ivlane + sbw * 8, wl, gr, t, acc2);
+                    E::template task<NT>(my_stage + c_stage * STAGE_BYTES, part, xlane + sbw * 256, bstep, gslane + sbw * gs_sb, gs_step, ivlane + sbw * 8, wl, gr, t, acc2);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty0 + c_stage * 8);
                 ++consumed;
@@ -454,17 +475,17 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 if (NT == 1 && (i & 1)) continue;
-                acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 1);
+                if (!QUAD) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 1);
                 acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 2);
                 if (pair) {
-                    acc2[i] += __shfl_xor_sync(0xffffffffu, acc2[i], 1);
+                    if (!QUAD) acc2[i] += __shfl_xor_sync(0xffffffffu, acc2[i], 1);
                     acc2[i] += __shfl_xor_sync(0xffffffffu, acc2[i], 2);
                 }
             }
         }
         // ---- the parts of the unit meet; part 0 adds them in part order ----
-        const bool holds = WIDE || t == 0;
-        const uint32_t rec = WIDE ? lane : g;
+        const bool holds = WIDE || (QUAD ? t < 2 : t == 0);
+        const uint32_t rec = WIDE ? lane : QUAD ? g * 2 + t : g;
         float4 *buf = parts + (size_t)((slot * 2 + (uidx & 1u)) * (PARTS - 1)) * (pair ? 2 : 1) * REC;
         if (part > 0 && holds) {
             float4 *dst = buf + (size_t)(part - 1) * (pair ? 2 : 1) * REC;
@@ -518,8 +539,8 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
         // time (one round trip for all of them), then the warp finishes those it was last for.
         __threadfence();
         __syncwarp();
-        const bool holds = WIDE || t == 0;
-        const uint32_t rec = WIDE ? lane : g;
+        const bool holds = WIDE || (QUAD ? t < 2 : t == 0);
+        const uint32_t rec = WIDE ? lane : QUAD ? g * 2 + t : g;
         for (uint32_t base = 0; base < my_units; base += 32) {
             const uint32_t mine_u = base + lane;
             uint32_t last = 0;
@@ -598,7 +619,7 @@ template <class E, class G, int NT>
 static bool fill_geometry(const FastJob &job, Params &p, Plan &plan) {
     constexpr int SLOTS = G::SLOTS, PARTS = G::PARTS;
     if (job.tokens < 1 || job.tokens > 8 || job.count < 1 || job.count > 4) return false;
-    if (NT == 8 ? job.tokens < 3 : job.tokens != (uint32_t)NT) return false;
+    if (NT == 8 ? job.tokens < 3 : NT == 4 ? (job.tokens < 3 || job.tokens > 4) : job.tokens != (uint32_t)NT) return false;
     if (job.columns == 0 || job.columns % 256 != 0) return false;
     if ((uintptr_t)job.in % 16 != 0 || job.in_stride % 4 != 0 || job.in_stride > 0xffffffffull) return false;
     if (job.mode != ACT_NONE && (job.count != 2 || job.seg[0].rows != job.seg[1].rows)) return false;

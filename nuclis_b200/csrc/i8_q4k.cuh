@@ -53,15 +53,15 @@ struct Q4K {
     }
 
     // One task (superblock `part` of the stage): task rows gr and gr + 8 against every B column. xb: this lane's digit row at the task's
-    // superblock (its 8 bytes of group 0); the digit rows of the next mma (wide) lie 8 * pitch further.
+    // superblock (its 8 bytes of group 0); the digit rows of the next mma lie `bstep` bytes further.
     // gsb: this lane's word of the group sums. iv: 1 / the activation scale of the lane's token(s) at this superblock.
     // acc: (row gr, token a), (gr, a + 1), (gr + 8, a), (gr + 8, a + 1); with one token the odd entries stay untouched.
     template <int NT>
-    __device__ static __forceinline__ void task(const uint8_t *stage, uint32_t part, const uint8_t *xb, uint32_t pitch, const uint8_t *gsb, uint32_t gs_step, const float *iv,
-                                                float wl, uint32_t gr, uint32_t t, float acc[4]) {
+    __device__ static __forceinline__ void task(const uint8_t *stage, uint32_t part, const uint8_t *xb, uint32_t bstep, const uint8_t *gsb, uint32_t gs_step, const float *iv,
+                                                const float (&wl)[3], uint32_t gr, uint32_t t, float acc[4]) {
         const uint8_t *task = stage + part * ROW_BYTES;
         constexpr bool WIDE = NT == 8;
-        constexpr int NC = WIDE ? 3 : 1;
+        constexpr int NC = mma_count<NT>();
         constexpr int STEP = NT == 1 ? 2 : 1;  // one token: accumulator columns 0 and 2 only
         const uint8_t *r0 = task + gr * ROW_PITCH, *r1 = r0 + 8 * ROW_PITCH;
         const uint4 h0 = *(const uint4 *)r0, h1 = *(const uint4 *)r1;
@@ -78,8 +78,8 @@ struct Q4K {
             const uint32_t ao[4] = {q0.x & 0xf0f0f0f0u, q1.x & 0xf0f0f0f0u, q0.y & 0xf0f0f0f0u, q1.y & 0xf0f0f0f0u};
 #pragma unroll
             for (int j = 0; j < NC; ++j) {
-                const uint2 be = *(const uint2 *)(xb + (size_t)j * 8 * pitch + (2 * c) * 32);
-                const uint2 bo = *(const uint2 *)(xb + (size_t)j * 8 * pitch + (2 * c + 1) * 32);
+                const uint2 be = *(const uint2 *)(xb + j * bstep + (2 * c) * 32);
+                const uint2 bo = *(const uint2 *)(xb + j * bstep + (2 * c + 1) * 32);
                 int ce[4], co[4];
                 imma_u8(ce, ae, be.x, be.y);
                 imma_u8(co, ao, bo.x, bo.y);
@@ -98,11 +98,12 @@ struct Q4K {
         const float dm0 = -4096.0f * a.dmin, dm1 = -4096.0f * b.dmin;
 #pragma unroll
         for (int i = 0; i < 4; i += STEP) {
-            // 16 * sum_g s_g * sum(q * digit) per plane (below 2^29); wide: the planes recombined in F32
-            float f = (float)((ie[0][i] << 4) + io[0][i]);
-            if (WIDE) f = fmaf((float)((ie[2][i] << 4) + io[2][i]), 65536.0f, fmaf((float)((ie[1][i] << 4) + io[1][i]), 256.0f, f));
+            // 16 * sum_g s_g * sum(q * digit) per plane (below 2^29), each plane with the weight of its digits, met in F32
+            float f = (float)((ie[0][i] << 4) + io[0][i]) * wl[0];
+#pragma unroll
+            for (int j = 1; j < NC; ++j) f = fmaf((float)((ie[j][i] << 4) + io[j][i]), wl[j], f);
             const float ivi = (i & 1) ? iv1 : iv0;
-            acc[i] = fmaf(f, (i < 2 ? a.d : b.d) * (ivi * wl), acc[i]);
+            acc[i] = fmaf(f, (i < 2 ? a.d : b.d) * ivi, acc[i]);
             acc[i] = fmaf(cm[i], (i < 2 ? dm0 : dm1) * ivi, acc[i]);
         }
     }

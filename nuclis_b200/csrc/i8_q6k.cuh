@@ -47,10 +47,10 @@ struct Q6K {
     // One task (record `part` of the stage): task rows gr and gr + 8 against every B column. xb: this lane's four
     // bytes of group 0 in its digit row; gsb: its first word of the group sums (the second lies 16 bytes further).
     template <int NT>
-    __device__ static __forceinline__ void task(const uint8_t *stage, uint32_t part, const uint8_t *xb, uint32_t pitch, const uint8_t *gsb, uint32_t gs_step, const float *iv,
-                                                float wl, uint32_t gr, uint32_t t, float acc[4]) {
+    __device__ static __forceinline__ void task(const uint8_t *stage, uint32_t part, const uint8_t *xb, uint32_t bstep, const uint8_t *gsb, uint32_t gs_step, const float *iv,
+                                                const float (&wl)[3], uint32_t gr, uint32_t t, float acc[4]) {
         constexpr bool WIDE = NT == 8;
-        constexpr int NC = WIDE ? 3 : 1;
+        constexpr int NC = mma_count<NT>();
         constexpr int STEP = NT == 1 ? 2 : 1;
         const uint8_t *r0 = stage + gr * ROW_PITCH + part * ROW_BYTES, *r1 = r0 + 8 * ROW_PITCH;
         int acci[NC][4];
@@ -78,7 +78,7 @@ struct Q6K {
                 const int s1 = (gi & 3) == 0 ? sbyte<0>(w1) : (gi & 3) == 1 ? sbyte<1>(w1) : (gi & 3) == 2 ? sbyte<2>(w1) : sbyte<3>(w1);
 #pragma unroll
                 for (int j = 0; j < NC; ++j) {
-                    const uint32_t b = *(const uint32_t *)(xb + (size_t)j * 8 * pitch + gi * 16);
+                    const uint32_t b = *(const uint32_t *)(xb + j * bstep + gi * 16);
                     int c[4];
                     imma_k16_u8(c, v0, v1, b);
 #pragma unroll
@@ -99,10 +99,11 @@ struct Q6K {
         const float d0 = __half2float(dsc[gr]), d1 = __half2float(dsc[gr + 8]);
 #pragma unroll
         for (int i = 0; i < 4; i += STEP) {
-            float f = (float)acci[0][i];
-            if (WIDE) f = fmaf((float)acci[2][i], 65536.0f, fmaf((float)acci[1][i], 256.0f, f));
+            float f = (float)acci[0][i] * wl[0];
+#pragma unroll
+            for (int j = 1; j < NC; ++j) f = fmaf((float)acci[j][i], wl[j], f);
             const float ivi = (i & 1) ? iv1 : iv0, d = i < 2 ? d0 : d1;
-            acc[i] = fmaf(f, d * (ivi * wl), acc[i]);
+            acc[i] = fmaf(f, d * ivi, acc[i]);
             acc[i] = fmaf(cm[i], -65536.0f * d * ivi, acc[i]);  // 32 * 2^11
         }
     }
