@@ -15,10 +15,10 @@
 //
 // An encoding supplies a policy class E: the bytes of a task (16 weight rows x one superblock), the
 // copy that fetches it, and the mma loop over one task. Work split, task ring, programmatic dependent
-// launch and the sums across K parts and K slices are those of the earlier fp16 skeleton
-// (decode_kernel.cuh), whose helpers this file uses.
+// launch and the sums across K parts and K slices are described at run_op below; the small device helpers
+// (barriers, copies) are in gemv_common.cuh.
 #pragma once
-#include "decode_kernel.cuh"
+#include "gemv_common.cuh"
 
 namespace nu {
 namespace i8 {
@@ -118,13 +118,13 @@ __device__ __forceinline__ void unit_rows(const Params &p, uint32_t unit, uint32
 }
 
 // Writes the finished sums a lane holds for a unit. v: (row r, token a), (row r, token a + 1), (row r + 8, a), (row r + 8, a + 1)
-// with r = row_of(g); narrow: a = 0 and only quad lane 0 holds sums; four tokens: a = 2t in quad lanes 0 and 1; wide: a = 2t.
+// with r the task row of the lane's mma row (E::row); narrow: a = 0 and only quad lane 0 holds sums; four tokens: a = 2t in quad lanes 0 and 1; wide: a = 2t.
 // w: the up sums in pair mode.
 template <int NT>
-__device__ __forceinline__ void write_unit(const Params &p, uint32_t unit, uint32_t g, uint32_t t, const float v[4], const float w[4]) {
+__device__ __forceinline__ void write_unit(const Params &p, uint32_t unit, uint32_t r, uint32_t t, const float v[4], const float w[4]) {
     constexpr bool WIDE = NT == 8, QUAD = NT == 4;
     if (QUAD ? t >= 2 : (!WIDE && t != 0)) return;
-    const uint32_t r = row_of(g), tok0 = (WIDE || QUAD) ? 2 * t : 0;
+    const uint32_t tok0 = (WIDE || QUAD) ? 2 * t : 0;
     if (p.mode != ACT_NONE) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -381,7 +381,7 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
                 // 16 columns: four), scaled to fit fp16, as pieces hi + lo
                 constexpr uint32_t GLANES = E::GROUP / 4, GPER = 128 / E::GROUP;  // lanes and groups per 128 columns
 #pragma unroll
-                for (int hf = 0; hf < 2; ++hf) {
+                for (int hf = 0; hf < 2 && E::GROUP_SUMS; ++hf) {
                     int s = gsum[hf];
                     s += __shfl_xor_sync(0xffffffffu, s, 1);
                     s += __shfl_xor_sync(0xffffffffu, s, 2);
@@ -404,7 +404,7 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
     // This lane's B column n = g. Narrow: column = plane * 2 + token, columns 6 and 7 and the columns of a
     // token that is not there read column 0 (finite integers; their sums are never used). Wide: plane d is
     // the mma d, column = token.
-    const uint32_t gr = row_of(g);
+    const uint32_t gr = E::row(g);  // the task row this lane's mma row stands for (the encoding's shared-memory pitch decides)
     const uint8_t *xlane;
     const uint8_t *gslane;
     uint32_t gs_step;   // bytes from a lane's hi group sums to its lo group sums (wide)
@@ -531,7 +531,7 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
             dst[rec] = make_float4(acc[0], acc[1], acc[2], acc[3]);
             if (pair) dst[REC + rec] = make_float4(acc2[0], acc2[1], acc2[2], acc2[3]);
         } else {
-            write_unit<NT>(p, unit, g, t, acc, acc2);
+            write_unit<NT>(p, unit, gr, t, acc, acc2);
         }
     }
     if (p.nks > 1 && part == 0 && my_units) {
@@ -571,7 +571,7 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
                         }
                     }
                     const float v4[4] = {s.x, s.y, s.z, s.w}, w4[4] = {s2.x, s2.y, s2.z, s2.w};
-                    write_unit<NT>(p, unit, g, t, v4, w4);
+                    write_unit<NT>(p, unit, gr, t, v4, w4);
                 }
                 if (lane == 0) p.counters[unit] = 0;  // leave the scratch as it was found
             }
@@ -764,6 +764,8 @@ static int launch_geometry(cudaStream_t s, const FastJob &job, const Params &p, 
 bool q4k_i8_fill(const FastJob &job, i8::Params &p, i8::Plan &plan, bool maps);
 bool q6k_i8_fill(const FastJob &job, i8::Params &p, i8::Plan &plan, bool maps);
 
+// A uint8 tensor [rows][row_bytes] with `stride` bytes between rows, copied in boxes of box_rows x box_bytes (dispatch.cu).
+bool encode_weight_map(CUtensorMap *map, const uint8_t *base, uint64_t row_bytes, uint64_t rows, uint64_t stride, uint32_t box_bytes, uint32_t box_rows);
 bool encode_tiled_map(CUtensorMap *map, CUtensorMapDataType type, uint32_t elem_bytes, const void *base, uint64_t inner, uint64_t outer,
                       uint64_t stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle);
 

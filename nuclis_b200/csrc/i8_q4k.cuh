@@ -38,6 +38,7 @@ struct Q4K {
                                                           // lie 8 banks apart, which the lanes' 8-byte loads need (row_of)
     static constexpr int STAGE_BYTES = 16 * ROW_PITCH;    // 11520, a multiple of 128
     static constexpr int GROUP = 32;                      // columns per scale group
+    static constexpr bool GROUP_SUMS = true;               // the minima / the bias need the sums of X over the scale groups
     static constexpr int GS_BYTES = 16;                   // staged group sums per superblock and B column: eight fp16
     static constexpr float GS_SCALE = 0.000244140625f;    // 2^-12: a group sum of X (below 2^27) fits fp16
     static constexpr int PLANE_SKEW = 32;                 // digit rows 32 bytes apart round the banks: 8-byte loads, 4 lanes a row
@@ -47,6 +48,8 @@ struct Q4K {
     // One box of 16 rows x 720 bytes. Measured on B200: boxes of 16 x 144 bytes stream at 3.3 TB/s however many are
     // in flight (the copy engine's cost is per row of a box), 16 x 720 bytes at 6.2 TB/s. The tensor map counts in
     // 4-byte elements (a box side is at most 256 elements). Superblocks past the row are filled with zeros.
+    __device__ static __forceinline__ uint32_t row(uint32_t g) { return row_of(g); }
+
     __device__ static __forceinline__ void issue(const Params &p, uint32_t seg, uint32_t sb, uint32_t row0, uint32_t dst, uint32_t bar, uint64_t policy) {
         mbar_expect_tx(bar, STAGE_BYTES);
         tma_load_2d(dst, &p.map[seg], sb * (ROW_BYTES / 4), row0, bar, policy);

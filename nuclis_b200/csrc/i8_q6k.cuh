@@ -32,11 +32,14 @@ struct Q6K {
     static constexpr int MAIN_BYTES = 16 * ROW_PITCH;        // 9,984 = 78 x 128
     static constexpr int STAGE_BYTES = MAIN_BYTES + 128;     // + the 3 x 16 super-scales (96 bytes)
     static constexpr int GROUP = 16;
+    static constexpr bool GROUP_SUMS = true;               // the minima / the bias need the sums of X over the scale groups
     static constexpr int GS_BYTES = 32;                      // sixteen fp16 group sums per superblock and B column
     static constexpr float GS_SCALE = 0.00048828125f;        // 2^-11: a group sum of X (below 2^26) fits fp16
     static constexpr int PLANE_SKEW = 16;
     static constexpr int LANE_BYTES = 4;
     static constexpr float UNIT = 1.0f;
+
+    __device__ static __forceinline__ uint32_t row(uint32_t g) { return row_of(g); }
 
     __device__ static __forceinline__ void issue(const Params &p, uint32_t seg, uint32_t sb, uint32_t row0, uint32_t dst, uint32_t bar, uint64_t policy) {
         mbar_expect_tx(bar, MAIN_BYTES + STAGE_SBS * 32);

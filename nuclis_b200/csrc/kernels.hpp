@@ -109,21 +109,16 @@ bool q4k_i8_plan(const FastJob &job, uint32_t *slices, uint32_t *blocks);
 bool q6k_i8_configure();
 bool q6k_i8_supported(const FastJob &job);
 int launch_q6k_i8(cudaStream_t s, const FastJob &job);
+// ---- 1..8 activation rows on planar Q8_0, integer tensor path (gemv_q8_0_i8.cu) -----
+bool q8_0_i8_configure();
+bool q8_0_i8_supported(const FastJob &job);
+int launch_q8_0_i8(cudaStream_t s, const FastJob &job);
 // ---- a run of one-token integer-path jobs as one persistent launch (gemv_chain.cu) --
 constexpr int kChainMax = 16;
 bool chain_configure();
 bool chain_supported(const FastJob &job);
 // jobs[0..n), 2 <= n <= kChainMax, in order; arrivals: two zero words the kernel leaves zero. 0: nothing was launched.
 int launch_chain(cudaStream_t s, const FastJob *jobs, uint32_t n, uint32_t *arrivals, int sm_count);
-// ---- decode GEMV (one activation row) on the planar forms --------------------------
-// 2..8 token rows on planar Q8_0 (gemv_q8_0_rows.cu)
-bool q8_0_rows_configure();
-bool q8_0_rows_supported(const FastJob &job);
-int launch_q8_0_rows(cudaStream_t s, const FastJob &job);
-bool q8_0_decode_configure();
-bool q8_0_decode_supported(const FastJob &job);
-int launch_q8_0_decode(cudaStream_t s, const FastJob &job);
-
 // ---- prefill GEMM on tcgen05 (many token rows, bf16 operands, f32 accumulate) -------
 struct PrefillJob {
     uint32_t enc, layout;
