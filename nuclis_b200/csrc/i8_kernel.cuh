@@ -352,8 +352,7 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
                 const uint32_t sb = q / p.tokens, tok = q - sb * p.tokens;
                 float mx = fmaxf(fmaxf(fmaxf(fabsf(xa[j].x), fabsf(xa[j].y)), fmaxf(fabsf(xa[j].z), fabsf(xa[j].w))),
                                  fmaxf(fmaxf(fabsf(xb2[j].x), fabsf(xb2[j].y)), fmaxf(fabsf(xb2[j].z), fabsf(xb2[j].w))));
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                mx = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(mx)));  // (not negative: its bits order as it does)
                 // 2^k puts the largest |x| in [2^21, 2^22). A row of zeros or of values below 2^-105 is staged as
                 // zeros; an infinity or a NaN makes the superblock's factor a NaN, as F32 arithmetic would the sums.
                 const uint32_t e = (__float_as_uint(mx) >> 23) & 0xffu;
@@ -369,12 +368,13 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
                     int x0 = ok ? __float2int_rn(v.x * scale) : 0, x1 = ok ? __float2int_rn(v.y * scale) : 0;
                     int x2 = ok ? __float2int_rn(v.z * scale) : 0, x3 = ok ? __float2int_rn(v.w * scale) : 0;
                     gsum[hf] = (x0 + x1) + (x2 + x3);
+                    // The balanced digits of x are the bytes of x + 0x808080, each less 128: with u_i those bytes,
+                    // sum (u_i - 128) 256^i = x. As signed bytes, u - 128 is u ^ 0x80.
+                    const uint32_t y0 = (uint32_t)x0 + 0x808080u, y1 = (uint32_t)x1 + 0x808080u, y2 = (uint32_t)x2 + 0x808080u, y3 = (uint32_t)x3 + 0x808080u;
 #pragma unroll
                     for (int d = 0; d < 3; ++d) {
-                        // the low bytes are the balanced digits; what is left is (x + 128) >> 8
-                        const uint32_t lo = __byte_perm((uint32_t)x0, (uint32_t)x1, 0x0040), hi = __byte_perm((uint32_t)x2, (uint32_t)x3, 0x0040);
-                        *(uint32_t *)(row0 + d * plane_step + hf * 128) = __byte_perm(lo, hi, 0x5410);
-                        x0 = (x0 + 128) >> 8; x1 = (x1 + 128) >> 8; x2 = (x2 + 128) >> 8; x3 = (x3 + 128) >> 8;
+                        const uint32_t lo = __byte_perm(y0, y1, 0x0040 + 0x11 * d), hi = __byte_perm(y2, y3, 0x0040 + 0x11 * d);
+                        *(uint32_t *)(row0 + d * plane_step + hf * 128) = __byte_perm(lo, hi, 0x5410) ^ 0x80808080u;
                     }
                 }
                 // group sums of X over the encoding's scale groups (exact integers below 2^27; 32 columns: eight lanes,
