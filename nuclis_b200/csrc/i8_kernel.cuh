@@ -332,14 +332,17 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
 
     // ---- stage the slice's activations: a warp takes one (superblock, token) pair at a time ----
     // A pass keeps up to SBW pairs of a warp in registers between the loads and the conversion.
-    const uint32_t pairs = n * p.tokens;
+    // (token count: a constant of the one- and two-token instances; else a division by it is a multiplication by its
+    // 16-bit reciprocal, exact for the few hundred pairs of a slice)
+    const uint32_t ntok = NT <= 2 ? (uint32_t)NT : p.tokens, rtok = (65536u + ntok - 1u) / ntok;
+    const uint32_t pairs = n * ntok;
     for (uint32_t pass0 = 0; pass0 < pairs; pass0 += SBW * WARPS) {
         float4 xa[SBW], xb2[SBW];
 #pragma unroll
         for (int j = 0; j < SBW; ++j) {
             const uint32_t q = pass0 + warp + j * WARPS;
             if (q < pairs) {
-                const uint32_t sb = q / p.tokens, tok = q - sb * p.tokens;
+                const uint32_t sb = NT <= 2 ? q / ntok : (q * rtok) >> 16, tok = q - sb * ntok;
                 const float4 *src = (const float4 *)(p.in + (size_t)tok * p.in_stride) + (size_t)(sb0 + sb) * 64;
                 xa[j] = __ldcg(src + lane);  // L2: in a chain another block wrote them during this launch
                 xb2[j] = __ldcg(src + 32 + lane);
@@ -349,7 +352,7 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
         for (int j = 0; j < SBW; ++j) {
             const uint32_t q = pass0 + warp + j * WARPS;
             if (q < pairs) {  // uniform per warp
-                const uint32_t sb = q / p.tokens, tok = q - sb * p.tokens;
+                const uint32_t sb = NT <= 2 ? q / ntok : (q * rtok) >> 16, tok = q - sb * ntok;
                 float mx = fmaxf(fmaxf(fmaxf(fabsf(xa[j].x), fabsf(xa[j].y)), fmaxf(fabsf(xa[j].z), fabsf(xa[j].w))),
                                  fmaxf(fmaxf(fabsf(xb2[j].x), fabsf(xb2[j].y)), fmaxf(fabsf(xb2[j].z), fabsf(xb2[j].w))));
                 mx = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(mx)));  // (not negative: its bits order as it does)
@@ -365,8 +368,8 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
                     const float4 v = hf ? xb2[j] : xa[j];
-                    int x0 = ok ? __float2int_rn(v.x * scale) : 0, x1 = ok ? __float2int_rn(v.y * scale) : 0;
-                    int x2 = ok ? __float2int_rn(v.z * scale) : 0, x3 = ok ? __float2int_rn(v.w * scale) : 0;
+                    // (scale is 0 when the row is not to be staged: the products are 0 or NaN, which converts to 0)
+                    const int x0 = __float2int_rn(v.x * scale), x1 = __float2int_rn(v.y * scale), x2 = __float2int_rn(v.z * scale), x3 = __float2int_rn(v.w * scale);
                     gsum[hf] = (x0 + x1) + (x2 + x3);
                     // The balanced digits of x are the bytes of x + 0x808080, each less 128: with u_i those bytes,
                     // sum (u_i - 128) 256^i = x. As signed bytes, u - 128 is u ^ 0x80.
