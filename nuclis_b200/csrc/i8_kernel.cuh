@@ -472,7 +472,8 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
                 if (++c_stage == STAGES) { c_stage = 0; c_phase ^= 1u; }
             }
         }
-        if (part >= np) continue;  // this warp has no superblocks in this slice
+        // (a warp without superblocks in this slice, part >= np, holds zeros; it still meets the others below, so that
+        // the warps of a slot leave the unit together: the pass after the loop counts on that)
         if (!WIDE) {
             // the quad's lanes hold the three digit planes (and the two pieces of the minima): add them
 #pragma unroll
@@ -490,12 +491,12 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
         const bool holds = WIDE || (QUAD ? t < 2 : t == 0);
         const uint32_t rec = WIDE ? lane : QUAD ? g * 2 + t : g;
         float4 *buf = parts + (size_t)((slot * 2 + (uidx & 1u)) * (PARTS - 1)) * (pair ? 2 : 1) * REC;
-        if (part > 0 && holds) {
+        if (part > 0 && part < np && holds) {
             float4 *dst = buf + (size_t)(part - 1) * (pair ? 2 : 1) * REC;
             dst[rec] = make_float4(acc[0], acc[1], acc[2], acc[3]);
             if (pair) dst[REC + rec] = make_float4(acc2[0], acc2[1], acc2[2], acc2[3]);
         }
-        if (np > 1) named_barrier(1 + slot, 32 * np);
+        named_barrier(1 + slot, 32 * PARTS);
         if (part != 0) continue;
         if (holds)
             for (uint32_t k = 1; k < np; ++k) {
@@ -537,22 +538,33 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
             write_unit<NT>(p, unit, gr, t, acc, acc2);
         }
     }
-    if (p.nks > 1 && part == 0 && my_units) {
-        // The last block to arrive for a unit adds the slices in order. Lanes announce 32 units at a
-        // time (one round trip for all of them), then the warp finishes those it was last for.
-        __threadfence();
-        __syncwarp();
+    if (p.nks > 1 && my_units) {
+        // The last block to arrive for a unit adds the slices in order. The slot's first warp announces 32 units at a
+        // time (one round trip for all of them); the units it was last for are then finished by all the warps of the
+        // slot, one unit a warp at a time: each is a chain of dependent loads, and with eight token rows a slot has
+        // several of them (one warp alone: 4.8 us for 15 units; measured).
+        uint32_t *slot_mask = (uint32_t *)(smem + 640) + slot;  // (a free word behind the barriers)
+        if (part == 0) {
+            __threadfence();
+            __syncwarp();
+        }
         const bool holds = WIDE || (QUAD ? t < 2 : t == 0);
         const uint32_t rec = WIDE ? lane : QUAD ? g * 2 + t : g;
         for (uint32_t base = 0; base < my_units; base += 32) {
-            const uint32_t mine_u = base + lane;
-            uint32_t last = 0;
-            if (mine_u < my_units) last = atomicAdd(p.counters + item_unit(mine_u), 1u) == p.nks - 1;
-            uint32_t mask = __ballot_sync(0xffffffffu, last != 0);
-            if (mask) __threadfence();
-            while (mask) {
+            if (part == 0) {
+                const uint32_t mine_u = base + lane;
+                uint32_t last = 0;
+                if (mine_u < my_units) last = atomicAdd(p.counters + item_unit(mine_u), 1u) == p.nks - 1;
+                const uint32_t found = __ballot_sync(0xffffffffu, last != 0);
+                if (found) __threadfence();
+                if (lane == 0) *slot_mask = found;
+            }
+            named_barrier(1 + slot, 32 * PARTS);
+            uint32_t mask = *slot_mask;
+            for (uint32_t turn = 0; mask; ++turn) {
                 const uint32_t u = base + (uint32_t)__ffs((int)mask) - 1;
                 mask &= mask - 1;
+                if (turn % PARTS != part) continue;
                 const uint32_t unit = item_unit(u);
                 if (holds) {
                     const size_t per = (size_t)(pair ? 2 : 1) * REC;
@@ -578,6 +590,7 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
                 }
                 if (lane == 0) p.counters[unit] = 0;  // leave the scratch as it was found
             }
+            if (base + 32 < my_units) named_barrier(1 + slot, 32 * PARTS);  // the word is written again
         }
     }
     if (__any_sync(0xffffffffu, failed || stuck)) {
