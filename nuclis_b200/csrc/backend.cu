@@ -493,21 +493,6 @@ int Backend::matvec(const Buffer &weights, const Matrix &m, const Buffer &input,
     return cuda(cudaGetLastError(), "matvec: launch");
 }
 
-// A few token rows of an encoding that has a one-row decode kernel but no multi-row one yet:
-// one pass of the decode kernel per token row (the weights are re-read per row, still far
-// faster than the generic kernel).
-bool Backend::decodePasses(FastJob job, const float *in, size_t in_stride, float *out, size_t out_stride, uint32_t tokens) {
-    job.tokens = 1;
-    job.in = in;
-    if (!fast_supported(job)) return false;
-    for (uint32_t t = 0; t < tokens; ++t) {
-        job.in = in + (size_t)t * in_stride;
-        job.seg[0].out = out + (size_t)t * out_stride;
-        launches_ += launch_fast(stream_, job);
-    }
-    return true;
-}
-
 // ops/matvec.zig:149-165.
 int Backend::matvecRows(const Buffer &weights, const Matrix &m, const Buffer &input, size_t in_stride,
                         const Buffer &output, size_t out_stride, size_t tokens) {
@@ -530,7 +515,6 @@ int Backend::matvecRows(const Buffer &weights, const Matrix &m, const Buffer &in
     job.seg[0] = {w, stride, (uint32_t)m.rows, out, out_stride};
     job.serial = written(weights); job.partials = partials_; job.partials_floats = partials_floats_; job.counters = counters_; job.counters_len = counters_len_; job.sm_count = sm_count_;
     if (!generic_only && fast_supported(job)) launches_ += launch_fast(stream_, job);
-    else if (!generic_only && decodePasses(job, in, in_stride, out, out_stride, (uint32_t)tokens)) {}
     else launches_ += launch_matmul_generic(stream_, m.encoding, m.layout, w, stride, (uint32_t)m.rows, (uint32_t)m.columns, in, false, in_stride, out, out_stride, (uint32_t)tokens);
     wrote(output);
     opBoundary();
@@ -564,9 +548,7 @@ int Backend::matmul(const Buffer &weights, const Matrix &m, const Buffer &input,
         job.tokens = (uint32_t)(tokens < 8 ? tokens : 8);
         job.in = (const float *)in;
         job.seg[0] = {w, stride, (uint32_t)m.rows, out, out_stride};
-        if (!fast_supported(job) && tokens <= 8 && decodePasses(job, (const float *)in, in_stride, out, out_stride, (uint32_t)tokens)) {
-            done = true;
-        } else if (fast_supported(job)) {
+        if (fast_supported(job)) {
             for (size_t t0 = 0; t0 < tokens; t0 += 8) {
                 job.tokens = (uint32_t)(tokens - t0 < 8 ? tokens - t0 : 8);
                 job.in = (const float *)in + t0 * in_stride;

@@ -121,7 +121,6 @@ private:
     int runGraph(cudaGraphExec_t exec, uint32_t count, float *elapsed_ms);
     int checkKernelStatus();
     int flushPending();
-    bool decodePasses(FastJob job, const float *in, size_t in_stride, float *out, size_t out_stride, uint32_t tokens);
 
     int device_ = 0;
     int sm_count_ = 0;
