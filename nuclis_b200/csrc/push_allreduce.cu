@@ -87,31 +87,39 @@ __global__ void __launch_bounds__(256) push_allreduce_kernel(PushParams p) {
     const unsigned long long t0 = global_ns();
     bool failed = false;
     for (uint32_t i = first; i < pairs && !failed; i += step) {
+        const bool both = 2 * i + 1 < p.count;  // the last word pair of an odd count has one element
+        // all ranks' words are requested at once (eight dependent round trips to L2 would be the whole latency of the
+        // call at eight ranks); then each is polled until it carries the tag
+        uint4 w[PUSH_MAX_RANKS];
+#pragma unroll
+        for (int r = 0; r < PUSH_MAX_RANKS; ++r)
+            if ((uint32_t)r < p.ranks && !(PUSH && (uint32_t)r == p.rank))
+                w[r] = load_words((const uint4 *)(p.inbox[p.rank] + ((size_t)parity * p.ranks + r) * p.capacity) + i);
         float s0 = 0.0f, s1 = 0.0f;
-        for (uint32_t r = 0; r < p.ranks; ++r) {
+#pragma unroll
+        for (int r = 0; r < PUSH_MAX_RANKS; ++r) {
+            if ((uint32_t)r >= p.ranks || failed) continue;
             float a, b;
-            if (PUSH && r == p.rank) {
+            if (PUSH && (uint32_t)r == p.rank) {
                 a = p.buf[2 * i];
-                b = 2 * i + 1 < p.count ? p.buf[2 * i + 1] : 0.0f;
+                b = both ? p.buf[2 * i + 1] : 0.0f;
             } else {
                 const uint4 *src = (const uint4 *)(p.inbox[p.rank] + ((size_t)parity * p.ranks + r) * p.capacity) + i;
-                const bool both = 2 * i + 1 < p.count;  // the last word pair of an odd count has one element
-                uint4 w = load_words(src);
                 uint32_t n = 0;
-                while ((w.y != tag || (both && w.w != tag)) && ++n < kPushSpinLimit) {
+                while ((w[r].y != tag || (both && w[r].w != tag)) && ++n < kPushSpinLimit) {
                     if ((n & 255u) == 0 && global_ns() - t0 > p.wait_ns) break;
-                    w = load_words(src);
+                    w[r] = load_words(src);
                 }
-                if (w.y != tag || (both && w.w != tag)) { failed = true; break; }
-                a = __uint_as_float(w.x);
-                b = both ? __uint_as_float(w.z) : 0.0f;
+                if (w[r].y != tag || (both && w[r].w != tag)) { failed = true; continue; }
+                a = __uint_as_float(w[r].x);
+                b = both ? __uint_as_float(w[r].z) : 0.0f;
             }
             if (r == 0) { s0 = a; s1 = b; }
             else { s0 += a; s1 += b; }
         }
         if (!failed) {
             p.buf[2 * i] = s0;
-            if (2 * i + 1 < p.count) p.buf[2 * i + 1] = s1;
+            if (both) p.buf[2 * i + 1] = s1;
         }
     }
     if (__syncthreads_or(failed)) {
