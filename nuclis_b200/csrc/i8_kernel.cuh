@@ -9,9 +9,11 @@
 // accumulated in F32. An element of x is off by at most 2^-22 of its superblock's largest value.
 //
 // The B operand's 8 columns hold (digit plane, token): with one or two tokens one mma serves all
-// three planes (column = plane * 2 + token); with three to eight tokens each plane takes an mma of its
+// three planes (column = plane * 2 + token); with three or four tokens two mmas do (planes 0 and 1 in
+// the first, plane 2 in half of the second); with five to eight tokens each plane takes an mma of its
 // own (column = token). The k index of an mma is a column within one scale group, so the group's
-// integer scale multiplies the int32 sums after the mma (one IMAD per accumulator register).
+// scale multiplies the int32 sums after the mma (an integer scale by one IMAD per accumulator
+// register, Q8_0's f16 scale in F32).
 //
 // An encoding supplies a policy class E: the bytes of a task (16 weight rows x one superblock), the
 // copy that fetches it, and the mma loop over one task. Work split, task ring, programmatic dependent
