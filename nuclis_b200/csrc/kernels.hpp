@@ -113,6 +113,10 @@ int launch_q6k_i8(cudaStream_t s, const FastJob &job);
 bool q8_0_i8_configure();
 bool q8_0_i8_supported(const FastJob &job);
 int launch_q8_0_i8(cudaStream_t s, const FastJob &job);
+// ---- 1..8 activation rows on planar Q5_0 / Q5_1, integer tensor path (gemv_q5_i8.cu) -
+bool q5_i8_configure();
+bool q5_i8_supported(const FastJob &job);
+int launch_q5_i8(cudaStream_t s, const FastJob &job);
 // ---- a run of one-token integer-path jobs as one persistent launch (gemv_chain.cu) --
 constexpr int kChainMax = 16;
 bool chain_configure();

@@ -15,6 +15,12 @@
 //     code plane  [rows][columns] int8: the 32 codes of each block, blocks in row order
 //     scale plane [columns/32][rows] f16: the d of each block, transposed
 //
+//   Q5_0, layout 3, and Q5_1, layout 4 (rows a multiple of 16, columns a multiple of 256):
+//     main plane  [rows][superblocks of 256 columns][160]: the 16 nibble bytes of each of the eight blocks
+//                 (128 bytes), then their eight 32-bit planes of high bits (32 bytes)
+//     scale plane [superblocks][rows][8] f16: the d of the eight blocks of a row's superblock side by side;
+//                 Q5_1: [superblocks][rows][16]: the eight d, then the eight m
+//
 // Every byte is copied, none is changed: decoding the planar form gives the
 // values of the GGUF form bit for bit (dequant16_planar in nu_device.cuh).
 #include "kernels.hpp"
@@ -25,6 +31,8 @@ namespace nu {
 uint32_t prepared_layout(uint32_t enc, uint32_t rows, uint32_t columns) {
     if (enc == Q6_K && rows % 16 == 0 && columns % 256 == 0) return 1;
     if (enc == Q8_0 && rows % 16 == 0 && columns % 256 == 0) return 2;
+    if (enc == Q5_0 && rows % 16 == 0 && columns % 256 == 0) return 3;
+    if (enc == Q5_1 && rows % 16 == 0 && columns % 256 == 0) return 4;
     return 0;
 }
 
@@ -58,6 +66,26 @@ __global__ void prepare_q8_0_kernel(const uint8_t *src, uint8_t *dst, uint32_t r
     else dst[blocks * 32 + ((size_t)blk * rows + row) * 2 + b] = src[id];
 }
 
+// Q5_0 (22-byte blocks: d, 4 bytes of high bits, 16 nibble bytes) and Q5_1 (24: d, m, high bits, nibbles).
+__global__ void prepare_q5_kernel(const uint8_t *src, uint8_t *dst, uint32_t rows, uint32_t ksb, uint32_t block_bytes) {
+    const size_t blocks = (size_t)rows * ksb * 8;
+    const size_t id = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (id >= blocks * block_bytes) return;
+    const size_t block = id / block_bytes;
+    const uint32_t b = (uint32_t)(id % block_bytes), head = block_bytes - 20;  // 2 or 4 bytes of scales
+    const uint32_t row = (uint32_t)(block / (ksb * 8)), kb = (uint32_t)(block % (ksb * 8)), sb = kb / 8, c = kb % 8;
+    uint8_t *rec = dst + ((size_t)row * ksb + sb) * 160;
+    if (b >= head + 4) {
+        rec[c * 16 + (b - head - 4)] = src[id];
+    } else if (b >= head) {
+        rec[128 + c * 4 + (b - head)] = src[id];
+    } else {
+        // d: bytes 0, 1; m (Q5_1): bytes 2, 3
+        uint8_t *sc = dst + (size_t)rows * ksb * 160 + ((size_t)sb * rows + row) * (head * 8);
+        sc[(b / 2) * 16 + c * 2 + (b & 1)] = src[id];
+    }
+}
+
 __global__ void copy_bytes_kernel(const uint8_t *src, uint8_t *dst, size_t n) {
     const size_t id = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (id < n) dst[id] = src[id];
@@ -71,6 +99,8 @@ int launch_prepare(cudaStream_t s, uint32_t enc, const uint8_t *src, uint8_t *ds
         prepare_q6k_kernel<<<(unsigned)((bytes + 255) / 256), 256, 0, s>>>(src, dst, rows, columns / 256);
     } else if (to == 2) {
         prepare_q8_0_kernel<<<(unsigned)((bytes + 255) / 256), 256, 0, s>>>(src, dst, rows, columns / 32);
+    } else if (to == 3 || to == 4) {
+        prepare_q5_kernel<<<(unsigned)((bytes + 255) / 256), 256, 0, s>>>(src, dst, rows, columns / 256, (uint32_t)l.bytes);
     } else {
         copy_bytes_kernel<<<(unsigned)((bytes + 255) / 256), 256, 0, s>>>(src, dst, bytes);
     }

@@ -259,10 +259,11 @@ def test_wrap_caches_by_address_and_ids_are_not_reused(backend):
 
 # ---- the planar form of nu_cuda_matrix_prepare (Q6_K) ---------------------------------------------
 
-PLANAR = {enc.Q6_K: 1, enc.Q8_0: 2}
+PLANAR = {enc.Q6_K: 1, enc.Q8_0: 2, enc.Q5_0: 3, enc.Q5_1: 4}
+PREPARED = [enc.Q6_K, enc.Q8_0, enc.Q5_0, enc.Q5_1]
 
 
-@pytest.mark.parametrize("encoding", [enc.Q6_K, enc.Q8_0])
+@pytest.mark.parametrize("encoding", PREPARED)
 def test_prepared_form_decodes_bit_for_bit(backend, golden_rows, encoding):
     # golden blocks tiled into 16 rows, then random rows: every row of the prepared form decodes to
     # the bits the CPU decoder gives for the GGUF form
@@ -285,7 +286,7 @@ def test_prepared_form_decodes_bit_for_bit(backend, golden_rows, encoding):
         backend.release(out)
 
 
-@pytest.mark.parametrize("encoding", [enc.Q6_K, enc.Q8_0])
+@pytest.mark.parametrize("encoding", PREPARED)
 @pytest.mark.parametrize("shape", [(80, 1280), (4096, 4096), (17408, 5120), (5120, 17408)])
 @pytest.mark.parametrize("generic", [False, True])
 def test_prepared_matvec_matches_oracle(backend, encoding, shape, generic):
@@ -334,8 +335,8 @@ def test_prepare_contract(backend):
     backend.unwrap(w4)
 
 
-@pytest.mark.parametrize("encoding", [enc.Q6_K, enc.Q8_0])
-@pytest.mark.parametrize("tokens", [2, 8])
+@pytest.mark.parametrize("encoding", PREPARED)
+@pytest.mark.parametrize("tokens", [2, 3, 8])
 def test_prepared_matvec_rows_match_oracle(backend, encoding, tokens):
     rows, columns = 1056, 2304
     w, x, m = make_case(encoding, rows, columns, tokens, seed=91 + tokens)
