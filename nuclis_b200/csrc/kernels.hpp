@@ -113,10 +113,15 @@ int launch_q6k_i8(cudaStream_t s, const FastJob &job);
 bool q8_0_i8_configure();
 bool q8_0_i8_supported(const FastJob &job);
 int launch_q8_0_i8(cudaStream_t s, const FastJob &job);
-// ---- 1..8 activation rows on planar Q5_0 / Q5_1, integer tensor path (gemv_q5_i8.cu) -
-bool q5_i8_configure();
-bool q5_i8_supported(const FastJob &job);
-int launch_q5_i8(cudaStream_t s, const FastJob &job);
+// ---- 1..8 activation rows on planar Q5_0 / Q5_1 / Q4_0 / IQ4_NL, integer tensor path (gemv_block32_i8.cu) -
+bool block32_i8_configure();
+bool block32_i8_supported(const FastJob &job);
+int launch_block32_i8(cudaStream_t s, const FastJob &job);
+
+// ---- 1..8 activation rows on Q5_K, integer tensor path (gemv_q5k_i8.cu) ------------
+bool q5k_i8_configure();
+bool q5k_i8_supported(const FastJob &job);
+int launch_q5k_i8(cudaStream_t s, const FastJob &job);
 // ---- a run of one-token integer-path jobs as one persistent launch (gemv_chain.cu) --
 constexpr int kChainMax = 16;
 bool chain_configure();

@@ -42,7 +42,7 @@ __device__ __forceinline__ void decode16(uint32_t enc, uint32_t layout, const ui
                                          uint32_t seg, float v[16]) {
     if (layout == 1) dequant16_planar_q6k(w, rows, columns / 256, r, seg, v);
     else if (layout == 2) dequant16_planar_q8_0(w, rows, columns, r, seg, v);
-    else if (layout == 3 || layout == 4) dequant16_planar_q5(layout == 4, w, rows, columns / 256, r, seg, v);
+    else if (layout >= 3 && layout <= 5) dequant16_planar_block32(enc, w, rows, columns / 256, r, seg, v);
     else dequant16(enc, w + (size_t)r * stride, seg, v);
 }
 

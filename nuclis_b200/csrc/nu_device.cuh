@@ -234,18 +234,24 @@ __device__ __forceinline__ void dequant16_planar_q8_0(const uint8_t *base, uint3
     for (int i = 0; i < 16; ++i) out[i] = __fmul_rn(d, (float)(int8_t)q[i]);
 }
 
-// The same from the planar form of a Q5_0 (offset false) or Q5_1 matrix (prepare.cu): 16 values are one half of a block.
-__device__ __forceinline__ void dequant16_planar_q5(bool offset, const uint8_t *base, uint32_t rows, uint32_t ksb, uint32_t row, uint32_t seg, float out[16]) {
+// The same from the planar form of a Q5_0, Q5_1, Q4_0 or IQ4_NL matrix (prepare.cu): 16 values are one half of a block.
+__device__ __forceinline__ void dequant16_planar_block32(uint32_t enc, const uint8_t *base, uint32_t rows, uint32_t ksb, uint32_t row, uint32_t seg, float out[16]) {
+    const bool offset = enc == Q5_1, fifth = enc == Q5_0 || enc == Q5_1;
+    const uint32_t record = fifth ? 160 : 128;
     const uint32_t sb = seg / 16, c = (seg % 16) / 2, hi = seg % 2;
-    const uint8_t *rec = base + ((size_t)row * ksb + sb) * 160;
-    const uint8_t *sc = base + (size_t)rows * ksb * 160 + ((size_t)sb * rows + row) * (offset ? 32 : 16);
+    const uint8_t *rec = base + ((size_t)row * ksb + sb) * record;
+    const uint8_t *sc = base + (size_t)rows * ksb * record + ((size_t)sb * rows + row) * (offset ? 32 : 16);
     const float d = half_at(sc + c * 2), m = offset ? half_at(sc + 16 + c * 2) : 0.0f;
-    const uint8_t *plane = rec + 128 + c * 4;
-    const uint32_t qh = (uint32_t)plane[0] | ((uint32_t)plane[1] << 8) | ((uint32_t)plane[2] << 16) | ((uint32_t)plane[3] << 24);
+    uint32_t qh = 0;
+    if (fifth) {
+        const uint8_t *plane = rec + 128 + c * 4;
+        qh = (uint32_t)plane[0] | ((uint32_t)plane[1] << 8) | ((uint32_t)plane[2] << 16) | ((uint32_t)plane[3] << 24);
+    }
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-        const int q = (int)(((rec[c * 16 + i] >> (hi * 4)) & 15u) | (((qh >> (i + hi * 16)) & 1u) << 4));
-        out[i] = offset ? __fadd_rn(__fmul_rn(d, (float)q), m) : __fmul_rn(d, (float)(q - 16));
+        const uint32_t code = (rec[c * 16 + i] >> (hi * 4)) & 15u;
+        const int q = (int)(code | (((qh >> (i + hi * 16)) & 1u) << 4));
+        out[i] = enc == IQ4_NL ? __fmul_rn(d, (float)iq4_value(code)) : enc == Q4_0 ? __fmul_rn(d, (float)(q - 8)) : offset ? __fadd_rn(__fmul_rn(d, (float)q), m) : __fmul_rn(d, (float)(q - 16));
     }
 }
 

@@ -135,7 +135,7 @@ __device__ __forceinline__ void decode16_generic(const Params &p, const uint8_t 
     const uint32_t seg = k0 / 16 + q;
     if (p.layout == 1) dequant16_planar_q6k(w, p.rows, p.columns / 256, r, seg, v);
     else if (p.layout == 2) dequant16_planar_q8_0(w, p.rows, p.columns, r, seg, v);
-    else if (p.layout == 3 || p.layout == 4) dequant16_planar_q5(p.layout == 4, w, p.rows, p.columns / 256, r, seg, v);
+    else if (p.layout >= 3 && p.layout <= 5) dequant16_planar_block32(p.enc, w, p.rows, p.columns / 256, r, seg, v);
     else dequant16(p.enc, w + (size_t)r * p.stride, seg, v);
 #pragma unroll
     for (int c = 0; c < 2; ++c)

@@ -21,6 +21,10 @@
 //     scale plane [superblocks][rows][8] f16: the d of the eight blocks of a row's superblock side by side;
 //                 Q5_1: [superblocks][rows][16]: the eight d, then the eight m
 //
+//   Q4_0 and IQ4_NL, layout 5 (18-byte blocks: d, 16 nibble bytes; the same conditions):
+//     main plane  [rows][superblocks][128]: the 16 nibble bytes of each of the eight blocks
+//     scale plane [superblocks][rows][8] f16
+//
 // Every byte is copied, none is changed: decoding the planar form gives the
 // values of the GGUF form bit for bit (dequant16_planar in nu_device.cuh).
 #include "kernels.hpp"
@@ -33,6 +37,7 @@ uint32_t prepared_layout(uint32_t enc, uint32_t rows, uint32_t columns) {
     if (enc == Q8_0 && rows % 16 == 0 && columns % 256 == 0) return 2;
     if (enc == Q5_0 && rows % 16 == 0 && columns % 256 == 0) return 3;
     if (enc == Q5_1 && rows % 16 == 0 && columns % 256 == 0) return 4;
+    if ((enc == Q4_0 || enc == IQ4_NL) && rows % 16 == 0 && columns % 256 == 0) return 5;
     return 0;
 }
 
@@ -66,22 +71,24 @@ __global__ void prepare_q8_0_kernel(const uint8_t *src, uint8_t *dst, uint32_t r
     else dst[blocks * 32 + ((size_t)blk * rows + row) * 2 + b] = src[id];
 }
 
-// Q5_0 (22-byte blocks: d, 4 bytes of high bits, 16 nibble bytes) and Q5_1 (24: d, m, high bits, nibbles).
-__global__ void prepare_q5_kernel(const uint8_t *src, uint8_t *dst, uint32_t rows, uint32_t ksb, uint32_t block_bytes) {
+// Q5_0 (22-byte blocks: d, 4 bytes of high bits, 16 nibble bytes), Q5_1 (24: d, m, high bits, nibbles) and
+// Q4_0 / IQ4_NL (18: d, nibbles). head: the bytes of scales a block starts with; high: its bytes of high bits (4 or 0).
+__global__ void prepare_block32_kernel(const uint8_t *src, uint8_t *dst, uint32_t rows, uint32_t ksb, uint32_t head, uint32_t high) {
+    const uint32_t block_bytes = head + high + 16, record = 128 + 8 * high;
     const size_t blocks = (size_t)rows * ksb * 8;
     const size_t id = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (id >= blocks * block_bytes) return;
     const size_t block = id / block_bytes;
-    const uint32_t b = (uint32_t)(id % block_bytes), head = block_bytes - 20;  // 2 or 4 bytes of scales
+    const uint32_t b = (uint32_t)(id % block_bytes);
     const uint32_t row = (uint32_t)(block / (ksb * 8)), kb = (uint32_t)(block % (ksb * 8)), sb = kb / 8, c = kb % 8;
-    uint8_t *rec = dst + ((size_t)row * ksb + sb) * 160;
-    if (b >= head + 4) {
-        rec[c * 16 + (b - head - 4)] = src[id];
+    uint8_t *rec = dst + ((size_t)row * ksb + sb) * record;
+    if (b >= head + high) {
+        rec[c * 16 + (b - head - high)] = src[id];
     } else if (b >= head) {
         rec[128 + c * 4 + (b - head)] = src[id];
     } else {
         // d: bytes 0, 1; m (Q5_1): bytes 2, 3
-        uint8_t *sc = dst + (size_t)rows * ksb * 160 + ((size_t)sb * rows + row) * (head * 8);
+        uint8_t *sc = dst + (size_t)rows * ksb * record + ((size_t)sb * rows + row) * (head * 8);
         sc[(b / 2) * 16 + c * 2 + (b & 1)] = src[id];
     }
 }
@@ -99,8 +106,9 @@ int launch_prepare(cudaStream_t s, uint32_t enc, const uint8_t *src, uint8_t *ds
         prepare_q6k_kernel<<<(unsigned)((bytes + 255) / 256), 256, 0, s>>>(src, dst, rows, columns / 256);
     } else if (to == 2) {
         prepare_q8_0_kernel<<<(unsigned)((bytes + 255) / 256), 256, 0, s>>>(src, dst, rows, columns / 32);
-    } else if (to == 3 || to == 4) {
-        prepare_q5_kernel<<<(unsigned)((bytes + 255) / 256), 256, 0, s>>>(src, dst, rows, columns / 256, (uint32_t)l.bytes);
+    } else if (to == 3 || to == 4 || to == 5) {
+        const uint32_t high = to == 5 ? 0u : 4u;
+        prepare_block32_kernel<<<(unsigned)((bytes + 255) / 256), 256, 0, s>>>(src, dst, rows, columns / 256, (uint32_t)l.bytes - 16u - high, high);
     } else {
         copy_bytes_kernel<<<(unsigned)((bytes + 255) / 256), 256, 0, s>>>(src, dst, bytes);
     }
