@@ -1,9 +1,9 @@
 // GEMV and small-batch GEMM (1..8 activation rows) for sm_100a on the integer tensor path for the encodings made
-// of 32-element blocks under an f16 scale: Q5_0, Q5_1, Q4_0 and IQ4_NL, reading the planar forms that
-// launch_prepare writes at load time (prepare.cu: GGUF blocks of 18, 22 and 24 bytes start on 2-byte boundaries).
+// of 32-element blocks under an f16 scale (Q5_0, Q5_1, Q4_0, IQ4_NL) and IQ4_XS, reading the planar forms that
+// launch_prepare writes at load time (prepare.cu: GGUF blocks of 18, 22 and 24 bytes start on 2-byte boundaries, IQ4_XS superblocks of 136 on 8-byte ones).
 // The kernel behind Backend.matvec, matvecRows, small matmul and matvecSegments on prepared weights of these
 // encodings; the reference runs them on its generic nu_matvec
-// (inference/src/backends/metal/kernels/matvec.metal:5-21; decoders inference/src/quant/decode.zig:46-53, 73-81, 125-143).
+// (inference/src/backends/metal/kernels/matvec.metal:5-21; decoders inference/src/quant/decode.zig:46-53, 73-81, 125-143, 214-228).
 // The scheme is that of i8_kernel.cuh and gemv_q4k_i8.cu; i8_block32.cuh says what these encodings change: codes
 // assembled as bytes (nibble | fifth bit << 4, or the IQ4_NL table value) on m16n8k32, f16 block scales applied in
 // F32, the offset (-16 d, -8 d, or m) through the group sums of X.
@@ -39,6 +39,7 @@ static int kind_of(const FastJob &job) {
     if (job.enc == Q5_1 && job.layout == 4) return KIND_Q5_1;
     if (job.enc == Q4_0 && job.layout == 5) return KIND_Q4_0;
     if (job.enc == IQ4_NL && job.layout == 5) return KIND_IQ4_NL;
+    if (job.enc == IQ4_XS && job.layout == 6) return KIND_IQ4_XS;
     return -1;
 }
 
@@ -48,6 +49,7 @@ static bool fill(const FastJob &job, Params &p, Plan &plan, bool maps) {
     case KIND_Q5_1: return fill_kind<KIND_Q5_1>(job, p, plan, maps);
     case KIND_Q4_0: return fill_kind<KIND_Q4_0>(job, p, plan, maps);
     case KIND_IQ4_NL: return fill_kind<KIND_IQ4_NL>(job, p, plan, maps);
+    case KIND_IQ4_XS: return fill_kind<KIND_IQ4_XS>(job, p, plan, maps);
     default: return false;
     }
 }
@@ -67,7 +69,8 @@ static bool configure_kind() {
 }  // namespace i8
 
 bool block32_i8_configure() {
-    return i8::configure_kind<i8::KIND_Q5_0>() && i8::configure_kind<i8::KIND_Q5_1>() && i8::configure_kind<i8::KIND_Q4_0>() && i8::configure_kind<i8::KIND_IQ4_NL>();
+    return i8::configure_kind<i8::KIND_Q5_0>() && i8::configure_kind<i8::KIND_Q5_1>() && i8::configure_kind<i8::KIND_Q4_0>() && i8::configure_kind<i8::KIND_IQ4_NL>() &&
+           i8::configure_kind<i8::KIND_IQ4_XS>();
 }
 
 bool block32_i8_supported(const FastJob &job) {
@@ -84,7 +87,8 @@ int launch_block32_i8(cudaStream_t s, const FastJob &job) {
     case i8::KIND_Q5_0: return i8::launch_kind<i8::KIND_Q5_0>(s, job, p, plan);
     case i8::KIND_Q5_1: return i8::launch_kind<i8::KIND_Q5_1>(s, job, p, plan);
     case i8::KIND_Q4_0: return i8::launch_kind<i8::KIND_Q4_0>(s, job, p, plan);
-    default: return i8::launch_kind<i8::KIND_IQ4_NL>(s, job, p, plan);
+    case i8::KIND_IQ4_NL: return i8::launch_kind<i8::KIND_IQ4_NL>(s, job, p, plan);
+    default: return i8::launch_kind<i8::KIND_IQ4_XS>(s, job, p, plan);
     }
 }
 

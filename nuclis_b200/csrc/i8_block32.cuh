@@ -1,5 +1,6 @@
 // The policy of the integer-path skeleton (i8_kernel.cuh) for the planar forms of the encodings made of 32-element
-// blocks under an f16 scale: Q5_0, Q5_1, Q4_0 and IQ4_NL. The bytes of a task, the copies that fetch a stage, and the
+// blocks under an f16 scale: Q5_0, Q5_1, Q4_0 and IQ4_NL, and for IQ4_XS (IQ4_NL's codes, eight blocks under one f16
+// scale and eight six-bit ones). The bytes of a task, the copies that fetch a stage, and the
 // mma loop over one task. gemv_block32_i8.cu has the scheme and the host side.
 #pragma once
 #include "i8_kernel.cuh"
@@ -27,14 +28,26 @@ __device__ __forceinline__ uint32_t iq4_lookup(uint32_t n) {
     return (lo & ~upper) | (hi & upper);
 }
 
-enum Block32Kind : int { KIND_Q5_0 = 0, KIND_Q5_1 = 1, KIND_Q4_0 = 2, KIND_IQ4_NL = 3 };
+// The eight six-bit scales of an IQ4_XS superblock row (decode.zig:214-228: block g has four bits in nibble g of the
+// header's second word and two bits at 2g of the first word's upper half) as bytes: blocks 0, 2, 4, 6 in even,
+// 1, 3, 5, 7 in odd.
+__device__ __forceinline__ void xs_scales(const uint2 &hdr, uint32_t &even, uint32_t &odd) {
+    uint32_t h = hdr.x >> 16;                // nibble k: the top bits of blocks 2k (low pair) and 2k + 1 (high pair)
+    h = (h | (h << 8)) & 0x00ff00ffu;
+    h = (h | (h << 4)) & 0x0f0f0f0fu;        // nibble k now in byte k
+    even = (hdr.y & 0x0f0f0f0fu) | ((h & 0x03030303u) << 4);
+    odd = ((hdr.y >> 4) & 0x0f0f0f0fu) | ((h & 0x0c0c0c0cu) << 2);
+}
 
-// Q5_1: value = d * q + m; Q5_0: d * (q - 16); Q4_0: d * (q - 8); IQ4_NL: d * table[q].
+enum Block32Kind : int { KIND_Q5_0 = 0, KIND_Q5_1 = 1, KIND_Q4_0 = 2, KIND_IQ4_NL = 3, KIND_IQ4_XS = 4 };
+
+// Q5_1: value = d * q + m; Q5_0: d * (q - 16); Q4_0: d * (q - 8); IQ4_NL: d * table[q]; IQ4_XS: d * (s - 32) * table[q].
 template <int KIND>
 struct Block32 {
     static constexpr bool FIFTH = KIND == KIND_Q5_0 || KIND == KIND_Q5_1;   // a plane of fifth bits follows the nibbles
     static constexpr bool OFFSET = KIND == KIND_Q5_1;
-    static constexpr bool TABLE = KIND == KIND_IQ4_NL;
+    static constexpr bool TABLE = KIND == KIND_IQ4_NL || KIND == KIND_IQ4_XS;
+    static constexpr bool SUPER = KIND == KIND_IQ4_XS;       // the header of a superblock row: d, two bits of each scale, four bits of each
     static constexpr int ROW_BYTES = FIFTH ? 160 : 128;      // one planar record: 8 x 16 nibble bytes (then 8 x 4 bytes of high bits)
     static constexpr int STAGE_SBS = 2;
     static constexpr int ROW_PITCH = STAGE_SBS * ROW_BYTES + 16;  // 336 (272) bytes = 84 (68) words: the eight rows a warp's 4-byte
@@ -42,7 +55,7 @@ struct Block32 {
                                                              // (320 or 256 would put them 16 or 0 apart). The 16 bytes more are the
                                                              // row's next bytes.
     static constexpr int MAIN_BYTES = 16 * ROW_PITCH;        // 5,376 = 42 x 128 (4,352 = 34 x 128)
-    static constexpr int SC_ROW = OFFSET ? 32 : 16;          // scale bytes per row and superblock: eight d (and eight m)
+    static constexpr int SC_ROW = OFFSET ? 32 : SUPER ? 8 : 16;  // scale bytes per row and superblock: eight d (and eight m); the IQ4_XS header
     static constexpr int STAGE_BYTES = MAIN_BYTES + STAGE_SBS * 16 * SC_ROW;
     static constexpr int GROUP = 32;                         // one block
     static constexpr bool GROUP_SUMS = !TABLE;               // the offset (16 d, 8 d, or m) meets the sums of X over the blocks
@@ -76,6 +89,13 @@ struct Block32 {
         constexpr int STEP = NT == 1 ? 2 : 1;
         const uint8_t *r0 = stage + gr * ROW_PITCH + part * ROW_BYTES, *r1 = r0 + 8 * ROW_PITCH;
         const uint8_t *sc0 = stage + MAIN_BYTES + (part * 16 + gr) * SC_ROW, *sc1 = sc0 + 8 * SC_ROW;
+        uint2 hd0 = make_uint2(0u, 0u), hd1 = hd0;
+        uint32_t se0 = 0, so0 = 0, se1 = 0, so1 = 0;  // the six-bit scales of the even and of the odd blocks, a byte each
+        if (SUPER) {
+            hd0 = *(const uint2 *)sc0, hd1 = *(const uint2 *)sc1;
+            xs_scales(hd0, se0, so0);
+            xs_scales(hd1, se1, so1);
+        }
         float f[NC][4];
 #pragma unroll
         for (int j = 0; j < NC; ++j)
@@ -94,7 +114,14 @@ struct Block32 {
                 const uint32_t h0 = *(const uint32_t *)(r0 + 128 + c * 4) >> (4 * t), h1 = *(const uint32_t *)(r1 + 128 + c * 4) >> (4 * t);
                 a[0] |= spread4(h0 & 15u), a[1] |= spread4(h1 & 15u), a[2] |= spread4((h0 >> 16) & 15u), a[3] |= spread4((h1 >> 16) & 15u);
             }
-            const float d0 = __half2float(*(const __half *)(sc0 + c * 2)), d1 = __half2float(*(const __half *)(sc1 + c * 2));
+            float d0, d1;
+            if (SUPER) {
+                // byte c / 2 of the even or odd scales as a float through the 2^23 magic number, minus 32
+                d0 = __uint_as_float(prmt((c & 1) ? so0 : se0, 0x4b000000u, 0x7650u + c / 2)) - 8388640.0f;
+                d1 = __uint_as_float(prmt((c & 1) ? so1 : se1, 0x4b000000u, 0x7650u + c / 2)) - 8388640.0f;
+            } else {
+                d0 = __half2float(*(const __half *)(sc0 + c * 2)), d1 = __half2float(*(const __half *)(sc1 + c * 2));
+            }
 #pragma unroll
             for (int j = 0; j < NC; ++j) {
                 const uint32_t b0 = *(const uint32_t *)(xb + j * bstep + c * 32), b1 = *(const uint32_t *)(xb + j * bstep + c * 32 + 16);
@@ -120,6 +147,7 @@ struct Block32 {
 #pragma unroll
             for (int j = 1; j < NC; ++j) v = fmaf(f[j][i], wl[j], v);
             const float ivi = (i & 1) ? iv1 : iv0;
+            if (SUPER) v *= __half2float(__ushort_as_half((unsigned short)((i < 2 ? hd0.x : hd1.x) & 0xffffu)));
             acc[i] = fmaf(v, ivi, acc[i]);
             if (GROUP_SUMS) acc[i] = fmaf(cm[i], OFF * ivi, acc[i]);
         }

@@ -255,6 +255,19 @@ __device__ __forceinline__ void dequant16_planar_block32(uint32_t enc, const uin
     }
 }
 
+// The same from the planar form of an IQ4_XS matrix (prepare.cu).
+__device__ __forceinline__ void dequant16_planar_iq4_xs(const uint8_t *base, uint32_t rows, uint32_t ksb, uint32_t row, uint32_t seg, float out[16]) {
+    const uint32_t sb = seg / 16, g = (seg % 16) / 2, hi = seg % 2;
+    const uint8_t *q = base + ((size_t)row * ksb + sb) * 128 + g * 16;
+    const uint8_t *hdr = base + (size_t)rows * ksb * 128 + ((size_t)sb * rows + row) * 8;
+    const uint32_t high = (uint32_t)hdr[2] | ((uint32_t)hdr[3] << 8);
+    const uint32_t low = (hdr[4 + g / 2] >> (4 * (g % 2))) & 15u;
+    const int scale = (int)(low | (((high >> (2 * g)) & 3u) << 4)) - 32;
+    const float multiplier = __fmul_rn(half_at(hdr), (float)scale);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) out[i] = __fmul_rn(multiplier, (float)iq4_value((q[i] >> (hi * 4)) & 15u));
+}
+
 // F32 forms of the activations, as the reference's GPU kernels compute them
 // (inference/src/backends/metal/kernels/common.metal:6-16).
 __device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + expf(-x)); }

@@ -136,6 +136,7 @@ __device__ __forceinline__ void decode16_generic(const Params &p, const uint8_t 
     if (p.layout == 1) dequant16_planar_q6k(w, p.rows, p.columns / 256, r, seg, v);
     else if (p.layout == 2) dequant16_planar_q8_0(w, p.rows, p.columns, r, seg, v);
     else if (p.layout >= 3 && p.layout <= 5) dequant16_planar_block32(p.enc, w, p.rows, p.columns / 256, r, seg, v);
+    else if (p.layout == 6) dequant16_planar_iq4_xs(w, p.rows, p.columns / 256, r, seg, v);
     else dequant16(p.enc, w + (size_t)r * p.stride, seg, v);
 #pragma unroll
     for (int c = 0; c < 2; ++c)

@@ -25,6 +25,10 @@
 //     main plane  [rows][superblocks][128]: the 16 nibble bytes of each of the eight blocks
 //     scale plane [superblocks][rows][8] f16
 //
+//   IQ4_XS, layout 6 (136-byte superblocks: d, 16 bits and 4 bytes of scales, 128 nibble bytes; the same conditions):
+//     main plane  [rows][superblocks][128]: the nibble bytes
+//     header plane [superblocks][rows][8]: the first eight bytes of each superblock
+//
 // Every byte is copied, none is changed: decoding the planar form gives the
 // values of the GGUF form bit for bit (dequant16_planar in nu_device.cuh).
 #include "kernels.hpp"
@@ -38,6 +42,7 @@ uint32_t prepared_layout(uint32_t enc, uint32_t rows, uint32_t columns) {
     if (enc == Q5_0 && rows % 16 == 0 && columns % 256 == 0) return 3;
     if (enc == Q5_1 && rows % 16 == 0 && columns % 256 == 0) return 4;
     if ((enc == Q4_0 || enc == IQ4_NL) && rows % 16 == 0 && columns % 256 == 0) return 5;
+    if (enc == IQ4_XS && rows % 16 == 0 && columns % 256 == 0) return 6;
     return 0;
 }
 
@@ -93,6 +98,17 @@ __global__ void prepare_block32_kernel(const uint8_t *src, uint8_t *dst, uint32_
     }
 }
 
+__global__ void prepare_iq4_xs_kernel(const uint8_t *src, uint8_t *dst, uint32_t rows, uint32_t ksb) {
+    const size_t blocks = (size_t)rows * ksb;
+    const size_t id = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (id >= blocks * 136) return;
+    const size_t block = id / 136;
+    const uint32_t b = (uint32_t)(id % 136);
+    const uint32_t row = (uint32_t)(block / ksb), sb = (uint32_t)(block % ksb);
+    if (b >= 8) dst[block * 128 + (b - 8)] = src[id];
+    else dst[blocks * 128 + ((size_t)sb * rows + row) * 8 + b] = src[id];
+}
+
 __global__ void copy_bytes_kernel(const uint8_t *src, uint8_t *dst, size_t n) {
     const size_t id = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (id < n) dst[id] = src[id];
@@ -109,6 +125,8 @@ int launch_prepare(cudaStream_t s, uint32_t enc, const uint8_t *src, uint8_t *ds
     } else if (to == 3 || to == 4 || to == 5) {
         const uint32_t high = to == 5 ? 0u : 4u;
         prepare_block32_kernel<<<(unsigned)((bytes + 255) / 256), 256, 0, s>>>(src, dst, rows, columns / 256, (uint32_t)l.bytes - 16u - high, high);
+    } else if (to == 6) {
+        prepare_iq4_xs_kernel<<<(unsigned)((bytes + 255) / 256), 256, 0, s>>>(src, dst, rows, columns / 256);
     } else {
         copy_bytes_kernel<<<(unsigned)((bytes + 255) / 256), 256, 0, s>>>(src, dst, bytes);
     }
