@@ -57,7 +57,7 @@ typedef enum nu_status {
 } nu_status;
 
 /* GGML encoding ids served (inference/src/tensor/encoding.zig:29-56). */
-enum { NU_F32 = 0, NU_F16 = 1, NU_Q4_0 = 2, NU_Q5_0 = 6, NU_Q5_1 = 7, NU_Q8_0 = 8, NU_Q2_K = 10, NU_Q3_K = 11, NU_Q4_K = 12, NU_Q5_K = 13, NU_Q6_K = 14, NU_BF16 = 30 };
+enum { NU_F32 = 0, NU_F16 = 1, NU_Q4_0 = 2, NU_Q5_0 = 6, NU_Q5_1 = 7, NU_Q8_0 = 8, NU_Q2_K = 10, NU_Q3_K = 11, NU_Q4_K = 12, NU_Q5_K = 13, NU_Q6_K = 14, NU_IQ4_NL = 20, NU_IQ4_XS = 23, NU_BF16 = 30 };
 
 /* `Buffer` of backends/metal/root.zig:62-86 without the host pointer: device
  * memory is not host-addressable here; use upload/download. */
@@ -151,7 +151,8 @@ uint64_t nu_cuda_created_bytes(const nu_cuda *h);
 /* Re-lays a matrix once, at load time, into the form the specialized kernels read
  * (no reference analogue; the reference wraps the file bytes as they are,
  * root.zig:217-230). GGUF rows of some encodings start on 2-byte boundaries
- * (Q6_K blocks are 210 bytes, Q8_0 blocks 34, Q5_0 22, Q5_1 24), which no vector load or bulk copy can address;
+ * (Q6_K blocks are 210 bytes, Q8_0 blocks 34, Q4_0 and IQ4_NL 18, Q5_0 22, Q5_1 24; IQ4_XS superblocks, 136 bytes,
+ * on 8-byte ones), which no vector load or bulk copy can address;
  * the prepared form holds the same bytes in 16-byte aligned planes and decodes
  * to the same values bit for bit. `prepared` must be as long as the matrix and
  * must not overlap it; `layout` receives the value to put in `nu_matrix.layout`
