@@ -197,11 +197,11 @@ def run_reference(args, rank: int, world: int):
 # ---- one operator alone, through the C ABI, device-timed over distinct weights ----------------------
 
 ALGO_BPW = {12: 0.5625, 14: 0.8203125, 8: 1.0625}
-ENC_NAME = {12: "q4_k", 14: "q6_k", 8: "q8_0"}
+ENC_NAME = {12: "q4_k", 14: "q6_k", 8: "q8_0", 13: "q5_k", 2: "q4_0", 6: "q5_0", 7: "q5_1", 20: "iq4_nl", 23: "iq4_xs"}
 
 
 def device_matrices(b, encoding: int, rows: int, columns: int, copies: int, seed: int, prepare: bool):
-    """`copies` distinct random matrices drawn on the device; Q6_K / Q8_0 in the prepared planar form when `prepare`."""
+    """`copies` distinct random matrices drawn on the device; the encodings that have a prepared planar form in it when `prepare`."""
     import torch
     from nuclis_b200 import Matrix, encoding as enc, synth
     from nuclis_b200.stack import device_tensor
@@ -213,7 +213,7 @@ def device_matrices(b, encoding: int, rows: int, columns: int, copies: int, seed
         synth.fill_matrix_torch(device_tensor(wb), encoding, rows, columns, seed * 1000 + i)
         torch.cuda.synchronize()
         mm = m
-        if prepare and encoding in (enc.Q6_K, enc.Q8_0):
+        if prepare and encoding in (enc.Q6_K, enc.Q8_0, enc.Q4_0, enc.Q5_0, enc.Q5_1, enc.IQ4_NL, enc.IQ4_XS):
             pb, mm = b.prepare(wb, m)
             b.release(wb)
             wb = pb
@@ -487,7 +487,15 @@ def other_configs(b, args, stack8_value=None) -> dict:
             cpu_us, cores = cpu_gemv_sample(e, rows, columns)
             row["cpu_baseline"] = {"us_m1": cpu_us, "cores": cores, "kind": "port"}
             sweep[f"{ENC_NAME[e]}_{rows}x{columns}"] = row
-    out["config1"] = {"workload": "dequant-fused GEMV / small-M GEMM sweep (Q6_K and Q8_0 in the prepared planar form)", "peak_gbs": peaks["hbm_gbs"],
+    # the other encodings of the integer path: one shape, one and eight tokens
+    for e in (enc.Q5_K, enc.Q4_0, enc.Q5_0, enc.Q5_1, enc.IQ4_NL, enc.IQ4_XS):
+        row = {}
+        for m in (1, 8):
+            us, algo, copies = time_gemv(b, e, 17408, 5120, m)
+            row[f"m{m}"] = {"us": us, "gbs": algo / us / 1e3, "frac": algo / us / 1e3 / peaks["hbm_gbs"]}
+        row["m8_over_m1"] = row["m8"]["us"] / row["m1"]["us"]
+        sweep[f"{ENC_NAME[e]}_17408x5120"] = row
+    out["config1"] = {"workload": "dequant-fused GEMV / small-M GEMM sweep (all but Q4_K and Q5_K in the prepared planar form)", "peak_gbs": peaks["hbm_gbs"],
                       "peak_source": kind, "cases": sweep}
     if stack8_value is not None:
         out["config2_m8"] = stack8_value

@@ -171,5 +171,13 @@ def fill_matrix_torch(dst, encoding: int, rows: int, columns: int, seed: int) ->
         codes = torch.randint(-127, 128, (blocks, 32), device=dst.device, generator=gen, dtype=torch.int8)
         view[:, 2:34] = codes.view(torch.uint8)
         view[:, 0:2] = scales(blocks, 2e-3)
+    elif encoding == enc.Q5_K:
+        view[:, 0:2] = scales(blocks, 1e-3)
+        view[:, 2:4] = scales(blocks, 5e-4)
+    elif encoding in (enc.Q4_0, enc.Q5_0, enc.IQ4_NL, enc.IQ4_XS):
+        view[:, 0:2] = scales(blocks, 2e-3)   # d leads the block; the other bytes are codes and scale bits, all values legal
+    elif encoding == enc.Q5_1:
+        view[:, 0:2] = scales(blocks, 2e-3)
+        view[:, 2:4] = scales(blocks, 1e-2)
     else:
         raise ValueError(f"no generator for encoding {encoding}")
