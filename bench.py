@@ -197,7 +197,7 @@ def run_reference(args, rank: int, world: int):
 # ---- one operator alone, through the C ABI, device-timed over distinct weights ----------------------
 
 ALGO_BPW = {12: 0.5625, 14: 0.8203125, 8: 1.0625}
-ENC_NAME = {12: "q4_k", 14: "q6_k", 8: "q8_0", 13: "q5_k", 2: "q4_0", 6: "q5_0", 7: "q5_1", 20: "iq4_nl", 23: "iq4_xs"}
+ENC_NAME = {12: "q4_k", 14: "q6_k", 8: "q8_0", 13: "q5_k", 2: "q4_0", 6: "q5_0", 7: "q5_1", 20: "iq4_nl", 23: "iq4_xs", 10: "q2_k", 11: "q3_k"}
 
 
 def device_matrices(b, encoding: int, rows: int, columns: int, copies: int, seed: int, prepare: bool):
@@ -213,7 +213,7 @@ def device_matrices(b, encoding: int, rows: int, columns: int, copies: int, seed
         synth.fill_matrix_torch(device_tensor(wb), encoding, rows, columns, seed * 1000 + i)
         torch.cuda.synchronize()
         mm = m
-        if prepare and encoding in (enc.Q6_K, enc.Q8_0, enc.Q4_0, enc.Q5_0, enc.Q5_1, enc.IQ4_NL, enc.IQ4_XS):
+        if prepare and encoding in (enc.Q6_K, enc.Q8_0, enc.Q4_0, enc.Q5_0, enc.Q5_1, enc.IQ4_NL, enc.IQ4_XS, enc.Q2_K, enc.Q3_K):
             pb, mm = b.prepare(wb, m)
             b.release(wb)
             wb = pb
@@ -488,7 +488,7 @@ def other_configs(b, args, stack8_value=None) -> dict:
             row["cpu_baseline"] = {"us_m1": cpu_us, "cores": cores, "kind": "port"}
             sweep[f"{ENC_NAME[e]}_{rows}x{columns}"] = row
     # the other encodings of the integer path: one shape, one and eight tokens
-    for e in (enc.Q5_K, enc.Q4_0, enc.Q5_0, enc.Q5_1, enc.IQ4_NL, enc.IQ4_XS):
+    for e in (enc.Q5_K, enc.Q4_0, enc.Q5_0, enc.Q5_1, enc.IQ4_NL, enc.IQ4_XS, enc.Q2_K, enc.Q3_K):
         row = {}
         for m in (1, 8):
             us, algo, copies = time_gemv(b, e, 17408, 5120, m)

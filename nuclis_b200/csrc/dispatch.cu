@@ -5,8 +5,9 @@
 //   planar Q8_0, 1..8 tokens:    i8_kernel<Q80>   (gemv_q8_0_i8.cu, i8_q8_0.cuh)
 //   planar Q5_0 / Q5_1 / Q4_0 / IQ4_NL: i8_kernel<Block32<>> (gemv_block32_i8.cu, i8_block32.cuh)
 //   Q5_K, 1..8 tokens:           i8_kernel<Q5K>   (gemv_q5k_i8.cu, i8_q5k.cuh)
+//   planar Q2_K / Q3_K:          i8_kernel<Q2K / Q3K> (gemv_q23k_i8.cu, i8_q2k.cuh, i8_q3k.cuh)
 //   runs of one-token jobs:      chain_kernel     (gemv_chain.cu; opt-in)
-// Everything else (other encodings, unaligned views, GGUF-form Q6_K / Q8_0) is declined here and
+// Everything else (F32 / F16 / BF16, unaligned views, the GGUF forms of the encodings that have a planar one) is declined here and
 // served by the generic kernels (kernels_generic.cu).
 #include <cuda.h>
 
@@ -56,11 +57,11 @@ bool encode_weight_map(CUtensorMap *map, const uint8_t *base, uint64_t row_bytes
 }
 
 bool fast_supported(const FastJob &job) {
-    return q4k_i8_supported(job) || q6k_i8_supported(job) || q8_0_i8_supported(job) || block32_i8_supported(job) || q5k_i8_supported(job);
+    return q4k_i8_supported(job) || q6k_i8_supported(job) || q8_0_i8_supported(job) || block32_i8_supported(job) || q5k_i8_supported(job) || q23k_i8_supported(job);
 }
 
 bool fast_configure() {
-    return q4k_i8_configure() && q6k_i8_configure() && q8_0_i8_configure() && block32_i8_configure() && q5k_i8_configure() && prefill_configure() && expert_gemv_configure() && chain_configure();
+    return q4k_i8_configure() && q6k_i8_configure() && q8_0_i8_configure() && block32_i8_configure() && q5k_i8_configure() && q23k_i8_configure() && prefill_configure() && expert_gemv_configure() && chain_configure();
 }
 
 int launch_fast(cudaStream_t s, const FastJob &job) {
@@ -69,6 +70,7 @@ int launch_fast(cudaStream_t s, const FastJob &job) {
     if (q8_0_i8_supported(job)) return launch_q8_0_i8(s, job);
     if (block32_i8_supported(job)) return launch_block32_i8(s, job);
     if (q5k_i8_supported(job)) return launch_q5k_i8(s, job);
+    if (q23k_i8_supported(job)) return launch_q23k_i8(s, job);
     return 0;
 }
 

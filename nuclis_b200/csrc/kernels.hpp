@@ -122,6 +122,11 @@ int launch_block32_i8(cudaStream_t s, const FastJob &job);
 bool q5k_i8_configure();
 bool q5k_i8_supported(const FastJob &job);
 int launch_q5k_i8(cudaStream_t s, const FastJob &job);
+
+// ---- 1..8 activation rows on planar Q2_K / Q3_K, integer tensor path (gemv_q23k_i8.cu) -
+bool q23k_i8_configure();
+bool q23k_i8_supported(const FastJob &job);
+int launch_q23k_i8(cudaStream_t s, const FastJob &job);
 // ---- a run of one-token integer-path jobs as one persistent launch (gemv_chain.cu) --
 constexpr int kChainMax = 16;
 bool chain_configure();

@@ -44,6 +44,8 @@ __device__ __forceinline__ void decode16(uint32_t enc, uint32_t layout, const ui
     else if (layout == 2) dequant16_planar_q8_0(w, rows, columns, r, seg, v);
     else if (layout >= 3 && layout <= 5) dequant16_planar_block32(enc, w, rows, columns / 256, r, seg, v);
     else if (layout == 6) dequant16_planar_iq4_xs(w, rows, columns / 256, r, seg, v);
+    else if (layout == 7) dequant16_planar_q2k(w, rows, columns / 256, r, seg, v);
+    else if (layout == 8) dequant16_planar_q3k(w, rows, columns / 256, r, seg, v);
     else dequant16(enc, w + (size_t)r * stride, seg, v);
 }
 

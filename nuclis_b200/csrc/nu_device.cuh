@@ -268,6 +268,36 @@ __device__ __forceinline__ void dequant16_planar_iq4_xs(const uint8_t *base, uin
     for (int i = 0; i < 16; ++i) out[i] = __fmul_rn(multiplier, (float)iq4_value((q[i] >> (hi * 4)) & 15u));
 }
 
+// The same from the planar forms of Q2_K and Q3_K matrices (prepare.cu).
+__device__ __forceinline__ void dequant16_planar_q2k(const uint8_t *base, uint32_t rows, uint32_t ksb, uint32_t row, uint32_t seg, float out[16]) {
+    const uint32_t sb = seg / 16, g = seg % 16, i0 = g * 16;
+    const uint8_t *rec = base + ((size_t)row * ksb + sb) * 80;
+    const uint8_t *tail = base + (size_t)rows * ksb * 80 + ((size_t)sb * rows + row) * 4;
+    const float multiplier = __fmul_rn(half_at(tail), (float)(rec[g] & 15u));
+    const float offset = __fmul_rn(half_at(tail + 2), (float)(rec[g] >> 4));
+    const uint8_t *q = rec + 16 + (i0 / 128) * 32 + i0 % 32;
+    const uint32_t shift = 2 * ((i0 % 128) / 32);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) out[i] = __fsub_rn(__fmul_rn(multiplier, (float)((q[i] >> shift) & 3u)), offset);
+}
+__device__ __forceinline__ void dequant16_planar_q3k(const uint8_t *base, uint32_t rows, uint32_t ksb, uint32_t row, uint32_t seg, float out[16]) {
+    const uint32_t sb = seg / 16, g = seg % 16, i0 = g * 16;
+    const uint8_t *rec = base + ((size_t)row * ksb + sb) * 96;
+    const uint8_t *tile = base + (size_t)rows * ksb * 96 + ((size_t)sb * (rows / 16) + row / 16) * 224;
+    const uint8_t *scales = tile + (row % 16) * 12;
+    const uint32_t nibble = g < 8 ? (scales[g] & 15u) : (uint32_t)(scales[g - 8] >> 4);
+    const uint32_t upper = ((uint32_t)scales[8 + g % 4] >> (2 * (g / 4))) & 3u;
+    const float multiplier = __fmul_rn(half_at(tile + 192 + (row % 16) * 2), (float)((int)(nibble | (upper << 4)) - 32));
+    const uint8_t *q = rec + 32 + (i0 / 128) * 32 + i0 % 32;
+    const uint8_t *mask = rec + i0 % 32;
+    const uint32_t low_shift = 2 * ((i0 % 128) / 32), sign_shift = i0 / 32;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int low = (int)((q[i] >> low_shift) & 3u);
+        out[i] = __fmul_rn(multiplier, (float)(low - (((mask[i] >> sign_shift) & 1u) ? 0 : 4)));
+    }
+}
+
 // F32 forms of the activations, as the reference's GPU kernels compute them
 // (inference/src/backends/metal/kernels/common.metal:6-16).
 __device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + expf(-x)); }

@@ -137,6 +137,8 @@ __device__ __forceinline__ void decode16_generic(const Params &p, const uint8_t 
     else if (p.layout == 2) dequant16_planar_q8_0(w, p.rows, p.columns, r, seg, v);
     else if (p.layout >= 3 && p.layout <= 5) dequant16_planar_block32(p.enc, w, p.rows, p.columns / 256, r, seg, v);
     else if (p.layout == 6) dequant16_planar_iq4_xs(w, p.rows, p.columns / 256, r, seg, v);
+    else if (p.layout == 7) dequant16_planar_q2k(w, p.rows, p.columns / 256, r, seg, v);
+    else if (p.layout == 8) dequant16_planar_q3k(w, p.rows, p.columns / 256, r, seg, v);
     else dequant16(p.enc, w + (size_t)r * p.stride, seg, v);
 #pragma unroll
     for (int c = 0; c < 2; ++c)

@@ -29,6 +29,14 @@
 //     main plane  [rows][superblocks][128]: the nibble bytes
 //     header plane [superblocks][rows][8]: the first eight bytes of each superblock
 //
+//   Q2_K, layout 7 (84-byte superblocks: 16 scale bytes, 64 code bytes, d, dmin; the same conditions):
+//     main plane  [rows][superblocks][80]: the scale and code bytes
+//     tail plane  [superblocks][rows][4]: d, dmin
+//
+//   Q3_K, layout 8 (110-byte superblocks: 32 mask bytes, 64 code bytes, 12 scale bytes, d; the same conditions):
+//     main plane  [rows][superblocks][96]: the mask and code bytes
+//     tail plane  [superblocks][rows / 16][224]: the 12 scale bytes of each of 16 rows, then their 16 d
+//
 // Every byte is copied, none is changed: decoding the planar form gives the
 // values of the GGUF form bit for bit (dequant16_planar in nu_device.cuh).
 #include "kernels.hpp"
@@ -43,6 +51,8 @@ uint32_t prepared_layout(uint32_t enc, uint32_t rows, uint32_t columns) {
     if (enc == Q5_1 && rows % 16 == 0 && columns % 256 == 0) return 4;
     if ((enc == Q4_0 || enc == IQ4_NL) && rows % 16 == 0 && columns % 256 == 0) return 5;
     if (enc == IQ4_XS && rows % 16 == 0 && columns % 256 == 0) return 6;
+    if (enc == Q2_K && rows % 16 == 0 && columns % 256 == 0) return 7;
+    if (enc == Q3_K && rows % 16 == 0 && columns % 256 == 0) return 8;
     return 0;
 }
 
@@ -109,6 +119,33 @@ __global__ void prepare_iq4_xs_kernel(const uint8_t *src, uint8_t *dst, uint32_t
     else dst[blocks * 128 + ((size_t)sb * rows + row) * 8 + b] = src[id];
 }
 
+__global__ void prepare_q2k_kernel(const uint8_t *src, uint8_t *dst, uint32_t rows, uint32_t ksb) {
+    const size_t blocks = (size_t)rows * ksb;
+    const size_t id = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (id >= blocks * 84) return;
+    const size_t block = id / 84;
+    const uint32_t b = (uint32_t)(id % 84);
+    const uint32_t row = (uint32_t)(block / ksb), sb = (uint32_t)(block % ksb);
+    if (b < 80) dst[block * 80 + b] = src[id];
+    else dst[blocks * 80 + ((size_t)sb * rows + row) * 4 + (b - 80)] = src[id];
+}
+
+__global__ void prepare_q3k_kernel(const uint8_t *src, uint8_t *dst, uint32_t rows, uint32_t ksb) {
+    const size_t blocks = (size_t)rows * ksb;
+    const size_t id = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (id >= blocks * 110) return;
+    const size_t block = id / 110;
+    const uint32_t b = (uint32_t)(id % 110);
+    const uint32_t row = (uint32_t)(block / ksb), sb = (uint32_t)(block % ksb);
+    if (b < 96) {
+        dst[block * 96 + b] = src[id];
+        return;
+    }
+    uint8_t *tile = dst + blocks * 96 + ((size_t)sb * (rows / 16) + row / 16) * 224;
+    if (b < 108) tile[(row % 16) * 12 + (b - 96)] = src[id];
+    else tile[192 + (row % 16) * 2 + (b - 108)] = src[id];
+}
+
 __global__ void copy_bytes_kernel(const uint8_t *src, uint8_t *dst, size_t n) {
     const size_t id = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (id < n) dst[id] = src[id];
@@ -125,6 +162,10 @@ int launch_prepare(cudaStream_t s, uint32_t enc, const uint8_t *src, uint8_t *ds
     } else if (to == 3 || to == 4 || to == 5) {
         const uint32_t high = to == 5 ? 0u : 4u;
         prepare_block32_kernel<<<(unsigned)((bytes + 255) / 256), 256, 0, s>>>(src, dst, rows, columns / 256, (uint32_t)l.bytes - 16u - high, high);
+    } else if (to == 7) {
+        prepare_q2k_kernel<<<(unsigned)((bytes + 255) / 256), 256, 0, s>>>(src, dst, rows, columns / 256);
+    } else if (to == 8) {
+        prepare_q3k_kernel<<<(unsigned)((bytes + 255) / 256), 256, 0, s>>>(src, dst, rows, columns / 256);
     } else if (to == 6) {
         prepare_iq4_xs_kernel<<<(unsigned)((bytes + 255) / 256), 256, 0, s>>>(src, dst, rows, columns / 256);
     } else {

@@ -7,7 +7,7 @@ descriptors can be sized before any device call.
 from __future__ import annotations
 
 F32, F16, Q8_0, Q4_K, Q6_K, BF16 = 0, 1, 8, 12, 14, 30
-Q4_0, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K, IQ4_NL, IQ4_XS = 2, 6, 7, 10, 11, 13, 20, 23  # bit-exact generic decoders at any alignment; Q5_K, and the prepared forms of Q4_0, Q5_0, Q5_1, IQ4_NL, IQ4_XS, also on the integer tensor path
+Q4_0, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K, IQ4_NL, IQ4_XS = 2, 6, 7, 10, 11, 13, 20, 23  # bit-exact generic decoders at any alignment; Q5_K, and the prepared forms of the others, also on the integer tensor path
 
 LAYOUTS = {
     F32: ("F32", 1, 4),

@@ -244,10 +244,10 @@ class View:
 
     def upload(self, backend: Backend, tensor: Tensor, prepare: bool = True) -> tuple[Buffer, Matrix]:
         """Wraps a 2-D tensor into device memory (uploaded once, cached by address, as `Backend.wrap` does) and, for
-        the encodings whose GGUF rows the specialized kernels cannot address (Q6_K, Q8_0, Q5_0, Q5_1, Q4_0, IQ4_NL, IQ4_XS), re-lays it planar."""
+        the encodings whose GGUF rows the specialized kernels cannot address (Q6_K, Q8_0, Q5_0, Q5_1, Q4_0, IQ4_NL, IQ4_XS, Q2_K, Q3_K), re-lays it planar."""
         m, data = self.matrix(tensor)
         buf = backend.wrap(data)
-        if prepare and m.encoding in (enc.Q6_K, enc.Q8_0, enc.Q5_0, enc.Q5_1, enc.Q4_0, enc.IQ4_NL, enc.IQ4_XS) and m.rows % 16 == 0 and m.columns % 256 == 0:
+        if prepare and m.encoding in (enc.Q6_K, enc.Q8_0, enc.Q5_0, enc.Q5_1, enc.Q4_0, enc.IQ4_NL, enc.IQ4_XS, enc.Q2_K, enc.Q3_K) and m.rows % 16 == 0 and m.columns % 256 == 0:
             planar, m = backend.prepare(buf, m)
             backend.unwrap(data)
             buf = planar

@@ -179,5 +179,10 @@ def fill_matrix_torch(dst, encoding: int, rows: int, columns: int, seed: int) ->
     elif encoding == enc.Q5_1:
         view[:, 0:2] = scales(blocks, 2e-3)
         view[:, 2:4] = scales(blocks, 1e-2)
+    elif encoding == enc.Q2_K:
+        view[:, 80:82] = scales(blocks, 5e-3)
+        view[:, 82:84] = scales(blocks, 5e-3)
+    elif encoding == enc.Q3_K:
+        view[:, 108:110] = scales(blocks, 2e-3)
     else:
         raise ValueError(f"no generator for encoding {encoding}")

@@ -259,8 +259,8 @@ def test_wrap_caches_by_address_and_ids_are_not_reused(backend):
 
 # ---- the planar form of nu_cuda_matrix_prepare (Q6_K) ---------------------------------------------
 
-PLANAR = {enc.Q6_K: 1, enc.Q8_0: 2, enc.Q5_0: 3, enc.Q5_1: 4, enc.Q4_0: 5, enc.IQ4_NL: 5, enc.IQ4_XS: 6}
-PREPARED = [enc.Q6_K, enc.Q8_0, enc.Q5_0, enc.Q5_1, enc.Q4_0, enc.IQ4_NL, enc.IQ4_XS]
+PLANAR = {enc.Q6_K: 1, enc.Q8_0: 2, enc.Q5_0: 3, enc.Q5_1: 4, enc.Q4_0: 5, enc.IQ4_NL: 5, enc.IQ4_XS: 6, enc.Q2_K: 7, enc.Q3_K: 8}
+PREPARED = [enc.Q6_K, enc.Q8_0, enc.Q5_0, enc.Q5_1, enc.Q4_0, enc.IQ4_NL, enc.IQ4_XS, enc.Q2_K, enc.Q3_K]
 
 
 @pytest.mark.parametrize("encoding", PREPARED)
