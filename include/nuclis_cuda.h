@@ -151,8 +151,8 @@ uint64_t nu_cuda_created_bytes(const nu_cuda *h);
 /* Re-lays a matrix once, at load time, into the form the specialized kernels read
  * (no reference analogue; the reference wraps the file bytes as they are,
  * root.zig:217-230). GGUF rows of some encodings start on 2-byte boundaries
- * (Q6_K blocks are 210 bytes, Q8_0 blocks 34, Q4_0 and IQ4_NL 18, Q5_0 22, Q5_1 24; IQ4_XS superblocks, 136 bytes,
- * on 8-byte ones), which no vector load or bulk copy can address;
+ * (Q6_K blocks are 210 bytes, Q8_0 blocks 34, Q4_0 and IQ4_NL 18, Q5_0 22, Q5_1 24, Q3_K superblocks 110; IQ4_XS
+ * and Q2_K superblocks, 136 and 84 bytes, on 8- and 4-byte ones), which no vector load or bulk copy can address;
  * the prepared form holds the same bytes in 16-byte aligned planes and decodes
  * to the same values bit for bit. `prepared` must be as long as the matrix and
  * must not overlap it; `layout` receives the value to put in `nu_matrix.layout`
