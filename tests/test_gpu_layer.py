@@ -38,7 +38,11 @@ def weights(b, encoding, rows, columns, seed, prepare):
     return wb, m, w
 
 
-@pytest.mark.parametrize("encoding,prepare", [(enc.Q4_K, False), (enc.Q6_K, True), (enc.Q8_0, True)])
+EVERY = [(enc.Q4_K, False), (enc.Q5_K, False), (enc.Q6_K, True), (enc.Q8_0, True), (enc.Q4_0, True), (enc.Q5_0, True), (enc.Q5_1, True),
+         (enc.IQ4_NL, True), (enc.IQ4_XS, True), (enc.Q2_K, True), (enc.Q3_K, True)]
+
+
+@pytest.mark.parametrize("encoding,prepare", EVERY)
 def test_plain_segments_share_one_input(backend, encoding, prepare):
     b = backend
     columns, rows = 1280, [512, 256, 272]
@@ -80,6 +84,26 @@ def test_gate_up_pair_writes_the_activated_product(backend, mode, shape):
     got = out.floats()[:rows]
     # the product of two sums each within the matvec bound: compare on the whole vector
     assert rel_l2(got, want) <= 1e-5
+    for buf in (xb, gb, ub, out):
+        b.release(buf)
+
+
+@pytest.mark.parametrize("encoding,prepare", EVERY[1:])
+def test_gate_up_pair_on_the_other_encodings(backend, encoding, prepare):
+    b = backend
+    rows, columns = 1056, 1280
+    x = synth.activations(1, columns, 12)[0]
+    xb = upload(b, x)
+    gb, m, wg = weights(b, encoding, rows, columns, 33, prepare)
+    ub, _, wu = weights(b, encoding, rows, columns, 34, prepare)
+    out = b.create(rows * 4)
+    b.begin()
+    b.matvec_segments([Segment(gb, m, out), Segment(ub, m, out)], xb, SegmentMode.silu_mul_pair)
+    b.commit()
+    g = oracle.matvec(encoding, rows, columns, wg, x)
+    u = oracle.matvec(encoding, rows, columns, wu, x)
+    want = oracle.silu(g).astype(np.float64) * u.astype(np.float64)
+    assert rel_l2(out.floats()[:rows], want) <= 1e-5
     for buf in (xb, gb, ub, out):
         b.release(buf)
 

@@ -89,6 +89,18 @@ def test_prefill_accepts_f32_activations_and_the_planar_form(backend):
     assert np.array_equal(a, c)  # the planar form decodes to the same bits, so the same products
 
 
+@pytest.mark.parametrize("encoding", [enc.Q8_0, enc.Q5_0, enc.Q5_1, enc.Q4_0, enc.IQ4_NL, enc.IQ4_XS, enc.Q2_K, enc.Q3_K])
+def test_prefill_reads_every_planar_form(backend, encoding):
+    # the prefill tiles decode the prepared form of every encoding to the bits of the GGUF form: identical products
+    rows, columns, tokens = 144, 1280, 33
+    w = synth.matrix(encoding, rows, columns, seed=80 + encoding)
+    x = synth.activations(tokens, columns, seed=81)
+    m = Matrix(encoding, rows, columns, w.size)
+    a = run_matmul(backend, w, m, x, BF16)
+    c = run_matmul(backend, w, m, x, BF16, prepare=True)
+    assert np.array_equal(a, c)
+
+
 @pytest.mark.parametrize("case", [(enc.Q4_K, 17408, 5120, False), (enc.Q6_K, 5120, 17408, True)])
 def test_prefill_config_shapes_at_512_tokens(backend, case):
     encoding, rows, columns, prepare = case
