@@ -152,9 +152,22 @@ __device__ __forceinline__ void codes4_fma(uint32_t t4, float mul, float add, ui
     hi = pack_bf16(fmaf(byte_f32(t4, 2), mul, add), fmaf(byte_f32(t4, 3), mul, add));
 }
 __device__ __forceinline__ uint4 ldg16(const uint8_t *ptr) { return __ldg((const uint4 *)ptr); }
+// Four bits of x into bit 4 of four bytes: bit i of x lands on bit 8 i of x * 0x00204081 (no two terms meet).
+__device__ __forceinline__ uint32_t bits4_to_bit4(uint32_t x) { return ((x * 0x00204081u) & 0x01010101u) << 4; }
+// The IQ4_NL values (inference/src/quant/decode.zig:437) of the four nibbles in the low 16 bits of n, as bytes in nibble
+// order: a permute takes a nibble's low three bits as an index into eight table bytes, a second one reads the other
+// eight, a third (sign-replicating, on n and n << 4, whose bytes carry the nibbles' top bits as signs) picks between them.
+__device__ __forceinline__ uint32_t iq4_lookup4(uint32_t n) {
+    uint32_t lo, hi, upper;
+    const uint32_t sel = n & 0x7777u;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(lo) : "r"(0xbfad9881u), "r"(0xf6eaddcfu), "r"(sel));
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(0x26190d01u), "r"(0x71594535u), "r"(sel));
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(upper) : "r"(n), "r"(n << 4), "r"(0x9d8cu));
+    return (lo & ~upper) | (hi & upper);
+}
 
 // MODE: 0 the generic decoders (any encoding and layout), 1 Q4_K with 16-byte aligned rows, 2 planar Q6_K, 3 planar Q8_0,
-// 4 GGUF Q8_0 rows.
+// 4 GGUF Q8_0 rows, 5 Q5_K with 16-byte aligned rows, 6 the planar forms of Q5_0, Q5_1, Q4_0, IQ4_NL and IQ4_XS.
 // BPS: blocks per SM the instance is built for (registers capped accordingly). Two blocks of two stages share an SM's
 // shared and tensor memory: one block's epilogue and prologue run under the other's main loop.
 template <int BN, int STAGES, int MODE, int BPS>
@@ -239,26 +252,32 @@ __global__ void __launch_bounds__(THREADS, BPS) prefill_kernel(const __grid_cons
             if (++s == STAGES) { s = 0; ++round; }
             return true;
         };
-        if (MODE == 1) {
+        if (MODE == 1 || MODE == 5) {
             // Q4_K: a K step is one group pair of a superblock: 32 quant bytes whose low nibbles are the even
             // group (columns 0..31 of the step) and high nibbles the odd group (columns 32..63). Piece p holds
             // bytes 16 p .. 16 p + 15: columns 16 p .. + 15 of both groups. Values are (d*s)*q - dmin*m with one
             // rounding, like the reference decoder (inference/src/quant/decode.zig:147-170), then rounded to bf16.
+            // Q5_K (MODE 5): 32 bytes of fifth bits sit between the header and the nibbles; bit g of byte c belongs to
+            // column c of group g, so the piece's 16 bytes of them serve all four K steps of the superblock.
+            constexpr bool FIFTH = MODE == 5;
+            constexpr int SB_BYTES = FIFTH ? 176 : 144, QS = FIFTH ? 48 : 16;
             const uint8_t *blk = wbase + (size_t)grow * p.stride;
             const uint32_t nsb = p.columns / 256;
-            // the five 16-byte loads of a superblock are requested a whole superblock (four K steps) ahead
-            uint4 hdr_n = ldg16(blk), q_n[4];
+            // the five (six) 16-byte loads of a superblock are requested a whole superblock (four K steps) ahead
+            uint4 hdr_n = ldg16(blk), q_n[4], f_n = make_uint4(0u, 0u, 0u, 0u);
+            if (FIFTH) f_n = ldg16(blk + 16 + piece * 16);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) q_n[j] = ldg16(blk + 16 + j * 32 + piece * 16);
-            for (uint32_t sb = 0; sb < nsb && ok; ++sb, blk += 144) {
-                const uint4 hdr = hdr_n;
+            for (int j = 0; j < 4; ++j) q_n[j] = ldg16(blk + QS + j * 32 + piece * 16);
+            for (uint32_t sb = 0; sb < nsb && ok; ++sb, blk += SB_BYTES) {
+                const uint4 hdr = hdr_n, fifth = f_n;
                 uint4 q_c[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) q_c[j] = q_n[j];
                 if (sb + 1 < nsb) {
-                    hdr_n = ldg16(blk + 144);
+                    hdr_n = ldg16(blk + SB_BYTES);
+                    if (FIFTH) f_n = ldg16(blk + SB_BYTES + 16 + piece * 16);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) q_n[j] = ldg16(blk + 160 + j * 32 + piece * 16);
+                    for (int j = 0; j < 4; ++j) q_n[j] = ldg16(blk + SB_BYTES + QS + j * 32 + piece * 16);
                 }
                 const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu))), dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
 #pragma unroll
@@ -276,13 +295,24 @@ __global__ void __launch_bounds__(THREADS, BPS) prefill_kernel(const __grid_cons
                         ndm[e] = -__fmul_rn(dmin, (float)m6);
                     }
                     const uint32_t words[4] = {qq.x, qq.y, qq.z, qq.w};
+                    const uint32_t fw[4] = {fifth.x, fifth.y, fifth.z, fifth.w};
+                    uint32_t even[4], odd[4];
+#pragma unroll
+                    for (int m = 0; m < 4; ++m) {
+                        even[m] = words[m] & 0x0f0f0f0fu;
+                        odd[m] = (words[m] >> 4) & 0x0f0f0f0fu;
+                        if (FIFTH) {
+                            even[m] |= (j < 2 ? fw[m] << (4 - 2 * j) : fw[m] >> (2 * j - 4)) & 0x10101010u;  // bit 2j of each byte to bit 4
+                            odd[m] |= (j < 2 ? fw[m] << (3 - 2 * j) : fw[m] >> (2 * j - 3)) & 0x10101010u;   // bit 2j + 1
+                        }
+                    }
                     uint4 chunks[4];  // 0, 1: the even group's 16 columns; 2, 3: the odd group's
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {
-                        codes4_fma(words[c * 2] & 0x0f0f0f0fu, ds[0], ndm[0], chunks[c].x, chunks[c].y);
-                        codes4_fma(words[c * 2 + 1] & 0x0f0f0f0fu, ds[0], ndm[0], chunks[c].z, chunks[c].w);
-                        codes4_fma((words[c * 2] >> 4) & 0x0f0f0f0fu, ds[1], ndm[1], chunks[2 + c].x, chunks[2 + c].y);
-                        codes4_fma((words[c * 2 + 1] >> 4) & 0x0f0f0f0fu, ds[1], ndm[1], chunks[2 + c].z, chunks[2 + c].w);
+                        codes4_fma(even[c * 2], ds[0], ndm[0], chunks[c].x, chunks[c].y);
+                        codes4_fma(even[c * 2 + 1], ds[0], ndm[0], chunks[c].z, chunks[c].w);
+                        codes4_fma(odd[c * 2], ds[1], ndm[1], chunks[2 + c].x, chunks[2 + c].y);
+                        codes4_fma(odd[c * 2 + 1], ds[1], ndm[1], chunks[2 + c].z, chunks[2 + c].w);
                     }
                     ok = put(chunks, piece * 2, 4 + piece * 2);
                     if (!ok) break;
@@ -419,6 +449,74 @@ __global__ void __launch_bounds__(THREADS, BPS) prefill_kernel(const __grid_cons
                 }
                 ok = put(chunks, piece * 4, piece * 4 + 2);
             }
+        } else if (MODE == 6) {
+            // The planar forms of the 32-element block encodings (prepare.cu, layouts 3..6: Q5_0, Q5_1, Q4_0, IQ4_NL, IQ4_XS):
+            // piece p takes block 2k + p of K step k: 16 nibble bytes (low nibbles: columns 0..15 of the block, high: 16..31),
+            // for Q5_0 / Q5_1 a 32-bit plane of fifth bits, and its scale(s) from the second plane. Every value is
+            // code * mul + add with one rounding: the exact value the reference decoder rounds
+            // (inference/src/quant/decode.zig:46-53, 73-81, 125-143, 214-228), then rounded to bf16.
+            const uint32_t enc = p.enc, nsb = p.columns / 256;
+            const bool fifth = enc == Q5_0 || enc == Q5_1, table = enc == IQ4_NL || enc == IQ4_XS;
+            const uint32_t record = fifth ? 160u : 128u, sc_row = enc == Q5_1 ? 32u : enc == IQ4_XS ? 8u : 16u;
+            const uint8_t *rec = wbase + (size_t)grow * nsb * record;
+            const uint8_t *sc = wbase + (size_t)p.rows * nsb * record + (size_t)grow * sc_row;
+            const size_t sc_step = (size_t)p.rows * sc_row;
+            struct Raw { uint4 nib; uint32_t high; uint32_t d, m; uint2 hdr; };
+            auto fetch = [&](uint32_t k) {
+                const uint32_t sb = k >> 2, c = 2 * (k & 3u) + piece;
+                const uint8_t *r8 = rec + (size_t)sb * record, *s8 = sc + (size_t)sb * sc_step;
+                Raw raw;
+                raw.nib = ldg16(r8 + c * 16);
+                raw.high = fifth ? __ldg((const uint32_t *)(r8 + 128 + c * 4)) : 0u;
+                raw.hdr = make_uint2(0u, 0u);
+                raw.d = raw.m = 0;
+                if (enc == IQ4_XS) raw.hdr = __ldg((const uint2 *)s8);
+                else raw.d = __ldg((const unsigned short *)(s8 + c * 2));
+                if (enc == Q5_1) raw.m = __ldg((const unsigned short *)(s8 + 16 + c * 2));
+                return raw;
+            };
+            Raw next = fetch(0);
+            for (uint32_t k = 0; k < ksteps && ok; ++k) {
+                const Raw raw = next;
+                if (k + 1 < ksteps) next = fetch(k + 1);
+                float mul, add;
+                if (enc == IQ4_XS) {
+                    const uint32_t c = 2 * (k & 3u) + piece;
+                    const int scale = (int)(((raw.hdr.y >> (4 * c)) & 15u) | (((raw.hdr.x >> (16 + 2 * c)) & 3u) << 4)) - 32;
+                    mul = __fmul_rn(__half2float(__ushort_as_half((unsigned short)(raw.hdr.x & 0xffffu))), (float)scale);
+                    add = -128.0f * mul;
+                } else {
+                    mul = __half2float(__ushort_as_half((unsigned short)raw.d));
+                    add = enc == Q5_1 ? __half2float(__ushort_as_half((unsigned short)raw.m)) : enc == Q5_0 ? -16.0f * mul : enc == Q4_0 ? -8.0f * mul : -128.0f * mul;
+                }
+                const uint32_t nw[4] = {raw.nib.x, raw.nib.y, raw.nib.z, raw.nib.w};
+                uint32_t lo[4], hi[4];
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    if (table) {
+                        // the table values of the nibbles of each half-word come out in nibble order: (lo0, hi0, lo1, hi1), (lo2, hi2, lo3, hi3)
+                        const uint32_t a = iq4_lookup4(nw[m]), b = iq4_lookup4(nw[m] >> 16);
+                        lo[m] = __byte_perm(a, b, 0x6420) ^ 0x80808080u;  // signed bytes biased to 0..255; the bias leaves through `add`
+                        hi[m] = __byte_perm(a, b, 0x7531) ^ 0x80808080u;
+                    } else {
+                        lo[m] = nw[m] & 0x0f0f0f0fu;
+                        hi[m] = (nw[m] >> 4) & 0x0f0f0f0fu;
+                        if (fifth) {
+                            lo[m] |= bits4_to_bit4((raw.high >> (4 * m)) & 15u);
+                            hi[m] |= bits4_to_bit4((raw.high >> (16 + 4 * m)) & 15u);
+                        }
+                    }
+                }
+                uint4 chunks[4];
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    codes4_fma(lo[c * 2], mul, add, chunks[c].x, chunks[c].y);
+                    codes4_fma(lo[c * 2 + 1], mul, add, chunks[c].z, chunks[c].w);
+                    codes4_fma(hi[c * 2], mul, add, chunks[2 + c].x, chunks[2 + c].y);
+                    codes4_fma(hi[c * 2 + 1], mul, add, chunks[2 + c].z, chunks[2 + c].w);
+                }
+                ok = put(chunks, piece * 4, piece * 4 + 2);
+            }
         } else {
             for (uint32_t k = 0; k < ksteps && ok; ++k) {
                 uint4 chunks[4];
@@ -520,7 +618,7 @@ static bool configure_one() {
 template <int BN, int STAGES, int BPS>
 static bool configure_bn() {
     return configure_one<BN, STAGES, 0, BPS>() && configure_one<BN, STAGES, 1, BPS>() && configure_one<BN, STAGES, 2, BPS>() && configure_one<BN, STAGES, 3, BPS>() &&
-           configure_one<BN, STAGES, 4, BPS>();
+           configure_one<BN, STAGES, 4, BPS>() && configure_one<BN, STAGES, 5, BPS>() && configure_one<BN, STAGES, 6, BPS>();
 }
 
 bool prefill_configure() { return configure_bn<256, 4, 1>() && configure_bn<256, 2, 2>() && configure_bn<128, 6, 1>() && configure_bn<64, 8, 1>() && configure_bn<64, 4, 2>(); }
@@ -535,6 +633,8 @@ static void launch_bn(dim3 grid, cudaStream_t s, const prefill::Params &p, int m
     case 2: prefill::prefill_kernel<BN, STAGES, 2, BPS><<<grid, prefill::THREADS, bytes, s>>>(p); break;
     case 3: prefill::prefill_kernel<BN, STAGES, 3, BPS><<<grid, prefill::THREADS, bytes, s>>>(p); break;
     case 4: prefill::prefill_kernel<BN, STAGES, 4, BPS><<<grid, prefill::THREADS, bytes, s>>>(p); break;
+    case 5: prefill::prefill_kernel<BN, STAGES, 5, BPS><<<grid, prefill::THREADS, bytes, s>>>(p); break;
+    case 6: prefill::prefill_kernel<BN, STAGES, 6, BPS><<<grid, prefill::THREADS, bytes, s>>>(p); break;
     default: prefill::prefill_kernel<BN, STAGES, 0, BPS><<<grid, prefill::THREADS, bytes, s>>>(p); break;
     }
 }
@@ -573,10 +673,12 @@ int launch_prefill(cudaStream_t s, const PrefillJob &j) {
         grid = dim3(grid.x * grid.y, 1);
     }
     const bool q8_rows = j.layout == 0 && j.enc == Q8_0 && (uintptr_t)j.w % 4 == 0 && j.stride % 2 == 0;
-    const int mode = q8_rows ? 4 : !p.fast ? 0 : j.enc == Q4_K ? 1 : j.layout == 1 ? 2 : 3;
+    const bool q5k_rows = j.layout == 0 && j.enc == Q5_K && (uintptr_t)j.w % 16 == 0 && j.stride % 16 == 0 && j.columns % 256 == 0;
+    const bool block32 = j.layout >= 3 && j.layout <= 6;
+    const int mode = q8_rows ? 4 : q5k_rows ? 5 : block32 ? 6 : !p.fast ? 0 : j.enc == Q4_K ? 1 : j.layout == 1 ? 2 : 3;
     // Two blocks per SM (two stages each) when there are more blocks than SMs and the decoder is light enough for the
     // smaller register budget (measured: Q4_K 933 -> 1,067 TFLOP/s; planar Q6_K loses a little).
-    const bool two = bn == 256 && (mode == 1 || mode == 3 || mode == 4) && (size_t)grid.x * grid.y > (size_t)j.sm_count;
+    const bool two = bn == 256 && (mode == 1 || mode == 3 || mode == 4 || mode == 5 || mode == 6) && (size_t)grid.x * grid.y > (size_t)j.sm_count;
     if (two) launch_bn<256, 2, 2>(grid, s, p, mode);
     else if (bn == 256) launch_bn<256, 4, 1>(grid, s, p, mode);
     else if (bn == 128) launch_bn<128, 6, 1>(grid, s, p, mode);
