@@ -167,7 +167,8 @@ __device__ __forceinline__ uint32_t iq4_lookup4(uint32_t n) {
 }
 
 // MODE: 0 the generic decoders (any encoding and layout), 1 Q4_K with 16-byte aligned rows, 2 planar Q6_K, 3 planar Q8_0,
-// 4 GGUF Q8_0 rows, 5 Q5_K with 16-byte aligned rows, 6 the planar forms of Q5_0, Q5_1, Q4_0, IQ4_NL and IQ4_XS.
+// 4 GGUF Q8_0 rows, 5 Q5_K with 16-byte aligned rows, 6 the planar forms of Q5_0, Q5_1, Q4_0, IQ4_NL and IQ4_XS,
+// 7 the planar forms of Q2_K and Q3_K.
 // BPS: blocks per SM the instance is built for (registers capped accordingly). Two blocks of two stages share an SM's
 // shared and tensor memory: one block's epilogue and prologue run under the other's main loop.
 template <int BN, int STAGES, int MODE, int BPS>
@@ -517,6 +518,81 @@ __global__ void __launch_bounds__(THREADS, BPS) prefill_kernel(const __grid_cons
                 }
                 ok = put(chunks, piece * 4, piece * 4 + 2);
             }
+        } else if (MODE == 7) {
+            // The planar forms of Q2_K and Q3_K (prepare.cu, layouts 7 and 8). K step s of a superblock is the two-bit fields
+            // 2 (s & 1) and 2 (s & 1) + 1 of the 32 code bytes of half s >> 1; piece p takes field j = 2 (s & 1) + p: 32
+            // columns, groups 8 (s >> 1) + 2 j and the next. Q2_K: value = (d * scale) * code - dmin * minimum; Q3_K: the third
+            // bit of a code is bit 4 (s >> 1) + j of the 32 mask bytes, value = (d * (scale - 32)) * (code - 4). One
+            // rounding each, the value the reference decoder rounds (inference/src/quant/decode.zig:174-196, 260-275).
+            const bool q3 = p.enc == Q3_K;
+            const uint32_t nsb = p.columns / 256, record = q3 ? 96u : 80u, codes_at = q3 ? 32u : 16u;
+            const uint8_t *rec = wbase + (size_t)grow * nsb * record;
+            const uint8_t *tail = wbase + (size_t)p.rows * nsb * record + (q3 ? (size_t)(grow / 16) * 224 : (size_t)grow * 4);
+            const size_t tail_step = q3 ? (size_t)(p.rows / 16) * 224 : (size_t)p.rows * 4;
+            struct Raw { uint4 qa, qb, ma, mb; };
+            auto fetch = [&](uint32_t k) {
+                const uint8_t *r8 = rec + (size_t)(k >> 2) * record;
+                Raw raw;
+                raw.qa = ldg16(r8 + codes_at + ((k >> 1) & 1u) * 32);
+                raw.qb = ldg16(r8 + codes_at + ((k >> 1) & 1u) * 32 + 16);
+                raw.ma = raw.mb = make_uint4(0u, 0u, 0u, 0u);
+                if (q3) { raw.ma = ldg16(r8); raw.mb = ldg16(r8 + 16); }
+                return raw;
+            };
+            Raw next = fetch(0);
+            uint32_t sw[4] = {0u, 0u, 0u, 0u};  // the scale bytes of the row's superblock: 16 (Q2_K) or 12 (Q3_K)
+            float d = 0.0f, dmin = 0.0f;
+            for (uint32_t k = 0; k < ksteps && ok; ++k) {
+                const Raw raw = next;
+                if (k + 1 < ksteps) next = fetch(k + 1);
+                if ((k & 3u) == 0) {
+                    const uint8_t *t8 = tail + (size_t)(k >> 2) * tail_step;
+                    if (q3) {
+                        const uint32_t *sc = (const uint32_t *)(t8 + (grow % 16) * 12);
+                        sw[0] = __ldg(sc); sw[1] = __ldg(sc + 1); sw[2] = __ldg(sc + 2);
+                        d = __half2float(__ushort_as_half(__ldg((const unsigned short *)(t8 + 192 + (grow % 16) * 2))));
+                    } else {
+                        const uint4 sc = ldg16(rec + (size_t)(k >> 2) * record);
+                        sw[0] = sc.x; sw[1] = sc.y; sw[2] = sc.z; sw[3] = sc.w;
+                        const uint32_t dd = __ldg((const uint32_t *)t8);
+                        d = __half2float(__ushort_as_half((unsigned short)(dd & 0xffffu)));
+                        dmin = __half2float(__ushort_as_half((unsigned short)(dd >> 16)));
+                    }
+                }
+                const uint32_t n = (k >> 1) & 1u, j = 2 * (k & 1u) + piece, g0 = 8 * n + 2 * j;
+                float mul[2], add[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const uint32_t g = g0 + e;
+                    if (q3) {
+                        const uint32_t lowb = ((((g & 7u) >> 2) ? sw[1] : sw[0]) >> (8 * (g & 3u))) & 0xffu, nibble = g < 8 ? (lowb & 15u) : (lowb >> 4);
+                        const uint32_t upper = (sw[2] >> (8 * (g & 3u) + 2 * (g >> 2))) & 3u;
+                        mul[e] = __fmul_rn(d, (float)((int)(nibble | (upper << 4)) - 32));
+                        add[e] = -4.0f * mul[e];
+                    } else {
+                        const uint32_t wsel = (g >> 2) == 0 ? sw[0] : (g >> 2) == 1 ? sw[1] : (g >> 2) == 2 ? sw[2] : sw[3];  // selects: the words stay in registers
+                        const uint32_t b = (wsel >> (8 * (g & 3u))) & 0xffu;
+                        mul[e] = __fmul_rn(d, (float)(b & 15u));
+                        add[e] = -__fmul_rn(dmin, (float)(b >> 4));
+                    }
+                }
+                const uint32_t qw[8] = {raw.qa.x, raw.qa.y, raw.qa.z, raw.qa.w, raw.qb.x, raw.qb.y, raw.qb.z, raw.qb.w};
+                const uint32_t mw[8] = {raw.ma.x, raw.ma.y, raw.ma.z, raw.ma.w, raw.mb.x, raw.mb.y, raw.mb.z, raw.mb.w};
+                const uint32_t bit = 4 * n + j;
+                uint32_t codes[8];
+#pragma unroll
+                for (int m = 0; m < 8; ++m) {
+                    codes[m] = (qw[m] >> (2 * j)) & 0x03030303u;
+                    if (q3) codes[m] |= ((mw[m] >> bit) & 0x01010101u) << 2;
+                }
+                uint4 chunks[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    codes4_fma(codes[c * 2], mul[c >> 1], add[c >> 1], chunks[c].x, chunks[c].y);
+                    codes4_fma(codes[c * 2 + 1], mul[c >> 1], add[c >> 1], chunks[c].z, chunks[c].w);
+                }
+                ok = put(chunks, piece * 4, piece * 4 + 2);
+            }
         } else {
             for (uint32_t k = 0; k < ksteps && ok; ++k) {
                 uint4 chunks[4];
@@ -618,7 +694,8 @@ static bool configure_one() {
 template <int BN, int STAGES, int BPS>
 static bool configure_bn() {
     return configure_one<BN, STAGES, 0, BPS>() && configure_one<BN, STAGES, 1, BPS>() && configure_one<BN, STAGES, 2, BPS>() && configure_one<BN, STAGES, 3, BPS>() &&
-           configure_one<BN, STAGES, 4, BPS>() && configure_one<BN, STAGES, 5, BPS>() && configure_one<BN, STAGES, 6, BPS>();
+           configure_one<BN, STAGES, 4, BPS>() && configure_one<BN, STAGES, 5, BPS>() && configure_one<BN, STAGES, 6, BPS>() &&
+           configure_one<BN, STAGES, 7, BPS>();
 }
 
 bool prefill_configure() { return configure_bn<256, 4, 1>() && configure_bn<256, 2, 2>() && configure_bn<128, 6, 1>() && configure_bn<64, 8, 1>() && configure_bn<64, 4, 2>(); }
@@ -635,6 +712,7 @@ static void launch_bn(dim3 grid, cudaStream_t s, const prefill::Params &p, int m
     case 4: prefill::prefill_kernel<BN, STAGES, 4, BPS><<<grid, prefill::THREADS, bytes, s>>>(p); break;
     case 5: prefill::prefill_kernel<BN, STAGES, 5, BPS><<<grid, prefill::THREADS, bytes, s>>>(p); break;
     case 6: prefill::prefill_kernel<BN, STAGES, 6, BPS><<<grid, prefill::THREADS, bytes, s>>>(p); break;
+    case 7: prefill::prefill_kernel<BN, STAGES, 7, BPS><<<grid, prefill::THREADS, bytes, s>>>(p); break;
     default: prefill::prefill_kernel<BN, STAGES, 0, BPS><<<grid, prefill::THREADS, bytes, s>>>(p); break;
     }
 }
@@ -675,10 +753,10 @@ int launch_prefill(cudaStream_t s, const PrefillJob &j) {
     const bool q8_rows = j.layout == 0 && j.enc == Q8_0 && (uintptr_t)j.w % 4 == 0 && j.stride % 2 == 0;
     const bool q5k_rows = j.layout == 0 && j.enc == Q5_K && (uintptr_t)j.w % 16 == 0 && j.stride % 16 == 0 && j.columns % 256 == 0;
     const bool block32 = j.layout >= 3 && j.layout <= 6;
-    const int mode = q8_rows ? 4 : q5k_rows ? 5 : block32 ? 6 : !p.fast ? 0 : j.enc == Q4_K ? 1 : j.layout == 1 ? 2 : 3;
+    const int mode = q8_rows ? 4 : q5k_rows ? 5 : block32 ? 6 : (j.layout == 7 || j.layout == 8) ? 7 : !p.fast ? 0 : j.enc == Q4_K ? 1 : j.layout == 1 ? 2 : 3;
     // Two blocks per SM (two stages each) when there are more blocks than SMs and the decoder is light enough for the
     // smaller register budget (measured: Q4_K 933 -> 1,067 TFLOP/s; planar Q6_K loses a little).
-    const bool two = bn == 256 && (mode == 1 || mode == 3 || mode == 4 || mode == 5 || mode == 6) && (size_t)grid.x * grid.y > (size_t)j.sm_count;
+    const bool two = bn == 256 && (mode == 1 || mode == 3 || mode == 4 || mode == 5 || mode == 6 || mode == 7) && (size_t)grid.x * grid.y > (size_t)j.sm_count;
     if (two) launch_bn<256, 2, 2>(grid, s, p, mode);
     else if (bn == 256) launch_bn<256, 4, 1>(grid, s, p, mode);
     else if (bn == 128) launch_bn<128, 6, 1>(grid, s, p, mode);
