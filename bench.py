@@ -510,6 +510,11 @@ def other_configs(b, args, stack8_value=None) -> dict:
                 "us": us, "tflops": tf, "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": tf / peaks["bf16_tflops"],
                                                      "frac_of_sustained": tf / peaks["bf16_tflops_sustained"], "peak_source": f"{kind} cuBLAS bf16 (burst)"},
                 "cpu_baseline": {"tflops": flops / (cpu_us * tokens) / 1e6, "cores": cores, "kind": "port", "sample": "one token row on the CPU oracle, scaled to the token count"}}
+    # the other encodings: one shape, 4,096 token rows
+    for e in (enc.Q8_0, enc.Q5_K, enc.Q4_0, enc.Q5_0, enc.Q5_1, enc.IQ4_NL, enc.IQ4_XS, enc.Q2_K, enc.Q3_K):
+        us, flops = time_prefill(b, e, 17408, 5120, 4096)
+        tf = flops / us / 1e6
+        pre[f"{ENC_NAME[e]}_17408x5120_t4096"] = {"us": us, "tflops": tf, "frac": tf / peaks["bf16_tflops"], "frac_of_sustained": tf / peaks["bf16_tflops_sustained"]}
     out["config3"] = {"workload": "prefill GEMM on tcgen05 (weights decoded to bf16 tiles, F32 accumulate)", "cases": pre}
     # config 4: the expert chain at 1 and 8 tokens
     ex = {}
