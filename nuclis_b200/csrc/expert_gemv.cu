@@ -1,10 +1,10 @@
 // Expert GEMV for the decode form of a mixture-of-experts layer: one launch multiplies every routed
 // slot's input by the matrix of the expert the slot selected (Backend.matvecExperts /
 // matvecExpertsGrouped, inference/src/backends/metal/ops/experts.zig:36-77; the reference's kernel
-// is nu_matvec_experts, kernels/experts.metal:16-36). Specialized for the two forms an expert
-// tensor of the 26B-A4B-style layer is stored in: Q4_K (gate_up, [experts][2 ff][hidden]) and
-// GGUF Q8_0 (down, [experts][hidden][ff] with ff = 704 = 22 blocks); everything else stays on the
-// generic kernel.
+// is nu_matvec_experts, kernels/experts.metal:16-36). Specialized for the forms an expert
+// tensor of the 26B-A4B-style layer is stored in: Q4_K (gate_up, [experts][2 ff][hidden]) and, for
+// down ([experts][hidden][ff] with ff = 704 = 22 blocks), GGUF Q8_0, Q5_0, Q5_1, Q4_0 and IQ4_NL;
+// everything else stays on the generic kernel.
 //
 // The work is a few to a few hundred megabytes spread over up to 64 small matrices picked by
 // device-side indices, so the kernels use plain loads instead of tensor maps (an expert's address is
@@ -329,6 +329,158 @@ __global__ void __launch_bounds__(X8_WARPS * 32) expert_gemv_q8_0_kernel(const u
     }
 }
 
+// ---- the 32-element blocks of four- and five-bit codes: Q5_0, Q5_1, Q4_0, IQ4_NL (GGUF rows) -------------------
+// The forms a 26B-A4B-style file keeps its down experts in (inference/src/models/gemma4.zig:259-268). The scheme is
+// the Q8_0 kernel's: the block's 32 weight rows travel to shared memory as 4-byte copies, a lane per row and a warp per
+// block of 32 columns, the digits of a block one broadcast address. What differs is how a block's bytes become the
+// 32 codes dp4a takes: the 16 nibble bytes hold elements 0..15 in their low and 16..31 in their high nibbles
+// (inference/src/quant/decode.zig:46-53), Q5_0 / Q5_1 add a bit from a 32-bit plane (:125-143), IQ4_NL looks the
+// nibble up in a table of signed bytes (:73-81). The offset (-16 d, -8 d, or m) multiplies the F32 sum of the
+// block's 32 inputs, prepared once with the digits.
+enum NibbleKind : int { NK_Q5_0 = 0, NK_Q5_1 = 1, NK_Q4_0 = 2, NK_IQ4_NL = 3 };
+
+// Four bits of x into bit 4 of four bytes: bit i of x lands on bit 8 i of x * 0x00204081 (no two terms meet).
+__device__ __forceinline__ uint32_t bits_to_bit4(uint32_t x) { return ((x * 0x00204081u) & 0x01010101u) << 4; }
+__device__ __forceinline__ uint32_t prmt_b32(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+// The IQ4_NL values of the four nibbles in the low 16 bits of n, as bytes in nibble order (the permute's sign-replicating
+// mode on n and n << 4 makes the mask that picks between the two halves of the table).
+__device__ __forceinline__ uint32_t iq4_bytes(uint32_t n) {
+    const uint32_t sel = n & 0x7777u;
+    const uint32_t lo = prmt_b32(0xbfad9881u, 0xf6eaddcfu, sel), hi = prmt_b32(0x26190d01u, 0x71594535u, sel);
+    const uint32_t upper = prmt_b32(n, n << 4, 0x9d8cu);
+    return (lo & ~upper) | (hi & upper);
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(X8_WARPS * 32) expert_gemv_nibble_kernel(const uint8_t *w, size_t stride, size_t expert_bytes, uint32_t experts, uint32_t rows,
+                                                                           uint32_t blocks, const uint32_t *indices, const float *in, size_t in_stride,
+                                                                           uint32_t in_group, float *out, size_t out_stride) {
+    constexpr uint32_t BS = KIND == NK_Q5_0 ? 22u : KIND == NK_Q5_1 ? 24u : 18u;          // bytes of a block
+    constexpr uint32_t QS = KIND == NK_Q5_0 ? 6u : KIND == NK_Q5_1 ? 8u : 2u;             // where its nibble bytes start
+    constexpr bool FIFTH = KIND == NK_Q5_0 || KIND == NK_Q5_1;
+    // [32 weight rows, `pitch` words each (+ one word: a shifted read may touch the word after a row)][3 planes of digits,
+    // blocks * 32 bytes each][blocks (inverse scale, sum of x) pairs][8 x 32 part sums]
+    extern __shared__ __align__(16) uint8_t smem[];
+    const uint32_t words = blocks * BS / 4;
+    const uint32_t pitch = words | 1u;
+    uint32_t *tile = (uint32_t *)smem;
+    uint8_t *planes = smem + (((size_t)(X8_ROWS * pitch + 1) * 4 + 15) & ~(size_t)15);
+    const uint32_t plane = blocks * 32;
+    float2 *chunk = (float2 *)(planes + 3 * plane);
+    float *parts = (float *)(chunk + blocks);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
+    const uint32_t slot = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t expert = min(indices[slot], experts - 1);
+    const uint32_t r0 = blockIdx.x * X8_ROWS;
+    const uint32_t nrows = min((uint32_t)X8_ROWS, rows - r0);
+    const uint8_t *base = w + (size_t)expert * expert_bytes + (size_t)r0 * stride;
+    for (uint32_t r = warp; r < nrows; r += X8_WARPS) {
+        const uint8_t *src = base + (size_t)r * stride;
+        uint32_t *dst = tile + r * pitch;
+        for (uint32_t c = lane; c < words; c += 32) cp_async4(dst + c, src + c * 4);
+    }
+    cp_async_commit();
+
+    const float *x = in + (size_t)(slot / in_group) * in_stride;
+    for (uint32_t b = warp; b < blocks; b += X8_WARPS) {
+        const float v = __ldg(x + b * 32 + lane);
+        float mx = fabsf(v), bad = 0.0f * v, sum = v;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            bad += __shfl_xor_sync(0xffffffffu, bad, o);
+            sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        }
+        mx += bad;
+        float scale, inv;
+        chunk_scale(mx, scale, inv);
+        int p0, p1, p2;
+        digits(v, scale, p0, p1, p2);
+        planes[b * 32 + lane] = (uint8_t)p0;
+        planes[plane + b * 32 + lane] = (uint8_t)p1;
+        planes[2 * plane + b * 32 + lane] = (uint8_t)p2;
+        if (lane == 0) chunk[b] = make_float2(inv, sum);
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+    float acc = 0.0f;
+    if (lane < nrows) {
+        const uint32_t *row = tile + lane * pitch;
+        for (uint32_t b = warp; b < blocks; b += X8_WARPS) {
+            // the block starts at byte BS b of the row, on a 2-byte boundary: its fields are read as aligned words shifted
+            // into place (the shift is the same for the whole warp)
+            const uint32_t off = b * BS, first = off >> 2, sh = (off & 2u) * 8u;
+            constexpr int NW = (int)(BS + 3) / 4 + 1;
+            uint32_t raw[NW];
+#pragma unroll
+            for (int i = 0; i < NW; ++i) raw[i] = row[first + i];
+            uint32_t f[NW - 1];  // the block's bytes from its start, as words
+#pragma unroll
+            for (int i = 0; i < NW - 1; ++i) f[i] = __funnelshift_r(raw[i], raw[i + 1], sh);
+            const float d = __half2float(__ushort_as_half((unsigned short)(f[0] & 0xffffu)));
+            // the nibble bytes start at byte QS of the block: 2 mod 4 (their words straddle those of f) except for Q5_1
+            uint32_t qs[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) qs[i] = __funnelshift_r(f[QS / 4 + i], f[QS / 4 + i + 1 < NW - 1 ? QS / 4 + i + 1 : NW - 2], (QS & 2u) * 8u);
+            uint32_t high = 0;
+            if (FIFTH) high = KIND == NK_Q5_0 ? __funnelshift_r(f[0], f[1], 16) : f[1];  // bytes 2..5 (Q5_0) or 4..7 (Q5_1)
+            uint32_t lo[4], hi[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (KIND == NK_IQ4_NL) {
+                    const uint32_t a = iq4_bytes(qs[i]), c = iq4_bytes(qs[i] >> 16);  // (lo0, hi0, lo1, hi1), (lo2, hi2, lo3, hi3)
+                    lo[i] = prmt_b32(a, c, 0x6420u);
+                    hi[i] = prmt_b32(a, c, 0x7531u);
+                } else {
+                    lo[i] = qs[i] & 0x0f0f0f0fu;
+                    hi[i] = (qs[i] >> 4) & 0x0f0f0f0fu;
+                    if (FIFTH) {
+                        lo[i] |= bits_to_bit4((high >> (4 * i)) & 15u);
+                        hi[i] |= bits_to_bit4((high >> (16 + 4 * i)) & 15u);
+                    }
+                }
+            }
+            const uint4 *dg = (const uint4 *)(planes + b * 32);
+            const uint4 *dg1 = (const uint4 *)(planes + plane + b * 32), *dg2 = (const uint4 *)(planes + 2 * plane + b * 32);
+            int a0 = 0, a1 = 0, a2 = 0;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint4 q0 = dg[h], q1 = dg1[h], q2 = dg2[h];
+                const uint32_t *c = h ? hi : lo;
+                if (KIND == NK_IQ4_NL) {
+                    a0 = dp4a_ss(c[0], q0.x, a0); a0 = dp4a_ss(c[1], q0.y, a0); a0 = dp4a_ss(c[2], q0.z, a0); a0 = dp4a_ss(c[3], q0.w, a0);
+                    a1 = dp4a_ss(c[0], q1.x, a1); a1 = dp4a_ss(c[1], q1.y, a1); a1 = dp4a_ss(c[2], q1.z, a1); a1 = dp4a_ss(c[3], q1.w, a1);
+                    a2 = dp4a_ss(c[0], q2.x, a2); a2 = dp4a_ss(c[1], q2.y, a2); a2 = dp4a_ss(c[2], q2.z, a2); a2 = dp4a_ss(c[3], q2.w, a2);
+                } else {
+                    a0 = dp4a_us(c[0], q0.x, a0); a0 = dp4a_us(c[1], q0.y, a0); a0 = dp4a_us(c[2], q0.z, a0); a0 = dp4a_us(c[3], q0.w, a0);
+                    a1 = dp4a_us(c[0], q1.x, a1); a1 = dp4a_us(c[1], q1.y, a1); a1 = dp4a_us(c[2], q1.z, a1); a1 = dp4a_us(c[3], q1.w, a1);
+                    a2 = dp4a_us(c[0], q2.x, a2); a2 = dp4a_us(c[1], q2.y, a2); a2 = dp4a_us(c[2], q2.z, a2); a2 = dp4a_us(c[3], q2.w, a2);
+                }
+            }
+            // a digit sum is below 2^18; times 2^14 it would not fit an int32: recombine in F32 (exact to 2^-24 relative)
+            const float v = (float)a2 * 16384.0f + ((float)a1 * 128.0f + (float)a0);
+            const float2 ch = chunk[b];
+            acc = fmaf(d * ch.x, v, acc);
+            if (KIND == NK_Q5_0) acc = fmaf(-16.0f * d, ch.y, acc);
+            if (KIND == NK_Q4_0) acc = fmaf(-8.0f * d, ch.y, acc);
+            if (KIND == NK_Q5_1) acc = fmaf(__half2float(__ushort_as_half((unsigned short)(f[0] >> 16))), ch.y, acc);
+        }
+    }
+    parts[warp * 32 + lane] = acc;
+    __syncthreads();
+    if (warp == 0 && lane < nrows) {
+        float sum = 0.0f;
+#pragma unroll
+        for (int k = 0; k < X8_WARPS; ++k) sum += parts[k * 32 + lane];
+        out[(size_t)slot * out_stride + r0 + lane] = sum;
+    }
+}
+
 }  // namespace
 
 constexpr uint32_t kMaxColumns = 16384;  // shared memory: about 4 bytes a column
@@ -337,7 +489,11 @@ constexpr uint32_t kMaxColumns = 16384;  // shared memory: about 4 bytes a colum
 // is current, so this runs once per handle, with the handle's device current (fast_configure).
 bool expert_gemv_configure() {
     return cudaFuncSetAttribute(expert_gemv_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(XQ_RING + kMaxColumns / 256 * (3 * 320 + 128))) == cudaSuccess &&
-           cudaFuncSetAttribute(expert_gemv_q8_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) == cudaSuccess;
+           cudaFuncSetAttribute(expert_gemv_q8_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) == cudaSuccess &&
+           cudaFuncSetAttribute(expert_gemv_nibble_kernel<NK_Q5_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) == cudaSuccess &&
+           cudaFuncSetAttribute(expert_gemv_nibble_kernel<NK_Q5_1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) == cudaSuccess &&
+           cudaFuncSetAttribute(expert_gemv_nibble_kernel<NK_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) == cudaSuccess &&
+           cudaFuncSetAttribute(expert_gemv_nibble_kernel<NK_IQ4_NL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) == cudaSuccess;
 }
 
 // Returns the number of kernels launched: 0 when the shape is not one of the specialized forms.
@@ -376,6 +532,25 @@ int launch_matvec_experts_fast(cudaStream_t s, uint32_t enc, const uint8_t *w, s
         cfg.blockDim = dim3(X8_WARPS * 32);
         cfg.dynamicSmemBytes = smem;
         cudaLaunchKernelEx(&cfg, expert_gemv_q8_0_kernel, w, stride, expert_bytes, experts, rows, blocks, indices, in, in_stride, in_group, out, out_stride);
+        return 1;
+    }
+    if (enc == Q5_0 || enc == Q5_1 || enc == Q4_0 || enc == IQ4_NL) {
+        // rows travel as 4-byte copies: rows of whole words (an even number of 18- or 22-byte blocks), rows and experts on
+        // 4-byte boundaries
+        const uint32_t bs = enc == Q5_0 ? 22u : enc == Q5_1 ? 24u : 18u;
+        if (columns % 32 != 0 || columns > kMaxColumns) return 0;
+        const uint32_t blocks = columns / 32;
+        if ((blocks * bs) % 4 != 0 || (uintptr_t)w % 4 != 0 || stride % 4 != 0 || expert_bytes % 4 != 0) return 0;
+        const uint32_t pitch = (blocks * bs / 4) | 1u;
+        const size_t smem = (((size_t)(X8_ROWS * pitch + 1) * 4 + 15) & ~(size_t)15) + (size_t)blocks * (3 * 32 + 8) + X8_WARPS * 32 * 4;
+        if (smem > 200 * 1024) return 0;
+        cfg.gridDim = dim3((rows + X8_ROWS - 1) / X8_ROWS, slots);
+        cfg.blockDim = dim3(X8_WARPS * 32);
+        cfg.dynamicSmemBytes = smem;
+        if (enc == Q5_0) cudaLaunchKernelEx(&cfg, expert_gemv_nibble_kernel<NK_Q5_0>, w, stride, expert_bytes, experts, rows, blocks, indices, in, in_stride, in_group, out, out_stride);
+        else if (enc == Q5_1) cudaLaunchKernelEx(&cfg, expert_gemv_nibble_kernel<NK_Q5_1>, w, stride, expert_bytes, experts, rows, blocks, indices, in, in_stride, in_group, out, out_stride);
+        else if (enc == Q4_0) cudaLaunchKernelEx(&cfg, expert_gemv_nibble_kernel<NK_Q4_0>, w, stride, expert_bytes, experts, rows, blocks, indices, in, in_stride, in_group, out, out_stride);
+        else cudaLaunchKernelEx(&cfg, expert_gemv_nibble_kernel<NK_IQ4_NL>, w, stride, expert_bytes, experts, rows, blocks, indices, in, in_stride, in_group, out, out_stride);
         return 1;
     }
     return 0;

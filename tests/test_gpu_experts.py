@@ -336,12 +336,14 @@ def test_gathered_matvec_reads_only_selected_experts(backend):
 
 
 @pytest.mark.parametrize("encoding,rows,cols", [(enc.Q4_K, 50, 768), (enc.Q4_K, 32, 256), (enc.Q4_K, 70, 2048), (enc.Q8_0, 37, 96), (enc.Q8_0, 37, 192), (enc.Q8_0, 8, 704), (enc.Q8_0, 150, 64),
-                                                (enc.Q6_K, 24, 512)])
+                                                (enc.Q6_K, 24, 512), (enc.Q5_0, 37, 192), (enc.Q5_0, 70, 704), (enc.Q5_1, 37, 96), (enc.Q5_1, 40, 704), (enc.Q4_0, 33, 128),
+                                                (enc.Q4_0, 64, 704), (enc.IQ4_NL, 37, 192), (enc.IQ4_NL, 8, 704), (enc.Q5_0, 20, 96), (enc.IQ4_XS, 24, 512)])
 @pytest.mark.parametrize("in_group", [1, 3])
 def test_expert_gemv_ragged_shapes(backend, encoding, rows, cols, in_group):
     """Row counts that do not fill a block, one to a few blocks per row, slots sharing an input row in groups
-    (ops/experts.zig:36-77: slot s reads input row s / in_group) — Q4_K and Q8_0 (an even number of blocks) on
-    the specialized kernels, the rest on the generic one, each against the oracle's matvec of the selected expert."""
+    (ops/experts.zig:36-77: slot s reads input row s / in_group) — Q4_K, and Q8_0, Q5_0, Q5_1, Q4_0, IQ4_NL with rows of
+    whole 32-bit words, on the specialized kernels, the rest (here also Q5_0 with three blocks a row) on the generic one,
+    each against the oracle's matvec of the selected expert."""
     experts, slots = 5, 7
     data = synth.matrix(encoding, experts * rows, cols, seed=40 + rows)
     per = data.size // experts
@@ -371,7 +373,7 @@ def test_expert_gemv_ragged_shapes(backend, encoding, rows, cols, in_group):
         backend.release(buf)
 
 
-@pytest.mark.parametrize("encoding,cols", [(enc.Q4_K, 512), (enc.Q8_0, 128)])
+@pytest.mark.parametrize("encoding,cols", [(enc.Q4_K, 512), (enc.Q8_0, 128), (enc.Q5_0, 128), (enc.Q5_1, 128), (enc.Q4_0, 128), (enc.IQ4_NL, 128)])
 def test_expert_gemv_extreme_inputs(backend, encoding, cols):
     """The specialized expert kernels turn the input row into fixed point per chunk of columns: rows scaled by
     1e+-20, a chunk of zeros and a chunk 2^40 times larger than its neighbours stay within the acceptance
