@@ -168,7 +168,7 @@ __device__ __forceinline__ uint32_t iq4_lookup4(uint32_t n) {
 
 // MODE: 0 the generic decoders (any encoding and layout), 1 Q4_K with 16-byte aligned rows, 2 planar Q6_K, 3 planar Q8_0,
 // 4 GGUF Q8_0 rows, 5 Q5_K with 16-byte aligned rows, 6 the planar forms of Q5_0, Q5_1, Q4_0, IQ4_NL and IQ4_XS,
-// 7 the planar forms of Q2_K and Q3_K.
+// 7 the planar forms of Q2_K and Q3_K, 8 GGUF rows of Q5_0, Q5_1, Q4_0 and IQ4_NL.
 // BPS: blocks per SM the instance is built for (registers capped accordingly). Two blocks of two stages share an SM's
 // shared and tensor memory: one block's epilogue and prologue run under the other's main loop.
 template <int BN, int STAGES, int MODE, int BPS>
@@ -518,6 +518,67 @@ __global__ void __launch_bounds__(THREADS, BPS) prefill_kernel(const __grid_cons
                 }
                 ok = put(chunks, piece * 4, piece * 4 + 2);
             }
+        } else if (MODE == 8) {
+            // GGUF rows of Q5_0, Q5_1, Q4_0 and IQ4_NL (blocks of 22, 24 and 18 bytes on 2-byte boundaries): what an expert
+            // tensor, which is never re-laid, is read as. Piece p takes block 2k + p of K step k. As for GGUF Q8_0 rows the
+            // block is fetched as the aligned 32-bit words around it and shifted into place; a word that only holds bytes
+            // past the block is read only when the shift needs it. The values are those of MODE 6.
+            const uint32_t enc = p.enc;
+            const bool fifth = enc == Q5_0 || enc == Q5_1, table = enc == IQ4_NL;
+            const uint32_t bs = enc == Q5_0 ? 22u : enc == Q5_1 ? 24u : 18u;
+            const uint8_t *blk = wbase + (size_t)grow * p.stride + piece * bs;
+            struct Raw { uint32_t w[7]; uint32_t sh; };
+            auto fetch = [&](const uint8_t *b8) {
+                Raw raw;
+                const uintptr_t at = (uintptr_t)b8;
+                const uint32_t *base = (const uint32_t *)(at & ~(uintptr_t)3);
+                raw.sh = (at & 2) ? 16u : 0u;
+                const uint32_t need = (bs + (raw.sh ? 2u : 0u) + 3u) / 4u;  // words that hold bytes of the block
+#pragma unroll
+                for (int i = 0; i < 7; ++i) raw.w[i] = (uint32_t)i < need ? __ldg(base + i) : 0u;
+                return raw;
+            };
+            Raw next = fetch(blk);
+            for (uint32_t k = 0; k < ksteps && ok; ++k) {
+                const Raw raw = next;
+                if (k + 1 < ksteps) {
+                    blk += 2 * bs;
+                    next = fetch(blk);
+                }
+                uint32_t f[6];  // the block's bytes from its start, as words
+#pragma unroll
+                for (int i = 0; i < 6; ++i) f[i] = __funnelshift_r(raw.w[i], raw.w[i + 1], raw.sh);
+                const float mul = __half2float(__ushort_as_half((unsigned short)(f[0] & 0xffffu)));
+                const float add = enc == Q5_1 ? __half2float(__ushort_as_half((unsigned short)(f[0] >> 16))) : enc == Q5_0 ? -16.0f * mul : enc == Q4_0 ? -8.0f * mul : -128.0f * mul;
+                const uint32_t high = enc == Q5_0 ? __funnelshift_r(f[0], f[1], 16) : f[1];  // bytes 2..5 (Q5_0) or 4..7 (Q5_1)
+                uint32_t lo[4], hi[4];
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    // the nibble bytes start at byte 6, 8 or 2 of the block
+                    const uint32_t q = enc == Q5_0 ? __funnelshift_r(f[1 + m], f[2 + m], 16) : enc == Q5_1 ? f[2 + m] : __funnelshift_r(f[m], f[1 + m], 16);
+                    if (table) {
+                        const uint32_t a = iq4_lookup4(q), b = iq4_lookup4(q >> 16);
+                        lo[m] = __byte_perm(a, b, 0x6420) ^ 0x80808080u;
+                        hi[m] = __byte_perm(a, b, 0x7531) ^ 0x80808080u;
+                    } else {
+                        lo[m] = q & 0x0f0f0f0fu;
+                        hi[m] = (q >> 4) & 0x0f0f0f0fu;
+                        if (fifth) {
+                            lo[m] |= bits4_to_bit4((high >> (4 * m)) & 15u);
+                            hi[m] |= bits4_to_bit4((high >> (16 + 4 * m)) & 15u);
+                        }
+                    }
+                }
+                uint4 chunks[4];
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    codes4_fma(lo[c * 2], mul, add, chunks[c].x, chunks[c].y);
+                    codes4_fma(lo[c * 2 + 1], mul, add, chunks[c].z, chunks[c].w);
+                    codes4_fma(hi[c * 2], mul, add, chunks[2 + c].x, chunks[2 + c].y);
+                    codes4_fma(hi[c * 2 + 1], mul, add, chunks[2 + c].z, chunks[2 + c].w);
+                }
+                ok = put(chunks, piece * 4, piece * 4 + 2);
+            }
         } else if (MODE == 7) {
             // The planar forms of Q2_K and Q3_K (prepare.cu, layouts 7 and 8). K step s of a superblock is the two-bit fields
             // 2 (s & 1) and 2 (s & 1) + 1 of the 32 code bytes of half s >> 1; piece p takes field j = 2 (s & 1) + p: 32
@@ -695,7 +756,7 @@ template <int BN, int STAGES, int BPS>
 static bool configure_bn() {
     return configure_one<BN, STAGES, 0, BPS>() && configure_one<BN, STAGES, 1, BPS>() && configure_one<BN, STAGES, 2, BPS>() && configure_one<BN, STAGES, 3, BPS>() &&
            configure_one<BN, STAGES, 4, BPS>() && configure_one<BN, STAGES, 5, BPS>() && configure_one<BN, STAGES, 6, BPS>() &&
-           configure_one<BN, STAGES, 7, BPS>();
+           configure_one<BN, STAGES, 7, BPS>() && configure_one<BN, STAGES, 8, BPS>();
 }
 
 bool prefill_configure() { return configure_bn<256, 4, 1>() && configure_bn<256, 2, 2>() && configure_bn<128, 6, 1>() && configure_bn<64, 8, 1>() && configure_bn<64, 4, 2>(); }
@@ -713,6 +774,7 @@ static void launch_bn(dim3 grid, cudaStream_t s, const prefill::Params &p, int m
     case 5: prefill::prefill_kernel<BN, STAGES, 5, BPS><<<grid, prefill::THREADS, bytes, s>>>(p); break;
     case 6: prefill::prefill_kernel<BN, STAGES, 6, BPS><<<grid, prefill::THREADS, bytes, s>>>(p); break;
     case 7: prefill::prefill_kernel<BN, STAGES, 7, BPS><<<grid, prefill::THREADS, bytes, s>>>(p); break;
+    case 8: prefill::prefill_kernel<BN, STAGES, 8, BPS><<<grid, prefill::THREADS, bytes, s>>>(p); break;
     default: prefill::prefill_kernel<BN, STAGES, 0, BPS><<<grid, prefill::THREADS, bytes, s>>>(p); break;
     }
 }
@@ -753,10 +815,11 @@ int launch_prefill(cudaStream_t s, const PrefillJob &j) {
     const bool q8_rows = j.layout == 0 && j.enc == Q8_0 && (uintptr_t)j.w % 4 == 0 && j.stride % 2 == 0;
     const bool q5k_rows = j.layout == 0 && j.enc == Q5_K && (uintptr_t)j.w % 16 == 0 && j.stride % 16 == 0 && j.columns % 256 == 0;
     const bool block32 = j.layout >= 3 && j.layout <= 6;
-    const int mode = q8_rows ? 4 : q5k_rows ? 5 : block32 ? 6 : (j.layout == 7 || j.layout == 8) ? 7 : !p.fast ? 0 : j.enc == Q4_K ? 1 : j.layout == 1 ? 2 : 3;
+    const bool nibble_rows = j.layout == 0 && (j.enc == Q5_0 || j.enc == Q5_1 || j.enc == Q4_0 || j.enc == IQ4_NL) && (uintptr_t)j.w % 4 == 0 && j.stride % 2 == 0;
+    const int mode = q8_rows ? 4 : q5k_rows ? 5 : block32 ? 6 : nibble_rows ? 8 : (j.layout == 7 || j.layout == 8) ? 7 : !p.fast ? 0 : j.enc == Q4_K ? 1 : j.layout == 1 ? 2 : 3;
     // Two blocks per SM (two stages each) when there are more blocks than SMs and the decoder is light enough for the
     // smaller register budget (measured: Q4_K 933 -> 1,067 TFLOP/s; planar Q6_K loses a little).
-    const bool two = bn == 256 && (mode == 1 || mode == 3 || mode == 4 || mode == 5 || mode == 6 || mode == 7) && (size_t)grid.x * grid.y > (size_t)j.sm_count;
+    const bool two = bn == 256 && (mode == 1 || mode == 3 || mode == 4 || mode == 5 || mode == 6 || mode == 7 || mode == 8) && (size_t)grid.x * grid.y > (size_t)j.sm_count;
     if (two) launch_bn<256, 2, 2>(grid, s, p, mode);
     else if (bn == 256) launch_bn<256, 4, 1>(grid, s, p, mode);
     else if (bn == 128) launch_bn<128, 6, 1>(grid, s, p, mode);
@@ -845,7 +908,9 @@ int launch_matmul_experts_fast(cudaStream_t s, uint32_t enc, const uint8_t *w, s
     // Two blocks of four stages per SM: with 64-row tiles the block is bound by its eight decoding warps, not by the tensor
     // core, and a second block doubles them (measured at 4,096 slot rows over 128 experts: the gate_up GEMM 425 -> see bench).
     const bool q8_rows = enc == Q8_0 && (uintptr_t)w % 4 == 0 && stride % 2 == 0 && expert_bytes % 4 == 0;
-    launch_bn<64, 4, 2>(grid, s, p, p.fast ? 1 : q8_rows ? 4 : 0);
+    const bool nibble_rows = (enc == Q5_0 || enc == Q5_1 || enc == Q4_0 || enc == IQ4_NL) && (uintptr_t)w % 4 == 0 && stride % 2 == 0 && expert_bytes % 4 == 0;
+    const bool q5k_rows = enc == Q5_K && (uintptr_t)w % 16 == 0 && stride % 16 == 0 && expert_bytes % 16 == 0 && columns % 256 == 0;
+    launch_bn<64, 4, 2>(grid, s, p, p.fast ? 1 : q8_rows ? 4 : q5k_rows ? 5 : nibble_rows ? 8 : 0);
     return 2;
 }
 

@@ -301,6 +301,44 @@ def test_grouped_prefill_on_the_tensor_cores_matches_cpu_ffn(backend, tensors, t
         backend.release(buf)
 
 
+@pytest.mark.parametrize("encoding", [enc.Q5_0, enc.Q5_1, enc.Q4_0, enc.IQ4_NL, enc.Q5_K])
+def test_grouped_prefill_reads_the_other_expert_encodings(backend, encoding):
+    """`matmulExperts` on an expert tensor stored in the forms real files use for their down experts (GGUF rows, never
+    re-laid): each sampled slot row against the oracle's matvec of its expert on the bf16-rounded input, at the bounds
+    of the dense prefill."""
+    from test_gpu_prefill import from_bf16_bits, to_bf16_bits
+    experts, rows, cols, tokens, k = 8, 136, 768, 160, 2
+    data = synth.matrix(encoding, experts * rows, cols, seed=950 + encoding)
+    per = data.size // experts
+    t = ExpertMatrix(encoding, experts, rows, cols, data.size)
+    rng = np.random.default_rng(encoding)
+    slots = tokens * k
+    x = rng.standard_normal((slots, cols)).astype(np.float32)
+    idx = rng.integers(0, experts, size=slots).astype(np.uint32)
+    wb = backend.wrap(data)
+    xb = backend.create(x.nbytes); xb.write(x)
+    ib = backend.create(slots * 4); ib.write(idx)
+    lists = backend.create(Backend.expert_lists_words(slots, experts) * 4)
+    y = backend.create(slots * rows * 4)
+    y.write(np.full(slots * rows, np.nan, dtype=np.float32))
+    backend.begin()
+    backend.expert_lists(ib, tokens, k, experts, lists)
+    backend.matmul_experts(wb, t, lists, tokens, k, xb, cols, 1, y, rows)
+    backend.commit()
+    got = y.floats().reshape(slots, rows)
+    assert np.all(np.isfinite(got))
+    for s in list(range(0, slots, 13)) + [slots - 1]:
+        e = int(idx[s])
+        xr = from_bf16_bits(to_bf16_bits(x[s]))
+        w_e = data[e * per:(e + 1) * per]
+        want = oracle.matvec(encoding, rows, cols, w_e, xr)
+        mag = oracle.matvec_abs(encoding, rows, cols, w_e, xr)
+        assert np.max(np.abs(got[s] - want) / (4e-3 * mag + 1e-6)) <= 1.0 and np.linalg.norm(got[s] - want) <= 2e-2 * np.linalg.norm(want), s
+    backend.unwrap(data)
+    for buf in (xb, ib, lists, y):
+        backend.release(buf)
+
+
 def test_gathered_matvec_reads_only_selected_experts(backend):
     # unselected experts hold NaN-decoding bytes (scale 0x7e00): a stray read poisons the output
     experts, rows, cols = 6, 32, 256
