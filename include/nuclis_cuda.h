@@ -224,6 +224,20 @@ size_t nu_cuda_matmul_padded(size_t tokens);
 int nu_cuda_matvec_segments(nu_cuda *h, const nu_segment *segments, size_t count,
                             const nu_buffer *input, uint32_t mode);
 
+/* `Backend.addRmsNorm` followed by `Backend.matvecSegments` on its output (ops/rowwise.zig:76-93, then
+ * ops/matvec.zig:245-343; the pair a decoder layer runs ahead of its projections,
+ * inference/src/models/qwen35_metal.zig:635-640) as ONE launch: the kernel's staging pass, which reads the whole
+ * input row in every block anyway, adds, takes the mean square and scales. No single call of the reference does
+ * this. The rows the segments multiply are norm(residual + input) * weight with `eps` inside the root;
+ * residual + input is written to `residual_out`, which must not overlap `residual` or `input` (every block reads
+ * them while one writes the sum: keep two residual buffers and swap them). `input` and `residual_out` may both be
+ * null: then it is `rmsNorm` + `matvecSegments`. One token row; buffers 16-byte aligned. Returns
+ * NU_ERR_MERGE_DECLINED, with nothing recorded, when the specialized kernel does not serve the segments: the caller
+ * then runs the two operators. */
+int nu_cuda_matvec_segments_normed(nu_cuda *h, const nu_segment *segments, size_t count, const nu_buffer *residual,
+                                   const nu_buffer *input, const nu_buffer *weight, const nu_buffer *residual_out,
+                                   float eps, uint32_t mode);
+
 /* `Backend.siluMul`, `Backend.geluMul` (ops/rowwise.zig:209, 230): gate[i] = act(gate[i]) * up[i]. */
 int nu_cuda_silu_mul(nu_cuda *h, const nu_buffer *gate, const nu_buffer *up, size_t count);
 int nu_cuda_gelu_mul(nu_cuda *h, const nu_buffer *gate, const nu_buffer *up, size_t count);

@@ -284,6 +284,18 @@ class Backend:
             arr[i] = _lib.CSegment(s.weights._c(), s.matrix._c(), s.output._c())
         self._check(self._lib.nu_cuda_matvec_segments(self._h, arr, len(segments), input._c(), int(mode)))
 
+    def matvec_segments_normed(self, segments: list[Segment], residual: Buffer, weight: Buffer, input: Buffer | None = None,
+                               residual_out: Buffer | None = None, eps: float = 1e-6, mode: SegmentMode = SegmentMode.plain) -> None:
+        """``addRmsNorm`` (ops/rowwise.zig:76-93) and ``matvecSegments`` on its output as one launch: the segments multiply
+        norm(residual + input) * weight, and residual + input goes to ``residual_out`` (a buffer of its own). Without
+        ``input`` / ``residual_out``: ``rmsNorm`` + ``matvecSegments``. Raises MergeDeclined when the specialized kernel
+        does not serve the segments."""
+        arr = (_lib.CSegment * max(len(segments), 1))()
+        for i, s in enumerate(segments):
+            arr[i] = _lib.CSegment(s.weights._c(), s.matrix._c(), s.output._c())
+        self._check(self._lib.nu_cuda_matvec_segments_normed(self._h, arr, len(segments), residual._c(), input._c() if input is not None else None, weight._c(),
+                                                             residual_out._c() if residual_out is not None else None, eps, int(mode)))
+
     def silu_mul(self, gate: Buffer, up: Buffer, count: int) -> None:
         self._check(self._lib.nu_cuda_silu_mul(self._h, gate._c(), up._c(), count))
 

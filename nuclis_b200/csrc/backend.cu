@@ -584,7 +584,7 @@ int Backend::matmul(const Buffer &weights, const Matrix &m, const Buffer &input,
 }
 
 // ops/matvec.zig:268-343.
-int Backend::matvecSegments(const Segment *segments, size_t count, const Buffer &input, uint32_t mode) {
+int Backend::segmentsJob(const Segment *segments, size_t count, const Buffer &input, uint32_t mode, const NormFuse *norm) {
     if (!segments || count == 0 || count > 4) return fail(NU_ERR_INVALID_SHAPE, "segments: 1..4 segments");
     if (mode > NU_SEGMENTS_GELU_MUL_PAIR) return fail(NU_ERR_INVALID_SHAPE, "segments: mode");
     const size_t columns = segments[0].matrix.columns;
@@ -624,12 +624,49 @@ int Backend::matvecSegments(const Segment *segments, size_t count, const Buffer 
     // One launch needs one unpacker: a merge of mixed encodings, or one the
     // specialized kernel does not serve, is declined before anything is
     // recorded and the caller runs the segments alone (ops/matvec.zig:245-257).
+    if (norm) {
+        job.norm_weight = norm->weight; job.norm_input = norm->input; job.residual_out = norm->residual_out; job.norm_eps = norm->eps;
+    }
     if (generic_only || !same_encoding || !fast_supported(job)) return fail(NU_ERR_MERGE_DECLINED, "segments: merge declined");
     if (int rc = needRecording(true)) return rc;
     if (int rc = chainOrLaunch(job)) return rc;
+    if (norm && norm->out_buffer) wrote(*norm->out_buffer);
     for (size_t i = 0; i < count; ++i) wrote(segments[i].output);
     opBoundary();
     return cuda(cudaGetLastError(), "segments: launch");
+}
+
+// No reference analogue as one call: `addRmsNorm` (ops/rowwise.zig:76-93) followed by `matvecSegments` on its output
+// (inference/src/models/qwen35_metal.zig:635-640), as one launch. The rows the projections multiply are
+// norm(residual + input) * weight; residual + input goes to residual_out, which must be a buffer of its own (every
+// block of the launch reads residual and input while one of them writes the sum). Declined like a merge when the
+// specialized kernel does not serve the segments: the caller then runs the two operators.
+int Backend::matvecSegmentsNormed(const Segment *segments, size_t count, const Buffer &residual, const Buffer *input, const Buffer &weight, const Buffer *residual_out,
+                                  float eps, uint32_t mode) {
+    if (!segments || count == 0 || count > 4) return fail(NU_ERR_INVALID_SHAPE, "segments_normed: 1..4 segments");
+    const size_t columns = segments[0].matrix.columns;
+    if (columns == 0 || columns > 0xffffffffull / 4 || !(eps > 0)) return fail(NU_ERR_INVALID_SHAPE, "segments_normed: shape");
+    if ((input != nullptr) != (residual_out != nullptr)) return fail(NU_ERR_INVALID_SHAPE, "segments_normed: input and residual_out go together");
+    NormFuse norm{};
+    norm.weight = (const float *)resolve(weight, columns * 4);
+    norm.input = input ? (const float *)resolve(*input, columns * 4) : nullptr;
+    norm.residual_out = residual_out ? (float *)resolve(*residual_out, columns * 4) : nullptr;
+    norm.eps = eps;
+    norm.out_buffer = residual_out;
+    if (!norm.weight || weight.offset % 16 != 0 || residual.offset % 16 != 0) return fail(NU_ERR_INVALID_SHAPE, "segments_normed: weight too short or not 16-byte aligned");
+    if (input) {
+        if (!norm.input || !norm.residual_out || input->offset % 16 != 0 || residual_out->offset % 16 != 0) return fail(NU_ERR_INVALID_SHAPE, "segments_normed: buffer too short or not 16-byte aligned");
+        if (overlaps(*residual_out, columns * 4, residual, columns * 4) || overlaps(*residual_out, columns * 4, *input, columns * 4) ||
+            overlaps(*residual_out, columns * 4, weight, columns * 4))
+            return fail(NU_ERR_INVALID_SHAPE, "segments_normed: residual_out overlaps an input");
+        for (size_t i = 0; i < count; ++i)
+            if (overlaps(*residual_out, columns * 4, segments[i].output, segments[i].matrix.rows * 4) || overlaps(*residual_out, columns * 4, segments[i].weights, segments[i].matrix.bytes))
+                return fail(NU_ERR_INVALID_SHAPE, "segments_normed: residual_out overlaps a segment");
+    }
+    for (size_t i = 0; i < count; ++i)
+        if (overlaps(segments[i].output, segments[i].matrix.rows * 4, weight, columns * 4) || (input && overlaps(segments[i].output, segments[i].matrix.rows * 4, *input, columns * 4)))
+            return fail(NU_ERR_INVALID_SHAPE, "segments_normed: an output overlaps the norm's inputs");
+    return segmentsJob(segments, count, residual, mode, &norm);
 }
 
 // ops/rowwise.zig:209-212, 230-233.
@@ -1150,6 +1187,11 @@ size_t nu_cuda_matmul_padded(size_t tokens) { return nu::Backend::matmulPadded(t
 int nu_cuda_matvec_segments(nu_cuda *h, const nu_segment *segments, size_t count, const nu_buffer *input, uint32_t mode) {
     NU_H(h); NU_P(input);
     return h->b->matvecSegments(segments, count, *input, mode);
+}
+int nu_cuda_matvec_segments_normed(nu_cuda *h, const nu_segment *segments, size_t count, const nu_buffer *residual, const nu_buffer *input, const nu_buffer *weight,
+                                   const nu_buffer *residual_out, float eps, uint32_t mode) {
+    NU_H(h); NU_P(segments && residual && weight);
+    return h->b->matvecSegmentsNormed(segments, count, *residual, input, *weight, residual_out, eps, mode);
 }
 int nu_cuda_silu_mul(nu_cuda *h, const nu_buffer *gate, const nu_buffer *up, size_t count) {
     NU_H(h); NU_P(gate && up);

@@ -71,7 +71,9 @@ public:
                    const Buffer &output, size_t out_stride, size_t tokens);
     int matmul(const Buffer &weights, const Matrix &matrix, const Buffer &input, uint32_t in_dtype, size_t in_stride,
                const Buffer &output, size_t out_stride, size_t tokens);
-    int matvecSegments(const Segment *segments, size_t count, const Buffer &input, uint32_t mode);
+    int matvecSegments(const Segment *segments, size_t count, const Buffer &input, uint32_t mode) { return segmentsJob(segments, count, input, mode, nullptr); }
+    int matvecSegmentsNormed(const Segment *segments, size_t count, const Buffer &residual, const Buffer *input, const Buffer &weight, const Buffer *residual_out,
+                             float eps, uint32_t mode);
     int actMul(uint32_t act, const Buffer &gate, const Buffer &up, size_t count);
     int rmsNorm(const Buffer &input, const Buffer &weight, const Buffer &output, const nu_norm &spec);
     int addRmsNorm(const Buffer &residual, const Buffer &input, const Buffer &weight, const Buffer &output, const nu_norm &spec);
@@ -165,6 +167,14 @@ private:
     FastChain *chain_ = nullptr;
     int flushChain();
     int chainOrLaunch(const FastJob &job);
+    // The add + RMS norm a merged launch folds into its staging pass: device pointers, resolved and checked.
+    struct NormFuse {
+        const float *weight, *input;
+        float *residual_out;
+        float eps;
+        const Buffer *out_buffer;  // what residual_out belongs to (marked written), or null
+    };
+    int segmentsJob(const Segment *segments, size_t count, const Buffer &input, uint32_t mode, const NormFuse *norm);
     unsigned long long peer_wait_ns_ = 2000000000ull;
 };
 

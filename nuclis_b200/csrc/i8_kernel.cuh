@@ -63,6 +63,13 @@ struct Params {
     uint32_t *counters;      // per unit
     uint32_t *status;        // set to 1 if a bounded wait ran out
     PushTarget push;         // ranks > 0: output rows go to the ranks' inboxes instead of `out`
+    // The add + RMS norm ahead of the projections, folded into the staging pass when norm_weight is set: the rows the
+    // kernel multiplies are (in + norm_input) * rsqrt(mean((in + norm_input)^2) + norm_eps) * norm_weight; block 0 writes
+    // in + norm_input to residual_out. norm_input and residual_out may be null; all three row sets share in_stride.
+    const float *norm_weight;
+    const float *norm_input;
+    float *residual_out;
+    float norm_eps;
 };
 
 // C = A(16 x 32, unsigned bytes) x B(32 x 8, signed bytes), int32, starting from zero.
@@ -171,7 +178,7 @@ __device__ __forceinline__ void write_unit(const Params &p, uint32_t unit, uint3
 // The barriers sit at a fixed place, a fixed distance apart per unit slot, so that the operators of a chain
 // (gemv_chain.cu), whose geometries differ, find the barriers the operator before them left.
 constexpr int kMaxStages = 5;
-constexpr int kBarBytes = 3584;               // 8 unit slots x (kMaxStages full + kMaxStages empty) x 8 bytes = 640, then room for two
+constexpr int kBarBytes = 3712;               // 8 unit slots x (kMaxStages full + kMaxStages empty) x 8 bytes = 640, then room for two
                                               // copies of an operator's Params (a chain keeps the current and the next one there)
 constexpr int kParamsAt = 768;                // the first copy; the second follows it
 static_assert(kParamsAt + 2 * sizeof(Params) <= kBarBytes && sizeof(Params) % 16 == 0, "the head of shared memory holds two Params");
@@ -338,6 +345,39 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
     // 16-bit reciprocal, exact for the few hundred pairs of a slice)
     const uint32_t ntok = NT <= 2 ? (uint32_t)NT : p.tokens, rtok = (65536u + ntok - 1u) / ntok;
     const uint32_t pairs = n * ntok;
+    // The fused add + RMS norm: every block reads the whole rows once for their mean squares (the slice it stages is
+    // not enough), block 0 also writes the sums of the add. The scratch is the part sums' memory, not in use yet:
+    // [0, 32) the warps' sums, [32, 40) 1 / rms of the tokens.
+    const bool normed = p.norm_weight != nullptr;
+    float *nscratch = (float *)parts;
+    if (normed) {
+        const uint32_t pieces = p.ksb * 64;
+        for (uint32_t tok = 0; tok < ntok; ++tok) {
+            const float4 *r4 = (const float4 *)(p.in + (size_t)tok * p.in_stride);
+            const float4 *a4 = p.norm_input ? (const float4 *)(p.norm_input + (size_t)tok * p.in_stride) : nullptr;
+            float4 *o4 = (p.residual_out && blockIdx.x == 0) ? (float4 *)(p.residual_out + (size_t)tok * p.in_stride) : nullptr;
+            float sum = 0.0f;
+            for (uint32_t i = tid; i < pieces; i += G::THREADS) {
+                float4 v = __ldcg(r4 + i);
+                if (a4) {
+                    const float4 a = __ldcg(a4 + i);
+                    v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+                }
+                if (o4) o4[i] = v;
+                sum += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if (lane == 0) nscratch[warp] = sum;
+            named_barrier(15, G::THREADS);
+            if (tid == 0) {
+                float total = 0.0f;
+                for (int w2 = 0; w2 < WARPS; ++w2) total += nscratch[w2];
+                nscratch[32 + tok] = rsqrtf(total / (float)(p.ksb * 256u) + p.norm_eps);
+            }
+            named_barrier(15, G::THREADS);
+        }
+    }
     for (uint32_t pass0 = 0; pass0 < pairs; pass0 += SBW * WARPS) {
         float4 xa[SBW], xb2[SBW];
 #pragma unroll
@@ -348,6 +388,20 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
                 const float4 *src = (const float4 *)(p.in + (size_t)tok * p.in_stride) + (size_t)(sb0 + sb) * 64;
                 xa[j] = __ldcg(src + lane);  // L2: in a chain another block wrote them during this launch
                 xb2[j] = __ldcg(src + 32 + lane);
+                if (normed) {
+                    const size_t col4 = (size_t)(sb0 + sb) * 64;
+                    if (p.norm_input) {
+                        const float4 *s2 = (const float4 *)(p.norm_input + (size_t)tok * p.in_stride) + col4;
+                        const float4 a = __ldcg(s2 + lane), b = __ldcg(s2 + 32 + lane);
+                        xa[j].x += a.x; xa[j].y += a.y; xa[j].z += a.z; xa[j].w += a.w;
+                        xb2[j].x += b.x; xb2[j].y += b.y; xb2[j].z += b.z; xb2[j].w += b.w;
+                    }
+                    const float4 *wv = (const float4 *)p.norm_weight + col4;
+                    const float4 wa = __ldg(wv + lane), wb = __ldg(wv + 32 + lane);
+                    const float r = nscratch[32 + tok];
+                    xa[j] = make_float4(xa[j].x * r * wa.x, xa[j].y * r * wa.y, xa[j].z * r * wa.z, xa[j].w * r * wa.w);
+                    xb2[j] = make_float4(xb2[j].x * r * wb.x, xb2[j].y * r * wb.y, xb2[j].z * r * wb.z, xb2[j].w * r * wb.w);
+                }
             }
         }
 #pragma unroll
@@ -732,6 +786,11 @@ static bool fill_geometry(const FastJob &job, Params &p, Plan &plan) {
     p.status = job.counters + job.counters_len;
     p.push = job.push;
     if (p.push.ranks && (job.mode != ACT_NONE || job.count != 1 || job.tokens != 1)) return false;  // one plain matrix, one token only
+    p.norm_weight = job.norm_weight;
+    p.norm_input = job.norm_input;
+    p.residual_out = job.residual_out;
+    p.norm_eps = job.norm_eps;
+    if (job.norm_weight && ((uintptr_t)job.norm_weight % 16 != 0 || (uintptr_t)job.norm_input % 16 != 0 || (uintptr_t)job.residual_out % 16 != 0)) return false;
     return true;
 }
 

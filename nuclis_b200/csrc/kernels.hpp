@@ -92,6 +92,13 @@ struct FastJob {
     int sm_count;
     bool serial;  // a weights buffer was written earlier in the same recording: no early start of the weight stream
     PushTarget push;
+    // The add + RMS norm ahead of the projections, folded into the kernel's staging pass when norm_weight is set
+    // (i8_kernel.cuh, Params): `in` is then the residual rows, norm_input what is added to them (or null),
+    // residual_out where the sums go (or null); all at in_stride.
+    const float *norm_weight;
+    const float *norm_input;
+    float *residual_out;
+    float norm_eps;
 };
 // Opts every variant into its dynamic shared memory size; once per device, outside any capture.
 bool fast_configure();

@@ -280,3 +280,76 @@ def test_norms_around_the_projections_match_the_oracle(backend, rows, width, pad
     assert np.array_equal(inplace, got)
     for buf in (xb, sb, wb, yb, x2):
         b.release(buf)
+
+
+@pytest.mark.parametrize("encoding,prepare", [(enc.Q4_K, False), (enc.Q5_K, False), (enc.Q6_K, True), (enc.Q8_0, True), (enc.Q5_0, True)])
+@pytest.mark.parametrize("shape", [(1056, 1280), (17408, 5120)])
+@pytest.mark.parametrize("with_add", [True, False])
+def test_add_rms_norm_folded_into_the_projections(backend, encoding, prepare, shape, with_add):
+    """`matvec_segments_normed`: `addRmsNorm` (ops/rowwise.zig:76-93) and the gate/up pair on its output
+    (inference/src/models/qwen35_metal.zig:635-640) as one launch. The product against the oracle on the CPU norm's
+    output (vector.zig:53-64: F64 sum of squares); residual + input bit for bit in the second residual buffer; and the
+    two separate operators agree with the one launch to the accuracy of the fixed-point staging."""
+    b = backend
+    rows, columns = shape
+    rng = np.random.default_rng(rows + columns)
+    res = (rng.standard_normal(columns) * 3).astype(np.float32)
+    inp = rng.standard_normal(columns).astype(np.float32)
+    wn = (1.0 + 0.1 * rng.standard_normal(columns)).astype(np.float32)
+    rb, ib, wnb, ob, yb = upload(b, res), upload(b, inp), upload(b, wn), b.create(columns * 4), b.create(columns * 4)
+    gb, m, wg = weights(b, encoding, rows, columns, 51, prepare)
+    ub, _, wu = weights(b, encoding, rows, columns, 52, prepare)
+    out, out2 = b.create(rows * 4), b.create(rows * 4)
+    ob.write(np.full(columns, np.nan, dtype=np.float32))
+    before = b.launch_count
+    b.begin()
+    b.matvec_segments_normed([Segment(gb, m, out), Segment(ub, m, out)], rb, wnb, input=ib if with_add else None, residual_out=ob if with_add else None,
+                             mode=SegmentMode.silu_mul_pair)
+    b.commit()
+    assert b.launch_count - before == 1
+    summed = res + inp if with_add else res
+    if with_add:
+        assert np.array_equal(ob.floats(), summed)
+    assert np.array_equal(rb.floats(), res)          # the residual that came in is not touched
+    xn = (oracle.rms_norm(summed).astype(np.float64) * wn).astype(np.float32)
+    g = oracle.matvec(encoding, rows, columns, wg, xn)
+    u = oracle.matvec(encoding, rows, columns, wu, xn)
+    want = oracle.silu(g).astype(np.float64) * u.astype(np.float64)
+    got = out.floats()[:rows]
+    assert rel_l2(got, want) <= 1e-5
+    # the two operators on their own
+    b.begin()
+    if with_add:
+        b.add_rms_norm(rb, ib, wnb, yb, 1, columns)
+    else:
+        b.rms_norm(rb, wnb, yb, 1, columns)
+    b.matvec_segments([Segment(gb, m, out2), Segment(ub, m, out2)], yb, SegmentMode.silu_mul_pair)
+    b.commit()
+    assert rel_l2(got, out2.floats()[:rows].astype(np.float64)) <= 2e-6
+    for buf in (rb, ib, wnb, ob, yb, gb, ub, out, out2):
+        b.release(buf)
+
+
+def test_folded_norm_contract(backend):
+    b = backend
+    columns, rows = 1280, 256
+    x = synth.activations(1, columns, 3)[0]
+    rb, ib, wnb, ob = upload(b, x), upload(b, x), upload(b, np.ones(columns, dtype=np.float32)), b.create(columns * 4)
+    a, ma, _ = weights(b, enc.Q4_K, rows, columns, 61, False)
+    c, mc, _ = weights(b, enc.Q6_K, rows, columns, 62, False)   # GGUF-form Q6_K: not served by the specialized kernel
+    o1 = b.create(rows * 4)
+    b.begin()
+    try:
+        with pytest.raises(NuclisError):
+            b.matvec_segments_normed([Segment(a, ma, o1)], rb, wnb, input=ib, residual_out=rb)        # the sum would land on the residual being read
+        with pytest.raises(NuclisError):
+            b.matvec_segments_normed([Segment(a, ma, o1)], rb, wnb, input=ib)                         # input without a place for the sum
+        with pytest.raises(NuclisError):
+            b.matvec_segments_normed([Segment(a, ma, o1)], rb, wnb, input=ib, residual_out=ob, eps=0.0)
+        with pytest.raises(NuclisError) as e:
+            b.matvec_segments_normed([Segment(c, mc, o1)], rb, wnb, input=ib, residual_out=ob)
+        assert e.value.status == 5   # MergeDeclined: the caller runs addRmsNorm and the matvec
+    finally:
+        b.discard()
+    for buf in (rb, ib, wnb, ob, a, c, o1):
+        b.release(buf)
