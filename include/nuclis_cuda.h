@@ -224,6 +224,15 @@ size_t nu_cuda_matmul_padded(size_t tokens);
 int nu_cuda_matvec_segments(nu_cuda *h, const nu_segment *segments, size_t count,
                             const nu_buffer *input, uint32_t mode);
 
+/* `Backend.matvec` followed by the residual `Backend.add` of its output (ops/matvec.zig:85-116, then
+ * ops/rowwise.zig:199-202; what a decoder layer does behind its O and down projections,
+ * inference/src/models/qwen35_metal.zig:640) as one launch: output = residual + W x, the add folded into the
+ * kernel's write. No single call of the reference does this. `output` may be `residual` itself; any other overlap
+ * is refused. A matrix the specialized kernels do not serve takes the generic matvec and the add: the call never
+ * declines. */
+int nu_cuda_matvec_add(nu_cuda *h, const nu_buffer *weights, const nu_matrix *matrix, const nu_buffer *input,
+                       const nu_buffer *residual, const nu_buffer *output);
+
 /* `Backend.addRmsNorm` followed by `Backend.matvecSegments` on its output (ops/rowwise.zig:76-93, then
  * ops/matvec.zig:245-343; the pair a decoder layer runs ahead of its projections,
  * inference/src/models/qwen35_metal.zig:635-640) as ONE launch: the kernel's staging pass, which reads the whole

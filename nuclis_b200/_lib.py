@@ -75,6 +75,7 @@ SIGNATURES = {
     "nu_cuda_matvec_rows": (cint, [vp, BP, MP, BP, sz, BP, sz, sz]),
     "nu_cuda_matmul": (cint, [vp, BP, MP, BP, u32, sz, BP, sz, sz]),
     "nu_cuda_matmul_padded": (sz, [sz]),
+    "nu_cuda_matvec_add": (cint, [vp, BP, MP, BP, BP, BP]),
     "nu_cuda_matvec_segments": (cint, [vp, SP, sz, BP, u32]),
     "nu_cuda_matvec_segments_normed": (cint, [vp, SP, sz, BP, BP, BP, BP, ctypes.c_float, u32]),
     "nu_cuda_silu_mul": (cint, [vp, BP, BP, sz]),

@@ -267,6 +267,11 @@ class Backend:
     def matvec(self, weights: Buffer, matrix: Matrix, input: Buffer, output: Buffer) -> None:
         self._check(self._lib.nu_cuda_matvec(self._h, weights._c(), matrix._c(), input._c(), output._c()))
 
+    def matvec_add(self, weights: Buffer, matrix: Matrix, input: Buffer, residual: Buffer, output: Buffer) -> None:
+        """``matvec`` and the residual ``add`` of its output (ops/matvec.zig:85-116, ops/rowwise.zig:199-202) as one launch:
+        output = residual + W x; ``output`` may be ``residual``."""
+        self._check(self._lib.nu_cuda_matvec_add(self._h, weights._c(), matrix._c(), input._c(), residual._c(), output._c()))
+
     def matvec_rows(self, weights: Buffer, matrix: Matrix, input: Buffer, in_stride: int, output: Buffer, out_stride: int, tokens: int) -> None:
         self._check(self._lib.nu_cuda_matvec_rows(self._h, weights._c(), matrix._c(), input._c(), in_stride, output._c(), out_stride, tokens))
 

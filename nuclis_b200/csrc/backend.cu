@@ -493,6 +493,46 @@ int Backend::matvec(const Buffer &weights, const Matrix &m, const Buffer &input,
     return cuda(cudaGetLastError(), "matvec: launch");
 }
 
+// No reference analogue as one call: `matvec` followed by the residual `add` of its output
+// (ops/matvec.zig:85-116, ops/rowwise.zig:199-202; inference/src/models/qwen35_metal.zig:640): output = residual + W x,
+// the add folded into the kernel's write. `output` may be `residual` itself. Matrices the specialized kernel does not
+// serve take the generic matvec and the add as two launches: the call never declines.
+int Backend::matvecAdd(const Buffer &weights, const Matrix &m, const Buffer &input, const Buffer &residual, const Buffer &output) {
+    if (m.rows == 0 || m.columns == 0 || m.columns % 16 != 0 || m.bytes % m.rows != 0) return fail(NU_ERR_INVALID_SHAPE, "matvec_add: shape");
+    const size_t stride = m.bytes / m.rows;
+    if (int rc = validateRow(m.encoding, stride, m.columns)) return fail(rc, "matvec_add: row layout");
+    if (!fits_u32(m.rows) || !fits_u32(m.columns)) return fail(NU_ERR_INVALID_SHAPE, "matvec_add: too large");
+    if (!layoutOk(m)) return fail(NU_ERR_INVALID_SHAPE, "matvec_add: unknown matrix layout");
+    const uint8_t *w = resolve(weights, m.bytes);
+    const float *in = (const float *)resolve(input, m.columns * 4);
+    const float *res = (const float *)resolve(residual, m.rows * 4);
+    float *out = (float *)resolve(output, m.rows * 4);
+    if (!w || !in || !res || !out || input.offset % 4 != 0 || output.offset % 4 != 0 || residual.offset % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "matvec_add: buffer too short");
+    const bool same = residual.id == output.id && residual.offset == output.offset;
+    if (!same && overlaps(residual, m.rows * 4, output, m.rows * 4)) return fail(NU_ERR_INVALID_SHAPE, "matvec_add: output overlaps the residual");
+    if (overlaps(output, m.rows * 4, input, m.columns * 4) || overlaps(output, m.rows * 4, weights, m.bytes)) return fail(NU_ERR_INVALID_SHAPE, "matvec_add: output overlaps an input");
+    if (int rc = needRecording(true)) return rc;
+    FastJob job{};
+    job.enc = m.encoding; job.layout = m.layout; job.columns = (uint32_t)m.columns; job.tokens = 1; job.in = in; job.in_stride = m.columns;
+    job.count = 1; job.mode = ACT_NONE;
+    job.seg[0] = {w, stride, (uint32_t)m.rows, out, m.rows};
+    job.add0 = res;
+    job.serial = written(weights); job.partials = partials_; job.partials_floats = partials_floats_; job.counters = counters_; job.counters_len = counters_len_; job.sm_count = sm_count_;
+    if (!generic_only && fast_supported(job)) {
+        if (int rc = chainOrLaunch(job)) return rc;
+    } else {
+        if (int rc = flushChain()) return rc;
+        // the products go to the handle's scratch (the generic kernel does not use it), then one pass adds them
+        if (m.rows > partials_floats_) return fail(NU_ERR_TOO_LARGE, "matvec_add: rows beyond the scratch");
+        launches_ += launch_matmul_generic(stream_, m.encoding, m.layout, w, stride, (uint32_t)m.rows, (uint32_t)m.columns, in, false, m.columns, partials_, m.rows, 1);
+        if (!same && cudaMemcpyAsync(out, res, m.rows * 4, cudaMemcpyDeviceToDevice, stream_) != cudaSuccess) return fail(NU_ERR_EXECUTION, "matvec_add: copy");
+        launches_ += launch_add(stream_, out, partials_, m.rows);
+    }
+    wrote(output);
+    opBoundary();
+    return cuda(cudaGetLastError(), "matvec_add: launch");
+}
+
 // ops/matvec.zig:149-165.
 int Backend::matvecRows(const Buffer &weights, const Matrix &m, const Buffer &input, size_t in_stride,
                         const Buffer &output, size_t out_stride, size_t tokens) {
@@ -1184,6 +1224,10 @@ int nu_cuda_matmul(nu_cuda *h, const nu_buffer *weights, const nu_matrix *matrix
     return h->b->matmul(*weights, *matrix, *input, in_dtype, in_stride, *output, out_stride, tokens);
 }
 size_t nu_cuda_matmul_padded(size_t tokens) { return nu::Backend::matmulPadded(tokens); }
+int nu_cuda_matvec_add(nu_cuda *h, const nu_buffer *weights, const nu_matrix *matrix, const nu_buffer *input, const nu_buffer *residual, const nu_buffer *output) {
+    NU_H(h); NU_P(weights && matrix && input && residual && output);
+    return h->b->matvecAdd(*weights, *matrix, *input, *residual, *output);
+}
 int nu_cuda_matvec_segments(nu_cuda *h, const nu_segment *segments, size_t count, const nu_buffer *input, uint32_t mode) {
     NU_H(h); NU_P(input);
     return h->b->matvecSegments(segments, count, *input, mode);

@@ -71,6 +71,7 @@ public:
                    const Buffer &output, size_t out_stride, size_t tokens);
     int matmul(const Buffer &weights, const Matrix &matrix, const Buffer &input, uint32_t in_dtype, size_t in_stride,
                const Buffer &output, size_t out_stride, size_t tokens);
+    int matvecAdd(const Buffer &weights, const Matrix &m, const Buffer &input, const Buffer &residual, const Buffer &output);
     int matvecSegments(const Segment *segments, size_t count, const Buffer &input, uint32_t mode) { return segmentsJob(segments, count, input, mode, nullptr); }
     int matvecSegmentsNormed(const Segment *segments, size_t count, const Buffer &residual, const Buffer *input, const Buffer &weight, const Buffer *residual_out,
                              float eps, uint32_t mode);

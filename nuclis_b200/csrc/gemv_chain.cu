@@ -135,7 +135,7 @@ bool chain_configure() {
 
 // Whether a job can be a link of a chain: one token, a weight stream that may start early, no fused push.
 bool chain_supported(const FastJob &job) {
-    if (job.tokens != 1 || job.serial || job.push.ranks || job.norm_weight) return false;
+    if (job.tokens != 1 || job.serial || job.push.ranks || job.norm_weight || job.add0) return false;
     i8::Params p;
     i8::Plan plan;
     return (q4k_i8_fill(job, p, plan, false) || q6k_i8_fill(job, p, plan, false)) && plan.nt == 1;

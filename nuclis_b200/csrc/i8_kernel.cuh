@@ -70,6 +70,7 @@ struct Params {
     const float *norm_input;
     float *residual_out;
     float norm_eps;
+    const float *add0;       // not null: segment 0's output rows are add0[token * out_stride + row] + the products (may be `out` itself)
 };
 
 // C = A(16 x 32, unsigned bytes) x B(32 x 8, signed bytes), int32, starting from zero.
@@ -169,7 +170,11 @@ __device__ __forceinline__ void write_unit(const Params &p, uint32_t unit, uint3
         if (row >= p.rows[seg]) continue;
 #pragma unroll
         for (int c = 0; c < 2; ++c)
-            if (tok0 + c < p.tokens) p.out[seg][(size_t)(tok0 + c) * p.out_stride[seg] + row] = v[2 * h + c];
+            if (tok0 + c < p.tokens) {
+                const size_t at = (size_t)(tok0 + c) * p.out_stride[seg] + row;
+                // the residual add behind a projection, folded into its write: the thread that writes a row is the only one that reads it
+                p.out[seg][at] = (p.add0 && seg == 0) ? p.add0[at] + v[2 * h + c] : v[2 * h + c];
+            }
     }
 }
 
@@ -790,6 +795,8 @@ static bool fill_geometry(const FastJob &job, Params &p, Plan &plan) {
     p.norm_input = job.norm_input;
     p.residual_out = job.residual_out;
     p.norm_eps = job.norm_eps;
+    p.add0 = job.add0;
+    if (job.add0 && (job.count != 1 || job.mode != ACT_NONE || job.push.ranks || (uintptr_t)job.add0 % 4 != 0)) return false;  // one plain matrix, no push
     if (job.norm_weight && ((uintptr_t)job.norm_weight % 16 != 0 || (uintptr_t)job.norm_input % 16 != 0 || (uintptr_t)job.residual_out % 16 != 0)) return false;
     return true;
 }

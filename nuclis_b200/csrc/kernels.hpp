@@ -99,6 +99,7 @@ struct FastJob {
     const float *norm_input;
     float *residual_out;
     float norm_eps;
+    const float *add0;  // not null: the output rows of the (single, plain) segment are add0[...] + the products, at the output's stride
 };
 // Opts every variant into its dynamic shared memory size; once per device, outside any capture.
 bool fast_configure();

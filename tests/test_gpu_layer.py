@@ -26,6 +26,16 @@ def upload(b, data):
     return buf
 
 
+def weights_from(b, w, m, prepare):
+    """The GGUF bytes `w` on the device (planar when `prepare`) and the descriptor to use with them."""
+    wb = upload(b, w)
+    if prepare:
+        pb, m = b.prepare(wb, m)
+        b.release(wb)
+        wb = pb
+    return wb, m, w
+
+
 def weights(b, encoding, rows, columns, seed, prepare):
     """A matrix on the device (planar when `prepare`), its descriptor and its GGUF bytes on the host."""
     w = synth.matrix(encoding, rows, columns, seed)
@@ -352,4 +362,37 @@ def test_folded_norm_contract(backend):
     finally:
         b.discard()
     for buf in (rb, ib, wnb, ob, a, c, o1):
+        b.release(buf)
+
+
+@pytest.mark.parametrize("encoding,prepare", [(enc.Q4_K, False), (enc.Q6_K, True), (enc.Q8_0, True), (enc.Q5_1, True), (enc.Q6_K, False)])
+@pytest.mark.parametrize("shape", [(80, 1280), (5120, 17408)])
+@pytest.mark.parametrize("in_place", [True, False])
+def test_residual_add_folded_into_the_projection(backend, encoding, prepare, shape, in_place):
+    """`matvec_add`: the down (or O) projection and the residual `add` behind it (inference/src/models/qwen35_metal.zig:640)
+    as one launch on the specialized kernels (5120 x 17408 runs split over K: the last block to arrive for a unit adds),
+    two on the generic one (GGUF-form Q6_K here). residual + W x against the oracle within the matvec bound."""
+    b = backend
+    rows, columns = shape
+    w, x, m = make_case(encoding, rows, columns, 1, seed=77 + rows)
+    want, mag = expect(encoding, rows, columns, w, x)
+    res = (np.random.default_rng(rows).standard_normal(rows) * 0.1).astype(np.float32)
+    wb, mm, _ = weights_from(b, w, m, prepare)
+    xb, rb = upload(b, x[0]), upload(b, res)
+    ob = rb if in_place else b.create(rows * 4)
+    fast = prepare or encoding == enc.Q4_K
+    before = b.launch_count
+    b.begin()
+    b.matvec_add(wb, mm, xb, rb, ob)
+    b.commit()
+    assert b.launch_count - before == (1 if fast and rows % 16 == 0 else 2)
+    got = ob.floats()[:rows]
+    assert_matvec_close(got - res, want[0], mag[0] + np.abs(res), f"matvec_add enc {encoding} {shape}")
+    if not in_place:
+        assert np.array_equal(rb.floats(), res)
+        b.begin()
+        with pytest.raises(NuclisError):
+            b.matvec_add(wb, mm, xb, rb, rb.slice(4, rb.len - 4))   # a shifted overlap of residual and output
+        b.discard()
+    for buf in {id(v): v for v in (wb, xb, rb, ob)}.values():
         b.release(buf)
