@@ -466,7 +466,7 @@ def layer_parity(b, tokens: int, rank: int, world: int, seed: int) -> dict:
 
 # ---- the other configurations, measured in the same run (one GPU) -----------------------------------
 
-def other_configs(b, args, stack8_value=None) -> dict:
+def other_configs(b, args, stack8_value=None, stack_norms=None) -> dict:
     from nuclis_b200 import encoding as enc
     peaks, kind = measured_peaks()
     out = {}
@@ -499,6 +499,8 @@ def other_configs(b, args, stack8_value=None) -> dict:
                       "peak_source": kind, "cases": sweep}
     if stack8_value is not None:
         out["config2_m8"] = stack8_value
+    if stack_norms is not None:
+        out["config2_with_norms"] = stack_norms
     # config 3: prefill GEMM, bf16 activations
     pre = {}
     for e, rows, columns in ((enc.Q4_K, 17408, 5120), (enc.Q6_K, 5120, 17408)):
@@ -645,12 +647,22 @@ def run_gpu(args, rank: int, world: int, local: int):
                            "chain_gbs": st2.algorithmic_bytes_per_step() / (ms2 * 1e-3) / 1e9, "operators_per_step": ops2}
             for buf in (st2.h, st2.qkv, st2.o, st2.g, st2.u, st2.d):
                 b.release(buf)
+            # the same layers as a pre-norm decoder runs them: RMS norm ahead of QKV and of gate/up, residual add behind O
+            # and down, folded into those four launches (matvec_segments_normed, matvec_add)
+            st3 = Stack(b, stack.shapes, stack.local, 1)
+            st3.layers, st3.m_down = stack.layers, stack.m_down
+            st3.enable_norms(args.seed)
+            ms3, e2e3, launches3, ops3, _, _ = time_stack(b, st3, args, barrier, rank)
+            stack_norms = {"workload": "config 2 with the RMS norms and residual adds of a pre-norm layer folded into its four launches, M=1", "tok_s": 1e3 / ms3,
+                           "ms_per_step": ms3, "e2e_tok_s": args.steps / e2e3, "operators_per_step": ops3, "launches_per_step": int(launches3)}
+            for buf in (st3.h, st3.qkv, st3.o, st3.g, st3.u, st3.d, st3.residual, st3.norm_attn, st3.norm_ffn):
+                b.release(buf)
             # the stack's weights make room for the other configurations' tensors
             for w in stack.layers:
                 for buf in (w.qkv, w.o, w.gate, w.up, w.down):
                     b.release(buf)
             stack.layers = []
-            configs = other_configs(b, args, stack_other)
+            configs = other_configs(b, args, stack_other, stack_norms)
         if world == 1 and not args.no_cpu:
             import oracle
             oracle.build()

@@ -130,7 +130,7 @@ __device__ __forceinline__ void unit_rows(const Params &p, uint32_t unit, uint32
 // Writes the finished sums a lane holds for a unit. v: (row r, token a), (row r, token a + 1), (row r + 8, a), (row r + 8, a + 1)
 // with r the task row of the lane's mma row (E::row); narrow: a = 0 and only quad lane 0 holds sums; four tokens: a = 2t in quad lanes 0 and 1; wide: a = 2t.
 // w: the up sums in pair mode.
-template <int NT>
+template <int NT, bool FOLD>
 __device__ __forceinline__ void write_unit(const Params &p, uint32_t unit, uint32_t r, uint32_t t, const float v[4], const float w[4]) {
     constexpr bool WIDE = NT == 8, QUAD = NT == 4;
     if (QUAD ? t >= 2 : (!WIDE && t != 0)) return;
@@ -173,7 +173,7 @@ __device__ __forceinline__ void write_unit(const Params &p, uint32_t unit, uint3
             if (tok0 + c < p.tokens) {
                 const size_t at = (size_t)(tok0 + c) * p.out_stride[seg] + row;
                 // the residual add behind a projection, folded into its write: the thread that writes a row is the only one that reads it
-                p.out[seg][at] = (p.add0 && seg == 0) ? p.add0[at] + v[2 * h + c] : v[2 * h + c];
+                p.out[seg][at] = (FOLD && p.add0 && seg == 0) ? p.add0[at] + v[2 * h + c] : v[2 * h + c];
             }
     }
 }
@@ -218,7 +218,9 @@ __device__ __forceinline__ void mbar_inval(uint32_t bar) { asm volatile("mbarrie
 // pm: where its tensor maps may be handed to the copy engine (the kernel's parameter space).
 // SHARE: the instance whose slots share the units of a block's last round (below); the host picks it per geometry
 // (fill_geometry).
-template <class E, class G, int NT, bool SHARE>
+// FOLD: the instance that can fold the add + RMS norm ahead of the projections into its staging pass and a residual add
+// into its write (Params::norm_weight, add0); the plain instance carries none of that code.
+template <class E, class G, int NT, bool SHARE, bool FOLD = false>
 __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const int STAGES, uint8_t *smem, const ChainLink link) {
     constexpr bool WIDE = NT == 8, QUAD = NT == 4;
     constexpr uint32_t TS = token_stride<NT>();
@@ -353,7 +355,7 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
     // The fused add + RMS norm: every block reads the whole rows once for their mean squares (the slice it stages is
     // not enough), block 0 also writes the sums of the add. The scratch is the part sums' memory, not in use yet:
     // [0, 32) the warps' sums, [32, 40) 1 / rms of the tokens.
-    const bool normed = p.norm_weight != nullptr;
+    const bool normed = FOLD && p.norm_weight != nullptr;
     float *nscratch = (float *)parts;
     if (normed) {
         const uint32_t pieces = p.ksb * 64;
@@ -596,7 +598,7 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
             dst[rec] = make_float4(acc[0], acc[1], acc[2], acc[3]);
             if (pair) dst[REC + rec] = make_float4(acc2[0], acc2[1], acc2[2], acc2[3]);
         } else {
-            write_unit<NT>(p, unit, gr, t, acc, acc2);
+            write_unit<NT, FOLD>(p, unit, gr, t, acc, acc2);
         }
     }
     if (p.nks > 1 && my_units) {
@@ -647,7 +649,7 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
                         }
                     }
                     const float v4[4] = {s.x, s.y, s.z, s.w}, w4[4] = {s2.x, s2.y, s2.z, s2.w};
-                    write_unit<NT>(p, unit, gr, t, v4, w4);
+                    write_unit<NT, FOLD>(p, unit, gr, t, v4, w4);
                 }
                 if (lane == 0) p.counters[unit] = 0;  // leave the scratch as it was found
             }
@@ -670,6 +672,13 @@ template <class E, class G, int NT, int STAGES, bool SHARE>
 __global__ void __launch_bounds__(G::THREADS, 1) i8_kernel(const __grid_constant__ Params p) {
     extern __shared__ __align__(128) uint8_t smem[];
     run_op<E, G, NT, SHARE>(p, p, STAGES, smem, ChainLink{nullptr, 0u, 0u, 0u});
+}
+
+// The one-token instance with the folds.
+template <class E, class G, int STAGES, bool SHARE>
+__global__ void __launch_bounds__(G::THREADS, 1) i8_fold_kernel(const __grid_constant__ Params p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    run_op<E, G, 1, SHARE, true>(p, p, STAGES, smem, ChainLink{nullptr, 0u, 0u, 0u});
 }
 
 constexpr size_t kSmemMax = 227 * 1024;
@@ -796,6 +805,7 @@ static bool fill_geometry(const FastJob &job, Params &p, Plan &plan) {
     p.residual_out = job.residual_out;
     p.norm_eps = job.norm_eps;
     p.add0 = job.add0;
+    if ((job.add0 || job.norm_weight) && NT != 1) return false;  // the folds exist in the one-token instance
     if (job.add0 && (job.count != 1 || job.mode != ACT_NONE || job.push.ranks || (uintptr_t)job.add0 % 4 != 0)) return false;  // one plain matrix, no push
     if (job.norm_weight && ((uintptr_t)job.norm_weight % 16 != 0 || (uintptr_t)job.norm_input % 16 != 0 || (uintptr_t)job.residual_out % 16 != 0)) return false;
     return true;
@@ -806,8 +816,14 @@ static bool configure_one() {
     return cudaFuncSetAttribute(i8_kernel<E, G, NT, STAGES, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax) == cudaSuccess &&
            cudaFuncSetAttribute(i8_kernel<E, G, NT, STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax) == cudaSuccess;
 }
+template <class E, class G, int STAGES>
+static bool configure_fold() {
+    return cudaFuncSetAttribute(i8_fold_kernel<E, G, STAGES, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax) == cudaSuccess &&
+           cudaFuncSetAttribute(i8_fold_kernel<E, G, STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax) == cudaSuccess;
+}
 template <class E, class G, int NT>
 static bool configure_geometry() {
+    if (NT == 1 && !(configure_fold<E, G, 2>() && configure_fold<E, G, 3>() && configure_fold<E, G, 4>() && configure_fold<E, G, 5>())) return false;
     return configure_one<E, G, NT, 2>() && configure_one<E, G, NT, 3>() && configure_one<E, G, NT, 4>() && configure_one<E, G, NT, 5>();
 }
 
@@ -824,6 +840,25 @@ static int launch_geometry(cudaStream_t s, const FastJob &job, const Params &p, 
     cfg.stream = s;
     cfg.attrs = attr;
     cfg.numAttrs = job.serial ? 0 : 1;
+    if (job.norm_weight || job.add0) {
+        if (NT != 1) return 0;  // (fill_geometry has refused these)
+        if (plan.share) {
+            switch (plan.stages) {
+            case 5: cudaLaunchKernelEx(&cfg, i8_fold_kernel<E, G, 5, true>, p); break;
+            case 4: cudaLaunchKernelEx(&cfg, i8_fold_kernel<E, G, 4, true>, p); break;
+            case 3: cudaLaunchKernelEx(&cfg, i8_fold_kernel<E, G, 3, true>, p); break;
+            default: cudaLaunchKernelEx(&cfg, i8_fold_kernel<E, G, 2, true>, p); break;
+            }
+        } else {
+            switch (plan.stages) {
+            case 5: cudaLaunchKernelEx(&cfg, i8_fold_kernel<E, G, 5, false>, p); break;
+            case 4: cudaLaunchKernelEx(&cfg, i8_fold_kernel<E, G, 4, false>, p); break;
+            case 3: cudaLaunchKernelEx(&cfg, i8_fold_kernel<E, G, 3, false>, p); break;
+            default: cudaLaunchKernelEx(&cfg, i8_fold_kernel<E, G, 2, false>, p); break;
+            }
+        }
+        return 1;
+    }
     if (plan.share) {
         switch (plan.stages) {
         case 5: cudaLaunchKernelEx(&cfg, i8_kernel<E, G, NT, 5, true>, p); break;

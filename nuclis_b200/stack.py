@@ -94,12 +94,43 @@ class Stack:
         self.m_down = m
 
     # ---- the recording of one step ----
+    def enable_norms(self, seed: int = 0) -> None:
+        """Adds what a pre-norm decoder layer has around its projections (inference/src/models/qwen35_metal.zig:635-640):
+        a residual row and the two RMS-norm weight rows (shared by the layers here: their values do not matter to the
+        timing). ``record`` then uses the folded operators: four launches a layer, as without the norms."""
+        import numpy as np
+        b, s = self.backend, self.shapes
+        rng = np.random.default_rng(seed + 17)
+        self.residual = b.create(s.hidden * 4)
+        self.residual0 = (rng.standard_normal(s.hidden) * 0.5).astype(np.float32)
+        self.norm_attn, self.norm_ffn = b.create(s.hidden * 4), b.create(s.hidden * 4)
+        self.norm_attn_host = (1.0 + 0.1 * rng.standard_normal(s.hidden)).astype(np.float32)
+        self.norm_ffn_host = (1.0 + 0.1 * rng.standard_normal(s.hidden)).astype(np.float32)
+        self.norm_attn.write(self.norm_attn_host)
+        self.norm_ffn.write(self.norm_ffn_host)
+        self.residual.write(self.residual0)
+
+    def record_with_norms(self) -> int:
+        """One token, one GPU: x += O(Q(norm(x))); x += down(silu(gate(norm(x))) * up(norm(x))) per layer, the norms folded
+        into the staging passes of QKV and of the gate/up pair, the adds into the writes of O and down."""
+        b = self.backend
+        a_in = self.qkv.slice(0, self.qkv.len)
+        for w in self.layers:
+            b.matvec_segments_normed([Segment(w.qkv, self.m_qkv, self.qkv)], self.residual, self.norm_attn)
+            b.matvec_add(w.o, self.m_o, a_in, self.residual, self.residual)
+            b.matvec_segments_normed([Segment(w.gate, self.m_gate, self.g), Segment(w.up, self.m_gate, self.g)], self.residual, self.norm_ffn,
+                                     mode=SegmentMode.silu_mul_pair)
+            b.matvec_add(w.down, self.m_down, self.g, self.residual, self.residual)
+        return 4 * len(self.layers)
+
     def record(self, allreduce: bool | None = None) -> int:
         """Records every layer's chain into the open recording; returns how many operators it recorded."""
         b, s, l, m = self.backend, self.shapes, self.local, self.tokens
         reduce = l.ranks > 1 if allreduce is None else allreduce
         ops = 0
         a_in = self.qkv.slice(0, self.qkv.len)  # the Q slice: the first q_rows floats of each token row
+        if getattr(self, "residual", None) is not None and m == 1 and not reduce:
+            return self.record_with_norms()
         for w in self.layers:
             if m == 1:
                 b.matvec(w.qkv, self.m_qkv, self.h, self.qkv)

@@ -396,3 +396,33 @@ def test_residual_add_folded_into_the_projection(backend, encoding, prepare, sha
         b.discard()
     for buf in {id(v): v for v in (wb, xb, rb, ob)}.values():
         b.release(buf)
+
+
+def test_pre_norm_layer_on_the_folded_operators_matches_the_oracle(backend):
+    """One layer of the stack as a pre-norm decoder runs it (`Stack.record_with_norms`): x += O(Q(norm(x))), then
+    x += down(silu(gate(norm(x))) * up(norm(x))), four launches; against the CPU oracle's norms, matvecs and adds."""
+    from nuclis_b200.shard import LayerShapes
+    from nuclis_b200.stack import Stack, make_stack
+    b = backend
+    shapes = LayerShapes(hidden=1280, ffn=2816, kv=256)
+    st = make_stack(b, 1, 1, shapes=shapes, seed=5, prepare=False)
+    w = st.layers[0]
+    host = {k: getattr(w, k).read() for k in ("qkv", "o", "gate", "up", "down")}
+    st.prepare_layer(w)
+    st.enable_norms(3)
+    before = b.launch_count
+    b.begin()
+    assert st.record() == 4
+    b.commit()
+    assert b.launch_count - before == 4
+    l = st.local
+    x = st.residual0.copy()
+    xn = (oracle.rms_norm(x).astype(np.float64) * st.norm_attn_host).astype(np.float32)
+    qkv = oracle.matvec(shapes.qkv_encoding, l.qkv_rows, shapes.hidden, host["qkv"], xn)
+    x = x + oracle.matvec(shapes.o_encoding, shapes.hidden, l.q_rows, host["o"], qkv[: l.q_rows])
+    xn = (oracle.rms_norm(x).astype(np.float64) * st.norm_ffn_host).astype(np.float32)
+    g = oracle.matvec(shapes.gate_up_encoding, l.ffn_rows, shapes.hidden, host["gate"], xn)
+    u = oracle.matvec(shapes.gate_up_encoding, l.ffn_rows, shapes.hidden, host["up"], xn)
+    act = (oracle.silu(g).astype(np.float64) * u).astype(np.float32)
+    x = x + oracle.matvec(shapes.down_encoding, shapes.hidden, l.ffn_rows, host["down"], act)
+    assert rel_l2(st.residual.floats(), x) <= 1e-5
