@@ -282,6 +282,15 @@ int nu_cuda_matvec_experts(nu_cuda *h, const nu_buffer *weights, const nu_expert
                            const nu_buffer *input, size_t in_stride, size_t in_group,
                            const nu_buffer *output, size_t out_stride);
 
+/* `Backend.matvecExpertsGrouped` on a gate_up tensor followed by `Backend.geluMulRows` on the two halves of its output
+ * (ops/experts.zig:36-77, then 106-117) as one launch: output[slot][i] = act(gate row i . x) * (up row i . x) for
+ * i < rows / 2, where `tensor` holds [gate rows][up rows] per expert. No single call of the reference does this.
+ * `act`: 1 SiLU, 2 GELU. Tensors the specialized kernel does not serve take the GEMV and the activation pass as
+ * two launches: the call never declines. */
+int nu_cuda_matvec_experts_gated(nu_cuda *h, const nu_buffer *weights, const nu_expert_matrix *tensor, const nu_buffer *indices,
+                                 size_t slots, const nu_buffer *input, size_t in_stride, size_t in_group,
+                                 const nu_buffer *output, size_t out_stride, uint32_t act);
+
 /* `Backend.geluMulRows` (ops/experts.zig:106-117). */
 int nu_cuda_gelu_mul_rows(nu_cuda *h, const nu_buffer *gate, const nu_buffer *up, const nu_buffer *output,
                           size_t width, size_t rows, size_t gate_stride, size_t up_stride, size_t out_stride);

@@ -90,6 +90,7 @@ SIGNATURES = {
     "nu_cuda_matmul_experts": (cint, [vp, BP, ctypes.POINTER(CExpertMatrix), BP, sz, sz, BP, sz, sz, BP, sz]),
     "nu_cuda_route_local": (cint, [vp, BP, BP, sz, sz, sz, BP, BP]),
     "nu_cuda_matvec_experts": (cint, [vp, BP, EP, BP, sz, BP, sz, sz, BP, sz]),
+    "nu_cuda_matvec_experts_gated": (cint, [vp, BP, EP, BP, sz, BP, sz, sz, BP, sz, u32]),
     "nu_cuda_gelu_mul_rows": (cint, [vp, BP, BP, BP, sz, sz, sz, sz, sz]),
     "nu_cuda_combine_experts": (cint, [vp, BP, BP, BP, BP, BP, ctypes.POINTER(CCombineShape)]),
     "nu_cuda_matvec_q4k_static": (cint, [vp, sz, u32, u32, vp, vp, vp, ctypes.c_char_p, sz]),

@@ -358,6 +358,13 @@ class Backend:
         self._check(self._lib.nu_cuda_matvec_experts(self._h, weights._c(), tensor._c(), indices._c(), slots, input._c(), in_stride, in_group,
                                                      output._c(), out_stride))
 
+    def matvec_experts_gated(self, weights: Buffer, tensor: ExpertMatrix, indices: Buffer, slots: int, input: Buffer, in_stride: int, in_group: int,
+                             output: Buffer, out_stride: int, act: int = 2) -> None:
+        """``matvecExpertsGrouped`` on a gate_up tensor and ``geluMulRows`` on its halves (ops/experts.zig:36-77, 106-117) as one
+        launch: output[slot][i] = act(gate row i . x) * (up row i . x); ``act``: 1 SiLU, 2 GELU."""
+        self._check(self._lib.nu_cuda_matvec_experts_gated(self._h, weights._c(), tensor._c(), indices._c(), slots, input._c(), in_stride, in_group,
+                                                           output._c(), out_stride, act))
+
     def gelu_mul_rows(self, gate: Buffer, up: Buffer, output: Buffer, width: int, rows: int, gate_stride: int, up_stride: int, out_stride: int) -> None:
         self._check(self._lib.nu_cuda_gelu_mul_rows(self._h, gate._c(), up._c(), output._c(), width, rows, gate_stride, up_stride, out_stride))
 

@@ -842,6 +842,43 @@ int Backend::matvecExpertsGrouped(const Buffer &weights, const ExpertMatrix &t, 
     return cuda(cudaGetLastError(), "experts: launch");
 }
 
+// No reference analogue as one call: `matvecExpertsGrouped` on a gate_up tensor followed by `geluMulRows` on its two halves
+// (ops/experts.zig:36-77, 106-117; inference/src/models/gemma4.zig runs them back to back): output[slot][i] =
+// act(gate row i . x) * (up row i . x) for i < rows / 2, one launch on the specialized Q4_K kernel; other tensors take the
+// generic GEMV into the handle's scratch and the activation pass, so the call never declines. act: 1 SiLU, 2 GELU.
+int Backend::matvecExpertsGated(const Buffer &weights, const ExpertMatrix &t, const Buffer &indices, size_t slots, const Buffer &input, size_t in_stride,
+                                size_t in_group, const Buffer &output, size_t out_stride, uint32_t act) {
+    if (act != ACT_SILU && act != ACT_GELU) return fail(NU_ERR_INVALID_SHAPE, "experts_gated: activation");
+    if (in_group == 0 || in_group > slots) return fail(NU_ERR_INVALID_SHAPE, "experts_gated: in_group");
+    if (t.experts == 0 || t.rows == 0 || t.rows % 2 != 0 || t.columns == 0 || t.bytes % t.experts != 0 || (t.bytes / t.experts) % t.rows != 0) return fail(NU_ERR_INVALID_SHAPE, "experts_gated: tensor shape");
+    const size_t per_expert = t.bytes / t.experts, stride = per_expert / t.rows, width = t.rows / 2;
+    if (validateRow(t.encoding, stride, t.columns) != NU_OK) return fail(NU_ERR_INVALID_SHAPE, "experts_gated: row layout");
+    if (t.columns % 16 != 0 || t.rows > 0xffffffffull / 4 || !fits_u32(t.experts) || !fits_u32(t.columns)) return fail(NU_ERR_INVALID_SHAPE, "experts_gated: sizes");
+    if (slots == 0 || slots > 0xffff || out_stride < width || (in_stride != 0 && in_stride < t.columns) || in_stride % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "experts_gated: slots or strides");
+    const uint8_t *w = resolve(weights, t.bytes);
+    const uint32_t *idx = (const uint32_t *)resolve(indices, slots * 4);
+    const float *in = (const float *)resolve(input, ((slots - 1) / in_group * in_stride + t.columns) * 4);
+    float *out = (float *)resolve(output, ((slots - 1) * out_stride + width) * 4);
+    if (!w || !idx || !in || !out || indices.offset % 4 != 0 || output.offset % 4 != 0 || input.offset % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "experts_gated: buffer too short");
+    if (overlaps(output, ((slots - 1) * out_stride + width) * 4, input, ((slots - 1) / in_group * in_stride + t.columns) * 4)) return fail(NU_ERR_INVALID_SHAPE, "experts_gated: output overlaps input");
+    if (int rc = needRecording()) return rc;
+    int launched = generic_only ? 0 : launch_matvec_experts_gated_fast(stream_, act, t.encoding, w, stride, per_expert, (uint32_t)t.experts, (uint32_t)t.rows, (uint32_t)t.columns,
+                                                                       idx, (uint32_t)slots, in, in_stride, (uint32_t)in_group, out, out_stride);
+    if (!launched) {
+        if (slots * t.rows > partials_floats_) return fail(NU_ERR_TOO_LARGE, "experts_gated: beyond the scratch");
+        int n = generic_only ? 0 : launch_matvec_experts_fast(stream_, t.encoding, w, stride, per_expert, (uint32_t)t.experts, (uint32_t)t.rows, (uint32_t)t.columns, idx,
+                                                              (uint32_t)slots, in, in_stride, (uint32_t)in_group, partials_, t.rows);
+        if (!n)
+            n = launch_matvec_experts_generic(stream_, t.encoding, w, stride, per_expert, (uint32_t)t.experts, (uint32_t)t.rows, (uint32_t)t.columns, idx, (uint32_t)slots, in,
+                                              in_stride, (uint32_t)in_group, partials_, t.rows);
+        launched = n + launch_act_mul_rows(stream_, act, partials_, partials_ + width, out, (uint32_t)width, (uint32_t)slots, t.rows, t.rows, out_stride);
+    }
+    launches_ += launched;
+    wrote(output);
+    opBoundary();
+    return cuda(cudaGetLastError(), "experts_gated: launch");
+}
+
 // ops/experts.zig:119-146: the lists buffer layout is the reference's (expertListsLayout).
 static size_t expertTileBound(size_t n, size_t experts) { return (n + 31) / 32 + experts; }
 static size_t expertListsWords(size_t n, size_t experts) { return experts + 3 + 3 * expertTileBound(n, experts) + n; }
@@ -1288,6 +1325,12 @@ int nu_cuda_matvec_experts(nu_cuda *h, const nu_buffer *weights, const nu_expert
                            const nu_buffer *input, size_t in_stride, size_t in_group, const nu_buffer *output, size_t out_stride) {
     NU_H(h); NU_P(weights && tensor && indices && input && output);
     return h->b->matvecExpertsGrouped(*weights, *tensor, *indices, slots, *input, in_stride, in_group, *output, out_stride);
+}
+int nu_cuda_matvec_experts_gated(nu_cuda *h, const nu_buffer *weights, const nu_expert_matrix *tensor, const nu_buffer *indices, size_t slots, const nu_buffer *input,
+                                 size_t in_stride, size_t in_group, const nu_buffer *output, size_t out_stride, uint32_t act) {
+    NU_H(h);
+    if (!weights || !tensor || !indices || !input || !output) return NU_ERR_INVALID_SHAPE;
+    return h->b->matvecExpertsGated(*weights, *tensor, *indices, slots, *input, in_stride, in_group, *output, out_stride, act);
 }
 int nu_cuda_gelu_mul_rows(nu_cuda *h, const nu_buffer *gate, const nu_buffer *up, const nu_buffer *output,
                           size_t width, size_t rows, size_t gate_stride, size_t up_stride, size_t out_stride) {

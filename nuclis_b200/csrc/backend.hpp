@@ -87,6 +87,8 @@ public:
     int expertLists(const Buffer &indices, size_t rows, size_t k, size_t experts, const Buffer &lists);
     int matmulExperts(const Buffer &weights, const ExpertMatrix &tensor, const Buffer &lists, size_t rows, size_t k, const Buffer &input, size_t in_stride,
                       size_t in_group, const Buffer &output, size_t out_stride);
+    int matvecExpertsGated(const Buffer &weights, const ExpertMatrix &t, const Buffer &indices, size_t slots, const Buffer &input, size_t in_stride, size_t in_group,
+                           const Buffer &output, size_t out_stride, uint32_t act);
     int geluMulRows(const Buffer &gate, const Buffer &up, const Buffer &output, size_t width, size_t rows,
                     size_t gate_stride, size_t up_stride, size_t out_stride);
     int combineExperts(const Buffer &values, const Buffer &weights, const Buffer &indices, const Buffer *scales,

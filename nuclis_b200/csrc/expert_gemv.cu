@@ -100,6 +100,10 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// ACT: 0 plain (a row of the tensor per output row); ACT_SILU / ACT_GELU: the tensor is [gate rows][up rows] and the
+// output row i is act(gate row i) * (up row i): a block then takes 16 gate rows and their 16 up rows, and the two
+// halves meet in shared memory (the activation pass behind the gate_up GEMV, ops/rowwise.zig:230-233, folded in).
+template <int ACT>
 __global__ void __launch_bounds__(XQ_THREADS) expert_gemv_q4k_kernel(const uint8_t *w, size_t stride, size_t expert_bytes, uint32_t experts, uint32_t rows,
                                                                      uint32_t ksb, const uint32_t *indices, const float *in, size_t in_stride,
                                                                      uint32_t in_group, float *out, size_t out_stride) {
@@ -115,8 +119,10 @@ __global__ void __launch_bounds__(XQ_THREADS) expert_gemv_q4k_kernel(const uint8
     asm volatile("griddepcontrol.launch_dependents;");
     const uint32_t slot = blockIdx.y;
     const uint32_t rl = threadIdx.x >> 3, p = threadIdx.x & 7;
-    const uint32_t r = blockIdx.x * XQ_ROWS + rl;
-    const bool live = r < rows;
+    const uint32_t half = rows / 2;  // gated: the gate rows; `rows` counts both halves of the tensor
+    const uint32_t pair_row = blockIdx.x * (XQ_ROWS / 2) + (rl & 15u);   // gated: the output row this lane's tensor row belongs to
+    const uint32_t r = ACT ? (rl < 16 ? pair_row : half + pair_row) : blockIdx.x * XQ_ROWS + rl;
+    const bool live = ACT ? pair_row < half : r < rows;
     // A corrupt routing buffer can never read past the tensor (experts.metal:25).
     const uint32_t expert = min(indices[slot], experts - 1);
     const uint8_t *row = w + (size_t)expert * expert_bytes + (size_t)(live ? r : 0) * stride;
@@ -222,6 +228,16 @@ __global__ void __launch_bounds__(XQ_THREADS) expert_gemv_q4k_kernel(const uint8
     acc += __shfl_xor_sync(0xffffffffu, acc, 1);
     acc += __shfl_xor_sync(0xffffffffu, acc, 2);
     acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+    if (ACT) {
+        __shared__ float gate_sums[XQ_ROWS / 2];
+        if (p == 0 && rl < 16) gate_sums[rl] = acc;
+        __syncthreads();
+        if (p == 0 && rl >= 16 && live) {
+            const float g = gate_sums[rl - 16];
+            out[(size_t)slot * out_stride + pair_row] = (ACT == ACT_SILU ? silu_f32(g) : gelu_f32(g)) * acc;
+        }
+        return;
+    }
     if (p == 0 && live) out[(size_t)slot * out_stride + r] = acc;
 }
 
@@ -488,7 +504,9 @@ constexpr uint32_t kMaxColumns = 16384;  // shared memory: about 4 bytes a colum
 // Opts both kernels into their dynamic shared memory sizes. The attribute belongs to the device that
 // is current, so this runs once per handle, with the handle's device current (fast_configure).
 bool expert_gemv_configure() {
-    return cudaFuncSetAttribute(expert_gemv_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(XQ_RING + kMaxColumns / 256 * (3 * 320 + 128))) == cudaSuccess &&
+    return cudaFuncSetAttribute(expert_gemv_q4k_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(XQ_RING + kMaxColumns / 256 * (3 * 320 + 128))) == cudaSuccess &&
+           cudaFuncSetAttribute(expert_gemv_q4k_kernel<ACT_SILU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(XQ_RING + kMaxColumns / 256 * (3 * 320 + 128))) == cudaSuccess &&
+           cudaFuncSetAttribute(expert_gemv_q4k_kernel<ACT_GELU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(XQ_RING + kMaxColumns / 256 * (3 * 320 + 128))) == cudaSuccess &&
            cudaFuncSetAttribute(expert_gemv_q8_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) == cudaSuccess &&
            cudaFuncSetAttribute(expert_gemv_nibble_kernel<NK_Q5_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) == cudaSuccess &&
            cudaFuncSetAttribute(expert_gemv_nibble_kernel<NK_Q5_1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) == cudaSuccess &&
@@ -517,7 +535,7 @@ int launch_matvec_experts_fast(cudaStream_t s, uint32_t enc, const uint8_t *w, s
         cfg.gridDim = dim3((rows + XQ_ROWS - 1) / XQ_ROWS, slots);
         cfg.blockDim = dim3(XQ_THREADS);
         cfg.dynamicSmemBytes = XQ_RING + (size_t)ksb * (3 * 320 + 128);
-        cudaLaunchKernelEx(&cfg, expert_gemv_q4k_kernel, w, stride, expert_bytes, experts, rows, ksb, indices, in, in_stride, in_group, out, out_stride);
+        cudaLaunchKernelEx(&cfg, expert_gemv_q4k_kernel<0>, w, stride, expert_bytes, experts, rows, ksb, indices, in, in_stride, in_group, out, out_stride);
         return 1;
     }
     if (enc == Q8_0) {
@@ -554,6 +572,31 @@ int launch_matvec_experts_fast(cudaStream_t s, uint32_t enc, const uint8_t *w, s
         return 1;
     }
     return 0;
+}
+
+// The gate_up GEMV with the activation pass folded in: out[slot][i] = act(gate row i) * (up row i), i < rows / 2, for a
+// Q4_K tensor of [gate rows][up rows] per expert. 0: not one of the specialized forms (the caller runs the two operators).
+int launch_matvec_experts_gated_fast(cudaStream_t s, uint32_t act, uint32_t enc, const uint8_t *w, size_t stride, size_t expert_bytes, uint32_t experts, uint32_t rows,
+                                     uint32_t columns, const uint32_t *indices, uint32_t slots, const float *in, size_t in_stride, uint32_t in_group,
+                                     float *out, size_t out_stride) {
+    if (slots > 65535 || enc != Q4_K || rows % 2 != 0 || (act != ACT_SILU && act != ACT_GELU)) return 0;
+    if ((uintptr_t)in % 16 != 0 || in_stride % 4 != 0) return 0;
+    if (columns % 256 != 0 || columns > kMaxColumns) return 0;
+    if ((uintptr_t)w % 16 != 0 || stride % 16 != 0 || expert_bytes % 16 != 0) return 0;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.stream = s;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const uint32_t ksb = columns / 256;
+    cfg.gridDim = dim3((rows / 2 + XQ_ROWS / 2 - 1) / (XQ_ROWS / 2), slots);
+    cfg.blockDim = dim3(XQ_THREADS);
+    cfg.dynamicSmemBytes = XQ_RING + (size_t)ksb * (3 * 320 + 128);
+    if (act == ACT_SILU) cudaLaunchKernelEx(&cfg, expert_gemv_q4k_kernel<ACT_SILU>, w, stride, expert_bytes, experts, rows, ksb, indices, in, in_stride, in_group, out, out_stride);
+    else cudaLaunchKernelEx(&cfg, expert_gemv_q4k_kernel<ACT_GELU>, w, stride, expert_bytes, experts, rows, ksb, indices, in, in_stride, in_group, out, out_stride);
+    return 1;
 }
 
 }  // namespace nu

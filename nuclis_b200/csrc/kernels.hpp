@@ -25,6 +25,10 @@ int launch_matmul_generic(cudaStream_t s, uint32_t enc, uint32_t layout, const u
 int launch_matvec_experts_fast(cudaStream_t s, uint32_t enc, const uint8_t *w, size_t stride, size_t expert_bytes, uint32_t experts, uint32_t rows,
                                uint32_t columns, const uint32_t *indices, uint32_t slots, const float *in, size_t in_stride, uint32_t in_group,
                                float *out, size_t out_stride);
+// The same with the activation pass folded in (a tensor of [gate rows][up rows] per expert; out row i = act(gate i) * up i).
+int launch_matvec_experts_gated_fast(cudaStream_t s, uint32_t act, uint32_t enc, const uint8_t *w, size_t stride, size_t expert_bytes, uint32_t experts, uint32_t rows,
+                                     uint32_t columns, const uint32_t *indices, uint32_t slots, const float *in, size_t in_stride, uint32_t in_group,
+                                     float *out, size_t out_stride);
 bool expert_gemv_configure();
 int launch_matvec_experts_generic(cudaStream_t s, uint32_t enc, const uint8_t *w, size_t stride, size_t expert_bytes,
                                   uint32_t experts, uint32_t rows, uint32_t columns, const uint32_t *indices, uint32_t slots,

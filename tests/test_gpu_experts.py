@@ -11,6 +11,7 @@ import pytest
 
 import oracle
 from nuclis_b200 import Backend, CombineShape, ExpertMatrix, NuclisError, encoding as enc, shard, synth
+from parity import rel_l2
 
 pytestmark = pytest.mark.gpu
 
@@ -336,6 +337,50 @@ def test_grouped_prefill_reads_the_other_expert_encodings(backend, encoding):
         assert np.max(np.abs(got[s] - want) / (4e-3 * mag + 1e-6)) <= 1.0 and np.linalg.norm(got[s] - want) <= 2e-2 * np.linalg.norm(want), s
     backend.unwrap(data)
     for buf in (xb, ib, lists, y):
+        backend.release(buf)
+
+
+@pytest.mark.parametrize("encoding,ff,cols", [(enc.Q4_K, 704, 2816), (enc.Q4_K, 40, 512), (enc.Q8_0, 48, 128)])
+@pytest.mark.parametrize("in_group", [1, 2])
+@pytest.mark.parametrize("act", [1, 2])
+def test_gate_up_with_the_activation_folded_in(backend, encoding, ff, cols, in_group, act):
+    """`matvec_experts_gated`: the gate_up GEMV and the activation pass behind it (ops/experts.zig:36-77, 106-117) as one
+    launch on the Q4_K kernel (a block takes 16 gate rows and their 16 up rows; 40 rows: a ragged last block), two on the
+    others. The same bits as the two operators give, and act(gate) * up against the oracle."""
+    experts, slots = 6, 8
+    data = synth.matrix(encoding, experts * 2 * ff, cols, seed=60 + ff)
+    per = data.size // experts
+    t = ExpertMatrix(encoding, experts, 2 * ff, cols, data.size)
+    rng = np.random.default_rng(ff + cols)
+    groups = slots // in_group
+    x = rng.standard_normal((groups, cols)).astype(np.float32)
+    idx = rng.integers(0, experts, size=slots).astype(np.uint32)
+    wb = backend.wrap(data)
+    xb = backend.create(x.nbytes); xb.write(x)
+    ib = backend.create(slots * 4); ib.write(idx)
+    gu = backend.create(slots * 2 * ff * 4)
+    hid, hid2 = backend.create(slots * ff * 4), backend.create(slots * ff * 4)
+    before = backend.launch_count
+    backend.begin()
+    backend.matvec_experts_gated(wb, t, ib, slots, xb, cols, in_group, hid, ff, act=act)
+    backend.commit()
+    assert backend.launch_count - before == (1 if encoding == enc.Q4_K else 2)
+    backend.begin()
+    backend.matvec_experts_grouped(wb, t, ib, slots, xb, cols, in_group, gu, 2 * ff)
+    if act == 2:
+        backend.gelu_mul_rows(gu, gu.slice(ff * 4, gu.len - ff * 4), hid2, ff, slots, 2 * ff, 2 * ff, ff)
+    backend.commit()
+    got = hid.floats().reshape(slots, ff)
+    if act == 2:
+        assert np.array_equal(got.view(np.uint32), hid2.floats().reshape(slots, ff).view(np.uint32))
+    for s in range(slots):
+        e = int(idx[s])
+        both = oracle.matvec(encoding, 2 * ff, cols, data[e * per:(e + 1) * per], x[s // in_group])
+        g, u = both[:ff], both[ff:]
+        want = (oracle.gelu(g) if act == 2 else oracle.silu(g)).astype(np.float64) * u
+        assert rel_l2(got[s], want) <= 1e-5, s
+    backend.unwrap(data)
+    for buf in (xb, ib, gu, hid, hid2):
         backend.release(buf)
 
 
