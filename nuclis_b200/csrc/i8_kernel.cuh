@@ -356,8 +356,12 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
     // not enough), block 0 also writes the sums of the add. The scratch is the part sums' memory, not in use yet:
     // [0, 32) the warps' sums, [32, 40) 1 / rms of the tokens.
     const bool normed = FOLD && p.norm_weight != nullptr;
+    // One token, the whole row staged by this block, a superblock per warp at most (the gate/up pair and QKV of a 5120-wide
+    // layer): the mean square comes from the values the staging pass holds in registers anyway, and the pass above it
+    // over the rows is not needed.
+    const bool merged = normed && NT == 1 && p.nks == 1 && pairs <= (uint32_t)WARPS;
     float *nscratch = (float *)parts;
-    if (normed) {
+    if (normed && !merged) {
         const uint32_t pieces = p.ksb * 64;
         for (uint32_t tok = 0; tok < ntok; ++tok) {
             const float4 *r4 = (const float4 *)(p.in + (size_t)tok * p.in_stride);
@@ -405,10 +409,33 @@ __device__ __forceinline__ void run_op(const Params &p, const Params &pm, const 
                     }
                     const float4 *wv = (const float4 *)p.norm_weight + col4;
                     const float4 wa = __ldg(wv + lane), wb = __ldg(wv + 32 + lane);
-                    const float r = nscratch[32 + tok];
+                    float r;
+                    if (merged) {
+                        // (one pair per warp: j == 0) the sums of the add leave from block 0, the squares meet across the warps
+                        if (p.residual_out && blockIdx.x == 0) {
+                            float4 *o4 = (float4 *)p.residual_out + col4;
+                            o4[lane] = xa[j];
+                            o4[32 + lane] = xb2[j];
+                        }
+                        float sum = (xa[j].x * xa[j].x + xa[j].y * xa[j].y + xa[j].z * xa[j].z + xa[j].w * xa[j].w) +
+                                    (xb2[j].x * xb2[j].x + xb2[j].y * xb2[j].y + xb2[j].z * xb2[j].z + xb2[j].w * xb2[j].w);
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                        if (lane == 0) nscratch[warp] = sum;
+                    }
+                    if (merged) {
+                        named_barrier(14, G::THREADS);  // every warp arrives here: those without a pair in the else branch below
+                        float total = 0.0f;
+                        for (uint32_t w2 = 0; w2 < pairs; ++w2) total += nscratch[w2];
+                        r = rsqrtf(total / (float)(p.ksb * 256u) + p.norm_eps);
+                    } else {
+                        r = nscratch[32 + tok];
+                    }
                     xa[j] = make_float4(xa[j].x * r * wa.x, xa[j].y * r * wa.y, xa[j].z * r * wa.z, xa[j].w * r * wa.w);
                     xb2[j] = make_float4(xb2[j].x * r * wb.x, xb2[j].y * r * wb.y, xb2[j].z * r * wb.z, xb2[j].w * r * wb.w);
                 }
+            } else if (merged && j == 0) {
+                named_barrier(14, G::THREADS);  // a warp without a superblock still meets the others
             }
         }
 #pragma unroll
