@@ -293,7 +293,7 @@ def test_norms_around_the_projections_match_the_oracle(backend, rows, width, pad
 
 
 @pytest.mark.parametrize("encoding,prepare", [(enc.Q4_K, False), (enc.Q5_K, False), (enc.Q6_K, True), (enc.Q8_0, True), (enc.Q5_0, True)])
-@pytest.mark.parametrize("shape", [(1056, 1280), (17408, 5120)])
+@pytest.mark.parametrize("shape", [(1056, 1280), (17408, 5120), (2048, 17408)])   # 17408 columns: K cut into slices, the rows read in a pass of their own
 @pytest.mark.parametrize("with_add", [True, False])
 def test_add_rms_norm_folded_into_the_projections(backend, encoding, prepare, shape, with_add):
     """`matvec_segments_normed`: `addRmsNorm` (ops/rowwise.zig:76-93) and the gate/up pair on its output
