@@ -633,6 +633,17 @@ def run_gpu(args, rank: int, world: int, local: int):
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
             ex[f"m{m}"] = {"us_per_chain": float(tt[0]), "parity_worst_over_bound": float(tt[1]), "experts_per_rank": case.local, "operators_per_chain": r["operators_per_chain"]}
         configs = {"config4_expert_parallel": {"workload": f"expert chain, 128 experts over {world} ranks, one allreduce of the combined outputs per chain", "cases": ex}}
+        if tokens == 1:
+            # the sharded stack as a pre-norm decoder runs it: the norms in the staging passes of QKV and gate/up, the residual
+            # adds in the gathers of the two sums (the same six launches a layer)
+            st3 = Stack(b, stack.shapes, stack.local, 1)
+            st3.layers, st3.m_down = stack.layers, stack.m_down
+            st3.enable_norms(args.seed)
+            ms3, e2e3, launches3, ops3, _, _ = time_stack(b, st3, args, barrier, rank)
+            t3 = torch.tensor([ms3, e2e3], dtype=torch.float64)
+            dist.all_reduce(t3, op=dist.ReduceOp.MAX)
+            configs["config2_with_norms"] = {"workload": f"config 2 with the RMS norms and residual adds of a pre-norm layer folded in, M=1, tp{world}", "tok_s": 1e3 / float(t3[0]),
+                                             "ms_per_step": float(t3[0]), "e2e_tok_s": args.steps / float(t3[1]), "operators_per_step": ops3, "launches_per_step": int(launches3)}
 
     roofline = cpu = None
     if rank == 0:

@@ -364,6 +364,10 @@ int nu_cuda_comm_unique_id(uint8_t id[NU_COMM_ID_BYTES]);
 int nu_cuda_comm_init(nu_cuda *h, const uint8_t id[NU_COMM_ID_BYTES], int ranks, int rank);
 /* In-place sum over the group of `count` floats at `buffer`; recorded like an operator. */
 int nu_cuda_allreduce_sum_f32(nu_cuda *h, const nu_buffer *buffer, size_t count);
+/* The same with the residual add behind a row-split projection folded in: residual[i] += sum over the group of
+ * buffer[i]; `buffer` is left with this rank's partial values or the sums, depending on the transport. Every rank
+ * adds the same sums in the same order, so identical residuals stay identical. `residual` must not overlap `buffer`. */
+int nu_cuda_allreduce_sum_add_f32(nu_cuda *h, const nu_buffer *buffer, const nu_buffer *residual, size_t count);
 /* One-shot allreduce over peer memory for short vectors (at most 65,536 floats): at 20 KB a
  * collective is pure latency, and this path costs one peer store and a local sum instead of
  * a library call. Each rank calls nu_cuda_comm_peer_handle (it allocates the rank's inbox and

@@ -99,6 +99,7 @@ SIGNATURES = {
     "nu_cuda_comm_unique_id": (cint, [u8p]),
     "nu_cuda_comm_init": (cint, [vp, u8p, cint, cint]),
     "nu_cuda_allreduce_sum_f32": (cint, [vp, BP, sz]),
+    "nu_cuda_allreduce_sum_add_f32": (cint, [vp, BP, BP, sz]),
     "nu_cuda_comm_destroy": (cint, [vp]),
     "nu_cuda_comm_peer_handle": (cint, [vp, u8p]),
     "nu_cuda_comm_attach_peers": (cint, [vp, u8p, cint, cint]),

@@ -390,6 +390,10 @@ class Backend:
     def allreduce_sum_f32(self, buffer: Buffer, count: int) -> None:
         self._check(self._lib.nu_cuda_allreduce_sum_f32(self._h, buffer._c(), count))
 
+    def allreduce_sum_add_f32(self, buffer: Buffer, residual: Buffer, count: int) -> None:
+        """residual += the sum over the group of ``buffer``: the residual add behind a row-split projection, in the sum's gather."""
+        self._check(self._lib.nu_cuda_allreduce_sum_add_f32(self._h, buffer._c(), residual._c(), count))
+
     def comm_peer_handle(self) -> bytes:
         """This rank's inbox for the one-shot allreduce, as a 64-byte interprocess handle."""
         buf = (ctypes.c_uint8 * 64)()

@@ -1086,10 +1086,17 @@ int Backend::setPeerWaitMs(uint32_t ms) {
     return NU_OK;
 }
 
-int Backend::allreduceSumF32(const Buffer &buffer, size_t count) {
+// add_to: the sums are added to this vector (the residual behind a row-split projection) and `buffer` keeps this rank's
+// partial values, or whatever the transport leaves there: the residual add folded into the sum's gather.
+int Backend::allreduceSumF32(const Buffer &buffer, size_t count, const Buffer *add_to) {
     if (count == 0) return fail(NU_ERR_INVALID_SHAPE, "allreduce: empty");
     float *p = (float *)resolve(buffer, count * 4);
     if (!p || buffer.offset % 4 != 0) return fail(NU_ERR_INVALID_SHAPE, "allreduce: buffer too short");
+    float *res = nullptr;
+    if (add_to) {
+        res = (float *)resolve(*add_to, count * 4);
+        if (!res || add_to->offset % 4 != 0 || overlaps(*add_to, count * 4, buffer, count * 4)) return fail(NU_ERR_INVALID_SHAPE, "allreduce: residual too short or overlapping the vector");
+    }
     if (peers_attached_ && count <= kPushCapacity) {
         // A one-token matvec whose whole output is this vector was held back: it becomes one kernel that
         // computes and pushes its rows into every rank's inbox, and the sum only gathers.
@@ -1101,6 +1108,7 @@ int Backend::allreduceSumF32(const Buffer &buffer, size_t count) {
         pp.seq = (uint32_t *)(inbox_ + kPushWordBytes);
         pp.status = counters_ + counters_len_;
         pp.wait_ns = peer_wait_ns_;
+        pp.add_to = res;
         if (fuse) {
             cudaSetDevice(device_);
             FastJob &job = pending_job_->job;
@@ -1112,6 +1120,7 @@ int Backend::allreduceSumF32(const Buffer &buffer, size_t count) {
                 opBoundary();
                 launches_ += launch_gather_sum(stream_, pp);
                 wrote(buffer);
+                if (add_to) wrote(*add_to);
                 opBoundary();
                 return cuda(cudaGetLastError(), "allreduce: launch");
             }
@@ -1120,6 +1129,7 @@ int Backend::allreduceSumF32(const Buffer &buffer, size_t count) {
         if (int rc = needRecording()) return rc;
         launches_ += launch_push_allreduce(stream_, pp);
         wrote(buffer);
+        if (add_to) wrote(*add_to);
         opBoundary();
         return cuda(cudaGetLastError(), "allreduce: launch");
     }
@@ -1132,6 +1142,12 @@ int Backend::allreduceSumF32(const Buffer &buffer, size_t count) {
     }
     wrote(buffer);
     opBoundary();  // a library collective: not counted among this library's own kernel launches
+    if (add_to) {
+        launches_ += launch_add(stream_, res, p, count);
+        wrote(*add_to);
+        opBoundary();
+        return cuda(cudaGetLastError(), "allreduce: add");
+    }
     return NU_OK;
 }
 
@@ -1346,6 +1362,7 @@ int nu_cuda_combine_experts(nu_cuda *h, const nu_buffer *values, const nu_buffer
 int nu_cuda_comm_unique_id(uint8_t id[NU_COMM_ID_BYTES]) { return id ? nu::unique_id(id) : NU_ERR_INVALID_SHAPE; }
 int nu_cuda_comm_init(nu_cuda *h, const uint8_t id[NU_COMM_ID_BYTES], int ranks, int rank) { NU_H(h); return h->b->commInit(id, ranks, rank); }
 int nu_cuda_allreduce_sum_f32(nu_cuda *h, const nu_buffer *buffer, size_t count) { NU_H(h); NU_P(buffer); return h->b->allreduceSumF32(*buffer, count); }
+int nu_cuda_allreduce_sum_add_f32(nu_cuda *h, const nu_buffer *buffer, const nu_buffer *residual, size_t count) { NU_H(h); NU_P(buffer && residual); return h->b->allreduceSumF32(*buffer, count, residual); }
 int nu_cuda_comm_destroy(nu_cuda *h) { NU_H(h); return h->b->commDestroy(); }
 int nu_cuda_comm_peer_handle(nu_cuda *h, uint8_t handle[NU_PEER_HANDLE_BYTES]) { NU_H(h); return h->b->peerHandle(handle); }
 int nu_cuda_comm_attach_peers(nu_cuda *h, const uint8_t *handles, int ranks, int rank) { NU_H(h); return h->b->attachPeers(handles, ranks, rank); }

@@ -96,7 +96,7 @@ public:
 
     // ---- collective ----
     int commInit(const uint8_t *id, int ranks, int rank);
-    int allreduceSumF32(const Buffer &buffer, size_t count);
+    int allreduceSumF32(const Buffer &buffer, size_t count, const Buffer *add_to = nullptr);
     int commDestroy();
     int peerHandle(uint8_t *out);
     int attachPeers(const uint8_t *handles, int ranks, int rank);

@@ -181,6 +181,7 @@ struct PushParams {
     uint32_t *seq;                      // local: sequence number, finished blocks, sticky failure
     uint32_t *status;
     unsigned long long wait_ns;         // how long a rank polls for its peers' words before it gives up
+    float *add_to;                      // not null: the sums are added to this vector (a residual) instead of replacing `buf`
 };
 int launch_push_allreduce(cudaStream_t s, const PushParams &p);
 // The second half alone: the vector was already pushed (by the GEMV that produced it) into every inbox, this rank's included.

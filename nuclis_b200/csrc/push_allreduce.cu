@@ -118,8 +118,14 @@ __global__ void __launch_bounds__(256) push_allreduce_kernel(PushParams p) {
             else { s0 += a; s1 += b; }
         }
         if (!failed) {
-            p.buf[2 * i] = s0;
-            if (both) p.buf[2 * i + 1] = s1;
+            if (p.add_to) {
+                // the residual add behind the projection whose outputs were summed: every rank adds the same sum to the same residual
+                p.add_to[2 * i] += s0;
+                if (both) p.add_to[2 * i + 1] += s1;
+            } else {
+                p.buf[2 * i] = s0;
+                if (both) p.buf[2 * i + 1] = s1;
+            }
         }
     }
     if (__syncthreads_or(failed)) {

@@ -110,18 +110,27 @@ class Stack:
         self.norm_ffn.write(self.norm_ffn_host)
         self.residual.write(self.residual0)
 
-    def record_with_norms(self) -> int:
-        """One token, one GPU: x += O(Q(norm(x))); x += down(silu(gate(norm(x))) * up(norm(x))) per layer, the norms folded
-        into the staging passes of QKV and of the gate/up pair, the adds into the writes of O and down."""
-        b = self.backend
+    def record_with_norms(self, reduce: bool = False) -> int:
+        """One token: x += O(Q(norm(x))); x += down(silu(gate(norm(x))) * up(norm(x))) per layer, the norms folded into the
+        staging passes of QKV and of the gate/up pair, the adds into the writes of O and down; with the layer split over
+        ranks (``reduce``) the adds are folded into the gathers of the two sums instead."""
+        b, hidden = self.backend, self.shapes.hidden
         a_in = self.qkv.slice(0, self.qkv.len)
         for w in self.layers:
             b.matvec_segments_normed([Segment(w.qkv, self.m_qkv, self.qkv)], self.residual, self.norm_attn)
-            b.matvec_add(w.o, self.m_o, a_in, self.residual, self.residual)
+            if reduce:
+                b.matvec(w.o, self.m_o, a_in, self.o)
+                b.allreduce_sum_add_f32(self.o, self.residual, hidden)
+            else:
+                b.matvec_add(w.o, self.m_o, a_in, self.residual, self.residual)
             b.matvec_segments_normed([Segment(w.gate, self.m_gate, self.g), Segment(w.up, self.m_gate, self.g)], self.residual, self.norm_ffn,
                                      mode=SegmentMode.silu_mul_pair)
-            b.matvec_add(w.down, self.m_down, self.g, self.residual, self.residual)
-        return 4 * len(self.layers)
+            if reduce:
+                b.matvec(w.down, self.m_down, self.g, self.d)
+                b.allreduce_sum_add_f32(self.d, self.residual, hidden)
+            else:
+                b.matvec_add(w.down, self.m_down, self.g, self.residual, self.residual)
+        return (6 if reduce else 4) * len(self.layers)
 
     def record(self, allreduce: bool | None = None) -> int:
         """Records every layer's chain into the open recording; returns how many operators it recorded."""
@@ -129,8 +138,8 @@ class Stack:
         reduce = l.ranks > 1 if allreduce is None else allreduce
         ops = 0
         a_in = self.qkv.slice(0, self.qkv.len)  # the Q slice: the first q_rows floats of each token row
-        if getattr(self, "residual", None) is not None and m == 1 and not reduce:
-            return self.record_with_norms()
+        if getattr(self, "residual", None) is not None and m == 1:
+            return self.record_with_norms(reduce)
         for w in self.layers:
             if m == 1:
                 b.matvec(w.qkv, self.m_qkv, self.h, self.qkv)

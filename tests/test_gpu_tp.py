@@ -1,5 +1,6 @@
 """The row-split layer stack on two GPUs against the CPU oracle: the peer-memory allreduce and the
-NCCL allreduce both reproduce the unsharded chain. Needs two GPUs; skipped on a one-GPU box (the
+NCCL allreduce both reproduce the unsharded chain, also with the residual adds folded into the sums and the RMS norm
+into the gate/up pair. Needs two GPUs; skipped on a one-GPU box (the
 host-side logic of the split is covered on the CPU by tests/test_shard.py)."""
 import os
 import subprocess
@@ -74,7 +75,31 @@ t = torch.from_numpy(got.view(np.int32).astype(np.int64)); lo = t.clone(); hi = 
 dist.all_reduce(lo, op=dist.ReduceOp.MIN); dist.all_reduce(hi, op=dist.ReduceOp.MAX)
 assert torch.equal(lo, hi), "ranks disagree"
 dist.barrier()
-if rank == 0: print("TP-GPU-OK", err)
+# the same layer as a pre-norm decoder runs it: the residual adds in the gathers of the two sums, the RMS norm in the
+# staging pass of the gate/up pair; executed once (the residual accumulates)
+rng = np.random.default_rng(11)
+r0 = (rng.standard_normal(shapes.hidden) * 0.5).astype(np.float32)
+wn = (1.0 + 0.1 * rng.standard_normal(shapes.hidden)).astype(np.float32)
+res, wnb = upload(r0), upload(wn)
+b.begin()
+b.matvec(wo_l, m_o, a_l, o)
+b.allreduce_sum_add_f32(o, res, shapes.hidden)
+b.matvec_segments_normed([Segment(wg_l, m_g, g), Segment(wu_l, m_g, g)], res, wnb, mode=SegmentMode.silu_mul_pair)
+b.matvec(wd_l, m_d, g, d)
+b.allreduce_sum_add_f32(d, res, shapes.hidden)
+b.commit()
+got2 = res.floats()[: shapes.hidden]
+x1 = r0 + o_ref
+xn = (oracle.rms_norm(x1).astype(np.float64) * wn).astype(np.float32)
+act2 = (oracle.silu(oracle.matvec(enc.Q4_K, shapes.ffn, shapes.hidden, wg, xn)) * oracle.matvec(enc.Q4_K, shapes.ffn, shapes.hidden, wu, xn)).astype(np.float32)
+x2 = x1 + oracle.matvec(enc.Q6_K, shapes.hidden, shapes.ffn, wd, act2)
+err2 = np.linalg.norm(got2 - x2) / np.linalg.norm(x2)
+assert err2 < 2e-5, err2
+t = torch.from_numpy(got2.view(np.int32).astype(np.int64)); lo = t.clone(); hi = t.clone()
+dist.all_reduce(lo, op=dist.ReduceOp.MIN); dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+assert torch.equal(lo, hi), "ranks disagree on the residual"
+dist.barrier()
+if rank == 0: print("TP-GPU-OK", err, err2)
 b.comm_destroy(); dist.destroy_process_group(); b.deinit()
 '''
 
