@@ -287,6 +287,20 @@ def test_prepared_form_decodes_bit_for_bit(backend, golden_rows, encoding):
 
 
 @pytest.mark.parametrize("encoding", PREPARED)
+def test_prepare_writes_the_bytes_of_the_host_mirror(backend, encoding):
+    # the device's re-layout against nuclis_b200.planar (numpy): the same bytes, so a loader may re-lay on either side
+    from nuclis_b200 import planar
+    rows, columns = 48, 1280
+    w, _, m = make_case(encoding, rows, columns, 1, seed=123)
+    wb = backend.wrap(w)
+    pb, pm = backend.prepare(wb, m)
+    want, layout = planar.relay(encoding, w, rows, columns)
+    assert pm.layout == layout and np.array_equal(pb.read(), want)
+    backend.unwrap(w)
+    backend.release(pb)
+
+
+@pytest.mark.parametrize("encoding", PREPARED)
 @pytest.mark.parametrize("shape", [(80, 1280), (4096, 4096), (17408, 5120), (5120, 17408)])
 @pytest.mark.parametrize("generic", [False, True])
 def test_prepared_matvec_matches_oracle(backend, encoding, shape, generic):
