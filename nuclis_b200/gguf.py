@@ -242,10 +242,18 @@ class View:
         data = self.bytes(tensor)
         return ExpertMatrix(tensor.encoding_id, tensor.dimensions[2], tensor.dimensions[1], tensor.dimensions[0], data.size), data
 
-    def upload(self, backend: Backend, tensor: Tensor, prepare: bool = True) -> tuple[Buffer, Matrix]:
+    def upload(self, backend: Backend, tensor: Tensor, prepare: bool | str = True) -> tuple[Buffer, Matrix]:
         """Wraps a 2-D tensor into device memory (uploaded once, cached by address, as `Backend.wrap` does) and, for
-        the encodings whose GGUF rows the specialized kernels cannot address (Q6_K, Q8_0, Q5_0, Q5_1, Q4_0, IQ4_NL, IQ4_XS, Q2_K, Q3_K), re-lays it planar."""
+        the encodings whose GGUF rows the specialized kernels cannot address (Q6_K, Q8_0, Q5_0, Q5_1, Q4_0, IQ4_NL, IQ4_XS, Q2_K, Q3_K), re-lays it planar.
+        ``prepare="host"`` re-lays on the host instead (`planar.relay`: the same bytes) and uploads the result: the device
+        then never holds the tensor twice, which matters for a model that fills the memory."""
         m, data = self.matrix(tensor)
+        if prepare == "host":
+            from . import planar
+            laid, layout = planar.relay(m.encoding, data, m.rows, m.columns)
+            buf = backend.create(laid.size)
+            buf.write(laid)
+            return buf, Matrix(m.encoding, m.rows, m.columns, m.bytes, layout)
         buf = backend.wrap(data)
         if prepare and m.encoding in (enc.Q6_K, enc.Q8_0, enc.Q5_0, enc.Q5_1, enc.Q4_0, enc.IQ4_NL, enc.IQ4_XS, enc.Q2_K, enc.Q3_K) and m.rows % 16 == 0 and m.columns % 256 == 0:
             planar, m = backend.prepare(buf, m)

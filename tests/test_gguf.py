@@ -122,6 +122,14 @@ def test_a_written_file_drives_the_kernels(tmp_path):
             want = oracle.matvec(t.encoding_id, rows, columns, data, x)
             mag = oracle.matvec_abs(t.encoding_id, rows, columns, data, x)
             assert_matvec_close(yb.floats(), want, mag, t.name)
+            # re-laid on the host instead: the same bytes on the device, the same result
+            hb, hm = view.upload(b, t, prepare="host")
+            assert hm.layout == m.layout and np.array_equal(hb.read(), wb.read())
+            y2 = b.create(rows * 4)
+            b.begin()
+            b.matvec(hb, hm, xb, y2)
+            b.commit()
+            assert np.array_equal(y2.floats().view(np.uint32), yb.floats().view(np.uint32))
 
 
 @pytest.mark.gpu
