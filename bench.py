@@ -741,7 +741,7 @@ def main():
     ap.add_argument("--chain", action="store_true", help="runs of matvecs as one persistent kernel each instead of kernels of their own (measured slower; off by default)")
     ap.add_argument("--nccl-only", action="store_true", help="sum the short vectors with NCCL instead of the peer-memory allreduce")
     ap.add_argument("--workload", default="stack", choices=["stack", "gemv", "prefill", "experts"])
-    ap.add_argument("--encoding", type=int, default=12, help="GGUF type id of the matrix of --workload gemv / prefill (12 Q4_K, 14 Q6_K, 8 Q8_0)")
+    ap.add_argument("--encoding", type=int, default=12, help="GGUF type id of the matrix of --workload gemv / prefill (12 Q4_K, 13 Q5_K, 14 Q6_K, 8 Q8_0, 2 Q4_0, 6 Q5_0, 7 Q5_1, 10 Q2_K, 11 Q3_K, 20 IQ4_NL, 23 IQ4_XS)")
     ap.add_argument("--rows", type=int, default=17408)
     ap.add_argument("--columns", type=int, default=5120)
     ap.add_argument("--min-bytes", type=float, default=3.2e8, help="distinct weight bytes cycled by --workload gemv")
