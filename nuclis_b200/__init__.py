@@ -4,6 +4,7 @@ The product is ``libnuclis_cuda.so`` (CUDA kernels behind the C ABI of
 ``include/nuclis_cuda.h``). This package is the Python host side: a ctypes
 mirror of the engine's ``metal.Backend`` operator interface (``Backend``,
 ``Buffer``, ``Matrix``), seeded generators of synthetic GGUF blocks, the
+GGUF reader, the host-side mirror of the load-time re-layout (``planar``), the
 tensor-parallel shard tables and the synthetic decode layer stack.
 
 There is no CPU fallback: importing works anywhere, but creating a
