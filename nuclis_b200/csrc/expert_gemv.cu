@@ -355,22 +355,6 @@ __global__ void __launch_bounds__(X8_WARPS * 32) expert_gemv_q8_0_kernel(const u
 // block's 32 inputs, prepared once with the digits.
 enum NibbleKind : int { NK_Q5_0 = 0, NK_Q5_1 = 1, NK_Q4_0 = 2, NK_IQ4_NL = 3 };
 
-// Four bits of x into bit 4 of four bytes: bit i of x lands on bit 8 i of x * 0x00204081 (no two terms meet).
-__device__ __forceinline__ uint32_t bits_to_bit4(uint32_t x) { return ((x * 0x00204081u) & 0x01010101u) << 4; }
-__device__ __forceinline__ uint32_t prmt_b32(uint32_t a, uint32_t b, uint32_t sel) {
-    uint32_t d;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
-    return d;
-}
-// The IQ4_NL values of the four nibbles in the low 16 bits of n, as bytes in nibble order (the permute's sign-replicating
-// mode on n and n << 4 makes the mask that picks between the two halves of the table).
-__device__ __forceinline__ uint32_t iq4_bytes(uint32_t n) {
-    const uint32_t sel = n & 0x7777u;
-    const uint32_t lo = prmt_b32(0xbfad9881u, 0xf6eaddcfu, sel), hi = prmt_b32(0x26190d01u, 0x71594535u, sel);
-    const uint32_t upper = prmt_b32(n, n << 4, 0x9d8cu);
-    return (lo & ~upper) | (hi & upper);
-}
-
 template <int KIND>
 __global__ void __launch_bounds__(X8_WARPS * 32) expert_gemv_nibble_kernel(const uint8_t *w, size_t stride, size_t expert_bytes, uint32_t experts, uint32_t rows,
                                                                            uint32_t blocks, const uint32_t *indices, const float *in, size_t in_stride,
@@ -449,15 +433,15 @@ __global__ void __launch_bounds__(X8_WARPS * 32) expert_gemv_nibble_kernel(const
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 if (KIND == NK_IQ4_NL) {
-                    const uint32_t a = iq4_bytes(qs[i]), c = iq4_bytes(qs[i] >> 16);  // (lo0, hi0, lo1, hi1), (lo2, hi2, lo3, hi3)
+                    const uint32_t a = iq4_lookup4(qs[i]), c = iq4_lookup4(qs[i] >> 16);  // (lo0, hi0, lo1, hi1), (lo2, hi2, lo3, hi3)
                     lo[i] = prmt_b32(a, c, 0x6420u);
                     hi[i] = prmt_b32(a, c, 0x7531u);
                 } else {
                     lo[i] = qs[i] & 0x0f0f0f0fu;
                     hi[i] = (qs[i] >> 4) & 0x0f0f0f0fu;
                     if (FIFTH) {
-                        lo[i] |= bits_to_bit4((high >> (4 * i)) & 15u);
-                        hi[i] |= bits_to_bit4((high >> (16 + 4 * i)) & 15u);
+                        lo[i] |= bits4_to_bit4((high >> (4 * i)) & 15u);
+                        hi[i] |= bits4_to_bit4((high >> (16 + 4 * i)) & 15u);
                     }
                 }
             }

@@ -8,26 +8,6 @@
 namespace nu {
 namespace i8 {
 
-// Four bits of x into bit 4 of four bytes: bit i of x lands on bit 8 i of x * 0x00204081 (no two terms meet).
-__device__ __forceinline__ uint32_t spread4(uint32_t x) { return ((x * 0x00204081u) & 0x01010101u) << 4; }
-
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-    uint32_t d;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
-    return d;
-}
-
-// The IQ4_NL values (inference/src/quant/decode.zig:437) of the four codes in the low 16 bits of n, one per nibble, as
-// bytes in nibble order. The permute takes a nibble's low three bits as a byte index into eight table entries; the
-// entries 8..15 come from a second permute, and a third (in its sign-replicating mode, on n and n << 4, whose bytes
-// have the nibbles' top bits as their signs) makes the byte mask that picks between the two.
-__device__ __forceinline__ uint32_t iq4_lookup(uint32_t n) {
-    const uint32_t sel = n & 0x7777u;
-    const uint32_t lo = prmt(0xbfad9881u, 0xf6eaddcfu, sel), hi = prmt(0x26190d01u, 0x71594535u, sel);
-    const uint32_t upper = prmt(n, n << 4, 0x9d8cu);
-    return (lo & ~upper) | (hi & upper);
-}
-
 // The eight six-bit scales of an IQ4_XS superblock row (decode.zig:214-228: block g has four bits in nibble g of the
 // header's second word and two bits at 2g of the first word's upper half) as bytes: blocks 0, 2, 4, 6 in even,
 // 1, 3, 5, 7 in odd.
@@ -106,19 +86,19 @@ struct Block32 {
             const uint32_t n0 = *(const uint32_t *)(r0 + c * 16 + t * 4), n1 = *(const uint32_t *)(r1 + c * 16 + t * 4);
             uint32_t a[4];
             if (TABLE) {
-                a[0] = iq4_lookup(n0), a[1] = iq4_lookup(n1), a[2] = iq4_lookup(n0 >> 16), a[3] = iq4_lookup(n1 >> 16);
+                a[0] = iq4_lookup4(n0), a[1] = iq4_lookup4(n1), a[2] = iq4_lookup4(n0 >> 16), a[3] = iq4_lookup4(n1 >> 16);
             } else {
                 a[0] = n0 & 0x0f0f0f0fu, a[1] = n1 & 0x0f0f0f0fu, a[2] = (n0 >> 4) & 0x0f0f0f0fu, a[3] = (n1 >> 4) & 0x0f0f0f0fu;
             }
             if (FIFTH) {
                 const uint32_t h0 = *(const uint32_t *)(r0 + 128 + c * 4) >> (4 * t), h1 = *(const uint32_t *)(r1 + 128 + c * 4) >> (4 * t);
-                a[0] |= spread4(h0 & 15u), a[1] |= spread4(h1 & 15u), a[2] |= spread4((h0 >> 16) & 15u), a[3] |= spread4((h1 >> 16) & 15u);
+                a[0] |= bits4_to_bit4(h0 & 15u), a[1] |= bits4_to_bit4(h1 & 15u), a[2] |= bits4_to_bit4((h0 >> 16) & 15u), a[3] |= bits4_to_bit4((h1 >> 16) & 15u);
             }
             float d0, d1;
             if (SUPER) {
                 // byte c / 2 of the even or odd scales as a float through the 2^23 magic number, minus 32
-                d0 = __uint_as_float(prmt((c & 1) ? so0 : se0, 0x4b000000u, 0x7650u + c / 2)) - 8388640.0f;
-                d1 = __uint_as_float(prmt((c & 1) ? so1 : se1, 0x4b000000u, 0x7650u + c / 2)) - 8388640.0f;
+                d0 = __uint_as_float(prmt_b32((c & 1) ? so0 : se0, 0x4b000000u, 0x7650u + c / 2)) - 8388640.0f;
+                d1 = __uint_as_float(prmt_b32((c & 1) ? so1 : se1, 0x4b000000u, 0x7650u + c / 2)) - 8388640.0f;
             } else {
                 d0 = __half2float(*(const __half *)(sc0 + c * 2)), d1 = __half2float(*(const __half *)(sc1 + c * 2));
             }
@@ -126,7 +106,7 @@ struct Block32 {
             for (int j = 0; j < NC; ++j) {
                 const uint32_t b0 = *(const uint32_t *)(xb + j * bstep + c * 32), b1 = *(const uint32_t *)(xb + j * bstep + c * 32 + 16);
                 int s[4];
-                if (TABLE) imma_s8(s, a, prmt(b0, b1, 0x5140u), prmt(b0, b1, 0x7362u));
+                if (TABLE) imma_s8(s, a, prmt_b32(b0, b1, 0x5140u), prmt_b32(b0, b1, 0x7362u));
                 else imma_u8(s, a, b0, b1);
 #pragma unroll
                 for (int i = 0; i < 4; i += STEP) f[j][i] = fmaf((float)s[i], i < 2 ? d0 : d1, f[j][i]);

@@ -46,6 +46,25 @@ __device__ __forceinline__ int iq4_value(uint32_t code) {
     return (int)(int8_t)(w >> ((code & 3u) * 8));
 }
 
+// ---- packed forms of the same lookups, for the kernels that keep four codes in a word ----
+__device__ __forceinline__ uint32_t prmt_b32(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+// The IQ4 values of the four nibbles in the low 16 bits of n, as signed bytes in nibble order. A permute takes a nibble's
+// low three bits as a byte index into eight table entries; the entries 8..15 come from a second permute, and a third (in
+// its sign-replicating mode, on n and n << 4, whose bytes have the nibbles' top bits as their signs) makes the byte mask
+// that picks between the two.
+__device__ __forceinline__ uint32_t iq4_lookup4(uint32_t n) {
+    const uint32_t sel = n & 0x7777u;
+    const uint32_t lo = prmt_b32(0xbfad9881u, 0xf6eaddcfu, sel), hi = prmt_b32(0x26190d01u, 0x71594535u, sel);
+    const uint32_t upper = prmt_b32(n, n << 4, 0x9d8cu);
+    return (lo & ~upper) | (hi & upper);
+}
+// Four bits of x into bit 4 of four bytes: bit i of x lands on bit 8 i of x * 0x00204081 (no two terms meet).
+__device__ __forceinline__ uint32_t bits4_to_bit4(uint32_t x) { return ((x * 0x00204081u) & 0x01010101u) << 4; }
+
 // Decodes the 16 consecutive values [16*seg, 16*seg+16) of one row.
 // Products and the subtraction are separate IEEE operations (no contraction),
 // as in the reference: (d*s)*q - (dmin*m) for Q4_K, (d*scale)*q for Q6_K.

@@ -152,20 +152,6 @@ __device__ __forceinline__ void codes4_fma(uint32_t t4, float mul, float add, ui
     hi = pack_bf16(fmaf(byte_f32(t4, 2), mul, add), fmaf(byte_f32(t4, 3), mul, add));
 }
 __device__ __forceinline__ uint4 ldg16(const uint8_t *ptr) { return __ldg((const uint4 *)ptr); }
-// Four bits of x into bit 4 of four bytes: bit i of x lands on bit 8 i of x * 0x00204081 (no two terms meet).
-__device__ __forceinline__ uint32_t bits4_to_bit4(uint32_t x) { return ((x * 0x00204081u) & 0x01010101u) << 4; }
-// The IQ4_NL values (inference/src/quant/decode.zig:437) of the four nibbles in the low 16 bits of n, as bytes in nibble
-// order: a permute takes a nibble's low three bits as an index into eight table bytes, a second one reads the other
-// eight, a third (sign-replicating, on n and n << 4, whose bytes carry the nibbles' top bits as signs) picks between them.
-__device__ __forceinline__ uint32_t iq4_lookup4(uint32_t n) {
-    uint32_t lo, hi, upper;
-    const uint32_t sel = n & 0x7777u;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(lo) : "r"(0xbfad9881u), "r"(0xf6eaddcfu), "r"(sel));
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(0x26190d01u), "r"(0x71594535u), "r"(sel));
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(upper) : "r"(n), "r"(n << 4), "r"(0x9d8cu));
-    return (lo & ~upper) | (hi & upper);
-}
-
 // MODE: 0 the generic decoders (any encoding and layout), 1 Q4_K with 16-byte aligned rows, 2 planar Q6_K, 3 planar Q8_0,
 // 4 GGUF Q8_0 rows, 5 Q5_K with 16-byte aligned rows, 6 the planar forms of Q5_0, Q5_1, Q4_0, IQ4_NL and IQ4_XS,
 // 7 the planar forms of Q2_K and Q3_K, 8 GGUF rows of Q5_0, Q5_1, Q4_0 and IQ4_NL.
